@@ -1,0 +1,1233 @@
+// Cache state machines. Every function here follows the bookkeeping of the
+// reference class it replaces (cited per function); the arithmetic and the row
+// movement run in the CUDA kernels of this library.
+#include "cache.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace kvc {
+
+int launch_attention(const AttnArgs &a, cudaStream_t stream);
+
+namespace {
+
+int64_t round_up(int64_t x, int64_t q) { return ((x + q - 1) / q) * q; }
+
+void require4(const kvc_tensor &t, const char *what) {
+    if (t.ndim != 4) fail(KVC_ERR_INVALID_ARG, std::string(what) + ": expected a 4-d tensor [B, H, S, D]");
+    if (!t.data && t.shape[0] * t.shape[1] * t.shape[2] * t.shape[3] != 0)
+        fail(KVC_ERR_INVALID_ARG, std::string(what) + ": null data pointer");
+    for (int i = 0; i < 4; ++i)
+        if (t.shape[i] < 0) fail(KVC_ERR_INVALID_ARG, std::string(what) + ": negative dimension");
+}
+
+void zero_rows(Array4 &a, int64_t first, int64_t count, cudaStream_t s) {
+    if (count <= 0 || !a.ptr) return;
+    const size_t pitch = (size_t)a.cap * a.W * a.esize();
+    KVC_CUDA(cudaMemset2DAsync((char *)a.ptr + (size_t)first * a.W * a.esize(), pitch, 0,
+                               (size_t)count * a.W * a.esize(), (size_t)(a.B * a.H), s));
+}
+
+void copy_rows(const Array4 &src, int64_t src_first, Array4 &dst, int64_t dst_first, int64_t count,
+               cudaStream_t s) {
+    if (count <= 0) return;
+    GatherArgs g;
+    g.src = src.ptr;
+    g.dst = dst.ptr;
+    g.s_sb = src.sb(); g.s_sh = src.sh(); g.s_st = src.st();
+    g.d_sb = dst.sb(); g.d_sh = dst.sh(); g.d_st = dst.st();
+    g.B = (int)src.B; g.H = (int)src.H; g.W = (int)src.W;
+    g.esize = (int)src.esize();
+    g.nseg = 1;
+    g.seg[0] = {src_first, count};
+    g.dst_start = dst_first;
+    launch_gather(g, s);
+}
+
+void gather_rows(const Array4 &src, Array4 &dst, const std::vector<GatherSeg> &segs, cudaStream_t s) {
+    if (segs.size() > 4) fail(KVC_ERR_INTERNAL, "ring re-order produced more than 4 segments");
+    GatherArgs g;
+    g.src = src.ptr;
+    g.dst = dst.ptr;
+    g.s_sb = src.sb(); g.s_sh = src.sh(); g.s_st = src.st();
+    g.d_sb = dst.sb(); g.d_sh = dst.sh(); g.d_st = dst.st();
+    g.B = (int)src.B; g.H = (int)src.H; g.W = (int)src.W;
+    g.esize = (int)src.esize();
+    g.nseg = (int)segs.size();
+    for (size_t i = 0; i < segs.size(); ++i) g.seg[i] = segs[i];
+    g.dst_start = 0;
+    launch_gather(g, s);
+}
+
+// Append the rows of `t` ([B, H, S, W], any strides) to `dst` at token `pos`.
+void append_pair(Array4 &kd, Array4 &vd, const kvc_tensor &k, const kvc_tensor &v, int64_t pos,
+                 cudaStream_t s) {
+    AppendArgs a;
+    a.k_src = k.data; a.v_src = v.data;
+    a.ks_sb = k.stride[0]; a.ks_sh = k.stride[1]; a.ks_ss = k.stride[2]; a.ks_sd = k.stride[3];
+    a.vs_sb = v.stride[0]; a.vs_sh = v.stride[1]; a.vs_ss = v.stride[2]; a.vs_sd = v.stride[3];
+    a.k_dst = kd.ptr; a.v_dst = vd.ptr;
+    a.kd_sb = kd.sb(); a.kd_sh = kd.sh(); a.kd_st = kd.st();
+    a.vd_sb = vd.sb(); a.vd_sh = vd.sh(); a.vd_st = vd.st();
+    a.B = (int)k.shape[0]; a.H = (int)k.shape[1]; a.S = (int)k.shape[2];
+    a.Dk = (int)k.shape[3]; a.Dv = (int)v.shape[3];
+    a.pos = pos;
+    a.esize = (int)dtype_size(k.dtype);
+    launch_append(a, s);
+}
+
+int64_t seg_total(const std::vector<GatherSeg> &v) {
+    int64_t n = 0;
+    for (auto &g : v) n += g.count;
+    return n;
+}
+
+void seg_push(std::vector<GatherSeg> &out, int64_t start, int64_t count) {
+    if (count <= 0) return;
+    if (!out.empty() && out.back().src_start + out.back().count == start) out.back().count += count;
+    else out.push_back({start, count});
+}
+
+// Sub-range [begin, end) of the sequence described by `in`.
+std::vector<GatherSeg> seg_slice(const std::vector<GatherSeg> &in, int64_t begin, int64_t end) {
+    std::vector<GatherSeg> out;
+    int64_t pos = 0;
+    for (auto &g : in) {
+        const int64_t lo = std::max(begin, pos), hi = std::min(end, pos + g.count);
+        if (hi > lo) seg_push(out, g.src_start + (lo - pos), hi - lo);
+        pos += g.count;
+    }
+    return out;
+}
+
+std::vector<GatherSeg> seg_concat(std::vector<GatherSeg> a, const std::vector<GatherSeg> &b) {
+    for (auto &g : b) seg_push(a, g.src_start, g.count);
+    return a;
+}
+
+// RotatingKVCache.temporalOrder (KVCache.swift:592-606) as a row mapping.
+std::vector<GatherSeg> rot_temporal(const kvc_cache *c) {
+    std::vector<GatherSeg> t;
+    if (c->idx < 0) fail(KVC_ERR_INVALID_STATE, "rotating cache: ring index is negative (trim past the ring start)");
+    if (c->idx == c->len) {
+        seg_push(t, 0, c->len);
+    } else if (c->idx < c->offset) {
+        const int64_t k0 = std::min<int64_t>(c->cfg.keep, c->len);
+        const int64_t id = std::min(c->idx, c->len);
+        seg_push(t, 0, k0);
+        seg_push(t, id, c->len - id);
+        seg_push(t, std::min<int64_t>(c->cfg.keep, id), id - std::min<int64_t>(c->cfg.keep, id));
+    } else {
+        seg_push(t, 0, std::min(c->idx, c->len));
+    }
+    return t;
+}
+
+// RotatingKVCache.trim(trimSize:_:) (KVCache.swift:576-590) applied to a sequence.
+std::vector<GatherSeg> rot_front_trim(const std::vector<GatherSeg> &seq, int64_t trim_size, int64_t keep) {
+    if (trim_size <= 0) return seq;
+    const int64_t n = seg_total(seq);
+    auto head = seg_slice(seq, 0, std::min(keep, n));
+    auto tail = seg_slice(seq, std::min(trim_size + keep, n), n);
+    return seg_concat(head, tail);
+}
+
+void ensure_like(Array4 &dst, const Array4 &like, int64_t need_cap, cudaStream_t s) {
+    if (dst.allocated() && dst.cap >= need_cap && dst.B == like.B && dst.H == like.H &&
+        dst.W == like.W && dst.dtype == like.dtype)
+        return;
+    dst.release(s);
+    dst.alloc(like.B, like.H, need_cap, like.W, like.dtype, s);
+}
+
+// Replace the ring contents by the rows `segs` selects (in that order).
+void rot_rebuild(kvc_cache *c, const std::vector<GatherSeg> &segs, int64_t extra_cap, cudaStream_t s) {
+    const int64_t n = seg_total(segs);
+    const int64_t need = std::max<int64_t>(std::max<int64_t>(n + extra_cap, c->cfg.max_size), c->k.cap);
+    ensure_like(c->k_alt, c->k, need, s);
+    ensure_like(c->v_alt, c->v, need, s);
+    gather_rows(c->k, c->k_alt, segs, s);
+    gather_rows(c->v, c->v_alt, segs, s);
+    std::swap(c->k, c->k_alt);
+    std::swap(c->v, c->v_alt);
+    c->len = n;
+}
+
+void check_new_rows(const kvc_cache *c, const Array4 &ka, const Array4 &va, const kvc_tensor &k,
+                    const kvc_tensor &v) {
+    if (!ka.allocated()) return;
+    if (k.shape[0] != ka.B || k.shape[1] != ka.H)
+        fail(KVC_ERR_INVALID_ARG, "update: batch / head count differs from the cached arrays");
+    (void)c; (void)va; (void)v;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------
+// Array4
+// ---------------------------------------------------------------------
+void Array4::alloc(int64_t b, int64_t h, int64_t c, int64_t w, int32_t dt, cudaStream_t s) {
+    B = b; H = h; cap = std::max<int64_t>(c, 1); W = w; dtype = dt;
+    ptr = dev_alloc(bytes(), s);
+    KVC_CUDA(cudaMemsetAsync(ptr, 0, bytes(), s));
+}
+
+void Array4::release(cudaStream_t s) {
+    if (ptr) dev_free(ptr, s);
+    ptr = nullptr;
+    cap = 0;
+}
+
+void Array4::ensure(int64_t need, int64_t keep_rows, int64_t step, cudaStream_t s) {
+    if (!ptr) fail(KVC_ERR_INTERNAL, "Array4::ensure on an unallocated array");
+    if (need <= cap) return;
+    step = std::max<int64_t>(step, 1);
+    const int64_t grown = round_up(cap + cap / 2, step);
+    const int64_t new_cap = std::max(round_up(need, step), grown);
+    Array4 next;
+    next.alloc(B, H, new_cap, W, dtype, s);
+    copy_rows(*this, 0, next, 0, std::min(keep_rows, cap), s);
+    dev_free(ptr, s);
+    *this = next;
+}
+
+kvc_tensor Array4::view(int64_t tokens, int64_t first) const {
+    kvc_tensor t{};
+    t.data = ptr ? (void *)((char *)ptr + (size_t)first * W * esize()) : nullptr;
+    t.dtype = dtype;
+    t.ndim = 4;
+    t.shape[0] = B; t.shape[1] = H; t.shape[2] = tokens; t.shape[3] = W;
+    t.stride[0] = sb(); t.stride[1] = sh(); t.stride[2] = st(); t.stride[3] = 1;
+    return t;
+}
+
+static kvc_tensor view3(const Array4 &a, int64_t tokens) {
+    kvc_tensor t = a.view(tokens);
+    t.ndim = 3;
+    t.shape[3] = 0;
+    t.stride[3] = 0;
+    return t;
+}
+
+}  // namespace kvc
+
+kvc_cache::~kvc_cache() {
+    cudaStream_t s = nullptr;
+    kvc::Array4 *arrays[] = {&k, &v, &k_alt, &v_alt, &k_view, &v_view, &kq, &ks, &kb, &vq, &vs, &vb,
+                             &kp, &kn, &vp, &vn, &restore.k, &restore.v, &restore.rk, &restore.rv};
+    for (auto *a : arrays) a->release(s);
+    for (int i = 0; i < 4; ++i)
+        if (stage[i]) kvc::dev_free(stage[i], s);
+    if (kcodec.signs_dev) kvc::dev_free(kcodec.signs_dev, s);
+    if (vcodec.signs_dev) kvc::dev_free(vcodec.signs_dev, s);
+}
+
+namespace kvc {
+
+int resolved_group_size(int requested, int kd, int vd) {
+    // resolvedKVQuantizationGroupSize (KVCache.swift:902-920): nearest of
+    // {32, 64, 128} dividing both head dims, ties to the smaller.
+    requested = std::max(1, requested);
+    int best = 0;
+    for (int g : {32, 64, 128}) {
+        if (kd % g || vd % g) continue;
+        if (!best) { best = g; continue; }
+        const int db = std::abs(best - requested), dg = std::abs(g - requested);
+        if (dg < db || (dg == db && g < best)) best = g;
+    }
+    return best;
+}
+
+// ---------------------------------------------------------------------
+// update
+// ---------------------------------------------------------------------
+
+// KVCacheSimple.update (KVCache.swift:404-447) and the raw prefill phase of
+// TurboQuantKVCache.update (TurboQuantKVCache.swift:802-846). Capacity grows
+// ahead of need, which the protocol surface cannot observe: every getter
+// exposes rows [0, offset) only.
+static void linear_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s) {
+    const int64_t S = k.shape[2];
+    const int64_t step = std::max<int32_t>(c->cfg.step, 1);
+    if (!c->k.allocated()) {
+        const int64_t cap = std::max<int64_t>(c->cfg.reserve_tokens, round_up(c->offset + std::max<int64_t>(S, 1), step));
+        c->k.alloc(k.shape[0], k.shape[1], cap, k.shape[3], k.dtype, s);
+        c->v.alloc(v.shape[0], v.shape[1], cap, v.shape[3], v.dtype, s);
+    } else {
+        KVC_REQUIRE(k.shape[0] == c->k.B && k.shape[1] == c->k.H && k.shape[3] == c->k.W &&
+                        v.shape[3] == c->v.W && k.dtype == c->k.dtype,
+                    "update: new keys/values do not match the cached shape or dtype");
+        c->k.ensure(c->offset + S, c->offset, step, s);
+        c->v.ensure(c->offset + S, c->offset, step, s);
+    }
+    if (S > 0) append_pair(c->k, c->v, k, v, c->offset, s);
+    c->offset += S;
+}
+
+// RotatingKVCache.updateInPlace (KVCache.swift:684-740), S == 1.
+static void rotating_update_in_place(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v,
+                                     cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov) {
+    const int64_t max_size = c->cfg.max_size, keep = c->cfg.keep;
+    const int64_t prev = c->offset;
+    if (!c->k.allocated() || (prev >= c->len && c->len < max_size)) {
+        const int64_t new_size = std::min<int64_t>(c->cfg.step, max_size - prev);
+        if (new_size <= 0)
+            fail(KVC_ERR_INVALID_STATE, "rotating cache: cannot grow (offset is past maxSize while the buffer is short)");
+        if (!c->k.allocated()) {
+            const int64_t cap = std::max<int64_t>(max_size, new_size);
+            c->k.alloc(k.shape[0], k.shape[1], cap, k.shape[3], k.dtype, s);
+            c->v.alloc(v.shape[0], v.shape[1], cap, v.shape[3], v.dtype, s);
+            c->len = 0;
+        } else {
+            c->k.ensure(c->len + new_size, c->len, c->cfg.step, s);
+            c->v.ensure(c->len + new_size, c->len, c->cfg.step, s);
+            zero_rows(c->k, c->len, new_size, s);
+            zero_rows(c->v, c->len, new_size, s);
+        }
+        c->len += new_size;
+        c->idx = prev;
+    }
+    KVC_REQUIRE(k.shape[0] == c->k.B && k.shape[1] == c->k.H && k.shape[3] == c->k.W &&
+                    v.shape[3] == c->v.W && k.dtype == c->k.dtype,
+                "update: new keys/values do not match the cached shape or dtype");
+    const int64_t trim_size = c->len - max_size;
+    if (trim_size > 0) {
+        std::vector<GatherSeg> all;
+        seg_push(all, 0, c->len);
+        rot_rebuild(c, rot_front_trim(all, trim_size, keep), 0, s);
+        c->idx = max_size;
+    }
+    if (c->idx == max_size) c->idx = keep;
+    if (c->idx < 0 || c->idx + 1 > c->len)
+        fail(KVC_ERR_INVALID_STATE, "rotating cache: ring index outside the buffer");
+    append_pair(c->k, c->v, k, v, c->idx, s);
+    c->offset += 1;
+    c->idx += 1;
+    const int64_t rows = c->offset < max_size ? std::min(c->offset, c->len) : c->len;
+    if (ok) *ok = c->k.view(rows);
+    if (ov) *ov = c->v.view(rows);
+}
+
+// RotatingKVCache.updateConcat (KVCache.swift:660-682), S > 1.
+static void rotating_update_concat(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v,
+                                   cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov) {
+    const int64_t S = k.shape[2];
+    const int64_t max_size = c->cfg.max_size, keep = c->cfg.keep;
+    if (!c->k.allocated()) {
+        const int64_t cap = std::max<int64_t>(S, max_size);
+        c->k.alloc(k.shape[0], k.shape[1], cap, k.shape[3], k.dtype, s);
+        c->v.alloc(v.shape[0], v.shape[1], cap, v.shape[3], v.dtype, s);
+        append_pair(c->k, c->v, k, v, 0, s);
+        c->len = S;
+    } else {
+        KVC_REQUIRE(k.shape[0] == c->k.B && k.shape[1] == c->k.H && k.shape[3] == c->k.W &&
+                        v.shape[3] == c->v.W && k.dtype == c->k.dtype,
+                    "update: new keys/values do not match the cached shape or dtype");
+        auto ordered = rot_temporal(c);
+        c->idx = seg_total(ordered);
+        const int64_t trim_size = c->idx - max_size + 1;
+        auto segs = rot_front_trim(ordered, trim_size, keep);
+        const int64_t n = seg_total(segs);
+        if (segs.size() == 1 && segs[0].src_start == 0) {
+            c->len = n;  // already in place: a prefix of the buffer
+            c->k.ensure(n + S, n, c->cfg.step, s);
+            c->v.ensure(n + S, n, c->cfg.step, s);
+        } else {
+            rot_rebuild(c, segs, S, s);
+        }
+        append_pair(c->k, c->v, k, v, n, s);
+        c->len = n + S;
+    }
+    c->offset += S;
+    c->idx = c->len;
+    if (ok) *ok = c->k.view(c->len);
+    if (ov) *ov = c->v.view(c->len);
+}
+
+void cache_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
+                  kvc_tensor *out_k, kvc_tensor *out_v) {
+    require4(k, "keys");
+    require4(v, "values");
+    KVC_REQUIRE(is_float_dtype(k.dtype) && k.dtype == v.dtype, "update: keys/values must share a floating dtype");
+    KVC_REQUIRE(k.shape[0] == v.shape[0] && k.shape[1] == v.shape[1] && k.shape[2] == v.shape[2],
+                "update: keys and values disagree on batch, heads or length");
+    if (c->open_round) fail(KVC_ERR_INVALID_STATE, "update: a staged round is open on this cache");
+    c->restore.valid = false;
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE:
+            linear_update(c, k, v, s);
+            if (out_k) *out_k = c->k.view(c->offset);
+            if (out_v) *out_v = c->v.view(c->offset);
+            return;
+        case KVC_KIND_TURBO:
+            if (c->compressed)
+                fail(KVC_ERR_INVALID_STATE, "update: the raw path is gone once a TurboQuant cache is compressed; use attention");
+            linear_update(c, k, v, s);
+            if (out_k) *out_k = c->k.view(c->offset);
+            if (out_v) *out_v = c->v.view(c->offset);
+            return;
+        case KVC_KIND_ROTATING:
+            check_new_rows(c, c->k, c->v, k, v);
+            if (k.shape[2] == 1) rotating_update_in_place(c, k, v, s, out_k, out_v);
+            else rotating_update_concat(c, k, v, s, out_k, out_v);
+            return;
+        case KVC_KIND_QUANTIZED:
+            // KVCache.swift:1106-1110
+            fail(KVC_ERR_INVALID_STATE, "`update` was called on `QuantizedKVCache`. Use `updateQuantized` instead.");
+        default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
+    }
+}
+
+// ---------------------------------------------------------------------
+// QuantizedKVCache.updateQuantized (KVCache.swift:1011-1102)
+// ---------------------------------------------------------------------
+static QuantAppendArgs quant_args(const kvc_tensor &x, Array4 &codes, Array4 &scales, Array4 &biases,
+                                  int group, int bits, int64_t pos) {
+    QuantAppendArgs a;
+    a.src = x.data; a.dtype = x.dtype;
+    a.s_sb = x.stride[0]; a.s_sh = x.stride[1]; a.s_ss = x.stride[2]; a.s_sd = x.stride[3];
+    a.codes = (uint32_t *)codes.ptr;
+    a.scales = scales.ptr; a.biases = biases.ptr;
+    a.c_sb = codes.sb(); a.c_sh = codes.sh(); a.c_st = codes.st();
+    a.g_sb = scales.sb(); a.g_sh = scales.sh(); a.g_st = scales.st();
+    a.B = (int)x.shape[0]; a.H = (int)x.shape[1]; a.S = (int)x.shape[2]; a.D = (int)x.shape[3];
+    a.group = group; a.bits = bits; a.pos = pos;
+    return a;
+}
+
+static void quant_triple_alloc(Array4 &q, Array4 &sc, Array4 &bi, int64_t B, int64_t H, int64_t cap,
+                               int D, int group, int bits, int32_t dtype, cudaStream_t s) {
+    q.alloc(B, H, cap, (int64_t)D * bits / 32, KVC_U32, s);
+    sc.alloc(B, H, cap, D / group, dtype, s);
+    bi.alloc(B, H, cap, D / group, dtype, s);
+}
+
+void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
+                            kvc_tensor out_k[3], kvc_tensor out_v[3]) {
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_QUANTIZED, "updateQuantized needs a QuantizedKVCache");
+    require4(k, "keys");
+    require4(v, "values");
+    KVC_REQUIRE(is_float_dtype(k.dtype) && k.dtype == v.dtype, "updateQuantized: keys/values must share a floating dtype");
+    KVC_REQUIRE(k.shape[0] == v.shape[0] && k.shape[1] == v.shape[1] && k.shape[2] == v.shape[2],
+                "updateQuantized: keys and values disagree on batch, heads or length");
+    const int kd = (int)k.shape[3], vd = (int)v.shape[3];
+    const int eff = resolved_group_size(c->group_size, kd, vd);
+    if (!eff)
+        fail(KVC_ERR_INVALID_ARG,
+             "KV cache quantization requires head dimensions divisible by one of the supported group sizes (32, 64, 128).");
+    if (eff != c->group_size && !c->kq.allocated() && c->offset == 0) c->group_size = eff;
+    KVC_REQUIRE(kd % c->group_size == 0 && vd % c->group_size == 0,
+                "updateQuantized: head dims are not multiples of the cache's group size");
+    const int64_t S = k.shape[2], prev = c->offset;
+    const int64_t step = std::max<int32_t>(c->cfg.step, 1);
+    if (!c->kq.allocated()) {
+        const int64_t cap = std::max<int64_t>(c->cfg.reserve_tokens, round_up(prev + std::max<int64_t>(S, 1), step));
+        quant_triple_alloc(c->kq, c->ks, c->kb, k.shape[0], k.shape[1], cap, kd, c->group_size, c->bits, k.dtype, s);
+        quant_triple_alloc(c->vq, c->vs, c->vb, v.shape[0], v.shape[1], cap, vd, c->group_size, c->bits, v.dtype, s);
+    } else {
+        KVC_REQUIRE(k.shape[0] == c->kq.B && k.shape[1] == c->kq.H &&
+                        (int64_t)kd * c->bits / 32 == c->kq.W && (int64_t)vd * c->bits / 32 == c->vq.W &&
+                        k.dtype == c->ks.dtype,
+                    "updateQuantized: new keys/values do not match the cached shape or dtype");
+        for (Array4 *a : {&c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb}) a->ensure(prev + S, prev, step, s);
+    }
+    if (S > 0) {
+        QuantAppendArgs qa = quant_args(k, c->kq, c->ks, c->kb, c->group_size, c->bits, prev);
+        QuantAppendArgs qv = quant_args(v, c->vq, c->vs, c->vb, c->group_size, c->bits, prev);
+        launch_affine_quantize2(qa, &qv, s);
+    }
+    c->offset = prev + S;
+    if (out_k) { out_k[0] = c->kq.view(c->offset); out_k[1] = c->ks.view(c->offset); out_k[2] = c->kb.view(c->offset); }
+    if (out_v) { out_v[0] = c->vq.view(c->offset); out_v[1] = c->vs.view(c->offset); out_v[2] = c->vb.view(c->offset); }
+}
+
+// ---------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------
+KVSource raw_source(const kvc_tensor &t) {
+    KVSource s;
+    s.kind = SRC_RAW;
+    s.dtype = t.dtype;
+    s.data = t.data;
+    s.sb = t.stride[0]; s.sh = t.stride[1]; s.st = t.stride[2];
+    return s;
+}
+
+static KVSource affine_source(const kvc_tensor &w, const kvc_tensor &sc, const kvc_tensor &bi, int group, int bits) {
+    KVSource s;
+    s.kind = SRC_AFFINE;
+    s.dtype = sc.dtype;
+    s.data = w.data; s.scales = sc.data; s.biases = bi.data;
+    s.sb = w.stride[0]; s.sh = w.stride[1]; s.st = w.stride[2];
+    s.gsb = sc.stride[0]; s.gsh = sc.stride[1]; s.gst = sc.stride[2];
+    s.bits = bits; s.group = group; s.words = (int)w.shape[3];
+    return s;
+}
+
+static KVSource turbo_source(const Array4 &p, const Array4 &n, const TurboCodec &codec) {
+    KVSource s;
+    s.kind = SRC_TURBO;
+    s.data = p.ptr; s.norms = (const float *)n.ptr;
+    s.sb = p.sb(); s.sh = p.sh(); s.st = p.st();
+    s.gsb = n.sb(); s.gsh = n.sh(); s.gst = n.st();
+    s.bits = codec.bits; s.words = (int)p.W;
+    for (size_t i = 0; i < codec.centroids.size() && i < 16; ++i) s.codebook[i] = codec.centroids[i];
+    return s;
+}
+
+AttnArgs make_attn_args(const kvc_tensor &q, const kvc_tensor &out, float scale, int32_t mask_mode,
+                        const kvc_tensor *mask, int64_t T, int Hkv) {
+    require4(q, "queries");
+    require4(out, "out");
+    KVC_REQUIRE(is_float_dtype(q.dtype) && out.dtype == q.dtype, "attention: output dtype must equal the query dtype");
+    KVC_REQUIRE(q.stride[3] == 1 && out.stride[3] == 1, "attention: queries/out must be contiguous along the head dim");
+    for (int i = 0; i < 4; ++i) KVC_REQUIRE(q.shape[i] == out.shape[i], "attention: out shape differs from queries");
+    AttnArgs a;
+    a.q = q.data; a.out = out.data; a.q_dtype = q.dtype;
+    a.q_sb = q.stride[0]; a.q_sh = q.stride[1]; a.q_sl = q.stride[2];
+    a.o_sb = out.stride[0]; a.o_sh = out.stride[1]; a.o_sl = out.stride[2];
+    a.B = (int)q.shape[0]; a.Hq = (int)q.shape[1]; a.L = (int)q.shape[2]; a.D = (int)q.shape[3];
+    a.Hkv = Hkv; a.T = T; a.scale = scale;
+    a.device = current_device();
+    a.mask.mode = mask_mode;
+    if (mask_mode == KVC_MASK_CAUSAL) {
+        a.mask.causal_offset = T - a.L;
+    } else if (mask_mode == KVC_MASK_ARRAY) {
+        KVC_REQUIRE(mask && mask->data, "attention: array mask mode needs a mask tensor");
+        KVC_REQUIRE(mask->ndim >= 1 && mask->ndim <= 4, "attention: mask must have 1..4 dims");
+        KVC_REQUIRE(mask->dtype == KVC_BOOL || is_float_dtype(mask->dtype), "attention: mask must be bool or floating");
+        a.mask.dtype = mask->dtype;
+        a.mask.data = mask->data;
+        const int64_t want[4] = {a.B, a.Hq, a.L, T};
+        int64_t st[4] = {0, 0, 0, 0};
+        for (int i = 0; i < mask->ndim; ++i) {
+            const int dst = 4 - mask->ndim + i;
+            if (mask->shape[i] == want[dst]) st[dst] = mask->stride[i];
+            else if (mask->shape[i] == 1) st[dst] = 0;
+            else fail(KVC_ERR_INVALID_ARG, "attention: mask is not broadcastable to [B, Hq, L, T]");
+        }
+        a.mask.sb = st[0]; a.mask.sh = st[1]; a.mask.sl = st[2]; a.mask.st = st[3];
+    } else if (mask_mode != KVC_MASK_NONE) {
+        fail(KVC_ERR_INVALID_ARG, "attention: unknown mask mode");
+    }
+    return a;
+}
+
+static void upload_signs(TurboCodec &codec, cudaStream_t s) {
+    if (codec.signs_dev) dev_free(codec.signs_dev, s);
+    codec.signs_dev = (float *)dev_alloc(codec.signs.size() * sizeof(float), s);
+    KVC_CUDA(cudaMemcpyAsync(codec.signs_dev, codec.signs.data(), codec.signs.size() * sizeof(float),
+                             cudaMemcpyHostToDevice, s));
+}
+
+void ensure_codecs(kvc_cache *c, int head_dim, cudaStream_t s) {
+    // TurboQuantKVCache.ensureCodecs (TurboQuantKVCache.swift:753-759): key codec
+    // seeded with `seed`, value codec with `seed + 1`.
+    if (c->codec_ready && c->vcodec.dim == head_dim) return;
+    KVC_REQUIRE(head_dim >= 32 && head_dim <= 1024 && (head_dim & (head_dim - 1)) == 0,
+                "TurboQuant: only the Walsh-Hadamard path (power-of-two head dim in [32, 1024]) is built");
+    auto build = [&](TurboCodec &codec, int bits, uint64_t seed, const std::vector<float> &uc,
+                     const std::vector<float> &us) {
+        codec.dim = head_dim;
+        codec.bits = bits;
+        if (!uc.empty()) {
+            KVC_REQUIRE((int)uc.size() == (1 << bits), "TurboQuant: codebook override has the wrong length");
+            codec.centroids = uc;
+            codec.boundaries.clear();
+            for (size_t i = 0; i + 1 < uc.size(); ++i) codec.boundaries.push_back((uc[i] + uc[i + 1]) / 2.0f);
+        } else {
+            turbo_codebook(head_dim, bits, codec.centroids, codec.boundaries);
+        }
+        if (!us.empty()) {
+            KVC_REQUIRE((int)us.size() == head_dim, "TurboQuant: sign override has the wrong length");
+            codec.signs = us;
+        } else {
+            turbo_signs(head_dim, seed, codec.signs);
+        }
+        upload_signs(codec, s);
+    };
+    if (!c->raw_key && !c->affine_key) build(c->kcodec, c->key_bits, c->cfg.seed, c->user_kc, c->user_ks);
+    if (!c->affine_value) build(c->vcodec, c->value_bits, c->cfg.seed + 1, c->user_vc, c->user_vs);
+    else c->vcodec.dim = head_dim;
+    c->codec_ready = true;
+}
+
+static TurboEncodeArgs turbo_args(const kvc_tensor &x, Array4 &packed, Array4 &norms,
+                                  const TurboCodec &codec, int64_t pos) {
+    TurboEncodeArgs a;
+    a.src = x.data; a.dtype = x.dtype;
+    a.s_sb = x.stride[0]; a.s_sh = x.stride[1]; a.s_ss = x.stride[2]; a.s_sd = x.stride[3];
+    a.packed = (uint32_t *)packed.ptr; a.norms = (float *)norms.ptr;
+    a.p_sb = packed.sb(); a.p_sh = packed.sh(); a.p_st = packed.st();
+    a.n_sb = norms.sb(); a.n_sh = norms.sh(); a.n_st = norms.st();
+    a.B = (int)x.shape[0]; a.H = (int)x.shape[1]; a.S = (int)x.shape[2]; a.D = (int)x.shape[3];
+    a.bits = codec.bits; a.pos = pos; a.signs = codec.signs_dev;
+    for (size_t i = 0; i < codec.boundaries.size() && i < 15; ++i) a.boundaries[i] = codec.boundaries[i];
+    return a;
+}
+
+static int turbo_pw(int count, int bits) { return (count * bits + 31) / 32; }
+
+// Encode S rows of K and V into the compressed arrays at token `pos`
+// (the kernel work of compressRawCacheInternal :924-1002 and encodeNewToken :1010-1147).
+static void turbo_encode_rows(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, int64_t pos, cudaStream_t s) {
+    if (k.shape[2] == 0) return;
+    const bool k_turbo = !c->raw_key && !c->affine_key;
+    const bool v_turbo = !c->affine_value;
+    if (k_turbo && v_turbo) {
+        TurboEncodeArgs ka = turbo_args(k, c->kp, c->kn, c->kcodec, pos);
+        TurboEncodeArgs va = turbo_args(v, c->vp, c->vn, c->vcodec, pos);
+        launch_turbo_encode2(ka, &va, s);
+    } else {
+        if (k_turbo) launch_turbo_encode(turbo_args(k, c->kp, c->kn, c->kcodec, pos), s);
+        if (v_turbo) launch_turbo_encode(turbo_args(v, c->vp, c->vn, c->vcodec, pos), s);
+    }
+    if (c->affine_key)
+        launch_affine_quantize(quant_args(k, c->kq, c->ks, c->kb, c->key_group, 8, pos), s);
+    if (c->affine_value)
+        launch_affine_quantize(quant_args(v, c->vq, c->vs, c->vb, c->key_group, c->value_bits, pos), s);
+    if (c->raw_key) {
+        // raw keys keep living in c->k; V of the raw pair is unused, append K only
+        AppendArgs a;
+        a.k_src = k.data; a.v_src = k.data;
+        a.ks_sb = k.stride[0]; a.ks_sh = k.stride[1]; a.ks_ss = k.stride[2]; a.ks_sd = k.stride[3];
+        a.vs_sb = a.ks_sb; a.vs_sh = a.ks_sh; a.vs_ss = a.ks_ss; a.vs_sd = a.ks_sd;
+        a.k_dst = c->k.ptr; a.v_dst = c->k.ptr;
+        a.kd_sb = c->k.sb(); a.kd_sh = c->k.sh(); a.kd_st = c->k.st();
+        a.vd_sb = a.kd_sb; a.vd_sh = a.kd_sh; a.vd_st = a.kd_st;
+        a.B = (int)k.shape[0]; a.H = (int)k.shape[1]; a.S = (int)k.shape[2];
+        a.Dk = (int)k.shape[3]; a.Dv = 0;
+        a.pos = pos; a.esize = (int)dtype_size(k.dtype);
+        launch_append(a, s);
+    }
+}
+
+static void turbo_alloc_compressed(kvc_cache *c, int64_t B, int64_t H, int D, int32_t dtype, int64_t cap, cudaStream_t s) {
+    const bool k_turbo = !c->raw_key && !c->affine_key;
+    if (k_turbo) {
+        c->kp.alloc(B, H, cap, turbo_pw(D, c->key_bits), KVC_U32, s);
+        c->kn.alloc(B, H, cap, 1, KVC_F32, s);
+    }
+    if (c->affine_key) {
+        const int g = resolved_group_size(c->key_group, D, D);
+        if (!g) fail(KVC_ERR_INVALID_ARG, "TurboQuant affine key quantization requires head dimensions divisible by 32, 64 or 128");
+        c->key_group = g;
+        quant_triple_alloc(c->kq, c->ks, c->kb, B, H, cap, D, g, 8, dtype, s);
+    }
+    if (c->affine_value) {
+        const int g = resolved_group_size(c->key_group, D, D);
+        if (!g) fail(KVC_ERR_INVALID_ARG, "affine value quantization requires head dimensions divisible by 32, 64 or 128");
+        c->key_group = g;
+        quant_triple_alloc(c->vq, c->vs, c->vb, B, H, cap, D, g, c->value_bits, dtype, s);
+    } else {
+        c->vp.alloc(B, H, cap, turbo_pw(D, c->value_bits), KVC_U32, s);
+        c->vn.alloc(B, H, cap, 1, KVC_F32, s);
+    }
+}
+
+static void turbo_ensure_compressed(kvc_cache *c, int64_t need, int64_t keep_rows, cudaStream_t s) {
+    const int64_t step = 256;
+    for (Array4 *a : {&c->kp, &c->kn, &c->vp, &c->vn, &c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb})
+        if (a->allocated()) a->ensure(need, keep_rows, step, s);
+    if (c->raw_key && c->k.allocated()) c->k.ensure(need, keep_rows, step, s);
+}
+
+// TurboQuantKVCache.compressRawCache (TurboQuantKVCache.swift:895-918).
+static void turbo_compress_raw(kvc_cache *c, cudaStream_t s) {
+    if (c->compressed || !c->k.allocated() || c->offset <= 0) return;
+    const int D = (int)c->k.W;
+    KVC_REQUIRE(c->v.W == c->k.W, "TurboQuant: key and value head dims must match");
+    ensure_codecs(c, D, s);
+    const int64_t cap = std::max<int64_t>(std::max<int64_t>(c->cfg.reserve_tokens, c->k.cap), round_up(c->offset, 256));
+    turbo_alloc_compressed(c, c->k.B, c->k.H, D, c->k.dtype, cap, s);
+    kvc_tensor kt = c->k.view(c->offset), vt = c->v.view(c->offset);
+    if (c->raw_key) {
+        // keys stay where they are (raw, in c->k); only values are encoded
+        (void)kt;
+        if (!c->affine_value) launch_turbo_encode(turbo_args(vt, c->vp, c->vn, c->vcodec, 0), s);
+        else launch_affine_quantize(quant_args(vt, c->vq, c->vs, c->vb, c->key_group, c->value_bits, 0), s);
+        c->v.release(s);
+    } else {
+        turbo_encode_rows(c, kt, vt, 0, s);
+        c->k.release(s);
+        c->v.release(s);
+    }
+    c->compressed = true;
+}
+
+// TurboQuantKVCache.compressedAttention (TurboQuantKVCache.swift:1164-1446).
+static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k,
+                                       const kvc_tensor &v, float scale, int32_t mask_mode,
+                                       const kvc_tensor *mask, const kvc_tensor &out, cudaStream_t s) {
+    const int D = (int)k.shape[3];
+    KVC_REQUIRE(v.shape[3] == D && q.shape[3] == D, "TurboQuant: query, key and value head dims must match");
+    if (!c->compressed) turbo_compress_raw(c, s);
+    ensure_codecs(c, D, s);
+    const int64_t S = k.shape[2], prev = c->offset;
+    if (!c->compressed) {
+        // nothing was cached yet: start directly in the compressed phase
+        const int64_t cap = std::max<int64_t>(c->cfg.reserve_tokens, round_up(std::max<int64_t>(S, 1), 256));
+        turbo_alloc_compressed(c, k.shape[0], k.shape[1], D, k.dtype, cap, s);
+        if (c->raw_key) c->k.alloc(k.shape[0], k.shape[1], cap, D, k.dtype, s);
+        c->compressed = true;
+    }
+    turbo_ensure_compressed(c, prev + S, prev, s);
+    turbo_encode_rows(c, k, v, prev, s);
+    c->offset = prev + S;
+
+    const int64_t T = c->offset;
+    const int L = (int)q.shape[2];
+    int32_t mode = mask_mode;
+    if (L == 1 && mode == KVC_MASK_CAUSAL) mode = KVC_MASK_NONE;
+    AttnArgs a = make_attn_args(q, out, scale, mode, mask, T, (int)k.shape[1]);
+    if (c->raw_key) {
+        a.k = raw_source(c->k.view(T));
+    } else if (c->affine_key) {
+        a.k = affine_source(c->kq.view(T), c->ks.view(T), c->kb.view(T), c->key_group, 8);
+    } else {
+        a.k = turbo_source(c->kp, c->kn, c->kcodec);
+        a.q_signs = c->kcodec.signs_dev;
+    }
+    if (c->affine_value) {
+        a.v = affine_source(c->vq.view(T), c->vs.view(T), c->vb.view(T), c->key_group, c->value_bits);
+    } else {
+        a.v = turbo_source(c->vp, c->vn, c->vcodec);
+        a.o_signs = c->vcodec.signs_dev;
+    }
+    launch_attention(a, s);
+}
+
+void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, const kvc_tensor &v,
+                     float scale, int32_t mask_mode, const kvc_tensor *mask, const kvc_tensor &out,
+                     cudaStream_t s) {
+    require4(q, "queries");
+    require4(k, "keys");
+    require4(v, "values");
+    KVC_REQUIRE(q.shape[0] == k.shape[0], "attention: query and key batch differ");
+    KVC_REQUIRE(k.shape[1] > 0 && q.shape[1] % k.shape[1] == 0, "attention: Hq must be a multiple of Hkv");
+    KVC_REQUIRE(q.dtype == k.dtype, "attention: queries and keys must share a dtype");
+    const int Hkv = (int)k.shape[1];
+    switch (c->cfg.kind) {
+        case KVC_KIND_TURBO: {
+            const int L = (int)q.shape[2];
+            if (L > 1 && !c->compressed) {
+                // AttentionUtils.swift:56-63: raw prefill + plain SDPA
+                kvc_tensor ck, cv;
+                cache_update(c, k, v, s, &ck, &cv);
+                AttnArgs a = make_attn_args(q, out, scale, mask_mode, mask, ck.shape[2], Hkv);
+                a.k = raw_source(ck);
+                a.v = raw_source(cv);
+                launch_attention(a, s);
+            } else {
+                if (c->open_round) fail(KVC_ERR_INVALID_STATE, "attention: a staged round is open on this cache");
+                turbo_compressed_attention(c, q, k, v, scale, mask_mode, mask, out, s);
+            }
+            return;
+        }
+        case KVC_KIND_QUANTIZED: {
+            kvc_tensor qk[3], qv[3];
+            cache_update_quantized(c, k, v, s, qk, qv);
+            AttnArgs a = make_attn_args(q, out, scale, mask_mode, mask, c->offset, Hkv);
+            a.k = affine_source(qk[0], qk[1], qk[2], c->group_size, c->bits);
+            a.v = affine_source(qv[0], qv[1], qv[2], c->group_size, c->bits);
+            launch_attention(a, s);
+            return;
+        }
+        default: {
+            kvc_tensor ck, cv;
+            cache_update(c, k, v, s, &ck, &cv);
+            AttnArgs a = make_attn_args(q, out, scale, mask_mode, mask, ck.shape[2], Hkv);
+            a.k = raw_source(ck);
+            a.v = raw_source(cv);
+            launch_attention(a, s);
+            return;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------
+// trim / trimmable
+// ---------------------------------------------------------------------
+int64_t cache_trim(kvc_cache *c, int64_t n) {
+    if (c->open_round) fail(KVC_ERR_INVALID_STATE, "trim: a staged round is open on this cache");
+    c->restore.valid = false;
+    switch (c->cfg.kind) {
+        case KVC_KIND_ROTATING: {
+            // KVCache.swift:826-831: no validity check, idx moves with offset.
+            const int64_t t = std::min(c->offset, std::max<int64_t>(n, 0));
+            c->offset -= t;
+            c->idx -= t;
+            return t;
+        }
+        case KVC_KIND_TURBO: {
+            // TurboQuantKVCache.swift:1583-1603
+            if (n <= 0 || c->offset <= 0) return 0;
+            const int64_t t = std::min(n, c->offset);
+            c->offset -= t;
+            if (c->offset == 0) {
+                cudaStream_t s = nullptr;
+                for (Array4 *a : {&c->k, &c->v, &c->kp, &c->kn, &c->vp, &c->vn, &c->kq, &c->ks, &c->kb,
+                                  &c->vq, &c->vs, &c->vb})
+                    a->release(s);
+                c->compressed = false;
+            }
+            return t;
+        }
+        default: {
+            const int64_t t = std::min(c->offset, std::max<int64_t>(n, 0));
+            c->offset -= t;
+            return t;
+        }
+    }
+}
+
+bool cache_is_trimmable_after(const kvc_cache *c, int64_t positions) {
+    if (c->cfg.kind == KVC_KIND_ROTATING) return c->offset + positions < c->cfg.max_size;  // KVCache.swift:821-823
+    return true;
+}
+
+// ---------------------------------------------------------------------
+// state / metaState
+// ---------------------------------------------------------------------
+int cache_state_count(const kvc_cache *c) {
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE:
+        case KVC_KIND_ROTATING: return c->k.allocated() ? 2 : 0;
+        case KVC_KIND_QUANTIZED: return c->kq.allocated() ? 6 : 0;
+        case KVC_KIND_TURBO:
+            if (c->offset <= 0) return 0;
+            if (!c->compressed) return c->k.allocated() ? 2 : 0;
+            if (c->affine_value) return c->raw_key ? 4 : (c->affine_key ? 6 : 5);
+            if (c->affine_key) return 5;
+            if (c->raw_key) return 3;
+            return 4;
+        default: return 0;
+    }
+}
+
+kvc_tensor cache_state_get(kvc_cache *c, int index) {
+    const int n = cache_state_count(c);
+    if (index < 0 || index >= n) fail(KVC_ERR_INVALID_ARG, "state index out of range");
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE: return (index == 0 ? c->k : c->v).view(c->offset);
+        case KVC_KIND_ROTATING: {
+            // KVCache.swift:752-763: rows [0, offset) while the buffer is longer, else the whole ring
+            const int64_t rows = c->offset < c->len ? std::max<int64_t>(c->offset, 0) : c->len;
+            return (index == 0 ? c->k : c->v).view(rows);
+        }
+        case KVC_KIND_QUANTIZED: {
+            Array4 *arr[6] = {&c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb};
+            return arr[index]->view(c->offset);
+        }
+        case KVC_KIND_TURBO: {
+            if (!c->compressed) return (index == 0 ? c->k : c->v).view(c->offset);
+            std::vector<kvc_tensor> st;
+            if (c->affine_key) { st.push_back(c->kq.view(c->offset)); st.push_back(c->ks.view(c->offset)); st.push_back(c->kb.view(c->offset)); }
+            else if (c->raw_key) st.push_back(c->k.view(c->offset));
+            else { st.push_back(c->kp.view(c->offset)); st.push_back(view3(c->kn, c->offset)); }
+            if (c->affine_value) { st.push_back(c->vq.view(c->offset)); st.push_back(c->vs.view(c->offset)); st.push_back(c->vb.view(c->offset)); }
+            else { st.push_back(c->vp.view(c->offset)); st.push_back(view3(c->vn, c->offset)); }
+            return st[index];
+        }
+        default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
+    }
+}
+
+// Copy a strided [B, H, T, W] (or [B, H, T]) device tensor into a fresh array.
+static void adopt(Array4 &dst, const kvc_tensor &t, cudaStream_t s) {
+    kvc_tensor x = t;
+    if (x.ndim == 3) { x.ndim = 4; x.shape[3] = 1; x.stride[3] = 1; }
+    require4(x, "state array");
+    dst.release(s);
+    dst.alloc(x.shape[0], x.shape[1], std::max<int64_t>(x.shape[2], 1), x.shape[3], x.dtype, s);
+    if (x.shape[2] == 0) return;
+    AppendArgs a;
+    a.k_src = x.data; a.v_src = x.data;
+    a.ks_sb = x.stride[0]; a.ks_sh = x.stride[1]; a.ks_ss = x.stride[2]; a.ks_sd = x.stride[3];
+    a.vs_sb = a.ks_sb; a.vs_sh = a.ks_sh; a.vs_ss = a.ks_ss; a.vs_sd = a.ks_sd;
+    a.k_dst = dst.ptr; a.v_dst = dst.ptr;
+    a.kd_sb = dst.sb(); a.kd_sh = dst.sh(); a.kd_st = dst.st();
+    a.vd_sb = a.kd_sb; a.vd_sh = a.kd_sh; a.vd_st = a.kd_st;
+    a.B = (int)x.shape[0]; a.H = (int)x.shape[1]; a.S = (int)x.shape[2];
+    a.Dk = (int)x.shape[3]; a.Dv = 0;
+    a.pos = 0; a.esize = (int)dtype_size(x.dtype);
+    launch_append(a, s);
+}
+
+void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStream_t s) {
+    if (c->open_round) fail(KVC_ERR_INVALID_STATE, "state: a staged round is open on this cache");
+    c->restore.valid = false;
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE:
+            KVC_REQUIRE(count == 2, "KVCacheSimple state must have exactly 2 arrays (keys, values)");
+            adopt(c->k, arrays[0], s);
+            adopt(c->v, arrays[1], s);
+            c->offset = arrays[0].shape[2];  // KVCache.swift:467
+            return;
+        case KVC_KIND_ROTATING:
+            KVC_REQUIRE(count == 2, "RotatingKVCache state must have exactly 2 arrays");
+            adopt(c->k, arrays[0], s);
+            adopt(c->v, arrays[1], s);
+            c->len = arrays[0].shape[2];  // offset and idx travel in metaState (KVCache.swift:770-771)
+            return;
+        case KVC_KIND_QUANTIZED: {
+            if (count == 4) fail(KVC_ERR_UNSUPPORTED, "QuantizedKVCache state without biases (non-affine modes) is not built");
+            KVC_REQUIRE(count == 6, "QuantizedKVCache state must have exactly 6 or 4 arrays (3/2 for keys, 3/2 for values)");
+            Array4 *arr[6] = {&c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb};
+            for (int i = 0; i < 6; ++i) adopt(*arr[i], arrays[i], s);
+            return;
+        }
+        case KVC_KIND_TURBO: {
+            // TurboQuantKVCache.swift:1519-1567
+            for (Array4 *a : {&c->k, &c->v, &c->kp, &c->kn, &c->vp, &c->vn, &c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb})
+                a->release(s);
+            if (c->affine_key && count == 5 && !c->affine_value) {
+                adopt(c->kq, arrays[0], s); adopt(c->ks, arrays[1], s); adopt(c->kb, arrays[2], s);
+                adopt(c->vp, arrays[3], s); adopt(c->vn, arrays[4], s);
+                c->compressed = true;
+            } else if (c->raw_key && count == 3 && !c->affine_value) {
+                adopt(c->k, arrays[0], s); adopt(c->vp, arrays[1], s); adopt(c->vn, arrays[2], s);
+                c->compressed = true;
+            } else if (!c->affine_key && !c->raw_key && c->affine_value && count == 5) {
+                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
+                adopt(c->vq, arrays[2], s); adopt(c->vs, arrays[3], s); adopt(c->vb, arrays[4], s);
+                c->compressed = true;
+            } else if (!c->affine_key && !c->raw_key && count == 5) {
+                fail(KVC_ERR_UNSUPPORTED, "TurboQuant state with a key-calibration scale is not built");
+            } else if (count == 4 && !c->affine_value) {
+                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
+                adopt(c->vp, arrays[2], s); adopt(c->vn, arrays[3], s);
+                c->compressed = true;
+            } else if (count == 2) {
+                adopt(c->k, arrays[0], s); adopt(c->v, arrays[1], s);
+                c->compressed = false;
+            } else {
+                fail(KVC_ERR_INVALID_ARG, "TurboQuantKVCache state: unexpected number of arrays");
+            }
+            c->offset = arrays[0].shape[2];
+            return;
+        }
+        default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
+    }
+}
+
+std::vector<std::string> cache_meta_state(const kvc_cache *c) {
+    auto S = [](int64_t v) { return std::to_string(v); };
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE: return {""};  // BaseKVCache default (KVCache.swift:207-214)
+        case KVC_KIND_ROTATING:  // KVCache.swift:775-781
+            return {S(c->cfg.keep), S(c->cfg.max_size), S(c->cfg.step), S(c->offset), S(c->idx), c->origin};
+        case KVC_KIND_QUANTIZED:  // KVCache.swift:1148-1149
+            return {S(c->cfg.step), S(c->offset), S(c->group_size), S(c->bits)};
+        case KVC_KIND_TURBO:  // TurboQuantKVCache.swift:1570-1573
+            return {S(c->offset), S(c->cfg.bits), S(c->key_bits), S(c->value_bits), std::to_string(c->cfg.seed)};
+        default: return {};
+    }
+}
+
+static bool parse_int(const std::string &s, int64_t &out) {
+    if (s.empty()) return false;
+    char *end = nullptr;
+    const long long v = std::strtoll(s.c_str(), &end, 10);
+    if (!end || *end != '\0') return false;
+    out = v;
+    return true;
+}
+
+void cache_set_meta_state(kvc_cache *c, const std::vector<std::string> &m) {
+    if (c->open_round) fail(KVC_ERR_INVALID_STATE, "metaState: a staged round is open on this cache");
+    c->restore.valid = false;
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE:
+            KVC_REQUIRE(m.size() == 1 && m[0].empty(), "This cache has no meta_state but a meta_state was set.");
+            return;
+        case KVC_KIND_ROTATING: {
+            KVC_REQUIRE(m.size() == 5 || m.size() == 6, "RotatingKVCache metaState must have 5 or 6 values");
+            int64_t keep, step, off, idx, mx;
+            KVC_REQUIRE(parse_int(m[0], keep) && parse_int(m[2], step) && parse_int(m[3], off) && parse_int(m[4], idx),
+                        "Failed to convert metaState values to integers");
+            KVC_REQUIRE(m[1] != "None", "RotatingKVCache requires a non-nil maxSize. Cannot load cache with maxSize=None.");
+            KVC_REQUIRE(parse_int(m[1], mx), "Failed to convert maxCacheSize to integer");
+            std::string origin = "modelNative";
+            if (m.size() == 6) {
+                KVC_REQUIRE(m[5] == "modelNative" || m[5] == "requested", "Invalid RotatingKVCache capacity origin");
+                origin = m[5];
+            }
+            c->cfg.keep = (int32_t)keep; c->cfg.max_size = (int32_t)mx; c->cfg.step = (int32_t)step;
+            c->offset = off; c->idx = idx; c->origin = origin;
+            return;
+        }
+        case KVC_KIND_QUANTIZED: {
+            KVC_REQUIRE(m.size() == 4, "QuantizedKVCache metaState must have exactly 4 values");
+            int64_t off, g, b;
+            KVC_REQUIRE(parse_int(m[1], off) && parse_int(m[2], g) && parse_int(m[3], b),
+                        "Failed to convert QuantizedKVCache metaState values to integers");
+            c->offset = off; c->group_size = (int32_t)g; c->bits = (int32_t)b;
+            return;
+        }
+        case KVC_KIND_TURBO: {
+            int64_t off;
+            if (m.size() >= 5 && parse_int(m[0], off)) c->offset = off;  // TurboQuantKVCache.swift:1574-1579
+            return;
+        }
+        default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
+    }
+}
+
+// ---------------------------------------------------------------------
+// copy / conversions
+// ---------------------------------------------------------------------
+static void clone_array(const Array4 &src, Array4 &dst, int64_t rows, cudaStream_t s) {
+    if (!src.allocated()) return;
+    dst.alloc(src.B, src.H, std::max<int64_t>(rows, 1), src.W, src.dtype, s);
+    copy_rows(src, 0, dst, 0, std::min(rows, src.cap), s);
+}
+
+kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
+    // copy() (KVCache.swift:525-533, :877-885, :1177-1185): the new object adopts
+    // the `state` arrays and the metaState.
+    std::unique_ptr<kvc_cache> n(new kvc_cache());
+    n->cfg = c->cfg;
+    n->cfg.reserve_tokens = 0;
+    n->device = c->device;
+    n->offset = c->offset;
+    n->len = c->len; n->idx = c->idx; n->origin = c->origin;
+    n->group_size = c->group_size; n->bits = c->bits; n->group_resolved = c->group_resolved;
+    n->compressed = c->compressed;
+    n->key_bits = c->key_bits; n->value_bits = c->value_bits; n->key_group = c->key_group;
+    n->raw_key = c->raw_key; n->affine_key = c->affine_key; n->affine_value = c->affine_value;
+    n->user_kc = c->user_kc; n->user_vc = c->user_vc; n->user_ks = c->user_ks; n->user_vs = c->user_vs;
+    int64_t rows = c->offset;
+    if (c->cfg.kind == KVC_KIND_ROTATING) {
+        rows = c->offset < c->len ? std::max<int64_t>(c->offset, 0) : c->len;
+        n->len = c->k.allocated() ? rows : 0;
+    }
+    clone_array(c->k, n->k, rows, s); clone_array(c->v, n->v, rows, s);
+    clone_array(c->kq, n->kq, rows, s); clone_array(c->ks, n->ks, rows, s); clone_array(c->kb, n->kb, rows, s);
+    clone_array(c->vq, n->vq, rows, s); clone_array(c->vs, n->vs, rows, s); clone_array(c->vb, n->vb, rows, s);
+    clone_array(c->kp, n->kp, rows, s); clone_array(c->kn, n->kn, rows, s);
+    clone_array(c->vp, n->vp, rows, s); clone_array(c->vn, n->vn, rows, s);
+    return n.release();
+}
+
+static kvc_cache *new_cache(int kind) {
+    kvc_cache *n = new kvc_cache();
+    kvc_config_default(&n->cfg, kind);
+    return n;
+}
+
+kvc_cache *cache_to_quantized(const kvc_cache *c, int group, int bits, cudaStream_t s) {
+    // KVCacheSimple.toQuantized (KVCache.swift:486-523); RotatingKVCache.toQuantized always throws (:894-899).
+    if (c->cfg.kind == KVC_KIND_ROTATING)
+        fail(KVC_ERR_UNSUPPORTED, "RotatingKVCache quantization is not implemented because its temporal ordering requires dedicated handling.");
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_SIMPLE, "toQuantized needs a KVCacheSimple");
+    std::unique_ptr<kvc_cache> n(new_cache(KVC_KIND_QUANTIZED));
+    n->device = c->device;
+    n->bits = bits; n->cfg.bits = bits;
+    n->group_size = group; n->cfg.group_size = group;
+    n->offset = c->offset;
+    if (!c->k.allocated()) return n.release();
+    const int kd = (int)c->k.W, vd = (int)c->v.W;
+    const int eff = resolved_group_size(group, kd, vd);
+    if (!eff)
+        fail(KVC_ERR_INVALID_ARG,
+             "KV cache quantization requires head dimensions divisible by one of the supported group sizes (32, 64, 128).");
+    n->group_size = eff;
+    const int64_t rows = c->offset;
+    quant_triple_alloc(n->kq, n->ks, n->kb, c->k.B, c->k.H, rows, kd, eff, bits, c->k.dtype, s);
+    quant_triple_alloc(n->vq, n->vs, n->vb, c->v.B, c->v.H, rows, vd, eff, bits, c->v.dtype, s);
+    if (rows > 0) {
+        kvc_tensor kt = c->k.view(rows), vt = c->v.view(rows);
+        QuantAppendArgs qa = quant_args(kt, n->kq, n->ks, n->kb, eff, bits, 0);
+        QuantAppendArgs qv = quant_args(vt, n->vq, n->vs, n->vb, eff, bits, 0);
+        launch_affine_quantize2(qa, &qv, s);
+    }
+    return n.release();
+}
+
+kvc_cache *cache_to_unquantized(const kvc_cache *c, cudaStream_t s) {
+    // QuantizedKVCache.toUnquantized (KVCache.swift:1188-1209)
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_QUANTIZED, "toUnquantized needs a QuantizedKVCache");
+    std::unique_ptr<kvc_cache> n(new_cache(KVC_KIND_SIMPLE));
+    n->device = c->device;
+    n->offset = c->offset;
+    if (!c->kq.allocated()) return n.release();
+    const int64_t rows = c->offset;
+    const int kd = (int)(c->kq.W * 32 / c->bits), vd = (int)(c->vq.W * 32 / c->bits);
+    n->k.alloc(c->kq.B, c->kq.H, std::max<int64_t>(rows, 1), kd, c->ks.dtype, s);
+    n->v.alloc(c->vq.B, c->vq.H, std::max<int64_t>(rows, 1), vd, c->vs.dtype, s);
+    // one launch per (batch, head) plane keeps the row strides simple
+    for (int which = 0; which < 2; ++which) {
+        const Array4 &q = which ? c->vq : c->kq, &sc = which ? c->vs : c->ks, &bi = which ? c->vb : c->kb;
+        Array4 &o = which ? n->v : n->k;
+        for (int64_t bh = 0; bh < q.B * q.H; ++bh) {
+            DequantArgs d;
+            d.codes = (const uint32_t *)q.ptr + bh * q.sh();
+            d.scales = (const char *)sc.ptr + (size_t)bh * sc.sh() * sc.esize();
+            d.biases = (const char *)bi.ptr + (size_t)bh * bi.sh() * bi.esize();
+            d.out = (char *)o.ptr + (size_t)bh * o.sh() * o.esize();
+            d.dtype = sc.dtype; d.rows = rows;
+            d.c_srow = q.st(); d.g_srow = sc.st(); d.o_srow = o.st();
+            d.D = (int)o.W; d.group = c->group_size; d.bits = c->bits;
+            launch_affine_dequantize(d, s);
+        }
+    }
+    return n.release();
+}
+
+kvc_cache *cache_to_turbo(const kvc_cache *c, int kb, int vb, int kg, cudaStream_t s) {
+    // maybeTurboQuantizeKVCache per-layer conversion (TurboQuantKVCache.swift:1748-1759)
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_SIMPLE, "turbo conversion needs a KVCacheSimple");
+    kvc_config cfg;
+    kvc_config_default(&cfg, KVC_KIND_TURBO);
+    cfg.bits = std::max(kb, vb); cfg.key_bits = kb; cfg.value_bits = vb; cfg.key_group_size = kg;
+    kvc_cache *raw = nullptr;
+    if (kvc_create(&cfg, &raw) != KVC_OK) fail(KVC_ERR_INVALID_ARG, kvc_last_error_message());
+    std::unique_ptr<kvc_cache> n(raw);
+    if (c->k.allocated() && c->offset > 0) {
+        kvc_tensor kt = c->k.view(c->offset), vt = c->v.view(c->offset);
+        cache_update(n.get(), kt, vt, s, nullptr, nullptr);
+    }
+    return n.release();
+}
+
+// ---------------------------------------------------------------------
+// logical view / masks
+// ---------------------------------------------------------------------
+void cache_logical_view(kvc_cache *c, int64_t tail, cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov) {
+    // RotatingKVCache.logicalView(tail:) (KVCache.swift:631-658)
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_ROTATING, "logicalView needs a RotatingKVCache");
+    if (!c->k.allocated()) fail(KVC_ERR_INVALID_STATE, "logicalView: nothing has been written yet");
+    auto ordered = rot_temporal(c);
+    const int64_t available = seg_total(ordered);
+    const int64_t keep = c->cfg.keep;
+    const int64_t requested = std::min(std::max<int64_t>(tail, 0), available);
+    const int64_t bound = std::max(requested, std::min(keep, available));
+    const int64_t trim_size = available - bound;
+    std::vector<GatherSeg> segs = ordered;
+    if (trim_size > 0) {
+        if (keep == 0) segs = seg_slice(ordered, trim_size, available);
+        else segs = rot_front_trim(ordered, trim_size, keep);
+    }
+    const int64_t n = seg_total(segs);
+    if (segs.size() <= 1) {
+        const int64_t first = segs.empty() ? 0 : segs[0].src_start;
+        if (ok) *ok = c->k.view(n, first);
+        if (ov) *ov = c->v.view(n, first);
+        return;
+    }
+    ensure_like(c->k_view, c->k, std::max<int64_t>(n, c->cfg.max_size), s);
+    ensure_like(c->v_view, c->v, std::max<int64_t>(n, c->cfg.max_size), s);
+    gather_rows(c->k, c->k_view, segs, s);
+    gather_rows(c->v, c->v_view, segs, s);
+    if (ok) *ok = c->k_view.view(n);
+    if (ov) *ov = c->v_view.view(n);
+}
+
+void cache_make_mask(const kvc_cache *c, int n, int64_t window, bool return_array, int32_t *mode,
+                     int64_t *rows, int64_t *cols, void *out_mask, cudaStream_t s) {
+    *rows = 0; *cols = 0;
+    if (c->cfg.kind == KVC_KIND_ROTATING) {
+        // RotatingKVCache.makeMask (KVCache.swift:834-871)
+        const int64_t max_size = c->cfg.max_size;
+        if (n > 1) {
+            const int64_t actual = window >= 0 ? window : max_size;
+            const int64_t capped = std::min(max_size - 1, c->offset);
+            if (capped + n > actual || return_array) {
+                *mode = KVC_MASK_ARRAY; *rows = n; *cols = capped + n;
+                if (out_mask) launch_causal_mask((uint8_t *)out_mask, n, capped, actual, s);
+                return;
+            }
+            *mode = KVC_MASK_CAUSAL;
+            return;
+        }
+        if (window < 0) { *mode = KVC_MASK_NONE; return; }
+        if (c->offset >= window && max_size > window) {
+            int64_t cur = c->idx;
+            if (cur >= max_size) cur = 0;
+            const int64_t size = c->offset < max_size ? c->offset + 1 : max_size;
+            *mode = KVC_MASK_ARRAY; *rows = 1; *cols = size;
+            if (out_mask) launch_rolled_mask((uint8_t *)out_mask, size, window, cur + 1, s);
+            return;
+        }
+        *mode = KVC_MASK_NONE;
+        return;
+    }
+    // BaseKVCache.makeMask (KVCache.swift:236-250)
+    if (n == 1) { *mode = KVC_MASK_NONE; return; }
+    if (return_array || (window >= 0 && n > window)) {
+        *mode = KVC_MASK_ARRAY; *rows = n; *cols = c->offset + n;
+        if (out_mask) launch_causal_mask((uint8_t *)out_mask, n, c->offset, window, s);
+        return;
+    }
+    *mode = KVC_MASK_CAUSAL;
+}
+
+// ---------------------------------------------------------------------
+// TurboQuant codebooks and sign vectors
+// ---------------------------------------------------------------------
+void turbo_codebook(int dim, int bits, std::vector<float> &centroids, std::vector<float> &bounds) {
+    // Lloyd-Max quantiser for one coordinate of a random unit vector in R^dim,
+    // density proportional to (1 - x^2)^((dim-3)/2) on [-1, 1]: weighted k-means
+    // on a 32768-point grid, 100 sweeps from quantile initialisation, the same
+    // procedure TurboQuantCodebook.generateCentroids (TurboQuantKVCache.swift:174-233)
+    // runs; carried out here in double precision.
+    const int levels = 1 << bits;
+    const int grid_n = 32768;
+    std::vector<double> grid(grid_n), w(grid_n);
+    const double expo = (dim - 3) / 2.0;
+    double total = 0;
+    for (int i = 0; i < grid_n; ++i) {
+        const double x = -1.0 + 2.0 * i / (grid_n - 1);
+        grid[i] = x;
+        w[i] = std::pow(std::max(1.0 - x * x, 1e-30), expo);
+        total += w[i];
+    }
+    std::vector<double> cen(levels, 0.0);
+    {
+        double cum = 0;
+        int ci = 0;
+        for (int i = 0; i < grid_n && ci < levels; ++i) {
+            cum += w[i];
+            while (ci < levels && cum >= (ci + 0.5) / levels * total) cen[ci++] = grid[i];
+        }
+        const double sigma = 1.0 / std::sqrt((double)dim);
+        while (ci < levels) { cen[ci] = (ci ? cen[ci - 1] : 0.0) + sigma; ++ci; }
+    }
+    for (int it = 0; it < 100; ++it) {
+        std::vector<double> sums(levels, 0.0), cnt(levels, 0.0);
+        int j = 0;
+        for (int i = 0; i < grid_n; ++i) {
+            while (j + 1 < levels && std::fabs(grid[i] - cen[j + 1]) < std::fabs(grid[i] - cen[j])) ++j;
+            sums[j] += grid[i] * w[i];
+            cnt[j] += w[i];
+        }
+        for (int k = 0; k < levels; ++k)
+            if (cnt[k] > 0) cen[k] = sums[k] / cnt[k];
+        std::sort(cen.begin(), cen.end());
+    }
+    centroids.resize(levels);
+    for (int k = 0; k < levels; ++k) centroids[k] = (float)cen[k];
+    bounds.resize(levels - 1);
+    for (int k = 0; k + 1 < levels; ++k) bounds[k] = (centroids[k] + centroids[k + 1]) / 2.0f;
+}
+
+void turbo_signs(int dim, uint64_t seed, std::vector<float> &signs) {
+    // The reference draws the signs from MLXRandom (TurboQuantKVCache.swift:289-298),
+    // whose stream is not reproducible outside MLX. This library defines its own:
+    // splitmix64 seeded with `seed`, one draw per dimension, top bit set -> +1.
+    signs.resize(dim);
+    uint64_t x = seed;
+    for (int i = 0; i < dim; ++i) {
+        x += 0x9E3779B97F4A7C15ull;
+        uint64_t z = x;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z = z ^ (z >> 31);
+        signs[i] = (z >> 63) ? 1.0f : -1.0f;
+    }
+}
+
+}  // namespace kvc

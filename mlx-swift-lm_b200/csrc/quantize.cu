@@ -1,0 +1,393 @@
+// Group-wise affine quantisation (MLX `quantized` / `dequantized`, affine mode)
+// and the TurboQuant fused Walsh-Hadamard encode.
+//
+// Both produce integer codes that must be bit-identical to the CPU oracle, so
+// every floating-point step uses the explicit round-to-nearest intrinsics
+// (never contracted into FMAs) and one fixed reduction tree:
+//   * a row of D elements is owned by 32 lanes, lane l holding the E = D/32
+//     contiguous elements [l*E, l*E+E);
+//   * sums run sequentially over a lane's own elements, then over the xor
+//     butterfly 16, 8, 4, 2, 1 across lanes.
+#include "common.h"
+
+namespace kvc {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// MLX affine quantisation of one group given its min and max:
+//   scale = max((max-min)/(2^b-1), 1e-7); the sign of the scale and the
+//   anchoring edge follow the larger-magnitude end, the scale is re-derived so
+//   that the edge maps to an integer code, and codes are
+//   rint((w - bias)/scale) clamped to [0, 2^b-1].
+__device__ __forceinline__ void affine_params(float w_min, float w_max, float n_bins,
+                                              float &scale, float &bias) {
+    scale = fmaxf(__fdiv_rn(__fsub_rn(w_max, w_min), n_bins), 1e-7f);
+    const bool side = fabsf(w_min) > fabsf(w_max);
+    scale = side ? scale : -scale;
+    const float edge = side ? w_min : w_max;
+    const float q0 = rintf(__fdiv_rn(edge, scale));
+    bias = 0.f;
+    if (q0 != 0.f) {
+        scale = __fdiv_rn(edge, q0);
+        bias = edge;
+    }
+}
+
+__device__ __forceinline__ uint32_t affine_code(float w, float scale, float bias, float n_bins) {
+    float q = rintf(__fdiv_rn(__fsub_rn(w, bias), scale));
+    q = fminf(fmaxf(q, 0.f), n_bins);
+    return (uint32_t)q;
+}
+
+// One warp per (tensor, b, h, s) row; E elements per lane.
+template <typename T, int E>
+__global__ void affine_quantize_warp_kernel(QuantAppendArgs ka, QuantAppendArgs va, int64_t k_rows,
+                                            int64_t total_rows) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= total_rows) return;
+    const bool is_v = row >= k_rows;
+    const QuantAppendArgs &a = is_v ? va : ka;
+    int64_t r = is_v ? row - k_rows : row;
+    const int s = (int)(r % a.S);
+    r /= a.S;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
+    float v[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = to_float<T>(src[(int64_t)(lane * E + i) * a.s_sd]);
+
+    float w_min = v[0], w_max = v[0];
+#pragma unroll
+    for (int i = 1; i < E; ++i) {
+        w_min = fminf(w_min, v[i]);
+        w_max = fmaxf(w_max, v[i]);
+    }
+    const int lanes_per_group = a.group / E;  // power of two, <= 32
+    for (int m = lanes_per_group >> 1; m >= 1; m >>= 1) {
+        w_min = fminf(w_min, __shfl_xor_sync(0xffffffffu, w_min, m));
+        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, m));
+    }
+    const float n_bins = (float)((1 << a.bits) - 1);
+    float scale, bias;
+    affine_params(w_min, w_max, n_bins, scale, bias);
+
+    const int64_t t = a.pos + s;
+    if ((lane % lanes_per_group) == 0) {
+        const int g = lane / lanes_per_group;
+        const int64_t gi = b * a.g_sb + h * a.g_sh + t * a.g_st + g;
+        ((T *)a.scales)[gi] = from_float<T>(scale);
+        ((T *)a.biases)[gi] = from_float<T>(bias);
+    }
+
+    // Pack: the lane's E codes occupy E*bits consecutive bits starting at bit
+    // lane*E*bits of the row (low bits first).
+    uint32_t *dst = a.codes + b * a.c_sb + h * a.c_sh + t * a.c_st;
+    const int nbits = E * a.bits;  // a power of two in [2, 64]
+    uint64_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+        acc |= (uint64_t)affine_code(v[i], scale, bias, n_bins) << (i * a.bits);
+    if (nbits == 64) {
+        dst[lane * 2] = (uint32_t)acc;
+        dst[lane * 2 + 1] = (uint32_t)(acc >> 32);
+    } else if (nbits == 32) {
+        dst[lane] = (uint32_t)acc;
+    } else {
+        const uint32_t part = (uint32_t)acc;
+        const int lpw = 32 / nbits;  // lanes per word
+        uint32_t word = part;
+        for (int k = 1; k < lpw; ++k) {
+            const uint32_t other = __shfl_down_sync(0xffffffffu, part, k);
+            word |= other << (k * nbits);
+        }
+        if ((lane % lpw) == 0) dst[lane / lpw] = word;
+    }
+}
+
+// General shapes: one thread per group.
+template <typename T>
+__global__ void affine_quantize_group_kernel(QuantAppendArgs ka, QuantAppendArgs va,
+                                             int64_t k_groups, int64_t total_groups) {
+    int64_t gidx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gidx >= total_groups) return;
+    const bool is_v = gidx >= k_groups;
+    const QuantAppendArgs &a = is_v ? va : ka;
+    if (is_v) gidx -= k_groups;
+    const int gpr = a.D / a.group;
+    const int g = (int)(gidx % gpr);
+    int64_t r = gidx / gpr;
+    const int s = (int)(r % a.S);
+    r /= a.S;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss + (int64_t)g * a.group * a.s_sd;
+    float w_min = to_float<T>(src[0]), w_max = w_min;
+    for (int i = 1; i < a.group; ++i) {
+        const float x = to_float<T>(src[i * a.s_sd]);
+        w_min = fminf(w_min, x);
+        w_max = fmaxf(w_max, x);
+    }
+    const float n_bins = (float)((1 << a.bits) - 1);
+    float scale, bias;
+    affine_params(w_min, w_max, n_bins, scale, bias);
+    const int64_t t = a.pos + s;
+    const int64_t gi = b * a.g_sb + h * a.g_sh + t * a.g_st + g;
+    ((T *)a.scales)[gi] = from_float<T>(scale);
+    ((T *)a.biases)[gi] = from_float<T>(bias);
+    uint32_t *dst = a.codes + b * a.c_sb + h * a.c_sh + t * a.c_st + (int64_t)g * a.group * a.bits / 32;
+    const int per_word = 32 / a.bits;
+    for (int w = 0; w < a.group / per_word; ++w) {
+        uint32_t word = 0;
+        for (int k = 0; k < per_word; ++k)
+            word |= affine_code(to_float<T>(src[(int64_t)(w * per_word + k) * a.s_sd]), scale, bias, n_bins)
+                    << (k * a.bits);
+        dst[w] = word;
+    }
+}
+
+template <typename T>
+__global__ void affine_dequantize_kernel(DequantArgs a, int64_t total) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int d = (int)(i % a.D);
+    const int64_t row = i / a.D;
+    const uint32_t word = a.codes[row * a.c_srow + (d * a.bits) / 32];
+    const uint32_t code = (word >> ((d * a.bits) % 32)) & ((1u << a.bits) - 1u);
+    const int g = d / a.group;
+    const float sc = to_float<T>(((const T *)a.scales)[row * a.g_srow + g]);
+    const float bi = to_float<T>(((const T *)a.biases)[row * a.g_srow + g]);
+    // MLX dequantises in the array dtype: scale * q + bias.
+    const float val = __fadd_rn(__fmul_rn(sc, (float)code), bi);
+    ((T *)a.out)[row * a.o_srow + d] = from_float<T>(val);
+}
+
+template <typename T>
+void quantize_dispatch(const QuantAppendArgs &k, const QuantAppendArgs &v, bool have_v,
+                       cudaStream_t stream) {
+    const QuantAppendArgs &vv = have_v ? v : k;
+    const int64_t k_rows = (int64_t)k.B * k.H * k.S;
+    const int64_t v_rows = have_v ? (int64_t)v.B * v.H * v.S : 0;
+    auto warp_ok = [](const QuantAppendArgs &a) {
+        if (a.D % 32 != 0) return false;
+        const int E = a.D / 32;
+        if (!(E == 1 || E == 2 || E == 4 || E == 8)) return false;
+        if (a.group % E != 0) return false;
+        const int lpg = a.group / E;
+        if (lpg < 1 || lpg > 32 || (lpg & (lpg - 1))) return false;
+        const int nbits = E * a.bits;
+        return (nbits >= 32) ? (nbits % 32 == 0) : (32 % nbits == 0);
+    };
+    const bool same_shape = !have_v || (k.D == v.D && k.group == v.group && k.bits == v.bits);
+    if (same_shape && warp_ok(k)) {
+        const int64_t total = k_rows + v_rows;
+        const int warps = 8;
+        const unsigned blocks = (unsigned)((total + warps - 1) / warps);
+        switch (k.D / 32) {
+            case 1: affine_quantize_warp_kernel<T, 1><<<blocks, warps * 32, 0, stream>>>(k, vv, k_rows, total); break;
+            case 2: affine_quantize_warp_kernel<T, 2><<<blocks, warps * 32, 0, stream>>>(k, vv, k_rows, total); break;
+            case 4: affine_quantize_warp_kernel<T, 4><<<blocks, warps * 32, 0, stream>>>(k, vv, k_rows, total); break;
+            case 8: affine_quantize_warp_kernel<T, 8><<<blocks, warps * 32, 0, stream>>>(k, vv, k_rows, total); break;
+        }
+    } else {
+        const int64_t k_groups = k_rows * (k.D / k.group);
+        const int64_t v_groups = have_v ? v_rows * (v.D / v.group) : 0;
+        const int64_t total = k_groups + v_groups;
+        affine_quantize_group_kernel<T><<<(unsigned)((total + 127) / 128), 128, 0, stream>>>(
+            k, vv, k_groups, total);
+    }
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+}  // namespace
+
+void launch_affine_quantize2(const QuantAppendArgs &k, const QuantAppendArgs *v, cudaStream_t stream) {
+    if ((int64_t)k.B * k.H * k.S == 0) return;
+    auto check = [](const QuantAppendArgs &a) {
+        KVC_REQUIRE(a.bits == 2 || a.bits == 4 || a.bits == 8,
+                    "affine quantisation supports 2, 4 or 8 bits");
+        KVC_REQUIRE(a.group > 0 && a.D % a.group == 0, "head dim must be a multiple of the group size");
+        KVC_REQUIRE((a.group * a.bits) % 32 == 0, "group must fill whole 32-bit words");
+    };
+    check(k);
+    if (v) {
+        check(*v);
+        KVC_REQUIRE(v->dtype == k.dtype, "keys and values must share a dtype");
+    }
+    const QuantAppendArgs dummy = k;
+    switch (k.dtype) {
+        case KVC_F32: quantize_dispatch<float>(k, v ? *v : dummy, v != nullptr, stream); break;
+        case KVC_F16: quantize_dispatch<__half>(k, v ? *v : dummy, v != nullptr, stream); break;
+        case KVC_BF16: quantize_dispatch<__nv_bfloat16>(k, v ? *v : dummy, v != nullptr, stream); break;
+        default: fail(KVC_ERR_INVALID_ARG, "affine quantisation needs a floating dtype");
+    }
+}
+
+void launch_affine_quantize(const QuantAppendArgs &a, cudaStream_t stream) {
+    launch_affine_quantize2(a, nullptr, stream);
+}
+
+void launch_affine_dequantize(const DequantArgs &a, cudaStream_t stream) {
+    const int64_t total = a.rows * a.D;
+    if (total <= 0) return;
+    KVC_REQUIRE(a.bits == 2 || a.bits == 4 || a.bits == 8, "affine dequantisation supports 2, 4 or 8 bits");
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    switch (a.dtype) {
+        case KVC_F32: affine_dequantize_kernel<float><<<blocks, 256, 0, stream>>>(a, total); break;
+        case KVC_F16: affine_dequantize_kernel<__half><<<blocks, 256, 0, stream>>>(a, total); break;
+        case KVC_BF16: affine_dequantize_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a, total); break;
+        default: fail(KVC_ERR_INVALID_ARG, "affine dequantisation needs a floating dtype");
+    }
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+// ---------------------------------------------------------------------
+// TurboQuant fused WHT encode
+// ---------------------------------------------------------------------
+namespace {
+
+template <typename T, int E>
+__global__ void turbo_encode_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, int64_t k_rows,
+                                    int64_t total_rows, float inv_sqrt_dim) {
+    extern __shared__ uint32_t s_words[];  // [warps][PWmax]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= total_rows) return;  // whole warp exits together
+    const bool is_v = row >= k_rows;
+    const TurboEncodeArgs &a = is_v ? va : ka;
+    int64_t r = is_v ? row - k_rows : row;
+    const int s = (int)(r % a.S);
+    r /= a.S;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+    constexpr int D = E * 32;
+
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
+    float v[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = to_float<T>(src[(int64_t)(lane * E + i) * a.s_sd]);
+
+    // L2 norm over the fixed reduction tree.
+    float sq = __fmul_rn(v[0], v[0]);
+#pragma unroll
+    for (int i = 1; i < E; ++i) sq = __fadd_rn(sq, __fmul_rn(v[i], v[i]));
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, m));
+    const float norm = __fsqrt_rn(sq);
+    const float inv_norm = (norm > 1e-8f) ? __fdiv_rn(1.0f, norm) : 0.0f;
+
+    // unit-normalise and flip signs: x * (inv_norm * sign)
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = __fmul_rn(v[i], __fmul_rn(inv_norm, a.signs[lane * E + i]));
+
+    // Walsh-Hadamard butterfly, stage s pairs elements 2^s apart: (a, b) -> (a+b, a-b).
+#pragma unroll
+    for (int st = 1; st < E; st <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            if ((i & st) == 0) {
+                const float lo = v[i], hi = v[i + st];
+                v[i] = __fadd_rn(lo, hi);
+                v[i + st] = __fsub_rn(lo, hi);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = (lane & m) ? __fsub_rn(other, v[i]) : __fadd_rn(other, v[i]);
+        }
+    }
+
+    // boundary quantise + pack (low bits first, codes may straddle words)
+    const int pw = (D * a.bits + 31) / 32;
+    uint32_t *words = s_words + warp * ((1024 * 4 + 31) / 32);
+    for (int w = lane; w < pw; w += 32) words[w] = 0;
+    __syncwarp();
+    const int levels_m1 = (1 << a.bits) - 1;
+    const uint32_t mask = (uint32_t)levels_m1;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const float rotated = __fmul_rn(v[i], inv_sqrt_dim);
+        uint32_t idx = 0;
+        for (int bd = 0; bd < levels_m1; ++bd) idx += (rotated > a.boundaries[bd]) ? 1u : 0u;
+        idx &= mask;
+        const int bit = (lane * E + i) * a.bits;
+        const int w = bit >> 5, sh = bit & 31;
+        atomicOr(&words[w], idx << sh);
+        if (sh + a.bits > 32) atomicOr(&words[w + 1], idx >> (32 - sh));
+    }
+    __syncwarp();
+    const int64_t t = a.pos + s;
+    uint32_t *dst = a.packed + b * a.p_sb + h * a.p_sh + t * a.p_st;
+    for (int w = lane; w < pw; w += 32) dst[w] = words[w];
+    if (lane == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = norm;
+}
+
+template <typename T>
+void turbo_dispatch(const TurboEncodeArgs &k, const TurboEncodeArgs &v, bool have_v, cudaStream_t stream) {
+    const int64_t k_rows = (int64_t)k.B * k.H * k.S;
+    const int64_t v_rows = have_v ? (int64_t)v.B * v.H * v.S : 0;
+    const int64_t total = k_rows + v_rows;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)((total + warps - 1) / warps);
+    const size_t smem = warps * ((1024 * 4 + 31) / 32) * sizeof(uint32_t);
+    const float inv_sqrt_dim = 1.0f / sqrtf((float)k.D);
+#define KVC_TE(EE)                                                                               \
+    turbo_encode_kernel<T, EE><<<blocks, warps * 32, smem, stream>>>(k, v, k_rows, total, inv_sqrt_dim)
+    switch (k.D / 32) {
+        case 1: KVC_TE(1); break;
+        case 2: KVC_TE(2); break;
+        case 4: KVC_TE(4); break;
+        case 8: KVC_TE(8); break;
+        case 16: KVC_TE(16); break;
+        case 32: KVC_TE(32); break;
+        default: fail(KVC_ERR_UNSUPPORTED, "turbo encode: head dim must be a power of two in [32, 1024]");
+    }
+#undef KVC_TE
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+}  // namespace
+
+void launch_turbo_encode2(const TurboEncodeArgs &k, const TurboEncodeArgs *v, cudaStream_t stream) {
+    if ((int64_t)k.B * k.H * k.S == 0) return;
+    KVC_REQUIRE(k.bits >= 1 && k.bits <= 4, "turbo encode supports 1..4 bits");
+    KVC_REQUIRE(k.D >= 32 && k.D <= 1024 && (k.D & (k.D - 1)) == 0,
+                "turbo encode (Walsh-Hadamard path) needs a power-of-two head dim in [32, 1024]");
+    if (v) {
+        KVC_REQUIRE(v->D == k.D && v->dtype == k.dtype, "turbo encode: K and V must share dim and dtype");
+        KVC_REQUIRE(v->bits >= 1 && v->bits <= 4, "turbo encode supports 1..4 bits");
+    }
+    const TurboEncodeArgs &vv = v ? *v : k;
+    switch (k.dtype) {
+        case KVC_F32: turbo_dispatch<float>(k, vv, v != nullptr, stream); break;
+        case KVC_F16: turbo_dispatch<__half>(k, vv, v != nullptr, stream); break;
+        case KVC_BF16: turbo_dispatch<__nv_bfloat16>(k, vv, v != nullptr, stream); break;
+        default: fail(KVC_ERR_INVALID_ARG, "turbo encode needs a floating dtype");
+    }
+}
+
+void launch_turbo_encode(const TurboEncodeArgs &a, cudaStream_t stream) {
+    launch_turbo_encode2(a, nullptr, stream);
+}
+
+}  // namespace kvc

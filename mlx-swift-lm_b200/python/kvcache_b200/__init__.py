@@ -1,0 +1,685 @@
+"""ctypes binding of libkvcache_b200.so with the reference's names.
+
+The classes mirror the cache classes of mlx-swift-lm's MLXLMCommon
+(KVCacheSimple, RotatingKVCache, QuantizedKVCache, TurboQuantKVCache) and the
+free functions attentionWithCacheUpdate / quantizedScaledDotProductAttention,
+so that tests read like the reference's own. Every call goes through the C ABI
+declared in include/kvcache_b200.h; torch only supplies device memory and
+streams. There is no fallback: if the shared library is missing, importing this
+package raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional, Sequence, Tuple
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PKG = os.path.abspath(os.path.join(_HERE, "..", ".."))
+LIB_PATH = os.path.join(_PKG, "lib", "libkvcache_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python mlx-swift-lm_b200/build.py` "
+        "(there is no CPU or PyTorch fallback for this library)")
+
+_lib = ctypes.CDLL(LIB_PATH)
+
+KVC_MAX_DIMS = 5
+F32, F16, BF16, U32, BOOL = 0, 1, 2, 3, 4
+KIND_SIMPLE, KIND_ROTATING, KIND_QUANTIZED, KIND_TURBO = 0, 1, 2, 3
+MASK_NONE, MASK_CAUSAL, MASK_ARRAY = 0, 1, 2
+
+OK = 0
+ERR_INTERNAL, ERR_INVALID_ARG, ERR_INVALID_STATE, ERR_UNSUPPORTED = -1, -2, -3, -4
+ERR_CUDA, ERR_OOM, ERR_NOT_TRIMMABLE, ERR_TIMEOUT, ERR_COMM = -5, -6, -7, -8, -9
+
+
+class KVCError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[kvc {status}] {message}")
+        self.status = status
+        self.message = message
+
+
+class Tensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("ndim", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * KVC_MAX_DIMS), ("stride", ctypes.c_int64 * KVC_MAX_DIMS)]
+
+
+class Config(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("device", ctypes.c_int32), ("step", ctypes.c_int32),
+                ("max_size", ctypes.c_int32), ("keep", ctypes.c_int32), ("group_size", ctypes.c_int32),
+                ("bits", ctypes.c_int32), ("key_bits", ctypes.c_int32), ("value_bits", ctypes.c_int32),
+                ("key_group_size", ctypes.c_int32), ("seed", ctypes.c_uint64),
+                ("reserve_tokens", ctypes.c_int64), ("turbo_affine_values", ctypes.c_int32)]
+
+
+_vp = ctypes.c_void_p
+_TP = ctypes.POINTER(Tensor)
+
+_lib.kvc_version.restype = ctypes.c_char_p
+_lib.kvc_last_error_message.restype = ctypes.c_char_p
+_lib.kvc_offset.restype = ctypes.c_int64
+_lib.kvc_offset.argtypes = [_vp]
+_lib.kvc_max_size.restype = ctypes.c_int64
+_lib.kvc_max_size.argtypes = [_vp]
+_lib.kvc_ring_index.restype = ctypes.c_int64
+_lib.kvc_ring_index.argtypes = [_vp]
+_lib.kvc_memory_bytes.restype = ctypes.c_int64
+_lib.kvc_memory_bytes.argtypes = [_vp]
+_lib.kvc_round_offset.restype = ctypes.c_int64
+_lib.kvc_round_offset.argtypes = [_vp]
+_lib.kvc_launch_count.restype = ctypes.c_int64
+_lib.kvc_free.argtypes = [_vp]
+_lib.kvc_free.restype = None
+_lib.kvc_round_free.argtypes = [_vp]
+_lib.kvc_round_free.restype = None
+_lib.kvc_comm_free.argtypes = [_vp]
+_lib.kvc_comm_free.restype = None
+for _name in ("kvc_kind_of", "kvc_group_size", "kvc_bits", "kvc_is_compressed", "kvc_is_trimmable",
+              "kvc_state_count"):
+    getattr(_lib, _name).argtypes = [_vp]
+_lib.kvc_is_trimmable_after.argtypes = [_vp, ctypes.c_int64]
+_lib.kvc_set_offset.argtypes = [_vp, ctypes.c_int64]
+_lib.kvc_attention.argtypes = [_vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp]
+_lib.kvc_attention_host.argtypes = [_vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp,
+                                    ctypes.c_int32]
+_lib.kvc_round_attention.argtypes = [_vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp]
+_lib.kvc_sdpa.argtypes = [_TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp]
+_lib.kvc_quantized_sdpa.argtypes = [_TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, ctypes.c_int32,
+                                    ctypes.c_int32, _TP, _vp]
+_lib.kvc_attention_sharded.argtypes = [_vp, _vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP,
+                                       ctypes.c_int32, _vp]
+_lib.kvc_update.argtypes = [_vp, _TP, _TP, _vp, _TP, _TP]
+_lib.kvc_update_quantized.argtypes = [_vp, _TP, _TP, _vp, _TP, _TP]
+_lib.kvc_round_update.argtypes = [_vp, _TP, _TP, _vp, _TP, _TP]
+_lib.kvc_logical_view.argtypes = [_vp, ctypes.c_int64, _vp, _TP, _TP]
+_lib.kvc_state_get.argtypes = [_vp, ctypes.c_int32, _TP]
+_lib.kvc_state_set.argtypes = [_vp, _TP, ctypes.c_int32, _vp]
+_lib.kvc_state_export.argtypes = [_vp, ctypes.c_int32, _vp, ctypes.c_size_t, _TP, _vp]
+_lib.kvc_trim.argtypes = [_vp, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)]
+_lib.kvc_reserve.argtypes = [_vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                             ctypes.c_int32, _vp]
+_lib.kvc_copy.argtypes = [_vp, _vp, ctypes.POINTER(_vp)]
+_lib.kvc_to_quantized.argtypes = [_vp, ctypes.c_int32, ctypes.c_int32, _vp, ctypes.POINTER(_vp)]
+_lib.kvc_to_unquantized.argtypes = [_vp, _vp, ctypes.POINTER(_vp)]
+_lib.kvc_to_turbo.argtypes = [_vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp, ctypes.POINTER(_vp)]
+_lib.kvc_round_begin.argtypes = [_vp, ctypes.c_int32, ctypes.POINTER(_vp)]
+_lib.kvc_round_commit.argtypes = [_vp, ctypes.c_int32, _vp]
+_lib.kvc_round_rollback.argtypes = [_vp, _vp]
+_lib.kvc_rewind_last_round.argtypes = [_vp, ctypes.c_int64, _vp, ctypes.POINTER(ctypes.c_int64)]
+_lib.kvc_meta_state.argtypes = [_vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]
+_lib.kvc_set_meta_state.argtypes = [_vp, ctypes.c_char_p]
+_lib.kvc_make_mask.argtypes = [_vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32,
+                               ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64),
+                               ctypes.POINTER(ctypes.c_int64), _vp, _vp]
+_lib.kvc_affine_quantize.argtypes = [_TP, ctypes.c_int32, ctypes.c_int32, _TP, _TP, _TP, _vp]
+_lib.kvc_affine_dequantize.argtypes = [_TP, _TP, _TP, ctypes.c_int32, ctypes.c_int32, _TP, _vp]
+_lib.kvc_turbo_encode.argtypes = [_TP, _vp, ctypes.POINTER(ctypes.c_float), ctypes.c_int32, _TP, _TP, _vp]
+_lib.kvc_turbo_codebook.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
+                                    ctypes.POINTER(ctypes.c_float)]
+_lib.kvc_turbo_signs.argtypes = [ctypes.c_int32, ctypes.c_uint64, ctypes.POINTER(ctypes.c_float)]
+_lib.kvc_turbo_set_codec.argtypes = [_vp] + [ctypes.POINTER(ctypes.c_float)] * 4 + [ctypes.c_int32]
+_lib.kvc_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int64,
+                                       ctypes.POINTER(ctypes.c_int64)]
+_lib.kvc_can_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32]
+_lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
+_lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
+
+
+def lib() -> ctypes.CDLL:
+    return _lib
+
+
+def version() -> str:
+    return _lib.kvc_version().decode()
+
+
+def device_available() -> bool:
+    return bool(_lib.kvc_device_available())
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(_lib.kvc_launch_count(1 if reset else 0))
+
+
+def check(status: int) -> None:
+    if status != OK:
+        msg = _lib.kvc_last_error_message()
+        raise KVCError(status, msg.decode() if msg else "unknown error")
+
+
+# ---------------------------------------------------------------------------
+# torch <-> kvc_tensor
+# ---------------------------------------------------------------------------
+
+def _torch():
+    import torch
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: U32,
+            torch.uint32: U32, torch.bool: BOOL, torch.uint8: BOOL}[t.dtype]
+
+
+def _torch_dtype(code: int):
+    torch = _torch()
+    return {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16, U32: torch.int32, BOOL: torch.uint8}[code]
+
+
+def as_tensor(t) -> Tensor:
+    """Describe a torch tensor (device or host) as a kvc_tensor."""
+    out = Tensor()
+    out.data = t.data_ptr()
+    out.dtype = _dtype_code(t)
+    out.ndim = t.dim()
+    for i in range(t.dim()):
+        out.shape[i] = t.shape[i]
+        out.stride[i] = t.stride(i)
+    return out
+
+
+def view_to_torch(v: Tensor, device):
+    """Wrap a kvc_tensor view of library memory as a torch tensor (no copy)."""
+    torch = _torch()
+    nd = v.ndim
+    shape = [int(v.shape[i]) for i in range(nd)]
+    stride = [int(v.stride[i]) for i in range(nd)]
+    dt = _torch_dtype(v.dtype)
+    esize = torch.empty((), dtype=dt).element_size()
+    if any(s == 0 for s in shape) or not v.data:
+        return torch.empty(shape, dtype=dt, device=device)
+    extent = 1 + sum((shape[i] - 1) * stride[i] for i in range(nd))
+    return _from_pointer(int(v.data), extent * esize, dt, device).as_strided(shape, stride)
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ carrier for a raw device pointer."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _from_pointer(ptr: int, nbytes: int, dtype, device):
+    torch = _torch()
+    base = torch.as_tensor(_CudaArray(ptr, nbytes), device=device)
+    return base.view(dtype)
+
+
+def _stream_ptr(stream=None) -> int:
+    torch = _torch()
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream)
+
+
+def _mask_args(mask):
+    if mask is None or (isinstance(mask, str) and mask == "none"):
+        return MASK_NONE, None, None
+    if isinstance(mask, str):
+        if mask == "causal":
+            return MASK_CAUSAL, None, None
+        raise ValueError(f"unknown mask mode {mask!r}")
+    torch = _torch()
+    m = mask
+    if m.dtype == torch.bool:
+        m = m.to(torch.uint8)
+    t = as_tensor(m)
+    return MASK_ARRAY, ctypes.byref(t), (m, t)
+
+
+# ---------------------------------------------------------------------------
+# cache classes
+# ---------------------------------------------------------------------------
+
+class KVCache:
+    """Base of the four cache classes; owns one kvc_cache handle."""
+
+    def __init__(self, handle: int, device=None):
+        self._h = ctypes.c_void_p(handle)
+        self._device = device
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            _lib.kvc_free(h)
+            self._h = None
+
+    @classmethod
+    def _create(cls, cfg: Config):
+        h = ctypes.c_void_p()
+        check(_lib.kvc_create(ctypes.byref(cfg), ctypes.byref(h)))
+        return h.value
+
+    @staticmethod
+    def _config(kind: int, **kw) -> Config:
+        cfg = Config()
+        _lib.kvc_config_default(ctypes.byref(cfg), kind)
+        for k, v in kw.items():
+            if v is not None:
+                setattr(cfg, k, v)
+        return cfg
+
+    def _dev(self, like=None):
+        if like is not None:
+            self._device = like.device
+        return self._device
+
+    # --- protocol surface -------------------------------------------------
+    @property
+    def offset(self) -> int:
+        return int(_lib.kvc_offset(self._h))
+
+    @offset.setter
+    def offset(self, n: int):
+        check(_lib.kvc_set_offset(self._h, n))
+
+    @property
+    def max_size(self) -> Optional[int]:
+        m = int(_lib.kvc_max_size(self._h))
+        return None if m < 0 else m
+
+    def update(self, keys, values, stream=None):
+        ok, ov = Tensor(), Tensor()
+        tk, tv = as_tensor(keys), as_tensor(values)
+        check(_lib.kvc_update(self._h, ctypes.byref(tk), ctypes.byref(tv), _stream_ptr(stream),
+                              ctypes.byref(ok), ctypes.byref(ov)))
+        dev = self._dev(keys)
+        return view_to_torch(ok, dev), view_to_torch(ov, dev)
+
+    @property
+    def state(self) -> List:
+        n = int(_lib.kvc_state_count(self._h))
+        out = []
+        for i in range(n):
+            t = Tensor()
+            check(_lib.kvc_state_get(self._h, i, ctypes.byref(t)))
+            out.append(view_to_torch(t, self._device))
+        return out
+
+    @state.setter
+    def state(self, arrays: Sequence):
+        arr = (Tensor * max(len(arrays), 1))()
+        for i, a in enumerate(arrays):
+            arr[i] = as_tensor(a)
+            self._device = a.device
+        check(_lib.kvc_state_set(self._h, arr, len(arrays), _stream_ptr()))
+
+    def export_state(self, index: int):
+        """Device -> host copy of state array `index` as a contiguous torch tensor."""
+        torch = _torch()
+        desc = Tensor()
+        check(_lib.kvc_state_export(self._h, index, None, 0, ctypes.byref(desc), _stream_ptr()))
+        shape = [int(desc.shape[i]) for i in range(desc.ndim)]
+        out = torch.empty(shape, dtype=_torch_dtype(desc.dtype))
+        check(_lib.kvc_state_export(self._h, index, out.data_ptr(), out.numel() * out.element_size(),
+                                    ctypes.byref(desc), _stream_ptr()))
+        return out
+
+    @property
+    def meta_state(self) -> List[str]:
+        n = ctypes.c_size_t()
+        check(_lib.kvc_meta_state(self._h, None, 0, ctypes.byref(n)))
+        buf = ctypes.create_string_buffer(n.value)
+        check(_lib.kvc_meta_state(self._h, buf, n.value, ctypes.byref(n)))
+        return buf.value.decode().split("\n")
+
+    @meta_state.setter
+    def meta_state(self, values: Sequence[str]):
+        check(_lib.kvc_set_meta_state(self._h, "\n".join(values).encode()))
+
+    @property
+    def is_trimmable(self) -> bool:
+        return bool(_lib.kvc_is_trimmable(self._h))
+
+    def is_trimmable_after(self, positions: int) -> bool:
+        return bool(_lib.kvc_is_trimmable_after(self._h, positions))
+
+    def trim(self, n: int) -> int:
+        out = ctypes.c_int64()
+        check(_lib.kvc_trim(self._h, n, ctypes.byref(out)))
+        return int(out.value)
+
+    def make_mask(self, n: int, window_size: Optional[int] = None, return_array: bool = False):
+        """Returns "none", "causal" or a bool tensor, like makeMask(n:windowSize:returnArray:)."""
+        torch = _torch()
+        mode, rows, cols = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64()
+        ws = -1 if window_size is None else window_size
+        check(_lib.kvc_make_mask(self._h, n, ws, int(return_array), ctypes.byref(mode), ctypes.byref(rows),
+                                 ctypes.byref(cols), None, None))
+        if mode.value == MASK_NONE:
+            return "none"
+        if mode.value == MASK_CAUSAL:
+            return "causal"
+        dev = self._device if self._device is not None else torch.device("cuda")
+        out = torch.empty((rows.value, cols.value), dtype=torch.uint8, device=dev)
+        check(_lib.kvc_make_mask(self._h, n, ws, int(return_array), ctypes.byref(mode), ctypes.byref(rows),
+                                 ctypes.byref(cols), out.data_ptr(), _stream_ptr()))
+        out = out.bool()
+        return out[0] if n == 1 else out
+
+    def copy(self):
+        h = ctypes.c_void_p()
+        check(_lib.kvc_copy(self._h, _stream_ptr(), ctypes.byref(h)))
+        new = object.__new__(type(self))
+        KVCache.__init__(new, h.value, self._device)
+        return new
+
+    def reserve(self, tokens: int, batch: int, kv_heads: int, head_dim: int, dtype, stream=None):
+        torch = _torch()
+        code = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[dtype]
+        check(_lib.kvc_reserve(self._h, tokens, batch, kv_heads, head_dim, code, _stream_ptr(stream)))
+
+    @property
+    def memory_bytes(self) -> int:
+        return int(_lib.kvc_memory_bytes(self._h))
+
+    def attention(self, queries, keys, values, scale: float, mask="none", out=None, stream=None):
+        """attentionWithCacheUpdate for this cache; returns [B, Hq, L, D] in the query dtype."""
+        torch = _torch()
+        self._dev(queries)
+        if out is None:
+            out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+        mode, mptr, _keep = _mask_args(mask)
+        tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+        check(_lib.kvc_attention(self._h, ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                 ctypes.c_float(scale), mode, mptr, ctypes.byref(to), _stream_ptr(stream)))
+        return out
+
+    def attention_host(self, queries, keys, values, scale: float, mask="none", out=None, stream=None,
+                       synchronize: bool = True):
+        """Same, with every tensor in host memory (the end-to-end entry point)."""
+        torch = _torch()
+        if out is None:
+            out = torch.empty(queries.shape, dtype=queries.dtype)
+        mode, mptr, _keep = _mask_args(mask)
+        tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+        check(_lib.kvc_attention_host(self._h, ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                      ctypes.c_float(scale), mode, mptr, ctypes.byref(to),
+                                      _stream_ptr(stream), 1 if synchronize else 0))
+        return out
+
+
+class KVCacheSimple(KVCache):
+    def __init__(self, step: int = 256, reserve_tokens: int = 0):
+        super().__init__(self._create(self._config(KIND_SIMPLE, step=step, reserve_tokens=reserve_tokens)))
+
+    def to_quantized(self, group_size: int = 64, bits: int = 4) -> "QuantizedKVCache":
+        h = ctypes.c_void_p()
+        check(_lib.kvc_to_quantized(self._h, group_size, bits, _stream_ptr(), ctypes.byref(h)))
+        new = object.__new__(QuantizedKVCache)
+        KVCache.__init__(new, h.value, self._device)
+        return new
+
+    def to_turbo(self, key_bits: int, value_bits: int, key_group_size: int = 64) -> "TurboQuantKVCache":
+        h = ctypes.c_void_p()
+        check(_lib.kvc_to_turbo(self._h, key_bits, value_bits, key_group_size, _stream_ptr(), ctypes.byref(h)))
+        new = object.__new__(TurboQuantKVCache)
+        KVCache.__init__(new, h.value, self._device)
+        return new
+
+
+class RotatingKVCache(KVCache):
+    def __init__(self, max_size: int, keep: int = 0, step: int = 256):
+        super().__init__(self._create(self._config(KIND_ROTATING, max_size=max_size, keep=keep, step=step)))
+
+    @property
+    def idx(self) -> int:
+        return int(_lib.kvc_ring_index(self._h))
+
+    def logical_view(self, tail: int, stream=None):
+        ok, ov = Tensor(), Tensor()
+        st = _lib.kvc_logical_view(self._h, tail, _stream_ptr(stream), ctypes.byref(ok), ctypes.byref(ov))
+        if st == ERR_INVALID_STATE:
+            return None
+        check(st)
+        return view_to_torch(ok, self._device), view_to_torch(ov, self._device)
+
+    def to_quantized(self, group_size: int = 64, bits: int = 4):
+        h = ctypes.c_void_p()
+        check(_lib.kvc_to_quantized(self._h, group_size, bits, _stream_ptr(), ctypes.byref(h)))
+
+    def rewind_last_round(self, count: int, stream=None) -> int:
+        out = ctypes.c_int64()
+        check(_lib.kvc_rewind_last_round(self._h, count, _stream_ptr(stream), ctypes.byref(out)))
+        return int(out.value)
+
+
+class QuantizedKVCache(KVCache):
+    def __init__(self, group_size: int = 64, bits: int = 8, reserve_tokens: int = 0):
+        super().__init__(self._create(self._config(KIND_QUANTIZED, group_size=group_size, bits=bits,
+                                                   reserve_tokens=reserve_tokens)))
+
+    @property
+    def group_size(self) -> int:
+        return int(_lib.kvc_group_size(self._h))
+
+    @property
+    def bits(self) -> int:
+        return int(_lib.kvc_bits(self._h))
+
+    def update_quantized(self, keys, values, stream=None):
+        ok, ov = (Tensor * 3)(), (Tensor * 3)()
+        tk, tv = as_tensor(keys), as_tensor(values)
+        check(_lib.kvc_update_quantized(self._h, ctypes.byref(tk), ctypes.byref(tv), _stream_ptr(stream), ok, ov))
+        dev = self._dev(keys)
+        return (tuple(view_to_torch(ok[i], dev) for i in range(3)),
+                tuple(view_to_torch(ov[i], dev) for i in range(3)))
+
+    def to_unquantized(self) -> KVCacheSimple:
+        h = ctypes.c_void_p()
+        check(_lib.kvc_to_unquantized(self._h, _stream_ptr(), ctypes.byref(h)))
+        new = object.__new__(KVCacheSimple)
+        KVCache.__init__(new, h.value, self._device)
+        return new
+
+
+class TurboQuantKVCache(KVCache):
+    def __init__(self, bits: int = 4, key_bits: Optional[int] = None, value_bits: Optional[int] = None,
+                 seed: int = 42, key_group_size: int = 64, affine_values: bool = False, reserve_tokens: int = 0):
+        super().__init__(self._create(self._config(
+            KIND_TURBO, bits=bits, key_bits=-1 if key_bits is None else key_bits,
+            value_bits=-1 if value_bits is None else value_bits, seed=seed, key_group_size=key_group_size,
+            turbo_affine_values=1 if affine_values else 0, reserve_tokens=reserve_tokens)))
+
+    @property
+    def is_compressed(self) -> bool:
+        return bool(_lib.kvc_is_compressed(self._h))
+
+    def set_codec(self, key_centroids=None, value_centroids=None, key_signs=None, value_signs=None, dim=0):
+        def arr(x):
+            if x is None:
+                return None
+            return (ctypes.c_float * len(x))(*[float(v) for v in x])
+        check(_lib.kvc_turbo_set_codec(self._h, arr(key_centroids), arr(value_centroids), arr(key_signs),
+                                       arr(value_signs), dim))
+
+    def compressed_attention(self, queries, keys, values, scale, mask="none", out=None, stream=None):
+        return self.attention(queries, keys, values, scale, mask, out, stream)
+
+
+class StagedRound:
+    """kvc_round: one cache's share of a speculative verify round."""
+
+    def __init__(self, cache: KVCache, max_positions: int):
+        h = ctypes.c_void_p()
+        check(_lib.kvc_round_begin(cache._h, max_positions, ctypes.byref(h)))
+        self._h = h
+        self.cache = cache
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            _lib.kvc_round_free(h)
+            self._h = None
+
+    @property
+    def offset(self) -> int:
+        return int(_lib.kvc_round_offset(self._h))
+
+    def update(self, keys, values, stream=None):
+        ok, ov = Tensor(), Tensor()
+        tk, tv = as_tensor(keys), as_tensor(values)
+        check(_lib.kvc_round_update(self._h, ctypes.byref(tk), ctypes.byref(tv), _stream_ptr(stream),
+                                    ctypes.byref(ok), ctypes.byref(ov)))
+        return view_to_torch(ok, keys.device), view_to_torch(ov, keys.device)
+
+    def attention(self, queries, keys, values, scale, mask="none", out=None, stream=None):
+        torch = _torch()
+        if out is None:
+            out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+        mode, mptr, _keep = _mask_args(mask)
+        tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+        check(_lib.kvc_round_attention(self._h, ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                       ctypes.c_float(scale), mode, mptr, ctypes.byref(to), _stream_ptr(stream)))
+        return out
+
+    def commit(self, retaining: int, stream=None):
+        check(_lib.kvc_round_commit(self._h, retaining, _stream_ptr(stream)))
+
+    def rollback(self, stream=None):
+        check(_lib.kvc_round_rollback(self._h, _stream_ptr(stream)))
+
+
+# ---------------------------------------------------------------------------
+# free functions
+# ---------------------------------------------------------------------------
+
+def attention_with_cache_update(queries, keys, values, cache: Optional[KVCache], scale: float, mask="none"):
+    """attentionWithCacheUpdate(queries:keys:values:cache:scale:mask:)."""
+    if cache is None:
+        return scaled_dot_product_attention(queries, keys, values, scale, mask)
+    return cache.attention(queries, keys, values, scale, mask)
+
+
+def scaled_dot_product_attention(queries, keys, values, scale: float, mask="none", out=None, stream=None):
+    torch = _torch()
+    if out is None:
+        out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+    mode, mptr, _keep = _mask_args(mask)
+    tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+    check(_lib.kvc_sdpa(ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv), ctypes.c_float(scale), mode, mptr,
+                        ctypes.byref(to), _stream_ptr(stream)))
+    return out
+
+
+def quantized_scaled_dot_product_attention(queries, quantized_keys, quantized_values, scale: float,
+                                           mask="none", group_size: int = 64, bits: int = 8, out=None,
+                                           stream=None):
+    torch = _torch()
+    if out is None:
+        out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+    mode, mptr, _keep = _mask_args(mask)
+    qk, qv = (Tensor * 3)(), (Tensor * 3)()
+    for i in range(3):
+        qk[i] = as_tensor(quantized_keys[i])
+        qv[i] = as_tensor(quantized_values[i])
+    tq, to = as_tensor(queries), as_tensor(out)
+    check(_lib.kvc_quantized_sdpa(ctypes.byref(tq), qk, qv, ctypes.c_float(scale), mode, mptr, group_size, bits,
+                                  ctypes.byref(to), _stream_ptr(stream)))
+    return out
+
+
+def quantized(x, group_size: int = 64, bits: int = 4, stream=None):
+    """MLX quantized(_:groupSize:bits:) -> (wq int32-viewed uint32, scales, biases)."""
+    torch = _torch()
+    D = x.shape[-1]
+    x = x.contiguous()
+    codes = torch.empty(x.shape[:-1] + (D * bits // 32,), dtype=torch.int32, device=x.device)
+    scales = torch.empty(x.shape[:-1] + (D // group_size,), dtype=x.dtype, device=x.device)
+    biases = torch.empty_like(scales)
+    tx, tc, ts, tb = as_tensor(x), as_tensor(codes), as_tensor(scales), as_tensor(biases)
+    check(_lib.kvc_affine_quantize(ctypes.byref(tx), group_size, bits, ctypes.byref(tc), ctypes.byref(ts),
+                                   ctypes.byref(tb), _stream_ptr(stream)))
+    return codes, scales, biases
+
+
+def dequantized(codes, scales, biases, group_size: int = 64, bits: int = 4, stream=None):
+    torch = _torch()
+    D = codes.shape[-1] * 32 // bits
+    out = torch.empty(codes.shape[:-1] + (D,), dtype=scales.dtype, device=codes.device)
+    tc, ts, tb, to = (as_tensor(codes.contiguous()), as_tensor(scales.contiguous()),
+                      as_tensor(biases.contiguous()), as_tensor(out))
+    check(_lib.kvc_affine_dequantize(ctypes.byref(tc), ctypes.byref(ts), ctypes.byref(tb), group_size, bits,
+                                     ctypes.byref(to), _stream_ptr(stream)))
+    return out
+
+
+def turbo_codebook(dim: int, bits: int) -> Tuple[List[float], List[float]]:
+    c = (ctypes.c_float * (1 << bits))()
+    b = (ctypes.c_float * ((1 << bits) - 1))()
+    check(_lib.kvc_turbo_codebook(dim, bits, c, b))
+    return list(c), list(b)
+
+
+def turbo_signs(dim: int, seed: int) -> List[float]:
+    s = (ctypes.c_float * dim)()
+    check(_lib.kvc_turbo_signs(dim, seed, s))
+    return list(s)
+
+
+def turbo_packed_width(count: int, bits: int) -> int:
+    return int(_lib.kvc_turbo_packed_width(count, bits))
+
+
+def turbo_encode(rows, signs, boundaries, bits: int, stream=None):
+    """fusedEncodeWHT: rows [N, D] -> (packed int32-viewed uint32 [N, PW], norms f32 [N])."""
+    torch = _torch()
+    rows = rows.contiguous()
+    n, D = rows.shape
+    pw = turbo_packed_width(D, bits)
+    packed = torch.empty((n, pw), dtype=torch.int32, device=rows.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=rows.device)
+    signs_dev = torch.as_tensor(signs, dtype=torch.float32, device=rows.device).contiguous()
+    b = (ctypes.c_float * len(boundaries))(*[float(v) for v in boundaries])
+    tr, tp, tn = as_tensor(rows), as_tensor(packed), as_tensor(norms)
+    check(_lib.kvc_turbo_encode(ctypes.byref(tr), signs_dev.data_ptr(), b, bits, ctypes.byref(tp),
+                                ctypes.byref(tn), _stream_ptr(stream)))
+    return packed, norms
+
+
+def trim_prompt_cache(caches: Sequence[KVCache], num_tokens: int) -> int:
+    arr = (_vp * len(caches))(*[c._h for c in caches])
+    out = ctypes.c_int64()
+    check(_lib.kvc_trim_prompt_cache(arr, len(caches), num_tokens, ctypes.byref(out)))
+    return int(out.value)
+
+
+def can_trim_prompt_cache(caches: Sequence[KVCache]) -> bool:
+    arr = (_vp * len(caches))(*[c._h for c in caches])
+    return bool(_lib.kvc_can_trim_prompt_cache(arr, len(caches)))
+
+
+class Comm:
+    """kvc_comm: NCCL communicator for KV-head / batch sharded attention."""
+
+    def __init__(self, rank: int, world: int, unique_id: bytes):
+        h = ctypes.c_void_p()
+        check(_lib.kvc_comm_init(rank, world, unique_id, ctypes.byref(h)))
+        self._h = h
+        self.rank, self.world = rank, world
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = ctypes.create_string_buffer(128)
+        check(_lib.kvc_comm_unique_id(buf))
+        return buf.raw
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            _lib.kvc_comm_free(h)
+            self._h = None
+
+    def attention_sharded(self, cache: KVCache, queries, keys, values, scale, out_full, mask="none",
+                          shard_axis: int = 1, stream=None):
+        mode, mptr, _keep = _mask_args(mask)
+        tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out_full)
+        check(_lib.kvc_attention_sharded(self._h, cache._h, ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv),
+                                         ctypes.c_float(scale), mode, mptr, ctypes.byref(to), shard_axis,
+                                         _stream_ptr(stream)))
+        return out_full

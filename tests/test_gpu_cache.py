@@ -1,0 +1,219 @@
+"""GPU parity: cache contents, ring indices, metaState and packed affine codes
+produced by the CUDA library through its C ABI must be bit-identical to the CPU
+oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+import scenarios as sc
+from helpers import bits_equal, from_oracle, seeded, to_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be(kvc, cuda):
+    return sc.GpuBackend(kvc, cuda)
+
+
+@pytest.mark.parametrize("scenario", sc.ALL_SIMPLE, ids=lambda f: f.__name__)
+def test_reference_cache_semantics(be, scenario):
+    scenario(be)
+
+
+@pytest.mark.parametrize("case", sc.COMMIT_CASES, ids=lambda c: f"w{c['window']}p{c['prefill']}k{c.get('keep', 0)}")
+def test_commit_equivalence(be, case):
+    sc.commit_equivalence(be, **case)
+
+
+@pytest.mark.parametrize("case", sc.REWIND_CASES, ids=lambda c: f"w{c['window']}p{c['prefill']}r{c['rewinding']}k{c.get('keep', 0)}")
+def test_rewind(be, case):
+    sc.rewind_matches_emitted_only_replay(be, **case)
+
+
+def _same_state(gpu_cache, ora_cache):
+    gs, os_ = gpu_cache.state, ora_cache.state
+    assert len(gs) == len(os_)
+    for g, o in zip(gs, os_):
+        assert tuple(g.shape) == tuple(o.shape), (g.shape, o.shape)
+        assert bits_equal(g, np.ascontiguousarray(o))
+    assert gpu_cache.offset == ora_cache.offset
+    assert list(gpu_cache.meta_state) == list(ora_cache.meta_state)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_simple_cache_append_growth_trim(kvc, oracle, cuda, dtype):
+    B, H, D = 2, 3, 64
+    g, o = kvc.KVCacheSimple(step=16), oracle.KVCacheSimple(step=16)
+    seed = 0
+    for S in (5, 1, 1, 16, 40, 1, 7):
+        k, v = seeded((B, H, S, D), seed, dtype), seeded((B, H, S, D), seed + 1, dtype)
+        seed += 2
+        gk, gv = g.update(k.to(cuda), v.to(cuda))
+        ok, ov = o.update(to_oracle(k), to_oracle(v))
+        assert bits_equal(gk, np.ascontiguousarray(ok)) and bits_equal(gv, np.ascontiguousarray(ov))
+        _same_state(g, o)
+    assert g.trim(9) == o.trim(9)
+    k, v = seeded((B, H, 3, D), 99, dtype), seeded((B, H, 3, D), 100, dtype)
+    g.update(k.to(cuda), v.to(cuda))
+    o.update(to_oracle(k), to_oracle(v))
+    _same_state(g, o)
+    assert g.trim(10_000) == o.trim(10_000) and g.offset == 0
+    cp = g.copy()
+    _same_state(cp, o)
+
+
+def test_simple_cache_accepts_strided_inputs(kvc, oracle, cuda):
+    # models hand over keys as a transposed [B, S, H, D] projection
+    B, H, S, D = 2, 4, 6, 32
+    base_k, base_v = seeded((B, S, H, D), 1, torch.bfloat16), seeded((B, S, H, D), 2, torch.bfloat16)
+    k, v = base_k.to(cuda).transpose(1, 2), base_v.to(cuda).transpose(1, 2)
+    assert not k.is_contiguous()
+    g, o = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    g.update(k, v)
+    o.update(to_oracle(base_k.transpose(1, 2).contiguous()), to_oracle(base_v.transpose(1, 2).contiguous()))
+    _same_state(g, o)
+    # and an inner stride != 1 (element-wise path)
+    wide = seeded((B, H, S, 2 * D), 3, torch.float32).to(cuda)
+    g2, o2 = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    g2.update(wide[..., ::2], wide[..., 1::2])
+    o2.update(to_oracle(wide[..., ::2].contiguous()), to_oracle(wide[..., 1::2].contiguous()))
+    _same_state(g2, o2)
+
+
+@pytest.mark.parametrize("keep", [0, 3])
+def test_rotating_cache_random_walk(kvc, oracle, cuda, keep):
+    """Mixed single/multi-token writes and pre-wrap trims: physical ring, idx,
+    offset and metaState identical after every step."""
+    rng = np.random.default_rng(keep)
+    B, H, D, W = 2, 2, 32, 24
+    g, o = kvc.RotatingKVCache(W, keep, step=8), oracle.RotatingKVCache(W, keep, step=8)
+    seed = 10
+    for step in range(60):
+        S = int(rng.choice([1, 1, 1, 2, 5, 30]))
+        k, v = seeded((B, H, S, D), seed, torch.bfloat16), seeded((B, H, S, D), seed + 1, torch.bfloat16)
+        seed += 2
+        gk, gv = g.update(k.to(cuda), v.to(cuda))
+        ok, ov = o.update(to_oracle(k), to_oracle(v))
+        assert tuple(gk.shape) == tuple(ok.shape)
+        assert bits_equal(gk, np.ascontiguousarray(ok)) and bits_equal(gv, np.ascontiguousarray(ov))
+        _same_state(g, o)
+        assert g.idx == o.idx
+        if o.is_trimmable_after(0) and o.offset > 2 and rng.random() < 0.3 and o.idx >= 2:
+            assert g.trim(2) == o.trim(2)
+            _same_state(g, o)
+        for n, w in ((1, None), (1, 8), (4, None), (4, 8)):
+            gm, om = g.make_mask(n, w), o.make_mask(n, w)
+            if isinstance(om, str):
+                assert gm == om
+            else:
+                assert np.array_equal(gm.cpu().numpy(), om)
+
+
+def test_rotating_window_config_shape(kvc, oracle, cuda):
+    """Sliding-window benchmark shape scaled down: chunked prefill past the
+    window, then decode with wraparound, head_dim 256, bf16."""
+    B, H, D, W = 2, 1, 256, 64
+    g, o = kvc.RotatingKVCache(W), oracle.RotatingKVCache(W)
+    seed = 0
+    for _ in range(4):
+        k, v = seeded((B, H, 64, D), seed, torch.bfloat16), seeded((B, H, 64, D), seed + 1, torch.bfloat16)
+        seed += 2
+        g.update(k.to(cuda), v.to(cuda))
+        o.update(to_oracle(k), to_oracle(v))
+        _same_state(g, o)
+    for _ in range(2 * W + 5):
+        k, v = seeded((B, H, 1, D), seed, torch.bfloat16), seeded((B, H, 1, D), seed + 1, torch.bfloat16)
+        seed += 2
+        g.update(k.to(cuda), v.to(cuda))
+        o.update(to_oracle(k), to_oracle(v))
+    _same_state(g, o)
+    # the list-level trim is all-or-nothing and refuses a wrapped ring (KVCache.swift:2302-2306)
+    simple = kvc.KVCacheSimple()
+    simple.update(k.to(cuda), v.to(cuda))
+    assert not kvc.can_trim_prompt_cache([simple, g])
+    assert kvc.trim_prompt_cache([simple, g], 64) == 0 and simple.offset == 1
+    assert kvc.trim_prompt_cache([simple], 64) == 1
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("bits", [8, 4, 2])
+@pytest.mark.parametrize("D,group", [(64, 64), (128, 64), (128, 32), (256, 128), (32, 64), (96, 32)])
+def test_affine_codes_bit_exact(kvc, oracle, cuda, dtype, bits, D, group):
+    B, H = 2, 2
+    g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
+    seed = 0
+    for S in (9, 1, 1, 300, 1):
+        k = seeded((B, H, S, D), seed, dtype, outlier_frac=0.05)
+        v = seeded((B, H, S, D), seed + 1, dtype)
+        if S == 9:
+            k[:, :, 0] = 0          # degenerate all-equal group
+            v[:, :, 1] = 1.5
+            k[:, :, 2] = -k[:, :, 2].abs()
+        seed += 2
+        gq = g.update_quantized(k.to(cuda), v.to(cuda))
+        oq = o.update_quantized(to_oracle(k), to_oracle(v))
+        for gt, ot in zip(gq[0] + gq[1], oq[0] + oq[1]):
+            assert bits_equal(gt, np.ascontiguousarray(ot))
+    assert g.group_size == o.group_size
+    _same_state(g, o)
+    cp = g.copy()
+    _same_state(cp, o)
+    g.trim(7); o.trim(7)
+    _same_state(g, o)
+
+
+def test_quantized_cache_rejects_what_the_reference_rejects(kvc, cuda):
+    q = kvc.QuantizedKVCache()
+    x = torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(kvc.KVCError) as e:
+        q.update(x, x)  # KVCache.swift:1106-1110
+    assert e.value.status == kvc.ERR_INVALID_STATE
+    bad = torch.zeros(1, 2, 4, 5, dtype=torch.float32, device=cuda)
+    with pytest.raises(kvc.KVCError):
+        q.update_quantized(bad, bad)
+    s = kvc.KVCacheSimple()
+    s.state = [bad, bad]
+    with pytest.raises(kvc.KVCError):
+        s.to_quantized(64, 4)  # KVCacheTests.swift:538-551
+    with pytest.raises(kvc.KVCError):
+        kvc.RotatingKVCache(32).to_quantized()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_to_quantized_and_back(kvc, oracle, cuda, dtype):
+    B, H, T, D = 2, 2, 37, 128
+    k, v = seeded((B, H, T, D), 5, dtype), seeded((B, H, T, D), 6, dtype)
+    g, o = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    g.update(k.to(cuda), v.to(cuda))
+    o.update(to_oracle(k), to_oracle(v))
+    gq, oq = g.to_quantized(64, 4), o.to_quantized(64, 4)
+    _same_state(gq, oq)
+    gu, ou = gq.to_unquantized(), oq.to_unquantized()
+    _same_state(gu, ou)
+    codes, scales, biases = kvc.quantized(k.to(cuda), 64, 4)
+    oc, os_, ob = oracle.affine_quantize(to_oracle(k), 64, 4)
+    assert bits_equal(codes, oc) and bits_equal(scales, os_) and bits_equal(biases, ob)
+    deq = kvc.dequantized(codes, scales, biases, 64, 4)
+    assert bits_equal(deq, oracle.affine_dequantize(oc, os_, ob, 64, 4))
+
+
+def test_state_round_trip_and_export(kvc, oracle, cuda):
+    B, H, T, D = 2, 2, 20, 64
+    k, v = seeded((B, H, T, D), 7, torch.bfloat16), seeded((B, H, T, D), 8, torch.bfloat16)
+    g = kvc.KVCacheSimple()
+    g.update(k.to(cuda), v.to(cuda))
+    host = g.export_state(0)
+    assert host.shape == (B, H, T, D) and torch.equal(host, k)
+    fresh = kvc.KVCacheSimple()
+    fresh.state = g.state
+    assert fresh.offset == T and torch.equal(fresh.export_state(1), v)
+    r = kvc.RotatingKVCache(8)
+    for t in range(11):
+        r.update(k[:, :, t:t + 1].to(cuda), v[:, :, t:t + 1].to(cuda))
+    r2 = kvc.RotatingKVCache(8)
+    r2.state = r.state
+    r2.meta_state = r.meta_state
+    assert list(r2.meta_state) == list(r.meta_state)
+    assert torch.equal(r2.export_state(0), r.export_state(0))
+    assert g.memory_bytes > 0

@@ -1,0 +1,112 @@
+"""GPU parity for the TurboQuant path: packed codebook indices and norms are
+bit-identical to the oracle's Walsh-Hadamard encode; compressed attention
+(decode and the multi-token causal verify chunk) is within tolerance."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_library_codebook_and_signs_match_the_oracle(kvc, oracle):
+    for dim in (64, 128, 256):
+        for bits in (2, 3, 4):
+            c, b = kvc.turbo_codebook(dim, bits)
+            ref = oracle.generate_centroids(dim, bits)
+            assert np.max(np.abs(np.array(c, dtype=np.float32) - ref)) < 2e-4
+            assert len(b) == (1 << bits) - 1 and all(b[i] < b[i + 1] for i in range(len(b) - 1))
+        assert np.array_equal(np.array(kvc.turbo_signs(dim, 42), dtype=np.float32), oracle.wht_signs(dim, 42))
+    assert kvc.turbo_packed_width(128, 3) == 12 and kvc.turbo_packed_width(128, 4) == 16
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("D", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_turbo_encode_bit_exact(kvc, oracle, cuda, dtype, D, bits):
+    rows = 517
+    x = seeded((rows, D), D + bits, dtype, outlier_frac=0.02)
+    x[3] = 0                      # zero row: norm floor
+    x[4] = x[4].abs()             # one-sided row
+    x[5, 1:] = 0                  # a single spike
+    signs = oracle.wht_signs(D, 42)
+    cb = np.array(kvc.turbo_codebook(D, bits)[0], dtype=np.float32)
+    bounds = oracle.boundaries_of(cb)
+    packed, norms = kvc.turbo_encode(x.to(cuda), signs, bounds, bits)
+    rp, rn = oracle.turbo_encode(to_oracle(x), signs, bounds, bits)
+    assert bits_equal(norms, rn), "norms differ"
+    assert bits_equal(packed, rp), "packed indices differ"
+
+
+def _pair(kvc, oracle, **kw):
+    g = kvc.TurboQuantKVCache(**kw)
+    kb = kw.get("key_bits", kw.get("bits", 4))
+    vb = kw.get("value_bits", kw.get("bits", 4))
+    return g, kb, vb
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kw", [dict(bits=4), dict(bits=4, key_bits=3, value_bits=4), dict(bits=3),
+                                dict(bits=4, key_bits=0, value_bits=4), dict(bits=4, key_bits=8, value_bits=3),
+                                dict(bits=4, key_bits=3, value_bits=4, affine_values=True)],
+                         ids=["turbo4", "k3v4", "turbo3", "turbo0v4", "turbo8v3", "k3-affine-v4"])
+def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
+    B, Hq, Hkv, D, P = 2, 8, 2, 128, 250
+    g = kvc.TurboQuantKVCache(**kw)
+    kcb = np.array(kvc.turbo_codebook(D, kw.get("key_bits", kw["bits"]))[0], dtype=np.float32) if kw.get("key_bits", kw["bits"]) in (1, 2, 3, 4) else None
+    vcb = np.array(kvc.turbo_codebook(D, kw.get("value_bits", kw["bits"]))[0], dtype=np.float32) if not kw.get("affine_values") else None
+    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    scale = D ** -0.5
+    q, k, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype), seeded((B, Hkv, P, D), 3, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")      # raw prefill + plain SDPA
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert not g.is_compressed and g.offset == P
+    for step in range(12):                                                     # crosses the 256-row boundary
+        q, k, v = (seeded((B, Hq, 1, D), 10 + 3 * step, dtype), seeded((B, Hkv, 1, D), 11 + 3 * step, dtype),
+                   seeded((B, Hkv, 1, D), 12 + 3 * step, dtype))
+        out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"decode step {step}"
+    assert g.is_compressed and g.offset == o.offset == P + 12
+    L = 6                                                                       # 5 draft tokens + bonus
+    q, k, v = seeded((B, Hq, L, D), 90, dtype), seeded((B, Hkv, L, D), 91, dtype), seeded((B, Hkv, L, D), 92, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype], "verify chunk"
+    assert g.trim(L - 2) == o.trim(L - 2)                                       # reject 4 of the 6
+    gs, os_ = g.state, o.state
+    assert len(gs) == len(os_)
+    for a, b in zip(gs, os_):
+        assert tuple(a.shape) == tuple(b.shape) and bits_equal(a, np.ascontiguousarray(b))
+    assert list(g.meta_state) == list(o.meta_state)
+    mask = torch.ones((1, 1, 1, g.offset + 1), dtype=torch.bool)
+    mask[..., ::3] = False
+    q, k, v = seeded((B, Hq, 1, D), 95, dtype), seeded((B, Hkv, 1, D), 96, dtype), seeded((B, Hkv, 1, D), 97, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, mask.to(cuda))
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, mask.numpy())
+    assert max_abs_diff(out, ref) <= TOL[dtype], "array mask"
+    assert g.trim(10_000) == o.trim(10_000) and g.offset == 0 and not g.is_compressed and g.state == []
+
+
+def test_turbo_starts_compressed_when_first_call_is_decode(kvc, oracle, cuda):
+    B, Hq, Hkv, D = 1, 4, 1, 64
+    g = kvc.TurboQuantKVCache(bits=4)
+    cb = np.array(kvc.turbo_codebook(D, 4)[0], dtype=np.float32)
+    o = oracle.TurboQuantKVCache(bits=4, key_codebook=cb, value_codebook=cb)
+    for step in range(5):
+        q, k, v = seeded((B, Hq, 1, D), step, torch.float32), seeded((B, Hkv, 1, D), 50 + step, torch.float32), seeded((B, Hkv, 1, D), 70 + step, torch.float32)
+        out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.125)
+        ref = o.compressed_attention(to_oracle(q), to_oracle(k), to_oracle(v), 0.125)
+        assert max_abs_diff(out, ref) <= 1e-4
+    assert g.is_compressed and len(g.state) == 4
+
+
+def test_simple_to_turbo_conversion(kvc, cuda):
+    s = kvc.KVCacheSimple()
+    k = seeded((1, 2, 9, 64), 1, torch.bfloat16).to(cuda)
+    s.update(k, k)
+    t = s.to_turbo(4, 4)
+    assert t.offset == 9 and not t.is_compressed and len(t.state) == 2
+    assert torch.equal(t.state[0], s.state[0])
