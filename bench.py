@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""KV-cache decode benchmark.
+
+One "step" is one decode step of the workload: every layer appends one new
+token per sequence to its cache and attends over the whole cache
+(attentionWithCacheUpdate per layer). The headline metric is decode tokens/s
+(batch tokens per step / step time) together with the achieved HBM bandwidth
+of the dominant attention kernel against the measured copy peak.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Under torchrun (N > 1) the KV heads (or, when there are fewer heads than GPUs,
+the batch) are sharded across ranks and every layer ends with an all-gather of
+the attention outputs; total work is fixed, so scaling is "strong".
+Inputs are synthetic (seeded N(0,1)); no dataset is involved.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "mlx-swift-lm_b200", "python"), os.path.join(ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "kv_cache_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+# Shapes are BASELINE.json's configs; `context` is the cache length when the
+# timed decode starts.
+WORKLOADS = {
+    "cfg2_simple_bf16_llama3_8b": dict(kind="simple", layers=32, Hq=32, Hkv=8, D=128, B=8, dtype="bf16",
+                                       context=8192, chunk=512),
+    "cfg1_quant8_f32_llama32_1b": dict(kind="quantized", bits=8, group=64, layers=16, Hq=32, Hkv=8, D=64, B=1,
+                                       dtype="f32", context=1024, chunk=1024),
+    "cfg4_quant4_bf16_qwen2_7b": dict(kind="quantized", bits=4, group=64, layers=28, Hq=28, Hkv=4, D=128, B=32,
+                                      dtype="bf16", context=17408, chunk=512),
+    "cfg5_turbo_k3v4_llama3_70b": dict(kind="turbo", key_bits=3, value_bits=4, layers=80, Hq=64, Hkv=8, D=128,
+                                       B=16, dtype="bf16", context=32768, chunk=512),
+}
+DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
+
+
+def bytes_per_token_head(w) -> float:
+    """Algorithmic bytes of K plus V for one cached token of one KV head."""
+    D = w["D"]
+    es = 4 if w["dtype"] == "f32" else 2
+    if w["kind"] in ("simple", "rotating"):
+        return 2 * D * es
+    if w["kind"] == "quantized":
+        per = D * w["bits"] / 8 + 2 * (D // w["group"]) * es
+        return 2 * per
+    kpw = (D * w["key_bits"] + 31) // 32 * 4 + 4
+    vpw = (D * w["value_bits"] + 31) // 32 * 4 + 4
+    return kpw + vpw
+
+
+def torch_dtype(name):
+    import torch
+    return {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[name]
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+
+    def summary(self, t0: float, t1: float):
+        sel = [r for ts, r in self.rows if t0 <= ts <= t1 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not sel:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(r[1]) for r in sel if r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in sel if r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in sel:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sel)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (the oracle, timed): reference implementation of the path on host cores
+# ---------------------------------------------------------------------------
+
+def cpu_decode_step_time(w, budget_s: float, steps: int = 1, warmup: int = 0):
+    """Times the oracle's decode step (append + attention per layer) on a bounded
+    sample: `layers_sample` layer calls per step over one layer's cache arrays,
+    scaled to the workload's layer count. Returns (seconds per full step, info)."""
+    import numpy as np
+    import kvcache_oracle as orc
+
+    orc.build()
+    B, Hq, Hkv, D, T0 = w["B"], w["Hq"], w["Hkv"], w["D"], w["context"]
+    rng = np.random.default_rng(0)
+    es_dtype = np.float32 if w["dtype"] == "f32" else np.uint16
+
+    def rnd(shape):
+        x = rng.standard_normal(shape, dtype=np.float32)
+        return x if w["dtype"] == "f32" else orc.f32_to_bf16_bits(x)
+
+    cap = T0 + 64
+    q = rnd((B, Hq, 1, D))
+    nk, nv = rnd((B, Hkv, 1, D)), rnd((B, Hkv, 1, D))
+    scale = D ** -0.5
+    if w["kind"] == "simple":
+        K = np.empty((B, Hkv, cap, D), dtype=es_dtype)
+        V = np.empty((B, Hkv, cap, D), dtype=es_dtype)
+        blk = rnd((B, Hkv, 1024, D))
+        for t in range(0, cap, 1024):
+            n = min(1024, cap - t)
+            K[:, :, t:t + n] = blk[:, :, :n]
+            V[:, :, t:t + n] = blk[:, :, :n]
+
+        def layer_call(T):
+            orc.append_rows(nk, K, T)
+            orc.append_rows(nv, V, T)
+            return orc.attention(q, orc.RawSource(K[:, :, :T + 1]), orc.RawSource(V[:, :, :T + 1]), scale, precise=False)
+    elif w["kind"] == "quantized":
+        blk = rnd((B, Hkv, 1024, D))
+        qk = orc.affine_quantize(blk, w["group"], w["bits"])
+        reps = (cap + 1023) // 1024
+        ck = [np.ascontiguousarray(np.concatenate([a] * reps, axis=2)[:, :, :cap]) for a in qk]
+        cv = [a.copy() for a in ck]
+
+        def layer_call(T):
+            nq = orc.affine_quantize(nk, w["group"], w["bits"])
+            nq2 = orc.affine_quantize(nv, w["group"], w["bits"])
+            for i in range(3):
+                ck[i][:, :, T:T + 1] = nq[i]
+                cv[i][:, :, T:T + 1] = nq2[i]
+            return orc.attention(q, orc.AffineSource(*(a[:, :, :T + 1] for a in ck), w["group"], w["bits"]),
+                                 orc.AffineSource(*(a[:, :, :T + 1] for a in cv), w["group"], w["bits"]), scale,
+                                 precise=False)
+    else:
+        kc = orc.MSECodec(D, w["key_bits"], 42)
+        vc = orc.MSECodec(D, w["value_bits"], 43)
+        blk = rnd((B, Hkv, 1024, D))
+        kp, kn = kc.encode(blk)
+        vp, vn = vc.encode(blk)
+        reps = (cap + 1023) // 1024
+        KP = np.ascontiguousarray(np.concatenate([kp] * reps, axis=2)[:, :, :cap])
+        KN = np.ascontiguousarray(np.concatenate([kn] * reps, axis=2)[:, :, :cap])
+        VP = np.ascontiguousarray(np.concatenate([vp] * reps, axis=2)[:, :, :cap])
+        VN = np.ascontiguousarray(np.concatenate([vn] * reps, axis=2)[:, :, :cap])
+
+        def layer_call(T):
+            a, b = kc.encode(nk)
+            c, d = vc.encode(nv)
+            KP[:, :, T:T + 1], KN[:, :, T:T + 1], VP[:, :, T:T + 1], VN[:, :, T:T + 1] = a, b, c, d
+            return orc.attention(q, orc.TurboSource(KP[:, :, :T + 1], KN[:, :, :T + 1], kc.codebook, w["key_bits"]),
+                                 orc.TurboSource(VP[:, :, :T + 1], VN[:, :, :T + 1], vc.codebook, w["value_bits"]),
+                                 scale, q_signs=kc.signs, o_signs=vc.signs, precise=False)
+
+    t0 = time.perf_counter()
+    layer_call(T0)
+    t_layer = time.perf_counter() - t0
+    total_calls = max(1, int(budget_s / max(t_layer, 1e-6)))
+    per_step = max(1, min(w["layers"], total_calls // max(1, steps + warmup)))
+    times = []
+    T = T0
+    for s in range(warmup + steps):
+        t0 = time.perf_counter()
+        for _ in range(per_step):
+            layer_call(T)
+        dt = time.perf_counter() - t0
+        T = min(T + 1, cap - 2)
+        if s >= warmup:
+            times.append(dt * w["layers"] / per_step)
+    info = {"cores": orc.num_threads(),
+            "sample": f"{per_step} of {w['layers']} layer calls per step (append + attention over one layer's "
+                      f"cache at context {T0}), scaled to {w['layers']} layers; {steps} timed steps"}
+    return sum(times) / len(times), info
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    sec, info = cpu_decode_step_time(w, budget_s=90.0, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    value = w["B"] / sec
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "impl": "reference",
+            "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D", "B", "context")},
+                       "timing": "CPU restatement of the reference path (MLX itself is unavailable on this box)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def make_cache(kvc, w, reserve):
+    if w["kind"] == "simple":
+        return kvc.KVCacheSimple(step=256, reserve_tokens=reserve)
+    if w["kind"] == "quantized":
+        return kvc.QuantizedKVCache(w["group"], w["bits"], reserve_tokens=reserve)
+    if w["kind"] == "turbo":
+        return kvc.TurboQuantKVCache(bits=max(w["key_bits"], w["value_bits"]), key_bits=w["key_bits"],
+                                     value_bits=w["value_bits"], reserve_tokens=reserve)
+    raise ValueError(w["kind"])
+
+
+def fill_cache(kvc, cache, w, Bl, Hl, chunk_k, chunk_v):
+    remaining = w["context"]
+    while remaining > 0:
+        n = min(remaining, chunk_k.shape[2])
+        k, v = chunk_k[:, :, :n], chunk_v[:, :, :n]
+        if w["kind"] == "simple":
+            cache.update(k, v)
+        elif w["kind"] == "quantized":
+            cache.update_quantized(k, v)
+        else:
+            cache.append_compressed(k, v)
+        remaining -= n
+
+
+def run_ours(args, w, rank, world, local_rank):
+    import torch
+    import kvcache_b200 as kvc
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (the library has no CPU fallback)"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    dtype = torch_dtype(w["dtype"])
+    B, Hq, Hkv, D, Lyr = w["B"], w["Hq"], w["Hkv"], w["D"], w["layers"]
+    # partition: KV heads across ranks, batch when there are fewer heads than ranks
+    if Hkv % world == 0 and Hkv >= world:
+        shard_axis, Bl, Hkvl, Hql = 1, B, Hkv // world, Hq // world
+        parallelism = f"kv-head x{world}" if world > 1 else "single"
+    else:
+        assert B % world == 0, "batch must divide across ranks when heads do not"
+        shard_axis, Bl, Hkvl, Hql = 0, B // world, Hkv, Hq
+        parallelism = f"batch x{world}"
+    steps, warmup = args.steps, args.warmup
+    total_steps = warmup + steps * 2 + 64
+    reserve = w["context"] + total_steps + 8
+
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    chunk = min(w["chunk"], w["context"])
+    chunk_k = torch.randn((Bl, Hkvl, chunk, D), generator=g).to(dtype).to(dev)
+    chunk_v = torch.randn((Bl, Hkvl, chunk, D), generator=g).to(dtype).to(dev)
+    caches = [make_cache(kvc, w, reserve) for _ in range(Lyr)]
+    for c in caches:
+        fill_cache(kvc, c, w, Bl, Hkvl, chunk_k, chunk_v)
+    torch.cuda.synchronize()
+
+    # per-layer step inputs, resident in HBM
+    qs = [torch.randn((Bl, Hql, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    ks = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    vs = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    scale = D ** -0.5
+    comm = None
+    if world > 1:
+        uid = [kvc.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = kvc.Comm(rank, world, uid[0])
+        outs = [torch.empty((B, Hq, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+    else:
+        outs = [torch.empty((Bl, Hql, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+    step = kvc.DecodeStep(caches, qs, ks, vs, outs, scale)
+
+    def one_step():
+        if comm is not None:
+            step.run_sharded(comm, shard_axis)
+        else:
+            step.run()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    barrier()
+    ctx0 = caches[0].offset
+    kvc.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    barrier()
+    w1 = time.perf_counter()
+    launches = kvc.launch_count()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = ms_total / steps
+    value = B * steps / (ms_total * 1e-3)
+    time.sleep(0.15)
+    sampler.stop()
+    clocks = sampler.summary(w0, w1)
+
+    # roofline pass: bracket the dominant attention kernel with events
+    kvc.timing_enable(True)
+    kvc.timing_read(reset=True)
+    rsteps = min(steps, 16)
+    ctx_r0 = caches[0].offset
+    for _ in range(rsteps):
+        one_step()
+    torch.cuda.synchronize()
+    k_ms, k_n = kvc.timing_read(reset=True)
+    kvc.timing_enable(False)
+    ctx_mid = ctx_r0 + (rsteps + 1) / 2
+    es = 4 if w["dtype"] == "f32" else 2
+    alg_bytes = Bl * Hkvl * ctx_mid * bytes_per_token_head(w) + 2 * Bl * Hql * D * es
+    k_avg_ms = k_ms / max(k_n, 1)
+    achieved = alg_bytes / (k_avg_ms * 1e-3) / 1e9 if k_n else None
+    peak, peak_src = 6545.0, "fallback 6545 GB/s (MEASURED_PEAKS.json absent)"
+    mp = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(mp):
+        try:
+            peak = float(json.load(open(mp))["hbm_gbs"])
+            peak_src = "MEASURED_PEAKS.json hbm_gbs (measured copy)"
+        except Exception:
+            pass
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "kernel": "attention partial (dominant)", "launch_ms": k_avg_ms, "launches_timed": k_n,
+                "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_src}
+
+    # end to end through the host-buffer entry point
+    hq = [torch.randn((Bl, Hql, 1, D), generator=g).to(dtype).pin_memory() for _ in range(Lyr)]
+    hk = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).pin_memory() for _ in range(Lyr)]
+    hv = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).pin_memory() for _ in range(Lyr)]
+    ho = [torch.empty((Bl, Hql, 1, D), dtype=dtype).pin_memory() for _ in range(Lyr)]
+    hstep = kvc.DecodeStep(caches, hq, hk, hv, ho, scale, host=True)
+    for _ in range(min(warmup, 3)):
+        hstep.run(synchronize=True)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        hstep.run(synchronize=True)
+        _ = float(ho[-1][0, 0, 0, 0])  # the step's result is read on the host
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    h2d = Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es
+    d2h = Lyr * Bl * Hql * D * es
+    e2e = {"value": B * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "note": "kvc_attention_host per layer (pinned host q/k/v in, output out), one stream sync per step"
+                   + ("; per-rank shard only, no gather" if world > 1 else "")}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, info = cpu_decode_step_time(w, budget_s=15.0, steps=1, warmup=0)
+        cpu_baseline = {"value": B / sec, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": w["dtype"], "data": "synthetic",
+                "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D", "B")},
+                           "context_start": ctx0, "parallelism": parallelism,
+                           "l2": "inputs larger than L2 (per-layer K+V working set "
+                                 f"{Bl * Hkvl * ctx0 * bytes_per_token_head(w) / 1e6:.0f} MB; all layers "
+                                 f"{Lyr * Bl * Hkvl * ctx0 * bytes_per_token_head(w) / 1e9:.2f} GB per step)"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
+                "cpu_baseline": cpu_baseline}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    run_ours(args, w, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -214,8 +214,7 @@ kvc_status kvc_attention(kvc_cache *cache, const kvc_tensor *queries, const kvc_
  * inputs, kvc_attention, and the device-to-host copy of the result on `stream`.
  * With synchronize != 0 the call returns after the result has landed in
  * `out`; with 0 the caller synchronises the stream itself (e.g. once per
- * decode step). When queries, keys and values sit back to back in host memory
- * (each padded to 256 bytes) they travel in a single copy. */
+ * decode step). */
 kvc_status kvc_attention_host(kvc_cache *cache, const kvc_tensor *queries, const kvc_tensor *keys,
                               const kvc_tensor *values, float scale, int32_t mask_mode,
                               const kvc_tensor *mask, const kvc_tensor *out, void *stream,
@@ -391,6 +390,13 @@ kvc_status kvc_attention_sharded(kvc_comm *comm, kvc_cache *cache, const kvc_ten
                                  int32_t mask_mode, const kvc_tensor *mask,
                                  const kvc_tensor *out_full, int32_t shard_axis, void *stream);
 
+/* kvc_attention_sharded on caches[i] for i in [0, count): the layers of one
+ * decode step, each followed by its all-gather, issued back to back. */
+kvc_status kvc_attention_sharded_batch(kvc_comm *comm, kvc_cache *const *caches, int32_t count,
+                                       const kvc_tensor *queries, const kvc_tensor *keys,
+                                       const kvc_tensor *values, float scale, int32_t mask_mode,
+                                       const kvc_tensor *outs_full, int32_t shard_axis, void *stream);
+
 /* ------------------------------------------------------------------ */
 /* instrumentation                                                     */
 /* ------------------------------------------------------------------ */
@@ -398,6 +404,25 @@ kvc_status kvc_attention_sharded(kvc_comm *comm, kvc_cache *cache, const kvc_ten
 /* Number of kernels this library launched from the calling thread since the
  * last reset; pass reset != 0 to zero the counter after reading it. */
 int64_t    kvc_launch_count(int32_t reset);
+
+/* The calls one decode step makes, issued back to back: kvc_attention (or,
+ * with host != 0, kvc_attention_host) on caches[i] with q[i], k[i], v[i],
+ * outs[i] for i in [0, count). This is the loop over layers of
+ * TokenIterator.step (Evaluate.swift:905-916) as a native caller would run it;
+ * mask arrays are not supported here. synchronize != 0 waits for the stream
+ * once at the end. */
+kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kvc_tensor *queries,
+                               const kvc_tensor *keys, const kvc_tensor *values, float scale,
+                               int32_t mask_mode, const kvc_tensor *outs, void *stream,
+                               int32_t host, int32_t synchronize);
+
+/* Event timing of the dominant attention kernel. While enabled, every
+ * attention call brackets its main kernel (not the merge or append kernels)
+ * with CUDA events on the launching stream; kvc_timing_read waits for the
+ * recorded events and returns the accumulated milliseconds and launch count.
+ * Off by default; meant for a dedicated measurement pass. */
+void       kvc_timing_enable(int32_t on);
+kvc_status kvc_timing_read(double *total_ms, int64_t *launches, int32_t reset);
 
 #ifdef __cplusplus
 }

@@ -351,8 +351,10 @@ int launch_attention_general(const AttnArgs &a, cudaStream_t stream) {
     }
     KVC_REQUIRE(a.Hkv * row_chunks <= 65535 && a.B <= 65535, "attention: grid too large");
     dim3 grid((unsigned)splits, (unsigned)(a.Hkv * row_chunks), (unsigned)a.B);
+    KernelTimer timer(stream);
     attn_general_partial<<<grid, G_THREADS, smem, stream>>>(a, o_part, ml_part, splits,
                                                             tokens_per_split, row_chunks);
+    timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
     launch_merge(o_part, ml_part, splits, a, stream);

@@ -322,16 +322,9 @@ kvc_status kvc_attention_host(kvc_cache *c, const kvc_tensor *q, const kvc_tenso
         // one staging slab: q | k | v | out
         char *slab = (char *)stage_get(c, 0, al(qb) + al(kb) + al(vb) + al(ob), s);
         char *dq = slab, *dk = dq + al(qb), *dv = dk + al(kb), *dout = dv + al(vb);
-        const bool adjacent = (const char *)k->data == (const char *)q->data + al(qb) &&
-                              (const char *)v->data == (const char *)k->data + al(kb);
-        if (adjacent) {
-            // the caller laid q, k, v out back to back (256-byte aligned): one copy
-            KVC_CUDA(cudaMemcpyAsync(dq, q->data, al(qb) + al(kb) + vb, cudaMemcpyHostToDevice, s));
-        } else {
-            KVC_CUDA(cudaMemcpyAsync(dq, q->data, qb, cudaMemcpyHostToDevice, s));
-            KVC_CUDA(cudaMemcpyAsync(dk, k->data, kb, cudaMemcpyHostToDevice, s));
-            KVC_CUDA(cudaMemcpyAsync(dv, v->data, vb, cudaMemcpyHostToDevice, s));
-        }
+        KVC_CUDA(cudaMemcpyAsync(dq, q->data, qb, cudaMemcpyHostToDevice, s));
+        KVC_CUDA(cudaMemcpyAsync(dk, k->data, kb, cudaMemcpyHostToDevice, s));
+        KVC_CUDA(cudaMemcpyAsync(dv, v->data, vb, cudaMemcpyHostToDevice, s));
         kvc_tensor tq = *q, tk = *k, tv = *v, to = *out, tm;
         tq.data = dq; tk.data = dk; tv.data = dv; to.data = dout;
         const kvc_tensor *pm = nullptr;
@@ -797,6 +790,30 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev, cons
         for (int i = 0; i < (1 << bits) - 1; ++i) a.boundaries[i] = boundaries_host[i];
         kvc::launch_turbo_encode(a, as_stream(stream));
     });
+}
+
+kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kvc_tensor *q,
+                               const kvc_tensor *k, const kvc_tensor *v, float scale,
+                               int32_t mask_mode, const kvc_tensor *outs, void *stream,
+                               int32_t host, int32_t synchronize) {
+    if (!caches || !q || !k || !v || !outs) return set_error(KVC_ERR_INVALID_ARG, "kvc_attention_batch: null argument");
+    for (int i = 0; i < count; ++i) {
+        kvc_status st = host ? kvc_attention_host(caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
+                                                  &outs[i], stream, 0)
+                             : kvc_attention(caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
+                                             &outs[i], stream);
+        if (st != KVC_OK) return st;
+    }
+    if (synchronize) {
+        return guarded([&] { KVC_CUDA(cudaStreamSynchronize(as_stream(stream))); });
+    }
+    return KVC_OK;
+}
+
+void kvc_timing_enable(int32_t on) { kvc::timing_set(on != 0); }
+
+kvc_status kvc_timing_read(double *total_ms, int64_t *launches, int32_t reset) {
+    return guarded([&] { kvc::timing_read(total_ms, launches, reset != 0); });
 }
 
 int64_t kvc_launch_count(int32_t reset) {

@@ -217,4 +217,18 @@ kvc_status kvc_attention_sharded(kvc_comm *comm, kvc_cache *cache, const kvc_ten
     }
 }
 
+kvc_status kvc_attention_sharded_batch(kvc_comm *comm, kvc_cache *const *caches, int32_t count,
+                                       const kvc_tensor *q, const kvc_tensor *k, const kvc_tensor *v,
+                                       float scale, int32_t mask_mode, const kvc_tensor *outs_full,
+                                       int32_t shard_axis, void *stream) {
+    if (!caches || !q || !k || !v || !outs_full)
+        return kvc_internal_set_error(KVC_ERR_INVALID_ARG, "kvc_attention_sharded_batch: null argument");
+    for (int i = 0; i < count; ++i) {
+        kvc_status st = kvc_attention_sharded(comm, caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
+                                              &outs_full[i], shard_axis, stream);
+        if (st != KVC_OK) return st;
+    }
+    return KVC_OK;
+}
+
 }  // extern "C"

@@ -213,4 +213,24 @@ void launch_rolled_mask(uint8_t *out, int64_t size, int64_t window, int64_t shif
 // last reset (benchmarks report it).
 extern thread_local int64_t g_launch_count;
 
+// Event timing of the dominant attention kernel (off unless a benchmark enables it).
+bool timing_enabled();
+void timing_set(bool on);
+void timing_begin(cudaStream_t s, cudaEvent_t *start, cudaEvent_t *stop);
+void timing_end(cudaStream_t s, cudaEvent_t start, cudaEvent_t stop);
+void timing_read(double *total_ms, int64_t *launches, bool reset);
+
+struct KernelTimer {
+    cudaStream_t s;
+    cudaEvent_t a = nullptr, b = nullptr;
+    bool on;
+    explicit KernelTimer(cudaStream_t stream) : s(stream), on(timing_enabled()) {
+        if (on) timing_begin(s, &a, &b);
+    }
+    void stop() {
+        if (on) timing_end(s, a, b);
+        on = false;
+    }
+};
+
 }  // namespace kvc

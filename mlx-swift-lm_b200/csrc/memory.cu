@@ -101,3 +101,62 @@ void *scratch_get(int device, size_t bytes, cudaStream_t stream) {
 }
 
 }  // namespace kvc
+
+// ---------------------------------------------------------------------
+// Optional timing of the dominant attention kernel: when enabled, the launch
+// wrappers bracket that one kernel with CUDA events on the launching stream.
+// Off by default; benchmarks switch it on for a dedicated roofline pass.
+// ---------------------------------------------------------------------
+namespace kvc {
+namespace {
+struct TimingState {
+    bool on = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pool;
+    double total_ms = 0;
+    int64_t launches = 0;
+};
+TimingState g_timing;
+}  // namespace
+
+bool timing_enabled() { return g_timing.on; }
+
+void timing_set(bool on) {
+    g_timing.on = on;
+}
+
+void timing_begin(cudaStream_t s, cudaEvent_t *start, cudaEvent_t *stop) {
+    if (!g_timing.pool.empty()) {
+        *start = g_timing.pool.back().first;
+        *stop = g_timing.pool.back().second;
+        g_timing.pool.pop_back();
+    } else {
+        KVC_CUDA(cudaEventCreate(start));
+        KVC_CUDA(cudaEventCreate(stop));
+    }
+    KVC_CUDA(cudaEventRecord(*start, s));
+}
+
+void timing_end(cudaStream_t s, cudaEvent_t start, cudaEvent_t stop) {
+    KVC_CUDA(cudaEventRecord(stop, s));
+    g_timing.pending.emplace_back(start, stop);
+}
+
+void timing_read(double *total_ms, int64_t *launches, bool reset) {
+    for (auto &p : g_timing.pending) {
+        KVC_CUDA(cudaEventSynchronize(p.second));
+        float ms = 0.f;
+        KVC_CUDA(cudaEventElapsedTime(&ms, p.first, p.second));
+        g_timing.total_ms += ms;
+        g_timing.launches += 1;
+        g_timing.pool.push_back(p);
+    }
+    g_timing.pending.clear();
+    if (total_ms) *total_ms = g_timing.total_ms;
+    if (launches) *launches = g_timing.launches;
+    if (reset) {
+        g_timing.total_ms = 0;
+        g_timing.launches = 0;
+    }
+}
+}  // namespace kvc

@@ -126,6 +126,13 @@ _lib.kvc_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctyp
 _lib.kvc_can_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32]
 _lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
 _lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
+_lib.kvc_attention_batch.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP, ctypes.c_float,
+                                     ctypes.c_int32, _TP, _vp, ctypes.c_int32, ctypes.c_int32]
+_lib.kvc_attention_sharded_batch.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP,
+                                             ctypes.c_float, ctypes.c_int32, _TP, ctypes.c_int32, _vp]
+_lib.kvc_timing_enable.argtypes = [ctypes.c_int32]
+_lib.kvc_timing_enable.restype = None
+_lib.kvc_timing_read.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int64), ctypes.c_int32]
 
 
 def lib() -> ctypes.CDLL:
@@ -640,6 +647,48 @@ def turbo_encode(rows, signs, boundaries, bits: int, stream=None):
     check(_lib.kvc_turbo_encode(ctypes.byref(tr), signs_dev.data_ptr(), b, bits, ctypes.byref(tp),
                                 ctypes.byref(tn), _stream_ptr(stream)))
     return packed, norms
+
+
+class DecodeStep:
+    """Pre-marshalled arguments of one decode step over a list of caches.
+
+    The tensors of every layer are described once; `run()` then issues the
+    whole step with a single C call (kvc_attention_batch), which is how a native
+    caller would drive the per-layer calls without interpreter overhead.
+    """
+
+    def __init__(self, caches: Sequence[KVCache], queries, keys, values, outs, scale: float,
+                 mask: str = "none", host: bool = False):
+        n = len(caches)
+        assert len(queries) == len(keys) == len(values) == len(outs) == n
+        self._keep = (list(caches), list(queries), list(keys), list(values), list(outs))
+        self.n = n
+        self.handles = (_vp * n)(*[c._h for c in caches])
+        self.q = (Tensor * n)(*[as_tensor(t) for t in queries])
+        self.k = (Tensor * n)(*[as_tensor(t) for t in keys])
+        self.v = (Tensor * n)(*[as_tensor(t) for t in values])
+        self.o = (Tensor * n)(*[as_tensor(t) for t in outs])
+        self.scale = ctypes.c_float(scale)
+        self.mode = {"none": MASK_NONE, "causal": MASK_CAUSAL}[mask]
+        self.host = 1 if host else 0
+
+    def run(self, stream=None, synchronize: bool = False):
+        check(_lib.kvc_attention_batch(self.handles, self.n, self.q, self.k, self.v, self.scale, self.mode,
+                                       self.o, _stream_ptr(stream), self.host, 1 if synchronize else 0))
+
+    def run_sharded(self, comm: "Comm", shard_axis: int = 1, stream=None):
+        check(_lib.kvc_attention_sharded_batch(comm._h, self.handles, self.n, self.q, self.k, self.v, self.scale,
+                                               self.mode, self.o, shard_axis, _stream_ptr(stream)))
+
+
+def timing_enable(on: bool) -> None:
+    _lib.kvc_timing_enable(1 if on else 0)
+
+
+def timing_read(reset: bool = True) -> Tuple[float, int]:
+    ms, n = ctypes.c_double(), ctypes.c_int64()
+    check(_lib.kvc_timing_read(ctypes.byref(ms), ctypes.byref(n), 1 if reset else 0))
+    return float(ms.value), int(n.value)
 
 
 def trim_prompt_cache(caches: Sequence[KVCache], num_tokens: int) -> int:
