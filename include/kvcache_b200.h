@@ -416,6 +416,14 @@ kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kv
                                int32_t mask_mode, const kvc_tensor *outs, void *stream,
                                int32_t host, int32_t synchronize);
 
+/* Device-side waits in the attention kernels (on shared-memory barriers fed
+ * by TMA) are bounded. A wait that runs out stores a non-zero code in a
+ * per-device status word instead of spinning forever; this call copies the
+ * word of the current device back (synchronising with it). 0 = no wait ever
+ * ran out; -1 = the word could not be read. The affected call's output is
+ * undefined when the status is non-zero (KVC_ERR_TIMEOUT territory). */
+int32_t    kvc_device_status(void);
+
 /* Event timing of the dominant attention kernel. While enabled, every
  * attention call brackets its main kernel (not the merge or append kernels)
  * with CUDA events on the launching stream; kvc_timing_read waits for the

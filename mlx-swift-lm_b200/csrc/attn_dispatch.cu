@@ -2,11 +2,27 @@
 // the shape and representation match one, the general kernel otherwise.
 #include "common.h"
 
+#include <cstdlib>
+
 namespace kvc {
 
 int launch_attention_general(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
+
+namespace {
+// KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
+// compare the two paths on the device).
+bool force_general() {
+    const char *e = std::getenv("KVC_ATTENTION_PATH");
+    return e && e[0] == 'g';
+}
+}  // namespace
 
 int launch_attention(const AttnArgs &a, cudaStream_t stream) {
+    if (!force_general()) {
+        int n = launch_attention_decode(a, stream);
+        if (n > 0) return n;
+    }
     return launch_attention_general(a, stream);
 }
 

@@ -1,0 +1,90 @@
+"""The specialised decode kernel (TMA-staged, tensor-core) against the oracle and
+against the general kernel, on the shapes the benchmark configurations use."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, max_abs_diff, seeded, to_oracle
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,D,T", [
+    (8, 32, 8, 128, 777),      # Llama-3-8B attention shape
+    (4, 4, 1, 256, 512),       # Gemma-3-1B local layer, full window
+    (4, 4, 1, 256, 37),
+    (1, 32, 8, 64, 1280),      # Llama-3.2-1B
+    (2, 28, 4, 128, 3000),     # Qwen2-7B: 7 query heads per KV head
+    (2, 64, 8, 128, 4097),     # Llama-3-70B: 8 query heads per KV head
+    (1, 16, 1, 128, 200),      # 16 rows: the full MMA tile
+    (3, 8, 2, 128, 1), (3, 8, 2, 128, 63), (3, 8, 2, 128, 64), (3, 8, 2, 128, 65),
+])
+def test_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, D, T):
+    q = seeded((B, Hq, 1, D), 1, dtype)
+    k, v = seeded((B, Hkv, T, D), 2, dtype), seeded((B, Hkv, T, D), 3, dtype)
+    out = kvc.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5)
+    ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), D ** -0.5)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_decode_kernel_reads_strided_cache_views(kvc, oracle, cuda):
+    """The cache hands the kernel views whose head stride is the capacity, not the length."""
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    cache = kvc.KVCacheSimple(reserve_tokens=4096)
+    o = oracle.KVCacheSimple()
+    for step, S in enumerate((700, 1, 1, 1)):
+        q, k, v = (seeded((B, Hq, 1, D), 3 * step, torch.bfloat16), seeded((B, Hkv, S, D), 3 * step + 1, torch.bfloat16),
+                   seeded((B, Hkv, S, D), 3 * step + 2, torch.bfloat16))
+        if S > 1:
+            cache.update(k.to(cuda), v.to(cuda))
+            o.update(to_oracle(k), to_oracle(v))
+            continue
+        out = cache.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.09)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, 0.09)
+        assert max_abs_diff(out, ref) <= 2e-2
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_small_causal_chunk_on_the_decode_kernel(kvc, oracle, cuda):
+    # 2 query heads per KV head x 6 positions = 12 rows: still one MMA tile
+    B, Hq, Hkv, D, L, T = 2, 4, 2, 128, 6, 333
+    q = seeded((B, Hq, L, D), 5, torch.bfloat16)
+    k, v = seeded((B, Hkv, T, D), 6, torch.bfloat16), seeded((B, Hkv, T, D), 7, torch.bfloat16)
+    out = kvc.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.1, "causal")
+    ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), 0.1, "causal")
+    assert max_abs_diff(out, ref) <= 2e-2
+
+
+def test_general_and_decode_kernels_agree():
+    """Same inputs through both device paths (the general one forced by the
+    environment switch in a child process)."""
+    code = r"""
+import os, sys, torch
+sys.path.insert(0, os.path.join(%r, "mlx-swift-lm_b200", "python"))
+sys.path.insert(0, os.path.join(%r, "tests"))
+import kvcache_b200 as kvc
+from helpers import seeded
+dev = torch.device("cuda:0")
+q = seeded((2, 32, 1, 128), 1, torch.bfloat16).to(dev)
+k = seeded((2, 8, 2049, 128), 2, torch.bfloat16).to(dev)
+v = seeded((2, 8, 2049, 128), 3, torch.bfloat16).to(dev)
+out = kvc.scaled_dot_product_attention(q, k, v, 0.088)
+torch.save(out.float().cpu(), sys.argv[1])
+print(kvc.launch_count())
+""" % (ROOT, ROOT)
+    outs = []
+    for path in ("decode", "general"):
+        env = dict(os.environ)
+        env["KVC_ATTENTION_PATH"] = path
+        f = f"/tmp/kvc_path_{path}.pt"
+        subprocess.run([sys.executable, "-c", code, f], check=True, env=env, timeout=300)
+        outs.append(torch.load(f))
+    assert float((outs[0] - outs[1]).abs().max()) <= 2e-2
