@@ -45,6 +45,9 @@ WORKLOADS = {
     "cfg5_turbo_k3v4_llama3_70b": dict(kind="turbo", key_bits=3, value_bits=4, layers=80, Hq=64, Hkv=8, D=128,
                                        B=16, dtype="bf16", context=32768, chunk=512),
 }
+# Two layers of the default workload: the small case for multi-pass ncu captures
+# (per-layer working set 269 MB > L2, 0.6 GB on the device).
+WORKLOADS["cfg2_profile_2layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=2)
 DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
 
 
