@@ -1,0 +1,235 @@
+// Swift face of libkvcache_b200: classes with the member names of
+// MLXLMCommon's KVCache protocol (Libraries/MLXLMCommon/KVCache.swift:46-104)
+// that forward to the C ABI in kvcache_b200.h. In the mlx-swift-lm tree these
+// classes adopt `KVCache` / `QuantizedKVCacheProtocol` directly; here the
+// array type is abstracted as `DeviceArray` so the file compiles without MLX.
+//
+// Not compiled in this repository's build image (no Swift toolchain); the C ABI
+// underneath is what the test-suite exercises.
+import CKVCacheB200
+
+/// What the wrapper needs from an array type: a device pointer, a dtype, a shape
+/// and element strides. `MLXArray` on a CUDA backend provides all four.
+public protocol DeviceArray {
+    var devicePointer: UnsafeMutableRawPointer? { get }
+    var kvcDType: Int32 { get }
+    var shape: [Int] { get }
+    var elementStrides: [Int] { get }
+    /// Wrap library-owned memory (a view into the cache) without copying.
+    static func view(_ t: kvc_tensor) -> Self
+    static func empty(shape: [Int], kvcDType: Int32) -> Self
+}
+
+public struct KVCacheB200Error: Error, CustomStringConvertible {
+    public let status: Int32
+    public let description: String
+}
+
+@inline(__always)
+func check(_ status: kvc_status) throws {
+    if status != 0 {
+        let msg = kvc_last_error_message().map { String(cString: $0) } ?? "unknown error"
+        throw KVCacheB200Error(status: status, description: msg)
+    }
+}
+
+/// The reference traps on programmer errors (fatalError / precondition); the
+/// wrapper keeps that convention for the non-throwing protocol members.
+@inline(__always)
+func must(_ status: kvc_status) {
+    do { try check(status) } catch { fatalError("\(error)") }
+}
+
+func describe<A: DeviceArray>(_ a: A) -> kvc_tensor {
+    var t = kvc_tensor()
+    t.data = a.devicePointer
+    t.dtype = a.kvcDType
+    t.ndim = Int32(a.shape.count)
+    withUnsafeMutablePointer(to: &t.shape) { p in
+        p.withMemoryRebound(to: Int64.self, capacity: 5) { s in
+            for (i, d) in a.shape.enumerated() { s[i] = Int64(d) }
+        }
+    }
+    withUnsafeMutablePointer(to: &t.stride) { p in
+        p.withMemoryRebound(to: Int64.self, capacity: 5) { s in
+            for (i, d) in a.elementStrides.enumerated() { s[i] = Int64(d) }
+        }
+    }
+    return t
+}
+
+public enum MaskMode<A: DeviceArray> {
+    case none, causal
+    case array(A)
+}
+
+/// Base class: owns one kvc_cache handle. Mirrors BaseKVCache (KVCache.swift:184-251).
+open class B200KVCache<A: DeviceArray> {
+    let handle: OpaquePointer
+    public var stream: UnsafeMutableRawPointer? = nil
+
+    init(config: kvc_config) {
+        var cfg = config
+        var h: OpaquePointer? = nil
+        must(kvc_create(&cfg, &h))
+        handle = h!
+    }
+
+    init(adopting h: OpaquePointer) { handle = h }
+
+    deinit { kvc_free(handle) }
+
+    public var offset: Int {
+        get { Int(kvc_offset(handle)) }
+        set { must(kvc_set_offset(handle, Int64(newValue))) }
+    }
+
+    public var maxSize: Int? {
+        let m = kvc_max_size(handle)
+        return m < 0 ? nil : Int(m)
+    }
+
+    /// update(keys:values:) -> (keys, values): views of the cached arrays.
+    public func update(keys: A, values: A) -> (A, A) {
+        var k = describe(keys), v = describe(values)
+        var ok = kvc_tensor(), ov = kvc_tensor()
+        must(kvc_update(handle, &k, &v, stream, &ok, &ov))
+        return (A.view(ok), A.view(ov))
+    }
+
+    public var state: [A] {
+        get {
+            (0 ..< Int(kvc_state_count(handle))).map { i in
+                var t = kvc_tensor()
+                must(kvc_state_get(handle, Int32(i), &t))
+                return A.view(t)
+            }
+        }
+        set {
+            var arrays = newValue.map(describe)
+            must(kvc_state_set(handle, &arrays, Int32(arrays.count), stream))
+        }
+    }
+
+    public var metaState: [String] {
+        get {
+            var n = 0
+            must(kvc_meta_state(handle, nil, 0, &n))
+            var buf = [CChar](repeating: 0, count: n)
+            must(kvc_meta_state(handle, &buf, n, &n))
+            return String(cString: buf).split(separator: "\n", omittingEmptySubsequences: false).map(String.init)
+        }
+        set { must(kvc_set_meta_state(handle, newValue.joined(separator: "\n"))) }
+    }
+
+    public var isTrimmable: Bool { kvc_is_trimmable(handle) != 0 }
+    public func isTrimmable(after positions: Int) -> Bool { kvc_is_trimmable_after(handle, Int64(positions)) != 0 }
+
+    @discardableResult
+    public func trim(_ n: Int) -> Int {
+        var t: Int64 = 0
+        must(kvc_trim(handle, Int64(n), &t))
+        return Int(t)
+    }
+
+    public func copy() -> B200KVCache<A> {
+        var h: OpaquePointer? = nil
+        must(kvc_copy(handle, stream, &h))
+        return B200KVCache<A>(adopting: h!)
+    }
+
+    /// attentionWithCacheUpdate for this cache (AttentionUtils.swift:37-95).
+    public func attention(queries: A, keys: A, values: A, scale: Float, mask: MaskMode<A> = .none) -> A {
+        let out = A.empty(shape: queries.shape, kvcDType: queries.kvcDType)
+        var q = describe(queries), k = describe(keys), v = describe(values), o = describe(out)
+        switch mask {
+        case .none: must(kvc_attention(handle, &q, &k, &v, scale, Int32(KVC_MASK_NONE.rawValue), nil, &o, stream))
+        case .causal: must(kvc_attention(handle, &q, &k, &v, scale, Int32(KVC_MASK_CAUSAL.rawValue), nil, &o, stream))
+        case .array(let m):
+            var mt = describe(m)
+            must(kvc_attention(handle, &q, &k, &v, scale, Int32(KVC_MASK_ARRAY.rawValue), &mt, &o, stream))
+        }
+        return out
+    }
+}
+
+func defaults(_ kind: kvc_kind) -> kvc_config {
+    var cfg = kvc_config()
+    kvc_config_default(&cfg, Int32(kind.rawValue))
+    return cfg
+}
+
+public final class KVCacheSimpleB200<A: DeviceArray>: B200KVCache<A> {
+    public init(step: Int = 256) {
+        var cfg = defaults(KVC_KIND_SIMPLE)
+        cfg.step = Int32(step)
+        super.init(config: cfg)
+    }
+
+    public func toQuantized(groupSize: Int = 64, bits: Int = 4) throws -> QuantizedKVCacheB200<A> {
+        var h: OpaquePointer? = nil
+        try check(kvc_to_quantized(handle, Int32(groupSize), Int32(bits), stream, &h))
+        return QuantizedKVCacheB200<A>(adopting: h!)
+    }
+}
+
+public final class RotatingKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    public init(maxSize: Int, keep: Int = 0, step: Int = 256) {
+        var cfg = defaults(KVC_KIND_ROTATING)
+        cfg.max_size = Int32(maxSize)
+        cfg.keep = Int32(keep)
+        cfg.step = Int32(step)
+        super.init(config: cfg)
+    }
+
+    /// logicalView(tail:) (KVCache.swift:631-658); nil before the first write.
+    public func logicalView(tail: Int) -> (A, A)? {
+        var k = kvc_tensor(), v = kvc_tensor()
+        let st = kvc_logical_view(handle, Int64(tail), stream, &k, &v)
+        if st == KVC_ERR_INVALID_STATE { return nil }
+        must(st)
+        return (A.view(k), A.view(v))
+    }
+}
+
+public final class QuantizedKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    public init(groupSize: Int = 64, bits: Int = 8) {
+        var cfg = defaults(KVC_KIND_QUANTIZED)
+        cfg.group_size = Int32(groupSize)
+        cfg.bits = Int32(bits)
+        super.init(config: cfg)
+    }
+
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
+    public var groupSize: Int { Int(kvc_group_size(handle)) }
+    public var bits: Int { Int(kvc_bits(handle)) }
+
+    /// updateQuantized(keys:values:) (KVCache.swift:1011-1102).
+    public func updateQuantized(keys: A, values: A) -> ((A, A, A?), (A, A, A?)) {
+        var k = describe(keys), v = describe(values)
+        var ok = [kvc_tensor](repeating: kvc_tensor(), count: 3)
+        var ov = [kvc_tensor](repeating: kvc_tensor(), count: 3)
+        must(kvc_update_quantized(handle, &k, &v, stream, &ok, &ov))
+        return ((A.view(ok[0]), A.view(ok[1]), A.view(ok[2])), (A.view(ov[0]), A.view(ov[1]), A.view(ov[2])))
+    }
+}
+
+public final class TurboQuantKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    public init(bits: Int = 4, keyBits: Int? = nil, valueBits: Int? = nil, seed: UInt64 = 42, keyGroupSize: Int = 64) {
+        var cfg = defaults(KVC_KIND_TURBO)
+        cfg.bits = Int32(bits)
+        cfg.key_bits = Int32(keyBits ?? -1)
+        cfg.value_bits = Int32(valueBits ?? -1)
+        cfg.seed = seed
+        cfg.key_group_size = Int32(keyGroupSize)
+        super.init(config: cfg)
+    }
+
+    public var isCompressed: Bool { kvc_is_compressed(handle) != 0 }
+
+    /// compressedAttention(queries:keys:values:scale:mask:) (TurboQuantKVCache.swift:1164-1446).
+    public func compressedAttention(queries: A, keys: A, values: A, scale: Float, mask: MaskMode<A> = .none) -> A {
+        attention(queries: queries, keys: keys, values: values, scale: scale, mask: mask)
+    }
+}
