@@ -227,6 +227,25 @@ kvc_status kvc_sdpa(const kvc_tensor *queries, const kvc_tensor *keys, const kvc
                     float scale, int32_t mask_mode, const kvc_tensor *mask,
                     const kvc_tensor *out, void *stream);
 
+/* kvc_sdpa without any allocation. No counterpart in the reference.
+ * For hosts that must keep the CUDA allocator off the request path: a server
+ * whose own pool owns the device's memory budget, or a decoder that cannot
+ * tolerate the device-wide synchronisation of cudaMalloc/cudaFree. The
+ * regular entry points keep split-K partials in an arena that grows on demand;
+ * this one keeps them in a fixed 4 MiB array inside the library's device image
+ * (present on every GPU that loads the library, until the process exits), and
+ * it calls no cudaMalloc, cudaFree or other allocating routine.
+ * Limits: raw f32/f16/bf16 K/V contiguous along the head dim, D <= 256, mask
+ * none or causal, and B*Hq*L*(4*D+8) + 256 bytes must fit the array; larger
+ * calls are rejected with KVC_ERR_INVALID_ARG (use kvc_sdpa for those).
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current; make that call before any
+ * stream capture. All calls share the array: calls whose kernels can overlap
+ * on the GPU race on it, so keep them on one stream or order them. */
+kvc_status kvc_sdpa_noalloc(const kvc_tensor *queries, const kvc_tensor *keys,
+                            const kvc_tensor *values, float scale, int32_t mask_mode,
+                            const kvc_tensor *out, void *stream);
+
 /* quantizedScaledDotProductAttention(queries:quantizedKeys:quantizedValues:scale:mask:groupSize:bits:mode:)
  *   KVCache.swift:2351-2447.  qk/qv: (codes u32, scales, biases). */
 kvc_status kvc_quantized_sdpa(const kvc_tensor *queries, const kvc_tensor qk[3],

@@ -30,6 +30,7 @@ SOURCES = [
     "round.cu",
     "capi.cu",
     "comm.cu",
+    "noalloc.cu",
 ]
 
 NVCC_FLAGS = [

@@ -87,6 +87,7 @@ _lib.kvc_attention_host.argtypes = [_vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c
                                     ctypes.c_int32]
 _lib.kvc_round_attention.argtypes = [_vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp]
 _lib.kvc_sdpa.argtypes = [_TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP, _vp]
+_lib.kvc_sdpa_noalloc.argtypes = [_TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _vp]
 _lib.kvc_quantized_sdpa.argtypes = [_TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, ctypes.c_int32,
                                     ctypes.c_int32, _TP, _vp]
 _lib.kvc_attention_sharded.argtypes = [_vp, _vp, _TP, _TP, _TP, ctypes.c_float, ctypes.c_int32, _TP, _TP,
@@ -571,6 +572,21 @@ def scaled_dot_product_attention(queries, keys, values, scale: float, mask="none
     tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
     check(_lib.kvc_sdpa(ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv), ctypes.c_float(scale), mode, mptr,
                         ctypes.byref(to), _stream_ptr(stream)))
+    return out
+
+
+def scaled_dot_product_attention_noalloc(queries, keys, values, scale: float, mask="none", out=None,
+                                         stream=None):
+    """kvc_sdpa_noalloc: same result as scaled_dot_product_attention, but the library
+    allocates nothing (split partials live in a fixed array of the device image).
+    `out` should be supplied by callers that must not allocate themselves."""
+    torch = _torch()
+    if out is None:
+        out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+    mode, _mptr, _keep = _mask_args(mask)
+    tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+    check(_lib.kvc_sdpa_noalloc(ctypes.byref(tq), ctypes.byref(tk), ctypes.byref(tv), ctypes.c_float(scale), mode,
+                                ctypes.byref(to), _stream_ptr(stream)))
     return out
 
 
