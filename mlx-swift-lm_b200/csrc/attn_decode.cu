@@ -4,20 +4,24 @@
 // four consumer warps streams its token range through a ring of shared-memory
 // stages: the producer issues tiled TMA loads (cp.async.bulk.tensor, 128-byte
 // swizzle) of K and V tiles straight from the cache arrays and signals an
-// mbarrier per stage; each consumer warp owns 16 of a tile's 64 tokens, scores all
-// query rows of the GQA group against them with m16n8k16 tensor-core MMAs
+// mbarrier per stage; each consumer warp owns 16 of a tile's 64 tokens, scores
+// all query rows of the GQA group against them with m16n8k16 tensor-core MMAs
 // (queries are the 16-row A operand, so every K/V byte is read from HBM and
 // from shared memory exactly once for the whole group), keeps an online
 // softmax in registers and accumulates P.V with a second MMA. The four warps'
-// states are merged in shared memory and written as one un-normalised partial
-// per unit; the log-sum-exp merge kernel combines the splits.
+// states are merged in shared memory into one un-normalised partial per unit.
+// The last unit of a (batch, head) to finish - found with a ticket counter -
+// merges the partials of all splits with a log-sum-exp reduction and writes
+// the output row, so no second kernel is needed.
 //
-// Shared-memory layout of a tile: boxes of [tokens][64 elements] (128 bytes
-// per row), 16-byte chunk c of row r stored at chunk c ^ (r & 7). The operand
-// fragments are built from whole 16-byte chunks: the k-slot <-> head-dim
-// assignment of the Q.K^T MMAs and the column <-> head-dim assignment of the
-// P.V MMAs are permutations chosen so that every lane reads full chunks and
-// every quarter-warp touches all eight chunk columns (no bank conflicts).
+// Shared-memory layout of a tile: boxes of [64 tokens][64 elements] (128 bytes
+// per row), 16-byte chunk c of row r stored at chunk c ^ (r & 7).
+//   * K operand (B fragment, "col-major"): a lane reads whole 16-byte chunks of
+//     its token's row; the k-slot <-> head-dim assignment of the MMAs is a
+//     permutation (shared with the Q fragments) chosen so that a quarter-warp
+//     touches all eight chunk columns: no bank conflicts, no shuffles.
+//   * V operand: ldmatrix.trans over eight consecutive token rows, which the
+//     swizzle spreads over all eight chunk columns as well.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records an error
 // code in a device status word and the CTA leaves its loops.
@@ -26,31 +30,35 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace kvc {
-
-void launch_merge(const float *o_part, const float2 *ml_part, int splits, const AttnArgs &a,
-                  cudaStream_t stream);
 
 namespace {
 
 constexpr int CONSUMER_WARPS = 4;
 constexpr int DEC_THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int TILE_T = 64;  // tokens per tile: one 16-token block per consumer warp
+constexpr int BOX_BYTES = TILE_T * 128;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr int COUNTER_BYTES = 64 * 1024;  // ticket counters at the start of the scratch arena
 
 struct DecodeParams {
     const void *q;
-    int64_t q_sb, q_sh, q_sl;
+    void *out;
+    int64_t q_sb, q_sh, q_sl, o_sb, o_sh, o_sl;
     float *o_part;
     float2 *ml_part;
+    int *counters;
     int *status;
     int32_t B, Hq, Hkv, L;
     int64_t T;
-    int32_t splits;
-    int32_t tiles_per_split;
-    int32_t causal;  // 0 / 1
+    int32_t splits;       // units per (batch, head)
+    int32_t tiles_base;   // tiles per unit; the first tiles_rem units take one more
+    int32_t tiles_rem;
+    int32_t causal;
+    int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
 };
@@ -100,11 +108,23 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <typename T> struct MmaType;
 template <> struct MmaType<__nv_bfloat16> {
     static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
             "{%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -114,11 +134,13 @@ template <> struct MmaType<__nv_bfloat16> {
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
         return r;
     }
+    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
+        ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v);
+    }
 };
 template <> struct MmaType<__half> {
     static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
             "{%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -128,29 +150,28 @@ template <> struct MmaType<__half> {
         asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
         return r;
     }
+    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
+        ((__half *)p)[i] = __float2half_rn(v);
+    }
 };
-
-// Address of 16-byte chunk `chunk` of row `row` inside a [rows][128 B] box with the 128-byte swizzle.
-__device__ __forceinline__ const uint4 *box_chunk(const char *box, int row, int chunk) {
-    return (const uint4 *)(box + row * 128 + ((chunk ^ (row & 7)) << 4));
-}
 
 template <typename T, int D, int NSTAGE>
 __global__ void __launch_bounds__(DEC_THREADS, (D <= 128 ? 2 : 1))
 attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                    const DecodeParams p) {
     constexpr int TILE_BYTES = TILE_T * D * 2;     // one K (or V) tile
-    constexpr int BOXES = D / 64;                  // 64-element boxes per row
-    constexpr int BOX_BYTES = TILE_T * 128;
+    constexpr int BOXES = D / 64;                  // [64 tokens][64 elements] boxes per tile
     constexpr int KSTEPS = D / 16;
-    constexpr int NT_O = D / 8;                    // output n-tiles
+    constexpr int NT_O = D / 8;                    // output n-tiles (8 head dims each)
+    constexpr int RED_STRIDE = D + 8;              // padded row of the cross-warp merge buffer
     static_assert(TILE_T == 16 * CONSUMER_WARPS, "one 16-token block per consumer warp");
+    static_assert(CONSUMER_WARPS * 16 * RED_STRIDE * 4 + 1024 <= NSTAGE * 2 * TILE_BYTES, "merge buffer must fit");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // [NSTAGE][K tile | V tile], then barriers
     unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *full = (uint64_t *)(stages + (size_t)NSTAGE * 2 * TILE_BYTES);
     uint64_t *empty = full + NSTAGE;
+    int *is_last = (int *)(empty + NSTAGE);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x % p.splits;
@@ -159,9 +180,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;
 
-    const int64_t total_tiles = (p.T + TILE_T - 1) / TILE_T;
-    const int64_t tile_begin = (int64_t)split * p.tiles_per_split;
-    const int ntiles = (int)max((int64_t)0, min((int64_t)p.tiles_per_split, total_tiles - tile_begin));
+    // balanced split of the tile range
+    const int tile_begin = split * p.tiles_base + min(split, p.tiles_rem);
+    const int ntiles = p.tiles_base + (split < p.tiles_rem ? 1 : 0);
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -174,7 +195,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     __syncthreads();
 
     bool ok = true;
-    // Per-lane state of the consumer warps (rows g and g+8 of the 16-row tile).
     const int g = lane >> 2, c = lane & 3;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o_acc[NT_O][4];
@@ -191,7 +211,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                 unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
                 unsigned char *vt = kt + TILE_BYTES;
                 mbar_expect_tx(&full[s], 2 * TILE_BYTES);
-                const int t0 = (int)((tile_begin + it) * TILE_T);
+                const int t0 = (tile_begin + it) * TILE_T;
 #pragma unroll
                 for (int bx = 0; bx < BOXES; ++bx) {
                     tma_load_4d(kt + bx * BOX_BYTES, &kmap, &full[s], bx * 64, t0, hk, b);
@@ -203,6 +223,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     } else {
         // ---------------- consumers ----------------
         // Query fragments: rows r < R of this KV head's group; row r <-> (rep index r / L, position r % L).
+        // k-step ks = (box bx, pass ps, half h): lane c covers chunk 2c + ps of the box, elements 4h..4h+3.
         uint32_t qa[KSTEPS][4];
         int64_t row_limit[2];
 #pragma unroll
@@ -213,8 +234,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
         }
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
-            // k-step ks = (box bx, pass ps, half h): lane c covers chunk y = 2c + ps of the box,
-            // elements 4h..4h+3 of that chunk.
             const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
             const int d0 = bx * 64 + (2 * c + ps) * 8 + 4 * h;
 #pragma unroll
@@ -231,77 +250,94 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                 qa[ks][2 + half] = w1;  // a2 / a3: k-slots 2c+8, 2c+9
             }
         }
+        // Lane-constant byte offsets inside a box.
+        //   K: token row (16*warp + 8*j + g), chunk (2c + ps) ^ g
+        //   V (ldmatrix): lane supplies the row of matrix i = lane / 8: token 16*warp + 8*(i & 1) + (lane & 7),
+        //                 chunk (2*cp + (i >> 1)) ^ (lane & 7) for chunk pair cp
+        const int blk = warp;
+        uint32_t k_off[2];
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) k_off[ps] = (uint32_t)((blk * 16 + g) * 128 + (((2 * c + ps) ^ g) << 4));
+        uint32_t v_off[4];
+        {
+            const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int cp = 0; cp < 4; ++cp)
+                v_off[cp] = (uint32_t)((blk * 16 + (mi & 1) * 8 + rr) * 128 + (((2 * cp + (mi >> 1)) ^ rr) << 4));
+        }
 
         for (int it = 0; it < ntiles && ok; ++it) {
             const int s = it % NSTAGE;
             ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
             if (!ok) break;
-            const char *kt = (const char *)stages + (size_t)s * 2 * TILE_BYTES;
-            const char *vt = kt + TILE_BYTES;
-            const int64_t t_tile = (tile_begin + it) * TILE_T;
+            if (p.debug_skip) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                continue;
+            }
+            const unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
+            const uint32_t vt_addr = smem_u32(kt + TILE_BYTES);
+            const int64_t t_blk = (int64_t)(tile_begin + it) * TILE_T + blk * 16;
 
-            {
-                const int blk = warp;  // this warp's 16 tokens of the tile
-                // ---- S = Q K^T for 16 tokens (two n-tiles of 8) ----
-                float sc[2][4];
+            // ---- S = Q K^T for 16 tokens (two n-tiles of 8), the two accumulator chains interleaved ----
+            float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
-                    const int row = blk * 16 + j * 8 + g;  // this lane's token (B-fragment column g)
+            for (int bx = 0; bx < BOXES; ++bx) {
 #pragma unroll
-                    for (int bx = 0; bx < BOXES; ++bx) {
-#pragma unroll
-                        for (int ps = 0; ps < 2; ++ps) {
-                            const uint4 kv = *box_chunk(kt + bx * BOX_BYTES, row, 2 * c + ps);
-                            const int ks = bx * 4 + ps * 2;
-                            MmaType<T>::mma(sc[j], qa[ks], kv.x, kv.y);
-                            MmaType<T>::mma(sc[j], qa[ks + 1], kv.z, kv.w);
-                        }
-                    }
+                for (int ps = 0; ps < 2; ++ps) {
+                    const uint4 k0 = *(const uint4 *)(kt + bx * BOX_BYTES + k_off[ps]);
+                    const uint4 k1 = *(const uint4 *)(kt + bx * BOX_BYTES + k_off[ps] + 8 * 128);
+                    const int ks = bx * 4 + ps * 2;
+                    MmaType<T>::mma(sc[0], qa[ks], k0.x, k0.y);
+                    MmaType<T>::mma(sc[1], qa[ks], k1.x, k1.y);
+                    MmaType<T>::mma(sc[0], qa[ks + 1], k0.z, k0.w);
+                    MmaType<T>::mma(sc[1], qa[ks + 1], k1.z, k1.w);
                 }
-                // ---- online softmax (log2 domain) ----
-                float tmax[2] = {-INFINITY, -INFINITY};
+            }
+            // ---- online softmax (log2 domain) ----
+            float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const int64_t t = t_blk + j * 8 + 2 * c + (e & 1);
+                    float v = sc[j][e] * p.scale_log2;
+                    v = (t <= row_limit[half]) ? v : -INFINITY;
+                    sc[j][e] = v;
+                    tmax[half] = fmaxf(tmax[half], v);
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 1));
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 2));
+                const float m_new = fmaxf(m_run[half], tmax[half]);
+                alpha[half] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[half] - m_new);
+                m_run[half] = m_new;
+            }
+            uint32_t pa[4];
+            {
+                float pr[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int half = e >> 1;
-                        const int64_t t = t_tile + blk * 16 + j * 8 + 2 * c + (e & 1);
-                        float v = sc[j][e] * p.scale_log2;
-                        v = (t <= row_limit[half]) ? v : -INFINITY;
-                        sc[j][e] = v;
-                        tmax[half] = fmaxf(tmax[half], v);
+                        pr[j][e] = (m_run[half] == -INFINITY) ? 0.f : fast_exp2(sc[j][e] - m_run[half]);
                     }
-                }
-                float alpha[2];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 1));
-                    tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 2));
-                    const float m_new = fmaxf(m_run[half], tmax[half]);
-                    alpha[half] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[half] - m_new);
-                    m_run[half] = m_new;
-                }
-                uint32_t pa[4];
-                {
-                    float pr[2][4];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int half = e >> 1;
-                            pr[j][e] = (m_run[half] == -INFINITY) ? 0.f : exp2f(sc[j][e] - m_run[half]);
-                        }
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        l_run[half] = l_run[half] * alpha[half] + pr[0][2 * half] + pr[0][2 * half + 1] +
-                                      pr[1][2 * half] + pr[1][2 * half + 1];
-                    pa[0] = MmaType<T>::pack(pr[0][0], pr[0][1]);  // row g,   k-slots 2c, 2c+1   (n-tile 0)
-                    pa[1] = MmaType<T>::pack(pr[0][2], pr[0][3]);  // row g+8
-                    pa[2] = MmaType<T>::pack(pr[1][0], pr[1][1]);  // row g,   k-slots 2c+8, 2c+9 (n-tile 1)
-                    pa[3] = MmaType<T>::pack(pr[1][2], pr[1][3]);  // row g+8
-                }
-                // ---- O = O * alpha + P V ----
+                for (int half = 0; half < 2; ++half)
+                    l_run[half] = l_run[half] * alpha[half] + pr[0][2 * half] + pr[0][2 * half + 1] +
+                                  pr[1][2 * half] + pr[1][2 * half + 1];
+                pa[0] = MmaType<T>::pack(pr[0][0], pr[0][1]);  // row g,   k-slots 2c, 2c+1   (tokens 0..7)
+                pa[1] = MmaType<T>::pack(pr[0][2], pr[0][3]);  // row g+8
+                pa[2] = MmaType<T>::pack(pr[1][0], pr[1][1]);  // row g,   k-slots 2c+8, 2c+9 (tokens 8..15)
+                pa[3] = MmaType<T>::pack(pr[1][2], pr[1][3]);  // row g+8
+            }
+            // ---- O = O * alpha + P V (rescale only when some row's maximum moved) ----
+            if (__any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f))) {
 #pragma unroll
                 for (int nt = 0; nt < NT_O; ++nt) {
                     o_acc[nt][0] *= alpha[0];
@@ -309,27 +345,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
                     o_acc[nt][2] *= alpha[1];
                     o_acc[nt][3] *= alpha[1];
                 }
-                const int r0 = blk * 16 + 2 * c;  // tokens of k-slots 2c, 2c+1; +8 for 2c+8, 2c+9
+            }
 #pragma unroll
-                for (int bx = 0; bx < BOXES; ++bx) {
-                    const char *box = vt + bx * BOX_BYTES;
-                    // chunk g of four token rows: 8 head dims x 4 tokens
-                    const uint4 v0 = *box_chunk(box, r0, g);
-                    const uint4 v1 = *box_chunk(box, r0 + 1, g);
-                    const uint4 v2 = *box_chunk(box, r0 + 8, g);
-                    const uint4 v3 = *box_chunk(box, r0 + 9, g);
-                    const uint32_t w0[4] = {v0.x, v0.y, v0.z, v0.w};
-                    const uint32_t w1[4] = {v1.x, v1.y, v1.z, v1.w};
-                    const uint32_t w2[4] = {v2.x, v2.y, v2.z, v2.w};
-                    const uint32_t w3[4] = {v3.x, v3.y, v3.z, v3.w};
+            for (int bx = 0; bx < BOXES; ++bx) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        // MMA column g <-> head dim 64*bx + 8*g + e
-                        const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-                        const uint32_t b0 = __byte_perm(w0[e >> 1], w1[e >> 1], sel);
-                        const uint32_t b1 = __byte_perm(w2[e >> 1], w3[e >> 1], sel);
-                        MmaType<T>::mma(o_acc[bx * 8 + e], pa, b0, b1);
-                    }
+                for (int cp = 0; cp < 4; ++cp) {
+                    // four 8x8 matrices: (tokens 0..7 | 8..15) x (chunk 2cp | 2cp+1) of this box
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vt_addr + bx * BOX_BYTES + v_off[cp]);
+                    MmaType<T>::mma(o_acc[bx * 8 + 2 * cp], pa, vf[0], vf[1]);
+                    MmaType<T>::mma(o_acc[bx * 8 + 2 * cp + 1], pa, vf[2], vf[3]);
                 }
             }
             __syncwarp();
@@ -340,24 +365,20 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
 
     // ---------------- merge the four consumer warps ----------------
     __syncthreads();
-    float *red_o = (float *)stages;                         // [4][16][D]
-    float *red_ml = red_o + CONSUMER_WARPS * 16 * D;        // [4][16][2]
+    float *red_o = (float *)stages;                                  // [4][16][RED_STRIDE]
+    float *red_ml = red_o + CONSUMER_WARPS * 16 * RED_STRIDE;        // [4][16][2]
     if (warp < CONSUMER_WARPS) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
             l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
         }
-        float *wo = red_o + warp * 16 * D;
+        float *wo = red_o + warp * 16 * RED_STRIDE;
 #pragma unroll
         for (int nt = 0; nt < NT_O; ++nt) {
-            // n-tile (bx, e): C columns 2c, 2c+1 <-> head dims 64*bx + 8*(2c) + e, 64*bx + 8*(2c+1) + e
-            const int bx = nt / 8, e = nt % 8;
-            const int d_a = bx * 64 + 16 * c + e, d_b = d_a + 8;
-            wo[g * D + d_a] = o_acc[nt][0];
-            wo[g * D + d_b] = o_acc[nt][1];
-            wo[(g + 8) * D + d_a] = o_acc[nt][2];
-            wo[(g + 8) * D + d_b] = o_acc[nt][3];
+            // n-tile nt: C columns 2c, 2c+1 <-> head dims 8*nt + 2c, 8*nt + 2c + 1
+            *(float2 *)&wo[g * RED_STRIDE + 8 * nt + 2 * c] = make_float2(o_acc[nt][0], o_acc[nt][1]);
+            *(float2 *)&wo[(g + 8) * RED_STRIDE + 8 * nt + 2 * c] = make_float2(o_acc[nt][2], o_acc[nt][3]);
         }
         if (c == 0) {
             red_ml[(warp * 16 + g) * 2 + 0] = m_run[0];
@@ -367,7 +388,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
         }
     }
     __syncthreads();
-    constexpr float LN2 = 0.6931471805599453f;
+    const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;  // rows of this group are consecutive query rows
     for (int i = tid; i < R * D; i += DEC_THREADS) {
         const int r = i / D, d = i % D;
         float m = -INFINITY;
@@ -377,15 +398,54 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
 #pragma unroll
         for (int w = 0; w < CONSUMER_WARPS; ++w) {
             const float mw = red_ml[(w * 16 + r) * 2];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-            o += red_o[(w * 16 + r) * D + d] * f;
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+            o += red_o[(w * 16 + r) * RED_STRIDE + d] * f;
             l += red_ml[(w * 16 + r) * 2 + 1] * f;
         }
+        const int64_t base = (qrow0 + r) * p.splits + split;
+        __stcg(&p.o_part[base * D + d], o);
+        if (d == 0) __stcg(&p.ml_part[base], make_float2(m, l));  // m stays in the log2 domain
+    }
+
+    // ---------------- last unit of this (batch, head) merges the splits ----------------
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int ticket = atomicAdd(&p.counters[bh], 1);
+        const int last = (ticket == p.splits - 1) ? 1 : 0;
+        if (last) p.counters[bh] = 0;  // self-resetting for the next launch
+        *is_last = last;
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    __threadfence();
+    float *w_split = (float *)stages;  // [R][splits] merge weights (reuses the stage memory)
+    for (int r = warp; r < R; r += DEC_THREADS / 32) {
+        float m = -INFINITY;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) m = fmaxf(m, __ldcg(&p.ml_part[(qrow0 + r) * p.splits + sidx]).x);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float lsum = 0.f;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) {
+            const float2 ml = __ldcg(&p.ml_part[(qrow0 + r) * p.splits + sidx]);
+            const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
+            w_split[r * p.splits + sidx] = f;
+            lsum += ml.y * f;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        __syncwarp();
+        for (int sidx = lane; sidx < p.splits; sidx += 32) w_split[r * p.splits + sidx] *= inv;
+    }
+    __syncthreads();
+    for (int i = tid; i < R * D; i += DEC_THREADS) {
+        const int r = i / D, d = i % D;
+        float o = 0.f;
+        const float *src = p.o_part + ((qrow0 + r) * p.splits) * D + d;
+        for (int sidx = 0; sidx < p.splits; ++sidx) o = fmaf(__ldcg(src + (int64_t)sidx * D), w_split[r * p.splits + sidx], o);
         const int hq = hk * rep + r / p.L, lq = r % p.L;
-        const int64_t qrow = ((int64_t)b * p.Hq + hq) * p.L + lq;
-        const int64_t base = qrow * p.splits + split;
-        p.o_part[base * D + d] = o;
-        if (d == 0) p.ml_part[base] = make_float2(m == -INFINITY ? -INFINITY : m * LN2, l);
+        MmaType<T>::store(p.out, b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d, o);
     }
 }
 
@@ -410,13 +470,13 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-bool make_map(CUtensorMap *map, const KVSource &s, int D, int64_t T, int Hkv, int B, int tile_t) {
+bool make_map(CUtensorMap *map, const KVSource &s, int D, int64_t T, int Hkv, int B) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)Hkv, (cuuint64_t)B};
     const cuuint64_t strides[3] = {(cuuint64_t)s.st * 2, (cuuint64_t)(Hkv > 1 ? s.sh : s.st * T) * 2,
                                    (cuuint64_t)(B > 1 ? s.sb : (Hkv > 1 ? s.sh * Hkv : s.st * T)) * 2};
-    const cuuint32_t box[4] = {64, (cuuint32_t)tile_t, 1, 1};
+    const cuuint32_t box[4] = {64, (cuuint32_t)TILE_T, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = s.dtype == KVC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(map, dt, 4, const_cast<void *>(s.data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -455,7 +515,7 @@ int *status_word(int device) {
 template <typename T, int D, int NSTAGE>
 void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const DecodeParams &p, int units,
                   cudaStream_t stream) {
-    const size_t smem = (size_t)NSTAGE * 2 * (TILE_T * D * 2) + 2 * NSTAGE * sizeof(uint64_t) + 1024;
+    const size_t smem = (size_t)NSTAGE * 2 * (TILE_T * D * 2) + 2 * NSTAGE * sizeof(uint64_t) + 64 + 1024;
     static bool configured[64] = {false};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -497,25 +557,33 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     if (rep * a.L > 16 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     if (!source_fits(a.k, a.D, a.Hkv, a.B) || !source_fits(a.v, a.D, a.Hkv, a.B)) return 0;
     if (((uintptr_t)a.q & 3) || (a.q_sb & 1) || (a.q_sh & 1) || (a.q_sl & 1)) return 0;
-    if ((int64_t)a.B * a.Hkv > 65535 * 16) return 0;
-
-    const int tile_t = TILE_T;
-    CUtensorMap kmap, vmap;
-    if (!make_map(&kmap, a.k, a.D, a.T, a.Hkv, a.B, tile_t) || !make_map(&vmap, a.v, a.D, a.T, a.Hkv, a.B, tile_t))
-        return 0;
-    int *status = status_word(a.device);
-    if (!status) return 0;
-
-    const int64_t tiles = (a.T + tile_t - 1) / tile_t;
     const int64_t bh = (int64_t)a.B * a.Hkv;
-    const int sms = sm_count(a.device);
-    // aim for ~6 units per SM so the hardware scheduler balances the tail, but
-    // keep at least 4 tiles (one per consumer warp) in a unit
-    int64_t want_units = (int64_t)sms * 6;
-    int64_t splits = std::max<int64_t>(1, std::min<int64_t>((want_units + bh - 1) / bh, (tiles + 3) / 4));
-    splits = std::min<int64_t>(splits, 256);
-    int64_t tiles_per_split = (tiles + splits - 1) / splits;
-    splits = (tiles + tiles_per_split - 1) / tiles_per_split;
+    if (bh * (int64_t)sizeof(int) > COUNTER_BYTES) return 0;
+
+    CUtensorMap kmap, vmap;
+    if (!make_map(&kmap, a.k, a.D, a.T, a.Hkv, a.B) || !make_map(&vmap, a.v, a.D, a.T, a.Hkv, a.B)) return 0;
+    int *status = status_word(a.device);
+    int *counters = counters_get(a.device, stream, COUNTER_BYTES);
+    if (!status || !counters) return 0;
+
+    // Units per (batch, head): minimise waves x (tiles per unit + fixed cost), with
+    // `slots` CTAs resident at once; ties go to fewer splits.
+    const int64_t tiles = (a.T + TILE_T - 1) / TILE_T;
+    const int slots = sm_count(a.device) * (a.D <= 128 ? 2 : 1);
+    int64_t best_s = 1;
+    double best_cost = 1e30;
+    const int64_t max_s = std::min<int64_t>(tiles, 64);
+    for (int64_t s = 1; s <= max_s; ++s) {
+        const int64_t units = bh * s;
+        const int64_t waves = (units + slots - 1) / slots;
+        const int64_t per = (tiles + s - 1) / s;
+        const double cost = (double)waves * ((double)per + 2.5);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best_s = s;
+        }
+    }
+    const int64_t splits = best_s;
 
     const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
     const size_t o_bytes = (size_t)qrows * splits * a.D * sizeof(float);
@@ -525,11 +593,19 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     float2 *ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
 
     DecodeParams p;
-    p.q = a.q; p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
-    p.o_part = o_part; p.ml_part = ml_part; p.status = status;
+    p.q = a.q; p.out = a.out;
+    p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.o_part = o_part; p.ml_part = ml_part; p.counters = counters; p.status = status;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
-    p.splits = (int)splits; p.tiles_per_split = (int)tiles_per_split;
+    p.splits = (int)splits;
+    p.tiles_base = (int)(tiles / splits);
+    p.tiles_rem = (int)(tiles % splits);
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    {
+        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
+        p.debug_skip = (e && e[0] == '1') ? 1 : 0;
+    }
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     const int units = (int)(bh * splits);
@@ -545,8 +621,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
         else KVC_DEC(__half, 256, 3);
     }
 #undef KVC_DEC
-    launch_merge(o_part, ml_part, (int)splits, a, stream);
-    return 2;
+    return 1;
 }
 
 }  // namespace kvc

@@ -61,9 +61,11 @@ inline bool is_float_dtype(int32_t dt) { return dt == KVC_F32 || dt == KVC_F16 |
 // ---------------------------------------------------------------------
 void *dev_alloc(size_t bytes, cudaStream_t stream);
 void dev_free(void *ptr, cudaStream_t stream);
-// Per-device scratch that grows on demand and is reused by every attention
-// call on that device (split-K partials, staged queries).
+// Scratch that grows on demand, one arena per (device, stream), reused by every
+// attention call enqueued on that stream (split-K partials).
 void *scratch_get(int device, size_t bytes, cudaStream_t stream);
+// Zero-initialised ticket counters of the same (device, stream) arena; fixed size.
+int *counters_get(int device, cudaStream_t stream, size_t bytes);
 int current_device();
 int sm_count(int device);
 

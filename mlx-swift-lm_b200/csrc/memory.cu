@@ -1,9 +1,11 @@
 // Device memory plumbing: stream-ordered allocation from the device's default
 // memory pool (kept warm so re-allocation never goes back to the driver), and a
-// per-device scratch arena for attention partials.
+// scratch arena per (device, stream) for attention partials.
 #include "common.h"
 
+#include <map>
 #include <mutex>
+#include <utility>
 #include <vector>
 
 namespace kvc {
@@ -20,8 +22,6 @@ namespace {
 struct DeviceInfo {
     bool pool_ready = false;
     int sms = 0;
-    void *scratch = nullptr;
-    size_t scratch_bytes = 0;
 };
 std::mutex g_mu;
 std::vector<DeviceInfo> g_devices;
@@ -74,29 +74,59 @@ void dev_free(void *ptr, cudaStream_t stream) {
     }
 }
 
+// Scratch arenas are keyed by (device, stream): calls on one stream reuse one
+// arena in stream order, calls on different streams never share one.
+namespace {
+struct Arena {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    int *counters = nullptr;
+};
+std::map<std::pair<int, cudaStream_t>, Arena> g_arenas;
+}  // namespace
+
 void *scratch_get(int device, size_t bytes, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(g_mu);
-    DeviceInfo &di = info_locked(device);
-    if (di.scratch_bytes >= bytes) return di.scratch;
+    Arena &ar = g_arenas[{device, stream}];
+    if (ar.bytes >= bytes) return ar.ptr;
     // Grow geometrically. The old arena may still be read by work already
     // enqueued; cudaFree synchronises the device before releasing it.
-    size_t want = di.scratch_bytes ? di.scratch_bytes : (size_t)8 << 20;
+    size_t want = ar.bytes ? ar.bytes : (size_t)8 << 20;
     while (want < bytes) want *= 2;
-    if (di.scratch) {
-        cudaError_t e = cudaFree(di.scratch);
+    if (ar.ptr) {
+        cudaError_t e = cudaFree(ar.ptr);
         if (e != cudaSuccess) (void)cudaGetLastError();
-        di.scratch = nullptr;
-        di.scratch_bytes = 0;
+        ar.ptr = nullptr;
+        ar.bytes = 0;
     }
-    (void)stream;
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, want);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
         fail(KVC_ERR_OUT_OF_MEMORY, std::string("scratch cudaMalloc: ") + cudaGetErrorString(e));
     }
-    di.scratch = p;
-    di.scratch_bytes = want;
+    ar.ptr = p;
+    ar.bytes = want;
+    return p;
+}
+
+int *counters_get(int device, cudaStream_t stream, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    Arena &ar = g_arenas[{device, stream}];
+    if (ar.counters) return ar.counters;
+    int *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        fail(KVC_ERR_OUT_OF_MEMORY, std::string("counter cudaMalloc: ") + cudaGetErrorString(e));
+    }
+    e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        (void)cudaFree(p);
+        fail(KVC_ERR_CUDA, std::string("counter cudaMemset: ") + cudaGetErrorString(e));
+    }
+    ar.counters = p;
     return p;
 }
 
