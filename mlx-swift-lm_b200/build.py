@@ -25,6 +25,7 @@ SOURCES = [
     "quantize.cu",
     "attn_general.cu",
     "attn_decode.cu",
+    "attn_packed.cu",
     "attn_dispatch.cu",
     "cache.cu",
     "round.cu",

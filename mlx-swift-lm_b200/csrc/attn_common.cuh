@@ -1,0 +1,236 @@
+// Device primitives shared by the TMA-staged attention kernels: mbarrier
+// (bounded waits), TMA tile and bulk loads, ldmatrix, fast exp2 and the
+// m16n8k16 tensor-core MMA for f16 / bf16 operands.
+#pragma once
+
+#include "common.h"
+
+#include <cuda.h>
+
+namespace kvc {
+namespace dev {
+
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait; returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
+                                            int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T> struct MmaType;
+template <> struct MmaType<__nv_bfloat16> {
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        uint32_t r;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
+    }
+    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
+        ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v);
+    }
+};
+template <> struct MmaType<__half> {
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        uint32_t r;
+        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
+    }
+    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
+        ((__half *)p)[i] = __float2half_rn(v);
+    }
+};
+
+
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---------------------------------------------------------------------
+// End of a work unit: merge the consumer warps of the CTA into one partial,
+// publish it, and let the last unit of the (batch, head) merge all splits.
+// ---------------------------------------------------------------------
+struct UnitOut {
+    float *o_part;      // [query row][split][D]
+    float2 *ml_part;    // [query row][split] (log2-domain max, sum)
+    int *counters;      // one ticket per (batch, head), self-resetting
+    void *out;
+    int32_t out_dtype;
+    int64_t o_sb, o_sh, o_sl;
+    const float *o_signs;  // optional: rotate merged rows back (TurboQuant values)
+    int32_t splits, Hq, L;
+};
+
+__device__ __forceinline__ void store_out(void *p, int32_t dtype, int64_t i, float v) {
+    switch (dtype) {
+        case KVC_F32: ((float *)p)[i] = v; break;
+        case KVC_F16: ((__half *)p)[i] = __float2half_rn(v); break;
+        default: ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v); break;
+    }
+}
+
+// Preconditions: every consumer warp w < NWARPS has written its un-normalised
+// rows to red_o[(w*16 + r) * red_stride + d] and (max, sum) to red_ml[(w*16 + r)*2],
+// followed by a __syncthreads(). `work` is shared memory that does not overlap
+// red_o / red_ml, at least R * max(splits, D) floats; `flag` one int of shared memory.
+template <int D, int NWARPS>
+__device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float *red_ml, int red_stride,
+                              float *work, int *flag, int b, int hk, int rep, int R, int split, int bh) {
+    const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L;  // the group's rows are consecutive query rows
+    for (int i = tid; i < R * D; i += nthreads) {
+        const int r = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, red_ml[(w * 16 + r) * 2]);
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = red_ml[(w * 16 + r) * 2];
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+            o += red_o[(w * 16 + r) * red_stride + d] * f;
+            l += red_ml[(w * 16 + r) * 2 + 1] * f;
+        }
+        const int64_t base = (qrow0 + r) * u.splits + split;
+        __stcg(&u.o_part[base * D + d], o);
+        if (d == 0) __stcg(&u.ml_part[base], make_float2(m, l));
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int ticket = atomicAdd(&u.counters[bh], 1);
+        const int last = (ticket == u.splits - 1) ? 1 : 0;
+        if (last) u.counters[bh] = 0;
+        *flag = last;
+    }
+    __syncthreads();
+    if (!*flag) return;
+    __threadfence();
+    // merge weights per (row, split)
+    for (int r = warp; r < R; r += nthreads / 32) {
+        float m = -INFINITY;
+        for (int s = lane; s < u.splits; s += 32) m = fmaxf(m, __ldcg(&u.ml_part[(qrow0 + r) * u.splits + s]).x);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float lsum = 0.f;
+        for (int s = lane; s < u.splits; s += 32) {
+            const float2 ml = __ldcg(&u.ml_part[(qrow0 + r) * u.splits + s]);
+            const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
+            work[r * u.splits + s] = f;
+            lsum += ml.y * f;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        __syncwarp();
+        for (int s = lane; s < u.splits; s += 32) work[r * u.splits + s] *= inv;
+    }
+    __syncthreads();
+    if (!u.o_signs) {
+        for (int i = tid; i < R * D; i += nthreads) {
+            const int r = i / D, d = i % D;
+            float o = 0.f;
+            const float *src = u.o_part + ((qrow0 + r) * u.splits) * D + d;
+            for (int s = 0; s < u.splits; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * u.splits + s], o);
+            const int hq = hk * rep + r / u.L, lq = r % u.L;
+            store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, o);
+        }
+        return;
+    }
+    // TurboQuant values: the merged rows are in the rotated basis; out = signs * H(o) / sqrt(D).
+    float *rows = work + R * u.splits;  // [R][D]
+    for (int i = tid; i < R * D; i += nthreads) {
+        const int r = i / D, d = i % D;
+        float o = 0.f;
+        const float *src = u.o_part + ((qrow0 + r) * u.splits) * D + d;
+        for (int s = 0; s < u.splits; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * u.splits + s], o);
+        rows[i] = o;
+    }
+    for (int half = 1; half < D; half <<= 1) {
+        __syncthreads();
+        for (int pidx = tid; pidx < R * (D / 2); pidx += nthreads) {
+            const int r = pidx / (D / 2), j = pidx % (D / 2);
+            const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
+            const float x = rows[r * D + i0], y = rows[r * D + i1];
+            rows[r * D + i0] = x + y;
+            rows[r * D + i1] = x - y;
+        }
+    }
+    __syncthreads();
+    const float f = rsqrtf((float)D);
+    for (int i = tid; i < R * D; i += nthreads) {
+        const int r = i / D, d = i % D;
+        const int hq = hk * rep + r / u.L, lq = r % u.L;
+        store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, rows[i] * f * u.o_signs[d]);
+    }
+}
+
+}  // namespace dev
+}  // namespace kvc

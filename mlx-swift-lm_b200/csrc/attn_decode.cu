@@ -25,9 +25,7 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records an error
 // code in a device status word and the CTA leaves its loops.
-#include "common.h"
-
-#include <cuda.h>
+#include "attn_common.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -37,11 +35,12 @@ namespace kvc {
 
 namespace {
 
+using namespace dev;
+
 constexpr int CONSUMER_WARPS = 4;
 constexpr int DEC_THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int TILE_T = 64;  // tokens per tile: one 16-token block per consumer warp
 constexpr int BOX_BYTES = TILE_T * 128;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
 constexpr int COUNTER_BYTES = 64 * 1024;  // ticket counters at the start of the scratch arena
 
 struct DecodeParams {
@@ -58,101 +57,10 @@ struct DecodeParams {
     int32_t tiles_base;   // tiles per unit; the first tiles_rem units take one more
     int32_t tiles_rem;
     int32_t causal;
+    int32_t out_dtype;
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// Bounded wait; returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n"
-            "}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
-                                            int z, int w) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
-        : "memory");
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr)
-                 : "memory");
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-template <typename T> struct MmaType;
-template <> struct MmaType<__nv_bfloat16> {
-    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-            "{%0,%1,%2,%3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        uint32_t r;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-        return r;
-    }
-    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
-        ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v);
-    }
-};
-template <> struct MmaType<__half> {
-    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-            "{%0,%1,%2,%3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        uint32_t r;
-        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-        return r;
-    }
-    static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
-        ((__half *)p)[i] = __float2half_rn(v);
-    }
 };
 
 template <typename T, int D, int NSTAGE>
@@ -165,7 +73,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     constexpr int NT_O = D / 8;                    // output n-tiles (8 head dims each)
     constexpr int RED_STRIDE = D + 8;              // padded row of the cross-warp merge buffer
     static_assert(TILE_T == 16 * CONSUMER_WARPS, "one 16-token block per consumer warp");
-    static_assert(CONSUMER_WARPS * 16 * RED_STRIDE * 4 + 1024 <= NSTAGE * 2 * TILE_BYTES, "merge buffer must fit");
+    static_assert(CONSUMER_WARPS * 16 * RED_STRIDE * 4 + 512 + 16 * 64 * 4 <= NSTAGE * 2 * TILE_BYTES, "merge buffers must fit");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -388,65 +296,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
         }
     }
     __syncthreads();
-    const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;  // rows of this group are consecutive query rows
-    for (int i = tid; i < R * D; i += DEC_THREADS) {
-        const int r = i / D, d = i % D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, red_ml[(w * 16 + r) * 2]);
-        float o = 0.f, l = 0.f;
-#pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) {
-            const float mw = red_ml[(w * 16 + r) * 2];
-            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
-            o += red_o[(w * 16 + r) * RED_STRIDE + d] * f;
-            l += red_ml[(w * 16 + r) * 2 + 1] * f;
-        }
-        const int64_t base = (qrow0 + r) * p.splits + split;
-        __stcg(&p.o_part[base * D + d], o);
-        if (d == 0) __stcg(&p.ml_part[base], make_float2(m, l));  // m stays in the log2 domain
-    }
-
-    // ---------------- last unit of this (batch, head) merges the splits ----------------
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int ticket = atomicAdd(&p.counters[bh], 1);
-        const int last = (ticket == p.splits - 1) ? 1 : 0;
-        if (last) p.counters[bh] = 0;  // self-resetting for the next launch
-        *is_last = last;
-    }
-    __syncthreads();
-    if (!*is_last) return;
-    __threadfence();
-    float *w_split = (float *)stages;  // [R][splits] merge weights (reuses the stage memory)
-    for (int r = warp; r < R; r += DEC_THREADS / 32) {
-        float m = -INFINITY;
-        for (int sidx = lane; sidx < p.splits; sidx += 32) m = fmaxf(m, __ldcg(&p.ml_part[(qrow0 + r) * p.splits + sidx]).x);
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float lsum = 0.f;
-        for (int sidx = lane; sidx < p.splits; sidx += 32) {
-            const float2 ml = __ldcg(&p.ml_part[(qrow0 + r) * p.splits + sidx]);
-            const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
-            w_split[r * p.splits + sidx] = f;
-            lsum += ml.y * f;
-        }
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        __syncwarp();
-        for (int sidx = lane; sidx < p.splits; sidx += 32) w_split[r * p.splits + sidx] *= inv;
-    }
-    __syncthreads();
-    for (int i = tid; i < R * D; i += DEC_THREADS) {
-        const int r = i / D, d = i % D;
-        float o = 0.f;
-        const float *src = p.o_part + ((qrow0 + r) * p.splits) * D + d;
-        for (int sidx = 0; sidx < p.splits; ++sidx) o = fmaf(__ldcg(src + (int64_t)sidx * D), w_split[r * p.splits + sidx], o);
-        const int hq = hk * rep + r / p.L, lq = r % p.L;
-        MmaType<T>::store(p.out, b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d, o);
-    }
+    UnitOut u;
+    u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+    u.out = p.out; u.out_dtype = p.out_dtype;
+    u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+    u.o_signs = nullptr;
+    u.splits = p.splits; u.Hq = p.Hq; u.L = p.L;
+    // work area behind the cross-warp buffers (the stage ring is idle by now)
+    float *work = red_ml + CONSUMER_WARPS * 16 * 2;
+    unit_epilogue<D, CONSUMER_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
 }
 
 // ---------------------------------------------------------------------
@@ -593,7 +451,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     float2 *ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
 
     DecodeParams p;
-    p.q = a.q; p.out = a.out;
+    p.q = a.q; p.out = a.out; p.out_dtype = a.q_dtype;
     p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
     p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
     p.o_part = o_part; p.ml_part = ml_part; p.counters = counters; p.status = status;

@@ -8,6 +8,7 @@ namespace kvc {
 
 int launch_attention_general(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_affine(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
@@ -21,6 +22,8 @@ bool force_general() {
 int launch_attention(const AttnArgs &a, cudaStream_t stream) {
     if (!force_general()) {
         int n = launch_attention_decode(a, stream);
+        if (n > 0) return n;
+        n = launch_attention_affine(a, stream);
         if (n > 0) return n;
     }
     return launch_attention_general(a, stream);

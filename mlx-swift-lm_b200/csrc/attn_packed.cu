@@ -1,0 +1,1012 @@
+// Split-K flash decoding over the group-wise affine-quantised cache
+// (QuantizedKVCache, 4- or 8-bit codes) on sm_100a.
+//
+// Same CTA structure as the raw-cache decode kernel: a producer warp streams
+// tiles of 64 tokens through an mbarrier ring, here with untiled TMA bulk copies
+// (cp.async.bulk) because every array of the packed cache is contiguous per
+// (batch, head): codes [64 x D*bits/8 bytes], scales and biases [64 x D/group]
+// for K and for V. Four consumer warps take 16 tokens each.
+//
+// Dequantisation happens in registers and is folded around the tensor-core MMAs:
+//   scores:  q . (s*c + b) = s * (q . c) + b * sum(q)      per group of the row
+//            -> the MMA runs on the raw integer codes (exact in f16) with one
+//               accumulator per group; scale and bias are applied to the 16x8
+//               score fragment afterwards;
+//   values:  sum_t p_t (s_t c_t + b_t) = sum_t (p_t s_t) c_t + sum_t p_t b_t
+//            -> the probabilities are pre-multiplied by the token's scale (one A
+//               fragment per group), the bias term is a per-row scalar sum.
+// Codes become f16 operands with the exponent trick: (x & 0x000F000F) | 0x64006400
+// is the f16 pair (1024 + n_lo, 1024 + n_hi), one subtraction removes the 1024.
+// K codes are read as whole words of the token's row (the k-slot <-> head-dim
+// assignment is a permutation shared with the query fragments, kept inside one
+// quantisation group per MMA); V codes go through ldmatrix.trans, which hands
+// each lane the 16-bit units of two consecutive tokens in one register, exactly
+// the token-pair layout the P.V operand needs.
+#include "attn_common.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace kvc {
+
+namespace {
+
+using namespace dev;
+
+constexpr int PK_WARPS = 4;
+constexpr int PK_THREADS = (PK_WARPS + 1) * 32;
+constexpr int PK_TILE = 64;
+constexpr int PK_COUNTER_BYTES = 64 * 1024;
+
+struct AffineParams {
+    const void *q;
+    void *out;
+    int64_t q_sb, q_sh, q_sl, o_sb, o_sh, o_sl;
+    const uint32_t *kc, *vc;           // codes
+    const void *ks, *kb, *vs, *vb;     // scales / biases (dtype T)
+    int64_t kc_sb, kc_sh, vc_sb, vc_sh;  // word strides (token stride = words per row)
+    int64_t kg_sb, kg_sh, vg_sb, vg_sh;  // element strides of scales/biases (token stride = groups)
+    float *o_part;
+    float2 *ml_part;
+    int *counters;
+    int *status;
+    int32_t B, Hq, Hkv, L;
+    int64_t T;
+    int32_t splits, tiles_base, tiles_rem;
+    int32_t causal;
+    int32_t out_dtype;
+    int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
+    int64_t causal_offset;
+    float scale_log2;
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t hsub2_1024(uint32_t x) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0x64006400u));
+    return r;
+}
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Operand pair (b0, b1) number `which` of a packed code word, as f16 pairs minus nothing
+// (the caller subtracts 1024). 4-bit: word = nibbles n0..n7, pair 0 = {(n0,n4),(n1,n5)},
+// pair 1 = {(n2,n6),(n3,n7)}. 8-bit: word = bytes b0..b3, single pair {(b0,b1),(b2,b3)}.
+template <int BITS>
+__device__ __forceinline__ void code_pair(uint32_t w, int which, uint32_t &b0, uint32_t &b1) {
+    if (BITS == 4) {
+        const uint32_t x = w >> (8 * which);
+        b0 = hsub2_1024((x & 0x000F000Fu) | 0x64006400u);
+        b1 = hsub2_1024(((x >> 4) & 0x000F000Fu) | 0x64006400u);
+    } else {
+        b0 = hsub2_1024(__byte_perm(w, 0x64646464u, 0x4140));
+        b1 = hsub2_1024(__byte_perm(w, 0x64646464u, 0x4342));
+    }
+}
+
+// Head dims that the four k-slot pairs of MMA `m` (within a lane's word `wl` of a
+// group) stand for; used once to lay the query fragments out to match.
+template <int BITS>
+__device__ __forceinline__ void kslot_dims(int word_in_row, int which, int (&d)[4]) {
+    if (BITS == 4) {
+        const int base = word_in_row * 8 + 2 * which;
+        d[0] = base;       // k-slot 2c
+        d[1] = base + 4;   // k-slot 2c+1
+        d[2] = base + 1;   // k-slot 2c+8
+        d[3] = base + 5;   // k-slot 2c+9
+    } else {
+        const int base = word_in_row * 4;
+        d[0] = base; d[1] = base + 1; d[2] = base + 2; d[3] = base + 3;
+    }
+}
+
+template <typename T, int D, int BITS, int GROUP, int NSTAGE>
+__global__ void __launch_bounds__(PK_THREADS, 2)
+attn_affine_kernel(const AffineParams p) {
+    constexpr int G = D / GROUP;                  // groups per row
+    constexpr int RB = D * BITS / 8;              // code bytes per row
+    constexpr int WPR = RB / 4;                   // words per row
+    constexpr int WPG = GROUP * BITS / 32;        // words per group
+    constexpr int WPL = WPG / 4;                  // words per lane per group
+    constexpr int MPW = (BITS == 4) ? 2 : 1;      // MMAs per word
+    constexpr int MPG = WPL * MPW;                // MMAs (k-steps) per group
+    constexpr int SB = G * 2;                     // scale (or bias) bytes per token
+    constexpr int CODE_TILE = PK_TILE * RB;
+    constexpr int SC_TILE = PK_TILE * SB;
+    constexpr int STAGE_BYTES = 2 * CODE_TILE + 4 * SC_TILE;
+    constexpr int EPU = 16 / BITS;                // elements per 16-bit unit
+    constexpr int CH = RB / 16;                   // 16-byte chunks per row
+    constexpr int NT_O = D / 8;
+    constexpr int RED_STRIDE = D + 8;
+    static_assert(WPL >= 1 && G >= 1 && G <= 4, "unsupported group layout");
+    static_assert(CH % 2 == 0, "rows must hold an even number of 16-byte chunks");
+    static_assert(STAGE_BYTES % 16 == 0 && SC_TILE % 16 == 0, "bulk copies need 16-byte multiples");
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    constexpr int RING = NSTAGE * STAGE_BYTES;
+    constexpr int RED_BYTES = PK_WARPS * 16 * RED_STRIDE * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
+    constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
+    uint64_t *full = (uint64_t *)(stages + ((BODY + 15) / 16) * 16);
+    uint64_t *empty = full + NSTAGE;
+    int *is_last = (int *)(empty + NSTAGE);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % p.splits;
+    const int bh = blockIdx.x / p.splits;
+    const int hk = bh % p.Hkv, b = bh / p.Hkv;
+    const int rep = p.Hq / p.Hkv;
+    const int R = rep * p.L;
+    const int tile_begin = split * p.tiles_base + min(split, p.tiles_rem);
+    const int ntiles = p.tiles_base + (split < p.tiles_rem ? 1 : 0);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], PK_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    bool ok = true;
+    const int g = lane >> 2, c = lane & 3;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float bsum[2][G];  // sum_t p_t * bias_t per row half and value group
+    float o_acc[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) bsum[h][gr] = 0.f;
+
+    if (warp == PK_WARPS) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            const uint32_t *kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
+            const uint32_t *vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
+            const T *ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
+            const T *kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
+            const T *vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
+            const T *vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
+            for (int it = 0; it < ntiles && ok; ++it) {
+                const int s = it % NSTAGE;
+                if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                if (!ok) break;
+                unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+                const int64_t t0 = (int64_t)(tile_begin + it) * PK_TILE;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                bulk_load(st, kc + t0 * WPR, CODE_TILE, &full[s]);
+                bulk_load(st + CODE_TILE, vc + t0 * WPR, CODE_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE, ks + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, SC_TILE, &full[s]);
+            }
+            if (!ok) atomicExch(p.status, 3);
+        }
+    } else {
+        // ---------------- consumers ----------------
+        // Query fragments (f16), laid out to match the code words each lane reads, and
+        // sum(q) per row half and key group for the bias term.
+        uint32_t qa[G][MPG][4];
+        float qsum[2][G];
+        int64_t row_limit[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = g + 8 * half;
+            const int l = r % p.L;
+            row_limit[half] = (r < R) ? (p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) qsum[half][gr] = 0.f;
+        }
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) {
+#pragma unroll
+            for (int m = 0; m < MPG; ++m) {
+                const int wl = m / MPW, which = m % MPW;
+                int dd[4];
+                kslot_dims<BITS>(gr * WPG + c * WPL + wl, which, dd);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int r = g + 8 * half;
+                    float x[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (r < R) {
+                        const int hq = hk * rep + r / p.L, l = r % p.L;
+                        const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]])));
+                    }
+                    qa[gr][m][half] = pack_h2(x[0], x[1]);      // a0 / a1
+                    qa[gr][m][2 + half] = pack_h2(x[2], x[3]);  // a2 / a3
+                    qsum[half][gr] += x[0] + x[1] + x[2] + x[3];
+                }
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                qsum[half][gr] += __shfl_xor_sync(0xffffffffu, qsum[half][gr], 1);
+                qsum[half][gr] += __shfl_xor_sync(0xffffffffu, qsum[half][gr], 2);
+            }
+
+        const int blk = warp;
+        // ldmatrix row address of this lane inside a V code tile: matrix mi = lane / 8
+        const int v_tok = blk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const int v_chunk_off = (lane >> 4);  // 0 or 1: second chunk of the pair
+
+        for (int it = 0; it < ntiles && ok; ++it) {
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) break;
+            const unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+            const unsigned char *kct = st;
+            const unsigned char *vct = st + CODE_TILE;
+            const T *kst = (const T *)(st + 2 * CODE_TILE);
+            const T *kbt = (const T *)(st + 2 * CODE_TILE + SC_TILE);
+            const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
+            const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
+            const int64_t t_blk = (int64_t)(tile_begin + it) * PK_TILE + blk * 16;
+
+            // ---- integer dot products q . c per group, two n-tiles of 8 tokens ----
+            float acc[2][G][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int gr = 0; gr < G; ++gr) acc[j][gr][0] = acc[j][gr][1] = acc[j][gr][2] = acc[j][gr][3] = 0.f;
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                uint32_t w[2][WPL];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t *wp = (const uint32_t *)(kct + (blk * 16 + j * 8 + g) * RB) + gr * WPG + c * WPL;
+#pragma unroll
+                    for (int k = 0; k < WPL; ++k) w[j][k] = wp[k];
+                }
+#pragma unroll
+                for (int m = 0; m < MPG; ++m) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        uint32_t b0, b1;
+                        code_pair<BITS>(w[j][m / MPW], m % MPW, b0, b1);
+                        mma_f16(acc[j][gr], qa[gr][m], b0, b1);
+                    }
+                }
+            }
+            // ---- scores = s * acc + b * sum(q), masked, in the log2 domain ----
+            float sc[2][4];
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const int tl = blk * 16 + j * 8 + 2 * c + (e & 1);  // token inside the tile
+                    float v = 0.f;
+#pragma unroll
+                    for (int gr = 0; gr < G; ++gr)
+                        v += to_f32<T>(kst[tl * G + gr]) * acc[j][gr][e] + to_f32<T>(kbt[tl * G + gr]) * qsum[half][gr];
+                    v *= p.scale_log2;
+                    const int64_t t = t_blk + j * 8 + 2 * c + (e & 1);
+                    v = (t <= row_limit[half]) ? v : -INFINITY;
+                    sc[j][e] = v;
+                    tmax[half] = fmaxf(tmax[half], v);
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 1));
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 2));
+                const float m_new = fmaxf(m_run[half], tmax[half]);
+                alpha[half] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[half] - m_new);
+                m_run[half] = m_new;
+            }
+            float pr[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    pr[j][e] = (m_run[half] == -INFINITY) ? 0.f : fast_exp2(sc[j][e] - m_run[half]);
+                }
+            const bool rescale = __any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f));
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                l_run[half] = l_run[half] * alpha[half] + pr[0][2 * half] + pr[0][2 * half + 1] + pr[1][2 * half] +
+                              pr[1][2 * half + 1];
+            }
+            if (rescale) {
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    o_acc[nt][0] *= alpha[0];
+                    o_acc[nt][1] *= alpha[0];
+                    o_acc[nt][2] *= alpha[1];
+                    o_acc[nt][3] *= alpha[1];
+                }
+#pragma unroll
+                for (int gr = 0; gr < G; ++gr) {
+                    bsum[0][gr] *= alpha[0];
+                    bsum[1][gr] *= alpha[1];
+                }
+            }
+            // ---- per-group A fragments p * s_v, and the bias sums ----
+            uint32_t pa[G][4];
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                float sv[2][2], bv[2][2];  // [n-tile j][token 2c + 0/1]
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int tl = blk * 16 + j * 8 + 2 * c + k;
+                        sv[j][k] = to_f32<T>(vst[tl * G + gr]);
+                        bv[j][k] = to_f32<T>(vbt[tl * G + gr]);
+                    }
+                pa[gr][0] = pack_h2(pr[0][0] * sv[0][0], pr[0][1] * sv[0][1]);
+                pa[gr][1] = pack_h2(pr[0][2] * sv[0][0], pr[0][3] * sv[0][1]);
+                pa[gr][2] = pack_h2(pr[1][0] * sv[1][0], pr[1][1] * sv[1][1]);
+                pa[gr][3] = pack_h2(pr[1][2] * sv[1][0], pr[1][3] * sv[1][1]);
+                bsum[0][gr] += pr[0][0] * bv[0][0] + pr[0][1] * bv[0][1] + pr[1][0] * bv[1][0] + pr[1][1] * bv[1][1];
+                bsum[1][gr] += pr[0][2] * bv[0][0] + pr[0][3] * bv[0][1] + pr[1][2] * bv[1][0] + pr[1][3] * bv[1][1];
+            }
+            // ---- O += (p s) . codes: ldmatrix.trans hands out token pairs per 16-bit unit ----
+            const uint32_t v_row = smem_u32(vct + v_tok * RB);
+#pragma unroll
+            for (int cp = 0; cp < CH / 2; ++cp) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, v_row + (2 * cp + v_chunk_off) * 16);
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2) {
+                    const int chunk = 2 * cp + q2;
+                    constexpr int dims_per_chunk = 8 * EPU;
+                    const int gr = (chunk * dims_per_chunk) / GROUP;
+#pragma unroll
+                    for (int i = 0; i < EPU; ++i) {
+                        uint32_t b0, b1;
+                        if (BITS == 4) {
+                            b0 = hsub2_1024(((vf[2 * q2] >> (4 * i)) & 0x000F000Fu) | 0x64006400u);
+                            b1 = hsub2_1024(((vf[2 * q2 + 1] >> (4 * i)) & 0x000F000Fu) | 0x64006400u);
+                        } else {
+                            const uint32_t sel = i ? 0x4341u : 0x4240u;
+                            b0 = hsub2_1024(__byte_perm(vf[2 * q2], 0x64646464u, sel));
+                            b1 = hsub2_1024(__byte_perm(vf[2 * q2 + 1], 0x64646464u, sel));
+                        }
+                        mma_f16(o_acc[chunk * EPU + i], pa[gr], b0, b1);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, 4);
+    }
+
+    // ---------------- merge the consumer warps, then the splits ----------------
+    __syncthreads();
+    float *red_o = (float *)stages;
+    float *red_ml = red_o + PK_WARPS * 16 * RED_STRIDE;
+    if (warp < PK_WARPS) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                bsum[half][gr] += __shfl_xor_sync(0xffffffffu, bsum[half][gr], 1);
+                bsum[half][gr] += __shfl_xor_sync(0xffffffffu, bsum[half][gr], 2);
+            }
+        }
+        float *wo = red_o + warp * 16 * RED_STRIDE;
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            // n-tile nt = chunk * EPU + i: columns 2c, 2c+1 <-> dims chunk*8*EPU + EPU*col + i
+            const int chunk = nt / EPU, i = nt % EPU;
+            const int d0 = chunk * 8 * EPU + EPU * (2 * c) + i, d1 = d0 + EPU;
+            const int gr = d0 / GROUP;
+            wo[g * RED_STRIDE + d0] = o_acc[nt][0] + bsum[0][gr];
+            wo[g * RED_STRIDE + d1] = o_acc[nt][1] + bsum[0][gr];
+            wo[(g + 8) * RED_STRIDE + d0] = o_acc[nt][2] + bsum[1][gr];
+            wo[(g + 8) * RED_STRIDE + d1] = o_acc[nt][3] + bsum[1][gr];
+        }
+        if (c == 0) {
+            red_ml[(warp * 16 + g) * 2 + 0] = m_run[0];
+            red_ml[(warp * 16 + g) * 2 + 1] = l_run[0];
+            red_ml[(warp * 16 + g + 8) * 2 + 0] = m_run[1];
+            red_ml[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+        }
+    }
+    __syncthreads();
+    UnitOut u;
+    u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+    u.out = p.out; u.out_dtype = p.out_dtype;
+    u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+    u.o_signs = nullptr;
+    u.splits = p.splits; u.Hq = p.Hq; u.L = p.L;
+    float *work = red_ml + PK_WARPS * 16 * 2;
+    unit_epilogue<D, PK_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
+}
+
+// ---------------------------------------------------------------------
+// Decode orientation (at most 8 query rows per KV head, i.e. GQA ratio <= 8
+// with one new token): the MMAs are transposed so that tokens (for Q.K^T) and
+// head dims (for P.V) fill the 16-row M side and the query rows the 8-column N
+// side. Compared with the kernel above this halves the MMA count and the
+// accumulator registers (three CTAs per SM instead of two), which is what the
+// latency-bound conversion chain needs.
+//   S^T[16 tok x 8 rows]  = K[16 tok x 16 d] . Q^T[16 d x 8 rows]      (A = codes)
+//   O^T[16 d  x 8 rows]  += V^T[16 d x 16 tok] . P'^T[16 tok x 8 rows]  (A = codes via ldmatrix.trans)
+// P'^T reaches its B-fragment layout with movmatrix (an 8x8 transpose across
+// the warp). Codes are turned into f16 with the exponent trick and NO
+// subtraction: 4-bit codes land in mantissa bits 6..9 of 0x4C00 (= 16 + n),
+// 8-bit codes in the low byte of 0x6400 (= 1024 + n); the constant offset is
+// folded into the bias term (b - OFF * s), which is exact algebra.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+
+// f16 pair (OFF + code_lo, OFF + code_hi) number k of a word. 4-bit: nibbles (k, k+4), k = 0..3.
+// 8-bit: bytes (2k, 2k+1), k = 0..1.
+template <int BITS>
+__device__ __forceinline__ uint32_t code_f16_pair(uint32_t w, int k) {
+    if (BITS == 4) {
+        uint32_t x;
+        switch (k) {
+            case 0: x = w << 6; break;
+            case 1: x = w << 2; break;
+            case 2: x = w >> 2; break;
+            default: x = w >> 6; break;
+        }
+        return (x & 0x03C003C0u) | 0x4C004C00u;
+    }
+    return __byte_perm(w, 0x64646464u, k ? 0x4342 : 0x4140);
+}
+
+// Same for the register ldmatrix.trans returns from a V code tile: element i of the two
+// 16-bit units (token 2c in the low half, token 2c+1 in the high half).
+template <int BITS>
+__device__ __forceinline__ uint32_t unit_f16_pair(uint32_t v, int i) {
+    if (BITS == 4) {
+        uint32_t x;
+        switch (i) {
+            case 0: x = v << 6; break;
+            case 1: x = v << 2; break;
+            case 2: x = v >> 2; break;
+            default: x = v >> 6; break;
+        }
+        return (x & 0x03C003C0u) | 0x4C004C00u;
+    }
+    return __byte_perm(v, 0x64646464u, i ? 0x4341 : 0x4240);
+}
+
+template <typename T, int D, int BITS, int GROUP, int NSTAGE>
+__global__ void __launch_bounds__(PK_THREADS, 3)
+attn_affine_decode8_kernel(const AffineParams p) {
+    constexpr int G = D / GROUP;
+    constexpr int RB = D * BITS / 8;
+    constexpr int WPR = RB / 4;
+    constexpr int WPG = GROUP * BITS / 32;
+    constexpr int WPL = WPG / 4;
+    constexpr int MPW = (BITS == 4) ? 2 : 1;
+    constexpr int MPG = WPL * MPW;
+    constexpr int SB = G * 2;
+    constexpr int CODE_TILE = PK_TILE * RB;
+    constexpr int SC_TILE = PK_TILE * SB;
+    constexpr int STAGE_BYTES = 2 * CODE_TILE + 4 * SC_TILE;
+    constexpr int EPU = 16 / BITS;
+    constexpr int CH = RB / 16;
+    constexpr int MT_O = D / 16;                  // output m-tiles (16 head dims each)
+    constexpr int RED_STRIDE = D + 8;
+    constexpr float OFF = (BITS == 4) ? 16.f : 1024.f;
+    static_assert(WPL >= 1 && G >= 1 && G <= 4, "unsupported group layout");
+    static_assert((2 * 8 * EPU) <= GROUP, "a pair of 16-byte chunks must stay inside one group");
+    static_assert(STAGE_BYTES % 16 == 0 && SC_TILE % 16 == 0, "bulk copies need 16-byte multiples");
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    constexpr int RING = NSTAGE * STAGE_BYTES;
+    constexpr int RED_BYTES = PK_WARPS * 16 * RED_STRIDE * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
+    constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
+    uint64_t *full = (uint64_t *)(stages + ((BODY + 15) / 16) * 16);
+    uint64_t *empty = full + NSTAGE;
+    int *is_last = (int *)(empty + NSTAGE);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % p.splits;
+    const int bh = blockIdx.x / p.splits;
+    const int hk = bh % p.Hkv, b = bh / p.Hkv;
+    const int rep = p.Hq / p.Hkv;
+    const int R = rep * p.L;  // <= 8
+    const int tile_begin = split * p.tiles_base + min(split, p.tiles_rem);
+    const int ntiles = p.tiles_base + (split < p.tiles_rem ? 1 : 0);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], PK_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    bool ok = true;
+    const int g = lane >> 2, c = lane & 3;
+    // per-lane state for query rows 2c and 2c+1
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float bsum[2][G];
+    float o_acc[MT_O][4];
+#pragma unroll
+    for (int i = 0; i < MT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) bsum[h][gr] = 0.f;
+
+    if (warp == PK_WARPS) {
+        if (lane == 0) {
+            const uint32_t *kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
+            const uint32_t *vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
+            const T *ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
+            const T *kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
+            const T *vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
+            const T *vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
+            for (int it = 0; it < ntiles && ok; ++it) {
+                const int s = it % NSTAGE;
+                if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                if (!ok) break;
+                unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+                const int64_t t0 = (int64_t)(tile_begin + it) * PK_TILE;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                bulk_load(st, kc + t0 * WPR, CODE_TILE, &full[s]);
+                bulk_load(st + CODE_TILE, vc + t0 * WPR, CODE_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE, ks + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, SC_TILE, &full[s]);
+                bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, SC_TILE, &full[s]);
+            }
+            if (!ok) atomicExch(p.status, 5);
+        }
+    } else {
+        // Q^T fragments: B operand column = query row g; k-slots follow the code words.
+        uint32_t qb[G][MPG][2];
+        float qsum_own[G];
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) qsum_own[gr] = 0.f;
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) {
+#pragma unroll
+            for (int m = 0; m < MPG; ++m) {
+                int dd[4];
+                kslot_dims<BITS>(gr * WPG + c * WPL + m / MPW, m % MPW, dd);
+                float x[4] = {0.f, 0.f, 0.f, 0.f};
+                if (g < R) {
+                    const int hq = hk * rep + g / p.L, l = g % p.L;
+                    const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]])));
+                }
+                qb[gr][m][0] = pack_h2(x[0], x[1]);
+                qb[gr][m][1] = pack_h2(x[2], x[3]);
+                qsum_own[gr] += x[0] + x[1] + x[2] + x[3];
+            }
+        }
+        float qsum[2][G];  // sum(q) of rows 2c, 2c+1
+        int64_t row_limit[2];
+#pragma unroll
+        for (int gr = 0; gr < G; ++gr) {
+            float v = qsum_own[gr];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            qsum[0][gr] = __shfl_sync(0xffffffffu, v, (2 * c) * 4);
+            qsum[1][gr] = __shfl_sync(0xffffffffu, v, (2 * c + 1) * 4);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int r = 2 * c + k;
+            const int l = r % p.L;
+            row_limit[k] = (r < R) ? (p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+        }
+
+        const int blk = warp;
+        // ldmatrix rows: matrix mi = lane / 8 -> tokens (mi >> 1) * 8 + lane % 8, chunk parity mi & 1
+        const int v_tok = blk * 16 + ((lane >> 4) & 1) * 8 + (lane & 7);
+        const int v_chunk_off = (lane >> 3) & 1;
+
+        for (int it = 0; it < ntiles && ok; ++it) {
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) break;
+            if (p.debug_skip) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                continue;
+            }
+            const unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+            const unsigned char *kct = st;
+            const unsigned char *vct = st + CODE_TILE;
+            const T *kst = (const T *)(st + 2 * CODE_TILE);
+            const T *kbt = (const T *)(st + 2 * CODE_TILE + SC_TILE);
+            const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
+            const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
+            const int64_t t_blk = (int64_t)(tile_begin + it) * PK_TILE + blk * 16;
+            const int tl0 = blk * 16 + g, tl1 = tl0 + 8;  // this lane's two tokens inside the tile
+
+            // ---- S^T = codes . Q^T per group ----
+            float acc[G][4];
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                acc[gr][0] = acc[gr][1] = acc[gr][2] = acc[gr][3] = 0.f;
+                const uint32_t *w0 = (const uint32_t *)(kct + tl0 * RB) + gr * WPG + c * WPL;
+                const uint32_t *w1 = (const uint32_t *)(kct + tl1 * RB) + gr * WPG + c * WPL;
+                uint32_t wa[WPL], wb[WPL];
+#pragma unroll
+                for (int k = 0; k < WPL; ++k) {
+                    wa[k] = w0[k];
+                    wb[k] = w1[k];
+                }
+#pragma unroll
+                for (int m = 0; m < MPG; ++m) {
+                    const int wi = m / MPW, which = m % MPW;
+                    uint32_t a[4];
+                    a[0] = code_f16_pair<BITS>(wa[wi], 2 * which);       // token g,   k-slots 2c, 2c+1
+                    a[1] = code_f16_pair<BITS>(wb[wi], 2 * which);       // token g+8
+                    a[2] = code_f16_pair<BITS>(wa[wi], 2 * which + 1);   // token g,   k-slots 2c+8, 2c+9
+                    a[3] = code_f16_pair<BITS>(wb[wi], 2 * which + 1);   // token g+8
+                    mma_f16(acc[gr], a, qb[gr][m][0], qb[gr][m][1]);
+                }
+            }
+            // ---- scores: s * acc + (b - OFF s) * sum(q) ----
+            float sc[4];
+            {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int gr = 0; gr < G; ++gr) {
+                    const float s0 = to_f32<T>(kst[tl0 * G + gr]), s1 = to_f32<T>(kst[tl1 * G + gr]);
+                    const float b0 = to_f32<T>(kbt[tl0 * G + gr]) - OFF * s0;
+                    const float b1 = to_f32<T>(kbt[tl1 * G + gr]) - OFF * s1;
+                    v[0] += s0 * acc[gr][0] + b0 * qsum[0][gr];
+                    v[1] += s0 * acc[gr][1] + b0 * qsum[1][gr];
+                    v[2] += s1 * acc[gr][2] + b1 * qsum[0][gr];
+                    v[3] += s1 * acc[gr][3] + b1 * qsum[1][gr];
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t t = t_blk + g + ((e >> 1) ? 8 : 0);
+                    sc[e] = (t <= row_limit[e & 1]) ? v[e] * p.scale_log2 : -INFINITY;
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                float mx = fmaxf(sc[k], sc[k + 2]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_run[k], mx);
+                alpha[k] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[k] - m_new);
+                m_run[k] = m_new;
+            }
+            float pr[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pr[e] = (m_run[e & 1] == -INFINITY) ? 0.f : fast_exp2(sc[e] - m_run[e & 1]);
+            const bool rescale = __any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f));
+            l_run[0] = l_run[0] * alpha[0] + pr[0] + pr[2];
+            l_run[1] = l_run[1] * alpha[1] + pr[1] + pr[3];
+            if (rescale) {
+#pragma unroll
+                for (int mt = 0; mt < MT_O; ++mt) {
+                    o_acc[mt][0] *= alpha[0];
+                    o_acc[mt][1] *= alpha[1];
+                    o_acc[mt][2] *= alpha[0];
+                    o_acc[mt][3] *= alpha[1];
+                }
+#pragma unroll
+                for (int gr = 0; gr < G; ++gr) {
+                    bsum[0][gr] *= alpha[0];
+                    bsum[1][gr] *= alpha[1];
+                }
+            }
+            // ---- P'^T = (p * s_v)^T per group, moved to the B-fragment layout ----
+            uint32_t pb[G][2];
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                const float s0 = to_f32<T>(vst[tl0 * G + gr]), s1 = to_f32<T>(vst[tl1 * G + gr]);
+                const float b0 = to_f32<T>(vbt[tl0 * G + gr]), b1 = to_f32<T>(vbt[tl1 * G + gr]);
+                const uint32_t x0 = pack_h2(pr[0] * s0, pr[1] * s0);  // tokens 0..7 of the block
+                const uint32_t x1 = pack_h2(pr[2] * s1, pr[3] * s1);  // tokens 8..15
+                pb[gr][0] = movmatrix_trans(x0);
+                pb[gr][1] = movmatrix_trans(x1);
+                // The MMA sees the f16-rounded p*s times (OFF + code); take OFF times exactly
+                // those rounded values back out, so the offset cancels without error.
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&x0));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&x1));
+                bsum[0][gr] += pr[0] * b0 + pr[2] * b1 - OFF * (f0.x + f1.x);
+                bsum[1][gr] += pr[1] * b0 + pr[3] * b1 - OFF * (f0.y + f1.y);
+            }
+            // ---- O^T += codes^T . P'^T ----
+            const uint32_t v_row = smem_u32(vct + v_tok * RB);
+#pragma unroll
+            for (int cp = 0; cp < CH / 2; ++cp) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, v_row + (2 * cp + v_chunk_off) * 16);
+                constexpr int dims_per_pair = 2 * 8 * EPU;
+                const int gr = (cp * dims_per_pair) / GROUP;
+#pragma unroll
+                for (int i = 0; i < EPU; ++i) {
+                    uint32_t a[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) a[k] = unit_f16_pair<BITS>(vf[k], i);
+                    mma_f16(o_acc[cp * EPU + i], a, pb[gr][0], pb[gr][1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, 6);
+    }
+
+    __syncthreads();
+    float *red_o = (float *)stages;
+    float *red_ml = red_o + PK_WARPS * 16 * RED_STRIDE;
+    if (warp < PK_WARPS) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 4);
+            l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 8);
+            l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 16);
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) {
+                bsum[k][gr] += __shfl_xor_sync(0xffffffffu, bsum[k][gr], 4);
+                bsum[k][gr] += __shfl_xor_sync(0xffffffffu, bsum[k][gr], 8);
+                bsum[k][gr] += __shfl_xor_sync(0xffffffffu, bsum[k][gr], 16);
+            }
+        }
+        float *wo = red_o + warp * 16 * RED_STRIDE;
+#pragma unroll
+        for (int mt = 0; mt < MT_O; ++mt) {
+            // m-tile mt = cp * EPU + i: d-row g <-> dim (2cp)*8*EPU + EPU*g + i, d-row g+8 <-> next chunk
+            const int cp = mt / EPU, i = mt % EPU;
+            const int d0 = (2 * cp) * 8 * EPU + EPU * g + i, d1 = d0 + 8 * EPU;
+            const int gr = d0 / GROUP;
+            wo[(2 * c) * RED_STRIDE + d0] = o_acc[mt][0] + bsum[0][gr];
+            wo[(2 * c + 1) * RED_STRIDE + d0] = o_acc[mt][1] + bsum[1][gr];
+            wo[(2 * c) * RED_STRIDE + d1] = o_acc[mt][2] + bsum[0][gr];
+            wo[(2 * c + 1) * RED_STRIDE + d1] = o_acc[mt][3] + bsum[1][gr];
+        }
+        if (g == 0) {
+            red_ml[(warp * 16 + 2 * c) * 2 + 0] = m_run[0];
+            red_ml[(warp * 16 + 2 * c) * 2 + 1] = l_run[0];
+            red_ml[(warp * 16 + 2 * c + 1) * 2 + 0] = m_run[1];
+            red_ml[(warp * 16 + 2 * c + 1) * 2 + 1] = l_run[1];
+        }
+    }
+    __syncthreads();
+    UnitOut u;
+    u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+    u.out = p.out; u.out_dtype = p.out_dtype;
+    u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+    u.o_signs = nullptr;
+    u.splits = p.splits; u.Hq = p.Hq; u.L = p.L;
+    float *work = red_ml + PK_WARPS * 16 * 2;
+    unit_epilogue<D, PK_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
+}
+
+int *packed_status_word(int device) {
+    static int *words[64] = {nullptr};
+    if (device < 0 || device >= 64) return nullptr;
+    if (!words[device]) {
+        int *w = nullptr;
+        if (cudaMalloc(&w, sizeof(int)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        (void)cudaMemset(w, 0, sizeof(int));
+        words[device] = w;
+    }
+    return words[device];
+}
+
+template <typename T, int D, int BITS, int GROUP, int NSTAGE>
+void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) {
+    constexpr int G = D / GROUP;
+    constexpr int RB = D * BITS / 8;
+    constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
+    constexpr int RED_BYTES = PK_WARPS * 16 * (D + 8) * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
+    constexpr int BODY = NSTAGE * STAGE_BYTES > RED_BYTES ? NSTAGE * STAGE_BYTES : RED_BYTES;
+    const size_t smem = (size_t)BODY + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + 128;
+    static bool configured[64] = {false};
+    const int dev = current_device();
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_kernel<T, D, BITS, GROUP, NSTAGE>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_kernel<T, D, BITS, GROUP, NSTAGE>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+        configured[dev] = true;
+    }
+    KernelTimer timer(stream);
+    attn_affine_kernel<T, D, BITS, GROUP, NSTAGE><<<units, PK_THREADS, smem, stream>>>(p);
+    timer.stop();
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+template <typename T, int D, int BITS, int GROUP, int NSTAGE>
+void launch_affine8_typed(const AffineParams &p, int units, cudaStream_t stream) {
+    constexpr int G = D / GROUP;
+    constexpr int RB = D * BITS / 8;
+    constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
+    constexpr int RED_BYTES = PK_WARPS * 16 * (D + 8) * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
+    constexpr int BODY = NSTAGE * STAGE_BYTES > RED_BYTES ? NSTAGE * STAGE_BYTES : RED_BYTES;
+    const size_t smem = (size_t)BODY + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + 128;
+    static bool configured[64] = {false};
+    const int dev = current_device();
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+        configured[dev] = true;
+    }
+    KernelTimer timer(stream);
+    attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE><<<units, PK_THREADS, smem, stream>>>(p);
+    timer.stop();
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+bool affine_source_fits(const KVSource &s, int D, int64_t T) {
+    if (s.kind != SRC_AFFINE || (s.dtype != KVC_BF16 && s.dtype != KVC_F16)) return false;
+    if (s.bits != 4 && s.bits != 8) return false;
+    if (s.group != 32 && s.group != 64 && s.group != 128) return false;
+    if (D % s.group) return false;
+    const int wpr = D * s.bits / 32, G = D / s.group;
+    if (s.st != wpr || s.gst != G) return false;  // rows must be contiguous
+    const int64_t padded = (T + PK_TILE - 1) / PK_TILE * PK_TILE;
+    // a full last tile must stay inside the (batch, head) slab, and slabs must keep 16-byte alignment
+    if (s.sh < padded * wpr || s.gsh < padded * G) return false;
+    if ((s.sh * 4) % 16 || (s.sb * 4) % 16 || (s.gsh * 2) % 16 || (s.gsb * 2) % 16) return false;
+    if (((uintptr_t)s.data & 15) || ((uintptr_t)s.scales & 15) || ((uintptr_t)s.biases & 15)) return false;
+    return true;
+}
+
+}  // namespace
+
+int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
+    if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
+    if (a.D != 64 && a.D != 128) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib) return 0;
+    if (a.k.kind != SRC_AFFINE || a.v.kind != SRC_AFFINE) return 0;
+    if (a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
+    if (a.k.bits != a.v.bits || a.k.group != a.v.group) return 0;
+    if (a.Hkv <= 0 || a.Hq % a.Hkv) return 0;
+    const int rep = a.Hq / a.Hkv;
+    if (rep * a.L > 16 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    if (!affine_source_fits(a.k, a.D, a.T) || !affine_source_fits(a.v, a.D, a.T)) return 0;
+    if (a.D / a.k.group > 4 || (a.k.group * a.k.bits) / 32 < 4) return 0;
+    if (((uintptr_t)a.q & 1)) return 0;
+    const int64_t bh = (int64_t)a.B * a.Hkv;
+    if (bh * (int64_t)sizeof(int) > PK_COUNTER_BYTES) return 0;
+    int *status = packed_status_word(a.device);
+    if (!status) return 0;
+    int *counters = counters_get(a.device, stream, PK_COUNTER_BYTES);
+
+    const int64_t tiles = (a.T + PK_TILE - 1) / PK_TILE;
+    // at most 8 query rows and chunk pairs inside one group: transposed decode kernel, 3 CTAs per SM
+    const bool decode8 = rep * a.L <= 8 && (2 * 8 * (16 / a.k.bits)) <= a.k.group;
+    const int slots = sm_count(a.device) * (decode8 ? 3 : 2);
+    int64_t best_s = 1;
+    double best_cost = 1e30;
+    const int64_t max_s = std::min<int64_t>(tiles, 64);
+    for (int64_t s = 1; s <= max_s; ++s) {
+        const int64_t units = bh * s;
+        const int64_t waves = (units + slots - 1) / slots;
+        const int64_t per = (tiles + s - 1) / s;
+        const double cost = (double)waves * ((double)per + 6.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best_s = s;
+        }
+    }
+    const int64_t splits = best_s;
+    const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
+    const size_t o_bytes = (size_t)qrows * splits * a.D * sizeof(float);
+    const size_t ml_bytes = (size_t)qrows * splits * sizeof(float2);
+    char *scratch = (char *)scratch_get(a.device, o_bytes + ml_bytes + 256, stream);
+
+    AffineParams p;
+    p.q = a.q; p.out = a.out; p.out_dtype = a.q_dtype;
+    p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.kc = (const uint32_t *)a.k.data; p.vc = (const uint32_t *)a.v.data;
+    p.ks = a.k.scales; p.kb = a.k.biases; p.vs = a.v.scales; p.vb = a.v.biases;
+    p.kc_sb = a.k.sb; p.kc_sh = a.k.sh; p.vc_sb = a.v.sb; p.vc_sh = a.v.sh;
+    p.kg_sb = a.k.gsb; p.kg_sh = a.k.gsh; p.vg_sb = a.v.gsb; p.vg_sh = a.v.gsh;
+    p.o_part = (float *)scratch;
+    p.ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
+    p.counters = counters; p.status = status;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
+    p.splits = (int)splits;
+    p.tiles_base = (int)(tiles / splits);
+    p.tiles_rem = (int)(tiles % splits);
+    p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    {
+        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
+        p.debug_skip = (e && e[0] == '1') ? 1 : 0;
+    }
+    p.causal_offset = a.mask.causal_offset;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    const int units = (int)(bh * splits);
+
+    const int bits = a.k.bits, group = a.k.group;
+#define KVC_AFF8(TT, DD, BB, GG, NS)                                         \
+    if (a.D == DD && bits == BB && group == GG) {                            \
+        launch_affine8_typed<TT, DD, BB, GG, NS>(p, units, stream);          \
+        return 1;                                                            \
+    }
+    if (decode8) {
+        if (a.q_dtype == KVC_BF16) {
+            KVC_AFF8(__nv_bfloat16, 128, 4, 64, 6)
+            KVC_AFF8(__nv_bfloat16, 128, 8, 64, 4)
+            KVC_AFF8(__nv_bfloat16, 128, 4, 128, 6)
+            KVC_AFF8(__nv_bfloat16, 128, 8, 128, 4)
+            KVC_AFF8(__nv_bfloat16, 128, 8, 32, 4)
+            KVC_AFF8(__nv_bfloat16, 64, 4, 64, 8)
+            KVC_AFF8(__nv_bfloat16, 64, 8, 64, 6)
+        } else {
+            KVC_AFF8(__half, 128, 4, 64, 6)
+            KVC_AFF8(__half, 128, 8, 64, 4)
+            KVC_AFF8(__half, 128, 4, 128, 6)
+            KVC_AFF8(__half, 128, 8, 128, 4)
+            KVC_AFF8(__half, 128, 8, 32, 4)
+            KVC_AFF8(__half, 64, 4, 64, 8)
+            KVC_AFF8(__half, 64, 8, 64, 6)
+        }
+    }
+#undef KVC_AFF8
+#define KVC_AFF(TT, DD, BB, GG, NS)                                          \
+    if (a.D == DD && bits == BB && group == GG) {                            \
+        launch_affine_typed<TT, DD, BB, GG, NS>(p, units, stream);           \
+        return 1;                                                            \
+    }
+    if (a.q_dtype == KVC_BF16) {
+        KVC_AFF(__nv_bfloat16, 128, 4, 64, 8)
+        KVC_AFF(__nv_bfloat16, 128, 8, 64, 5)
+        KVC_AFF(__nv_bfloat16, 128, 4, 32, 8)
+        KVC_AFF(__nv_bfloat16, 128, 4, 128, 8)
+        KVC_AFF(__nv_bfloat16, 128, 8, 128, 5)
+        KVC_AFF(__nv_bfloat16, 64, 4, 64, 8)
+        KVC_AFF(__nv_bfloat16, 64, 8, 64, 8)
+    } else {
+        KVC_AFF(__half, 128, 4, 64, 8)
+        KVC_AFF(__half, 128, 8, 64, 5)
+        KVC_AFF(__half, 128, 4, 32, 8)
+        KVC_AFF(__half, 128, 4, 128, 8)
+        KVC_AFF(__half, 128, 8, 128, 5)
+        KVC_AFF(__half, 64, 4, 64, 8)
+        KVC_AFF(__half, 64, 8, 64, 8)
+    }
+#undef KVC_AFF
+    return 0;
+}
+
+}  // namespace kvc

@@ -169,7 +169,9 @@ void check_new_rows(const kvc_cache *c, const Array4 &ka, const Array4 &va, cons
 // Array4
 // ---------------------------------------------------------------------
 void Array4::alloc(int64_t b, int64_t h, int64_t c, int64_t w, int32_t dt, cudaStream_t s) {
-    B = b; H = h; cap = std::max<int64_t>(c, 1); W = w; dtype = dt;
+    // capacity in whole 64-token tiles: the TMA-staged attention kernels copy full
+    // tiles, and a tile must never reach past the (batch, head) slab
+    B = b; H = h; cap = round_up(std::max<int64_t>(c, 1), 64); W = w; dtype = dt;
     ptr = dev_alloc(bytes(), s);
     KVC_CUDA(cudaMemsetAsync(ptr, 0, bytes(), s));
 }

@@ -1,0 +1,70 @@
+"""The TMA-staged tensor-core decode kernels over packed caches (affine codes,
+TurboQuant indices) against the oracle, driven through the cache objects the
+way attentionWithCacheUpdate drives them."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,D,bits,group,P", [
+    (2, 28, 4, 128, 4, 64, 3000),    # Qwen2-7B shape, 4-bit (7 query heads per KV head)
+    (2, 32, 8, 128, 8, 64, 1000),
+    (1, 32, 8, 64, 8, 64, 1024),     # Llama-3.2-1B shape
+    (2, 8, 2, 128, 4, 32, 200),
+    (2, 8, 2, 128, 4, 128, 77),
+    (1, 64, 8, 128, 8, 128, 129),
+    (2, 16, 4, 64, 4, 64, 63),
+])
+def test_affine_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, D, bits, group, P):
+    g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
+    k = seeded((B, Hkv, P, D), 1, dtype, outlier_frac=0.01)
+    v = seeded((B, Hkv, P, D), 2, dtype, outlier_frac=0.01)
+    g.update_quantized(k.to(cuda), v.to(cuda))
+    o.update_quantized(to_oracle(k), to_oracle(v))
+    scale = D ** -0.5
+    for step in range(3):
+        q = seeded((B, Hq, 1, D), 10 + step, dtype)
+        k1, v1 = seeded((B, Hkv, 1, D), 20 + step, dtype), seeded((B, Hkv, 1, D), 30 + step, dtype)
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, scale)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"step {step}"
+    assert kvc.lib().kvc_device_status() == 0
+    for a, b in zip(g.state, o.state):
+        assert bits_equal(a, np.ascontiguousarray(b))
+
+
+def test_affine_small_causal_chunk(kvc, oracle, cuda):
+    B, Hq, Hkv, D, L = 2, 4, 2, 128, 6
+    g, o = kvc.QuantizedKVCache(64, 4), oracle.QuantizedKVCache(64, 4)
+    k, v = seeded((B, Hkv, 500, D), 1, torch.bfloat16), seeded((B, Hkv, 500, D), 2, torch.bfloat16)
+    g.update_quantized(k.to(cuda), v.to(cuda))
+    o.update_quantized(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, torch.bfloat16)
+    k1, v1 = seeded((B, Hkv, L, D), 4, torch.bfloat16), seeded((B, Hkv, L, D), 5, torch.bfloat16)
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), 0.09, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, 0.09, "causal")
+    assert max_abs_diff(out, ref) <= 2e-2
+
+
+def test_affine_kernel_with_large_queries_and_scales(kvc, oracle, cuda):
+    """Outlier channels x20 in K/V and queries of magnitude ~10: the f16 operand
+    path must stay within tolerance."""
+    B, Hq, Hkv, D = 1, 8, 2, 128
+    g, o = kvc.QuantizedKVCache(64, 4), oracle.QuantizedKVCache(64, 4)
+    k = seeded((B, Hkv, 700, D), 1, torch.bfloat16, outlier_frac=0.05)
+    v = seeded((B, Hkv, 700, D), 2, torch.bfloat16, outlier_frac=0.05)
+    g.update_quantized(k.to(cuda), v.to(cuda))
+    o.update_quantized(to_oracle(k), to_oracle(v))
+    q = (seeded((B, Hq, 1, D), 3, torch.float32) * 4).to(torch.bfloat16)
+    k1, v1 = seeded((B, Hkv, 1, D), 4, torch.bfloat16), seeded((B, Hkv, 1, D), 5, torch.bfloat16)
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
+    from helpers import oracle_f32
+    biggest = float(np.abs(oracle_f32(ref)).max())
+    # outlier channels make outputs larger than 1; one bf16 ulp at |x| is x * 2^-8
+    assert max_abs_diff(out, ref) <= 2e-2 * max(1.0, biggest)
