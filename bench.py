@@ -9,9 +9,12 @@ of the dominant attention kernel against the measured copy peak.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Under torchrun (N > 1) the KV heads (or, when there are fewer heads than GPUs,
-the batch) are sharded across ranks and every layer ends with an all-gather of
-the attention outputs; total work is fixed, so scaling is "strong".
+Under torchrun (N > 1) the default partition is by sequence: caches of different
+sequences never exchange data, so every rank serves its own batch of B
+sequences with no data-path collective and the job's value is the sum over
+ranks ("weak" scaling). `--parallel heads` instead shards the KV heads of ONE
+batch across ranks and ends every layer with an all-gather of the attention
+outputs (total work fixed, "strong" scaling).
 Inputs are synthetic (seeded N(0,1)); no dataset is involved.
 """
 from __future__ import annotations
@@ -64,6 +67,32 @@ def bytes_per_token_head(w) -> float:
     kpw = (D * w["key_bits"] + 31) // 32 * 4 + 4
     vpw = (D * w["value_bits"] + 31) // 32 * 4 + 4
     return kpw + vpw
+
+
+def partition(w, world: int, mode: str):
+    """Per-rank shape of the workload on `world` ranks.
+
+    Returns dict(shard_axis, B_local, Hkv_local, Hq_local, B_global, scaling,
+    parallelism, collective). mode "sequences": each rank holds B whole sequences
+    (independent caches; nothing crosses ranks). mode "heads": one batch of B,
+    KV heads split across ranks (batch split when heads do not divide), outputs
+    all-gathered per layer."""
+    B, Hq, Hkv = w["B"], w["Hq"], w["Hkv"]
+    if world == 1:
+        return dict(shard_axis=1, B_local=B, Hkv_local=Hkv, Hq_local=Hq, B_global=B, scaling="weak",
+                    parallelism="single", collective=False)
+    if mode == "sequences":
+        return dict(shard_axis=0, B_local=B, Hkv_local=Hkv, Hq_local=Hq, B_global=B * world, scaling="weak",
+                    parallelism=f"sequences x{world} (B={B} per rank, no collective)", collective=False)
+    if mode != "heads":
+        raise ValueError(f"unknown partition mode {mode!r}")
+    if Hkv % world == 0:
+        return dict(shard_axis=1, B_local=B, Hkv_local=Hkv // world, Hq_local=Hq // world, B_global=B,
+                    scaling="strong", parallelism=f"kv-head x{world} + all-gather", collective=True)
+    if B % world:
+        raise ValueError("neither the KV heads nor the batch divide across the ranks")
+    return dict(shard_axis=0, B_local=B // world, Hkv_local=Hkv, Hq_local=Hq, B_global=B, scaling="strong",
+                parallelism=f"batch x{world} + all-gather", collective=True)
 
 
 def torch_dtype(name):
@@ -224,7 +253,7 @@ def run_reference(args, w, rank, world):
     sec, info = cpu_decode_step_time(w, budget_s=90.0, steps=max(1, args.steps), warmup=min(args.warmup, 1))
     value = w["B"] / sec
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "impl": "reference",
             "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D", "B", "context")},
                        "timing": "CPU restatement of the reference path (MLX itself is unavailable on this box)"},
@@ -276,15 +305,10 @@ def run_ours(args, w, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
 
     dtype = torch_dtype(w["dtype"])
-    B, Hq, Hkv, D, Lyr = w["B"], w["Hq"], w["Hkv"], w["D"], w["layers"]
-    # partition: KV heads across ranks, batch when there are fewer heads than ranks
-    if Hkv % world == 0 and Hkv >= world:
-        shard_axis, Bl, Hkvl, Hql = 1, B, Hkv // world, Hq // world
-        parallelism = f"kv-head x{world}" if world > 1 else "single"
-    else:
-        assert B % world == 0, "batch must divide across ranks when heads do not"
-        shard_axis, Bl, Hkvl, Hql = 0, B // world, Hkv, Hq
-        parallelism = f"batch x{world}"
+    Hq, D, Lyr = w["Hq"], w["D"], w["layers"]
+    part = partition(w, world, args.parallel)
+    shard_axis, Bl, Hkvl, Hql = part["shard_axis"], part["B_local"], part["Hkv_local"], part["Hq_local"]
+    B, parallelism = part["B_global"], part["parallelism"]
     steps, warmup = args.steps, args.warmup
     total_steps = warmup + steps * 2 + 64
     reserve = w["context"] + total_steps + 8
@@ -304,7 +328,7 @@ def run_ours(args, w, rank, world, local_rank):
     vs = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
     scale = D ** -0.5
     comm = None
-    if world > 1:
+    if part["collective"]:
         uid = [kvc.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         comm = kvc.Comm(rank, world, uid[0])
@@ -398,11 +422,11 @@ def run_ours(args, w, rank, world, local_rank):
         _ = float(ho[-1][0, 0, 0, 0])  # the step's result is read on the host
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
-    h2d = Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es
-    d2h = Lyr * Bl * Hql * D * es
+    h2d = world * Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es  # summed over ranks
+    d2h = world * Lyr * Bl * Hql * D * es
     e2e = {"value": B * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "note": "kvc_attention_host per layer (pinned host q/k/v in, output out), one stream sync per step"
-                   + ("; per-rank shard only, no gather" if world > 1 else "")}
+                   + ("; every rank runs its own shard, bytes summed over ranks, time is the max" if world > 1 else "")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -411,9 +435,9 @@ def run_ours(args, w, rank, world, local_rank):
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": part["scaling"], "vs_baseline": None,
                 "dtype": w["dtype"], "data": "synthetic",
-                "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D", "B")},
+                "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D")}, "B": B,
                            "context_start": ctx0, "parallelism": parallelism,
                            "l2": "inputs larger than L2 (per-layer K+V working set "
                                  f"{Bl * Hkvl * ctx0 * bytes_per_token_head(w) / 1e6:.0f} MB; all layers "
@@ -434,6 +458,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="sequences", choices=["sequences", "heads"],
+                    help="N>1 partition: independent sequences per rank (weak) or KV heads of one batch (strong)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
