@@ -287,7 +287,7 @@ def fill_cache(kvc, cache, w, Bl, Hl, chunk_k, chunk_v):
         elif w["kind"] == "quantized":
             cache.update_quantized(k, v)
         else:
-            cache.append_compressed(k, v)
+            cache.encode_new_token(k, v)
         remaining -= n
 
 

@@ -387,6 +387,15 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev,
                             const float *boundaries_host, int32_t bits,
                             const kvc_tensor *packed, const kvc_tensor *norms, void *stream);
 
+/* Compressed-domain append without attention: compresses a raw prefix if the
+ * cache still holds one, then encodes keys/values [B, H, S, D] and appends them
+ * (the cache-side half of compressedAttention, TurboQuantKVCache.swift:1176-1200:
+ * compressRawCache :895 + encodeNewToken :1010-1147). Chunked prefill into the
+ * compressed representation uses this so that the raw prefix never has to exist
+ * in full. */
+kvc_status kvc_turbo_encode_new_token(kvc_cache *cache, const kvc_tensor *keys,
+                                      const kvc_tensor *values, void *stream);
+
 /* ------------------------------------------------------------------ */
 /* multi-GPU: KV-head (or batch) sharded attention + all-gather        */
 /* ------------------------------------------------------------------ */

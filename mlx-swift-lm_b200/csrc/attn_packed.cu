@@ -453,10 +453,25 @@ attn_affine_kernel(const AffineParams p) {
 //   S^T[16 tok x 8 rows]  = K[16 tok x 16 d] . Q^T[16 d x 8 rows]      (A = codes)
 //   O^T[16 d  x 8 rows]  += V^T[16 d x 16 tok] . P'^T[16 tok x 8 rows]  (A = codes via ldmatrix.trans)
 // P'^T reaches its B-fragment layout with movmatrix (an 8x8 transpose across
-// the warp). Codes are turned into f16 with the exponent trick and NO
-// subtraction: 4-bit codes land in mantissa bits 6..9 of 0x4C00 (= 16 + n),
-// 8-bit codes in the low byte of 0x6400 (= 1024 + n); the constant offset is
-// folded into the bias term (b - OFF * s), which is exact algebra.
+// the warp).
+//
+// The loop is bound by instruction issue (integer pipe first), not by the tensor
+// pipe, so every step is written for instruction count:
+//   * codes become f16 operands with one mask-or per operand register and one
+//     shift per word (CodeWord / UnitPair below);
+//   * on the K side the operands keep their exponent offset and the 1/16 factor of
+//     the low nibbles: the query fragments carry the factor 16 for those k-slots
+//     and the offset leaves as OFF * sum(q') after the MMA (a per-row constant);
+//     the accumulators restart every tile, so the cancellation costs ~1e-4 of a
+//     logit at most;
+//   * on the V side the accumulators run over the whole split, so the operands are
+//     made exact integer codes with one half2 FMA each (the FMA pipe has room);
+//   * the query is pre-multiplied by scale * log2(e), scores come out of the MMA in
+//     the exp2 domain;
+//   * the running maximum is lazy: a tile only takes the shuffle-reduce / rescale
+//     path when one of its scores exceeds the running maximum by more than 2^8,
+//     otherwise probabilities are exp2(score - stale max) <= 256, well inside f16;
+//   * the causal / length mask is only evaluated on the tiles that cross a limit.
 // ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     uint32_t r;
@@ -464,38 +479,109 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     return r;
 }
 
-// f16 pair (OFF + code_lo, OFF + code_hi) number k of a word. 4-bit: nibbles (k, k+4), k = 0..3.
-// 8-bit: bytes (2k, 2k+1), k = 0..1.
+// ---- code words -> f16 operand pairs without per-element shifts ----
+// 4-bit: a word holds nibbles n0..n7. Masking a nibble in place under the exponent of
+// 64.0 (0x5400, ulp 1/16) gives  64 + n/16  for the nibbles at bits 0..3 of a half
+// ("low" pairs) and  64 + n  for those at bits 4..7 ("high" pairs); one shift by 8
+// brings the other two nibbles of each half into reach. Pair k of a word:
+//   k = 0: (n0, n4) low    k = 1: (n1, n5) high    k = 2: (n2, n6) low    k = 3: (n3, n7) high
+// 8-bit: bytes under the exponent of 1024.0 (0x6400, ulp 1): 1024 + n, pairs (b0,b1), (b2,b3).
 template <int BITS>
-__device__ __forceinline__ uint32_t code_f16_pair(uint32_t w, int k) {
-    if (BITS == 4) {
-        uint32_t x;
-        switch (k) {
-            case 0: x = w << 6; break;
-            case 1: x = w << 2; break;
-            case 2: x = w >> 2; break;
-            default: x = w >> 6; break;
+struct CodeWord {
+    uint32_t w, w8;
+    __device__ __forceinline__ explicit CodeWord(uint32_t word) : w(word), w8(BITS == 4 ? (word >> 8) : 0u) {}
+    // pair k of the word, still carrying its offset (and the 1/16 factor of low pairs)
+    __device__ __forceinline__ uint32_t raw(int k) const {
+        if (BITS == 4) {
+            const uint32_t x = (k & 2) ? w8 : w;
+            return (k & 1) ? ((x & 0x00F000F0u) | 0x54005400u) : ((x & 0x000F000Fu) | 0x54005400u);
         }
-        return (x & 0x03C003C0u) | 0x4C004C00u;
+        return __byte_perm(w, 0x64646464u, k ? 0x4342 : 0x4140);
     }
-    return __byte_perm(w, 0x64646464u, k ? 0x4342 : 0x4140);
+    // pair k as exact integer codes in f16
+    __device__ __forceinline__ uint32_t exact(int k) const {
+        const uint32_t x = raw(k);
+        uint32_t r;
+        if (BITS == 4) {
+            if (k & 1) asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0xD400D400u));             // - 64
+            else asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0x4C004C00u), "r"(0xE400E400u));  // * 16 - 1024
+        } else {
+            asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0xE400E400u));                       // - 1024
+        }
+        return r;
+    }
+};
+
+// The register ldmatrix.trans returns from a V code tile holds two 16-bit units (token 2c in
+// the low half, token 2c+1 in the high half); element i of both units as exact f16 codes.
+// 4-bit units hold 4 elements (same nibble positions as above), 8-bit units 2.
+template <int BITS>
+struct UnitPair {
+    uint32_t v, v8;
+    __device__ __forceinline__ explicit UnitPair(uint32_t reg) : v(reg), v8(BITS == 4 ? (reg >> 8) : 0u) {}
+    __device__ __forceinline__ uint32_t exact(int i) const {
+        uint32_t x, r;
+        if (BITS == 4) {
+            const uint32_t src = (i & 2) ? v8 : v;
+            if (i & 1) {
+                x = (src & 0x00F000F0u) | 0x54005400u;
+                asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0xD400D400u));
+            } else {
+                x = (src & 0x000F000Fu) | 0x54005400u;
+                asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0x4C004C00u), "r"(0xE400E400u));
+            }
+        } else {
+            x = __byte_perm(v, 0x64646464u, i ? 0x4341 : 0x4240);
+            asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0xE400E400u));
+        }
+        return r;
+    }
+};
+
+// Two consecutive scale / bias elements (storage dtype T) as floats.
+template <typename T> __device__ __forceinline__ float2 unpack_pair(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+template <> __device__ __forceinline__ float2 unpack_pair<__half>(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&w));
 }
 
-// Same for the register ldmatrix.trans returns from a V code tile: element i of the two
-// 16-bit units (token 2c in the low half, token 2c+1 in the high half).
-template <int BITS>
-__device__ __forceinline__ uint32_t unit_f16_pair(uint32_t v, int i) {
-    if (BITS == 4) {
-        uint32_t x;
-        switch (i) {
-            case 0: x = v << 6; break;
-            case 1: x = v << 2; break;
-            case 2: x = v >> 2; break;
-            default: x = v >> 6; break;
+// The G group values of token `tok` from a [tokens][G] tile in shared memory.
+template <typename T, int G>
+__device__ __forceinline__ void load_groups(const T *tile, int tok, float (&out)[G]) {
+    if (G == 1) {
+        out[0] = to_f32<T>(tile[tok]);
+    } else {
+        const uint32_t *p32 = reinterpret_cast<const uint32_t *>(tile + tok * G);
+#pragma unroll
+        for (int i = 0; i < G / 2; ++i) {
+            const float2 f = unpack_pair<T>(p32[i]);
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
         }
-        return (x & 0x03C003C0u) | 0x4C004C00u;
     }
-    return __byte_perm(v, 0x64646464u, i ? 0x4341 : 0x4240);
+}
+
+// N consecutive 32-bit words from shared memory with the widest loads the count allows.
+template <int N>
+__device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&dst)[N]) {
+    if (N % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const uint4 x = reinterpret_cast<const uint4 *>(src)[i];
+            dst[4 * i] = x.x; dst[4 * i + 1] = x.y; dst[4 * i + 2] = x.z; dst[4 * i + 3] = x.w;
+        }
+    } else if (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            const uint2 x = reinterpret_cast<const uint2 *>(src)[i];
+            dst[2 * i] = x.x; dst[2 * i + 1] = x.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) dst[i] = src[i];
+    }
 }
 
 template <typename T, int D, int BITS, int GROUP, int NSTAGE>
@@ -588,10 +674,16 @@ attn_affine_decode8_kernel(const AffineParams p) {
         }
     } else {
         // Q^T fragments: B operand column = query row g; k-slots follow the code words.
+        // q' = f16(q * scale * log2 e); the k-slots fed by low nibbles carry 16 q'.
+        // K_EXACT: the K operands are made exact integer codes like the V operands (one half2
+        // FMA each); otherwise they keep offset and nibble factor and the query carries them.
+        constexpr bool K_EXACT = true;
+        constexpr float LOWMUL = K_EXACT ? 1.f : ((BITS == 4) ? 16.f : 1.f);
+        constexpr float OFFK = K_EXACT ? 0.f : ((BITS == 4) ? 64.f : 1024.f);
         uint32_t qb[G][MPG][2];
-        float qsum_own[G];
+        float qsum_own[G], qoff_own[G];
 #pragma unroll
-        for (int gr = 0; gr < G; ++gr) qsum_own[gr] = 0.f;
+        for (int gr = 0; gr < G; ++gr) qsum_own[gr] = qoff_own[gr] = 0.f;
 #pragma unroll
         for (int gr = 0; gr < G; ++gr) {
 #pragma unroll
@@ -603,34 +695,51 @@ attn_affine_decode8_kernel(const AffineParams p) {
                     const int hq = hk * rep + g / p.L, l = g % p.L;
                     const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]])));
+                    for (int k = 0; k < 4; ++k)
+                        x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]]) * p.scale_log2));
                 }
-                qb[gr][m][0] = pack_h2(x[0], x[1]);
-                qb[gr][m][1] = pack_h2(x[2], x[3]);
+                qb[gr][m][0] = pack_h2(x[0] * LOWMUL, x[1] * LOWMUL);   // k-slots 2c, 2c+1: low pairs
+                qb[gr][m][1] = pack_h2(x[2], x[3]);                     // k-slots 2c+8, 2c+9: high pairs
                 qsum_own[gr] += x[0] + x[1] + x[2] + x[3];
+                qoff_own[gr] += LOWMUL * (x[0] + x[1]) + x[2] + x[3];
             }
         }
-        float qsum[2][G];  // sum(q) of rows 2c, 2c+1
-        int64_t row_limit[2];
+        float qsum[2][G];    // sum(q') of rows 2c, 2c+1 (multiplies the bias)
+        float negoff[2][G];  // -OFF * sum of the operand-side q' (takes the exponent offset back out)
 #pragma unroll
         for (int gr = 0; gr < G; ++gr) {
-            float v = qsum_own[gr];
+            float v = qsum_own[gr], w = qoff_own[gr];
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
+            w += __shfl_xor_sync(0xffffffffu, w, 1);
+            w += __shfl_xor_sync(0xffffffffu, w, 2);
             qsum[0][gr] = __shfl_sync(0xffffffffu, v, (2 * c) * 4);
             qsum[1][gr] = __shfl_sync(0xffffffffu, v, (2 * c + 1) * 4);
+            negoff[0][gr] = -OFFK * __shfl_sync(0xffffffffu, w, (2 * c) * 4);
+            negoff[1][gr] = -OFFK * __shfl_sync(0xffffffffu, w, (2 * c + 1) * 4);
         }
+        // Last visible token per row. Rows past R hold zero queries and are never written
+        // out; they take the limit of a real row so that they do not force the mask path.
+        int row_limit[2];
+        const int t_last = (int)(p.T - 1);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int r = 2 * c + k;
-            const int l = r % p.L;
-            row_limit[k] = (r < R) ? (p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+            const int l = (r < R) ? r % p.L : 0;
+            row_limit[k] = p.causal ? (int)min((int64_t)t_last, p.causal_offset + l) : t_last;
         }
+        const int min_limit = p.causal ? (int)min((int64_t)t_last, p.causal_offset) : t_last;
+        constexpr float M_INIT = -1e30f, LAZY = 8.f;
+        m_run[0] = m_run[1] = M_INIT;
+        float m_thr[2] = {M_INIT, M_INIT};  // m_run + LAZY once a maximum exists
 
         const int blk = warp;
         // ldmatrix rows: matrix mi = lane / 8 -> tokens (mi >> 1) * 8 + lane % 8, chunk parity mi & 1
         const int v_tok = blk * 16 + ((lane >> 4) & 1) * 8 + (lane & 7);
         const int v_chunk_off = (lane >> 3) & 1;
+        const int tl0 = blk * 16 + g, tl1 = tl0 + 8;  // this lane's two tokens inside a tile
+        const uint32_t k_off0 = tl0 * RB + c * WPL * 4, k_off1 = tl1 * RB + c * WPL * 4;
+        const uint32_t v_off = v_tok * RB + v_chunk_off * 16;
 
         for (int it = 0; it < ntiles && ok; ++it) {
             const int s = it % NSTAGE;
@@ -648,120 +757,137 @@ attn_affine_decode8_kernel(const AffineParams p) {
             const T *kbt = (const T *)(st + 2 * CODE_TILE + SC_TILE);
             const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
             const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
-            const int64_t t_blk = (int64_t)(tile_begin + it) * PK_TILE + blk * 16;
-            const int tl0 = blk * 16 + g, tl1 = tl0 + 8;  // this lane's two tokens inside the tile
+            const int t_blk = (tile_begin + it) * PK_TILE + blk * 16;
 
-            // ---- S^T = codes . Q^T per group ----
+            // ---- S^T = codes . Q'^T per group (operands keep offset and nibble factor) ----
             float acc[G][4];
 #pragma unroll
             for (int gr = 0; gr < G; ++gr) {
                 acc[gr][0] = acc[gr][1] = acc[gr][2] = acc[gr][3] = 0.f;
-                const uint32_t *w0 = (const uint32_t *)(kct + tl0 * RB) + gr * WPG + c * WPL;
-                const uint32_t *w1 = (const uint32_t *)(kct + tl1 * RB) + gr * WPG + c * WPL;
                 uint32_t wa[WPL], wb[WPL];
+                load_words<WPL>((const uint32_t *)(kct + k_off0) + gr * WPG, wa);
+                load_words<WPL>((const uint32_t *)(kct + k_off1) + gr * WPG, wb);
 #pragma unroll
-                for (int k = 0; k < WPL; ++k) {
-                    wa[k] = w0[k];
-                    wb[k] = w1[k];
-                }
+                for (int wi = 0; wi < WPL; ++wi) {
+                    const CodeWord<BITS> ca(wa[wi]), cb(wb[wi]);
 #pragma unroll
-                for (int m = 0; m < MPG; ++m) {
-                    const int wi = m / MPW, which = m % MPW;
-                    uint32_t a[4];
-                    a[0] = code_f16_pair<BITS>(wa[wi], 2 * which);       // token g,   k-slots 2c, 2c+1
-                    a[1] = code_f16_pair<BITS>(wb[wi], 2 * which);       // token g+8
-                    a[2] = code_f16_pair<BITS>(wa[wi], 2 * which + 1);   // token g,   k-slots 2c+8, 2c+9
-                    a[3] = code_f16_pair<BITS>(wb[wi], 2 * which + 1);   // token g+8
-                    mma_f16(acc[gr], a, qb[gr][m][0], qb[gr][m][1]);
+                    for (int which = 0; which < MPW; ++which) {
+                        uint32_t a[4];
+                        if (K_EXACT) {
+                            a[0] = ca.exact(2 * which);       // token g,   k-slots 2c, 2c+1
+                            a[1] = cb.exact(2 * which);       // token g+8
+                            a[2] = ca.exact(2 * which + 1);   // token g,   k-slots 2c+8, 2c+9
+                            a[3] = cb.exact(2 * which + 1);   // token g+8
+                        } else {
+                            a[0] = ca.raw(2 * which);
+                            a[1] = cb.raw(2 * which);
+                            a[2] = ca.raw(2 * which + 1);
+                            a[3] = cb.raw(2 * which + 1);
+                        }
+                        mma_f16(acc[gr], a, qb[gr][wi * MPW + which][0], qb[gr][wi * MPW + which][1]);
+                    }
                 }
             }
-            // ---- scores: s * acc + (b - OFF s) * sum(q) ----
-            float sc[4];
+            // ---- scores (already in the exp2 domain): s * (acc - OFF qoff) + b * sum(q') ----
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};
             {
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                float s0[G], s1[G], b0[G], b1[G];
+                load_groups<T, G>(kst, tl0, s0);
+                load_groups<T, G>(kst, tl1, s1);
+                load_groups<T, G>(kbt, tl0, b0);
+                load_groups<T, G>(kbt, tl1, b1);
 #pragma unroll
                 for (int gr = 0; gr < G; ++gr) {
-                    const float s0 = to_f32<T>(kst[tl0 * G + gr]), s1 = to_f32<T>(kst[tl1 * G + gr]);
-                    const float b0 = to_f32<T>(kbt[tl0 * G + gr]) - OFF * s0;
-                    const float b1 = to_f32<T>(kbt[tl1 * G + gr]) - OFF * s1;
-                    v[0] += s0 * acc[gr][0] + b0 * qsum[0][gr];
-                    v[1] += s0 * acc[gr][1] + b0 * qsum[1][gr];
-                    v[2] += s1 * acc[gr][2] + b1 * qsum[0][gr];
-                    v[3] += s1 * acc[gr][3] + b1 * qsum[1][gr];
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int64_t t = t_blk + g + ((e >> 1) ? 8 : 0);
-                    sc[e] = (t <= row_limit[e & 1]) ? v[e] * p.scale_log2 : -INFINITY;
+                    const float n0 = K_EXACT ? 0.f : negoff[0][gr], n1 = K_EXACT ? 0.f : negoff[1][gr];
+                    sc[0] = fmaf(s0[gr], acc[gr][0] + n0, fmaf(b0[gr], qsum[0][gr], sc[0]));
+                    sc[1] = fmaf(s0[gr], acc[gr][1] + n1, fmaf(b0[gr], qsum[1][gr], sc[1]));
+                    sc[2] = fmaf(s1[gr], acc[gr][2] + n0, fmaf(b1[gr], qsum[0][gr], sc[2]));
+                    sc[3] = fmaf(s1[gr], acc[gr][3] + n1, fmaf(b1[gr], qsum[1][gr], sc[3]));
                 }
             }
-            float alpha[2];
+            if (t_blk + 15 > min_limit) {  // warp-uniform: only tiles that cross a limit
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                float mx = fmaxf(sc[k], sc[k + 2]);
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float m_new = fmaxf(m_run[k], mx);
-                alpha[k] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[k] - m_new);
-                m_run[k] = m_new;
+                for (int e = 0; e < 4; ++e) {
+                    const int t = t_blk + g + ((e >> 1) ? 8 : 0);
+                    if (t > row_limit[e & 1]) sc[e] = -INFINITY;
+                }
+            }
+            // ---- lazy running maximum ----
+            {
+                const float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+                if (__any_sync(0xffffffffu, (mx0 > m_thr[0]) | (mx1 > m_thr[1]))) {
+                    float mx[2] = {mx0, mx1}, alpha[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 4));
+                        mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 8));
+                        mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 16));
+                        const float m_new = fmaxf(m_run[k], mx[k]);
+                        alpha[k] = fast_exp2(m_run[k] - m_new);
+                        m_run[k] = m_new;
+                        m_thr[k] = (m_new > M_INIT) ? m_new + LAZY : M_INIT;
+                        l_run[k] *= alpha[k];
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT_O; ++mt) {
+                        o_acc[mt][0] *= alpha[0];
+                        o_acc[mt][1] *= alpha[1];
+                        o_acc[mt][2] *= alpha[0];
+                        o_acc[mt][3] *= alpha[1];
+                    }
+#pragma unroll
+                    for (int gr = 0; gr < G; ++gr) {
+                        bsum[0][gr] *= alpha[0];
+                        bsum[1][gr] *= alpha[1];
+                    }
+                }
             }
             float pr[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) pr[e] = (m_run[e & 1] == -INFINITY) ? 0.f : fast_exp2(sc[e] - m_run[e & 1]);
-            const bool rescale = __any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f));
-            l_run[0] = l_run[0] * alpha[0] + pr[0] + pr[2];
-            l_run[1] = l_run[1] * alpha[1] + pr[1] + pr[3];
-            if (rescale) {
-#pragma unroll
-                for (int mt = 0; mt < MT_O; ++mt) {
-                    o_acc[mt][0] *= alpha[0];
-                    o_acc[mt][1] *= alpha[1];
-                    o_acc[mt][2] *= alpha[0];
-                    o_acc[mt][3] *= alpha[1];
-                }
-#pragma unroll
-                for (int gr = 0; gr < G; ++gr) {
-                    bsum[0][gr] *= alpha[0];
-                    bsum[1][gr] *= alpha[1];
-                }
-            }
+            for (int e = 0; e < 4; ++e) pr[e] = fast_exp2(sc[e] - m_run[e & 1]);
+            l_run[0] += pr[0] + pr[2];
+            l_run[1] += pr[1] + pr[3];
             // ---- P'^T = (p * s_v)^T per group, moved to the B-fragment layout ----
             uint32_t pb[G][2];
+            {
+                float s0[G], s1[G], b0[G], b1[G];
+                load_groups<T, G>(vst, tl0, s0);
+                load_groups<T, G>(vst, tl1, s1);
+                load_groups<T, G>(vbt, tl0, b0);
+                load_groups<T, G>(vbt, tl1, b1);
 #pragma unroll
-            for (int gr = 0; gr < G; ++gr) {
-                const float s0 = to_f32<T>(vst[tl0 * G + gr]), s1 = to_f32<T>(vst[tl1 * G + gr]);
-                const float b0 = to_f32<T>(vbt[tl0 * G + gr]), b1 = to_f32<T>(vbt[tl1 * G + gr]);
-                const uint32_t x0 = pack_h2(pr[0] * s0, pr[1] * s0);  // tokens 0..7 of the block
-                const uint32_t x1 = pack_h2(pr[2] * s1, pr[3] * s1);  // tokens 8..15
-                pb[gr][0] = movmatrix_trans(x0);
-                pb[gr][1] = movmatrix_trans(x1);
-                // The MMA sees the f16-rounded p*s times (OFF + code); take OFF times exactly
-                // those rounded values back out, so the offset cancels without error.
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&x0));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&x1));
-                bsum[0][gr] += pr[0] * b0 + pr[2] * b1 - OFF * (f0.x + f1.x);
-                bsum[1][gr] += pr[1] * b0 + pr[3] * b1 - OFF * (f0.y + f1.y);
+                for (int gr = 0; gr < G; ++gr) {
+                    pb[gr][0] = movmatrix_trans(pack_h2(pr[0] * s0[gr], pr[1] * s0[gr]));  // tokens 0..7 of the block
+                    pb[gr][1] = movmatrix_trans(pack_h2(pr[2] * s1[gr], pr[3] * s1[gr]));  // tokens 8..15
+                    bsum[0][gr] = fmaf(pr[0], b0[gr], fmaf(pr[2], b1[gr], bsum[0][gr]));
+                    bsum[1][gr] = fmaf(pr[1], b0[gr], fmaf(pr[3], b1[gr], bsum[1][gr]));
+                }
             }
-            // ---- O^T += codes^T . P'^T ----
-            const uint32_t v_row = smem_u32(vct + v_tok * RB);
+            // ---- O^T += codes^T . P'^T (operands are the exact integer codes) ----
+            const uint32_t v_row = smem_u32(vct + v_off);
 #pragma unroll
             for (int cp = 0; cp < CH / 2; ++cp) {
                 uint32_t vf[4];
-                ldmatrix_x4_trans(vf, v_row + (2 * cp + v_chunk_off) * 16);
+                ldmatrix_x4_trans(vf, v_row + cp * 32);
                 constexpr int dims_per_pair = 2 * 8 * EPU;
                 const int gr = (cp * dims_per_pair) / GROUP;
+                const UnitPair<BITS> u0(vf[0]), u1(vf[1]), u2(vf[2]), u3(vf[3]);
 #pragma unroll
                 for (int i = 0; i < EPU; ++i) {
                     uint32_t a[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) a[k] = unit_f16_pair<BITS>(vf[k], i);
+                    a[0] = u0.exact(i);
+                    a[1] = u1.exact(i);
+                    a[2] = u2.exact(i);
+                    a[3] = u3.exact(i);
                     mma_f16(o_acc[cp * EPU + i], a, pb[gr][0], pb[gr][1]);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
         }
+        // a warp whose tokens were all masked reports "no maximum"
+        if (m_run[0] <= M_INIT) m_run[0] = -INFINITY;
+        if (m_run[1] <= M_INIT) m_run[1] = -INFINITY;
         if (!ok && lane == 0) atomicExch(p.status, 6);
     }
 

@@ -659,12 +659,16 @@ static void turbo_compress_raw(kvc_cache *c, cudaStream_t s) {
     c->compressed = true;
 }
 
-// TurboQuantKVCache.compressedAttention (TurboQuantKVCache.swift:1164-1446).
-static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k,
-                                       const kvc_tensor &v, float scale, int32_t mask_mode,
-                                       const kvc_tensor *mask, const kvc_tensor &out, cudaStream_t s) {
+// The cache-side half of compressedAttention: compress a raw prefix if there is one, then
+// encode the new rows and append them in the compressed domain
+// (TurboQuantKVCache.swift:1176-1200 -> compressRawCache :895, encodeNewToken :1010-1147).
+void cache_turbo_encode_new_token(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s) {
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_TURBO, "encode_new_token: not a TurboQuant cache");
+    if (c->open_round) fail(KVC_ERR_INVALID_STATE, "encode_new_token: a staged round is open on this cache");
+    require4(k, "keys");
+    require4(v, "values");
     const int D = (int)k.shape[3];
-    KVC_REQUIRE(v.shape[3] == D && q.shape[3] == D, "TurboQuant: query, key and value head dims must match");
+    KVC_REQUIRE(v.shape[3] == D, "TurboQuant: query, key and value head dims must match");
     if (!c->compressed) turbo_compress_raw(c, s);
     ensure_codecs(c, D, s);
     const int64_t S = k.shape[2], prev = c->offset;
@@ -678,6 +682,15 @@ static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const 
     turbo_ensure_compressed(c, prev + S, prev, s);
     turbo_encode_rows(c, k, v, prev, s);
     c->offset = prev + S;
+}
+
+// TurboQuantKVCache.compressedAttention (TurboQuantKVCache.swift:1164-1446).
+static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k,
+                                       const kvc_tensor &v, float scale, int32_t mask_mode,
+                                       const kvc_tensor *mask, const kvc_tensor &out, cudaStream_t s) {
+    const int D = (int)k.shape[3];
+    KVC_REQUIRE(q.shape[3] == D, "TurboQuant: query, key and value head dims must match");
+    cache_turbo_encode_new_token(c, k, v, s);
 
     const int64_t T = c->offset;
     const int L = (int)q.shape[2];

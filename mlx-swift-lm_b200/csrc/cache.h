@@ -120,6 +120,7 @@ void cache_set_meta_state(kvc_cache *c, const std::vector<std::string> &m);
 kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s);
 kvc_cache *cache_to_quantized(const kvc_cache *c, int group, int bits, cudaStream_t s);
 kvc_cache *cache_to_unquantized(const kvc_cache *c, cudaStream_t s);
+void cache_turbo_encode_new_token(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s);
 kvc_cache *cache_to_turbo(const kvc_cache *c, int kb, int vb, int kg, cudaStream_t s);
 void cache_logical_view(kvc_cache *c, int64_t tail, cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov);
 void cache_make_mask(const kvc_cache *c, int n, int64_t window, bool return_array, int32_t *mode,

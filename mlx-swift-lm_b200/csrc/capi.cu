@@ -793,6 +793,15 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev, cons
     });
 }
 
+kvc_status kvc_turbo_encode_new_token(kvc_cache *cache, const kvc_tensor *keys, const kvc_tensor *values,
+                                      void *stream) {
+    if (!cache || !keys || !values) return set_error(KVC_ERR_INVALID_ARG, "kvc_turbo_encode_new_token: null argument");
+    return guarded([&] {
+        DeviceGuard dg(cache->device);
+        kvc::cache_turbo_encode_new_token(cache, *keys, *values, as_stream(stream));
+    });
+}
+
 kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kvc_tensor *q,
                                const kvc_tensor *k, const kvc_tensor *v, float scale,
                                int32_t mask_mode, const kvc_tensor *outs, void *stream,

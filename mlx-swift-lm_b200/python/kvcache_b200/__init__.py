@@ -117,6 +117,8 @@ _lib.kvc_make_mask.argtypes = [_vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int
                                ctypes.POINTER(ctypes.c_int64), _vp, _vp]
 _lib.kvc_affine_quantize.argtypes = [_TP, ctypes.c_int32, ctypes.c_int32, _TP, _TP, _TP, _vp]
 _lib.kvc_affine_dequantize.argtypes = [_TP, _TP, _TP, ctypes.c_int32, ctypes.c_int32, _TP, _vp]
+_lib.kvc_turbo_encode_new_token.argtypes = [_vp, _TP, _TP, _vp]
+_lib.kvc_turbo_encode_new_token.restype = ctypes.c_int32
 _lib.kvc_turbo_encode.argtypes = [_TP, _vp, ctypes.POINTER(ctypes.c_float), ctypes.c_int32, _TP, _TP, _vp]
 _lib.kvc_turbo_codebook.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_float),
                                     ctypes.POINTER(ctypes.c_float)]
@@ -505,6 +507,11 @@ class TurboQuantKVCache(KVCache):
             return (ctypes.c_float * len(x))(*[float(v) for v in x])
         check(_lib.kvc_turbo_set_codec(self._h, arr(key_centroids), arr(value_centroids), arr(key_signs),
                                        arr(value_signs), dim))
+
+    def encode_new_token(self, keys, values, stream=None):
+        """Compressed-domain append of keys/values [B, H, S, D] (encodeNewToken); no attention."""
+        tk, tv = as_tensor(keys), as_tensor(values)
+        check(_lib.kvc_turbo_encode_new_token(self._h, ctypes.byref(tk), ctypes.byref(tv), _stream_ptr(stream)))
 
     def compressed_attention(self, queries, keys, values, scale, mask="none", out=None, stream=None):
         return self.attention(queries, keys, values, scale, mask, out, stream)

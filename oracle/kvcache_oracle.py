@@ -882,10 +882,11 @@ class TurboQuantKVCache(BaseKVCache):
         self.raw_values = None
         self.is_compressed = True
 
-    def compressed_attention(self, q, keys, values, scale, mask="none", precise=True):
-        """compressedAttention (:1164-1446)."""
+    def encode_new_token(self, keys, values):
+        """The cache-side half of compressedAttention (:1176-1200): compress a raw prefix if
+        there is one (compressRawCache :895), then encode and append the new rows
+        (encodeNewToken :1010-1147)."""
         D = keys.shape[-1]
-        L = q.shape[2]
         if not self.is_compressed:
             self._compress_raw()
         self._ensure_codecs(D)
@@ -893,6 +894,11 @@ class TurboQuantKVCache(BaseKVCache):
         self._encode_rows(keys, values, prev)
         self.offset = prev + keys.shape[2]
         self.is_compressed = True
+
+    def compressed_attention(self, q, keys, values, scale, mask="none", precise=True):
+        """compressedAttention (:1164-1446)."""
+        L = q.shape[2]
+        self.encode_new_token(keys, values)
         T = self.offset
         if isinstance(mask, str) and L == 1:
             mask = "none"

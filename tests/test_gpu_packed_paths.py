@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle
+from helpers import TOL, bits_equal, max_abs_diff, oracle_f32, seeded, to_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -32,7 +32,11 @@ def test_affine_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hk
         k1, v1 = seeded((B, Hkv, 1, D), 20 + step, dtype), seeded((B, Hkv, 1, D), 30 + step, dtype)
         out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), scale)
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, scale)
-        assert max_abs_diff(out, ref) <= TOL[dtype], f"step {step}"
+        # the x20 outlier channels of V make some outputs larger than 1: the tolerance is the
+        # stated one at unit scale and grows with the output magnitude (one bf16 ulp at |x| is
+        # x * 2^-8, so equal float results can still round one ulp apart)
+        biggest = float(np.abs(oracle_f32(ref)).max())
+        assert max_abs_diff(out, ref) <= TOL[dtype] * max(1.0, biggest), f"step {step}"
     assert kvc.lib().kvc_device_status() == 0
     for a, b in zip(g.state, o.state):
         assert bits_equal(a, np.ascontiguousarray(b))
@@ -64,7 +68,6 @@ def test_affine_kernel_with_large_queries_and_scales(kvc, oracle, cuda):
     k1, v1 = seeded((B, Hkv, 1, D), 4, torch.bfloat16), seeded((B, Hkv, 1, D), 5, torch.bfloat16)
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
-    from helpers import oracle_f32
     biggest = float(np.abs(oracle_f32(ref)).max())
     # outlier channels make outputs larger than 1; one bf16 ulp at |x| is x * 2^-8
     assert max_abs_diff(out, ref) <= 2e-2 * max(1.0, biggest)

@@ -110,3 +110,26 @@ def test_simple_to_turbo_conversion(kvc, cuda):
     t = s.to_turbo(4, 4)
     assert t.offset == 9 and not t.is_compressed and len(t.state) == 2
     assert torch.equal(t.state[0], s.state[0])
+
+
+@pytest.mark.parametrize("kw", [dict(bits=4), dict(bits=4, key_bits=3, value_bits=4)])
+def test_chunked_compressed_append_matches_oracle(kvc, oracle, cuda, kw):
+    """encodeNewToken without attention: chunked prefill straight into the compressed
+    representation gives the same packed state as the oracle, and decode on top agrees."""
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    dtype = torch.bfloat16
+    g = kvc.TurboQuantKVCache(reserve_tokens=700, **kw)
+    kcb = np.array(kvc.turbo_codebook(D, kw.get("key_bits", kw["bits"]))[0], dtype=np.float32)
+    vcb = np.array(kvc.turbo_codebook(D, kw.get("value_bits", kw["bits"]))[0], dtype=np.float32)
+    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    for i, n in enumerate([256, 100, 1, 243]):
+        k, v = seeded((B, Hkv, n, D), 2 * i, dtype), seeded((B, Hkv, n, D), 2 * i + 1, dtype)
+        g.encode_new_token(k.to(cuda), v.to(cuda))
+        o.encode_new_token(to_oracle(k), to_oracle(v))
+    assert g.is_compressed and g.offset == o.offset == 600
+    for a, b in zip(g.state, o.state):
+        assert tuple(a.shape) == tuple(b.shape) and bits_equal(a, np.ascontiguousarray(b))
+    q, k, v = seeded((B, Hq, 1, D), 50, dtype), seeded((B, Hkv, 1, D), 51, dtype), seeded((B, Hkv, 1, D), 52, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5)
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
