@@ -76,7 +76,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     static_assert(CONSUMER_WARPS * 16 * RED_STRIDE * 4 + 512 + 16 * 64 * 4 <= NSTAGE * 2 * TILE_BYTES, "merge buffers must fit");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // pointer + offset (no integer round trip) so that loads through it stay ld.shared
+    unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t *full = (uint64_t *)(stages + (size_t)NSTAGE * 2 * TILE_BYTES);
     uint64_t *empty = full + NSTAGE;
     int *is_last = (int *)(empty + NSTAGE);

@@ -136,7 +136,8 @@ attn_affine_kernel(const AffineParams p) {
     static_assert(STAGE_BYTES % 16 == 0 && SC_TILE % 16 == 0, "bulk copies need 16-byte multiples");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    // pointer + offset (no integer round trip) so that loads through it stay ld.shared
+    unsigned char *stages = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     constexpr int RING = NSTAGE * STAGE_BYTES;
     constexpr int RED_BYTES = PK_WARPS * 16 * RED_STRIDE * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
     constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
@@ -448,7 +449,7 @@ attn_affine_kernel(const AffineParams p) {
 // with one new token): the MMAs are transposed so that tokens (for Q.K^T) and
 // head dims (for P.V) fill the 16-row M side and the query rows the 8-column N
 // side. Compared with the kernel above this halves the MMA count and the
-// accumulator registers (three CTAs per SM instead of two), which is what the
+// accumulator registers (three or four CTAs per SM instead of two), which is what the
 // latency-bound conversion chain needs.
 //   S^T[16 tok x 8 rows]  = K[16 tok x 16 d] . Q^T[16 d x 8 rows]      (A = codes)
 //   O^T[16 d  x 8 rows]  += V^T[16 d x 16 tok] . P'^T[16 tok x 8 rows]  (A = codes via ldmatrix.trans)
@@ -459,13 +460,9 @@ attn_affine_kernel(const AffineParams p) {
 // pipe, so every step is written for instruction count:
 //   * codes become f16 operands with one mask-or per operand register and one
 //     shift per word (CodeWord / UnitPair below);
-//   * on the K side the operands keep their exponent offset and the 1/16 factor of
-//     the low nibbles: the query fragments carry the factor 16 for those k-slots
-//     and the offset leaves as OFF * sum(q') after the MMA (a per-row constant);
-//     the accumulators restart every tile, so the cancellation costs ~1e-4 of a
-//     logit at most;
-//   * on the V side the accumulators run over the whole split, so the operands are
-//     made exact integer codes with one half2 FMA each (the FMA pipe has room);
+//   * the masked bits are used as they are, as f16 SUBNORMALS (n * 2^-24 or n * 2^-20):
+//     exact, no offset to cancel and no second instruction; the power of two is folded
+//     into the query fragments / the exponential (K side) and the epilogue (V side);
 //   * the query is pre-multiplied by scale * log2(e), scores come out of the MMA in
 //     the exp2 domain;
 //   * the running maximum is lazy: a tile only takes the shuffle-reduce / rescale
@@ -498,6 +495,17 @@ struct CodeWord {
         }
         return __byte_perm(w, 0x64646464u, k ? 0x4342 : 0x4140);
     }
+    // pair k as f16 SUBNORMALS: the masked bits alone are n * 2^-24 (nibbles at bits 0..3 of a
+    // half, bytes) or n * 2^-20 (nibbles at bits 4..7): exact, no offset, one instruction.
+    // The tensor core takes subnormal f16 inputs at full precision; the power-of-two factor
+    // is constant per k-slot (K side) or per output tile (V side) and is applied elsewhere.
+    __device__ __forceinline__ uint32_t sub(int k) const {
+        if (BITS == 4) {
+            const uint32_t x = (k & 2) ? w8 : w;
+            return (k & 1) ? (x & 0x00F000F0u) : (x & 0x000F000Fu);
+        }
+        return __byte_perm(w, 0u, k ? 0x4342 : 0x4140);
+    }
     // pair k as exact integer codes in f16
     __device__ __forceinline__ uint32_t exact(int k) const {
         const uint32_t x = raw(k);
@@ -519,6 +527,15 @@ template <int BITS>
 struct UnitPair {
     uint32_t v, v8;
     __device__ __forceinline__ explicit UnitPair(uint32_t reg) : v(reg), v8(BITS == 4 ? (reg >> 8) : 0u) {}
+    // element i of both units as f16 subnormals (see CodeWord::sub): n * 2^-24, or n * 2^-20
+    // for the odd elements of 4-bit units
+    __device__ __forceinline__ uint32_t sub(int i) const {
+        if (BITS == 4) {
+            const uint32_t src = (i & 2) ? v8 : v;
+            return (i & 1) ? (src & 0x00F000F0u) : (src & 0x000F000Fu);
+        }
+        return __byte_perm(v, 0u, i ? 0x4341 : 0x4240);
+    }
     __device__ __forceinline__ uint32_t exact(int i) const {
         uint32_t x, r;
         if (BITS == 4) {
@@ -584,8 +601,8 @@ __device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&dst)[
     }
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE>
-__global__ void __launch_bounds__(PK_THREADS, 3)
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB>
+__global__ void __launch_bounds__(PK_THREADS, MINB)
 attn_affine_decode8_kernel(const AffineParams p) {
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
@@ -608,7 +625,8 @@ attn_affine_decode8_kernel(const AffineParams p) {
     static_assert(STAGE_BYTES % 16 == 0 && SC_TILE % 16 == 0, "bulk copies need 16-byte multiples");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char *stages = (unsigned char *)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    // pointer + offset (no integer round trip) so that loads through it stay ld.shared
+    unsigned char *stages = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     constexpr int RING = NSTAGE * STAGE_BYTES;
     constexpr int RED_BYTES = PK_WARPS * 16 * RED_STRIDE * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
     constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
@@ -674,16 +692,15 @@ attn_affine_decode8_kernel(const AffineParams p) {
         }
     } else {
         // Q^T fragments: B operand column = query row g; k-slots follow the code words.
-        // q' = f16(q * scale * log2 e); the k-slots fed by low nibbles carry 16 q'.
-        // K_EXACT: the K operands are made exact integer codes like the V operands (one half2
-        // FMA each); otherwise they keep offset and nibble factor and the query carries them.
-        constexpr bool K_EXACT = true;
-        constexpr float LOWMUL = K_EXACT ? 1.f : ((BITS == 4) ? 16.f : 1.f);
-        constexpr float OFFK = K_EXACT ? 0.f : ((BITS == 4) ? 64.f : 1024.f);
+        // q' = f16(q * scale * log2 e). The code operands are f16 subnormals n * 2^-24 (or
+        // n * 2^-20 for the nibbles at bits 4..7): the k-slots fed by the smaller form carry
+        // 16 q', so every product is n q' 2^-20 (4-bit) or n q' 2^-24 (8-bit) = n q' / KSCALE.
+        constexpr float LOWMUL = (BITS == 4) ? 16.f : 1.f;
+        constexpr float KSCALE = (BITS == 4) ? 1048576.f : 16777216.f;
         uint32_t qb[G][MPG][2];
-        float qsum_own[G], qoff_own[G];
+        float qsum_own[G];
 #pragma unroll
-        for (int gr = 0; gr < G; ++gr) qsum_own[gr] = qoff_own[gr] = 0.f;
+        for (int gr = 0; gr < G; ++gr) qsum_own[gr] = 0.f;
 #pragma unroll
         for (int gr = 0; gr < G; ++gr) {
 #pragma unroll
@@ -698,25 +715,22 @@ attn_affine_decode8_kernel(const AffineParams p) {
                     for (int k = 0; k < 4; ++k)
                         x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]]) * p.scale_log2));
                 }
-                qb[gr][m][0] = pack_h2(x[0] * LOWMUL, x[1] * LOWMUL);   // k-slots 2c, 2c+1: low pairs
-                qb[gr][m][1] = pack_h2(x[2], x[3]);                     // k-slots 2c+8, 2c+9: high pairs
+                qb[gr][m][0] = pack_h2(x[0] * LOWMUL, x[1] * LOWMUL);   // k-slots 2c, 2c+1
+                qb[gr][m][1] = pack_h2(x[2], x[3]);                     // k-slots 2c+8, 2c+9
                 qsum_own[gr] += x[0] + x[1] + x[2] + x[3];
-                qoff_own[gr] += LOWMUL * (x[0] + x[1]) + x[2] + x[3];
             }
         }
-        float qsum[2][G];    // sum(q') of rows 2c, 2c+1 (multiplies the bias)
-        float negoff[2][G];  // -OFF * sum of the operand-side q' (takes the exponent offset back out)
+        // sum(q') / KSCALE of rows 2c, 2c+1: multiplies the bias; scores stay in units of
+        // 1 / KSCALE until the exponential.
+        float qsum[2][G];
 #pragma unroll
         for (int gr = 0; gr < G; ++gr) {
-            float v = qsum_own[gr], w = qoff_own[gr];
+            float v = qsum_own[gr];
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
-            w += __shfl_xor_sync(0xffffffffu, w, 1);
-            w += __shfl_xor_sync(0xffffffffu, w, 2);
+            v *= (1.f / KSCALE);
             qsum[0][gr] = __shfl_sync(0xffffffffu, v, (2 * c) * 4);
             qsum[1][gr] = __shfl_sync(0xffffffffu, v, (2 * c + 1) * 4);
-            negoff[0][gr] = -OFFK * __shfl_sync(0xffffffffu, w, (2 * c) * 4);
-            negoff[1][gr] = -OFFK * __shfl_sync(0xffffffffu, w, (2 * c + 1) * 4);
         }
         // Last visible token per row. Rows past R hold zero queries and are never written
         // out; they take the limit of a real row so that they do not force the mask path.
@@ -731,7 +745,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
         const int min_limit = p.causal ? (int)min((int64_t)t_last, p.causal_offset) : t_last;
         constexpr float M_INIT = -1e30f, LAZY = 8.f;
         m_run[0] = m_run[1] = M_INIT;
-        float m_thr[2] = {M_INIT, M_INIT};  // m_run + LAZY once a maximum exists
+        float m_thr[2] = {M_INIT, M_INIT};  // (m_run + LAZY) / KSCALE once a maximum exists
 
         const int blk = warp;
         // ldmatrix rows: matrix mi = lane / 8 -> tokens (mi >> 1) * 8 + lane % 8, chunk parity mi & 1
@@ -741,11 +755,12 @@ attn_affine_decode8_kernel(const AffineParams p) {
         const uint32_t k_off0 = tl0 * RB + c * WPL * 4, k_off1 = tl1 * RB + c * WPL * 4;
         const uint32_t v_off = v_tok * RB + v_chunk_off * 16;
 
-        for (int it = 0; it < ntiles && ok; ++it) {
-            const int s = it % NSTAGE;
-            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+        int s = 0;
+        uint32_t phase = 0;
+        for (int it = 0; it < ntiles && ok; ++it, s = (s + 1 == NSTAGE) ? 0 : s + 1, phase ^= (s == 0)) {
+            ok = mbar_wait(&full[s], phase);
             if (!ok) break;
-            if (p.debug_skip) {
+            if (p.debug_skip & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -758,8 +773,46 @@ attn_affine_decode8_kernel(const AffineParams p) {
             const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
             const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
             const int t_blk = (tile_begin + it) * PK_TILE + blk * 16;
+            if (p.debug_skip & 6) {
+                // measurement aid (results are meaningless): 2 = only the K half, 4 = only the V half
+                if (p.debug_skip & 2) {
+#pragma unroll
+                    for (int gr = 0; gr < G; ++gr) {
+                        uint32_t wa[WPL], wb[WPL];
+                        load_words<WPL>((const uint32_t *)(kct + k_off0) + gr * WPG, wa);
+                        load_words<WPL>((const uint32_t *)(kct + k_off1) + gr * WPG, wb);
+#pragma unroll
+                        for (int wi = 0; wi < WPL; ++wi) {
+                            const CodeWord<BITS> ca(wa[wi]), cb(wb[wi]);
+#pragma unroll
+                            for (int which = 0; which < MPW; ++which) {
+                                uint32_t a[4] = {ca.exact(2 * which), cb.exact(2 * which), ca.exact(2 * which + 1),
+                                                 cb.exact(2 * which + 1)};
+                                mma_f16(o_acc[gr], a, qb[gr][wi * MPW + which][0], qb[gr][wi * MPW + which][1]);
+                            }
+                        }
+                    }
+                }
+                if (p.debug_skip & 4) {
+                    const uint32_t v_row = smem_u32(vct + v_off);
+#pragma unroll
+                    for (int cp = 0; cp < CH / 2; ++cp) {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, v_row + cp * 32);
+                        const UnitPair<BITS> u0(vf[0]), u1(vf[1]), u2(vf[2]), u3(vf[3]);
+#pragma unroll
+                        for (int i = 0; i < EPU; ++i) {
+                            uint32_t a[4] = {u0.exact(i), u1.exact(i), u2.exact(i), u3.exact(i)};
+                            mma_f16(o_acc[cp * EPU + i], a, qb[0][0][0], qb[0][0][1]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                continue;
+            }
 
-            // ---- S^T = codes . Q'^T per group (operands keep offset and nibble factor) ----
+            // ---- S^T = codes . Q'^T per group ----
             float acc[G][4];
 #pragma unroll
             for (int gr = 0; gr < G; ++gr) {
@@ -773,22 +826,15 @@ attn_affine_decode8_kernel(const AffineParams p) {
 #pragma unroll
                     for (int which = 0; which < MPW; ++which) {
                         uint32_t a[4];
-                        if (K_EXACT) {
-                            a[0] = ca.exact(2 * which);       // token g,   k-slots 2c, 2c+1
-                            a[1] = cb.exact(2 * which);       // token g+8
-                            a[2] = ca.exact(2 * which + 1);   // token g,   k-slots 2c+8, 2c+9
-                            a[3] = cb.exact(2 * which + 1);   // token g+8
-                        } else {
-                            a[0] = ca.raw(2 * which);
-                            a[1] = cb.raw(2 * which);
-                            a[2] = ca.raw(2 * which + 1);
-                            a[3] = cb.raw(2 * which + 1);
-                        }
+                        a[0] = ca.sub(2 * which);       // token g,   k-slots 2c, 2c+1
+                        a[1] = cb.sub(2 * which);       // token g+8
+                        a[2] = ca.sub(2 * which + 1);   // token g,   k-slots 2c+8, 2c+9
+                        a[3] = cb.sub(2 * which + 1);   // token g+8
                         mma_f16(acc[gr], a, qb[gr][wi * MPW + which][0], qb[gr][wi * MPW + which][1]);
                     }
                 }
             }
-            // ---- scores (already in the exp2 domain): s * (acc - OFF qoff) + b * sum(q') ----
+            // ---- scores in the exp2 domain, in units of 1 / KSCALE: s * acc + b * sum(q') / KSCALE ----
             float sc[4] = {0.f, 0.f, 0.f, 0.f};
             {
                 float s0[G], s1[G], b0[G], b1[G];
@@ -798,11 +844,10 @@ attn_affine_decode8_kernel(const AffineParams p) {
                 load_groups<T, G>(kbt, tl1, b1);
 #pragma unroll
                 for (int gr = 0; gr < G; ++gr) {
-                    const float n0 = K_EXACT ? 0.f : negoff[0][gr], n1 = K_EXACT ? 0.f : negoff[1][gr];
-                    sc[0] = fmaf(s0[gr], acc[gr][0] + n0, fmaf(b0[gr], qsum[0][gr], sc[0]));
-                    sc[1] = fmaf(s0[gr], acc[gr][1] + n1, fmaf(b0[gr], qsum[1][gr], sc[1]));
-                    sc[2] = fmaf(s1[gr], acc[gr][2] + n0, fmaf(b1[gr], qsum[0][gr], sc[2]));
-                    sc[3] = fmaf(s1[gr], acc[gr][3] + n1, fmaf(b1[gr], qsum[1][gr], sc[3]));
+                    sc[0] = fmaf(s0[gr], acc[gr][0], fmaf(b0[gr], qsum[0][gr], sc[0]));
+                    sc[1] = fmaf(s0[gr], acc[gr][1], fmaf(b0[gr], qsum[1][gr], sc[1]));
+                    sc[2] = fmaf(s1[gr], acc[gr][2], fmaf(b1[gr], qsum[0][gr], sc[2]));
+                    sc[3] = fmaf(s1[gr], acc[gr][3], fmaf(b1[gr], qsum[1][gr], sc[3]));
                 }
             }
             if (t_blk + 15 > min_limit) {  // warp-uniform: only tiles that cross a limit
@@ -822,10 +867,10 @@ attn_affine_decode8_kernel(const AffineParams p) {
                         mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 4));
                         mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 8));
                         mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], 16));
-                        const float m_new = fmaxf(m_run[k], mx[k]);
+                        const float m_new = fmaxf(m_run[k], mx[k] * KSCALE);
                         alpha[k] = fast_exp2(m_run[k] - m_new);
                         m_run[k] = m_new;
-                        m_thr[k] = (m_new > M_INIT) ? m_new + LAZY : M_INIT;
+                        m_thr[k] = (m_new > M_INIT) ? (m_new + LAZY) * (1.f / KSCALE) : M_INIT;
                         l_run[k] *= alpha[k];
                     }
 #pragma unroll
@@ -844,7 +889,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
             }
             float pr[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) pr[e] = fast_exp2(sc[e] - m_run[e & 1]);
+            for (int e = 0; e < 4; ++e) pr[e] = fast_exp2(fmaf(sc[e], KSCALE, -m_run[e & 1]));
             l_run[0] += pr[0] + pr[2];
             l_run[1] += pr[1] + pr[3];
             // ---- P'^T = (p * s_v)^T per group, moved to the B-fragment layout ----
@@ -863,7 +908,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
                     bsum[1][gr] = fmaf(pr[1], b0[gr], fmaf(pr[3], b1[gr], bsum[1][gr]));
                 }
             }
-            // ---- O^T += codes^T . P'^T (operands are the exact integer codes) ----
+            // ---- O^T += codes^T . P'^T (subnormal operands; the 2^24 / 2^20 leaves in the epilogue) ----
             const uint32_t v_row = smem_u32(vct + v_off);
 #pragma unroll
             for (int cp = 0; cp < CH / 2; ++cp) {
@@ -875,10 +920,10 @@ attn_affine_decode8_kernel(const AffineParams p) {
 #pragma unroll
                 for (int i = 0; i < EPU; ++i) {
                     uint32_t a[4];
-                    a[0] = u0.exact(i);
-                    a[1] = u1.exact(i);
-                    a[2] = u2.exact(i);
-                    a[3] = u3.exact(i);
+                    a[0] = u0.sub(i);
+                    a[1] = u1.sub(i);
+                    a[2] = u2.sub(i);
+                    a[3] = u3.sub(i);
                     mma_f16(o_acc[cp * EPU + i], a, pb[gr][0], pb[gr][1]);
                 }
             }
@@ -914,10 +959,11 @@ attn_affine_decode8_kernel(const AffineParams p) {
             const int cp = mt / EPU, i = mt % EPU;
             const int d0 = (2 * cp) * 8 * EPU + EPU * g + i, d1 = d0 + 8 * EPU;
             const int gr = d0 / GROUP;
-            wo[(2 * c) * RED_STRIDE + d0] = o_acc[mt][0] + bsum[0][gr];
-            wo[(2 * c + 1) * RED_STRIDE + d0] = o_acc[mt][1] + bsum[1][gr];
-            wo[(2 * c) * RED_STRIDE + d1] = o_acc[mt][2] + bsum[0][gr];
-            wo[(2 * c + 1) * RED_STRIDE + d1] = o_acc[mt][3] + bsum[1][gr];
+            const float vs = (BITS == 4 && (i & 1)) ? 1048576.f : 16777216.f;  // undo the subnormal factor
+            wo[(2 * c) * RED_STRIDE + d0] = fmaf(o_acc[mt][0], vs, bsum[0][gr]);
+            wo[(2 * c + 1) * RED_STRIDE + d0] = fmaf(o_acc[mt][1], vs, bsum[1][gr]);
+            wo[(2 * c) * RED_STRIDE + d1] = fmaf(o_acc[mt][2], vs, bsum[0][gr]);
+            wo[(2 * c + 1) * RED_STRIDE + d1] = fmaf(o_acc[mt][3], vs, bsum[1][gr]);
         }
         if (g == 0) {
             red_ml[(warp * 16 + 2 * c) * 2 + 0] = m_run[0];
@@ -976,7 +1022,7 @@ void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) 
     ++g_launch_count;
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE>
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB>
 void launch_affine8_typed(const AffineParams &p, int units, cudaStream_t stream) {
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
@@ -987,14 +1033,14 @@ void launch_affine8_typed(const AffineParams &p, int units, cudaStream_t stream)
     static bool configured[64] = {false};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, 100));
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE><<<units, PK_THREADS, smem, stream>>>(p);
+    attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB><<<units, PK_THREADS, smem, stream>>>(p);
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -1037,12 +1083,16 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     int *counters = counters_get(a.device, stream, PK_COUNTER_BYTES);
 
     const int64_t tiles = (a.T + PK_TILE - 1) / PK_TILE;
-    // at most 8 query rows and chunk pairs inside one group: transposed decode kernel, 3 CTAs per SM
+    // at most 8 query rows and chunk pairs inside one group: transposed decode kernel, 3 or 4 CTAs per SM
     const bool decode8 = rep * a.L <= 8 && (2 * 8 * (16 / a.k.bits)) <= a.k.group;
+    // resident CTAs per SM (a fourth CTA fits the 4-bit kernels at 94 registers but measured slower)
     const int slots = sm_count(a.device) * (decode8 ? 3 : 2);
     int64_t best_s = 1;
     double best_cost = 1e30;
     const int64_t max_s = std::min<int64_t>(tiles, 64);
+    // One wave of resident CTAs measures best (cfg4 shape: 384 CTAs on 444 slots, 90 us, against
+    // 97-102 us for 4..10 splits): a second wave pays the prologue / merge again and runs
+    // against a half-empty machine at its end.
     for (int64_t s = 1; s <= max_s; ++s) {
         const int64_t units = bh * s;
         const int64_t waves = (units + slots - 1) / slots;
@@ -1052,6 +1102,10 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
             best_cost = cost;
             best_s = s;
         }
+    }
+    if (const char *e = std::getenv("KVC_AFFINE_SPLITS")) {  // measurement aid
+        const int64_t forced = std::atoll(e);
+        if (forced >= 1 && forced <= max_s) best_s = forced;
     }
     const int64_t splits = best_s;
     const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
@@ -1077,7 +1131,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
     {
         const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-        p.debug_skip = (e && e[0] == '1') ? 1 : 0;
+        p.debug_skip = e ? std::atoi(e) : 0;
     }
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
@@ -1086,7 +1140,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     const int bits = a.k.bits, group = a.k.group;
 #define KVC_AFF8(TT, DD, BB, GG, NS)                                         \
     if (a.D == DD && bits == BB && group == GG) {                            \
-        launch_affine8_typed<TT, DD, BB, GG, NS>(p, units, stream);          \
+        launch_affine8_typed<TT, DD, BB, GG, NS, 3>(p, units, stream);         \
         return 1;                                                            \
     }
     if (decode8) {
