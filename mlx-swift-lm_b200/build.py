@@ -26,6 +26,7 @@ SOURCES = [
     "attn_general.cu",
     "attn_decode.cu",
     "attn_packed.cu",
+    "attn_turbo.cu",
     "attn_dispatch.cu",
     "cache.cu",
     "round.cu",

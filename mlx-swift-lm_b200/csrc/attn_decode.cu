@@ -354,23 +354,6 @@ bool source_fits(const KVSource &s, int D, int Hkv, int B) {
     return true;
 }
 
-int *status_word(int device) {
-    static int *words[64] = {nullptr};
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    if (device < 0 || device >= 64) return nullptr;
-    if (!words[device]) {
-        int *p = nullptr;
-        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return nullptr;
-        }
-        (void)cudaMemset(p, 0, sizeof(int));
-        words[device] = p;
-    }
-    return words[device];
-}
-
 template <typename T, int D, int NSTAGE>
 void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const DecodeParams &p, int units,
                   cudaStream_t stream) {
@@ -393,17 +376,6 @@ void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const Decode
 
 }  // namespace
 
-int decode_status(int device) {
-    int *w = status_word(device);
-    if (!w) return 0;
-    int v = 0;
-    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return -1;
-    }
-    return v;
-}
-
 // Returns the number of kernels launched, or 0 when the call does not fit this path.
 int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
@@ -421,7 +393,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
 
     CUtensorMap kmap, vmap;
     if (!make_map(&kmap, a.k, a.D, a.T, a.Hkv, a.B) || !make_map(&vmap, a.v, a.D, a.T, a.Hkv, a.B)) return 0;
-    int *status = status_word(a.device);
+    int *status = device_status_word(a.device);
     int *counters = counters_get(a.device, stream, COUNTER_BYTES);
     if (!status || !counters) return 0;
 

@@ -9,6 +9,7 @@ namespace kvc {
 int launch_attention_general(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_affine(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
@@ -24,6 +25,8 @@ int launch_attention(const AttnArgs &a, cudaStream_t stream) {
         int n = launch_attention_decode(a, stream);
         if (n > 0) return n;
         n = launch_attention_affine(a, stream);
+        if (n > 0) return n;
+        n = launch_attention_turbo(a, stream);
         if (n > 0) return n;
     }
     return launch_attention_general(a, stream);

@@ -60,26 +60,10 @@ struct AffineParams {
     float scale_log2;
 };
 
-template <typename T> __device__ __forceinline__ float to_f32(T v);
-template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
 __device__ __forceinline__ uint32_t hsub2_1024(uint32_t x) {
     uint32_t r;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0x64006400u));
     return r;
-}
-
-__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // Operand pair (b0, b1) number `which` of a packed code word, as f16 pairs minus nothing
@@ -470,12 +454,6 @@ attn_affine_kernel(const AffineParams p) {
 //     otherwise probabilities are exp2(score - stale max) <= 256, well inside f16;
 //   * the causal / length mask is only evaluated on the tiles that cross a limit.
 // ---------------------------------------------------------------------
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-    uint32_t r;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
-    return r;
-}
-
 // ---- code words -> f16 operand pairs without per-element shifts ----
 // 4-bit: a word holds nibbles n0..n7. Masking a nibble in place under the exponent of
 // 64.0 (0x5400, ulp 1/16) gives  64 + n/16  for the nibbles at bits 0..3 of a half
@@ -619,7 +597,6 @@ attn_affine_decode8_kernel(const AffineParams p) {
     constexpr int CH = RB / 16;
     constexpr int MT_O = D / 16;                  // output m-tiles (16 head dims each)
     constexpr int RED_STRIDE = D + 8;
-    constexpr float OFF = (BITS == 4) ? 16.f : 1024.f;
     static_assert(WPL >= 1 && G >= 1 && G <= 4, "unsupported group layout");
     static_assert((2 * 8 * EPU) <= GROUP, "a pair of 16-byte chunks must stay inside one group");
     static_assert(STAGE_BYTES % 16 == 0 && SC_TILE % 16 == 0, "bulk copies need 16-byte multiples");
@@ -983,21 +960,6 @@ attn_affine_decode8_kernel(const AffineParams p) {
     unit_epilogue<D, PK_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
 }
 
-int *packed_status_word(int device) {
-    static int *words[64] = {nullptr};
-    if (device < 0 || device >= 64) return nullptr;
-    if (!words[device]) {
-        int *w = nullptr;
-        if (cudaMalloc(&w, sizeof(int)) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return nullptr;
-        }
-        (void)cudaMemset(w, 0, sizeof(int));
-        words[device] = w;
-    }
-    return words[device];
-}
-
 template <typename T, int D, int BITS, int GROUP, int NSTAGE>
 void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) {
     constexpr int G = D / GROUP;
@@ -1078,7 +1040,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (((uintptr_t)a.q & 1)) return 0;
     const int64_t bh = (int64_t)a.B * a.Hkv;
     if (bh * (int64_t)sizeof(int) > PK_COUNTER_BYTES) return 0;
-    int *status = packed_status_word(a.device);
+    int *status = device_status_word(a.device);
     if (!status) return 0;
     int *counters = counters_get(a.device, stream, PK_COUNTER_BYTES);
 

@@ -16,7 +16,6 @@ void round_update(kvc_round *r, const kvc_tensor &k, const kvc_tensor &v, cudaSt
                   kvc_tensor *ok, kvc_tensor *ov);
 void round_commit(kvc_round *r, int retain, cudaStream_t s);
 int64_t rewind_last_round(kvc_cache *c, int64_t count, cudaStream_t s);
-int decode_status(int device);
 }  // namespace kvc
 
 namespace {
@@ -826,7 +825,7 @@ int32_t kvc_device_status(void) {
         (void)cudaGetLastError();
         return -1;
     }
-    return kvc::decode_status(dev);
+    return kvc::device_status(dev);
 }
 
 void kvc_timing_enable(int32_t on) { kvc::timing_set(on != 0); }

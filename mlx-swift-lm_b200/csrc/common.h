@@ -68,6 +68,8 @@ void *scratch_get(int device, size_t bytes, cudaStream_t stream);
 int *counters_get(int device, cudaStream_t stream, size_t bytes);
 int current_device();
 int sm_count(int device);
+int *device_status_word(int device);  // shared by all kernels with bounded waits
+int device_status(int device);        // reads it (0 = no wait ever ran out)
 
 // ---------------------------------------------------------------------
 // kernel launch descriptors

@@ -189,4 +189,34 @@ void timing_read(double *total_ms, int64_t *launches, bool reset) {
         g_timing.launches = 0;
     }
 }
+// One status word per device, shared by every kernel with bounded waits: a kernel whose
+// wait ran out stores a non-zero code here and returns; kvc_device_status reads it.
+int *device_status_word(int device) {
+    static int *words[64] = {nullptr};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) return nullptr;
+    if (!words[device]) {
+        int *p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        (void)cudaMemset(p, 0, sizeof(int));
+        words[device] = p;
+    }
+    return words[device];
+}
+
+int device_status(int device) {
+    int *w = device_status_word(device);
+    if (!w) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    return v;
+}
+
 }  // namespace kvc

@@ -71,3 +71,53 @@ def test_affine_kernel_with_large_queries_and_scales(kvc, oracle, cuda):
     biggest = float(np.abs(oracle_f32(ref)).max())
     # outlier channels make outputs larger than 1; one bf16 ulp at |x| is x * 2^-8
     assert max_abs_diff(out, ref) <= 2e-2 * max(1.0, biggest)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,P,kb,vb", [
+    (1, 64, 8, 3000, 3, 4),     # Llama-3-70B head layout, 3-bit keys / 4-bit values
+    (2, 8, 2, 700, 4, 4),
+    (2, 8, 2, 130, 4, 2),
+    (1, 16, 4, 257, 3, 3),
+    (2, 4, 4, 64, 2, 2),
+])
+def test_turbo_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, P, kb, vb):
+    """The lookup-table tensor-core decode kernel over packed TurboQuant rows (D = 128)."""
+    D = 128
+    kw = dict(bits=max(kb, vb), key_bits=kb, value_bits=vb)
+    g = kvc.TurboQuantKVCache(**kw)
+    kcb = np.array(kvc.turbo_codebook(D, kb)[0], dtype=np.float32)
+    vcb = np.array(kvc.turbo_codebook(D, vb)[0], dtype=np.float32)
+    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    scale = D ** -0.5
+    n0 = kvc.launch_count(reset=True)
+    for step in range(3):
+        q = seeded((B, Hq, 1, D), 10 + step, dtype)
+        k1, v1 = seeded((B, Hkv, 1, D), 20 + step, dtype), seeded((B, Hkv, 1, D), 30 + step, dtype)
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, scale)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"step {step}"
+    # one encode launch and ONE attention launch per step: the merge is folded into the kernel
+    assert kvc.launch_count(reset=True) <= 6
+    assert kvc.lib().kvc_device_status() == 0
+    for a, b in zip(g.state, o.state):
+        assert bits_equal(a, np.ascontiguousarray(b))
+
+
+def test_turbo_kernel_small_causal_chunk(kvc, oracle, cuda):
+    B, Hq, Hkv, D, L = 2, 4, 2, 128, 4     # 2 query heads per KV head x 4 positions = 8 rows
+    kw = dict(bits=4, key_bits=3, value_bits=4)
+    g = kvc.TurboQuantKVCache(**kw)
+    o = oracle.TurboQuantKVCache(key_codebook=np.array(kvc.turbo_codebook(D, 3)[0], dtype=np.float32),
+                                 value_codebook=np.array(kvc.turbo_codebook(D, 4)[0], dtype=np.float32), **kw)
+    k, v = seeded((B, Hkv, 500, D), 1, torch.bfloat16), seeded((B, Hkv, 500, D), 2, torch.bfloat16)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, torch.bfloat16)
+    k1, v1 = seeded((B, Hkv, L, D), 4, torch.bfloat16), seeded((B, Hkv, L, D), 5, torch.bfloat16)
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), 0.09, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, 0.09, "causal")
+    assert max_abs_diff(out, ref) <= 2e-2
