@@ -52,6 +52,7 @@ WORKLOADS = {
 # (per-layer working set 269 MB > L2, 0.6 GB on the device).
 WORKLOADS["cfg2_profile_2layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=2)
 WORKLOADS["cfg4_profile_2layers"] = dict(WORKLOADS["cfg4_quant4_bf16_qwen2_7b"], layers=2)
+WORKLOADS["cfg5_profile_2layers"] = dict(WORKLOADS["cfg5_turbo_k3v4_llama3_70b"], layers=2)
 DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
 
 
