@@ -59,6 +59,8 @@ struct DecodeParams {
     int32_t causal;
     int32_t out_dtype;
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
+    int32_t row_blocks;  // chunk kernel: 64-row blocks per (batch, head)
+    int32_t tiles_all;   // chunk kernel: tiles covering all T tokens
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
 };
@@ -309,6 +311,307 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
 }
 
 // ---------------------------------------------------------------------
+// Multi-token chunks (prefill chunks, speculative verify rounds): more than 16 query
+// rows per KV head. Same ring, tiles and fragment layouts as above, but the consumer
+// warps split the QUERY ROWS instead of the tokens: a CTA owns a block of 64 rows of one
+// (batch, KV head) group (row r <-> head r / L of the group, position r % L), warp w owns
+// rows 16w .. 16w+15 with their own softmax state and output accumulators, and every
+// warp walks all four 16-token blocks of each tile. Under a causal mask a CTA only
+// streams the tiles some row of its block can see. With one split per block the rows are
+// normalised and written straight to the output; otherwise partials go to scratch and the
+// last CTA of the block merges them.
+// ---------------------------------------------------------------------
+template <typename T, int D, int NSTAGE>
+__global__ void __launch_bounds__(DEC_THREADS, (D <= 128 ? 2 : 1))
+attn_chunk_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const DecodeParams p) {
+    constexpr int TILE_BYTES = TILE_T * D * 2;
+    constexpr int BOXES = D / 64;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NT_O = D / 8;
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t *full = (uint64_t *)(stages + (size_t)NSTAGE * 2 * TILE_BYTES);
+    uint64_t *empty = full + NSTAGE;
+    int *is_last = (int *)(empty + NSTAGE);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % p.splits;
+    const int unit = blockIdx.x / p.splits;
+    const int rb = unit % p.row_blocks;
+    const int bh = unit / p.row_blocks;
+    const int hk = bh % p.Hkv, b = bh / p.Hkv;
+    const int rep = p.Hq / p.Hkv;
+    const int R = rep * p.L;
+    const int r_lo = rb * 64, r_hi = min(R, r_lo + 64) - 1;
+
+    // tiles some row of the block can see, then this split's share of them
+    int tiles_needed = p.tiles_all;
+    if (p.causal) {
+        const int max_l = (r_lo / p.L == r_hi / p.L) ? (r_hi % p.L) : (p.L - 1);
+        const int64_t lim = min(p.T - 1, p.causal_offset + max_l);
+        tiles_needed = (int)min((int64_t)p.tiles_all, lim / TILE_T + 1);
+    }
+    const int t_base = tiles_needed / p.splits, t_rem = tiles_needed % p.splits;
+    const int tile_begin = split * t_base + min(split, t_rem);
+    const int ntiles = t_base + (split < t_rem ? 1 : 0);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    bool ok = true;
+    const int g = lane >> 2, c = lane & 3;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o_acc[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+    if (warp == CONSUMER_WARPS) {
+        if (lane == 0) {
+            for (int it = 0; it < ntiles && ok; ++it) {
+                const int s = it % NSTAGE;
+                if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                if (!ok) break;
+                unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
+                unsigned char *vt = kt + TILE_BYTES;
+                mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+                const int t0 = (tile_begin + it) * TILE_T;
+#pragma unroll
+                for (int bx = 0; bx < BOXES; ++bx) {
+                    tma_load_4d(kt + bx * BOX_BYTES, &kmap, &full[s], bx * 64, t0, hk, b);
+                    tma_load_4d(vt + bx * BOX_BYTES, &vmap, &full[s], bx * 64, t0, hk, b);
+                }
+            }
+            if (!ok) atomicExch(p.status, 3);
+        }
+    } else {
+        const int r_warp = r_lo + 16 * warp;
+        uint32_t qa[KSTEPS][4];
+        int row_limit[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = r_warp + g + 8 * half;
+            const int l = r % p.L;
+            row_limit[half] = (r < R) ? (int)(p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+        }
+        // the warp's widest and narrowest limits (rows past R excluded from the narrowest)
+        int lim_max = max(row_limit[0], row_limit[1]);
+        int lim_min = min(row_limit[0] < 0 ? 0x7fffffff : row_limit[0], row_limit[1] < 0 ? 0x7fffffff : row_limit[1]);
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+            lim_max = max(lim_max, __shfl_xor_sync(0xffffffffu, lim_max, o));
+            lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, o));
+        }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
+            const int d0 = bx * 64 + (2 * c + ps) * 8 + 4 * h;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = r_warp + g + 8 * half;
+                uint32_t w0 = 0, w1 = 0;
+                if (r < R) {
+                    const int hq = hk * rep + r / p.L, l = r % p.L;
+                    const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + d0;
+                    w0 = *(const uint32_t *)qp;
+                    w1 = *(const uint32_t *)(qp + 2);
+                }
+                qa[ks][half] = w0;
+                qa[ks][2 + half] = w1;
+            }
+        }
+        uint32_t k_off[2];
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) k_off[ps] = (uint32_t)(g * 128 + (((2 * c + ps) ^ g) << 4));
+        uint32_t v_off[4];
+        {
+            const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int cp = 0; cp < 4; ++cp)
+                v_off[cp] = (uint32_t)(((mi & 1) * 8 + rr) * 128 + (((2 * cp + (mi >> 1)) ^ rr) << 4));
+        }
+
+        for (int it = 0; it < ntiles && ok; ++it) {
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) break;
+            const unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
+            const uint32_t vt_addr = smem_u32(kt + TILE_BYTES);
+#pragma unroll 1
+            for (int blk = 0; blk < 4; ++blk) {
+                const int t_blk = (tile_begin + it) * TILE_T + blk * 16;
+                if (t_blk > lim_max) break;  // warp-uniform: nothing further in this tile is visible
+                const uint32_t boff = blk * 16 * 128;
+                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int bx = 0; bx < BOXES; ++bx) {
+#pragma unroll
+                    for (int ps = 0; ps < 2; ++ps) {
+                        const uint4 k0 = *(const uint4 *)(kt + bx * BOX_BYTES + boff + k_off[ps]);
+                        const uint4 k1 = *(const uint4 *)(kt + bx * BOX_BYTES + boff + k_off[ps] + 8 * 128);
+                        const int ks = bx * 4 + ps * 2;
+                        MmaType<T>::mma(sc[0], qa[ks], k0.x, k0.y);
+                        MmaType<T>::mma(sc[1], qa[ks], k1.x, k1.y);
+                        MmaType<T>::mma(sc[0], qa[ks + 1], k0.z, k0.w);
+                        MmaType<T>::mma(sc[1], qa[ks + 1], k1.z, k1.w);
+                    }
+                }
+                const bool edge = t_blk + 15 > lim_min;  // warp-uniform
+                float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int half = e >> 1;
+                        float v = sc[j][e] * p.scale_log2;
+                        if (edge) {
+                            const int t = t_blk + j * 8 + 2 * c + (e & 1);
+                            v = (t <= row_limit[half]) ? v : -INFINITY;
+                        }
+                        sc[j][e] = v;
+                        tmax[half] = fmaxf(tmax[half], v);
+                    }
+                }
+                float alpha[2];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 1));
+                    tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 2));
+                    const float m_new = fmaxf(m_run[half], tmax[half]);
+                    alpha[half] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[half] - m_new);
+                    m_run[half] = m_new;
+                }
+                uint32_t pa[4];
+                {
+                    float pr[2][4];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int half = e >> 1;
+                            pr[j][e] = (m_run[half] == -INFINITY) ? 0.f : fast_exp2(sc[j][e] - m_run[half]);
+                        }
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        l_run[half] = l_run[half] * alpha[half] + pr[0][2 * half] + pr[0][2 * half + 1] +
+                                      pr[1][2 * half] + pr[1][2 * half + 1];
+                    pa[0] = MmaType<T>::pack(pr[0][0], pr[0][1]);
+                    pa[1] = MmaType<T>::pack(pr[0][2], pr[0][3]);
+                    pa[2] = MmaType<T>::pack(pr[1][0], pr[1][1]);
+                    pa[3] = MmaType<T>::pack(pr[1][2], pr[1][3]);
+                }
+                if (__any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f))) {
+#pragma unroll
+                    for (int nt = 0; nt < NT_O; ++nt) {
+                        o_acc[nt][0] *= alpha[0];
+                        o_acc[nt][1] *= alpha[0];
+                        o_acc[nt][2] *= alpha[1];
+                        o_acc[nt][3] *= alpha[1];
+                    }
+                }
+#pragma unroll
+                for (int bx = 0; bx < BOXES; ++bx) {
+#pragma unroll
+                    for (int cp = 0; cp < 4; ++cp) {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, vt_addr + bx * BOX_BYTES + boff + v_off[cp]);
+                        MmaType<T>::mma(o_acc[bx * 8 + 2 * cp], pa, vf[0], vf[1]);
+                        MmaType<T>::mma(o_acc[bx * 8 + 2 * cp + 1], pa, vf[2], vf[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, 4);
+
+        // ---- the warp's 16 rows: straight to the output, or partials for the merge ----
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
+        }
+        const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = r_warp + g + 8 * half;
+            if (r >= R) continue;
+            if (p.splits == 1) {
+                const float inv = l_run[half] > 0.f ? 1.f / l_run[half] : 0.f;
+                const int hq = hk * rep + r / p.L, lq = r % p.L;
+                const int64_t base = b * p.o_sb + hq * p.o_sh + lq * p.o_sl;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    store_out(p.out, p.out_dtype, base + 8 * nt + 2 * c, o_acc[nt][2 * half] * inv);
+                    store_out(p.out, p.out_dtype, base + 8 * nt + 2 * c + 1, o_acc[nt][2 * half + 1] * inv);
+                }
+            } else {
+                const int64_t pbase = (qrow0 + r) * p.splits + split;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt)
+                    __stcg((float2 *)&p.o_part[pbase * D + 8 * nt + 2 * c],
+                           make_float2(o_acc[nt][2 * half], o_acc[nt][2 * half + 1]));
+                if (c == 0) __stcg(&p.ml_part[pbase], make_float2(m_run[half], l_run[half]));
+            }
+        }
+    }
+    if (p.splits == 1) return;
+
+    // ---- split merge by the last CTA of this row block ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int ticket = atomicAdd(&p.counters[unit], 1);
+        const int last = (ticket == p.splits - 1) ? 1 : 0;
+        if (last) p.counters[unit] = 0;
+        *is_last = last;
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    __threadfence();
+    float *work = (float *)stages;  // [rows of the block][splits] merge weights (the ring is idle)
+    const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;
+    const int nrows = r_hi - r_lo + 1;
+    for (int rr = warp; rr < nrows; rr += DEC_THREADS / 32) {
+        const int64_t row = qrow0 + r_lo + rr;
+        float m = -INFINITY;
+        for (int s = lane; s < p.splits; s += 32) m = fmaxf(m, __ldcg(&p.ml_part[row * p.splits + s]).x);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float lsum = 0.f;
+        for (int s = lane; s < p.splits; s += 32) {
+            const float2 ml = __ldcg(&p.ml_part[row * p.splits + s]);
+            const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
+            work[rr * p.splits + s] = f;
+            lsum += ml.y * f;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        __syncwarp();
+        for (int s = lane; s < p.splits; s += 32) work[rr * p.splits + s] *= inv;
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * D; i += DEC_THREADS) {
+        const int rr = i / D, d = i % D;
+        const int r = r_lo + rr;
+        float o = 0.f;
+        const float *src = p.o_part + ((qrow0 + r) * p.splits) * D + d;
+        for (int s = 0; s < p.splits; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[rr * p.splits + s], o);
+        const int hq = hk * rep + r / p.L, lq = r % p.L;
+        store_out(p.out, p.out_dtype, b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d, o);
+    }
+}
+
+// ---------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -374,6 +677,26 @@ void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const Decode
     ++g_launch_count;
 }
 
+template <typename T, int D, int NSTAGE>
+void launch_chunk_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const DecodeParams &p, int ctas,
+                        cudaStream_t stream) {
+    const size_t smem = (size_t)NSTAGE * 2 * (TILE_T * D * 2) + 2 * NSTAGE * sizeof(uint64_t) + 64 + 1024;
+    static bool configured[64] = {false};
+    const int dev = current_device();
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        KVC_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<T, D, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+        KVC_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<T, D, NSTAGE>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+        configured[dev] = true;
+    }
+    KernelTimer timer(stream);
+    attn_chunk_kernel<T, D, NSTAGE><<<ctas, DEC_THREADS, smem, stream>>>(kmap, vmap, p);
+    timer.stop();
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
 }  // namespace
 
 // Returns the number of kernels launched, or 0 when the call does not fit this path.
@@ -385,11 +708,14 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_signs || a.o_signs || a.q_calib) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv) return 0;
     const int rep = a.Hq / a.Hkv;
-    if (rep * a.L > 16 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    if (a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     if (!source_fits(a.k, a.D, a.Hkv, a.B) || !source_fits(a.v, a.D, a.Hkv, a.B)) return 0;
     if (((uintptr_t)a.q & 3) || (a.q_sb & 1) || (a.q_sh & 1) || (a.q_sl & 1)) return 0;
     const int64_t bh = (int64_t)a.B * a.Hkv;
-    if (bh * (int64_t)sizeof(int) > COUNTER_BYTES) return 0;
+    const bool chunk = rep * a.L > 16;  // more rows than one MMA row block: rows split across warps
+    const int64_t row_blocks = chunk ? ((int64_t)rep * a.L + 63) / 64 : 1;
+    if (bh * row_blocks * (int64_t)sizeof(int) > COUNTER_BYTES) return 0;
+    if (chunk && (int64_t)rep * a.L > (int64_t)1 << 24) return 0;
 
     CUtensorMap kmap, vmap;
     if (!make_map(&kmap, a.k, a.D, a.T, a.Hkv, a.B) || !make_map(&vmap, a.v, a.D, a.T, a.Hkv, a.B)) return 0;
@@ -405,7 +731,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     double best_cost = 1e30;
     const int64_t max_s = std::min<int64_t>(tiles, 64);
     for (int64_t s = 1; s <= max_s; ++s) {
-        const int64_t units = bh * s;
+        const int64_t units = bh * row_blocks * s;
         const int64_t waves = (units + slots - 1) / slots;
         const int64_t per = (tiles + s - 1) / s;
         const double cost = (double)waves * ((double)per + 2.5);
@@ -439,7 +765,25 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     }
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.row_blocks = (int)row_blocks;
+    p.tiles_all = (int)tiles;
     const int units = (int)(bh * splits);
+
+    if (chunk) {
+        const int ctas = (int)(bh * row_blocks * splits);
+#define KVC_CHK(TT, DD, NS) launch_chunk_typed<TT, DD, NS>(kmap, vmap, p, ctas, stream)
+        if (a.q_dtype == KVC_BF16) {
+            if (a.D == 64) KVC_CHK(__nv_bfloat16, 64, 6);
+            else if (a.D == 128) KVC_CHK(__nv_bfloat16, 128, 3);
+            else KVC_CHK(__nv_bfloat16, 256, 3);
+        } else {
+            if (a.D == 64) KVC_CHK(__half, 64, 6);
+            else if (a.D == 128) KVC_CHK(__half, 128, 3);
+            else KVC_CHK(__half, 256, 3);
+        }
+#undef KVC_CHK
+        return 1;
+    }
 
 #define KVC_DEC(TT, DD, NS) launch_typed<TT, DD, NS>(kmap, vmap, p, units, stream)
     if (a.q_dtype == KVC_BF16) {

@@ -88,3 +88,40 @@ print(kvc.launch_count())
         subprocess.run([sys.executable, "-c", code, f], check=True, env=env, timeout=300)
         outs.append(torch.load(f))
     assert float((outs[0] - outs[1]).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,D,L,T,mask", [
+    (2, 8, 2, 128, 64, 300, "causal"),      # prefill chunk on top of a 236-token prefix
+    (1, 64, 8, 128, 6, 2100, "causal"),     # verify round: 8 heads x 6 positions = 48 rows
+    (1, 8, 2, 128, 200, 200, "causal"),     # 800 rows per KV head: 13 row blocks, the last one partial
+    (2, 4, 1, 256, 40, 552, "causal"),      # head dim 256
+    (2, 8, 2, 64, 96, 130, "causal"),       # head dim 64
+    (1, 4, 1, 128, 17, 5000, "none"),       # few units, long context: several splits + merge
+    (1, 32, 8, 128, 5, 999, "none"),        # token count not a multiple of the tile
+    (1, 2, 1, 128, 512, 512, "causal"),     # one 512-token chunk from an empty cache
+])
+def test_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, D, L, T, mask):
+    """Multi-token chunks (more than 16 rows per KV head): rows split across the warps."""
+    q = seeded((B, Hq, L, D), 1, dtype)
+    k, v = seeded((B, Hkv, T, D), 2, dtype), seeded((B, Hkv, T, D), 3, dtype)
+    n0 = kvc.launch_count(reset=True)
+    out = kvc.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, mask)
+    assert kvc.launch_count(reset=True) == 1            # one kernel: partial + merge in one launch
+    ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), D ** -0.5, mask)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_chunked_prefill_through_the_cache(kvc, oracle, cuda):
+    """attentionWithCacheUpdate with 128-token chunks, then decode: chunk and decode kernels on one cache."""
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    cache, o = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    for step, S in enumerate((128, 128, 128, 1, 1)):
+        q, k, v = (seeded((B, Hq, S, D), 3 * step, torch.bfloat16), seeded((B, Hkv, S, D), 3 * step + 1, torch.bfloat16),
+                   seeded((B, Hkv, S, D), 3 * step + 2, torch.bfloat16))
+        mask = "causal" if S > 1 else "none"
+        out = cache.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.09, mask)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, 0.09, mask)
+        assert max_abs_diff(out, ref) <= 2e-2, f"step {step}"
+    assert kvc.lib().kvc_device_status() == 0
