@@ -426,7 +426,7 @@ def run_ours(args, w, rank, world, local_rank):
     h2d = world * Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es  # summed over ranks
     d2h = world * Lyr * Bl * Hql * D * es
     e2e = {"value": B * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "note": "kvc_attention_host per layer (pinned host q/k/v in, output out), one stream sync per step"
+           "note": "kvc_attention_batch with pinned host q/k/v in and outputs out for every layer (copies run on side streams ahead of / behind the layer kernels), one stream sync per step, result read on the host"
                    + ("; every rank runs its own shard, bytes summed over ranks, time is the max" if world > 1 else "")}
 
     cpu_baseline = None

@@ -4,6 +4,8 @@
 // the C boundary.
 #include "cache.h"
 
+#include <vector>
+
 #include <algorithm>
 #include <cstring>
 #include <memory>
@@ -304,6 +306,30 @@ kvc_status kvc_attention(kvc_cache *c, const kvc_tensor *q, const kvc_tensor *k,
         kvc::cache_attention(c, *q, *k, *v, scale, mask_mode, mask, *out, as_stream(stream));
     });
 }
+
+namespace {
+// Copy streams and a growing set of reusable events per device for the host-buffer batch call.
+struct SidePipe {
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    std::vector<cudaEvent_t> events;
+};
+
+SidePipe &side_pipe(int device, size_t need_events) {
+    static thread_local SidePipe pipes[64];
+    KVC_REQUIRE(device >= 0 && device < 64, "device index out of range");
+    SidePipe &p = pipes[device];
+    if (!p.h2d) {
+        KVC_CUDA(cudaStreamCreateWithFlags(&p.h2d, cudaStreamNonBlocking));
+        KVC_CUDA(cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking));
+    }
+    while (p.events.size() < need_events) {
+        cudaEvent_t e;
+        KVC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p.events.push_back(e);
+    }
+    return p;
+}
+}  // namespace
 
 kvc_status kvc_attention_host(kvc_cache *c, const kvc_tensor *q, const kvc_tensor *k,
                               const kvc_tensor *v, float scale, int32_t mask_mode,
@@ -806,6 +832,55 @@ kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kv
                                int32_t mask_mode, const kvc_tensor *outs, void *stream,
                                int32_t host, int32_t synchronize) {
     if (!caches || !q || !k || !v || !outs) return set_error(KVC_ERR_INVALID_ARG, "kvc_attention_batch: null argument");
+    if (host && count > 0 && mask_mode != KVC_MASK_ARRAY) {
+        for (int i = 0; i < count; ++i) KVC_CHECK_HANDLE(caches[i]);
+        return guarded([&] {
+            // Host buffers: every layer's inputs are known when the call is made, so their
+            // copies run ahead on a copy stream while earlier layers compute, and each output
+            // leaves on a third stream as soon as its layer is done. `stream` joins both at the end.
+            DeviceGuard dg(caches[0]->device);
+            cudaStream_t s = as_stream(stream);
+            SidePipe &pipe = side_pipe(kvc::current_device(), 2 * (size_t)count + 2);  // the guard has bound it
+            auto al = [](size_t x) { return (x + 255) / 256 * 256; };
+            std::vector<char *> slabs((size_t)count);
+            for (int i = 0; i < count; ++i) {
+                KVC_REQUIRE(caches[i]->device == caches[0]->device, "kvc_attention_batch: caches live on different devices");
+                KVC_REQUIRE(is_contiguous(q[i]) && is_contiguous(k[i]) && is_contiguous(v[i]) && is_contiguous(outs[i]),
+                            "kvc_attention_batch: host tensors must be contiguous");
+                slabs[(size_t)i] = (char *)stage_get(caches[i], 0,
+                                                     al(tensor_bytes_contiguous(q[i])) + al(tensor_bytes_contiguous(k[i])) +
+                                                         al(tensor_bytes_contiguous(v[i])) + al(tensor_bytes_contiguous(outs[i])), s);
+            }
+            cudaEvent_t start = pipe.events[0], done = pipe.events[1];
+            KVC_CUDA(cudaEventRecord(start, s));              // earlier work on `stream` still reads the slabs
+            KVC_CUDA(cudaStreamWaitEvent(pipe.h2d, start, 0));
+            for (int i = 0; i < count; ++i) {
+                const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
+                             vb = tensor_bytes_contiguous(v[i]);
+                char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb);
+                KVC_CUDA(cudaMemcpyAsync(dq, q[i].data, qb, cudaMemcpyHostToDevice, pipe.h2d));
+                KVC_CUDA(cudaMemcpyAsync(dk, k[i].data, kb, cudaMemcpyHostToDevice, pipe.h2d));
+                KVC_CUDA(cudaMemcpyAsync(dv, v[i].data, vb, cudaMemcpyHostToDevice, pipe.h2d));
+                KVC_CUDA(cudaEventRecord(pipe.events[2 + 2 * (size_t)i], pipe.h2d));
+            }
+            for (int i = 0; i < count; ++i) {
+                const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
+                             vb = tensor_bytes_contiguous(v[i]), ob = tensor_bytes_contiguous(outs[i]);
+                char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb), *dout = dv + al(vb);
+                kvc_tensor tq = q[i], tk = k[i], tv = v[i], to = outs[i];
+                tq.data = dq; tk.data = dk; tv.data = dv; to.data = dout;
+                KVC_CUDA(cudaStreamWaitEvent(s, pipe.events[2 + 2 * (size_t)i], 0));
+                kvc::cache_attention(caches[i], tq, tk, tv, scale, mask_mode, nullptr, to, s);
+                cudaEvent_t out_ready = pipe.events[3 + 2 * (size_t)i];
+                KVC_CUDA(cudaEventRecord(out_ready, s));
+                KVC_CUDA(cudaStreamWaitEvent(pipe.d2h, out_ready, 0));
+                KVC_CUDA(cudaMemcpyAsync(outs[i].data, dout, ob, cudaMemcpyDeviceToHost, pipe.d2h));
+            }
+            KVC_CUDA(cudaEventRecord(done, pipe.d2h));
+            KVC_CUDA(cudaStreamWaitEvent(s, done, 0));
+            if (synchronize) KVC_CUDA(cudaStreamSynchronize(s));
+        });
+    }
     for (int i = 0; i < count; ++i) {
         kvc_status st = host ? kvc_attention_host(caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
                                                   &outs[i], stream, 0)

@@ -156,3 +156,33 @@ def test_host_entry_point_matches_device_entry_point(kvc, cuda):
         dev = a.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.1, mode)
         host = b.attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), 0.1, mode)
         assert torch.equal(dev.cpu(), host)
+
+
+def test_batched_host_call_matches_per_layer_device_calls(kvc, cuda):
+    """kvc_attention_batch with host buffers: copies run ahead on side streams; the results and
+    the cache contents are those of the per-layer device calls, step after step."""
+    B, Hq, Hkv, D, layers = 2, 8, 2, 128, 5
+    dev_caches = [kvc.KVCacheSimple() for _ in range(layers)]
+    host_caches = [kvc.KVCacheSimple() for _ in range(layers)]
+    for i in range(layers):
+        k, v = seeded((B, Hkv, 40 + i, D), 100 + i, torch.bfloat16), seeded((B, Hkv, 40 + i, D), 200 + i, torch.bfloat16)
+        dev_caches[i].update(k.to(cuda), v.to(cuda))
+        host_caches[i].update(k.to(cuda), v.to(cuda))
+    hq = [torch.empty((B, Hq, 1, D), dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
+    hk = [torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
+    hv = [torch.empty((B, Hkv, 1, D), dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
+    ho = [torch.zeros((B, Hq, 1, D), dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
+    step = kvc.DecodeStep(host_caches, hq, hk, hv, ho, 0.1, host=True)
+    for it in range(4):
+        for i in range(layers):
+            hq[i].copy_(seeded((B, Hq, 1, D), 1000 + 10 * it + i, torch.bfloat16))
+            hk[i].copy_(seeded((B, Hkv, 1, D), 2000 + 10 * it + i, torch.bfloat16))
+            hv[i].copy_(seeded((B, Hkv, 1, D), 3000 + 10 * it + i, torch.bfloat16))
+        step.run(synchronize=True)
+        for i in range(layers):
+            ref = dev_caches[i].attention(hq[i].to(cuda), hk[i].to(cuda), hv[i].to(cuda), 0.1)
+            assert torch.equal(ref.cpu(), ho[i]), f"step {it} layer {i}"
+    for a, b in zip(dev_caches, host_caches):
+        assert a.offset == b.offset
+        for x, y in zip(a.state, b.state):
+            assert torch.equal(x, y)
