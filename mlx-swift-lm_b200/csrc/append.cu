@@ -12,6 +12,8 @@ namespace {
 template <typename V>
 __global__ void append_kernel(AppendArgs a, int64_t k_units, int64_t total_units,
                               int k_upr, int v_upr /* units per row */) {
+    // lets a dependent kernel launched with programmatic serialization begin its prologue now
+    asm volatile("griddepcontrol.launch_dependents;");
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total_units) return;
     const bool is_v = i >= k_units;

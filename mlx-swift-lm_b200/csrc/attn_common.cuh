@@ -5,6 +5,9 @@
 
 #include "common.h"
 
+#include <cstdlib>
+#include <utility>
+
 #include <cuda.h>
 
 namespace kvc {
@@ -69,6 +72,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// Programmatic dependent launch: a kernel launched with launch_pdl() may start while the
+// kernel before it on the stream is still running; everything it reads from global memory
+// must come after pdl_wait(), which returns once that kernel has completed and flushed.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
@@ -257,4 +265,27 @@ __device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float 
 }
 
 }  // namespace dev
+
+// Launch with programmatic stream serialization (see dev::pdl_wait). KVC_NO_PDL=1 falls
+// back to a plain launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+    static const bool off = [] {
+        const char *e = std::getenv("KVC_NO_PDL");
+        return e && e[0] == '1';
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = off ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace kvc

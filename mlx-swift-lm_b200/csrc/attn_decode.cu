@@ -104,6 +104,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
@@ -366,6 +367,7 @@ attn_chunk_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
@@ -671,7 +673,7 @@ void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const Decode
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_decode_kernel<T, D, NSTAGE><<<units, DEC_THREADS, smem, stream>>>(kmap, vmap, p);
+    KVC_CUDA(launch_pdl(attn_decode_kernel<T, D, NSTAGE>, dim3(units), dim3(DEC_THREADS), smem, stream, kmap, vmap, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -691,7 +693,7 @@ void launch_chunk_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const 
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_chunk_kernel<T, D, NSTAGE><<<ctas, DEC_THREADS, smem, stream>>>(kmap, vmap, p);
+    KVC_CUDA(launch_pdl(attn_chunk_kernel<T, D, NSTAGE>, dim3(ctas), dim3(DEC_THREADS), smem, stream, kmap, vmap, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;

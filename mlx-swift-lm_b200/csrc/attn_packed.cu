@@ -147,6 +147,7 @@ attn_affine_kernel(const AffineParams p) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
@@ -629,6 +630,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
@@ -978,7 +980,7 @@ void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) 
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_affine_kernel<T, D, BITS, GROUP, NSTAGE><<<units, PK_THREADS, smem, stream>>>(p);
+    KVC_CUDA(launch_pdl(attn_affine_kernel<T, D, BITS, GROUP, NSTAGE>, dim3(units), dim3(PK_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -1002,7 +1004,7 @@ void launch_affine8_typed(const AffineParams &p, int units, cudaStream_t stream)
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB><<<units, PK_THREADS, smem, stream>>>(p);
+    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>, dim3(units), dim3(PK_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;

@@ -152,6 +152,7 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         const int j = w >> 5;
         ((uint32_t *)vtab)[w] = pack_h2(p.vcb[j & ((1 << VB) - 1)], p.vcb[j >> VB]);
     }
+    pdl_wait();  // the tables came from kernel parameters; everything below reads global memory
     // ---- rotated queries: q' = H(signs * q) / sqrt(D) * scale * log2(e), rows past R are zero ----
     for (int i = tid; i < 8 * D; i += TQ_THREADS) {
         const int r = i / D, d = i % D;
@@ -398,7 +399,7 @@ void launch_turbo_typed(const TurboParams &p, int units, cudaStream_t stream) {
         configured[dev] = true;
     }
     KernelTimer timer(stream);
-    attn_turbo_decode8_kernel<T, KB, VB, NSTAGE><<<units, TQ_THREADS, smem, stream>>>(p);
+    KVC_CUDA(launch_pdl(attn_turbo_decode8_kernel<T, KB, VB, NSTAGE>, dim3(units), dim3(TQ_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;

@@ -53,6 +53,8 @@ __device__ __forceinline__ uint32_t affine_code(float w, float scale, float bias
 template <typename T, int E>
 __global__ void affine_quantize_warp_kernel(QuantAppendArgs ka, QuantAppendArgs va, int64_t k_rows,
                                             int64_t total_rows) {
+    // lets a dependent kernel launched with programmatic serialization begin its prologue now
+    asm volatile("griddepcontrol.launch_dependents;");
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= total_rows) return;
@@ -263,6 +265,8 @@ namespace {
 template <typename T, int E>
 __global__ void turbo_encode_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, int64_t k_rows,
                                     int64_t total_rows, float inv_sqrt_dim) {
+    // lets a dependent kernel launched with programmatic serialization begin its prologue now
+    asm volatile("griddepcontrol.launch_dependents;");
     extern __shared__ uint32_t s_words[];  // [warps][PWmax]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
