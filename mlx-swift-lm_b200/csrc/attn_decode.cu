@@ -60,7 +60,10 @@ struct DecodeParams {
     int32_t out_dtype;
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int32_t row_blocks;  // chunk kernel: 64-row blocks per (batch, head)
-    int32_t tiles_all;   // chunk kernel: tiles covering all T tokens
+    int32_t tiles_all;   // chunk / flat kernels: tiles covering all T tokens
+    int32_t flat_per, flat_rem;  // flat kernel: CTA c owns flat_per + (c < flat_rem) consecutive tiles
+    int32_t nslots;      // flat kernel: partial slots per (batch, head)
+    int32_t red_rows;    // flat kernel: rows of the cross-warp buffer (>= rows per KV head)
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
 };
@@ -309,6 +312,329 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
     // work area behind the cross-warp buffers (the stage ring is idle by now)
     float *work = red_ml + CONSUMER_WARPS * 16 * 2;
     unit_epilogue<D, CONSUMER_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
+}
+
+// ---------------------------------------------------------------------
+// Flat tile decomposition of the same decode computation. All (batch, head) units have
+// the same number of tiles, so the launch is one wave of resident CTAs and CTA c simply
+// owns the flat tile range [c W / G, (c + 1) W / G) of the W = units x tiles tiles. A
+// range that crosses a unit boundary is processed as consecutive segments: the producer
+// keeps streaming through the boundary, the consumers finish a segment (cross-warp
+// merge, partial to scratch, ticket) and start the next with fresh state. Every CTA does
+// the same amount of streaming whatever the shape, and the ramp at both ends of the
+// launch is paid once. The cross-warp buffer sits beside the ring (the ring stays live),
+// and the consumer warps synchronise among themselves with a named barrier that every
+// warp reaches whether or not one of its bounded waits has run out.
+// ---------------------------------------------------------------------
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ int64_t flat_lo(const DecodeParams &p, int c) {
+    return (int64_t)c * p.flat_per + min(c, p.flat_rem);
+}
+
+__device__ __forceinline__ int flat_cta_of(const DecodeParams &p, int64_t x) {
+    const int64_t big = (int64_t)p.flat_rem * (p.flat_per + 1);
+    return x < big ? (int)(x / (p.flat_per + 1)) : p.flat_rem + (int)((x - big) / p.flat_per);
+}
+
+template <typename T, int D, int NSTAGE>
+__global__ void __launch_bounds__(DEC_THREADS, (D <= 128 ? 2 : 1))
+attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                        const DecodeParams p) {
+    constexpr int TILE_BYTES = TILE_T * D * 2;
+    constexpr int BOXES = D / 64;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NT_O = D / 8;
+    constexpr int RED_STRIDE = D + 8;
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t *full = (uint64_t *)(stages + (size_t)NSTAGE * 2 * TILE_BYTES);
+    uint64_t *empty = full + NSTAGE;
+    int *is_last = (int *)(empty + NSTAGE);
+    float *red_o = (float *)(is_last + 4);                                   // [4][red_rows][RED_STRIDE]
+    float *red_ml = red_o + CONSUMER_WARPS * p.red_rows * RED_STRIDE;        // [4][red_rows][2]
+    float *work = red_ml + CONSUMER_WARPS * p.red_rows * 2;                  // [red_rows][nslots]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rep = p.Hq / p.Hkv;
+    const int R = rep * p.L;
+    const int tiles = p.tiles_all;
+    const int64_t x_lo = flat_lo(p, blockIdx.x), x_hi = flat_lo(p, blockIdx.x + 1);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
+
+    bool ok = true;
+    if (warp == CONSUMER_WARPS) {
+        // ---------------- producer: one stream of tiles across the segments ----------------
+        if (lane == 0) {
+            int it = 0;
+            for (int64_t x = x_lo; x < x_hi && ok;) {
+                const int unit = (int)(x / tiles), t0 = (int)(x % tiles);
+                const int n = (int)min((int64_t)(tiles - t0), x_hi - x);
+                const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                for (int j = 0; j < n && ok; ++j, ++it) {
+                    const int s = it % NSTAGE;
+                    if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                    if (!ok) break;
+                    unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
+                    unsigned char *vt = kt + TILE_BYTES;
+                    mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+                    const int tok = (t0 + j) * TILE_T;
+#pragma unroll
+                    for (int bx = 0; bx < BOXES; ++bx) {
+                        tma_load_4d(kt + bx * BOX_BYTES, &kmap, &full[s], bx * 64, tok, hk, b);
+                        tma_load_4d(vt + bx * BOX_BYTES, &vmap, &full[s], bx * 64, tok, hk, b);
+                    }
+                }
+                x += n;
+            }
+            if (!ok) atomicExch(p.status, 9);
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, c = lane & 3;
+    int64_t row_limit[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + 8 * half;
+        const int l = r % p.L;
+        row_limit[half] = (r < R) ? (p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+    }
+    const int blk = warp;
+    uint32_t k_off[2];
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) k_off[ps] = (uint32_t)((blk * 16 + g) * 128 + (((2 * c + ps) ^ g) << 4));
+    uint32_t v_off[4];
+    {
+        const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp)
+            v_off[cp] = (uint32_t)((blk * 16 + (mi & 1) * 8 + rr) * 128 + (((2 * cp + (mi >> 1)) ^ rr) << 4));
+    }
+
+    int it = 0;
+    for (int64_t x = x_lo; x < x_hi;) {
+        const int unit = (int)(x / tiles), t0 = (int)(x % tiles);
+        const int n = (int)min((int64_t)(tiles - t0), x_hi - x);
+        const int hk = unit % p.Hkv, b = unit / p.Hkv;
+
+        uint32_t qa[KSTEPS][4];
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
+            const int d0 = bx * 64 + (2 * c + ps) * 8 + 4 * h;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = g + 8 * half;
+                uint32_t w0 = 0, w1 = 0;
+                if (r < R) {
+                    const int hq = hk * rep + r / p.L, l = r % p.L;
+                    const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + d0;
+                    w0 = *(const uint32_t *)qp;
+                    w1 = *(const uint32_t *)(qp + 2);
+                }
+                qa[ks][half] = w0;
+                qa[ks][2 + half] = w1;
+            }
+        }
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        float o_acc[NT_O][4];
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+        for (int j = 0; j < n; ++j, ++it) {
+            if (!ok) continue;  // a wait ran out earlier: walk on to the barriers below
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, 10);
+                continue;
+            }
+            if (p.debug_skip) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                continue;
+            }
+            const unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
+            const uint32_t vt_addr = smem_u32(kt + TILE_BYTES);
+            const int64_t t_blk = (int64_t)(t0 + j) * TILE_T + blk * 16;
+
+            float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int bx = 0; bx < BOXES; ++bx) {
+#pragma unroll
+                for (int ps = 0; ps < 2; ++ps) {
+                    const uint4 k0 = *(const uint4 *)(kt + bx * BOX_BYTES + k_off[ps]);
+                    const uint4 k1 = *(const uint4 *)(kt + bx * BOX_BYTES + k_off[ps] + 8 * 128);
+                    const int ks = bx * 4 + ps * 2;
+                    MmaType<T>::mma(sc[0], qa[ks], k0.x, k0.y);
+                    MmaType<T>::mma(sc[1], qa[ks], k1.x, k1.y);
+                    MmaType<T>::mma(sc[0], qa[ks + 1], k0.z, k0.w);
+                    MmaType<T>::mma(sc[1], qa[ks + 1], k1.z, k1.w);
+                }
+            }
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int half = e >> 1;
+                    const int64_t t = t_blk + jj * 8 + 2 * c + (e & 1);
+                    float v = sc[jj][e] * p.scale_log2;
+                    v = (t <= row_limit[half]) ? v : -INFINITY;
+                    sc[jj][e] = v;
+                    tmax[half] = fmaxf(tmax[half], v);
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 1));
+                tmax[half] = fmaxf(tmax[half], __shfl_xor_sync(0xffffffffu, tmax[half], 2));
+                const float m_new = fmaxf(m_run[half], tmax[half]);
+                alpha[half] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[half] - m_new);
+                m_run[half] = m_new;
+            }
+            uint32_t pa[4];
+            {
+                float pr[2][4];
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int half = e >> 1;
+                        pr[jj][e] = (m_run[half] == -INFINITY) ? 0.f : fast_exp2(sc[jj][e] - m_run[half]);
+                    }
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+                    l_run[half] = l_run[half] * alpha[half] + pr[0][2 * half] + pr[0][2 * half + 1] +
+                                  pr[1][2 * half] + pr[1][2 * half + 1];
+                pa[0] = MmaType<T>::pack(pr[0][0], pr[0][1]);
+                pa[1] = MmaType<T>::pack(pr[0][2], pr[0][3]);
+                pa[2] = MmaType<T>::pack(pr[1][0], pr[1][1]);
+                pa[3] = MmaType<T>::pack(pr[1][2], pr[1][3]);
+            }
+            if (__any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f))) {
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    o_acc[nt][0] *= alpha[0];
+                    o_acc[nt][1] *= alpha[0];
+                    o_acc[nt][2] *= alpha[1];
+                    o_acc[nt][3] *= alpha[1];
+                }
+            }
+#pragma unroll
+            for (int bx = 0; bx < BOXES; ++bx) {
+#pragma unroll
+                for (int cp = 0; cp < 4; ++cp) {
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vt_addr + bx * BOX_BYTES + v_off[cp]);
+                    MmaType<T>::mma(o_acc[bx * 8 + 2 * cp], pa, vf[0], vf[1]);
+                    MmaType<T>::mma(o_acc[bx * 8 + 2 * cp + 1], pa, vf[2], vf[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // ---- end of the segment: merge the four warps, publish the partial, maybe merge the unit ----
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
+        }
+        {
+            float *wo = red_o + warp * p.red_rows * RED_STRIDE;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = g + 8 * half;
+                if (r >= R) continue;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt)
+                    *(float2 *)&wo[r * RED_STRIDE + 8 * nt + 2 * c] = make_float2(o_acc[nt][2 * half], o_acc[nt][2 * half + 1]);
+                if (c == 0) {
+                    red_ml[(warp * p.red_rows + r) * 2 + 0] = m_run[half];
+                    red_ml[(warp * p.red_rows + r) * 2 + 1] = l_run[half];
+                }
+            }
+        }
+        consumer_bar();
+        const int64_t x_unit = (int64_t)unit * tiles;
+        const int first_cta = flat_cta_of(p, x_unit);
+        const int expected = flat_cta_of(p, x_unit + tiles - 1) - first_cta + 1;
+        const int slot = (int)blockIdx.x - first_cta;
+        const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;
+        for (int i = tid; i < R * D; i += CONSUMER_WARPS * 32) {
+            const int r = i / D, d = i % D;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, red_ml[(w * p.red_rows + r) * 2]);
+            float o = 0.f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                const float mw = red_ml[(w * p.red_rows + r) * 2];
+                const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+                o += red_o[(w * p.red_rows + r) * RED_STRIDE + d] * f;
+                l += red_ml[(w * p.red_rows + r) * 2 + 1] * f;
+            }
+            const int64_t base = (qrow0 + r) * p.nslots + slot;
+            __stcg(&p.o_part[base * D + d], o);
+            if (d == 0) __stcg(&p.ml_part[base], make_float2(m, l));
+        }
+        __threadfence();
+        consumer_bar();
+        if (tid == 0) {
+            const int ticket = atomicAdd(&p.counters[unit], 1);
+            const int last = (ticket == expected - 1) ? 1 : 0;
+            if (last) p.counters[unit] = 0;
+            *is_last = last;
+        }
+        consumer_bar();
+        if (*is_last) {
+            __threadfence();
+            for (int r = warp; r < R; r += CONSUMER_WARPS) {
+                float m = -INFINITY;
+                for (int s = lane; s < expected; s += 32) m = fmaxf(m, __ldcg(&p.ml_part[(qrow0 + r) * p.nslots + s]).x);
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                float lsum = 0.f;
+                for (int s = lane; s < expected; s += 32) {
+                    const float2 ml = __ldcg(&p.ml_part[(qrow0 + r) * p.nslots + s]);
+                    const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
+                    work[r * p.nslots + s] = f;
+                    lsum += ml.y * f;
+                }
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+                const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+                __syncwarp();
+                for (int s = lane; s < expected; s += 32) work[r * p.nslots + s] *= inv;
+            }
+            consumer_bar();
+            for (int i = tid; i < R * D; i += CONSUMER_WARPS * 32) {
+                const int r = i / D, d = i % D;
+                float o = 0.f;
+                const float *src = p.o_part + ((qrow0 + r) * p.nslots) * D + d;
+                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * p.nslots + s], o);
+                const int hq = hk * rep + r / p.L, lq = r % p.L;
+                store_out(p.out, p.out_dtype, b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d, o);
+            }
+        }
+        consumer_bar();  // the buffers and the flag are reused by the next segment
+        x += n;
+    }
 }
 
 // ---------------------------------------------------------------------
@@ -680,6 +1006,25 @@ void launch_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const Decode
 }
 
 template <typename T, int D, int NSTAGE>
+void launch_flat_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const DecodeParams &p, int ctas, size_t smem,
+                       cudaStream_t stream) {
+    static size_t configured[64] = {0};
+    const int dev = current_device();
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+        KVC_CUDA(cudaFuncSetAttribute(attn_decode_flat_kernel<T, D, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+        KVC_CUDA(cudaFuncSetAttribute(attn_decode_flat_kernel<T, D, NSTAGE>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+        configured[dev] = smem;
+    }
+    KernelTimer timer(stream);
+    KVC_CUDA(launch_pdl(attn_decode_flat_kernel<T, D, NSTAGE>, dim3(ctas), dim3(DEC_THREADS), smem, stream, kmap, vmap, p));
+    timer.stop();
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+template <typename T, int D, int NSTAGE>
 void launch_chunk_typed(const CUtensorMap &kmap, const CUtensorMap &vmap, const DecodeParams &p, int ctas,
                         cudaStream_t stream) {
     const size_t smem = (size_t)NSTAGE * 2 * (TILE_T * D * 2) + 2 * NSTAGE * sizeof(uint64_t) + 64 + 1024;
@@ -725,10 +1070,67 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     int *counters = counters_get(a.device, stream, COUNTER_BYTES);
     if (!status || !counters) return 0;
 
-    // Units per (batch, head): minimise waves x (tiles per unit + fixed cost), with
-    // `slots` CTAs resident at once; ties go to fewer splits.
     const int64_t tiles = (a.T + TILE_T - 1) / TILE_T;
     const int slots = sm_count(a.device) * (a.D <= 128 ? 2 : 1);
+
+    // Decode (one MMA row block): flat decomposition over one wave of CTAs when its cross-warp
+    // buffer fits beside the ring; KVC_DECODE_FLAT=0 keeps the per-unit split kernel.
+    if (!chunk) {
+        static const bool flat_off = [] {
+            const char *e = std::getenv("KVC_DECODE_FLAT");
+            return e && e[0] == '0';
+        }();
+        const int R = rep * a.L;
+        const int64_t work = bh * tiles;
+        const int64_t ctas = std::min<int64_t>(slots, work);
+        const int64_t per = work / ctas, rem = work % ctas;
+        const int64_t nslots = (tiles + per - 1) / per + 1;
+        const int nstage = a.D == 64 ? 6 : 3;
+        const size_t ring = (size_t)nstage * 2 * (TILE_T * a.D * 2);
+        const size_t red = (size_t)CONSUMER_WARPS * R * (a.D + 8) * 4 + (size_t)CONSUMER_WARPS * R * 8 + (size_t)R * nslots * 4;
+        const size_t smem = ring + 2 * nstage * sizeof(uint64_t) + 64 + red + 1024;
+        const size_t budget = (a.D <= 128 ? 112 : 224) * 1024;
+        if (!flat_off && smem <= budget && nslots <= 64) {
+            const int64_t qrows_f = (int64_t)a.B * a.Hq * a.L;
+            const size_t o_bytes_f = (size_t)qrows_f * nslots * a.D * sizeof(float);
+            const size_t ml_bytes_f = (size_t)qrows_f * nslots * sizeof(float2);
+            char *scratch_f = (char *)scratch_get(a.device, o_bytes_f + ml_bytes_f + 256, stream);
+            DecodeParams p;
+            p.q = a.q; p.out = a.out; p.out_dtype = a.q_dtype;
+            p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
+            p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+            p.o_part = (float *)scratch_f;
+            p.ml_part = (float2 *)(scratch_f + ((o_bytes_f + 255) / 256) * 256);
+            p.counters = counters; p.status = status;
+            p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
+            p.splits = 1; p.tiles_base = 0; p.tiles_rem = 0; p.row_blocks = 1;
+            p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+            {
+                const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
+                p.debug_skip = (e && e[0] == '1') ? 1 : 0;
+            }
+            p.causal_offset = a.mask.causal_offset;
+            p.scale_log2 = a.scale * 1.4426950408889634f;
+            p.tiles_all = (int)tiles;
+            p.flat_per = (int)per; p.flat_rem = (int)rem;
+            p.nslots = (int)nslots; p.red_rows = R;
+#define KVC_FLAT(TT, DD, NS) launch_flat_typed<TT, DD, NS>(kmap, vmap, p, (int)ctas, smem, stream)
+            if (a.q_dtype == KVC_BF16) {
+                if (a.D == 64) KVC_FLAT(__nv_bfloat16, 64, 6);
+                else if (a.D == 128) KVC_FLAT(__nv_bfloat16, 128, 3);
+                else KVC_FLAT(__nv_bfloat16, 256, 3);
+            } else {
+                if (a.D == 64) KVC_FLAT(__half, 64, 6);
+                else if (a.D == 128) KVC_FLAT(__half, 128, 3);
+                else KVC_FLAT(__half, 256, 3);
+            }
+#undef KVC_FLAT
+            return 1;
+        }
+    }
+
+    // Units per (batch, head): minimise waves x (tiles per unit + fixed cost), with
+    // `slots` CTAs resident at once; ties go to fewer splits.
     int64_t best_s = 1;
     double best_cost = 1e30;
     const int64_t max_s = std::min<int64_t>(tiles, 64);
