@@ -264,6 +264,138 @@ __device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float 
     }
 }
 
+// ---------------------------------------------------------------------
+// Flat tile decomposition shared by the decode kernels. All (batch, head) units have
+// `tiles` tiles; CTA c owns the consecutive flat tiles [flat_lo(c), flat_lo(c + 1)) of the
+// units * tiles in the launch and walks them as segments (one per unit it touches). The
+// partial of a segment goes to slot (c - first CTA of the unit) of the unit's partials.
+// ---------------------------------------------------------------------
+struct FlatPlan {
+    int32_t tiles;     // tiles per unit
+    int32_t per, rem;  // CTA c owns per + (c < rem) tiles
+    int32_t nslots;    // partial slots per unit
+    int32_t red_rows;  // rows of the cross-warp buffers (>= query rows per unit)
+};
+
+__device__ __forceinline__ int64_t flat_lo(const FlatPlan &f, int c) { return (int64_t)c * f.per + min(c, f.rem); }
+
+__device__ __forceinline__ int flat_cta_of(const FlatPlan &f, int64_t x) {
+    const int64_t big = (int64_t)f.rem * (f.per + 1);
+    return x < big ? (int)(x / (f.per + 1)) : f.rem + (int)((x - big) / f.per);
+}
+
+// Barrier among the NW consumer warps only (the producer warp never joins it). Every consumer
+// warp reaches every one of these whether or not one of its bounded waits has run out.
+template <int NW>
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+}
+
+// End of a segment, called by all NW consumer warps (tid = 0 .. 32 NW - 1) after each has
+// written its un-normalised rows to red_o[(warp * red_rows + r) * red_stride + d] and
+// red_ml[(warp * red_rows + r) * 2 + {0, 1}] = (max, sum): merges the warps, writes the
+// segment's partial, takes a ticket and, in the CTA that completes the unit, merges all
+// partials (log-sum-exp) and writes the output rows (through signs * H(.) / sqrt(D) when
+// o_signs is set). `work` holds red_rows * nslots floats, plus red_rows * D when o_signs is set.
+template <int D, int NW>
+__device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const float *red_o, const float *red_ml,
+                                 int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int NT = NW * 32;
+    consumer_bar<NW>();
+    const int64_t x_unit = (int64_t)unit * f.tiles;
+    const int first_cta = flat_cta_of(f, x_unit);
+    const int expected = flat_cta_of(f, x_unit + f.tiles - 1) - first_cta + 1;
+    const int slot = (int)blockIdx.x - first_cta;
+    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L;
+    for (int i = tid; i < R * D; i += NT) {
+        const int r = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, red_ml[(w * f.red_rows + r) * 2]);
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = red_ml[(w * f.red_rows + r) * 2];
+            const float fw = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+            o += red_o[(w * f.red_rows + r) * red_stride + d] * fw;
+            l += red_ml[(w * f.red_rows + r) * 2 + 1] * fw;
+        }
+        const int64_t base = (qrow0 + r) * f.nslots + slot;
+        __stcg(&u.o_part[base * D + d], o);
+        if (d == 0) __stcg(&u.ml_part[base], make_float2(m, l));
+    }
+    __threadfence();
+    consumer_bar<NW>();
+    if (tid == 0) {
+        const int ticket = atomicAdd(&u.counters[unit], 1);
+        const int last = (ticket == expected - 1) ? 1 : 0;
+        if (last) u.counters[unit] = 0;
+        *flag = last;
+    }
+    consumer_bar<NW>();
+    if (*flag) {
+        __threadfence();
+        for (int r = warp; r < R; r += NW) {
+            float m = -INFINITY;
+            for (int s = lane; s < expected; s += 32) m = fmaxf(m, __ldcg(&u.ml_part[(qrow0 + r) * f.nslots + s]).x);
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float lsum = 0.f;
+            for (int s = lane; s < expected; s += 32) {
+                const float2 ml = __ldcg(&u.ml_part[(qrow0 + r) * f.nslots + s]);
+                const float fw = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
+                work[r * f.nslots + s] = fw;
+                lsum += ml.y * fw;
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            __syncwarp();
+            for (int s = lane; s < expected; s += 32) work[r * f.nslots + s] *= inv;
+        }
+        consumer_bar<NW>();
+        if (!u.o_signs) {
+            for (int i = tid; i < R * D; i += NT) {
+                const int r = i / D, d = i % D;
+                float o = 0.f;
+                const float *src = u.o_part + ((qrow0 + r) * f.nslots) * D + d;
+                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * f.nslots + s], o);
+                const int hq = hk * rep + r / u.L, lq = r % u.L;
+                store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, o);
+            }
+        } else {
+            // TurboQuant values: the merged rows are in the rotated basis; out = signs * H(o) / sqrt(D).
+            float *rows = work + f.red_rows * f.nslots;  // [R][D]
+            for (int i = tid; i < R * D; i += NT) {
+                const int r = i / D, d = i % D;
+                float o = 0.f;
+                const float *src = u.o_part + ((qrow0 + r) * f.nslots) * D + d;
+                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * f.nslots + s], o);
+                rows[i] = o;
+            }
+            for (int half = 1; half < D; half <<= 1) {
+                consumer_bar<NW>();
+                for (int pidx = tid; pidx < R * (D / 2); pidx += NT) {
+                    const int r = pidx / (D / 2), j = pidx % (D / 2);
+                    const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
+                    const float x = rows[r * D + i0], y = rows[r * D + i1];
+                    rows[r * D + i0] = x + y;
+                    rows[r * D + i1] = x - y;
+                }
+            }
+            consumer_bar<NW>();
+            const float fs = rsqrtf((float)D);
+            for (int i = tid; i < R * D; i += NT) {
+                const int r = i / D, d = i % D;
+                const int hq = hk * rep + r / u.L, lq = r % u.L;
+                store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, rows[i] * fs * u.o_signs[d]);
+            }
+        }
+    }
+    consumer_bar<NW>();  // buffers and flag are reused by the next segment
+}
+
 }  // namespace dev
 
 // Launch with programmatic stream serialization (see dev::pdl_wait). KVC_NO_PDL=1 falls

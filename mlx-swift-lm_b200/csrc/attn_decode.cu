@@ -60,10 +60,8 @@ struct DecodeParams {
     int32_t out_dtype;
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int32_t row_blocks;  // chunk kernel: 64-row blocks per (batch, head)
-    int32_t tiles_all;   // chunk / flat kernels: tiles covering all T tokens
-    int32_t flat_per, flat_rem;  // flat kernel: CTA c owns flat_per + (c < flat_rem) consecutive tiles
-    int32_t nslots;      // flat kernel: partial slots per (batch, head)
-    int32_t red_rows;    // flat kernel: rows of the cross-warp buffer (>= rows per KV head)
+    int32_t tiles_all;   // chunk kernel: tiles covering all T tokens
+    FlatPlan flat;       // flat kernel
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
 };
@@ -326,17 +324,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
 // and the consumer warps synchronise among themselves with a named barrier that every
 // warp reaches whether or not one of its bounded waits has run out.
 // ---------------------------------------------------------------------
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ int64_t flat_lo(const DecodeParams &p, int c) {
-    return (int64_t)c * p.flat_per + min(c, p.flat_rem);
-}
-
-__device__ __forceinline__ int flat_cta_of(const DecodeParams &p, int64_t x) {
-    const int64_t big = (int64_t)p.flat_rem * (p.flat_per + 1);
-    return x < big ? (int)(x / (p.flat_per + 1)) : p.flat_rem + (int)((x - big) / p.flat_per);
-}
-
 template <typename T, int D, int NSTAGE>
 __global__ void __launch_bounds__(DEC_THREADS, (D <= 128 ? 2 : 1))
 attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -352,15 +339,16 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     uint64_t *full = (uint64_t *)(stages + (size_t)NSTAGE * 2 * TILE_BYTES);
     uint64_t *empty = full + NSTAGE;
     int *is_last = (int *)(empty + NSTAGE);
+    const FlatPlan &fp = p.flat;
     float *red_o = (float *)(is_last + 4);                                   // [4][red_rows][RED_STRIDE]
-    float *red_ml = red_o + CONSUMER_WARPS * p.red_rows * RED_STRIDE;        // [4][red_rows][2]
-    float *work = red_ml + CONSUMER_WARPS * p.red_rows * 2;                  // [red_rows][nslots]
+    float *red_ml = red_o + CONSUMER_WARPS * fp.red_rows * RED_STRIDE;       // [4][red_rows][2]
+    float *work = red_ml + CONSUMER_WARPS * fp.red_rows * 2;                 // [red_rows][nslots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;
-    const int tiles = p.tiles_all;
-    const int64_t x_lo = flat_lo(p, blockIdx.x), x_hi = flat_lo(p, blockIdx.x + 1);
+    const int tiles = fp.tiles;
+    const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -556,7 +544,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
         }
         {
-            float *wo = red_o + warp * p.red_rows * RED_STRIDE;
+            float *wo = red_o + warp * fp.red_rows * RED_STRIDE;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int r = g + 8 * half;
@@ -565,74 +553,18 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                 for (int nt = 0; nt < NT_O; ++nt)
                     *(float2 *)&wo[r * RED_STRIDE + 8 * nt + 2 * c] = make_float2(o_acc[nt][2 * half], o_acc[nt][2 * half + 1]);
                 if (c == 0) {
-                    red_ml[(warp * p.red_rows + r) * 2 + 0] = m_run[half];
-                    red_ml[(warp * p.red_rows + r) * 2 + 1] = l_run[half];
+                    red_ml[(warp * fp.red_rows + r) * 2 + 0] = m_run[half];
+                    red_ml[(warp * fp.red_rows + r) * 2 + 1] = l_run[half];
                 }
             }
         }
-        consumer_bar();
-        const int64_t x_unit = (int64_t)unit * tiles;
-        const int first_cta = flat_cta_of(p, x_unit);
-        const int expected = flat_cta_of(p, x_unit + tiles - 1) - first_cta + 1;
-        const int slot = (int)blockIdx.x - first_cta;
-        const int64_t qrow0 = ((int64_t)b * p.Hq + hk * rep) * p.L;
-        for (int i = tid; i < R * D; i += CONSUMER_WARPS * 32) {
-            const int r = i / D, d = i % D;
-            float m = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, red_ml[(w * p.red_rows + r) * 2]);
-            float o = 0.f, l = 0.f;
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) {
-                const float mw = red_ml[(w * p.red_rows + r) * 2];
-                const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
-                o += red_o[(w * p.red_rows + r) * RED_STRIDE + d] * f;
-                l += red_ml[(w * p.red_rows + r) * 2 + 1] * f;
-            }
-            const int64_t base = (qrow0 + r) * p.nslots + slot;
-            __stcg(&p.o_part[base * D + d], o);
-            if (d == 0) __stcg(&p.ml_part[base], make_float2(m, l));
-        }
-        __threadfence();
-        consumer_bar();
-        if (tid == 0) {
-            const int ticket = atomicAdd(&p.counters[unit], 1);
-            const int last = (ticket == expected - 1) ? 1 : 0;
-            if (last) p.counters[unit] = 0;
-            *is_last = last;
-        }
-        consumer_bar();
-        if (*is_last) {
-            __threadfence();
-            for (int r = warp; r < R; r += CONSUMER_WARPS) {
-                float m = -INFINITY;
-                for (int s = lane; s < expected; s += 32) m = fmaxf(m, __ldcg(&p.ml_part[(qrow0 + r) * p.nslots + s]).x);
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                float lsum = 0.f;
-                for (int s = lane; s < expected; s += 32) {
-                    const float2 ml = __ldcg(&p.ml_part[(qrow0 + r) * p.nslots + s]);
-                    const float f = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
-                    work[r * p.nslots + s] = f;
-                    lsum += ml.y * f;
-                }
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-                const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-                __syncwarp();
-                for (int s = lane; s < expected; s += 32) work[r * p.nslots + s] *= inv;
-            }
-            consumer_bar();
-            for (int i = tid; i < R * D; i += CONSUMER_WARPS * 32) {
-                const int r = i / D, d = i % D;
-                float o = 0.f;
-                const float *src = p.o_part + ((qrow0 + r) * p.nslots) * D + d;
-                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * p.nslots + s], o);
-                const int hq = hk * rep + r / p.L, lq = r % p.L;
-                store_out(p.out, p.out_dtype, b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d, o);
-            }
-        }
-        consumer_bar();  // the buffers and the flag are reused by the next segment
+        UnitOut u;
+        u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+        u.out = p.out; u.out_dtype = p.out_dtype;
+        u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+        u.o_signs = nullptr;
+        u.splits = 0; u.Hq = p.Hq; u.L = p.L;
+        segment_epilogue<D, CONSUMER_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
         x += n;
     }
 }
@@ -1112,8 +1044,9 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.causal_offset = a.mask.causal_offset;
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.tiles_all = (int)tiles;
-            p.flat_per = (int)per; p.flat_rem = (int)rem;
-            p.nslots = (int)nslots; p.red_rows = R;
+            p.flat.tiles = (int)tiles;
+            p.flat.per = (int)per; p.flat.rem = (int)rem;
+            p.flat.nslots = (int)nslots; p.flat.red_rows = R;
 #define KVC_FLAT(TT, DD, NS) launch_flat_typed<TT, DD, NS>(kmap, vmap, p, (int)ctas, smem, stream)
             if (a.q_dtype == KVC_BF16) {
                 if (a.D == 64) KVC_FLAT(__nv_bfloat16, 64, 6);

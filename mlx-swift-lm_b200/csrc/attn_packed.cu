@@ -58,6 +58,7 @@ struct AffineParams {
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int64_t causal_offset;
     float scale_log2;
+    FlatPlan flat;  // decode8 kernel: flat tile decomposition
 };
 
 __device__ __forceinline__ uint32_t hsub2_1024(uint32_t x) {
@@ -606,20 +607,20 @@ attn_affine_decode8_kernel(const AffineParams p) {
     // pointer + offset (no integer round trip) so that loads through it stay ld.shared
     unsigned char *stages = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     constexpr int RING = NSTAGE * STAGE_BYTES;
-    constexpr int RED_BYTES = PK_WARPS * 16 * RED_STRIDE * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
-    constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
-    uint64_t *full = (uint64_t *)(stages + ((BODY + 15) / 16) * 16);
+    const FlatPlan &fp = p.flat;
+    uint64_t *full = (uint64_t *)(stages + ((RING + 15) / 16) * 16);
     uint64_t *empty = full + NSTAGE;
     int *is_last = (int *)(empty + NSTAGE);
+    // cross-warp buffers beside the ring (the ring stays live across segments)
+    float *red_o = (float *)(is_last + 4);                               // [4][red_rows][RED_STRIDE]
+    float *red_ml = red_o + PK_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
+    float *work = red_ml + PK_WARPS * fp.red_rows * 2;                   // [red_rows][nslots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x % p.splits;
-    const int bh = blockIdx.x / p.splits;
-    const int hk = bh % p.Hkv, b = bh / p.Hkv;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;  // <= 8
-    const int tile_begin = split * p.tiles_base + min(split, p.tiles_rem);
-    const int ntiles = p.tiles_base + (split < p.tiles_rem ? 1 : 0);
+    const int tiles = fp.tiles;
+    const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -634,42 +635,58 @@ attn_affine_decode8_kernel(const AffineParams p) {
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
-    // per-lane state for query rows 2c and 2c+1
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    float bsum[2][G];
-    float o_acc[MT_O][4];
-#pragma unroll
-    for (int i = 0; i < MT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int gr = 0; gr < G; ++gr) bsum[h][gr] = 0.f;
 
     if (warp == PK_WARPS) {
+        // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
-            const uint32_t *kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
-            const uint32_t *vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
-            const T *ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
-            const T *kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
-            const T *vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
-            const T *vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
-            for (int it = 0; it < ntiles && ok; ++it) {
-                const int s = it % NSTAGE;
-                if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
-                if (!ok) break;
-                unsigned char *st = stages + (size_t)s * STAGE_BYTES;
-                const int64_t t0 = (int64_t)(tile_begin + it) * PK_TILE;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                bulk_load(st, kc + t0 * WPR, CODE_TILE, &full[s]);
-                bulk_load(st + CODE_TILE, vc + t0 * WPR, CODE_TILE, &full[s]);
-                bulk_load(st + 2 * CODE_TILE, ks + t0 * G, SC_TILE, &full[s]);
-                bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, SC_TILE, &full[s]);
-                bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, SC_TILE, &full[s]);
-                bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, SC_TILE, &full[s]);
+            int it = 0;
+            for (int64_t x = x_lo; x < x_hi && ok;) {
+                const int unit = (int)(x / tiles), tb = (int)(x % tiles);
+                const int n = (int)min((int64_t)(tiles - tb), x_hi - x);
+                const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                const uint32_t *kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
+                const uint32_t *vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
+                const T *ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
+                const T *kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
+                const T *vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
+                const T *vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
+                for (int j = 0; j < n && ok; ++j, ++it) {
+                    const int s = it % NSTAGE;
+                    if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                    if (!ok) break;
+                    unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+                    const int64_t t0 = (int64_t)(tb + j) * PK_TILE;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    bulk_load(st, kc + t0 * WPR, CODE_TILE, &full[s]);
+                    bulk_load(st + CODE_TILE, vc + t0 * WPR, CODE_TILE, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE, ks + t0 * G, SC_TILE, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, SC_TILE, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, SC_TILE, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, SC_TILE, &full[s]);
+                }
+                x += n;
             }
             if (!ok) atomicExch(p.status, 5);
         }
-    } else {
+        return;
+    }
+
+    // ---------------- consumers: one segment per unit the CTA's tile range touches ----------------
+    int it = 0;
+    for (int64_t x = x_lo; x < x_hi;) {
+        const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
+        const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
+        const int hk = unit % p.Hkv, b = unit / p.Hkv;
+        // per-lane state for query rows 2c and 2c+1
+        float m_run[2], l_run[2] = {0.f, 0.f};
+        float bsum[2][G];
+        float o_acc[MT_O][4];
+#pragma unroll
+        for (int i = 0; i < MT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int gr = 0; gr < G; ++gr) bsum[h][gr] = 0.f;
         // Q^T fragments: B operand column = query row g; k-slots follow the code words.
         // q' = f16(q * scale * log2 e). The code operands are f16 subnormals n * 2^-24 (or
         // n * 2^-20 for the nibbles at bits 4..7): the k-slots fed by the smaller form carry
@@ -734,11 +751,14 @@ attn_affine_decode8_kernel(const AffineParams p) {
         const uint32_t k_off0 = tl0 * RB + c * WPL * 4, k_off1 = tl1 * RB + c * WPL * 4;
         const uint32_t v_off = v_tok * RB + v_chunk_off * 16;
 
-        int s = 0;
-        uint32_t phase = 0;
-        for (int it = 0; it < ntiles && ok; ++it, s = (s + 1 == NSTAGE) ? 0 : s + 1, phase ^= (s == 0)) {
-            ok = mbar_wait(&full[s], phase);
-            if (!ok) break;
+        for (int jt = 0; jt < ntiles; ++jt, ++it) {
+            if (!ok) continue;  // a wait ran out earlier: walk on to the segment's barriers
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, 6);
+                continue;
+            }
             if (p.debug_skip & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
@@ -751,7 +771,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
             const T *kbt = (const T *)(st + 2 * CODE_TILE + SC_TILE);
             const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
             const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
-            const int t_blk = (tile_begin + it) * PK_TILE + blk * 16;
+            const int t_blk = (tile_begin + jt) * PK_TILE + blk * 16;
             if (p.debug_skip & 6) {
                 // measurement aid (results are meaningless): 2 = only the K half, 4 = only the V half
                 if (p.debug_skip & 2) {
@@ -912,13 +932,8 @@ attn_affine_decode8_kernel(const AffineParams p) {
         // a warp whose tokens were all masked reports "no maximum"
         if (m_run[0] <= M_INIT) m_run[0] = -INFINITY;
         if (m_run[1] <= M_INIT) m_run[1] = -INFINITY;
-        if (!ok && lane == 0) atomicExch(p.status, 6);
-    }
 
-    __syncthreads();
-    float *red_o = (float *)stages;
-    float *red_ml = red_o + PK_WARPS * 16 * RED_STRIDE;
-    if (warp < PK_WARPS) {
+        // ---- end of the segment ----
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 4);
@@ -931,7 +946,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
                 bsum[k][gr] += __shfl_xor_sync(0xffffffffu, bsum[k][gr], 16);
             }
         }
-        float *wo = red_o + warp * 16 * RED_STRIDE;
+        float *wo = red_o + warp * fp.red_rows * RED_STRIDE;
 #pragma unroll
         for (int mt = 0; mt < MT_O; ++mt) {
             // m-tile mt = cp * EPU + i: d-row g <-> dim (2cp)*8*EPU + EPU*g + i, d-row g+8 <-> next chunk
@@ -939,27 +954,34 @@ attn_affine_decode8_kernel(const AffineParams p) {
             const int d0 = (2 * cp) * 8 * EPU + EPU * g + i, d1 = d0 + 8 * EPU;
             const int gr = d0 / GROUP;
             const float vs = (BITS == 4 && (i & 1)) ? 1048576.f : 16777216.f;  // undo the subnormal factor
-            wo[(2 * c) * RED_STRIDE + d0] = fmaf(o_acc[mt][0], vs, bsum[0][gr]);
-            wo[(2 * c + 1) * RED_STRIDE + d0] = fmaf(o_acc[mt][1], vs, bsum[1][gr]);
-            wo[(2 * c) * RED_STRIDE + d1] = fmaf(o_acc[mt][2], vs, bsum[0][gr]);
-            wo[(2 * c + 1) * RED_STRIDE + d1] = fmaf(o_acc[mt][3], vs, bsum[1][gr]);
+            if (2 * c < R) {
+                wo[(2 * c) * RED_STRIDE + d0] = fmaf(o_acc[mt][0], vs, bsum[0][gr]);
+                wo[(2 * c) * RED_STRIDE + d1] = fmaf(o_acc[mt][2], vs, bsum[0][gr]);
+            }
+            if (2 * c + 1 < R) {
+                wo[(2 * c + 1) * RED_STRIDE + d0] = fmaf(o_acc[mt][1], vs, bsum[1][gr]);
+                wo[(2 * c + 1) * RED_STRIDE + d1] = fmaf(o_acc[mt][3], vs, bsum[1][gr]);
+            }
         }
         if (g == 0) {
-            red_ml[(warp * 16 + 2 * c) * 2 + 0] = m_run[0];
-            red_ml[(warp * 16 + 2 * c) * 2 + 1] = l_run[0];
-            red_ml[(warp * 16 + 2 * c + 1) * 2 + 0] = m_run[1];
-            red_ml[(warp * 16 + 2 * c + 1) * 2 + 1] = l_run[1];
+            if (2 * c < R) {
+                red_ml[(warp * fp.red_rows + 2 * c) * 2 + 0] = m_run[0];
+                red_ml[(warp * fp.red_rows + 2 * c) * 2 + 1] = l_run[0];
+            }
+            if (2 * c + 1 < R) {
+                red_ml[(warp * fp.red_rows + 2 * c + 1) * 2 + 0] = m_run[1];
+                red_ml[(warp * fp.red_rows + 2 * c + 1) * 2 + 1] = l_run[1];
+            }
         }
+        UnitOut u;
+        u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+        u.out = p.out; u.out_dtype = p.out_dtype;
+        u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+        u.o_signs = nullptr;
+        u.splits = 0; u.Hq = p.Hq; u.L = p.L;
+        segment_epilogue<D, PK_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
+        x += ntiles;
     }
-    __syncthreads();
-    UnitOut u;
-    u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
-    u.out = p.out; u.out_dtype = p.out_dtype;
-    u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
-    u.o_signs = nullptr;
-    u.splits = p.splits; u.Hq = p.Hq; u.L = p.L;
-    float *work = red_ml + PK_WARPS * 16 * 2;
-    unit_epilogue<D, PK_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
 }
 
 template <typename T, int D, int BITS, int GROUP, int NSTAGE>
@@ -987,24 +1009,24 @@ void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) 
 }
 
 template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB>
-void launch_affine8_typed(const AffineParams &p, int units, cudaStream_t stream) {
+void launch_affine8_typed(const AffineParams &p, int ctas, cudaStream_t stream) {
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
     constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
-    constexpr int RED_BYTES = PK_WARPS * 16 * (D + 8) * 4 + PK_WARPS * 16 * 2 * 4 + 16 * 64 * 4;
-    constexpr int BODY = NSTAGE * STAGE_BYTES > RED_BYTES ? NSTAGE * STAGE_BYTES : RED_BYTES;
-    const size_t smem = (size_t)BODY + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + 128;
-    static bool configured[64] = {false};
+    const size_t red = (size_t)PK_WARPS * p.flat.red_rows * (D + 8) * 4 + (size_t)PK_WARPS * p.flat.red_rows * 8 +
+                       (size_t)p.flat.red_rows * p.flat.nslots * 4;
+    const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + red + 128;
+    static size_t configured[64] = {0};
     const int dev = current_device();
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
         KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-        configured[dev] = true;
+        configured[dev] = smem;
     }
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>, dim3(units), dim3(PK_THREADS), smem, stream, p));
+    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>, dim3(ctas), dim3(PK_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -1067,11 +1089,23 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
             best_s = s;
         }
     }
-    if (const char *e = std::getenv("KVC_AFFINE_SPLITS")) {  // measurement aid
-        const int64_t forced = std::atoll(e);
-        if (forced >= 1 && forced <= max_s) best_s = forced;
+    // decode8: flat decomposition over one wave of resident CTAs (every CTA streams the same number
+    // of tiles); the partial slots per unit take the place of the splits
+    const int64_t work_tiles = bh * tiles;
+    int flat_resident = 3;
+    {
+        // CTAs that fit an SM by shared memory: ring + cross-warp buffers (+1 KB the driver reserves)
+        const int ns = a.k.bits == 4 ? (a.D == 128 ? 6 : 8) : (a.D == 128 ? 4 : 6);
+        const size_t stage = (size_t)2 * PK_TILE * (a.D * a.k.bits / 8) + (size_t)4 * PK_TILE * (a.D / a.k.group) * 2;
+        const size_t red = (size_t)PK_WARPS * rep * a.L * (a.D + 8) * 4 + (size_t)PK_WARPS * rep * a.L * 8 + (size_t)rep * a.L * 64 * 4;
+        const size_t per_cta = ns * stage + red + 512 + 1024;
+        flat_resident = (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / per_cta));
     }
-    const int64_t splits = best_s;
+    const int64_t flat_ctas = std::min<int64_t>((int64_t)sm_count(a.device) * flat_resident, work_tiles);
+    const int64_t flat_per = work_tiles / flat_ctas, flat_rem = work_tiles % flat_ctas;
+    const int64_t flat_slots = (tiles + flat_per - 1) / flat_per + 1;
+    if (decode8 && flat_slots > 64) return 0;
+    const int64_t splits = decode8 ? flat_slots : best_s;
     const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
     const size_t o_bytes = (size_t)qrows * splits * a.D * sizeof(float);
     const size_t ml_bytes = (size_t)qrows * splits * sizeof(float2);
@@ -1099,7 +1133,10 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     }
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    const int units = (int)(bh * splits);
+    p.flat.tiles = (int)tiles;
+    p.flat.per = (int)flat_per; p.flat.rem = (int)flat_rem;
+    p.flat.nslots = (int)flat_slots; p.flat.red_rows = rep * a.L;
+    const int units = decode8 ? (int)flat_ctas : (int)(bh * splits);
 
     const int bits = a.k.bits, group = a.k.group;
 #define KVC_AFF8(TT, DD, BB, GG, NS)                                         \

@@ -65,6 +65,7 @@ struct TurboParams {
     int32_t debug_skip;  // measurement aid: 1 = consumers release tiles without computing
     int64_t causal_offset;
     float scale_log2;
+    FlatPlan flat;  // flat tile decomposition (one wave of CTAs, segments per unit)
 };
 
 // Byte offset (inside a lane-replicated table) of the entry for pair j of a lane's word
@@ -120,20 +121,20 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
     float *qrot = (float *)(vtab + VTAB);               // [8][D]
     unsigned char *stages = (unsigned char *)(qrot + 8 * D);
     constexpr int RING = NSTAGE * STAGE_BYTES;
-    constexpr int RED_BYTES = TQ_WARPS * 16 * RED_STRIDE * 4 + TQ_WARPS * 16 * 2 * 4 + 16 * 64 * 4 + 8 * D * 4;
-    constexpr int BODY = RING > RED_BYTES ? RING : RED_BYTES;
-    uint64_t *full = (uint64_t *)(stages + ((BODY + 15) / 16) * 16);
+    const FlatPlan &fp = p.flat;
+    uint64_t *full = (uint64_t *)(stages + ((RING + 15) / 16) * 16);
     uint64_t *empty = full + NSTAGE;
     int *is_last = (int *)(empty + NSTAGE);
+    // cross-warp buffers beside the ring (the ring stays live across segments)
+    float *red_o = (float *)(is_last + 4);                               // [4][red_rows][RED_STRIDE]
+    float *red_ml = red_o + TQ_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
+    float *work = red_ml + TQ_WARPS * fp.red_rows * 2;                   // [red_rows][nslots] + [red_rows][D]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x % p.splits;
-    const int bh = blockIdx.x / p.splits;
-    const int hk = bh % p.Hkv, b = bh / p.Hkv;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;  // <= 8
-    const int tile_begin = split * p.tiles_base + min(split, p.tiles_rem);
-    const int ntiles = p.tiles_base + (split < p.tiles_rem ? 1 : 0);
+    const int tiles = fp.tiles;
+    const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -143,7 +144,7 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    // ---- lookup tables: entry j = f16x2(centroid[j & m], centroid[j >> bits]) in every bank ----
+    // ---- lookup tables, once per CTA: entry j = f16x2(centroid[j & m], centroid[j >> bits]) in every bank ----
     for (int w = tid; w < KTAB / 4; w += TQ_THREADS) {
         const int j = w >> 5;
         ((uint32_t *)ktab)[w] = pack_h2(p.kcb[j & ((1 << KB) - 1)], p.kcb[j >> KB]);
@@ -152,57 +153,76 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         const int j = w >> 5;
         ((uint32_t *)vtab)[w] = pack_h2(p.vcb[j & ((1 << VB) - 1)], p.vcb[j >> VB]);
     }
-    pdl_wait();  // the tables came from kernel parameters; everything below reads global memory
-    // ---- rotated queries: q' = H(signs * q) / sqrt(D) * scale * log2(e), rows past R are zero ----
-    for (int i = tid; i < 8 * D; i += TQ_THREADS) {
-        const int r = i / D, d = i % D;
-        float x = 0.f;
-        if (r < R) {
-            const int hq = hk * rep + r / p.L, l = r % p.L;
-            x = to_f32<T>(((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d]) * p.q_signs[d];
-        }
-        qrot[i] = x;
-    }
-    for (int half = 1; half < D; half <<= 1) {
-        __syncthreads();
-        for (int pi = tid; pi < 8 * (D / 2); pi += TQ_THREADS) {
-            const int r = pi / (D / 2), j = pi % (D / 2);
-            const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
-            const float x = qrot[r * D + i0], y = qrot[r * D + i1];
-            qrot[r * D + i0] = x + y;
-            qrot[r * D + i1] = x - y;
-        }
-    }
     __syncthreads();
+    pdl_wait();  // the tables came from kernel parameters; everything below reads global memory
 
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    float o_acc[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
     if (warp == TQ_WARPS) {
+        // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
-            const uint32_t *kp = p.kp + b * p.kp_sb + hk * p.kp_sh;
-            const uint32_t *vp = p.vp + b * p.vp_sb + hk * p.vp_sh;
-            const float *kn = p.kn + b * p.kn_sb + hk * p.kn_sh;
-            const float *vn = p.vn + b * p.vn_sb + hk * p.vn_sh;
-            for (int it = 0; it < ntiles && ok; ++it) {
-                const int s = it % NSTAGE;
-                if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
-                if (!ok) break;
-                unsigned char *st = stages + (size_t)s * STAGE_BYTES;
-                const int64_t t0 = (int64_t)(tile_begin + it) * TQ_TILE;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                bulk_load(st, kp + t0 * KW, K_TILE, &full[s]);
-                bulk_load(st + K_TILE, vp + t0 * VW, V_TILE, &full[s]);
-                bulk_load(st + K_TILE + V_TILE, kn + t0, N_TILE, &full[s]);
-                bulk_load(st + K_TILE + V_TILE + N_TILE, vn + t0, N_TILE, &full[s]);
+            int it = 0;
+            for (int64_t x = x_lo; x < x_hi && ok;) {
+                const int unit = (int)(x / tiles), tb = (int)(x % tiles);
+                const int n = (int)min((int64_t)(tiles - tb), x_hi - x);
+                const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                const uint32_t *kp = p.kp + b * p.kp_sb + hk * p.kp_sh;
+                const uint32_t *vp = p.vp + b * p.vp_sb + hk * p.vp_sh;
+                const float *kn = p.kn + b * p.kn_sb + hk * p.kn_sh;
+                const float *vn = p.vn + b * p.vn_sb + hk * p.vn_sh;
+                for (int j = 0; j < n && ok; ++j, ++it) {
+                    const int s = it % NSTAGE;
+                    if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                    if (!ok) break;
+                    unsigned char *st = stages + (size_t)s * STAGE_BYTES;
+                    const int64_t t0 = (int64_t)(tb + j) * TQ_TILE;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    bulk_load(st, kp + t0 * KW, K_TILE, &full[s]);
+                    bulk_load(st + K_TILE, vp + t0 * VW, V_TILE, &full[s]);
+                    bulk_load(st + K_TILE + V_TILE, kn + t0, N_TILE, &full[s]);
+                    bulk_load(st + K_TILE + V_TILE + N_TILE, vn + t0, N_TILE, &full[s]);
+                }
+                x += n;
             }
             if (!ok) atomicExch(p.status, 7);
         }
-    } else {
+        return;
+    }
+
+    // ---------------- consumers: one segment per unit the CTA's tile range touches ----------------
+    constexpr int CT = TQ_WARPS * 32;
+    int it = 0;
+    for (int64_t x = x_lo; x < x_hi;) {
+        const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
+        const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
+        const int hk = unit % p.Hkv, b = unit / p.Hkv;
+        // ---- rotated queries of this unit: q' = H(signs * q) / sqrt(D) * scale * log2(e), rows past R zero ----
+        for (int i = tid; i < 8 * D; i += CT) {
+            const int r = i / D, d = i % D;
+            float xq = 0.f;
+            if (r < R) {
+                const int hq = hk * rep + r / p.L, l = r % p.L;
+                xq = to_f32<T>(((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d]) * p.q_signs[d];
+            }
+            qrot[i] = xq;
+        }
+        for (int half = 1; half < D; half <<= 1) {
+            consumer_bar<TQ_WARPS>();
+            for (int pi = tid; pi < 8 * (D / 2); pi += CT) {
+                const int r = pi / (D / 2), j = pi % (D / 2);
+                const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
+                const float xa = qrot[r * D + i0], ya = qrot[r * D + i1];
+                qrot[r * D + i0] = xa + ya;
+                qrot[r * D + i1] = xa - ya;
+            }
+        }
+        consumer_bar<TQ_WARPS>();
+        float m_run[2], l_run[2] = {0.f, 0.f};
+        float o_acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
         // Q'^T fragments (B operand, column = query row g). MMA m of the K side covers, from lane
         // c, the dims 32c + 4m + {0,1} (k-slots 2c, 2c+1) and 32c + 4m + {2,3} (k-slots 2c+8, 2c+9).
         const float qf = rsqrtf((float)D) * p.scale_log2;
@@ -231,11 +251,14 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         const uint32_t lane_bits = (uint32_t)lane << 2;
         const uint32_t ktab_a = smem_u32(ktab), vtab_a = smem_u32(vtab);
 
-        int s = 0;
-        uint32_t phase = 0;
-        for (int it = 0; it < ntiles && ok; ++it, s = (s + 1 == NSTAGE) ? 0 : s + 1, phase ^= (s == 0)) {
-            ok = mbar_wait(&full[s], phase);
-            if (!ok) break;
+        for (int jt = 0; jt < ntiles; ++jt, ++it) {
+            if (!ok) continue;  // a wait ran out earlier: walk on to the segment's barriers
+            const int s = it % NSTAGE;
+            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, 8);
+                continue;
+            }
             if (p.debug_skip & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
@@ -246,7 +269,7 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
             const uint32_t *vpt = (const uint32_t *)(st + K_TILE);
             const float *knt = (const float *)(st + K_TILE + V_TILE);
             const float *vnt = (const float *)(st + K_TILE + V_TILE + N_TILE);
-            const int t_blk = (tile_begin + it) * TQ_TILE + blk * 16;
+            const int t_blk = (tile_begin + jt) * TQ_TILE + blk * 16;
 
             // ---- S^T = centroids[idx_k] . Q'^T, two accumulator chains ----
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -339,67 +362,77 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         // a warp whose tokens were all masked reports "no maximum"
         if (m_run[0] <= M_INIT) m_run[0] = -INFINITY;
         if (m_run[1] <= M_INIT) m_run[1] = -INFINITY;
-        if (!ok && lane == 0) atomicExch(p.status, 8);
-    }
 
-    __syncthreads();
-    float *red_o = (float *)stages;
-    float *red_ml = red_o + TQ_WARPS * 16 * RED_STRIDE;
-    if (warp < TQ_WARPS) {
+        // ---- end of the segment ----
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 4);
             l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 8);
             l_run[k] += __shfl_xor_sync(0xffffffffu, l_run[k], 16);
         }
-        float *wo = red_o + warp * 16 * RED_STRIDE;
+        float *wo = red_o + warp * fp.red_rows * RED_STRIDE;
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
             // accumulator rows g / g+8 of tile mt stand for lookups j = 2 mt / 2 mt + 1
             const int d0 = 32 * (g >> 1) + 2 * (2 * mt) + (g & 1), d1 = d0 + 2;
-            wo[(2 * c) * RED_STRIDE + d0] = o_acc[mt][0];
-            wo[(2 * c + 1) * RED_STRIDE + d0] = o_acc[mt][1];
-            wo[(2 * c) * RED_STRIDE + d1] = o_acc[mt][2];
-            wo[(2 * c + 1) * RED_STRIDE + d1] = o_acc[mt][3];
+            if (2 * c < R) {
+                wo[(2 * c) * RED_STRIDE + d0] = o_acc[mt][0];
+                wo[(2 * c) * RED_STRIDE + d1] = o_acc[mt][2];
+            }
+            if (2 * c + 1 < R) {
+                wo[(2 * c + 1) * RED_STRIDE + d0] = o_acc[mt][1];
+                wo[(2 * c + 1) * RED_STRIDE + d1] = o_acc[mt][3];
+            }
         }
         if (g == 0) {
-            red_ml[(warp * 16 + 2 * c) * 2 + 0] = m_run[0];
-            red_ml[(warp * 16 + 2 * c) * 2 + 1] = l_run[0];
-            red_ml[(warp * 16 + 2 * c + 1) * 2 + 0] = m_run[1];
-            red_ml[(warp * 16 + 2 * c + 1) * 2 + 1] = l_run[1];
+            if (2 * c < R) {
+                red_ml[(warp * fp.red_rows + 2 * c) * 2 + 0] = m_run[0];
+                red_ml[(warp * fp.red_rows + 2 * c) * 2 + 1] = l_run[0];
+            }
+            if (2 * c + 1 < R) {
+                red_ml[(warp * fp.red_rows + 2 * c + 1) * 2 + 0] = m_run[1];
+                red_ml[(warp * fp.red_rows + 2 * c + 1) * 2 + 1] = l_run[1];
+            }
         }
+        UnitOut u;
+        u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
+        u.out = p.out; u.out_dtype = p.out_dtype;
+        u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+        u.o_signs = p.o_signs;
+        u.splits = 0; u.Hq = p.Hq; u.L = p.L;
+        segment_epilogue<D, TQ_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
+        x += ntiles;
     }
-    __syncthreads();
-    UnitOut u;
-    u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
-    u.out = p.out; u.out_dtype = p.out_dtype;
-    u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
-    u.o_signs = p.o_signs;
-    u.splits = p.splits; u.Hq = p.Hq; u.L = p.L;
-    float *work = red_ml + TQ_WARPS * 16 * 2;
-    unit_epilogue<D, TQ_WARPS>(u, red_o, red_ml, RED_STRIDE, work, is_last, b, hk, rep, R, split, bh);
 }
 
-template <typename T, int KB, int VB, int NSTAGE>
-void launch_turbo_typed(const TurboParams &p, int units, cudaStream_t stream) {
+template <int KB, int VB, int NSTAGE>
+constexpr size_t turbo_fixed_smem() {
     constexpr int D = TQ_D;
     constexpr int KW = D * KB / 32, VW = D * VB / 32;
     constexpr int KTAB = (1 << (2 * KB)) * 128, VTAB = (1 << (2 * VB)) * 128;
     constexpr int STAGE_BYTES = TQ_TILE * (KW + VW) * 4 + 2 * TQ_TILE * 4;
-    constexpr int RED_BYTES = TQ_WARPS * 16 * (D + 8) * 4 + TQ_WARPS * 16 * 2 * 4 + 16 * 64 * 4 + 8 * D * 4;
-    constexpr int BODY = NSTAGE * STAGE_BYTES > RED_BYTES ? NSTAGE * STAGE_BYTES : RED_BYTES;
-    const size_t smem = (size_t)KTAB + VTAB + 8 * D * 4 + BODY + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + 128;
-    static bool configured[64] = {false};
+    return (size_t)KTAB + VTAB + 8 * D * 4 + (size_t)NSTAGE * STAGE_BYTES + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + 128;
+}
+
+inline size_t turbo_red_smem(const FlatPlan &f) {
+    return (size_t)TQ_WARPS * f.red_rows * (TQ_D + 8) * 4 + (size_t)TQ_WARPS * f.red_rows * 8 +
+           (size_t)f.red_rows * f.nslots * 4 + (size_t)f.red_rows * TQ_D * 4;
+}
+
+template <typename T, int KB, int VB, int NSTAGE>
+void launch_turbo_typed(const TurboParams &p, int ctas, cudaStream_t stream) {
+    const size_t smem = turbo_fixed_smem<KB, VB, NSTAGE>() + turbo_red_smem(p.flat);
+    static size_t configured[64] = {0};
     const int dev = current_device();
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
         KVC_CUDA(cudaFuncSetAttribute(attn_turbo_decode8_kernel<T, KB, VB, NSTAGE>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         KVC_CUDA(cudaFuncSetAttribute(attn_turbo_decode8_kernel<T, KB, VB, NSTAGE>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-        configured[dev] = true;
+        configured[dev] = smem;
     }
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_turbo_decode8_kernel<T, KB, VB, NSTAGE>, dim3(units), dim3(TQ_THREADS), smem, stream, p));
+    KVC_CUDA(launch_pdl(attn_turbo_decode8_kernel<T, KB, VB, NSTAGE>, dim3(ctas), dim3(TQ_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -443,21 +476,27 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     int *counters = counters_get(a.device, stream, TQ_COUNTER_BYTES);
 
     const int64_t tiles = (a.T + TQ_TILE - 1) / TQ_TILE;
-    const int slots = sm_count(a.device) * 2;
-    int64_t best_s = 1;
-    double best_cost = 1e30;
-    const int64_t max_s = std::min<int64_t>(tiles, 64);
-    for (int64_t s = 1; s <= max_s; ++s) {
-        const int64_t units = bh * s;
-        const int64_t waves = (units + slots - 1) / slots;
-        const int64_t per = (tiles + s - 1) / s;
-        const double cost = (double)waves * ((double)per + 8.0);  // 8: table build, query rotation, merge
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best_s = s;
-        }
-    }
-    const int64_t splits = best_s;
+    // Flat decomposition over one wave: CTAs resident per SM by shared memory (tables + ring +
+    // cross-warp buffers, +1 KB the driver reserves per CTA), at most 2 by the launch bounds.
+    size_t fixed = 0;
+    if (kb == 3 && vb == 4) fixed = turbo_fixed_smem<3, 4, 5>();
+    else if (kb == 4 && vb == 4) fixed = turbo_fixed_smem<4, 4, 4>();
+    else if (kb == 4 && vb == 2) fixed = turbo_fixed_smem<4, 2, 7>();
+    else if (kb == 3 && vb == 3) fixed = turbo_fixed_smem<3, 3, 7>();
+    else fixed = turbo_fixed_smem<2, 2, 10>();
+    FlatPlan plan;
+    plan.tiles = (int)tiles;
+    plan.red_rows = rep * a.L;
+    plan.nslots = 64;
+    const size_t per_cta = fixed + turbo_red_smem(plan) + 1024;
+    const int resident = (int)std::max<size_t>(1, std::min<size_t>(2, (size_t)227 * 1024 / per_cta));
+    const int64_t work_tiles = bh * tiles;
+    const int64_t ctas = std::min<int64_t>((int64_t)sm_count(a.device) * resident, work_tiles);
+    plan.per = (int)(work_tiles / ctas);
+    plan.rem = (int)(work_tiles % ctas);
+    plan.nslots = (int)((tiles + plan.per - 1) / plan.per + 1);
+    if (plan.nslots > 64) return 0;
+    const int64_t splits = plan.nslots;
     const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
     const size_t o_bytes = (size_t)qrows * splits * a.D * sizeof(float);
     const size_t ml_bytes = (size_t)qrows * splits * sizeof(float2);
@@ -490,7 +529,8 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     }
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    const int units = (int)(bh * splits);
+    p.flat = plan;
+    const int units = (int)ctas;
 
 #define KVC_TQ(TT, KK, VV, NS)                                  \
     if (kb == KK && vb == VV) {                                 \
@@ -498,14 +538,14 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
         return 1;                                               \
     }
     if (a.q_dtype == KVC_BF16) {
-        KVC_TQ(__nv_bfloat16, 3, 4, 6)
-        KVC_TQ(__nv_bfloat16, 4, 4, 5)
+        KVC_TQ(__nv_bfloat16, 3, 4, 5)
+        KVC_TQ(__nv_bfloat16, 4, 4, 4)
         KVC_TQ(__nv_bfloat16, 4, 2, 7)
         KVC_TQ(__nv_bfloat16, 3, 3, 7)
         KVC_TQ(__nv_bfloat16, 2, 2, 10)
     } else {
-        KVC_TQ(__half, 3, 4, 6)
-        KVC_TQ(__half, 4, 4, 5)
+        KVC_TQ(__half, 3, 4, 5)
+        KVC_TQ(__half, 4, 4, 4)
         KVC_TQ(__half, 4, 2, 7)
         KVC_TQ(__half, 3, 3, 7)
         KVC_TQ(__half, 2, 2, 10)
