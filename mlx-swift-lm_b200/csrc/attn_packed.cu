@@ -672,7 +672,8 @@ attn_affine_decode8_kernel(const AffineParams p) {
     }
 
     // ---------------- consumers: one segment per unit the CTA's tile range touches ----------------
-    int it = 0;
+    int st_i = 0;          // ring stage of the next tile and its phase bit, carried across segments
+    uint32_t st_ph = 0;
     for (int64_t x = x_lo; x < x_hi;) {
         const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
         const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
@@ -751,10 +752,10 @@ attn_affine_decode8_kernel(const AffineParams p) {
         const uint32_t k_off0 = tl0 * RB + c * WPL * 4, k_off1 = tl1 * RB + c * WPL * 4;
         const uint32_t v_off = v_tok * RB + v_chunk_off * 16;
 
-        for (int jt = 0; jt < ntiles; ++jt, ++it) {
+        for (int jt = 0; jt < ntiles; ++jt, st_i = (st_i + 1 == NSTAGE) ? 0 : st_i + 1, st_ph ^= (st_i == 0)) {
             if (!ok) continue;  // a wait ran out earlier: walk on to the segment's barriers
-            const int s = it % NSTAGE;
-            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            const int s = st_i;
+            ok = mbar_wait(&full[s], st_ph);
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, 6);
                 continue;

@@ -192,7 +192,8 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
 
     // ---------------- consumers: one segment per unit the CTA's tile range touches ----------------
     constexpr int CT = TQ_WARPS * 32;
-    int it = 0;
+    int st_i = 0;          // ring stage of the next tile and its phase bit, carried across segments
+    uint32_t st_ph = 0;
     for (int64_t x = x_lo; x < x_hi;) {
         const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
         const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
@@ -251,10 +252,10 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
         const uint32_t lane_bits = (uint32_t)lane << 2;
         const uint32_t ktab_a = smem_u32(ktab), vtab_a = smem_u32(vtab);
 
-        for (int jt = 0; jt < ntiles; ++jt, ++it) {
+        for (int jt = 0; jt < ntiles; ++jt, st_i = (st_i + 1 == NSTAGE) ? 0 : st_i + 1, st_ph ^= (st_i == 0)) {
             if (!ok) continue;  // a wait ran out earlier: walk on to the segment's barriers
-            const int s = it % NSTAGE;
-            ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+            const int s = st_i;
+            ok = mbar_wait(&full[s], st_ph);
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, 8);
                 continue;
