@@ -10,6 +10,7 @@ int launch_attention_general(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_affine(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
@@ -27,6 +28,8 @@ int launch_attention(const AttnArgs &a, cudaStream_t stream) {
         n = launch_attention_affine(a, stream);
         if (n > 0) return n;
         n = launch_attention_turbo(a, stream);
+        if (n > 0) return n;
+        n = launch_attention_chunk_packed(a, stream);
         if (n > 0) return n;
     }
     return launch_attention_general(a, stream);

@@ -121,3 +121,58 @@ def test_turbo_kernel_small_causal_chunk(kvc, oracle, cuda):
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), 0.09, "causal")
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, 0.09, "causal")
     assert max_abs_diff(out, ref) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,bits,group,P,L", [
+    (2, 8, 2, 4, 64, 300, 64),       # prefill chunk over a quantised prefix: 256 rows per KV head
+    (1, 28, 4, 4, 64, 2100, 6),      # verify round, Qwen2-7B layout: 7 heads x 6 positions = 42 rows
+    (1, 8, 2, 8, 64, 500, 40),       # 8-bit, 160 rows: three row blocks, the last one partial
+    (1, 4, 1, 4, 32, 4000, 5),       # group 32; one unit, long prefix: several splits + merge
+    (2, 8, 2, 8, 128, 77, 33),       # group 128
+    (1, 2, 1, 4, 128, 0, 130),       # chunk into an empty cache
+])
+def test_affine_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, bits, group, P, L):
+    """Multi-token chunks over the affine cache: dequantise-to-shared-memory tensor-core kernel."""
+    D = 128
+    g, o = kvc.QuantizedKVCache(group, bits, reserve_tokens=P + L), oracle.QuantizedKVCache(group, bits)
+    if P:
+        k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+        g.update_quantized(k.to(cuda), v.to(cuda))
+        o.update_quantized(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, dtype)
+    k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
+    kvc.launch_count(reset=True)
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
+    assert kvc.launch_count(reset=True) == 2            # quantise-append + one attention launch
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,kb,vb,P,L", [
+    (1, 64, 8, 3, 4, 2100, 6),       # verify round, Llama-3-70B layout: 8 heads x 6 positions = 48 rows
+    (2, 8, 2, 4, 4, 300, 40),        # 160 rows per KV head
+    (1, 4, 1, 3, 3, 3000, 5),        # one unit, long prefix: several splits + merge + rotation
+    (1, 8, 2, 4, 2, 130, 17),
+    (1, 4, 2, 2, 2, 64, 9),
+])
+def test_turbo_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, kb, vb, P, L):
+    """Verify rounds / chunks over the TurboQuant cache (compressed phase)."""
+    D = 128
+    kw = dict(bits=max(kb, vb), key_bits=kb, value_bits=vb)
+    g = kvc.TurboQuantKVCache(reserve_tokens=P + L, **kw)
+    o = oracle.TurboQuantKVCache(key_codebook=np.array(kvc.turbo_codebook(D, kb)[0], dtype=np.float32),
+                                 value_codebook=np.array(kvc.turbo_codebook(D, vb)[0], dtype=np.float32), **kw)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, dtype)
+    k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
+    kvc.launch_count(reset=True)
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
+    assert kvc.launch_count(reset=True) == 2            # encode-append + one attention launch
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
