@@ -43,6 +43,10 @@ WORKLOADS = {
                                        context=8192, chunk=512),
     "cfg1_quant8_f32_llama32_1b": dict(kind="quantized", bits=8, group=64, layers=16, Hq=32, Hkv=8, D=64, B=1,
                                        dtype="f32", context=1024, chunk=1024),
+    # Gemma-3-1B: every sixth layer global (KVCacheSimple, step 1024), the others sliding-window
+    # RotatingKVCache(maxSize 512, keep 0); the rings have wrapped before the first timed step
+    "cfg3_rotating_bf16_gemma3_1b": dict(kind="gemma3", layers=26, Hq=4, Hkv=1, D=256, B=4, dtype="bf16",
+                                         context=2048, chunk=512, window=512),
     "cfg4_quant4_bf16_qwen2_7b": dict(kind="quantized", bits=4, group=64, layers=28, Hq=28, Hkv=4, D=128, B=32,
                                       dtype="bf16", context=17408, chunk=512),
     "cfg5_turbo_k3v4_llama3_70b": dict(kind="turbo", key_bits=3, value_bits=4, layers=80, Hq=64, Hkv=8, D=128,
@@ -60,7 +64,7 @@ def bytes_per_token_head(w) -> float:
     """Algorithmic bytes of K plus V for one cached token of one KV head."""
     D = w["D"]
     es = 4 if w["dtype"] == "f32" else 2
-    if w["kind"] in ("simple", "rotating"):
+    if w["kind"] in ("simple", "rotating", "gemma3"):
         return 2 * D * es
     if w["kind"] == "quantized":
         per = D * w["bits"] / 8 + 2 * (D // w["group"]) * es
@@ -167,6 +171,11 @@ def cpu_decode_step_time(w, budget_s: float, steps: int = 1, warmup: int = 0):
 
     orc.build()
     B, Hq, Hkv, D, T0 = w["B"], w["Hq"], w["Hkv"], w["D"], w["context"]
+    if w["kind"] == "gemma3":
+        # per-layer average of what a step reads: 22 wrapped 512-token rings and 4 full-context layers
+        n_glob = len([i for i in range(w["layers"]) if i % 6 == 5])
+        T0 = (n_glob * w["context"] + (w["layers"] - n_glob) * min(w["window"], w["context"])) // w["layers"]
+        w = dict(w, kind="simple")
     rng = np.random.default_rng(0)
     es_dtype = np.float32 if w["dtype"] == "f32" else np.uint16
 
@@ -267,7 +276,11 @@ def run_reference(args, w, rank, world):
 # GPU arm
 # ---------------------------------------------------------------------------
 
-def make_cache(kvc, w, reserve):
+def make_cache(kvc, w, reserve, layer=0):
+    if w["kind"] == "gemma3":
+        if layer % 6 == 5:
+            return kvc.KVCacheSimple(step=1024, reserve_tokens=reserve)
+        return kvc.RotatingKVCache(max_size=w["window"], keep=0)
     if w["kind"] == "simple":
         return kvc.KVCacheSimple(step=256, reserve_tokens=reserve)
     if w["kind"] == "quantized":
@@ -283,7 +296,7 @@ def fill_cache(kvc, cache, w, Bl, Hl, chunk_k, chunk_v):
     while remaining > 0:
         n = min(remaining, chunk_k.shape[2])
         k, v = chunk_k[:, :, :n], chunk_v[:, :, :n]
-        if w["kind"] == "simple":
+        if w["kind"] in ("simple", "gemma3"):
             cache.update(k, v)
         elif w["kind"] == "quantized":
             cache.update_quantized(k, v)
@@ -318,7 +331,7 @@ def run_ours(args, w, rank, world, local_rank):
     chunk = min(w["chunk"], w["context"])
     chunk_k = torch.randn((Bl, Hkvl, chunk, D), generator=g).to(dtype).to(dev)
     chunk_v = torch.randn((Bl, Hkvl, chunk, D), generator=g).to(dtype).to(dev)
-    caches = [make_cache(kvc, w, reserve) for _ in range(Lyr)]
+    caches = [make_cache(kvc, w, reserve, i) for i in range(Lyr)]
     for c in caches:
         fill_cache(kvc, c, w, Bl, Hkvl, chunk_k, chunk_v)
     torch.cuda.synchronize()
@@ -392,6 +405,9 @@ def run_ours(args, w, rank, world, local_rank):
     kvc.timing_enable(False)
     ctx_mid = ctx_r0 + (rsteps + 1) / 2
     es = 4 if w["dtype"] == "f32" else 2
+    if w["kind"] == "gemma3":
+        n_glob = len([i for i in range(Lyr) if i % 6 == 5])
+        ctx_mid = (n_glob * ctx_mid + (Lyr - n_glob) * min(w["window"], ctx_mid)) / Lyr   # average over the layers
     alg_bytes = Bl * Hkvl * ctx_mid * bytes_per_token_head(w) + 2 * Bl * Hql * D * es
     k_avg_ms = k_ms / max(k_n, 1)
     achieved = alg_bytes / (k_avg_ms * 1e-3) / 1e9 if k_n else None
