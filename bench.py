@@ -49,6 +49,11 @@ WORKLOADS = {
                                          context=2048, chunk=512, window=512),
     "cfg4_quant4_bf16_qwen2_7b": dict(kind="quantized", bits=4, group=64, layers=28, Hq=28, Hkv=4, D=128, B=32,
                                       dtype="bf16", context=17408, chunk=512),
+    # the same shape held the reference's way: 32 independent sequences (one cache per sequence and
+    # layer), lengths ~U[2048, 32768] from a seed, one var-len call per layer
+    "cfg4_ragged_quant4_bf16_qwen2_7b": dict(kind="quantized", ragged=True, bits=4, group=64, layers=28, Hq=28, Hkv=4,
+                                             D=128, B=32, dtype="bf16", context=17408, chunk=512,
+                                             min_len=2048, max_len=32768, seed=4),
     "cfg5_turbo_k3v4_llama3_70b": dict(kind="turbo", key_bits=3, value_bits=4, layers=80, Hq=64, Hkv=8, D=128,
                                        B=16, dtype="bf16", context=32768, chunk=512),
 }
@@ -56,6 +61,7 @@ WORKLOADS = {
 # (per-layer working set 269 MB > L2, 0.6 GB on the device).
 WORKLOADS["cfg2_profile_2layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=2)
 WORKLOADS["cfg4_profile_2layers"] = dict(WORKLOADS["cfg4_quant4_bf16_qwen2_7b"], layers=2)
+WORKLOADS["cfg4_ragged_profile_2layers"] = dict(WORKLOADS["cfg4_ragged_quant4_bf16_qwen2_7b"], layers=2)
 WORKLOADS["cfg5_profile_2layers"] = dict(WORKLOADS["cfg5_turbo_k3v4_llama3_70b"], layers=2)
 DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
 
@@ -305,9 +311,142 @@ def fill_cache(kvc, cache, w, Bl, Hl, chunk_k, chunk_v):
         remaining -= n
 
 
+def run_ragged(args, w, rank, world, local_rank):
+    """cfg4 the reference's way: every sequence has its own cache per layer (its own offset); one
+    kvc_attention_varlen call per layer appends and attends all sequences (two launches)."""
+    import numpy as np
+    import torch
+    import kvcache_b200 as kvc
+
+    assert world == 1, "the ragged workload is a single-GPU parity / measurement case"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dtype = torch_dtype(w["dtype"])
+    n, Hq, Hkv, D, Lyr = w["B"], w["Hq"], w["Hkv"], w["D"], w["layers"]
+    rng = np.random.default_rng(w["seed"])
+    lengths = [int(x) for x in rng.integers(w["min_len"], w["max_len"] + 1, size=n)]
+    steps, warmup = args.steps, args.warmup
+    total_steps = warmup + steps * 3 + 64
+    g = torch.Generator(device="cpu").manual_seed(99)
+    chunk_k = torch.randn((1, Hkv, w["chunk"], D), generator=g).to(dtype).to(dev)
+    chunk_v = torch.randn((1, Hkv, w["chunk"], D), generator=g).to(dtype).to(dev)
+    layers = []
+    for _ in range(Lyr):
+        caches = []
+        for t in lengths:
+            c = kvc.QuantizedKVCache(w["group"], w["bits"], reserve_tokens=t + total_steps + 8)
+            left = t
+            while left > 0:
+                m = min(left, w["chunk"])
+                c.update_quantized(chunk_k[:, :, :m], chunk_v[:, :, :m])
+                left -= m
+            caches.append(c)
+        layers.append(caches)
+    torch.cuda.synchronize()
+    scale = D ** -0.5
+    # per layer: stacked device tensors, sequence i uses row i
+    q_all = [torch.randn((n, Hq, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    k_all = [torch.randn((n, Hkv, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    v_all = [torch.randn((n, Hkv, 1, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    o_all = [torch.empty((n, Hq, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+    plans = [kvc.DecodeStep(layers[l], [q_all[l][i:i + 1] for i in range(n)], [k_all[l][i:i + 1] for i in range(n)],
+                            [v_all[l][i:i + 1] for i in range(n)], [o_all[l][i:i + 1] for i in range(n)], scale)
+             for l in range(Lyr)]
+
+    def one_step():
+        for pl in plans:
+            pl.run_varlen()
+
+    for _ in range(warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    torch.cuda.synchronize()
+    sum_t0 = sum(c.offset for c in layers[0])
+    kvc.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    w1 = time.perf_counter()
+    launches = kvc.launch_count()
+    ms_total = e0.elapsed_time(e1)
+    time.sleep(0.15)
+    sampler.stop()
+    clocks = sampler.summary(w0, w1)
+
+    kvc.timing_enable(True)
+    kvc.timing_read(reset=True)
+    rsteps = min(steps, 8)
+    sum_r0 = sum(c.offset for c in layers[0])
+    for _ in range(rsteps):
+        one_step()
+    torch.cuda.synchronize()
+    k_ms, k_n = kvc.timing_read(reset=True)
+    kvc.timing_enable(False)
+    alg_bytes = Hkv * (sum_r0 + n * (rsteps + 1) / 2) * bytes_per_token_head(w) + 2 * n * Hq * D * 2
+    k_avg_ms = k_ms / max(k_n, 1)
+    peak, peak_src = 6545.0, "fallback 6545 GB/s (MEASURED_PEAKS.json absent)"
+    mp = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(mp):
+        try:
+            peak = float(json.load(open(mp))["hbm_gbs"])
+            peak_src = "MEASURED_PEAKS.json hbm_gbs (measured copy)"
+        except Exception:
+            pass
+    achieved = alg_bytes / (k_avg_ms * 1e-3) / 1e9 if k_n else None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "kernel": "var-len attention (dominant)", "launch_ms": k_avg_ms, "launches_timed": k_n,
+                "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_src}
+
+    # end to end: pinned host q/k/v per layer -> device, var-len call, outputs back to the host
+    hq = [t.cpu().pin_memory() for t in q_all]
+    hk = [t.cpu().pin_memory() for t in k_all]
+    hv = [t.cpu().pin_memory() for t in v_all]
+    ho = [torch.empty((n, Hq, 1, D), dtype=dtype).pin_memory() for _ in range(Lyr)]
+
+    def e2e_step():
+        for l in range(Lyr):
+            q_all[l].copy_(hq[l], non_blocking=True)
+            k_all[l].copy_(hk[l], non_blocking=True)
+            v_all[l].copy_(hv[l], non_blocking=True)
+            plans[l].run_varlen()
+            ho[l].copy_(o_all[l], non_blocking=True)
+        torch.cuda.synchronize()
+        return float(ho[-1][0, 0, 0, 0])
+
+    for _ in range(min(warmup, 3)):
+        e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+    es = 2
+    e2e = {"value": n * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": Lyr * n * (Hq + 2 * Hkv) * D * es,
+           "d2h_bytes_per_step": Lyr * n * Hq * D * es,
+           "note": "per layer: pinned host q/k/v -> device, kvc_attention_varlen, outputs -> host; one sync per step"}
+    line = {"metric": METRIC, "value": n * steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": args.workload, "layers": Lyr, "Hq": Hq, "Hkv": Hkv, "D": D, "B": n,
+                       "sequence_lengths": {"min": min(lengths), "max": max(lengths), "sum": sum_t0},
+                       "parallelism": "single; 32 independent caches per layer, one var-len call per layer",
+                       "l2": f"inputs larger than L2 (per-layer working set {Hkv * sum_t0 * bytes_per_token_head(w) / 1e6:.0f} MB)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": None}
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch
     import kvcache_b200 as kvc
+
+    if w.get("ragged"):
+        return run_ragged(args, w, rank, world, local_rank)
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (the library has no CPU fallback)"
     dev = torch.device("cuda", local_rank)

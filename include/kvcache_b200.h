@@ -387,6 +387,17 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev,
                             const float *boundaries_host, int32_t bits,
                             const kvc_tensor *packed, const kvc_tensor *norms, void *stream);
 
+/* attentionWithCacheUpdate for `count` INDEPENDENT caches in one call: cache i appends keys[i] /
+ * values[i] (one new token, [1, Hkv, 1, D]) and attends queries[i] ([1, Hq, 1, D]) over its own
+ * length into outs[i]. This is a ragged decode batch the way the reference holds it (one cache
+ * object per sequence, `BaseKVCache.offset` per cache, KVCache.swift:185; AttentionUtils.swift:37-95
+ * called once per sequence), executed as ONE quantise-append launch and ONE attention launch when
+ * all caches are QuantizedKVCache of one layout (up to 32 per launch); any other mix is executed
+ * cache by cache with identical results. */
+kvc_status kvc_attention_varlen(kvc_cache *const *caches, int32_t count, const kvc_tensor *queries,
+                                const kvc_tensor *keys, const kvc_tensor *values, float scale,
+                                const kvc_tensor *outs, void *stream);
+
 /* Compressed-domain append without attention: compresses a raw prefix if the
  * cache still holds one, then encodes keys/values [B, H, S, D] and appends them
  * (the cache-side half of compressedAttention, TurboQuantKVCache.swift:1176-1200:

@@ -299,13 +299,18 @@ __device__ __forceinline__ void consumer_bar() {
 // o_signs is set). `work` holds red_rows * nslots floats, plus red_rows * D when o_signs is set.
 template <int D, int NW>
 __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const float *red_o, const float *red_ml,
-                                 int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R) {
+                                 int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R,
+                                 int64_t x_unit = -1, int unit_tiles = 0) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int NT = NW * 32;
     consumer_bar<NW>();
-    const int64_t x_unit = (int64_t)unit * f.tiles;
+    // the unit's flat tile range: uniform units unless the caller passes a var-len range
+    if (x_unit < 0) {
+        x_unit = (int64_t)unit * f.tiles;
+        unit_tiles = f.tiles;
+    }
     const int first_cta = flat_cta_of(f, x_unit);
-    const int expected = flat_cta_of(f, x_unit + f.tiles - 1) - first_cta + 1;
+    const int expected = flat_cta_of(f, x_unit + unit_tiles - 1) - first_cta + 1;
     const int slot = (int)blockIdx.x - first_cta;
     const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L;
     for (int i = tid; i < R * D; i += NT) {

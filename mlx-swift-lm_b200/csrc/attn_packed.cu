@@ -61,6 +61,22 @@ struct AffineParams {
     FlatPlan flat;  // decode8 kernel: flat tile decomposition
 };
 
+// One decode step for a list of independent caches (one sequence each, its own length) in one
+// launch: units are (sequence, KV head), sequence i has tiles[i] tiles per head and its units
+// start at flat tile Hkv * tile_prefix[i].
+struct VarlenAttnSeq {
+    const void *q;
+    void *out;
+    const uint32_t *kc, *vc;
+    const void *ks, *kb, *vs, *vb;
+    int64_t c_sh, g_sh;  // head strides (words / elements) of this cache's arrays
+    int32_t T, tile_prefix;
+};
+struct VarlenAttnTable {
+    int32_t n;
+    VarlenAttnSeq seq[KVC_VARLEN_MAX];
+};
+
 __device__ __forceinline__ uint32_t hsub2_1024(uint32_t x) {
     uint32_t r;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0x64006400u));
@@ -581,9 +597,33 @@ __device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&dst)[
     }
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB>
+// Flat tile x -> the unit (batch or sequence `b`, KV head `hk`) it belongs to, the tile index inside
+// the unit and the unit's tile count.
+template <bool VARLEN>
+__device__ __forceinline__ void resolve_unit(const AffineParams &p, const VarlenAttnTable &vt, int64_t x, int tiles,
+                                             int &unit, int &tile, int &utiles, int &hk, int &b) {
+    if (!VARLEN) {
+        unit = (int)(x / tiles);
+        tile = (int)(x % tiles);
+        utiles = tiles;
+        hk = unit % p.Hkv;
+        b = unit / p.Hkv;
+        return;
+    }
+    int i = 0;
+    for (int step = 16; step >= 1; step >>= 1)   // largest i with Hkv * tile_prefix[i] <= x
+        if (i + step < vt.n && (int64_t)p.Hkv * vt.seq[i + step].tile_prefix <= x) i += step;
+    const int64_t base = (int64_t)p.Hkv * vt.seq[i].tile_prefix;
+    utiles = (vt.seq[i].T + PK_TILE - 1) / PK_TILE;
+    hk = (int)((x - base) / utiles);
+    tile = (int)((x - base) % utiles);
+    b = i;
+    unit = i * p.Hkv + hk;
+}
+
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN>
 __global__ void __launch_bounds__(PK_THREADS, MINB)
-attn_affine_decode8_kernel(const AffineParams p) {
+attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenAttnTable vt) {
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
     constexpr int WPR = RB / 4;
@@ -641,15 +681,24 @@ attn_affine_decode8_kernel(const AffineParams p) {
         if (lane == 0) {
             int it = 0;
             for (int64_t x = x_lo; x < x_hi && ok;) {
-                const int unit = (int)(x / tiles), tb = (int)(x % tiles);
-                const int n = (int)min((int64_t)(tiles - tb), x_hi - x);
-                const int hk = unit % p.Hkv, b = unit / p.Hkv;
-                const uint32_t *kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
-                const uint32_t *vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
-                const T *ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
-                const T *kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
-                const T *vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
-                const T *vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
+                int unit, tb, utiles, hk, b;
+                resolve_unit<VARLEN>(p, vt, x, tiles, unit, tb, utiles, hk, b);
+                const int n = (int)min((int64_t)(utiles - tb), x_hi - x);
+                const uint32_t *kc, *vc;
+                const T *ks, *kb, *vs, *vb;
+                if (VARLEN) {
+                    const VarlenAttnSeq &sq = vt.seq[b];
+                    kc = sq.kc + hk * sq.c_sh; vc = sq.vc + hk * sq.c_sh;
+                    ks = (const T *)sq.ks + hk * sq.g_sh; kb = (const T *)sq.kb + hk * sq.g_sh;
+                    vs = (const T *)sq.vs + hk * sq.g_sh; vb = (const T *)sq.vb + hk * sq.g_sh;
+                } else {
+                    kc = p.kc + b * p.kc_sb + hk * p.kc_sh;
+                    vc = p.vc + b * p.vc_sb + hk * p.vc_sh;
+                    ks = (const T *)p.ks + b * p.kg_sb + hk * p.kg_sh;
+                    kb = (const T *)p.kb + b * p.kg_sb + hk * p.kg_sh;
+                    vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
+                    vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
+                }
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % NSTAGE;
                     if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
@@ -675,9 +724,10 @@ attn_affine_decode8_kernel(const AffineParams p) {
     int st_i = 0;          // ring stage of the next tile and its phase bit, carried across segments
     uint32_t st_ph = 0;
     for (int64_t x = x_lo; x < x_hi;) {
-        const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
-        const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
-        const int hk = unit % p.Hkv, b = unit / p.Hkv;
+        int unit, tile_begin, utiles, hk, b;
+        resolve_unit<VARLEN>(p, vt, x, tiles, unit, tile_begin, utiles, hk, b);
+        const int ntiles = (int)min((int64_t)(utiles - tile_begin), x_hi - x);
+        const int64_t T_seq = VARLEN ? (int64_t)vt.seq[b].T : p.T;   // tokens of this unit's sequence
         // per-lane state for query rows 2c and 2c+1
         float m_run[2], l_run[2] = {0.f, 0.f};
         float bsum[2][G];
@@ -707,7 +757,8 @@ attn_affine_decode8_kernel(const AffineParams p) {
                 float x[4] = {0.f, 0.f, 0.f, 0.f};
                 if (g < R) {
                     const int hq = hk * rep + g / p.L, l = g % p.L;
-                    const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
+                    const T *qp = VARLEN ? (const T *)vt.seq[b].q + hq * p.q_sh + l * p.q_sl
+                                         : (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]]) * p.scale_log2));
@@ -732,7 +783,7 @@ attn_affine_decode8_kernel(const AffineParams p) {
         // Last visible token per row. Rows past R hold zero queries and are never written
         // out; they take the limit of a real row so that they do not force the mask path.
         int row_limit[2];
-        const int t_last = (int)(p.T - 1);
+        const int t_last = (int)(T_seq - 1);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int r = 2 * c + k;
@@ -976,11 +1027,14 @@ attn_affine_decode8_kernel(const AffineParams p) {
         }
         UnitOut u;
         u.o_part = p.o_part; u.ml_part = p.ml_part; u.counters = p.counters;
-        u.out = p.out; u.out_dtype = p.out_dtype;
-        u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
+        u.out = VARLEN ? vt.seq[b].out : p.out;
+        u.out_dtype = p.out_dtype;
+        u.o_sb = VARLEN ? 0 : p.o_sb;   // var-len: `b` is the sequence, every sequence has its own output
+        u.o_sh = p.o_sh; u.o_sl = p.o_sl;
         u.o_signs = nullptr;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
-        segment_epilogue<D, PK_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
+        segment_epilogue<D, PK_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R,
+                                      x - tile_begin, utiles);
         x += ntiles;
     }
 }
@@ -1009,8 +1063,8 @@ void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) 
     ++g_launch_count;
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB>
-void launch_affine8_typed(const AffineParams &p, int ctas, cudaStream_t stream) {
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN>
+void launch_affine8_typed(const AffineParams &p, const VarlenAttnTable &vt, int ctas, cudaStream_t stream) {
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
     constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
@@ -1020,14 +1074,15 @@ void launch_affine8_typed(const AffineParams &p, int ctas, cudaStream_t stream) 
     static size_t configured[64] = {0};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, 100));
         configured[dev] = smem;
     }
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB>, dim3(ctas), dim3(PK_THREADS), smem, stream, p));
+    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>, dim3(ctas), dim3(PK_THREADS),
+                        smem, stream, p, vt));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -1049,6 +1104,104 @@ bool affine_source_fits(const KVSource &s, int D, int64_t T) {
 }
 
 }  // namespace
+
+namespace {
+const VarlenAttnTable kNoVarlen = {};
+
+int affine_resident_ctas(int D, int bits, int group, int rows) {
+    // CTAs that fit an SM by shared memory: ring + cross-warp buffers (+1 KB the driver reserves)
+    const int ns = bits == 4 ? (D == 128 ? 6 : 8) : (D == 128 ? 4 : 6);
+    const size_t stage = (size_t)2 * PK_TILE * (D * bits / 8) + (size_t)4 * PK_TILE * (D / group) * 2;
+    const size_t red = (size_t)PK_WARPS * rows * (D + 8) * 4 + (size_t)PK_WARPS * rows * 8 + (size_t)rows * 64 * 4;
+    const size_t per_cta = ns * stage + red + 512 + 1024;
+    return (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / per_cta));
+}
+}  // namespace
+
+// One decode step over n independent affine caches (B = 1, L = 1 each, same head layout and
+// quantisation) in one launch. Returns launches made, 0 when the calls do not fit.
+int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t stream) {
+    if (n < 1 || n > KVC_VARLEN_MAX) return 0;
+    const AttnArgs &a0 = args[0];
+    if (a0.q_dtype != KVC_BF16 && a0.q_dtype != KVC_F16) return 0;
+    if (a0.D != 64 && a0.D != 128) return 0;
+    if (a0.Hkv <= 0 || a0.Hq % a0.Hkv) return 0;
+    const int rep = a0.Hq / a0.Hkv;
+    if (rep > 8 || (2 * 8 * (16 / std::max(a0.k.bits, 1))) > a0.k.group) return 0;
+    VarlenAttnTable vt = {};
+    vt.n = n;
+    int64_t prefix = 0, max_tiles = 0;
+    for (int i = 0; i < n; ++i) {
+        const AttnArgs &a = args[i];
+        if (a.B != 1 || a.L != 1 || a.mask.mode != KVC_MASK_NONE || a.q_signs || a.o_signs || a.q_calib) return 0;
+        if (a.q_dtype != a0.q_dtype || a.D != a0.D || a.Hq != a0.Hq || a.Hkv != a0.Hkv || a.scale != a0.scale) return 0;
+        if (a.q_sh != a0.q_sh || a.q_sl != a0.q_sl || a.o_sh != a0.o_sh || a.o_sl != a0.o_sl) return 0;
+        if (a.k.kind != SRC_AFFINE || a.v.kind != SRC_AFFINE) return 0;
+        if (a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
+        if (a.k.bits != a0.k.bits || a.v.bits != a0.k.bits || a.k.group != a0.k.group || a.v.group != a0.k.group) return 0;
+        if (a.k.bits != 4 && a.k.bits != 8) return 0;
+        if (a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+        if (!affine_source_fits(a.k, a.D, a.T) || !affine_source_fits(a.v, a.D, a.T)) return 0;
+        if (a.k.sh != a.v.sh || a.k.gsh != a.v.gsh) return 0;
+        if (((uintptr_t)a.q & 1)) return 0;
+        VarlenAttnSeq &sq = vt.seq[i];
+        sq.q = a.q; sq.out = a.out;
+        sq.kc = (const uint32_t *)a.k.data; sq.vc = (const uint32_t *)a.v.data;
+        sq.ks = a.k.scales; sq.kb = a.k.biases; sq.vs = a.v.scales; sq.vb = a.v.biases;
+        sq.c_sh = a.k.sh; sq.g_sh = a.k.gsh;
+        sq.T = (int32_t)a.T;
+        sq.tile_prefix = (int32_t)prefix;
+        const int64_t tl = (a.T + PK_TILE - 1) / PK_TILE;
+        prefix += tl;
+        max_tiles = std::max(max_tiles, tl);
+    }
+    if (a0.D / a0.k.group > 4 || (a0.k.group * a0.k.bits) / 32 < 4) return 0;
+    const int64_t units = (int64_t)n * a0.Hkv;
+    if (units * (int64_t)sizeof(int) > PK_COUNTER_BYTES) return 0;
+    int *status = device_status_word(a0.device);
+    if (!status) return 0;
+    int *counters = counters_get(a0.device, stream, PK_COUNTER_BYTES);
+
+    const int64_t work_tiles = prefix * a0.Hkv;
+    const int resident = affine_resident_ctas(a0.D, a0.k.bits, a0.k.group, rep);
+    const int64_t ctas = std::min<int64_t>((int64_t)sm_count(a0.device) * resident, work_tiles);
+    AffineParams p = {};
+    p.flat.tiles = (int)max_tiles;
+    p.flat.per = (int)(work_tiles / ctas);
+    p.flat.rem = (int)(work_tiles % ctas);
+    p.flat.nslots = (int)((max_tiles + p.flat.per - 1) / p.flat.per + 1);
+    p.flat.red_rows = rep;
+    if (p.flat.nslots > 64) return 0;
+    const int64_t qrows = (int64_t)n * a0.Hq;
+    const size_t o_bytes = (size_t)qrows * p.flat.nslots * a0.D * sizeof(float);
+    const size_t ml_bytes = (size_t)qrows * p.flat.nslots * sizeof(float2);
+    char *scratch = (char *)scratch_get(a0.device, o_bytes + ml_bytes + 256, stream);
+    p.out_dtype = a0.q_dtype;
+    p.q_sh = a0.q_sh; p.q_sl = a0.q_sl; p.o_sh = a0.o_sh; p.o_sl = a0.o_sl;
+    p.o_part = (float *)scratch;
+    p.ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
+    p.counters = counters; p.status = status;
+    p.B = n; p.Hq = a0.Hq; p.Hkv = a0.Hkv; p.L = 1; p.T = 0;
+    p.splits = p.flat.nslots;
+    p.causal = 0;
+    p.causal_offset = 0;
+    p.scale_log2 = a0.scale * 1.4426950408889634f;
+    const int bits = a0.k.bits, group = a0.k.group;
+#define KVC_AFFV(TT, DD, BB, GG, NS)                                                        \
+    if (a0.D == DD && bits == BB && group == GG) {                                           \
+        launch_affine8_typed<TT, DD, BB, GG, NS, 3, true>(p, vt, (int)ctas, stream);         \
+        return 1;                                                                            \
+    }
+    if (a0.q_dtype == KVC_BF16) {
+        KVC_AFFV(__nv_bfloat16, 128, 4, 64, 6)
+        KVC_AFFV(__nv_bfloat16, 128, 8, 64, 4)
+    } else {
+        KVC_AFFV(__half, 128, 4, 64, 6)
+        KVC_AFFV(__half, 128, 8, 64, 4)
+    }
+#undef KVC_AFFV
+    return 0;
+}
 
 int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
@@ -1093,15 +1246,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     // decode8: flat decomposition over one wave of resident CTAs (every CTA streams the same number
     // of tiles); the partial slots per unit take the place of the splits
     const int64_t work_tiles = bh * tiles;
-    int flat_resident = 3;
-    {
-        // CTAs that fit an SM by shared memory: ring + cross-warp buffers (+1 KB the driver reserves)
-        const int ns = a.k.bits == 4 ? (a.D == 128 ? 6 : 8) : (a.D == 128 ? 4 : 6);
-        const size_t stage = (size_t)2 * PK_TILE * (a.D * a.k.bits / 8) + (size_t)4 * PK_TILE * (a.D / a.k.group) * 2;
-        const size_t red = (size_t)PK_WARPS * rep * a.L * (a.D + 8) * 4 + (size_t)PK_WARPS * rep * a.L * 8 + (size_t)rep * a.L * 64 * 4;
-        const size_t per_cta = ns * stage + red + 512 + 1024;
-        flat_resident = (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / per_cta));
-    }
+    const int flat_resident = affine_resident_ctas(a.D, a.k.bits, a.k.group, rep * a.L);
     const int64_t flat_ctas = std::min<int64_t>((int64_t)sm_count(a.device) * flat_resident, work_tiles);
     const int64_t flat_per = work_tiles / flat_ctas, flat_rem = work_tiles % flat_ctas;
     const int64_t flat_slots = (tiles + flat_per - 1) / flat_per + 1;
@@ -1142,7 +1287,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     const int bits = a.k.bits, group = a.k.group;
 #define KVC_AFF8(TT, DD, BB, GG, NS)                                         \
     if (a.D == DD && bits == BB && group == GG) {                            \
-        launch_affine8_typed<TT, DD, BB, GG, NS, 3>(p, units, stream);         \
+        launch_affine8_typed<TT, DD, BB, GG, NS, 3, false>(p, kNoVarlen, units, stream); \
         return 1;                                                            \
     }
     if (decode8) {

@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <vector>
 
 namespace kvc {
 
@@ -407,7 +408,7 @@ static void quant_triple_alloc(Array4 &q, Array4 &sc, Array4 &bi, int64_t B, int
 }
 
 void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
-                            kvc_tensor out_k[3], kvc_tensor out_v[3]) {
+                            kvc_tensor out_k[3], kvc_tensor out_v[3], bool defer_quantize) {
     KVC_REQUIRE(c->cfg.kind == KVC_KIND_QUANTIZED, "updateQuantized needs a QuantizedKVCache");
     require4(k, "keys");
     require4(v, "values");
@@ -435,7 +436,7 @@ void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor 
                     "updateQuantized: new keys/values do not match the cached shape or dtype");
         for (Array4 *a : {&c->kq, &c->ks, &c->kb, &c->vq, &c->vs, &c->vb}) a->ensure(prev + S, prev, step, s);
     }
-    if (S > 0) {
+    if (S > 0 && !defer_quantize) {
         QuantAppendArgs qa = quant_args(k, c->kq, c->ks, c->kb, c->group_size, c->bits, prev);
         QuantAppendArgs qv = quant_args(v, c->vq, c->vs, c->vb, c->group_size, c->bits, prev);
         launch_affine_quantize2(qa, &qv, s);
@@ -759,6 +760,79 @@ void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, con
             launch_attention(a, s);
             return;
         }
+    }
+}
+
+int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t stream);
+
+void cache_attention_varlen(kvc_cache *const *caches, int n, const kvc_tensor *q, const kvc_tensor *k,
+                            const kvc_tensor *v, float scale, const kvc_tensor *outs, cudaStream_t s) {
+    auto one_by_one = [&](int from, int to) {
+        for (int i = from; i < to; ++i) cache_attention(caches[i], q[i], k[i], v[i], scale, KVC_MASK_NONE, nullptr, outs[i], s);
+    };
+    auto row_contiguous = [](const kvc_tensor &t) {
+        return t.ndim == 4 && t.stride[3] == 1 && t.stride[1] == t.shape[3] * t.shape[2];
+    };
+    for (int from = 0; from < n; from += KVC_VARLEN_MAX) {
+        const int to = std::min(n, from + KVC_VARLEN_MAX), m = to - from;
+        bool fits = m > 1;
+        for (int i = from; i < to && fits; ++i) {
+            const kvc_cache *c = caches[i];
+            fits = c && c->cfg.kind == KVC_KIND_QUANTIZED && !c->open_round && c->device == caches[from]->device &&
+                   c->bits == caches[from]->bits && q[i].ndim == 4 && row_contiguous(k[i]) && row_contiguous(v[i]) &&
+                   k[i].shape[0] == 1 && k[i].shape[2] == 1 && q[i].shape[0] == 1 && q[i].shape[2] == 1 &&
+                   k[i].shape[1] == k[from].shape[1] && k[i].shape[3] == k[from].shape[3] &&
+                   v[i].shape[3] == k[from].shape[3] && k[i].dtype == k[from].dtype && q[i].dtype == k[i].dtype &&
+                   k[i].stride[1] == k[from].stride[1] && v[i].stride[1] == k[from].stride[1];
+        }
+        if (!fits) {
+            one_by_one(from, to);
+            continue;
+        }
+        // bookkeeping + growth per cache (no launch), then ONE quantise-append launch for all of them
+        VarlenQuantArgs qa = {};
+        qa.n = m;
+        qa.H = (int)k[from].shape[1];
+        qa.D = (int)k[from].shape[3];
+        qa.dtype = k[from].dtype;
+        qa.src_sh = k[from].stride[1];
+        std::vector<AttnArgs> args((size_t)m);
+        bool same_group = true;
+        for (int i = from; i < to; ++i) {
+            kvc_cache *c = caches[i];
+            const int64_t prev = c->offset;
+            kvc_tensor qk[3], qv[3];
+            cache_update_quantized(c, k[i], v[i], s, qk, qv, /*defer_quantize=*/true);
+            same_group = same_group && c->group_size == caches[from]->group_size;
+            VarlenQuantSeq &sq = qa.seq[i - from];
+            sq.ksrc = k[i].data; sq.vsrc = v[i].data;
+            sq.kcodes = (uint32_t *)c->kq.ptr + prev * c->kq.st();
+            sq.vcodes = (uint32_t *)c->vq.ptr + prev * c->vq.st();
+            const size_t es = dtype_size(c->ks.dtype);
+            sq.kscales = (char *)c->ks.ptr + prev * c->ks.st() * es;
+            sq.kbiases = (char *)c->kb.ptr + prev * c->kb.st() * es;
+            sq.vscales = (char *)c->vs.ptr + prev * c->vs.st() * es;
+            sq.vbiases = (char *)c->vb.ptr + prev * c->vb.st() * es;
+            sq.c_sh = c->kq.sh(); sq.g_sh = c->ks.sh();
+            same_group = same_group && c->vq.sh() == c->kq.sh() && c->vs.sh() == c->ks.sh();
+            AttnArgs a = make_attn_args(q[i], outs[i], scale, KVC_MASK_NONE, nullptr, c->offset, qa.H);
+            a.k = affine_source(qk[0], qk[1], qk[2], c->group_size, c->bits);
+            a.v = affine_source(qv[0], qv[1], qv[2], c->group_size, c->bits);
+            args[(size_t)(i - from)] = a;
+        }
+        qa.group = caches[from]->group_size;
+        qa.bits = caches[from]->bits;
+        if (!same_group || !launch_affine_quantize_varlen(qa, s)) {
+            for (int i = from; i < to; ++i) {
+                kvc_cache *c = caches[i];
+                const int64_t prev = c->offset - 1;
+                QuantAppendArgs ka = quant_args(k[i], c->kq, c->ks, c->kb, c->group_size, c->bits, prev);
+                QuantAppendArgs va = quant_args(v[i], c->vq, c->vs, c->vb, c->group_size, c->bits, prev);
+                launch_affine_quantize2(ka, &va, s);
+            }
+        }
+        if (!same_group || launch_attention_affine_varlen(args.data(), m, s) == 0)
+            for (int i = 0; i < m; ++i) launch_attention(args[(size_t)i], s);
     }
 }
 

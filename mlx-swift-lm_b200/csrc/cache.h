@@ -106,7 +106,11 @@ namespace kvc {
 void cache_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
                   kvc_tensor *out_k, kvc_tensor *out_v);
 void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
-                            kvc_tensor out_k[3], kvc_tensor out_v[3]);
+                            kvc_tensor out_k[3], kvc_tensor out_v[3], bool defer_quantize = false);
+// attentionWithCacheUpdate for a list of independent caches, one new token each: two launches for
+// the whole list when they are affine caches of one layout, otherwise one call per cache.
+void cache_attention_varlen(kvc_cache *const *caches, int n, const kvc_tensor *q, const kvc_tensor *k,
+                            const kvc_tensor *v, float scale, const kvc_tensor *outs, cudaStream_t s);
 void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, const kvc_tensor &v,
                      float scale, int32_t mask_mode, const kvc_tensor *mask, const kvc_tensor &out,
                      cudaStream_t s);

@@ -818,6 +818,18 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev, cons
     });
 }
 
+kvc_status kvc_attention_varlen(kvc_cache *const *caches, int32_t count, const kvc_tensor *queries,
+                                const kvc_tensor *keys, const kvc_tensor *values, float scale,
+                                const kvc_tensor *outs, void *stream) {
+    if (!caches || !queries || !keys || !values || !outs) return set_error(KVC_ERR_INVALID_ARG, "kvc_attention_varlen: null argument");
+    if (count <= 0) return KVC_OK;
+    for (int i = 0; i < count; ++i) KVC_CHECK_HANDLE(caches[i]);
+    return guarded([&] {
+        DeviceGuard dg(caches[0]->device);
+        kvc::cache_attention_varlen(caches, count, queries, keys, values, scale, outs, as_stream(stream));
+    });
+}
+
 kvc_status kvc_turbo_encode_new_token(kvc_cache *cache, const kvc_tensor *keys, const kvc_tensor *values,
                                       void *stream) {
     if (!cache || !keys || !values) return set_error(KVC_ERR_INVALID_ARG, "kvc_turbo_encode_new_token: null argument");

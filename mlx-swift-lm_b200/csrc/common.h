@@ -176,6 +176,22 @@ void launch_affine_quantize(const QuantAppendArgs &a, cudaStream_t stream);
 // K and V rows in one launch (v may be null).
 void launch_affine_quantize2(const QuantAppendArgs &k, const QuantAppendArgs *v, cudaStream_t stream);
 
+// Quantise-append of ONE new token for a list of independent caches in one launch.
+constexpr int KVC_VARLEN_MAX = 32;
+struct VarlenQuantSeq {
+    const void *ksrc, *vsrc;              // [H, D] rows of the new token
+    uint32_t *kcodes, *vcodes;            // head 0 at the append position
+    void *kscales, *kbiases, *vscales, *vbiases;
+    int64_t c_sh, g_sh;                   // head strides (words / elements) of this cache
+};
+struct VarlenQuantArgs {
+    int32_t n, H, D, group, bits, dtype;
+    int64_t src_sh;                       // head stride of the new rows (elements)
+    VarlenQuantSeq seq[KVC_VARLEN_MAX];
+};
+// false when the shape is outside the warp kernel's domain (the caller then loops over the caches)
+bool launch_affine_quantize_varlen(const VarlenQuantArgs &a, cudaStream_t stream);
+
 struct DequantArgs {
     const uint32_t *codes = nullptr;
     const void *scales = nullptr, *biases = nullptr;

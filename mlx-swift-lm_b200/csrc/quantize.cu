@@ -49,6 +49,61 @@ __device__ __forceinline__ uint32_t affine_code(float w, float scale, float bias
     return (uint32_t)q;
 }
 
+// One row (D = 32 E elements) by one warp: group min/max by shuffles, MLX affine parameters,
+// codes packed low bits first. `src` points at the row's first element, `dst` at its first code
+// word, `scales` / `biases` at its first group.
+template <typename T, int E>
+__device__ __forceinline__ void quantize_row_warp(const T *src, int64_t s_sd, uint32_t *dst, T *scales, T *biases,
+                                                  int group, int bits, int lane) {
+    float v[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) v[i] = to_float<T>(src[(int64_t)(lane * E + i) * s_sd]);
+
+    float w_min = v[0], w_max = v[0];
+#pragma unroll
+    for (int i = 1; i < E; ++i) {
+        w_min = fminf(w_min, v[i]);
+        w_max = fmaxf(w_max, v[i]);
+    }
+    const int lanes_per_group = group / E;  // power of two, <= 32
+    for (int m = lanes_per_group >> 1; m >= 1; m >>= 1) {
+        w_min = fminf(w_min, __shfl_xor_sync(0xffffffffu, w_min, m));
+        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, m));
+    }
+    const float n_bins = (float)((1 << bits) - 1);
+    float scale, bias;
+    affine_params(w_min, w_max, n_bins, scale, bias);
+
+    if ((lane % lanes_per_group) == 0) {
+        const int g = lane / lanes_per_group;
+        scales[g] = from_float<T>(scale);
+        biases[g] = from_float<T>(bias);
+    }
+
+    // Pack: the lane's E codes occupy E*bits consecutive bits starting at bit
+    // lane*E*bits of the row (low bits first).
+    const int nbits = E * bits;  // a power of two in [2, 64]
+    uint64_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+        acc |= (uint64_t)affine_code(v[i], scale, bias, n_bins) << (i * bits);
+    if (nbits == 64) {
+        dst[lane * 2] = (uint32_t)acc;
+        dst[lane * 2 + 1] = (uint32_t)(acc >> 32);
+    } else if (nbits == 32) {
+        dst[lane] = (uint32_t)acc;
+    } else {
+        const uint32_t part = (uint32_t)acc;
+        const int lpw = 32 / nbits;  // lanes per word
+        uint32_t word = part;
+        for (int k = 1; k < lpw; ++k) {
+            const uint32_t other = __shfl_down_sync(0xffffffffu, part, k);
+            word |= other << (k * nbits);
+        }
+        if ((lane % lpw) == 0) dst[lane / lpw] = word;
+    }
+}
+
 // One warp per (tensor, b, h, s) row; E elements per lane.
 template <typename T, int E>
 __global__ void affine_quantize_warp_kernel(QuantAppendArgs ka, QuantAppendArgs va, int64_t k_rows,
@@ -65,58 +120,30 @@ __global__ void affine_quantize_warp_kernel(QuantAppendArgs ka, QuantAppendArgs 
     r /= a.S;
     const int h = (int)(r % a.H);
     const int b = (int)(r / a.H);
-
-    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
-    float v[E];
-#pragma unroll
-    for (int i = 0; i < E; ++i) v[i] = to_float<T>(src[(int64_t)(lane * E + i) * a.s_sd]);
-
-    float w_min = v[0], w_max = v[0];
-#pragma unroll
-    for (int i = 1; i < E; ++i) {
-        w_min = fminf(w_min, v[i]);
-        w_max = fmaxf(w_max, v[i]);
-    }
-    const int lanes_per_group = a.group / E;  // power of two, <= 32
-    for (int m = lanes_per_group >> 1; m >= 1; m >>= 1) {
-        w_min = fminf(w_min, __shfl_xor_sync(0xffffffffu, w_min, m));
-        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, m));
-    }
-    const float n_bins = (float)((1 << a.bits) - 1);
-    float scale, bias;
-    affine_params(w_min, w_max, n_bins, scale, bias);
-
     const int64_t t = a.pos + s;
-    if ((lane % lanes_per_group) == 0) {
-        const int g = lane / lanes_per_group;
-        const int64_t gi = b * a.g_sb + h * a.g_sh + t * a.g_st + g;
-        ((T *)a.scales)[gi] = from_float<T>(scale);
-        ((T *)a.biases)[gi] = from_float<T>(bias);
-    }
+    quantize_row_warp<T, E>((const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss, a.s_sd,
+                            a.codes + b * a.c_sb + h * a.c_sh + t * a.c_st,
+                            (T *)a.scales + b * a.g_sb + h * a.g_sh + t * a.g_st,
+                            (T *)a.biases + b * a.g_sb + h * a.g_sh + t * a.g_st, a.group, a.bits, lane);
+}
 
-    // Pack: the lane's E codes occupy E*bits consecutive bits starting at bit
-    // lane*E*bits of the row (low bits first).
-    uint32_t *dst = a.codes + b * a.c_sb + h * a.c_sh + t * a.c_st;
-    const int nbits = E * a.bits;  // a power of two in [2, 64]
-    uint64_t acc = 0;
-#pragma unroll
-    for (int i = 0; i < E; ++i)
-        acc |= (uint64_t)affine_code(v[i], scale, bias, n_bins) << (i * a.bits);
-    if (nbits == 64) {
-        dst[lane * 2] = (uint32_t)acc;
-        dst[lane * 2 + 1] = (uint32_t)(acc >> 32);
-    } else if (nbits == 32) {
-        dst[lane] = (uint32_t)acc;
-    } else {
-        const uint32_t part = (uint32_t)acc;
-        const int lpw = 32 / nbits;  // lanes per word
-        uint32_t word = part;
-        for (int k = 1; k < lpw; ++k) {
-            const uint32_t other = __shfl_down_sync(0xffffffffu, part, k);
-            word |= other << (k * nbits);
-        }
-        if ((lane % lpw) == 0) dst[lane / lpw] = word;
-    }
+// The same rows for a list of independent caches (one new token each): row = (sequence, K or V,
+// head); every pointer of the table already addresses head 0 at the sequence's append position.
+template <typename T, int E>
+__global__ void affine_quantize_varlen_kernel(const __grid_constant__ VarlenQuantArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= a.n * 2 * a.H) return;
+    const int i = row / (2 * a.H), rr = row % (2 * a.H);
+    const bool is_v = rr >= a.H;
+    const int h = rr % a.H;
+    const VarlenQuantSeq &q = a.seq[i];
+    const T *src = (const T *)(is_v ? q.vsrc : q.ksrc) + (int64_t)h * a.src_sh;
+    uint32_t *codes = (is_v ? q.vcodes : q.kcodes) + (int64_t)h * q.c_sh;
+    T *scales = (T *)(is_v ? q.vscales : q.kscales) + (int64_t)h * q.g_sh;
+    T *biases = (T *)(is_v ? q.vbiases : q.kbiases) + (int64_t)h * q.g_sh;
+    quantize_row_warp<T, E>(src, 1, codes, scales, biases, a.group, a.bits, lane);
 }
 
 // General shapes: one thread per group.
@@ -215,6 +242,33 @@ void quantize_dispatch(const QuantAppendArgs &k, const QuantAppendArgs &v, bool 
 }
 
 }  // namespace
+
+bool launch_affine_quantize_varlen(const VarlenQuantArgs &a, cudaStream_t stream) {
+    if (a.D % 32 != 0 || a.n < 1 || a.n > KVC_VARLEN_MAX) return false;
+    const int E = a.D / 32;
+    if (!(E == 1 || E == 2 || E == 4 || E == 8) || a.group % E != 0) return false;
+    const int lpg = a.group / E;
+    if (lpg < 1 || lpg > 32 || (lpg & (lpg - 1))) return false;
+    const int nbits = E * a.bits;
+    if (!((nbits >= 32) ? (nbits % 32 == 0) : (32 % nbits == 0))) return false;
+    const int total = a.n * 2 * a.H, warps = 8;
+    const unsigned blocks = (unsigned)((total + warps - 1) / warps);
+#define KVC_QV(TT)                                                                                      \
+    switch (E) {                                                                                        \
+        case 1: affine_quantize_varlen_kernel<TT, 1><<<blocks, warps * 32, 0, stream>>>(a); break;     \
+        case 2: affine_quantize_varlen_kernel<TT, 2><<<blocks, warps * 32, 0, stream>>>(a); break;     \
+        case 4: affine_quantize_varlen_kernel<TT, 4><<<blocks, warps * 32, 0, stream>>>(a); break;     \
+        default: affine_quantize_varlen_kernel<TT, 8><<<blocks, warps * 32, 0, stream>>>(a); break;    \
+    }
+    if (a.dtype == KVC_BF16) { KVC_QV(__nv_bfloat16) }
+    else if (a.dtype == KVC_F16) { KVC_QV(__half) }
+    else if (a.dtype == KVC_F32) { KVC_QV(float) }
+    else return false;
+#undef KVC_QV
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+    return true;
+}
 
 void launch_affine_quantize2(const QuantAppendArgs &k, const QuantAppendArgs *v, cudaStream_t stream) {
     if ((int64_t)k.B * k.H * k.S == 0) return;

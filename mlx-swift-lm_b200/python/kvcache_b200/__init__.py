@@ -117,6 +117,8 @@ _lib.kvc_make_mask.argtypes = [_vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int
                                ctypes.POINTER(ctypes.c_int64), _vp, _vp]
 _lib.kvc_affine_quantize.argtypes = [_TP, ctypes.c_int32, ctypes.c_int32, _TP, _TP, _TP, _vp]
 _lib.kvc_affine_dequantize.argtypes = [_TP, _TP, _TP, ctypes.c_int32, ctypes.c_int32, _TP, _vp]
+_lib.kvc_attention_varlen.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP, ctypes.c_float, _TP, _vp]
+_lib.kvc_attention_varlen.restype = ctypes.c_int32
 _lib.kvc_turbo_encode_new_token.argtypes = [_vp, _TP, _TP, _vp]
 _lib.kvc_turbo_encode_new_token.restype = ctypes.c_int32
 _lib.kvc_turbo_encode.argtypes = [_TP, _vp, ctypes.POINTER(ctypes.c_float), ctypes.c_int32, _TP, _TP, _vp]
@@ -698,6 +700,11 @@ class DecodeStep:
     def run(self, stream=None, synchronize: bool = False):
         check(_lib.kvc_attention_batch(self.handles, self.n, self.q, self.k, self.v, self.scale, self.mode,
                                        self.o, _stream_ptr(stream), self.host, 1 if synchronize else 0))
+
+    def run_varlen(self, stream=None):
+        """The caches are independent sequences of one layer (one new token each): kvc_attention_varlen."""
+        check(_lib.kvc_attention_varlen(self.handles, self.n, self.q, self.k, self.v, self.scale, self.o,
+                                        _stream_ptr(stream)))
 
     def run_sharded(self, comm: "Comm", shard_axis: int = 1, stream=None):
         check(_lib.kvc_attention_sharded_batch(comm._h, self.handles, self.n, self.q, self.k, self.v, self.scale,

@@ -176,3 +176,41 @@ def test_turbo_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv,
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
     assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_varlen_decode_over_independent_caches(kvc, oracle, cuda, bits):
+    """A ragged decode batch held the reference's way (one cache per sequence): the var-len call
+    appends and attends all of them in two launches; per-sequence results equal the oracle's and
+    the per-cache calls', and the caches hold identical codes afterwards."""
+    Hq, Hkv, D, dtype = 28, 4, 128, torch.bfloat16
+    lengths = [37, 64, 1, 300, 2049, 511, 130, 65, 1000, 5]
+    n = len(lengths)
+    var = [kvc.QuantizedKVCache(64, bits, reserve_tokens=t + 8) for t in lengths]
+    one = [kvc.QuantizedKVCache(64, bits, reserve_tokens=t + 8) for t in lengths]
+    orc = [oracle.QuantizedKVCache(64, bits) for _ in lengths]
+    for i, t in enumerate(lengths):
+        k, v = seeded((1, Hkv, t, D), 10 * i, dtype), seeded((1, Hkv, t, D), 10 * i + 1, dtype)
+        for c in (var[i], one[i]):
+            c.update_quantized(k.to(cuda), v.to(cuda))
+        orc[i].update_quantized(to_oracle(k), to_oracle(v))
+    scale = D ** -0.5
+    for step in range(3):
+        q = [seeded((1, Hq, 1, D), 1000 + 100 * step + i, dtype) for i in range(n)]
+        k = [seeded((1, Hkv, 1, D), 2000 + 100 * step + i, dtype) for i in range(n)]
+        v = [seeded((1, Hkv, 1, D), 3000 + 100 * step + i, dtype) for i in range(n)]
+        dq, dk, dv = [t.to(cuda) for t in q], [t.to(cuda) for t in k], [t.to(cuda) for t in v]
+        outs = [torch.empty((1, Hq, 1, D), dtype=dtype, device=cuda) for _ in range(n)]
+        kvc.launch_count(reset=True)
+        kvc.DecodeStep(var, dq, dk, dv, outs, scale).run_varlen()
+        assert kvc.launch_count(reset=True) == 2
+        for i in range(n):
+            ref = oracle.attention_with_cache_update(to_oracle(q[i]), to_oracle(k[i]), to_oracle(v[i]), orc[i], scale)
+            assert max_abs_diff(outs[i], ref) <= TOL[dtype], f"step {step} sequence {i}"
+            single = one[i].attention(dq[i], dk[i], dv[i], scale)
+            assert max_abs_diff(outs[i], to_oracle(single)) <= 1e-2
+    assert kvc.lib().kvc_device_status() == 0
+    for a, b, o in zip(var, one, orc):
+        assert a.offset == b.offset == o.offset
+        for x, y in zip(a.state, b.state):
+            assert torch.equal(x, y)
