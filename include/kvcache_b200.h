@@ -387,6 +387,37 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev,
                             const float *boundaries_host, int32_t bits,
                             const kvc_tensor *packed, const kvc_tensor *norms, void *stream);
 
+/* ------------------------------------------------------------------ */
+/* list-level dynamic conversion (generation loop: maybeQuantizeKVCache) */
+/* ------------------------------------------------------------------ */
+
+/* resolveTurboScheme (TurboQuantKVCache.swift:1611-1635) / resolveAffineScheme (KVCache.swift:2455-2461):
+ * return 1 and fill the outputs for a known scheme name, 0 otherwise. key_bits 0 = raw keys,
+ * 8 = 8-bit affine keys. */
+int32_t kvc_resolve_turbo_scheme(const char *scheme, int32_t *key_bits, int32_t *value_bits);
+int32_t kvc_resolve_affine_scheme(const char *scheme, int32_t *bits, int32_t *group_size);
+
+/* KVCacheTree.turboQuantProtectedPaths (KVCacheTree.swift:118-134) on a flat list of layers: writes
+ * flags[i] = 1 for the layers that get 8-bit affine protection instead of a fragile TurboQuant scheme
+ * (0 < key_bits < 8, or value_bits <= 2): the first and last min(2, eligible / 2) layers among those
+ * whose kind is SIMPLE, QUANTIZED or TURBO. Pure host logic; kinds are KVC_KIND_* values. */
+kvc_status kvc_turbo_protected_layers(const int32_t *kinds, int32_t count, int32_t key_bits,
+                                      int32_t value_bits, int32_t *flags);
+
+/* maybeAffineQuantizeKVCache (KVCache.swift:2500-2520): every KVCacheSimple of the list whose offset
+ * exceeds compression_start is replaced by its toQuantized conversion (the old handle is freed, the
+ * slot receives the new one); layers whose shape cannot be quantised stay as they are. *complete = 0
+ * when some simple layer is still waiting for compression_start. */
+kvc_status kvc_maybe_affine_quantize(kvc_cache **caches, int32_t count, int32_t bits, int32_t group_size,
+                                     int64_t compression_start, void *stream, int32_t *complete);
+
+/* maybeTurboQuantizeKVCache (TurboQuantKVCache.swift:1690-1762): the same walk with a TurboQuant
+ * scheme; protected boundary layers become 8-bit affine (group 64) caches, the others
+ * TurboQuantKVCache(bits = max(key_bits, value_bits), key_bits, value_bits) holding the live rows in
+ * their raw phase; rotating layers are left alone. */
+kvc_status kvc_maybe_turbo_quantize(kvc_cache **caches, int32_t count, int32_t key_bits, int32_t value_bits,
+                                    int64_t quantized_kv_start, void *stream, int32_t *complete);
+
 /* attentionWithCacheUpdate for `count` INDEPENDENT caches in one call: cache i appends keys[i] /
  * values[i] (one new token, [1, Hkv, 1, D]) and attends queries[i] ([1, Hq, 1, D]) over its own
  * length into outs[i]. This is a ragged decode batch the way the reference holds it (one cache

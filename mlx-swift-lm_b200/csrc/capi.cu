@@ -656,6 +656,121 @@ kvc_status kvc_to_turbo(const kvc_cache *c, int32_t key_bits, int32_t value_bits
     });
 }
 
+// ---------------------------------------------------------------------
+// list-level dynamic conversion
+// ---------------------------------------------------------------------
+int32_t kvc_resolve_turbo_scheme(const char *scheme, int32_t *key_bits, int32_t *value_bits) {
+    if (!scheme) return 0;
+    static const struct { const char *name; int kb, vb; } table[] = {
+        {"turbo0v4", 0, 4}, {"turbo0v3", 0, 3}, {"turbo0v2", 0, 2}, {"turbo8v4", 8, 4}, {"turbo8v3", 8, 3},
+        {"turbo8v2", 8, 2}, {"turbo4", 4, 4},   {"turbo4v2", 4, 2}, {"turbo3", 3, 3},   {"turbo2", 2, 2}};
+    for (const auto &e : table)
+        if (std::strcmp(scheme, e.name) == 0) {
+            if (key_bits) *key_bits = e.kb;
+            if (value_bits) *value_bits = e.vb;
+            return 1;
+        }
+    return 0;
+}
+
+int32_t kvc_resolve_affine_scheme(const char *scheme, int32_t *bits, int32_t *group_size) {
+    if (!scheme) return 0;
+    int b = 0;
+    if (std::strcmp(scheme, "affine4") == 0) b = 4;
+    else if (std::strcmp(scheme, "affine8") == 0) b = 8;
+    else return 0;
+    if (bits) *bits = b;
+    if (group_size) *group_size = 64;
+    return 1;
+}
+
+kvc_status kvc_turbo_protected_layers(const int32_t *kinds, int32_t count, int32_t key_bits, int32_t value_bits,
+                                      int32_t *flags) {
+    if ((!kinds || !flags) && count > 0) return set_error(KVC_ERR_INVALID_ARG, "kvc_turbo_protected_layers: null argument");
+    for (int i = 0; i < count; ++i) flags[i] = 0;
+    const bool fragile = (key_bits > 0 && key_bits < 8) || value_bits <= 2;
+    if (!fragile) return KVC_OK;
+    std::vector<int> eligible;
+    for (int i = 0; i < count; ++i)
+        if (kinds[i] == KVC_KIND_SIMPLE || kinds[i] == KVC_KIND_QUANTIZED || kinds[i] == KVC_KIND_TURBO) eligible.push_back(i);
+    const int boundary = std::min<int>(2, (int)eligible.size() / 2);
+    for (int j = 0; j < boundary; ++j) {
+        flags[eligible[(size_t)j]] = 1;
+        flags[eligible[eligible.size() - 1 - (size_t)j]] = 1;
+    }
+    return KVC_OK;
+}
+
+kvc_status kvc_maybe_affine_quantize(kvc_cache **caches, int32_t count, int32_t bits, int32_t group_size,
+                                     int64_t compression_start, void *stream, int32_t *complete) {
+    if (!caches && count > 0) return set_error(KVC_ERR_INVALID_ARG, "kvc_maybe_affine_quantize: null argument");
+    return guarded([&] {
+        bool waiting = false;
+        for (int i = 0; i < count; ++i) {
+            kvc_cache *c = caches[i];
+            if (!c || c->cfg.kind != KVC_KIND_SIMPLE) continue;
+            if (c->offset <= compression_start) {
+                waiting = true;
+                continue;
+            }
+            DeviceGuard dg(c->device);
+            kvc_cache *q = nullptr;
+            try {
+                q = kvc::cache_to_quantized(c, group_size, bits, as_stream(stream));
+            } catch (const kvc::Error &) {
+                q = nullptr;  // `try? simple.toQuantized`: the layer stays in full precision
+            }
+            if (q) {
+                kvc_free(c);
+                caches[i] = q;
+            }
+        }
+        if (complete) *complete = waiting ? 0 : 1;
+    });
+}
+
+kvc_status kvc_maybe_turbo_quantize(kvc_cache **caches, int32_t count, int32_t key_bits, int32_t value_bits,
+                                    int64_t quantized_kv_start, void *stream, int32_t *complete) {
+    if (!caches && count > 0) return set_error(KVC_ERR_INVALID_ARG, "kvc_maybe_turbo_quantize: null argument");
+    return guarded([&] {
+        std::vector<int32_t> kinds((size_t)count), prot((size_t)count);
+        for (int i = 0; i < count; ++i) kinds[(size_t)i] = caches[i] ? caches[i]->cfg.kind : -1;
+        kvc_turbo_protected_layers(kinds.data(), count, key_bits, value_bits, prot.data());
+        bool waiting = false;
+        for (int i = 0; i < count; ++i) {
+            kvc_cache *c = caches[i];
+            if (!c || c->cfg.kind != KVC_KIND_SIMPLE) continue;
+            if (c->offset <= quantized_kv_start) {
+                waiting = true;
+                continue;
+            }
+            DeviceGuard dg(c->device);
+            kvc_cache *n = nullptr;
+            try {
+                if (prot[(size_t)i]) {
+                    n = kvc::cache_to_quantized(c, 64, 8, as_stream(stream));
+                } else {
+                    // affine-K mode quantises keys in groups: resolve the group size against this layer's
+                    // head dims up front and skip the layer when none of the supported sizes divides them
+                    int key_group = 64;
+                    if (key_bits == 8) {
+                        key_group = c->k.allocated() ? kvc::resolved_group_size(64, (int)c->k.W, (int)c->v.W) : 0;
+                        if (!key_group) continue;
+                    }
+                    n = kvc::cache_to_turbo(c, key_bits, value_bits, key_group, as_stream(stream));
+                }
+            } catch (const kvc::Error &) {
+                n = nullptr;  // unsupported realised shape: the layer stays in full precision
+            }
+            if (n) {
+                kvc_free(c);
+                caches[i] = n;
+            }
+        }
+        if (complete) *complete = waiting ? 0 : 1;
+    });
+}
+
 kvc_status kvc_logical_view(kvc_cache *c, int64_t tail, void *stream, kvc_tensor *out_k, kvc_tensor *out_v) {
     KVC_CHECK_HANDLE(c);
     return guarded([&] {

@@ -117,6 +117,19 @@ _lib.kvc_make_mask.argtypes = [_vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int
                                ctypes.POINTER(ctypes.c_int64), _vp, _vp]
 _lib.kvc_affine_quantize.argtypes = [_TP, ctypes.c_int32, ctypes.c_int32, _TP, _TP, _TP, _vp]
 _lib.kvc_affine_dequantize.argtypes = [_TP, _TP, _TP, ctypes.c_int32, ctypes.c_int32, _TP, _vp]
+_lib.kvc_resolve_turbo_scheme.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+_lib.kvc_resolve_turbo_scheme.restype = ctypes.c_int32
+_lib.kvc_resolve_affine_scheme.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+_lib.kvc_resolve_affine_scheme.restype = ctypes.c_int32
+_lib.kvc_turbo_protected_layers.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                            ctypes.POINTER(ctypes.c_int32)]
+_lib.kvc_turbo_protected_layers.restype = ctypes.c_int32
+_lib.kvc_maybe_affine_quantize.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
+                                           _vp, ctypes.POINTER(ctypes.c_int32)]
+_lib.kvc_maybe_affine_quantize.restype = ctypes.c_int32
+_lib.kvc_maybe_turbo_quantize.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
+                                          _vp, ctypes.POINTER(ctypes.c_int32)]
+_lib.kvc_maybe_turbo_quantize.restype = ctypes.c_int32
 _lib.kvc_attention_varlen.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP, ctypes.c_float, _TP, _vp]
 _lib.kvc_attention_varlen.restype = ctypes.c_int32
 _lib.kvc_turbo_encode_new_token.argtypes = [_vp, _TP, _TP, _vp]
@@ -762,3 +775,72 @@ class Comm:
                                          ctypes.c_float(scale), mode, mptr, ctypes.byref(to), shard_axis,
                                          _stream_ptr(stream)))
         return out_full
+
+
+# ---------------------------------------------------------------------------
+# list-level dynamic conversion (maybeQuantizeKVCache)
+# ---------------------------------------------------------------------------
+
+def resolve_turbo_scheme(scheme: Optional[str]):
+    """resolveTurboScheme: (key_bits, value_bits) or None."""
+    if scheme is None:
+        return None
+    kb, vb = ctypes.c_int32(), ctypes.c_int32()
+    if not _lib.kvc_resolve_turbo_scheme(scheme.encode(), ctypes.byref(kb), ctypes.byref(vb)):
+        return None
+    return int(kb.value), int(vb.value)
+
+
+def resolve_affine_scheme(scheme: Optional[str]):
+    """resolveAffineScheme: (bits, group_size) or None."""
+    if scheme is None:
+        return None
+    b, g = ctypes.c_int32(), ctypes.c_int32()
+    if not _lib.kvc_resolve_affine_scheme(scheme.encode(), ctypes.byref(b), ctypes.byref(g)):
+        return None
+    return int(b.value), int(g.value)
+
+
+def turbo_protected_layers(kinds: Sequence[int], key_bits: int, value_bits: int) -> List[bool]:
+    n = len(kinds)
+    arr = (ctypes.c_int32 * n)(*kinds)
+    out = (ctypes.c_int32 * n)()
+    check(_lib.kvc_turbo_protected_layers(arr, n, key_bits, value_bits, out))
+    return [bool(x) for x in out]
+
+
+def _wrap_handle(handle, like: "KVCache") -> "KVCache":
+    kind = int(_lib.kvc_kind_of(ctypes.c_void_p(handle)))
+    cls = {KIND_SIMPLE: KVCacheSimple, KIND_ROTATING: RotatingKVCache, KIND_QUANTIZED: QuantizedKVCache,
+           KIND_TURBO: TurboQuantKVCache}[kind]
+    obj = cls.__new__(cls)
+    KVCache.__init__(obj, handle, like._device)
+    return obj
+
+
+def _rewrite_list(caches: List["KVCache"], fn) -> bool:
+    n = len(caches)
+    arr = (_vp * n)(*[c._h for c in caches])
+    before = [int(ctypes.cast(arr[i], ctypes.c_void_p).value or 0) for i in range(n)]
+    done = ctypes.c_int32()
+    check(fn(arr, n, ctypes.byref(done)))
+    for i in range(n):
+        now = int(ctypes.cast(arr[i], ctypes.c_void_p).value or 0)
+        if now != before[i]:
+            caches[i]._h = None          # the library freed the old handle
+            caches[i] = _wrap_handle(now, caches[i])
+    return bool(done.value)
+
+
+def maybe_affine_quantize_kv_cache(caches: List["KVCache"], bits: int, group_size: int = 64,
+                                   compression_start: int = 0, stream=None) -> bool:
+    """maybeAffineQuantizeKVCache: rewrites the list in place; False while a layer still waits."""
+    return _rewrite_list(caches, lambda arr, n, done: _lib.kvc_maybe_affine_quantize(
+        arr, n, bits, group_size, compression_start, _stream_ptr(stream), done))
+
+
+def maybe_turbo_quantize_kv_cache(caches: List["KVCache"], key_bits: int, value_bits: int,
+                                  quantized_kv_start: int = 0, stream=None) -> bool:
+    """maybeTurboQuantizeKVCache: rewrites the list in place; False while a layer still waits."""
+    return _rewrite_list(caches, lambda arr, n, done: _lib.kvc_maybe_turbo_quantize(
+        arr, n, key_bits, value_bits, quantized_kv_start, _stream_ptr(stream), done))

@@ -217,3 +217,52 @@ def test_state_round_trip_and_export(kvc, oracle, cuda):
     assert list(r2.meta_state) == list(r.meta_state)
     assert torch.equal(r2.export_state(0), r.export_state(0))
     assert g.memory_bytes > 0
+
+
+def test_list_level_dynamic_conversion(kvc, cuda):
+    """maybeTurboQuantizeKVCache / maybeAffineQuantizeKVCache over a layer list: boundary layers get
+    8-bit affine protection, the others the requested scheme, rotating layers and layers below the
+    start threshold are left alone; converted layers equal the per-cache conversions."""
+    B, H, D = 1, 2, 128
+
+    def layers():
+        out = []
+        for i in range(7):
+            c = kvc.KVCacheSimple()
+            n = 5 if i == 3 else 40 + i
+            c.update(seeded((B, H, n, D), 10 + i, torch.bfloat16).to(cuda), seeded((B, H, n, D), 50 + i, torch.bfloat16).to(cuda))
+            out.append(c)
+        rot = kvc.RotatingKVCache(max_size=16)
+        rot.update(seeded((B, H, 30, D), 99, torch.bfloat16).to(cuda), seeded((B, H, 30, D), 98, torch.bfloat16).to(cuda))
+        out.insert(2, rot)
+        return out
+
+    caches, twins = layers(), layers()
+    done = kvc.maybe_turbo_quantize_kv_cache(caches, 4, 4, quantized_kv_start=10)
+    assert done is False                                  # one simple layer (5 tokens) still waits
+    kinds = [type(c).__name__ for c in caches]
+    assert kinds == ["QuantizedKVCache", "QuantizedKVCache", "RotatingKVCache", "TurboQuantKVCache", "KVCacheSimple",
+                     "TurboQuantKVCache", "QuantizedKVCache", "QuantizedKVCache"]
+    for i, c in enumerate(caches):
+        assert c.offset == twins[i].offset
+        if isinstance(c, kvc.QuantizedKVCache):
+            ref = twins[i].to_quantized(64, 8)
+            assert c.group_size == 64 and c.bits == 8
+            for x, y in zip(c.state, ref.state):
+                assert torch.equal(x, y)
+        elif isinstance(c, kvc.TurboQuantKVCache):
+            assert not c.is_compressed
+            for x, y in zip(c.state, twins[i].state):
+                assert torch.equal(x, y)                  # raw phase: the live rows were adopted
+    # decode still works on every converted layer
+    for c in caches:
+        if isinstance(c, kvc.RotatingKVCache):
+            continue
+        q, k, v = (seeded((B, 4, 1, D), 1, torch.bfloat16).to(cuda), seeded((B, H, 1, D), 2, torch.bfloat16).to(cuda),
+                   seeded((B, H, 1, D), 3, torch.bfloat16).to(cuda))
+        assert torch.isfinite(c.attention(q, k, v, 0.09).float()).all()
+
+    caches2 = layers()
+    assert kvc.maybe_affine_quantize_kv_cache(caches2, 4, 64, compression_start=0) is True
+    assert [type(c).__name__ for c in caches2] == ["QuantizedKVCache"] * 2 + ["RotatingKVCache"] + ["QuantizedKVCache"] * 5
+    assert all(c.bits == 4 for c in caches2 if isinstance(c, kvc.QuantizedKVCache))

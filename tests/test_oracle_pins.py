@@ -244,3 +244,30 @@ def test_turbo_causal_chunk_equals_per_position_decode(oracle):
         one = b.compressed_attention(q[:, :, l:l + 1], k[:, :, T + l:T + l + 1], v[:, :, T + l:T + l + 1], 0.125)
         assert float(np.max(np.abs(one[:, :, 0] - chunk[:, :, l]))) < 1e-5
     assert all(np.array_equal(x, y) for x, y in zip(a.state, b.state))
+
+
+def test_scheme_tables_and_boundary_protection_host_logic(kvc):
+    """resolveTurboScheme / resolveAffineScheme tables (TurboQuantKVCache.swift:1611-1635,
+    KVCache.swift:2455-2461) and turboQuantProtectedPaths (KVCacheTree.swift:118-134): host logic of
+    the library, no device needed."""
+    assert kvc.resolve_turbo_scheme("turbo4") == (4, 4)
+    assert kvc.resolve_turbo_scheme("turbo4v2") == (4, 2)
+    assert kvc.resolve_turbo_scheme("turbo0v3") == (0, 3)
+    assert kvc.resolve_turbo_scheme("turbo8v4") == (8, 4)
+    assert kvc.resolve_turbo_scheme("turbo3") == (3, 3) and kvc.resolve_turbo_scheme("turbo2") == (2, 2)
+    assert kvc.resolve_turbo_scheme("turbo5") is None and kvc.resolve_turbo_scheme(None) is None
+    assert kvc.resolve_affine_scheme("affine4") == (4, 64) and kvc.resolve_affine_scheme("affine8") == (8, 64)
+    assert kvc.resolve_affine_scheme("affine2") is None
+    S, R, Q, T = kvc.KIND_SIMPLE, kvc.KIND_ROTATING, kvc.KIND_QUANTIZED, kvc.KIND_TURBO
+    # fragile scheme, 8 eligible layers: two on each end
+    assert kvc.turbo_protected_layers([S] * 8, 4, 4) == [True, True, False, False, False, False, True, True]
+    # robust schemes (raw / 8-bit keys with values above 2 bits) protect nothing
+    assert kvc.turbo_protected_layers([S] * 8, 0, 4) == [False] * 8
+    assert kvc.turbo_protected_layers([S] * 8, 8, 3) == [False] * 8
+    # ... but 2-bit values are fragile whatever the keys are
+    assert kvc.turbo_protected_layers([S] * 6, 8, 2) == [True, True, False, False, True, True]
+    # rotating layers do not count: protection lands on the first / last ELIGIBLE layers
+    assert kvc.turbo_protected_layers([R, S, R, S, S, Q, T, R], 3, 3) == [False, True, False, True, False, True, True, False]
+    # min(2, eligible / 2): three eligible layers protect one on each end, one protects none
+    assert kvc.turbo_protected_layers([S, S, S], 4, 4) == [True, False, True]
+    assert kvc.turbo_protected_layers([S], 4, 4) == [False]
