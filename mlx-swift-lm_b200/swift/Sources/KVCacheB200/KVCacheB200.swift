@@ -65,8 +65,22 @@ public enum MaskMode<A: DeviceArray> {
 
 /// Base class: owns one kvc_cache handle. Mirrors BaseKVCache (KVCache.swift:184-251).
 open class B200KVCache<A: DeviceArray> {
-    let handle: OpaquePointer
+    private(set) var handle: OpaquePointer
+    private var ownsHandle = true
     public var stream: UnsafeMutableRawPointer? = nil
+
+    /// The library replaced (and freed) this wrapper's handle during a list-level conversion.
+    func forgetHandle() { ownsHandle = false }
+
+    /// Wrapper of the class that matches the handle's kind.
+    static func wrap(adopting h: OpaquePointer) -> B200KVCache<A> {
+        switch kvc_kind_of(h) {
+        case KVC_KIND_ROTATING: return RotatingKVCacheB200<A>(adopting: h)
+        case KVC_KIND_QUANTIZED: return QuantizedKVCacheB200<A>(adopting: h)
+        case KVC_KIND_TURBO: return TurboQuantKVCacheB200<A>(adopting: h)
+        default: return KVCacheSimpleB200<A>(adopting: h)
+        }
+    }
 
     init(config: kvc_config) {
         var cfg = config
@@ -77,7 +91,7 @@ open class B200KVCache<A: DeviceArray> {
 
     init(adopting h: OpaquePointer) { handle = h }
 
-    deinit { kvc_free(handle) }
+    deinit { if ownsHandle { kvc_free(handle) } }
 
     public var offset: Int {
         get { Int(kvc_offset(handle)) }
@@ -160,6 +174,8 @@ func defaults(_ kind: kvc_kind) -> kvc_config {
 }
 
 public final class KVCacheSimpleB200<A: DeviceArray>: B200KVCache<A> {
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
     public init(step: Int = 256) {
         var cfg = defaults(KVC_KIND_SIMPLE)
         cfg.step = Int32(step)
@@ -174,6 +190,8 @@ public final class KVCacheSimpleB200<A: DeviceArray>: B200KVCache<A> {
 }
 
 public final class RotatingKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
     public init(maxSize: Int, keep: Int = 0, step: Int = 256) {
         var cfg = defaults(KVC_KIND_ROTATING)
         cfg.max_size = Int32(maxSize)
@@ -216,6 +234,8 @@ public final class QuantizedKVCacheB200<A: DeviceArray>: B200KVCache<A> {
 }
 
 public final class TurboQuantKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
     public init(bits: Int = 4, keyBits: Int? = nil, valueBits: Int? = nil, seed: UInt64 = 42, keyGroupSize: Int = 64) {
         var cfg = defaults(KVC_KIND_TURBO)
         cfg.bits = Int32(bits)
@@ -232,4 +252,49 @@ public final class TurboQuantKVCacheB200<A: DeviceArray>: B200KVCache<A> {
     public func compressedAttention(queries: A, keys: A, values: A, scale: Float, mask: MaskMode<A> = .none) -> A {
         attention(queries: queries, keys: keys, values: values, scale: scale, mask: mask)
     }
+
+    /// The cache-side half of compressedAttention (compressRawCache :895 + encodeNewToken :1010-1147):
+    /// chunked prefill straight into the compressed representation.
+    public func encodeNewToken(keys: A, values: A) {
+        var k = describe(keys), v = describe(values)
+        must(kvc_turbo_encode_new_token(handle, &k, &v, stream))
+    }
+}
+
+/// resolveTurboScheme (TurboQuantKVCache.swift:1611-1635).
+public func resolveTurboSchemeB200(_ scheme: String?) -> (keyBits: Int, valueBits: Int)? {
+    guard let scheme else { return nil }
+    var kb: Int32 = 0, vb: Int32 = 0
+    guard kvc_resolve_turbo_scheme(scheme, &kb, &vb) != 0 else { return nil }
+    return (Int(kb), Int(vb))
+}
+
+/// maybeTurboQuantizeKVCache (TurboQuantKVCache.swift:1690-1762) over a flat layer list: converted
+/// layers get a new handle (the library frees the old one), the wrappers are rebuilt around them.
+@discardableResult
+public func maybeTurboQuantizeKVCacheB200<A: DeviceArray>(
+    cache: inout [B200KVCache<A>], keyBits: Int, valueBits: Int, quantizedKVStart: Int, stream: UnsafeMutableRawPointer? = nil
+) -> Bool {
+    var handles: [OpaquePointer?] = cache.map { $0.handle }
+    var complete: Int32 = 0
+    let status = handles.withUnsafeMutableBufferPointer {
+        kvc_maybe_turbo_quantize($0.baseAddress, Int32($0.count), Int32(keyBits), Int32(valueBits), Int64(quantizedKVStart), stream, &complete)
+    }
+    precondition(status == KVC_OK, String(cString: kvc_last_error_message()))
+    for i in cache.indices where handles[i] != cache[i].handle {
+        cache[i].forgetHandle()     // already freed by the library
+        cache[i] = B200KVCache<A>.wrap(adopting: handles[i]!)
+    }
+    return complete != 0
+}
+
+/// One decode step of a ragged batch held as one cache per sequence (kvc_attention_varlen): the
+/// per-sequence attentionWithCacheUpdate calls of a layer in two launches.
+public func attentionWithCacheUpdateVarlenB200<A: DeviceArray>(
+    queries: [A], keys: [A], values: [A], caches: [B200KVCache<A>], scale: Float, outs: [A], stream: UnsafeMutableRawPointer? = nil
+) {
+    var handles: [OpaquePointer?] = caches.map { $0.handle }
+    var q = queries.map(describe), k = keys.map(describe), v = values.map(describe), o = outs.map(describe)
+    let status = kvc_attention_varlen(&handles, Int32(handles.count), &q, &k, &v, scale, &o, stream)
+    precondition(status == KVC_OK, String(cString: kvc_last_error_message()))
 }
