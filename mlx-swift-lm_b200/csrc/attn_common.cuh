@@ -118,6 +118,9 @@ template <> struct MmaType<__nv_bfloat16> {
     static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
         ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v);
     }
+    static __device__ __forceinline__ float2 unpack(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    }
 };
 template <> struct MmaType<__half> {
     static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -133,6 +136,9 @@ template <> struct MmaType<__half> {
     }
     static __device__ __forceinline__ void store(void *p, int64_t i, float v) {
         ((__half *)p)[i] = __float2half_rn(v);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t w) {
+        return __half22float2(*reinterpret_cast<const __half2 *>(&w));
     }
 };
 

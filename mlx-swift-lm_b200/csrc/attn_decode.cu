@@ -62,6 +62,13 @@ struct DecodeParams {
     int32_t row_blocks;  // chunk kernel: 64-row blocks per (batch, head)
     int32_t tiles_all;   // chunk kernel: tiles covering all T tokens
     FlatPlan flat;       // flat kernel
+    // cache arrays as plain pointers (byte strides): fused append target, and the measurement aid
+    // debug_skip & 2 (linear bulk copies of the same bytes instead of the tiled TMA loads)
+    unsigned char *k_base, *v_base;
+    int64_t kv_sb, kv_sh, kv_st;
+    // fused append: the new rows [B, Hkv, D] of this step (null = the cache already holds them)
+    const void *new_k, *new_v;
+    int64_t nk_sb, nk_sh, nv_sb, nv_sh;  // element strides
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
 };
@@ -372,12 +379,22 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                 const int hk = unit % p.Hkv, b = unit / p.Hkv;
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % NSTAGE;
-                    if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                    if (it >= NSTAGE) {
+                        // measurement aid (debug_skip & 4): the producer alone recycles the ring
+                        if (p.debug_skip & 4) ok = mbar_wait(&full[s], ((it / NSTAGE) - 1) & 1);
+                        else ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
+                    }
                     if (!ok) break;
                     unsigned char *kt = stages + (size_t)s * 2 * TILE_BYTES;
                     unsigned char *vt = kt + TILE_BYTES;
                     mbar_expect_tx(&full[s], 2 * TILE_BYTES);
                     const int tok = (t0 + j) * TILE_T;
+                    if (p.debug_skip & 2) {
+                        const int64_t off = b * p.kv_sb + hk * p.kv_sh + (int64_t)tok * p.kv_st;
+                        bulk_load(kt, p.k_base + off, TILE_BYTES, &full[s]);
+                        bulk_load(vt, p.v_base + off, TILE_BYTES, &full[s]);
+                        continue;
+                    }
 #pragma unroll
                     for (int bx = 0; bx < BOXES; ++bx) {
                         tma_load_4d(kt + bx * BOX_BYTES, &kmap, &full[s], bx * 64, tok, hk, b);
@@ -393,12 +410,16 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 
     // ---------------- consumers ----------------
     const int g = lane >> 2, c = lane & 3;
+    // Fused append: token T - 1 is not in the cache yet; the tiles are masked up to T - 2 and the
+    // new row is scored from its source by warp 0 of the CTA that owns the unit's last tile.
+    const bool fused = p.new_k != nullptr;
+    const int64_t t_cached = p.T - (fused ? 2 : 1);
     int64_t row_limit[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int r = g + 8 * half;
         const int l = r % p.L;
-        row_limit[half] = (r < R) ? (p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1) : -1;
+        row_limit[half] = (r < R) ? (p.causal ? min(t_cached, p.causal_offset + l) : t_cached) : -1;
     }
     const int blk = warp;
     uint32_t k_off[2];
@@ -443,14 +464,14 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
         for (int j = 0; j < n; ++j, ++it) {
-            if (!ok) continue;  // a wait ran out earlier: walk on to the barriers below
+            if (!ok || (p.debug_skip & 4)) continue;  // a wait ran out earlier: walk on to the barriers below
             const int s = it % NSTAGE;
             ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, 10);
                 continue;
             }
-            if (p.debug_skip) {
+            if (p.debug_skip & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -535,6 +556,54 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        if (fused && warp == 0 && t0 + n == tiles) {
+            // ---- the step's new token: score q . k_new, fold it into this warp's state, store the rows ----
+            const T *kn = (const T *)p.new_k + b * p.nk_sb + hk * p.nk_sh;
+            const T *vn = (const T *)p.new_v + b * p.nv_sb + hk * p.nv_sh;
+            float dot[2] = {0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
+                const int d0 = bx * 64 + (2 * c + ps) * 8 + 4 * h;
+                const uint2 kw = *(const uint2 *)(kn + d0);
+                const float2 k01 = MmaType<T>::unpack(kw.x), k23 = MmaType<T>::unpack(kw.y);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const float2 q01 = MmaType<T>::unpack(qa[ks][half]), q23 = MmaType<T>::unpack(qa[ks][2 + half]);
+                    dot[half] += q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y;
+                }
+            }
+            float pn[2], alpha[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                dot[half] += __shfl_xor_sync(0xffffffffu, dot[half], 1);
+                dot[half] += __shfl_xor_sync(0xffffffffu, dot[half], 2);
+                const float sc_new = (g + 8 * half < R) ? dot[half] * p.scale_log2 : -INFINITY;
+                const float m_new = fmaxf(m_run[half], sc_new);
+                alpha[half] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[half] - m_new);
+                pn[half] = (m_new == -INFINITY) ? 0.f : fast_exp2(sc_new - m_new);
+                m_run[half] = m_new;
+                l_run[half] = l_run[half] * alpha[half] + (c == 0 ? pn[half] : 0.f);  // once per row
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT_O; ++nt) {
+                const float2 vv = MmaType<T>::unpack(*(const uint32_t *)(vn + 8 * nt + 2 * c));
+                o_acc[nt][0] = o_acc[nt][0] * alpha[0] + pn[0] * vv.x;
+                o_acc[nt][1] = o_acc[nt][1] * alpha[0] + pn[0] * vv.y;
+                o_acc[nt][2] = o_acc[nt][2] * alpha[1] + pn[1] * vv.x;
+                o_acc[nt][3] = o_acc[nt][3] * alpha[1] + pn[1] * vv.y;
+            }
+            // the append itself: rows of D elements, 16 bytes per lane
+            const int64_t row_off = b * p.kv_sb + hk * p.kv_sh + (p.T - 1) * p.kv_st;
+            constexpr int CHUNKS = D * 2 / 16;
+            for (int i = lane; i < 2 * CHUNKS; i += 32) {
+                const bool is_v = i >= CHUNKS;
+                const int ch = is_v ? i - CHUNKS : i;
+                const uint4 x = *(const uint4 *)((const unsigned char *)(is_v ? vn : kn) + ch * 16);
+                *(uint4 *)((is_v ? p.v_base : p.k_base) + row_off + ch * 16) = x;
+            }
         }
 
         // ---- end of the segment: merge the four warps, publish the partial, maybe merge the unit ----
@@ -1022,12 +1091,15 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
         const size_t red = (size_t)CONSUMER_WARPS * R * (a.D + 8) * 4 + (size_t)CONSUMER_WARPS * R * 8 + (size_t)R * nslots * 4;
         const size_t smem = ring + 2 * nstage * sizeof(uint64_t) + 64 + red + 1024;
         const size_t budget = (a.D <= 128 ? 112 : 224) * 1024;
-        if (!flat_off && smem <= budget && nslots <= 64) {
+        const bool fused_ok = !a.new_k || (a.L == 1 && a.mask.mode != KVC_MASK_CAUSAL && !((uintptr_t)a.new_k & 15) &&
+                                           !((uintptr_t)a.new_v & 15) && (a.nk_sb * 2) % 16 == 0 && (a.nk_sh * 2) % 16 == 0 &&
+                                           (a.nv_sb * 2) % 16 == 0 && (a.nv_sh * 2) % 16 == 0);
+        if (!flat_off && smem <= budget && nslots <= 64 && fused_ok) {
             const int64_t qrows_f = (int64_t)a.B * a.Hq * a.L;
             const size_t o_bytes_f = (size_t)qrows_f * nslots * a.D * sizeof(float);
             const size_t ml_bytes_f = (size_t)qrows_f * nslots * sizeof(float2);
             char *scratch_f = (char *)scratch_get(a.device, o_bytes_f + ml_bytes_f + 256, stream);
-            DecodeParams p;
+            DecodeParams p = {};
             p.q = a.q; p.out = a.out; p.out_dtype = a.q_dtype;
             p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
             p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
@@ -1039,8 +1111,12 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
             {
                 const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-                p.debug_skip = (e && e[0] == '1') ? 1 : 0;
+                p.debug_skip = e ? std::atoi(e) : 0;
             }
+            p.k_base = (unsigned char *)a.k.data; p.v_base = (unsigned char *)a.v.data;
+            p.kv_sb = a.k.sb * 2; p.kv_sh = a.k.sh * 2; p.kv_st = a.k.st * 2;
+            p.new_k = a.new_k; p.new_v = a.new_v;
+            p.nk_sb = a.nk_sb; p.nk_sh = a.nk_sh; p.nv_sb = a.nv_sb; p.nv_sh = a.nv_sh;
             p.causal_offset = a.mask.causal_offset;
             p.scale_log2 = a.scale * 1.4426950408889634f;
             p.tiles_all = (int)tiles;
@@ -1061,6 +1137,8 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             return 1;
         }
     }
+
+    if (a.new_k) return 0;  // only the flat decode kernel appends by itself; the caller appends and comes back
 
     // Units per (batch, head): minimise waves x (tiles per unit + fixed cost), with
     // `slots` CTAs resident at once; ties go to fewer splits.
@@ -1086,7 +1164,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     float *o_part = (float *)scratch;
     float2 *ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
 
-    DecodeParams p;
+    DecodeParams p = {};
     p.q = a.q; p.out = a.out; p.out_dtype = a.q_dtype;
     p.q_sb = a.q_sb; p.q_sh = a.q_sh; p.q_sl = a.q_sl;
     p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;

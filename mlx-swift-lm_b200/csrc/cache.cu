@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -251,7 +252,8 @@ int resolved_group_size(int requested, int kd, int vd) {
 // TurboQuantKVCache.update (TurboQuantKVCache.swift:802-846). Capacity grows
 // ahead of need, which the protocol surface cannot observe: every getter
 // exposes rows [0, offset) only.
-static void linear_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s) {
+static void linear_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
+                          bool defer_append = false) {
     const int64_t S = k.shape[2];
     const int64_t step = std::max<int32_t>(c->cfg.step, 1);
     if (!c->k.allocated()) {
@@ -265,7 +267,7 @@ static void linear_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v
         c->k.ensure(c->offset + S, c->offset, step, s);
         c->v.ensure(c->offset + S, c->offset, step, s);
     }
-    if (S > 0) append_pair(c->k, c->v, k, v, c->offset, s);
+    if (S > 0 && !defer_append) append_pair(c->k, c->v, k, v, c->offset, s);
     c->offset += S;
 }
 
@@ -449,6 +451,8 @@ void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor 
 // ---------------------------------------------------------------------
 // attention
 // ---------------------------------------------------------------------
+int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
+
 KVSource raw_source(const kvc_tensor &t) {
     KVSource s;
     s.kind = SRC_RAW;
@@ -752,6 +756,35 @@ void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, con
             return;
         }
         default: {
+            // Decode on a KVCacheSimple: the attention kernel appends the new row itself when it can
+            // (one launch per layer); otherwise the append runs first as its own launch.
+            static const bool fuse_off = [] {
+                const char *e = std::getenv("KVC_FUSED_APPEND");
+                return e && e[0] == '0';
+            }();
+            if (!fuse_off && c->cfg.kind == KVC_KIND_SIMPLE && k.shape[2] == 1 && q.shape[2] == 1 && !c->open_round &&
+                mask_mode != KVC_MASK_ARRAY && k.stride[3] == 1 && v.stride[3] == 1 &&
+                (k.dtype == KVC_BF16 || k.dtype == KVC_F16)) {
+                require4(k, "keys");
+                require4(v, "values");
+                KVC_REQUIRE(k.dtype == v.dtype && k.shape[0] == v.shape[0] && k.shape[1] == v.shape[1] && v.shape[2] == 1,
+                            "update: keys and values disagree on batch, heads or length");
+                c->restore.valid = false;
+                const int64_t prev = c->offset;
+                linear_update(c, k, v, s, /*defer_append=*/true);
+                kvc_tensor ck = c->k.view(c->offset), cv = c->v.view(c->offset);
+                AttnArgs a = make_attn_args(q, out, scale, KVC_MASK_NONE, nullptr, ck.shape[2], Hkv);
+                a.k = raw_source(ck);
+                a.v = raw_source(cv);
+                a.new_k = k.data; a.new_v = v.data;
+                a.nk_sb = k.stride[0]; a.nk_sh = k.stride[1];
+                a.nv_sb = v.stride[0]; a.nv_sh = v.stride[1];
+                if (launch_attention_decode(a, s) > 0) return;
+                append_pair(c->k, c->v, k, v, prev, s);
+                a.new_k = a.new_v = nullptr;
+                launch_attention(a, s);
+                return;
+            }
             kvc_tensor ck, cv;
             cache_update(c, k, v, s, &ck, &cv);
             AttnArgs a = make_attn_args(q, out, scale, mask_mode, mask, ck.shape[2], Hkv);

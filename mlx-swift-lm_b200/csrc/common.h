@@ -119,6 +119,10 @@ struct AttnArgs {
     MaskDesc mask;
     // TurboQuant: rotate queries by the key signs before scoring and un-rotate
     // the merged output by the value signs (device pointers to [D] floats).
+    // Fused append (decode, raw caches): the step's new key / value rows [B, Hkv, 1, D] have NOT been
+    // written to the cache yet; the kernel scores them from here and stores them at token T - 1 itself.
+    const void *new_k = nullptr, *new_v = nullptr;
+    int64_t nk_sb = 0, nk_sh = 0, nv_sb = 0, nv_sh = 0;  // element strides (inner stride 1)
     const float *q_signs = nullptr;
     const float *q_calib = nullptr;  // optional per-dim key-calibration scale
     const float *o_signs = nullptr;

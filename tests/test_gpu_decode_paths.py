@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, max_abs_diff, seeded, to_oracle
+from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -124,4 +124,34 @@ def test_chunked_prefill_through_the_cache(kvc, oracle, cuda):
         out = cache.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.09, mask)
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, 0.09, mask)
         assert max_abs_diff(out, ref) <= 2e-2, f"step {step}"
+    assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_append_decode_is_one_launch_and_bit_exact_cache(kvc, oracle, cuda, dtype):
+    """Decode on a KVCacheSimple: the attention kernel scores the new row from its source and writes
+    it into the cache itself (one launch per call); outputs match the oracle and the cache rows are
+    bit-identical, across a tile boundary (63 -> 66 tokens) and a growth step."""
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    g, o = kvc.KVCacheSimple(step=64), oracle.KVCacheSimple(step=64)
+    k, v = seeded((B, Hkv, 61, D), 1, dtype), seeded((B, Hkv, 61, D), 2, dtype)
+    g.update(k.to(cuda), v.to(cuda))
+    o.update(to_oracle(k), to_oracle(v))
+    for step in range(6):
+        q, k1, v1 = (seeded((B, Hq, 1, D), 10 + step, dtype), seeded((B, Hkv, 1, D), 20 + step, dtype),
+                     seeded((B, Hkv, 1, D), 30 + step, dtype))
+        kvc.launch_count(reset=True)
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
+        n = kvc.launch_count(reset=True)
+        assert n == 1 or g.offset in (65,), f"step {step}: {n} launches"     # 64 -> 65 grows the buffer (copies)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"step {step}"
+        for a, b in zip(g.state, o.state):
+            assert bits_equal(a, np.ascontiguousarray(b)), f"step {step}"
+    # an empty cache: the new token is the only one
+    e, eo = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    q, k1, v1 = seeded((B, Hq, 1, D), 90, dtype), seeded((B, Hkv, 1, D), 91, dtype), seeded((B, Hkv, 1, D), 92, dtype)
+    out = e.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), eo, D ** -0.5)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
