@@ -302,12 +302,12 @@ __device__ __forceinline__ void consumer_bar() {
 // red_ml[(warp * red_rows + r) * 2 + {0, 1}] = (max, sum): merges the warps, writes the
 // segment's partial, takes a ticket and, in the CTA that completes the unit, merges all
 // partials (log-sum-exp) and writes the output rows (through signs * H(.) / sqrt(D) when
-// o_signs is set). `work` holds red_rows * nslots floats, plus red_rows * D when o_signs is set.
+// o_signs is set). `work` holds red_rows * D floats when o_signs is set and is unused otherwise.
 template <int D, int NW>
 __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const float *red_o, const float *red_ml,
                                  int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R,
                                  int64_t x_unit = -1, int unit_tiles = 0) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x;
     constexpr int NT = NW * 32;
     consumer_bar<NW>();
     // the unit's flat tile range: uniform units unless the caller passes a var-len range
@@ -347,44 +347,48 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
     consumer_bar<NW>();
     if (*flag) {
         __threadfence();
-        for (int r = warp; r < R; r += NW) {
-            float m = -INFINITY;
-            for (int s = lane; s < expected; s += 32) m = fmaxf(m, __ldcg(&u.ml_part[(qrow0 + r) * f.nslots + s]).x);
+        // Every thread merges its own (row, dim) elements: the (max, sum) pairs and the partial
+        // values of all slots are loaded together (one round trip), the weights are recomputed per
+        // element (a unit has a handful of slots).
+        float *rows = work;  // [R][D], only for the rotated (TurboQuant) output
+        for (int i = tid; i < R * D; i += NT) {
+            const int r = i / D, d = i % D;
+            const float2 *mlp = u.ml_part + (qrow0 + r) * f.nslots;
+            const float *src = u.o_part + ((qrow0 + r) * f.nslots) * D + d;
+            float m = -INFINITY, o = 0.f, lsum = 0.f;
+            for (int s0 = 0; s0 < expected; s0 += 8) {   // all loads of a batch of 8 slots are issued together
+                float2 ml[8];
+                float ov[8];
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            float lsum = 0.f;
-            for (int s = lane; s < expected; s += 32) {
-                const float2 ml = __ldcg(&u.ml_part[(qrow0 + r) * f.nslots + s]);
-                const float fw = (ml.x == -INFINITY || ml.y <= 0.f) ? 0.f : fast_exp2(ml.x - m);
-                work[r * f.nslots + s] = fw;
-                lsum += ml.y * fw;
+                for (int j = 0; j < 8; ++j) {
+                    const bool in = s0 + j < expected;
+                    ml[j] = in ? __ldcg(&mlp[s0 + j]) : make_float2(-INFINITY, 0.f);
+                    ov[j] = in ? __ldcg(src + (int64_t)(s0 + j) * D) : 0.f;
+                }
+                float mb = m;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mb = fmaxf(mb, (ml[j].y > 0.f) ? ml[j].x : -INFINITY);
+                const float keep = (m == -INFINITY) ? 0.f : fast_exp2(m - mb);   // rescale what earlier batches gave
+                o *= keep;
+                lsum *= keep;
+                m = mb;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float fw = (ml[j].x == -INFINITY || ml[j].y <= 0.f) ? 0.f : fast_exp2(ml[j].x - m);
+                    lsum = fmaf(ml[j].y, fw, lsum);
+                    o = fmaf(ov[j], fw, o);
+                }
             }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            __syncwarp();
-            for (int s = lane; s < expected; s += 32) work[r * f.nslots + s] *= inv;
-        }
-        consumer_bar<NW>();
-        if (!u.o_signs) {
-            for (int i = tid; i < R * D; i += NT) {
-                const int r = i / D, d = i % D;
-                float o = 0.f;
-                const float *src = u.o_part + ((qrow0 + r) * f.nslots) * D + d;
-                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * f.nslots + s], o);
+            o = lsum > 0.f ? o / lsum : 0.f;
+            if (!u.o_signs) {
                 const int hq = hk * rep + r / u.L, lq = r % u.L;
                 store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, o);
-            }
-        } else {
-            // TurboQuant values: the merged rows are in the rotated basis; out = signs * H(o) / sqrt(D).
-            float *rows = work + f.red_rows * f.nslots;  // [R][D]
-            for (int i = tid; i < R * D; i += NT) {
-                const int r = i / D, d = i % D;
-                float o = 0.f;
-                const float *src = u.o_part + ((qrow0 + r) * f.nslots) * D + d;
-                for (int s = 0; s < expected; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * f.nslots + s], o);
+            } else {
                 rows[i] = o;
             }
+        }
+        if (u.o_signs) {
+            // TurboQuant values: the merged rows are in the rotated basis; out = signs * H(o) / sqrt(D).
             for (int half = 1; half < D; half <<= 1) {
                 consumer_bar<NW>();
                 for (int pidx = tid; pidx < R * (D / 2); pidx += NT) {

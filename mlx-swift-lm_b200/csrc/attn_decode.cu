@@ -62,6 +62,7 @@ struct DecodeParams {
     int32_t row_blocks;  // chunk kernel: 64-row blocks per (batch, head)
     int32_t tiles_all;   // chunk kernel: tiles covering all T tokens
     FlatPlan flat;       // flat kernel
+    int32_t q_bulk;      // flat kernel: the unit's query rows are one contiguous 16-byte aligned block
     // cache arrays as plain pointers (byte strides): fused append target, and the measurement aid
     // debug_skip & 2 (linear bulk copies of the same bytes instead of the tiled TMA loads)
     unsigned char *k_base, *v_base;
@@ -350,17 +351,28 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     float *red_o = (float *)(is_last + 4);                                   // [4][red_rows][RED_STRIDE]
     float *red_ml = red_o + CONSUMER_WARPS * fp.red_rows * RED_STRIDE;       // [4][red_rows][2]
     float *work = red_ml + CONSUMER_WARPS * fp.red_rows * 2;                 // [red_rows][nslots]
+    // Query rows of a segment's unit, brought in by the producer with one bulk copy (two buffers):
+    // plain loads issued by the consumers while the tile stream saturates the memory system cost
+    // several microseconds per segment.
+    uint64_t *qfull = (uint64_t *)(work + ((fp.red_rows * fp.nslots + 3) & ~3));   // keeps qbuf 16-byte aligned
+    uint64_t *qempty = qfull + 2;
+    unsigned char *qbuf = (unsigned char *)(qempty + 2);                      // [2][red_rows][D] elements
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;
     const int tiles = fp.tiles;
     const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
+    const uint32_t q_bytes = (uint32_t)R * D * 2;
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qfull[s], 1);
+            mbar_init(&qempty[s], CONSUMER_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -372,11 +384,19 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
-            int it = 0;
-            for (int64_t x = x_lo; x < x_hi && ok;) {
+            int it = 0, sg = 0;
+            for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 const int unit = (int)(x / tiles), t0 = (int)(x % tiles);
                 const int n = (int)min((int64_t)(tiles - t0), x_hi - x);
                 const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                if (p.q_bulk) {
+                    const int qb = sg & 1;
+                    if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&qfull[qb], q_bytes);
+                    bulk_load(qbuf + (size_t)qb * q_bytes, (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh, q_bytes,
+                              &qfull[qb]);
+                }
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % NSTAGE;
                     if (it >= NSTAGE) {
@@ -409,6 +429,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     }
 
     // ---------------- consumers ----------------
+    if (p.debug_skip & 8) return;  // measurement aid: no consumer work at all (with 4: producer-only streaming)
     const int g = lane >> 2, c = lane & 3;
     // Fused append: token T - 1 is not in the cache yet; the tiles are masked up to T - 2 and the
     // new row is scored from its source by warp 0 of the CTA that owns the unit's last tile.
@@ -433,13 +454,43 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             v_off[cp] = (uint32_t)((blk * 16 + (mi & 1) * 8 + rr) * 128 + (((2 * cp + (mi >> 1)) ^ rr) << 4));
     }
 
-    int it = 0;
-    for (int64_t x = x_lo; x < x_hi;) {
+    int it = 0, sg = 0;
+    for (int64_t x = x_lo; x < x_hi; ++sg) {
         const int unit = (int)(x / tiles), t0 = (int)(x % tiles);
         const int n = (int)min((int64_t)(tiles - t0), x_hi - x);
         const int hk = unit % p.Hkv, b = unit / p.Hkv;
 
+        if (fused && warp == 0 && t0 + n == tiles && lane < 4) {
+            // the new rows are consumed at the end of the segment: pull them towards L2 now
+            const char *kn = (const char *)((const T *)p.new_k + b * p.nk_sb + hk * p.nk_sh);
+            const char *vn = (const char *)((const T *)p.new_v + b * p.nv_sb + hk * p.nv_sh);
+            const char *line = ((lane & 1) ? vn : kn) + (lane >> 1) * 128;
+            if ((lane >> 1) * 128 < D * 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+        }
         uint32_t qa[KSTEPS][4];
+        if (p.q_bulk) {
+            const int qb = sg & 1;
+            if (ok) {
+                ok = mbar_wait(&qfull[qb], (sg >> 1) & 1);
+                if (!ok && lane == 0) atomicExch(p.status, 13);
+            }
+            const unsigned char *qs = qbuf + (size_t)qb * q_bytes;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
+                const int d0 = bx * 64 + (2 * c + ps) * 8 + 4 * h;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int r = g + 8 * half;
+                    uint2 w = make_uint2(0u, 0u);
+                    if (r < R && ok) w = *(const uint2 *)(qs + ((size_t)r * D + d0) * 2);
+                    qa[ks][half] = w.x;
+                    qa[ks][2 + half] = w.y;
+                }
+            }
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&qempty[qb]);
+        } else
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             const int bx = ks / 4, ps = (ks >> 1) & 1, h = ks & 1;
@@ -448,7 +499,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             for (int half = 0; half < 2; ++half) {
                 const int r = g + 8 * half;
                 uint32_t w0 = 0, w1 = 0;
-                if (r < R) {
+                if (r < R && !(p.debug_skip & 32)) {
                     const int hq = hk * rep + r / p.L, l = r % p.L;
                     const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + d0;
                     w0 = *(const uint32_t *)qp;
@@ -558,7 +609,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             if (lane == 0) mbar_arrive(&empty[s]);
         }
 
-        if (fused && warp == 0 && t0 + n == tiles) {
+        if (fused && warp == 0 && t0 + n == tiles && !(p.debug_skip & 32)) {
             // ---- the step's new token: score q . k_new, fold it into this warp's state, store the rows ----
             const T *kn = (const T *)p.new_k + b * p.nk_sb + hk * p.nk_sh;
             const T *vn = (const T *)p.new_v + b * p.nv_sb + hk * p.nv_sh;
@@ -633,7 +684,8 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
         u.o_signs = nullptr;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
-        segment_epilogue<D, CONSUMER_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
+        if (!(p.debug_skip & 16))
+            segment_epilogue<D, CONSUMER_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
         x += n;
     }
 }
@@ -1088,7 +1140,8 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
         const int64_t nslots = (tiles + per - 1) / per + 1;
         const int nstage = a.D == 64 ? 6 : 3;
         const size_t ring = (size_t)nstage * 2 * (TILE_T * a.D * 2);
-        const size_t red = (size_t)CONSUMER_WARPS * R * (a.D + 8) * 4 + (size_t)CONSUMER_WARPS * R * 8 + (size_t)R * nslots * 4;
+        const size_t red = (size_t)CONSUMER_WARPS * R * (a.D + 8) * 4 + (size_t)CONSUMER_WARPS * R * 8 + (size_t)R * nslots * 4 +
+                           16 + 4 * sizeof(uint64_t) + (size_t)2 * R * a.D * 2;
         const size_t smem = ring + 2 * nstage * sizeof(uint64_t) + 64 + red + 1024;
         const size_t budget = (a.D <= 128 ? 112 : 224) * 1024;
         const bool fused_ok = !a.new_k || (a.L == 1 && a.mask.mode != KVC_MASK_CAUSAL && !((uintptr_t)a.new_k & 15) &&
@@ -1123,6 +1176,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.flat.tiles = (int)tiles;
             p.flat.per = (int)per; p.flat.rem = (int)rem;
             p.flat.nslots = (int)nslots; p.flat.red_rows = R;
+            p.q_bulk = (a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
 #define KVC_FLAT(TT, DD, NS) launch_flat_typed<TT, DD, NS>(kmap, vmap, p, (int)ctas, smem, stream)
             if (a.q_dtype == KVC_BF16) {
                 if (a.D == 64) KVC_FLAT(__nv_bfloat16, 64, 6);
