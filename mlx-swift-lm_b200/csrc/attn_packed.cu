@@ -59,6 +59,7 @@ struct AffineParams {
     int64_t causal_offset;
     float scale_log2;
     FlatPlan flat;  // decode8 kernel: flat tile decomposition
+    int32_t q_bulk; // decode8 kernel: a unit's query rows are one contiguous 16-byte aligned block
 };
 
 // One decode step for a list of independent caches (one sequence each, its own length) in one
@@ -655,17 +656,26 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     float *red_o = (float *)(is_last + 4);                               // [4][red_rows][RED_STRIDE]
     float *red_ml = red_o + PK_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
     float *work = red_ml + PK_WARPS * fp.red_rows * 2;                   // [red_rows][nslots]
+    // query rows of a segment's unit, brought in by the producer with one bulk copy (two buffers)
+    uint64_t *qfull = (uint64_t *)(work + ((fp.red_rows * fp.nslots + 3) & ~3));
+    uint64_t *qempty = qfull + 2;
+    unsigned char *qbuf = (unsigned char *)(qempty + 2);                  // [2][red_rows][D] elements
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;  // <= 8
     const int tiles = fp.tiles;
     const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
+    const uint32_t q_bytes = (uint32_t)R * D * 2;
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], PK_WARPS);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qfull[s], 1);
+            mbar_init(&qempty[s], PK_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -679,11 +689,20 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     if (warp == PK_WARPS) {
         // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
-            int it = 0;
-            for (int64_t x = x_lo; x < x_hi && ok;) {
+            int it = 0, sg = 0;
+            for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 int unit, tb, utiles, hk, b;
                 resolve_unit<VARLEN>(p, vt, x, tiles, unit, tb, utiles, hk, b);
                 const int n = (int)min((int64_t)(utiles - tb), x_hi - x);
+                if (p.q_bulk) {
+                    const int qb = sg & 1;
+                    if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
+                    if (!ok) break;
+                    const T *qsrc = VARLEN ? (const T *)vt.seq[b].q + (int64_t)hk * rep * p.q_sh
+                                           : (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh;
+                    mbar_expect_tx(&qfull[qb], q_bytes);
+                    bulk_load(qbuf + (size_t)qb * q_bytes, qsrc, q_bytes, &qfull[qb]);
+                }
                 const uint32_t *kc, *vc;
                 const T *ks, *kb, *vs, *vb;
                 if (VARLEN) {
@@ -723,7 +742,8 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     // ---------------- consumers: one segment per unit the CTA's tile range touches ----------------
     int st_i = 0;          // ring stage of the next tile and its phase bit, carried across segments
     uint32_t st_ph = 0;
-    for (int64_t x = x_lo; x < x_hi;) {
+    int sg = 0;
+    for (int64_t x = x_lo; x < x_hi; ++sg) {
         int unit, tile_begin, utiles, hk, b;
         resolve_unit<VARLEN>(p, vt, x, tiles, unit, tile_begin, utiles, hk, b);
         const int ntiles = (int)min((int64_t)(utiles - tile_begin), x_hi - x);
@@ -744,6 +764,15 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
         // 16 q', so every product is n q' 2^-20 (4-bit) or n q' 2^-24 (8-bit) = n q' / KSCALE.
         constexpr float LOWMUL = (BITS == 4) ? 16.f : 1.f;
         constexpr float KSCALE = (BITS == 4) ? 1048576.f : 16777216.f;
+        const T *q_stage = nullptr;   // the unit's rows [R][D] in shared memory when the producer staged them
+        if (p.q_bulk) {
+            const int qslot = sg & 1;
+            if (ok) {
+                ok = mbar_wait(&qfull[qslot], (sg >> 1) & 1);
+                if (!ok && lane == 0) atomicExch(p.status, 14);
+            }
+            q_stage = (const T *)(qbuf + (size_t)qslot * q_bytes);
+        }
         uint32_t qb[G][MPG][2];
         float qsum_own[G];
 #pragma unroll
@@ -755,10 +784,11 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
                 int dd[4];
                 kslot_dims<BITS>(gr * WPG + c * WPL + m / MPW, m % MPW, dd);
                 float x[4] = {0.f, 0.f, 0.f, 0.f};
-                if (g < R) {
+                if (g < R && ok) {
                     const int hq = hk * rep + g / p.L, l = g % p.L;
-                    const T *qp = VARLEN ? (const T *)vt.seq[b].q + hq * p.q_sh + l * p.q_sl
-                                         : (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
+                    const T *qp = q_stage ? q_stage + g * D
+                                  : VARLEN ? (const T *)vt.seq[b].q + hq * p.q_sh + l * p.q_sl
+                                           : (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         x[k] = __half2float(__float2half_rn(to_f32<T>(qp[dd[k]]) * p.scale_log2));
@@ -779,6 +809,10 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
             v *= (1.f / KSCALE);
             qsum[0][gr] = __shfl_sync(0xffffffffu, v, (2 * c) * 4);
             qsum[1][gr] = __shfl_sync(0xffffffffu, v, (2 * c + 1) * 4);
+        }
+        if (p.q_bulk) {
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&qempty[sg & 1]);
         }
         // Last visible token per row. Rows past R hold zero queries and are never written
         // out; they take the limit of a real row so that they do not force the mask path.
@@ -1069,7 +1103,8 @@ void launch_affine8_typed(const AffineParams &p, const VarlenAttnTable &vt, int 
     constexpr int RB = D * BITS / 8;
     constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
     const size_t red = (size_t)PK_WARPS * p.flat.red_rows * (D + 8) * 4 + (size_t)PK_WARPS * p.flat.red_rows * 8 +
-                       (size_t)p.flat.red_rows * p.flat.nslots * 4;
+                       (size_t)p.flat.red_rows * p.flat.nslots * 4 + 16 + 4 * sizeof(uint64_t) +
+                       (size_t)2 * p.flat.red_rows * D * 2;
     const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + red + 128;
     static size_t configured[64] = {0};
     const int dev = current_device();
@@ -1110,9 +1145,10 @@ const VarlenAttnTable kNoVarlen = {};
 
 int affine_resident_ctas(int D, int bits, int group, int rows) {
     // CTAs that fit an SM by shared memory: ring + cross-warp buffers (+1 KB the driver reserves)
-    const int ns = bits == 4 ? (D == 128 ? 6 : 8) : (D == 128 ? 4 : 6);
+    const int ns = bits == 4 ? (D == 128 ? 5 : 8) : (D == 128 ? 4 : 6);
     const size_t stage = (size_t)2 * PK_TILE * (D * bits / 8) + (size_t)4 * PK_TILE * (D / group) * 2;
-    const size_t red = (size_t)PK_WARPS * rows * (D + 8) * 4 + (size_t)PK_WARPS * rows * 8 + (size_t)rows * 64 * 4;
+    const size_t red = (size_t)PK_WARPS * rows * (D + 8) * 4 + (size_t)PK_WARPS * rows * 8 + (size_t)rows * 64 * 4 +
+                       64 + (size_t)2 * rows * D * 2;
     const size_t per_cta = ns * stage + red + 512 + 1024;
     return (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / per_cta));
 }
@@ -1172,6 +1208,9 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
     p.flat.nslots = (int)((max_tiles + p.flat.per - 1) / p.flat.per + 1);
     p.flat.red_rows = rep;
     if (p.flat.nslots > 64) return 0;
+    p.q_bulk = a0.q_sh == a0.D ? 1 : 0;
+    for (int i = 0; i < n; ++i)
+        if ((uintptr_t)args[i].q & 15) p.q_bulk = 0;
     const int64_t qrows = (int64_t)n * a0.Hq;
     const size_t o_bytes = (size_t)qrows * p.flat.nslots * a0.D * sizeof(float);
     const size_t ml_bytes = (size_t)qrows * p.flat.nslots * sizeof(float2);
@@ -1193,10 +1232,10 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
         return 1;                                                                            \
     }
     if (a0.q_dtype == KVC_BF16) {
-        KVC_AFFV(__nv_bfloat16, 128, 4, 64, 6)
+        KVC_AFFV(__nv_bfloat16, 128, 4, 64, 5)
         KVC_AFFV(__nv_bfloat16, 128, 8, 64, 4)
     } else {
-        KVC_AFFV(__half, 128, 4, 64, 6)
+        KVC_AFFV(__half, 128, 4, 64, 5)
         KVC_AFFV(__half, 128, 8, 64, 4)
     }
 #undef KVC_AFFV
@@ -1282,6 +1321,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     p.flat.tiles = (int)tiles;
     p.flat.per = (int)flat_per; p.flat.rem = (int)flat_rem;
     p.flat.nslots = (int)flat_slots; p.flat.red_rows = rep * a.L;
+    p.q_bulk = (a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
     const int units = decode8 ? (int)flat_ctas : (int)(bh * splits);
 
     const int bits = a.k.bits, group = a.k.group;
@@ -1292,17 +1332,17 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     }
     if (decode8) {
         if (a.q_dtype == KVC_BF16) {
-            KVC_AFF8(__nv_bfloat16, 128, 4, 64, 6)
+            KVC_AFF8(__nv_bfloat16, 128, 4, 64, 5)
             KVC_AFF8(__nv_bfloat16, 128, 8, 64, 4)
-            KVC_AFF8(__nv_bfloat16, 128, 4, 128, 6)
+            KVC_AFF8(__nv_bfloat16, 128, 4, 128, 5)
             KVC_AFF8(__nv_bfloat16, 128, 8, 128, 4)
             KVC_AFF8(__nv_bfloat16, 128, 8, 32, 4)
             KVC_AFF8(__nv_bfloat16, 64, 4, 64, 8)
             KVC_AFF8(__nv_bfloat16, 64, 8, 64, 6)
         } else {
-            KVC_AFF8(__half, 128, 4, 64, 6)
+            KVC_AFF8(__half, 128, 4, 64, 5)
             KVC_AFF8(__half, 128, 8, 64, 4)
-            KVC_AFF8(__half, 128, 4, 128, 6)
+            KVC_AFF8(__half, 128, 4, 128, 5)
             KVC_AFF8(__half, 128, 8, 128, 4)
             KVC_AFF8(__half, 128, 8, 32, 4)
             KVC_AFF8(__half, 64, 4, 64, 8)

@@ -66,6 +66,7 @@ struct TurboParams {
     int64_t causal_offset;
     float scale_log2;
     FlatPlan flat;  // flat tile decomposition (one wave of CTAs, segments per unit)
+    int32_t q_bulk; // a unit's query rows are one contiguous 16-byte aligned block
 };
 
 // Byte offset (inside a lane-replicated table) of the entry for pair j of a lane's word
@@ -128,18 +129,27 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
     // cross-warp buffers beside the ring (the ring stays live across segments)
     float *red_o = (float *)(is_last + 4);                               // [4][red_rows][RED_STRIDE]
     float *red_ml = red_o + TQ_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
-    float *work = red_ml + TQ_WARPS * fp.red_rows * 2;                   // [red_rows][nslots] + [red_rows][D]
+    float *work = red_ml + TQ_WARPS * fp.red_rows * 2;                   // [red_rows][D] (rotated output rows)
+    // query rows of a segment's unit, brought in by the producer with one bulk copy (two buffers)
+    uint64_t *qfull = (uint64_t *)(work + ((fp.red_rows * fp.nslots + fp.red_rows * D + 3) & ~3));  // keeps qbuf 16-byte aligned
+    uint64_t *qempty = qfull + 2;
+    unsigned char *qbuf = (unsigned char *)(qempty + 2);                  // [2][red_rows][D] elements
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = p.Hq / p.Hkv;
     const int R = rep * p.L;  // <= 8
     const int tiles = fp.tiles;
     const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
+    const uint32_t q_bytes = (uint32_t)R * D * 2;
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], TQ_WARPS);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qfull[s], 1);
+            mbar_init(&qempty[s], TQ_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -162,11 +172,19 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
     if (warp == TQ_WARPS) {
         // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
-            int it = 0;
-            for (int64_t x = x_lo; x < x_hi && ok;) {
+            int it = 0, sg = 0;
+            for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 const int unit = (int)(x / tiles), tb = (int)(x % tiles);
                 const int n = (int)min((int64_t)(tiles - tb), x_hi - x);
                 const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                if (p.q_bulk) {
+                    const int qb = sg & 1;
+                    if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&qfull[qb], q_bytes);
+                    bulk_load(qbuf + (size_t)qb * q_bytes, (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh, q_bytes,
+                              &qfull[qb]);
+                }
                 const uint32_t *kp = p.kp + b * p.kp_sb + hk * p.kp_sh;
                 const uint32_t *vp = p.vp + b * p.vp_sb + hk * p.vp_sh;
                 const float *kn = p.kn + b * p.kn_sb + hk * p.kn_sh;
@@ -194,19 +212,33 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
     constexpr int CT = TQ_WARPS * 32;
     int st_i = 0;          // ring stage of the next tile and its phase bit, carried across segments
     uint32_t st_ph = 0;
-    for (int64_t x = x_lo; x < x_hi;) {
+    int sg = 0;
+    for (int64_t x = x_lo; x < x_hi; ++sg) {
         const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
         const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
         const int hk = unit % p.Hkv, b = unit / p.Hkv;
         // ---- rotated queries of this unit: q' = H(signs * q) / sqrt(D) * scale * log2(e), rows past R zero ----
+        const T *q_stage = nullptr;
+        if (p.q_bulk) {
+            if (ok) {
+                ok = mbar_wait(&qfull[sg & 1], (sg >> 1) & 1);
+                if (!ok && lane == 0) atomicExch(p.status, 15);
+            }
+            q_stage = (const T *)(qbuf + (size_t)(sg & 1) * q_bytes);
+        }
         for (int i = tid; i < 8 * D; i += CT) {
             const int r = i / D, d = i % D;
             float xq = 0.f;
-            if (r < R) {
+            if (r < R && ok) {
                 const int hq = hk * rep + r / p.L, l = r % p.L;
-                xq = to_f32<T>(((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d]) * p.q_signs[d];
+                const T qv = q_stage ? q_stage[r * D + d] : ((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d];
+                xq = to_f32<T>(qv) * p.q_signs[d];
             }
             qrot[i] = xq;
+        }
+        if (p.q_bulk) {
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&qempty[sg & 1]);
         }
         for (int half = 1; half < D; half <<= 1) {
             consumer_bar<TQ_WARPS>();
@@ -417,7 +449,8 @@ constexpr size_t turbo_fixed_smem() {
 
 inline size_t turbo_red_smem(const FlatPlan &f) {
     return (size_t)TQ_WARPS * f.red_rows * (TQ_D + 8) * 4 + (size_t)TQ_WARPS * f.red_rows * 8 +
-           (size_t)f.red_rows * f.nslots * 4 + (size_t)f.red_rows * TQ_D * 4;
+           (size_t)f.red_rows * f.nslots * 4 + (size_t)f.red_rows * TQ_D * 4 + 4 * sizeof(uint64_t) +
+           (size_t)2 * f.red_rows * TQ_D * 2 + 16;
 }
 
 template <typename T, int KB, int VB, int NSTAGE>
@@ -531,6 +564,7 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.flat = plan;
+    p.q_bulk = (a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
     const int units = (int)ctas;
 
 #define KVC_TQ(TT, KK, VV, NS)                                  \
