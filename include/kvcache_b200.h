@@ -388,6 +388,28 @@ kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev,
                             const kvc_tensor *packed, const kvc_tensor *norms, void *stream);
 
 /* ------------------------------------------------------------------ */
+/* prompt-cache files (safetensors, shared with Python mlx-lm)          */
+/* ------------------------------------------------------------------ */
+
+/* savePromptCache(url:cache:metadata:) (KVCache.swift:1797-1846): tensors "i.j" = array j of cache
+ * i's state, metadata "0.i.j" = its metaState strings, "1.<key>" = user metadata, "2.i" = class
+ * name ("KVCache", "RotatingKVCache", "QuantizedKVCache", "TurboQuantKVCache"). Synchronises the
+ * stream (the arrays are copied to the host). */
+kvc_status kvc_save_prompt_cache(const char *path, kvc_cache *const *caches, int32_t count,
+                                 const char *const *meta_keys, const char *const *meta_values,
+                                 int32_t meta_count, void *stream);
+
+/* loadPromptCache(url:) (KVCache.swift:1859-1987, restoreCacheFromMetaState :2031-2138): rebuilds
+ * the caches of a file on `device` (-1 = current). Writes up to `capacity` handles (owned by the
+ * caller) and the count; the user metadata into meta_buf as NUL-terminated strings, key then value,
+ * closed by an empty key (*meta_needed = bytes needed; a smaller buffer is zero-filled). Call once
+ * with out_caches = NULL to size both. Corrupt files (wrong array / metadata counts, unknown
+ * class, sizes that do not match shapes) and files carrying model state are rejected. */
+kvc_status kvc_load_prompt_cache(const char *path, int32_t device, kvc_cache **out_caches, int32_t capacity,
+                                 int32_t *out_count, char *meta_buf, size_t meta_len, size_t *meta_needed,
+                                 void *stream);
+
+/* ------------------------------------------------------------------ */
 /* list-level dynamic conversion (generation loop: maybeQuantizeKVCache) */
 /* ------------------------------------------------------------------ */
 

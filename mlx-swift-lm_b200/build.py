@@ -32,6 +32,7 @@ SOURCES = [
     "cache.cu",
     "round.cu",
     "capi.cu",
+    "promptcache.cu",
     "comm.cu",
     "noalloc.cu",
 ]

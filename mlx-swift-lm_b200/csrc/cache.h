@@ -121,6 +121,11 @@ kvc_tensor cache_state_get(kvc_cache *c, int index);
 void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStream_t s);
 std::vector<std::string> cache_meta_state(const kvc_cache *c);
 void cache_set_meta_state(kvc_cache *c, const std::vector<std::string> &m);
+// prompt-cache files (promptcache.cu)
+void save_prompt_cache(const char *path, kvc_cache *const *caches, int count, const char *const *keys,
+                       const char *const *values, int meta_count, cudaStream_t s);
+void load_prompt_cache(const char *path, int device, std::vector<kvc_cache *> &out,
+                       std::vector<std::pair<std::string, std::string>> &user_meta, cudaStream_t s);
 kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s);
 kvc_cache *cache_to_quantized(const kvc_cache *c, int group, int bits, cudaStream_t s);
 kvc_cache *cache_to_unquantized(const kvc_cache *c, cudaStream_t s);

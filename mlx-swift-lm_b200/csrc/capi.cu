@@ -4,6 +4,8 @@
 // the C boundary.
 #include "cache.h"
 
+#include <string>
+#include <utility>
 #include <vector>
 
 #include <algorithm>
@@ -653,6 +655,56 @@ kvc_status kvc_to_turbo(const kvc_cache *c, int32_t key_bits, int32_t value_bits
     return guarded([&] {
         DeviceGuard dg(c->device);
         *out = kvc::cache_to_turbo(c, key_bits, value_bits, key_group_size, as_stream(stream));
+    });
+}
+
+// ---------------------------------------------------------------------
+// prompt-cache files
+// ---------------------------------------------------------------------
+kvc_status kvc_save_prompt_cache(const char *path, kvc_cache *const *caches, int32_t count,
+                                 const char *const *meta_keys, const char *const *meta_values, int32_t meta_count,
+                                 void *stream) {
+    if (!path || (!caches && count > 0) || ((!meta_keys || !meta_values) && meta_count > 0))
+        return set_error(KVC_ERR_INVALID_ARG, "kvc_save_prompt_cache: null argument");
+    for (int i = 0; i < count; ++i) KVC_CHECK_HANDLE(caches[i]);
+    return guarded([&] {
+        DeviceGuard dg(count > 0 ? caches[0]->device : -1);
+        kvc::save_prompt_cache(path, caches, count, meta_keys, meta_values, meta_count, as_stream(stream));
+    });
+}
+
+kvc_status kvc_load_prompt_cache(const char *path, int32_t device, kvc_cache **out_caches, int32_t capacity,
+                                 int32_t *out_count, char *meta_buf, size_t meta_len, size_t *meta_needed,
+                                 void *stream) {
+    if (!path || !out_count) return set_error(KVC_ERR_INVALID_ARG, "kvc_load_prompt_cache: null argument");
+    *out_count = 0;
+    return guarded([&] {
+        DeviceGuard dg(device);
+        std::vector<kvc_cache *> caches;
+        std::vector<std::pair<std::string, std::string>> meta;
+        kvc::load_prompt_cache(path, device, caches, meta, as_stream(stream));
+        // NUL-terminated strings, key then value, closed by an empty key: values may hold any text
+        std::string joined;
+        for (size_t i = 0; i < meta.size(); ++i) {
+            joined += meta[i].first;
+            joined += '\0';
+            joined += meta[i].second;
+            joined += '\0';
+        }
+        joined += '\0';
+        if (meta_needed) *meta_needed = joined.size();
+        if (meta_buf && meta_len) {
+            if (meta_len >= joined.size()) std::memcpy(meta_buf, joined.data(), joined.size());
+            else std::memset(meta_buf, 0, meta_len);   // too small: reads as "no entries"
+        }
+        if ((int)caches.size() > capacity || !out_caches) {
+            for (kvc_cache *c : caches) kvc_free(c);
+            *out_count = (int32_t)caches.size();
+            if (out_caches) kvc::fail(KVC_ERR_INVALID_ARG, "kvc_load_prompt_cache: the file holds more caches than `capacity`");
+            return;
+        }
+        for (size_t i = 0; i < caches.size(); ++i) out_caches[i] = caches[i];
+        *out_count = (int32_t)caches.size();
     });
 }
 

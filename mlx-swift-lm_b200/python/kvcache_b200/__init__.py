@@ -117,6 +117,13 @@ _lib.kvc_make_mask.argtypes = [_vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int
                                ctypes.POINTER(ctypes.c_int64), _vp, _vp]
 _lib.kvc_affine_quantize.argtypes = [_TP, ctypes.c_int32, ctypes.c_int32, _TP, _TP, _TP, _vp]
 _lib.kvc_affine_dequantize.argtypes = [_TP, _TP, _TP, ctypes.c_int32, ctypes.c_int32, _TP, _vp]
+_lib.kvc_save_prompt_cache.argtypes = [ctypes.c_char_p, ctypes.POINTER(_vp), ctypes.c_int32, ctypes.POINTER(ctypes.c_char_p),
+                                       ctypes.POINTER(ctypes.c_char_p), ctypes.c_int32, _vp]
+_lib.kvc_save_prompt_cache.restype = ctypes.c_int32
+_lib.kvc_load_prompt_cache.argtypes = [ctypes.c_char_p, ctypes.c_int32, ctypes.POINTER(_vp), ctypes.c_int32,
+                                       ctypes.POINTER(ctypes.c_int32), ctypes.c_char_p, ctypes.c_size_t,
+                                       ctypes.POINTER(ctypes.c_size_t), _vp]
+_lib.kvc_load_prompt_cache.restype = ctypes.c_int32
 _lib.kvc_resolve_turbo_scheme.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
 _lib.kvc_resolve_turbo_scheme.restype = ctypes.c_int32
 _lib.kvc_resolve_affine_scheme.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
@@ -238,6 +245,8 @@ def _from_pointer(ptr: int, nbytes: int, dtype, device):
 def _stream_ptr(stream=None) -> int:
     torch = _torch()
     if stream is None:
+        if not torch.cuda.is_available():
+            return 0   # host-only calls (file headers, empty caches) on a machine without a device
         stream = torch.cuda.current_stream()
     return int(stream.cuda_stream)
 
@@ -844,3 +853,49 @@ def maybe_turbo_quantize_kv_cache(caches: List["KVCache"], key_bits: int, value_
     """maybeTurboQuantizeKVCache: rewrites the list in place; False while a layer still waits."""
     return _rewrite_list(caches, lambda arr, n, done: _lib.kvc_maybe_turbo_quantize(
         arr, n, key_bits, value_bits, quantized_kv_start, _stream_ptr(stream), done))
+
+
+# ---------------------------------------------------------------------------
+# prompt-cache files (savePromptCache / loadPromptCache)
+# ---------------------------------------------------------------------------
+
+def save_prompt_cache(path: str, caches: Sequence["KVCache"], metadata: Optional[dict] = None, stream=None) -> None:
+    """savePromptCache(url:cache:metadata:): a safetensors file in the mlx-lm prompt-cache layout."""
+    metadata = metadata or {}
+    n = len(caches)
+    arr = (_vp * n)(*[c._h for c in caches])
+    keys = (ctypes.c_char_p * len(metadata))(*[str(k).encode() for k in metadata])
+    vals = (ctypes.c_char_p * len(metadata))(*[str(v).encode() for v in metadata.values()])
+    check(_lib.kvc_save_prompt_cache(os.fsencode(path), arr, n, keys, vals, len(metadata), _stream_ptr(stream)))
+
+
+def load_prompt_cache(path: str, device: int = -1, stream=None):
+    """loadPromptCache(url:) -> (caches, metadata)."""
+    count, need = ctypes.c_int32(), ctypes.c_size_t()
+    # first pass: how many caches, how much metadata
+    check(_lib.kvc_load_prompt_cache(os.fsencode(path), device, None, 0, ctypes.byref(count), None, 0,
+                                     ctypes.byref(need), _stream_ptr(stream)))
+    n = int(count.value)
+    arr = (_vp * max(n, 1))()
+    buf = ctypes.create_string_buffer(max(int(need.value), 1))
+    check(_lib.kvc_load_prompt_cache(os.fsencode(path), device, arr, n, ctypes.byref(count), buf, len(buf),
+                                     ctypes.byref(need), _stream_ptr(stream)))
+    torch_dev = None
+    try:
+        import torch
+        if torch.cuda.is_available():
+            torch_dev = torch.device("cuda", torch.cuda.current_device() if device < 0 else device)
+    except Exception:
+        pass
+    caches = []
+    for i in range(int(count.value)):
+        h = int(ctypes.cast(arr[i], ctypes.c_void_p).value)
+        kind = int(_lib.kvc_kind_of(ctypes.c_void_p(h)))
+        cls = {KIND_SIMPLE: KVCacheSimple, KIND_ROTATING: RotatingKVCache, KIND_QUANTIZED: QuantizedKVCache,
+               KIND_TURBO: TurboQuantKVCache}[kind]
+        obj = cls.__new__(cls)
+        KVCache.__init__(obj, h, torch_dev)
+        caches.append(obj)
+    parts = buf.raw[:max(int(need.value) - 2, 0)].decode().split("\0") if int(need.value) > 1 else []
+    meta = {parts[i]: parts[i + 1] for i in range(0, len(parts) - 1, 2)}
+    return caches, meta

@@ -266,3 +266,76 @@ def test_list_level_dynamic_conversion(kvc, cuda):
     assert kvc.maybe_affine_quantize_kv_cache(caches2, 4, 64, compression_start=0) is True
     assert [type(c).__name__ for c in caches2] == ["QuantizedKVCache"] * 2 + ["RotatingKVCache"] + ["QuantizedKVCache"] * 5
     assert all(c.bits == 4 for c in caches2 if isinstance(c, kvc.QuantizedKVCache))
+
+
+def _filled(kvc, oracle, cuda, dtype):
+    """Four caches (library, oracle) over the same seeded tokens: simple, rotating past its window,
+    affine-quantized, turbo in its compressed phase."""
+    B, H, D = 1, 2, 64
+    g = [kvc.KVCacheSimple(), kvc.RotatingKVCache(max_size=16, keep=2), kvc.QuantizedKVCache(32, 4),
+         kvc.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=11)]
+    o = [oracle.KVCacheSimple(), oracle.RotatingKVCache(max_size=16, keep=2), oracle.QuantizedKVCache(32, 4),
+         oracle.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=11)]
+    seed = 300
+    for S in (12, 1, 1, 9, 1):
+        k, v = seeded((B, H, S, D), seed, dtype), seeded((B, H, S, D), seed + 1, dtype)
+        q = seeded((B, 2 * H, S, D), seed + 2, dtype)
+        seed += 3
+        for gc, oc in zip(g, o):
+            kvc.attention_with_cache_update(q.to(cuda), k.to(cuda), v.to(cuda), gc, D ** -0.5, "causal" if S > 1 else "none")
+            oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), oc, D ** -0.5,
+                                               "causal" if S > 1 else "none")
+    return g, o
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prompt_cache_file_round_trip(kvc, oracle, cuda, tmp_path, dtype):
+    """savePromptCache / loadPromptCache (KVCache.swift:1797-1913): a file written by the library holds
+    exactly the oracle caches' state arrays and metaState strings; loading it back (and loading the
+    oracle's own file) rebuilds caches whose state is bit-identical and whose next decode step
+    matches the original cache's bit for bit."""
+    import prompt_cache_oracle as pco
+    g, o = _filled(kvc, oracle, cuda, dtype)
+    assert g[3].is_compressed
+    path = str(tmp_path / "prompt.safetensors")
+    kvc.save_prompt_cache(path, g, {"tokens": "24"})
+    entries, user = pco.load(path)
+    assert user == {"tokens": "24"}
+    for e, oc in zip(entries, o):
+        want = pco.entry_of(oc, bf16=dtype == torch.bfloat16)
+        assert (e.class_name, e.meta_state) == (want.class_name, want.meta_state)
+        assert len(e.state) == len(want.state)
+        for a, b, abf, bbf in zip(e.state, want.state, e.bf16, want.bf16):
+            assert a.shape == b.shape and a.dtype == b.dtype and abf == bbf
+            assert a.tobytes() == b.tobytes()
+
+    opath = str(tmp_path / "oracle.safetensors")
+    pco.save(opath, [pco.entry_of(oc, bf16=dtype == torch.bfloat16) for oc in o], {"tokens": "24"})
+    B, H, D = 1, 2, 64
+    k, v = seeded((B, H, 1, D), 900, dtype).to(cuda), seeded((B, H, 1, D), 901, dtype).to(cuda)
+    q = seeded((B, 2 * H, 1, D), 902, dtype).to(cuda)
+    want_out = [kvc.attention_with_cache_update(q, k, v, c.copy(), D ** -0.5, "none") for c in g]
+    for p in (path, opath):
+        loaded, meta = kvc.load_prompt_cache(p)
+        assert meta == {"tokens": "24"}
+        assert [type(c) for c in loaded] == [type(c) for c in g]
+        for lc, gc, w in zip(loaded, g, want_out):
+            assert lc.offset == gc.offset and list(lc.meta_state) == list(gc.meta_state)
+            ls, gs = lc.state, gc.state
+            assert len(ls) == len(gs)
+            for a, b in zip(ls, gs):
+                assert a.shape == b.shape and a.dtype == b.dtype and torch.equal(a, b)
+            got = kvc.attention_with_cache_update(q, k, v, lc, D ** -0.5, "none")
+            assert torch.equal(got, w)
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_prompt_cache_legacy_rotating_metadata(kvc, cuda, tmp_path):
+    """KVCacheTests.swift:590-603: a five-field RotatingKVCache metaState (files written before the
+    capacity origin existed) loads, and reads back with the model-native origin appended."""
+    import prompt_cache_oracle as pco
+    p = str(tmp_path / "legacy.safetensors")
+    pco.save(p, [pco.Entry("RotatingKVCache", [np.zeros((1, 1, 1, 1), np.float32)] * 2, ["0", "32", "256", "1", "1"])])
+    (rot,), _ = kvc.load_prompt_cache(p)
+    assert isinstance(rot, kvc.RotatingKVCache)
+    assert list(rot.meta_state) == ["0", "32", "256", "1", "1", "modelNative"]

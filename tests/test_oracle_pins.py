@@ -271,3 +271,83 @@ def test_scheme_tables_and_boundary_protection_host_logic(kvc):
     # min(2, eligible / 2): three eligible layers protect one on each end, one protects none
     assert kvc.turbo_protected_layers([S, S, S], 4, 4) == [True, False, True]
     assert kvc.turbo_protected_layers([S], 4, 4) == [False]
+
+
+def test_prompt_cache_file_format_and_corrupt_rejection(kvc, tmp_path):
+    """savePromptCache / loadPromptCache wire format (KVCache.swift:1797-1846, :2031-2138) on empty
+    caches (no device needed): key layout of the safetensors header, class names, metaState strings,
+    user metadata; corrupt files are rejected the way restoreCacheFromMetaState rejects them."""
+    import json
+    import struct
+    caches = [kvc.KVCacheSimple(), kvc.RotatingKVCache(max_size=32, keep=4), kvc.QuantizedKVCache(32, 4),
+              kvc.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=7)]
+    path = str(tmp_path / "prompt.safetensors")
+    kvc.save_prompt_cache(path, caches, {"model": "tiny", "note": 'a "quoted"\nline'})
+    raw = open(path, "rb").read()
+    hlen = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + hlen])
+    meta = header["__metadata__"]
+    assert [meta[f"2.{i}"] for i in range(4)] == ["KVCache", "RotatingKVCache", "QuantizedKVCache", "TurboQuantKVCache"]
+    assert meta["0.0.0"] == ""                                      # KVCacheSimple: the single empty placeholder
+    assert [meta[f"0.1.{j}"] for j in range(5)] == ["4", "32", "256", "0", "0"]     # keep, maxSize, step, offset, idx
+    assert [meta[f"0.2.{j}"] for j in range(4)] == ["256", "0", "32", "4"]          # step, offset, groupSize, bits
+    assert meta["1.model"] == "tiny" and meta["1.note"] == 'a "quoted"\nline'
+    assert set(header) == {"__metadata__"}                           # empty caches carry no tensors
+
+    loaded, user = kvc.load_prompt_cache(path)
+    assert [type(c).__name__ for c in loaded] == ["KVCacheSimple", "RotatingKVCache", "QuantizedKVCache", "TurboQuantKVCache"]
+    assert user == {"model": "tiny", "note": 'a "quoted"\nline'}
+    assert loaded[1].max_size == 32 and list(loaded[1].meta_state)[:3] == ["4", "32", "256"]
+    assert loaded[2].group_size == 32 and loaded[2].bits == 4
+    assert list(loaded[3].meta_state) == list(caches[3].meta_state)
+
+    # the oracle's reader accepts the library's file and sees the same triples; the library accepts the oracle's
+    import prompt_cache_oracle as pco
+    entries, ouser = pco.load(path)
+    assert ouser == user
+    assert [(e.class_name, e.meta_state, len(e.state)) for e in entries] == \
+        [(pco.class_name_of(c), list(c.meta_state), 0) for c in caches]
+    opath = str(tmp_path / "oracle.safetensors")
+    pco.save(opath, entries, {"k": "v"})
+    again, user2 = kvc.load_prompt_cache(opath)
+    assert user2 == {"k": "v"}
+    assert [list(c.meta_state) for c in again] == [list(c.meta_state) for c in caches]
+    with pytest.raises(kvc.KVCError, match="reserved"):
+        kvc.save_prompt_cache(path, caches, {"__mlx_lm_state_count": "1"})
+
+    def fixture(class_name, array_count, metadata, shape=(1, 1, 1, 1)):
+        """writePromptCacheFixture of the reference's KVCacheTests.swift:30-47: float32 zero arrays "0.j"."""
+        p = str(tmp_path / "fixture.safetensors")
+        pco.save(p, [pco.Entry(class_name, [np.zeros(shape, np.float32)] * array_count, metadata)])
+        return p
+
+    # KVCacheTests.swift:566-588: invalid metadata and invalid state rank are rejected
+    for bad in (("KVCacheSimple", 0, ["unexpected"]),
+                ("RotatingKVCache", 0, ["0", "32", "invalid", "0", "0", "modelNative"]),
+                ("RotatingKVCache", 0, ["0", "32", "256", "0", "0", "invalid-origin"]),
+                ("QuantizedKVCache", 0, ["256", "invalid", "64", "4"]),
+                ("KVCacheSimple", 2, [""], (1, 1))):
+        with pytest.raises(kvc.KVCError):
+            kvc.load_prompt_cache(fixture(*bad))
+        with pytest.raises(pco.PromptCacheError):
+            pco.load(fixture(*bad))
+
+    def write(meta_dict, tensors=None):
+        blob = json.dumps({"__metadata__": meta_dict, **(tensors or {})}).encode()
+        p = str(tmp_path / "bad.safetensors")
+        open(p, "wb").write(struct.pack("<Q", len(blob)) + blob)
+        return p
+
+    for bad in ({"2.0": "KVCache", "0.0.0": "x"},                       # placeholder must be empty
+                {"2.0": "RotatingKVCache", "0.0.0": "0", "0.0.1": "8"},  # 2 metadata entries instead of 5 / 6
+                {"2.0": "QuantizedKVCache", "0.0.0": "256", "0.0.1": "0", "0.0.2": "sixty-four", "0.0.3": "4"},
+                {"2.0": "NoSuchCache", "0.0.0": ""},
+                {"2.0": "KVCache", "2.1": "KVCache", "0.0.0": ""},             # class count != metaState count
+                {"2.0": "KVCache", "0.0.0": "", "1.__mlx_lm_state_version": "1", "1.__mlx_lm_state_count": "1"},
+                {"2.0": "__mlx_lm_state_v1__:KVCache", "0.0.0": ""}):
+        with pytest.raises(kvc.KVCError):
+            kvc.load_prompt_cache(write(bad))
+    # an array whose cache index has no class entry (unflattenArrays, KVCache.swift:2166-2185)
+    with pytest.raises(kvc.KVCError):
+        kvc.load_prompt_cache(write({"2.0": "KVCache", "0.0.0": ""},
+                                    {"3.0": {"dtype": "F32", "shape": [1, 1, 1, 1], "data_offsets": [0, 4]}}))
