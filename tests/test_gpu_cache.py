@@ -275,7 +275,9 @@ def _filled(kvc, oracle, cuda, dtype):
     g = [kvc.KVCacheSimple(), kvc.RotatingKVCache(max_size=16, keep=2), kvc.QuantizedKVCache(32, 4),
          kvc.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=11)]
     o = [oracle.KVCacheSimple(), oracle.RotatingKVCache(max_size=16, keep=2), oracle.QuantizedKVCache(32, 4),
-         oracle.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=11)]
+         oracle.TurboQuantKVCache(bits=4, key_bits=3, value_bits=4, seed=11,
+                                  key_codebook=np.array(kvc.turbo_codebook(D, 3)[0], dtype=np.float32),
+                                  value_codebook=np.array(kvc.turbo_codebook(D, 4)[0], dtype=np.float32))]
     seed = 300
     for S in (12, 1, 1, 9, 1):
         k, v = seeded((B, H, S, D), seed, dtype), seeded((B, H, S, D), seed + 1, dtype)
