@@ -127,6 +127,129 @@ __global__ void affine_quantize_warp_kernel(QuantAppendArgs ka, QuantAppendArgs 
                             (T *)a.biases + b * a.g_sb + h * a.g_sh + t * a.g_st, a.group, a.bits, lane);
 }
 
+// Codes of VEC values of one group. The correctly rounded quotient (w - bias) / scale lies between
+// the products of (w - bias) with the reciprocal scaled by 1 -+ 4e-7. Each product is rounded to an
+// integer by a fused multiply-add with 1.5 * 2^23 (one rounding, ties to even, like rint): when both
+// ends give the same integer that is rint of the quotient as well; when they differ for any value
+// the lane redoes its values with the division itself. So the codes are those of affine_code bit for
+// bit. The clamps run on the biased floats (a NaN becomes code 0, as fmaxf(NaN, 0) makes it), and
+// the words accumulate the float bit patterns by multiply-add; MAGIC_SUM removes the bias's share.
+template <int VEC, int BITS>
+__device__ __forceinline__ uint64_t affine_codes_vec(const float (&v)[VEC], float scale, float bias) {
+    constexpr float n_bins = (float)((1 << BITS) - 1);
+    constexpr float MAGIC = 12582912.f;          // 1.5 * 2^23: x + MAGIC leaves rint(x) in the low mantissa bits
+    constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+    constexpr int PER_WORD = (VEC * BITS > 32) ? 32 / BITS : VEC;   // values per 32-bit word
+    uint32_t magic_sum = 0;
+#pragma unroll
+    for (int i = 0; i < PER_WORD; ++i) magic_sum += MAGIC_BITS << (i * BITS);
+    const float inv = __frcp_rn(scale);
+    const float inv_lo = fmaf(inv, -4e-7f, inv), inv_hi = fmaf(inv, 4e-7f, inv);
+    uint32_t w[2] = {0u, 0u};
+    uint32_t differ = 0;
+#pragma unroll
+    for (int i = VEC - 1; i >= 0; --i) {
+        const float x = __fsub_rn(v[i], bias);
+        const float u_lo = __fmaf_rn(x, inv_lo, MAGIC), u_hi = __fmaf_rn(x, inv_hi, MAGIC);
+        differ |= __float_as_uint(u_lo) ^ __float_as_uint(u_hi);
+        const float u = fminf(fmaxf(u_lo, MAGIC), MAGIC + n_bins);
+        w[i / PER_WORD] = (w[i / PER_WORD] << BITS) + __float_as_uint(u);
+    }
+    w[0] -= magic_sum;
+    if (VEC * BITS > 32) w[1] -= magic_sum;
+    // (products beyond 2^22 leave the integer grid of the biased floats but are far outside the code
+    // range, so the clamps settle them.) A reciprocal below 1e-30 has lost bits to the subnormal
+    // range: exact path, like a straddled tie.
+    if (differ != 0u || !(fabsf(inv) > 1e-30f) || !(fabsf(inv) < 1e30f)) {
+        w[0] = w[1] = 0u;
+#pragma unroll
+        for (int i = VEC - 1; i >= 0; --i)
+            w[i / PER_WORD] = (w[i / PER_WORD] << BITS) | affine_code(v[i], scale, bias, n_bins);
+    }
+    return (uint64_t)w[0] | ((uint64_t)w[1] << 32);
+}
+
+// Contiguous rows, 16 bytes per lane: a row takes LPR = D / VEC lanes (VEC = 8 for 16-bit types, 4 for
+// fp32), a warp covers 32 / LPR rows per pass and keeps U passes of loads in flight. Grid: x = chunks
+// of consecutive tokens, y = head, z = batch (keys first, then values), so a block works on one
+// (tensor, batch, head) and its pointers are uniform. Same parameters and codes as quantize_row_warp
+// (min / max are order-free).
+template <typename T, int LPR, int BITS, int U>
+__device__ __forceinline__ void affine_quantize_vec_body(const QuantAppendArgs &a, int b, int lpg_log2) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int RPP = 32 / LPR;
+    constexpr int NBITS = VEC * BITS;   // code bits per lane: 8, 16, 32 or 64
+    constexpr float n_bins = (float)((1 << BITS) - 1);
+    const int lane = threadIdx.x & 31;
+    const int sub = lane / LPR, l = lane % LPR;
+    const int h = blockIdx.y;
+    const int s0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (RPP * U) + sub;
+    if (s0 - sub >= a.S) return;   // whole warp
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + l * VEC;
+    uint32_t *codes = a.codes + b * a.c_sb + h * a.c_sh + a.pos * a.c_st;
+    const int64_t g0 = b * a.g_sb + h * a.g_sh + a.pos * a.g_st;
+    T *scales = (T *)a.scales + g0, *biases = (T *)a.biases + g0;
+
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int sr = s0 + u * RPP;
+        raw[u] = sr < a.S ? __ldg(reinterpret_cast<const uint4 *>(src + sr * a.s_ss)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const int lpg = 1 << lpg_log2;   // lanes per group
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int sr = s0 + u * RPP;
+        float v[VEC];
+        const T *e = reinterpret_cast<const T *>(&raw[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = to_float<T>(e[i]);
+        float w_min = v[0], w_max = v[0];
+#pragma unroll
+        for (int i = 1; i < VEC; ++i) {
+            w_min = fminf(w_min, v[i]);
+            w_max = fmaxf(w_max, v[i]);
+        }
+        for (int m = lpg >> 1; m >= 1; m >>= 1) {
+            w_min = fminf(w_min, __shfl_xor_sync(0xffffffffu, w_min, m));
+            w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, m));
+        }
+        float scale, bias;
+        affine_params(w_min, w_max, n_bins, scale, bias);
+        const uint64_t acc = affine_codes_vec<VEC, BITS>(v, scale, bias);
+        uint32_t word = (uint32_t)acc;
+        if (NBITS < 32) {
+            constexpr int LPW = NBITS < 32 ? 32 / NBITS : 1;   // lanes per word
+#pragma unroll
+            for (int k = 1; k < LPW; ++k) word |= __shfl_down_sync(0xffffffffu, (uint32_t)acc, k) << (k * NBITS);
+        }
+        if (sr < a.S) {
+            if ((l & (lpg - 1)) == 0) {
+                scales[sr * a.g_st + (l >> lpg_log2)] = from_float<T>(scale);
+                biases[sr * a.g_st + (l >> lpg_log2)] = from_float<T>(bias);
+            }
+            uint32_t *row = codes + sr * a.c_st;
+            if (NBITS == 64) {
+                *reinterpret_cast<uint2 *>(row + l * 2) = make_uint2((uint32_t)acc, (uint32_t)(acc >> 32));
+            } else if (NBITS == 32) {
+                row[l] = word;
+            } else {
+                constexpr int LPW = NBITS < 32 ? 32 / NBITS : 1;
+                if ((l % LPW) == 0) row[l / LPW] = word;
+            }
+        }
+    }
+}
+
+template <typename T, int LPR, int BITS, int U>
+__global__ void __launch_bounds__(256)
+affine_quantize_vec_kernel(QuantAppendArgs ka, QuantAppendArgs va, int lpg_log2) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    // keys and values share B, H and S; the branch is uniform over the block
+    if ((int)blockIdx.z >= ka.B) affine_quantize_vec_body<T, LPR, BITS, U>(va, (int)blockIdx.z - ka.B, lpg_log2);
+    else affine_quantize_vec_body<T, LPR, BITS, U>(ka, (int)blockIdx.z, lpg_log2);
+}
+
 // The same rows for a list of independent caches (one new token each): row = (sequence, K or V,
 // head); every pointer of the table already addresses head 0 at the sequence's append position.
 template <typename T, int E>
@@ -220,7 +343,45 @@ void quantize_dispatch(const QuantAppendArgs &k, const QuantAppendArgs &v, bool 
         return (nbits >= 32) ? (nbits % 32 == 0) : (32 % nbits == 0);
     };
     const bool same_shape = !have_v || (k.D == v.D && k.group == v.group && k.bits == v.bits);
-    if (same_shape && warp_ok(k)) {
+    // 16-byte lanes need contiguous, 16-byte aligned rows
+    constexpr int VEC = 16 / (int)sizeof(T);
+    auto vec_ok = [&](const QuantAppendArgs &a) {
+        const int lpr = a.D / VEC;
+        if (a.D % VEC != 0 || !(lpr == 8 || lpr == 16 || lpr == 32)) return false;
+        if (a.group % VEC != 0 || a.group / VEC > lpr || ((a.group / VEC) & (a.group / VEC - 1))) return false;
+        if (a.s_sd != 1 || a.s_sb % VEC || a.s_sh % VEC || a.s_ss % VEC) return false;
+        if ((reinterpret_cast<uintptr_t>(a.src) & 15) || (reinterpret_cast<uintptr_t>(a.codes) & 7)) return false;
+        return (a.c_sb % 2 == 0) && (a.c_sh % 2 == 0) && (a.c_st % 2 == 0);
+    };
+    const bool same_dims = !have_v || (k.B == v.B && k.H == v.H && k.S == v.S);
+    if (same_shape && same_dims && vec_ok(k) && (!have_v || vec_ok(v)) && k.H <= 65535 && 2 * (int64_t)k.B <= 65535) {
+        const int lpr = k.D / VEC, rpp = 32 / lpr;
+        int lpg_log2 = 0;
+        while ((1 << lpg_log2) < k.group / VEC) ++lpg_log2;
+        const bool deep = (int64_t)k.S >= 8 * rpp * 4;   // a block of 8 warps fills up with 4 passes per warp
+        const int rows_per_warp = rpp * (deep ? 4 : 1);
+        const int warps = std::max(1, std::min(8, (k.S + rows_per_warp - 1) / rows_per_warp));
+        const dim3 grid((unsigned)((k.S + warps * rows_per_warp - 1) / (warps * rows_per_warp)), (unsigned)k.H,
+                        (unsigned)(k.B * (have_v ? 2 : 1)));
+#define KVC_QVEC(LPR, BITS)                                                                                   \
+    do {                                                                                                      \
+        if (deep) affine_quantize_vec_kernel<T, LPR, BITS, 4><<<grid, warps * 32, 0, stream>>>(k, vv, lpg_log2); \
+        else affine_quantize_vec_kernel<T, LPR, BITS, 1><<<grid, warps * 32, 0, stream>>>(k, vv, lpg_log2);      \
+    } while (0)
+#define KVC_QVEC_B(LPR)                                            \
+    switch (k.bits) {                                              \
+        case 2: KVC_QVEC(LPR, 2); break;                           \
+        case 4: KVC_QVEC(LPR, 4); break;                           \
+        default: KVC_QVEC(LPR, 8); break;                          \
+    }
+        switch (lpr) {
+            case 8: KVC_QVEC_B(8); break;
+            case 16: KVC_QVEC_B(16); break;
+            default: KVC_QVEC_B(32); break;
+        }
+#undef KVC_QVEC_B
+#undef KVC_QVEC
+    } else if (same_shape && warp_ok(k)) {
         const int64_t total = k_rows + v_rows;
         const int warps = 8;
         const unsigned blocks = (unsigned)((total + warps - 1) / warps);
@@ -399,6 +560,172 @@ __global__ void turbo_encode_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, int6
     if (lane == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = norm;
 }
 
+// E consecutive elements of a contiguous row in as few loads as their size allows.
+template <typename T, int E>
+__device__ __forceinline__ void load_row_elems(const T *p, float (&v)[E]) {
+    constexpr int BYTES = E * (int)sizeof(T);
+    if constexpr (BYTES % 16 == 0) {
+        uint4 raw[BYTES / 16];
+#pragma unroll
+        for (int i = 0; i < BYTES / 16; ++i) raw[i] = __ldg(reinterpret_cast<const uint4 *>(p) + i);
+        const T *e = reinterpret_cast<const T *>(raw);
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_float<T>(e[i]);
+    } else if constexpr (BYTES == 8) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(p));
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_float<T>(e[i]);
+    } else if constexpr (BYTES == 4) {
+        const uint32_t raw = __ldg(reinterpret_cast<const uint32_t *>(p));
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_float<T>(e[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_float<T>(p[i]);
+    }
+}
+
+// The same encode for contiguous rows with E <= 8: vector loads, R rows per warp in flight, the
+// boundary count as a binary search over a shared-memory copy when the boundaries ascend (`sorted`),
+// the cross-lane butterfly as one fused multiply-add per value (x * (+-1) + other rounds once, like
+// the add or subtract it replaces), and the packed words assembled by shuffles. Grid: x = chunks of
+// consecutive tokens, y = head, z = batch (keys first, then values): a block works on one (tensor,
+// batch, head). Arithmetic and reduction order are those of turbo_encode_kernel, so norms and codes
+// are the same bits.
+template <typename T, int E, int R>
+__device__ __forceinline__ void turbo_encode_vec_body(const TurboEncodeArgs &a, int b, float inv_sqrt_dim, int sorted,
+                                                      float *s_bnd) {
+    const int lane = threadIdx.x & 31;
+    const int bits = a.bits;
+    const int levels_m1 = (1 << bits) - 1;
+    // unused upper entries hold +inf, so a search of fixed depth 4 serves every bit width
+    if (threadIdx.x < 15) s_bnd[threadIdx.x] = threadIdx.x < levels_m1 ? a.boundaries[threadIdx.x] : __int_as_float(0x7f800000);
+    __syncthreads();
+    const int h = blockIdx.y;
+    const int s0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
+    if (s0 >= a.S) return;  // whole warp
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + lane * E;
+    uint32_t *packed = a.packed + b * a.p_sb + h * a.p_sh + a.pos * a.p_st;
+    float *norms = a.norms + b * a.n_sb + h * a.n_sh + a.pos * a.n_st;
+
+    float v[R][E];
+    float sg[E];
+    load_row_elems<float, E>(a.signs + lane * E, sg);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[r][i] = 0.f;
+        if (s0 + r < a.S) load_row_elems<T, E>(src + (s0 + r) * a.s_ss, v[r]);
+    }
+
+    // L2 norm over the fixed reduction tree
+    float sq[R], norm[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        sq[r] = __fmul_rn(v[r][0], v[r][0]);
+#pragma unroll
+        for (int i = 1; i < E; ++i) sq[r] = __fadd_rn(sq[r], __fmul_rn(v[r][i], v[r][i]));
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1)
+#pragma unroll
+        for (int r = 0; r < R; ++r) sq[r] = __fadd_rn(sq[r], __shfl_xor_sync(0xffffffffu, sq[r], m));
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        norm[r] = __fsqrt_rn(sq[r]);
+        const float inv_norm = (norm[r] > 1e-8f) ? __frcp_rn(norm[r]) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[r][i] = __fmul_rn(v[r][i], __fmul_rn(inv_norm, sg[i]));
+        // in-lane butterfly stages
+#pragma unroll
+        for (int st = 1; st < E; st <<= 1)
+#pragma unroll
+            for (int i = 0; i < E; ++i)
+                if ((i & st) == 0) {
+                    const float lo = v[r][i], hi = v[r][i + st];
+                    v[r][i] = __fadd_rn(lo, hi);
+                    v[r][i + st] = __fsub_rn(lo, hi);
+                }
+    }
+    // cross-lane stages: the upper lane of a pair takes other - own, the lower one other + own
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const float sign = (lane & m) ? -1.f : 1.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[r][i] = __fmaf_rn(v[r][i], sign, __shfl_xor_sync(0xffffffffu, v[r][i], m));
+    }
+
+    const int nb = E * bits;               // bits per lane = words per row (<= 32)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        uint32_t chunk = 0;
+#pragma unroll
+        for (int i = E - 1; i >= 0; --i) {
+            const float rotated = __fmul_rn(v[r][i], inv_sqrt_dim);
+            uint32_t idx = 0;
+            if (sorted) {
+#pragma unroll
+                for (int step = 8; step >= 1; step >>= 1)
+                    if (rotated > s_bnd[idx + step - 1]) idx += step;
+            } else {
+                for (int bd = 0; bd < levels_m1; ++bd) idx += (rotated > s_bnd[bd]) ? 1u : 0u;
+            }
+            chunk = (chunk << bits) | idx;
+        }
+        const bool live = s0 + r < a.S;
+        uint32_t *dst = packed + (s0 + r) * a.p_st;
+        if (nb == 32) {
+            if (live) dst[lane] = chunk;
+        } else if ((nb & (nb - 1)) == 0) {
+            // 32 / nb lanes per word: fold neighbours in with a shuffle tree
+            uint32_t word = chunk;
+            for (int span = 1, sh = nb; sh < 32; span <<= 1, sh <<= 1)
+                word |= __shfl_down_sync(0xffffffffu, word, span) << sh;
+            const int lpw = 32 / nb;
+            if (live && (lane & (lpw - 1)) == 0) dst[lane / lpw] = word;
+        } else if (nb == 12) {
+            // eight lanes hold 96 bits = three words: pairs (24 bits), quads (48 bits), then the octet
+            const uint32_t pair = chunk | (__shfl_down_sync(0xffffffffu, chunk, 1) << 12);
+            const uint64_t quad = (uint64_t)pair | ((uint64_t)__shfl_down_sync(0xffffffffu, pair, 2) << 24);
+            const uint32_t hi_lo = __shfl_down_sync(0xffffffffu, (uint32_t)quad, 4);
+            const uint32_t hi_hi = __shfl_down_sync(0xffffffffu, (uint32_t)(quad >> 32), 4);
+            const uint64_t upper = (uint64_t)hi_lo | ((uint64_t)hi_hi << 32);   // bits 48..95 of the octet
+            if (live && (lane & 7) == 0) {
+                uint32_t *w = dst + (lane >> 3) * 3;
+                w[0] = (uint32_t)quad;
+                w[1] = (uint32_t)(quad >> 32) | (uint32_t)(upper << 16);
+                w[2] = (uint32_t)(upper >> 16);
+            }
+        } else {
+            // lane j holds bits [j nb, (j + 1) nb) of the row; lane w gathers word w
+            const int j0 = (32 * lane) / nb;
+            uint32_t word = 0;
+            for (int k = 0; k <= 32 / nb + 1; ++k) {
+                const int j = j0 + k;
+                const uint32_t c = __shfl_sync(0xffffffffu, chunk, j & 31);
+                const int lo = j * nb - 32 * lane;  // where lane j's chunk starts inside this word
+                if (j < 32 && lo < 32) word |= lo >= 0 ? c << lo : c >> (-lo);
+            }
+            if (live && lane < nb) dst[lane] = word;
+        }
+        if (live && lane == 0) norms[(s0 + r) * a.n_st] = norm[r];
+    }
+}
+
+template <typename T, int E, int R>
+__global__ void __launch_bounds__(256)
+turbo_encode_vec_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, float inv_sqrt_dim, int sorted) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    __shared__ float s_bnd[16];
+    // keys and values share B, H and S; the branch is uniform over the block
+    if ((int)blockIdx.z >= ka.B) turbo_encode_vec_body<T, E, R>(va, (int)blockIdx.z - ka.B, inv_sqrt_dim, sorted, s_bnd);
+    else turbo_encode_vec_body<T, E, R>(ka, (int)blockIdx.z, inv_sqrt_dim, sorted, s_bnd);
+}
+
 template <typename T>
 void turbo_dispatch(const TurboEncodeArgs &k, const TurboEncodeArgs &v, bool have_v, cudaStream_t stream) {
     const int64_t k_rows = (int64_t)k.B * k.H * k.S;
@@ -408,6 +735,39 @@ void turbo_dispatch(const TurboEncodeArgs &k, const TurboEncodeArgs &v, bool hav
     const unsigned blocks = (unsigned)((total + warps - 1) / warps);
     const size_t smem = warps * ((1024 * 4 + 31) / 32) * sizeof(uint32_t);
     const float inv_sqrt_dim = 1.0f / sqrtf((float)k.D);
+    const int E = k.D / 32;
+    auto vec_ok = [&](const TurboEncodeArgs &a) {
+        if (a.s_sd != 1 || a.s_sb % E || a.s_sh % E || a.s_ss % E) return false;
+        return (reinterpret_cast<uintptr_t>(a.src) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.signs) & 15) == 0;
+    };
+    auto ascending = [](const TurboEncodeArgs &a) {
+        for (int i = 0; i + 2 < (1 << a.bits); ++i)
+            if (!(a.boundaries[i] <= a.boundaries[i + 1])) return false;
+        return true;
+    };
+    const bool same_dims = !have_v || (k.B == v.B && k.H == v.H && k.S == v.S);
+    if (E <= 8 && same_dims && vec_ok(k) && (!have_v || vec_ok(v)) && k.H <= 65535 && 2 * (int64_t)k.B <= 65535) {
+        const int sorted = ascending(k) && (!have_v || ascending(v)) ? 1 : 0;
+        const bool deep = k.S >= 16;
+        const int rpw = deep ? 2 : 1;
+        const int vw = std::max(1, std::min(8, (k.S + rpw - 1) / rpw));
+        const dim3 grid((unsigned)((k.S + vw * rpw - 1) / (vw * rpw)), (unsigned)k.H, (unsigned)(k.B * (have_v ? 2 : 1)));
+#define KVC_TV(EE)                                                                                        \
+    do {                                                                                                  \
+        if (deep) turbo_encode_vec_kernel<T, EE, 2><<<grid, vw * 32, 0, stream>>>(k, v, inv_sqrt_dim, sorted); \
+        else turbo_encode_vec_kernel<T, EE, 1><<<grid, vw * 32, 0, stream>>>(k, v, inv_sqrt_dim, sorted);      \
+    } while (0)
+        switch (E) {
+            case 1: KVC_TV(1); break;
+            case 2: KVC_TV(2); break;
+            case 4: KVC_TV(4); break;
+            default: KVC_TV(8); break;
+        }
+#undef KVC_TV
+        KVC_CUDA(cudaGetLastError());
+        ++g_launch_count;
+        return;
+    }
 #define KVC_TE(EE)                                                                               \
     turbo_encode_kernel<T, EE><<<blocks, warps * 32, smem, stream>>>(k, v, k_rows, total, inv_sqrt_dim)
     switch (k.D / 32) {

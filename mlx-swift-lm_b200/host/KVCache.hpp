@@ -5,6 +5,8 @@
 #pragma once
 
 #include <cstdint>
+#include <map>
+#include <memory>
 #include <optional>
 #include <stdexcept>
 #include <string>
@@ -35,7 +37,7 @@ struct Mask {
 
 class KVCache {
   public:
-    virtual ~KVCache() { kvc_free(h_); }
+    virtual ~KVCache() { if (h_) kvc_free(h_); }
     KVCache(const KVCache &) = delete;
     KVCache &operator=(const KVCache &) = delete;
 
@@ -101,6 +103,44 @@ class KVCache {
                             mask.kind == MaskKind::array ? &mask.array : nullptr, &out, stream));
     }
 
+    // makeMask(n:windowSize:returnArray:): the mode, and for array masks the [rows, cols] shape;
+    // `maskOut` (device, bool, rows * cols bytes) may be null to query the shape only.
+    struct MaskInfo {
+        MaskKind kind;
+        int64_t rows, cols;
+    };
+    MaskInfo makeMask(int n, std::optional<int64_t> windowSize, bool returnArray, void *maskOut = nullptr) const {
+        int32_t mode = KVC_MASK_NONE;
+        int64_t rows = 0, cols = 0;
+        check(kvc_make_mask(h_, n, windowSize ? *windowSize : -1, returnArray ? 1 : 0, &mode, &rows, &cols,
+                            maskOut, stream));
+        return {mode == KVC_MASK_NONE ? MaskKind::none : mode == KVC_MASK_CAUSAL ? MaskKind::causal : MaskKind::array,
+                rows, cols};
+    }
+
+    // copy(): a deep copy of the same class
+    std::unique_ptr<KVCache> copy() const {
+        kvc_cache *out = nullptr;
+        check(kvc_copy(h_, stream, &out));
+        return wrap(out);
+    }
+
+    int32_t kind() const { return kvc_kind_of(h_); }
+    int64_t memoryBytes() const { return kvc_memory_bytes(h_); }
+    // capacity hint (no reference counterpart): room for `tokens` rows without regrowth
+    void reserve(int64_t tokens, int batch, int kvHeads, int headDim, int32_t dtype) {
+        check(kvc_reserve(h_, tokens, batch, kvHeads, headDim, dtype, stream));
+    }
+
+    // Adopt a handle under the class its kind names (results of conversions and file loads).
+    static std::unique_ptr<KVCache> wrap(kvc_cache *adopted);
+    // Give the handle up (list-level calls that replace handles in place).
+    kvc_cache *release() {
+        kvc_cache *h = h_;
+        h_ = nullptr;
+        return h;
+    }
+
     kvc_cache *handle() const { return h_; }
     void *stream = nullptr;
 
@@ -121,6 +161,18 @@ class KVCacheSimple : public KVCache {
   public:
     explicit KVCacheSimple(int step = 256) : KVCache(make(step)) {}
     explicit KVCacheSimple(kvc_cache *adopted) : KVCache(adopted) {}
+    // toQuantized(groupSize:bits:)
+    std::unique_ptr<KVCache> toQuantized(int groupSize = 64, int bits = 4) const {
+        kvc_cache *out = nullptr;
+        check(kvc_to_quantized(h_, groupSize, bits, stream, &out));
+        return wrap(out);
+    }
+    // the per-layer conversion of maybeTurboQuantizeKVCache
+    std::unique_ptr<KVCache> toTurbo(int keyBits, int valueBits, int keyGroupSize = 64) const {
+        kvc_cache *out = nullptr;
+        check(kvc_to_turbo(h_, keyBits, valueBits, keyGroupSize, stream, &out));
+        return wrap(out);
+    }
 
   private:
     static kvc_config make(int step) {
@@ -133,6 +185,7 @@ class KVCacheSimple : public KVCache {
 class RotatingKVCache : public KVCache {
   public:
     RotatingKVCache(int maxSize, int keep = 0, int step = 256) : KVCache(make(maxSize, keep, step)) {}
+    explicit RotatingKVCache(kvc_cache *adopted) : KVCache(adopted) {}
     int64_t idx() const { return kvc_ring_index(h_); }
     // logicalView(tail:); nullopt before the first write
     std::optional<std::pair<kvc_tensor, kvc_tensor>> logicalView(int64_t tail) {
@@ -163,6 +216,14 @@ class QuantizedKVCache : public KVCache {
     void updateQuantized(const kvc_tensor &keys, const kvc_tensor &values, kvc_tensor outK[3], kvc_tensor outV[3]) {
         check(kvc_update_quantized(h_, &keys, &values, stream, outK, outV));
     }
+    // getQuantizedState()
+    void getQuantizedState(kvc_tensor outK[3], kvc_tensor outV[3]) { check(kvc_quantized_state(h_, outK, outV)); }
+    // toUnquantized()
+    std::unique_ptr<KVCache> toUnquantized() const {
+        kvc_cache *out = nullptr;
+        check(kvc_to_unquantized(h_, stream, &out));
+        return wrap(out);
+    }
 
   private:
     static kvc_config make(int g, int b) {
@@ -178,7 +239,12 @@ class TurboQuantKVCache : public KVCache {
     explicit TurboQuantKVCache(int bits = 4, int keyBits = -1, int valueBits = -1, uint64_t seed = 42,
                                int keyGroupSize = 64)
         : KVCache(make(bits, keyBits, valueBits, seed, keyGroupSize)) {}
+    explicit TurboQuantKVCache(kvc_cache *adopted) : KVCache(adopted) {}
     bool isCompressed() const { return kvc_is_compressed(h_) != 0; }
+    // compressRawCache + encodeNewToken without the attention (chunked compressed prefill)
+    void encodeNewToken(const kvc_tensor &keys, const kvc_tensor &values) {
+        check(kvc_turbo_encode_new_token(h_, &keys, &values, stream));
+    }
 
   private:
     static kvc_config make(int bits, int kb, int vb, uint64_t seed, int kg) {
@@ -203,6 +269,162 @@ inline void attentionWithCacheUpdate(const kvc_tensor &queries, const kvc_tensor
                          : mask.kind == MaskKind::causal ? KVC_MASK_CAUSAL : KVC_MASK_ARRAY;
     check(kvc_sdpa(&queries, &keys, &values, scale, mode, mask.kind == MaskKind::array ? &mask.array : nullptr,
                    &out, stream));
+}
+
+inline std::unique_ptr<KVCache> KVCache::wrap(kvc_cache *adopted) {
+    switch (kvc_kind_of(adopted)) {
+        case KVC_KIND_SIMPLE: return std::make_unique<KVCacheSimple>(adopted);
+        case KVC_KIND_ROTATING: return std::make_unique<RotatingKVCache>(adopted);
+        case KVC_KIND_QUANTIZED: return std::make_unique<QuantizedKVCache>(adopted);
+        case KVC_KIND_TURBO: return std::make_unique<TurboQuantKVCache>(adopted);
+        default: kvc_free(adopted); throw Error(KVC_ERR_INTERNAL, "unknown cache kind");
+    }
+}
+
+// quantizedScaledDotProductAttention(queries:quantizedKeys:quantizedValues:scale:mask:groupSize:bits:)
+inline void quantizedScaledDotProductAttention(const kvc_tensor &queries, const kvc_tensor qk[3], const kvc_tensor qv[3],
+                                               float scale, const Mask &mask, int groupSize, int bits,
+                                               const kvc_tensor &out, void *stream = nullptr) {
+    const int32_t mode = mask.kind == MaskKind::none ? KVC_MASK_NONE
+                         : mask.kind == MaskKind::causal ? KVC_MASK_CAUSAL : KVC_MASK_ARRAY;
+    check(kvc_quantized_sdpa(&queries, qk, qv, scale, mode, mask.kind == MaskKind::array ? &mask.array : nullptr,
+                             groupSize, bits, &out, stream));
+}
+
+using CacheList = std::vector<std::unique_ptr<KVCache>>;
+
+namespace detail {
+inline std::vector<kvc_cache *> handles(const CacheList &caches) {
+    std::vector<kvc_cache *> h;
+    for (const auto &c : caches) h.push_back(c->handle());
+    return h;
+}
+// Re-adopt the handles a list-level conversion left in `h` (converted slots hold new handles, the old
+// ones were freed by the library).
+inline void readopt(CacheList &caches, const std::vector<kvc_cache *> &h) {
+    for (size_t i = 0; i < caches.size(); ++i)
+        if (caches[i]->handle() != h[i]) {
+            void *stream = caches[i]->stream;
+            caches[i]->release();
+            caches[i] = KVCache::wrap(h[i]);
+            caches[i]->stream = stream;
+        }
+}
+}  // namespace detail
+
+// canTrimPromptCache / trimPromptCache
+inline bool canTrimPromptCache(const CacheList &caches) {
+    const auto h = detail::handles(caches);
+    return kvc_can_trim_prompt_cache(h.data(), (int32_t)h.size()) != 0;
+}
+inline int64_t trimPromptCache(const CacheList &caches, int64_t numTokens) {
+    const auto h = detail::handles(caches);
+    int64_t t = 0;
+    check(kvc_trim_prompt_cache(h.data(), (int32_t)h.size(), numTokens, &t));
+    return t;
+}
+
+// resolveTurboScheme / resolveAffineScheme: (keyBits, valueBits) / (bits, groupSize), or nullopt
+inline std::optional<std::pair<int, int>> resolveTurboScheme(const std::string &scheme) {
+    int32_t a = 0, b = 0;
+    if (!kvc_resolve_turbo_scheme(scheme.c_str(), &a, &b)) return std::nullopt;
+    return std::make_pair((int)a, (int)b);
+}
+inline std::optional<std::pair<int, int>> resolveAffineScheme(const std::string &scheme) {
+    int32_t a = 0, b = 0;
+    if (!kvc_resolve_affine_scheme(scheme.c_str(), &a, &b)) return std::nullopt;
+    return std::make_pair((int)a, (int)b);
+}
+
+// maybeAffineQuantizeKVCache / maybeTurboQuantizeKVCache over a flat layer list; returns whether every
+// eligible layer has been converted.
+inline bool maybeAffineQuantizeKVCache(CacheList &caches, int bits, int groupSize, int64_t compressionStart,
+                                       void *stream = nullptr) {
+    auto h = detail::handles(caches);
+    int32_t complete = 0;
+    check(kvc_maybe_affine_quantize(h.data(), (int32_t)h.size(), bits, groupSize, compressionStart, stream, &complete));
+    detail::readopt(caches, h);
+    return complete != 0;
+}
+inline bool maybeTurboQuantizeKVCache(CacheList &caches, int keyBits, int valueBits, int64_t quantizedKVStart,
+                                      void *stream = nullptr) {
+    auto h = detail::handles(caches);
+    int32_t complete = 0;
+    check(kvc_maybe_turbo_quantize(h.data(), (int32_t)h.size(), keyBits, valueBits, quantizedKVStart, stream, &complete));
+    detail::readopt(caches, h);
+    return complete != 0;
+}
+
+// savePromptCache(url:cache:metadata:) / loadPromptCache(url:)
+inline void savePromptCache(const std::string &path, const CacheList &caches,
+                            const std::map<std::string, std::string> &metadata = {}, void *stream = nullptr) {
+    const auto h = detail::handles(caches);
+    std::vector<const char *> keys, values;
+    for (const auto &kv : metadata) {
+        keys.push_back(kv.first.c_str());
+        values.push_back(kv.second.c_str());
+    }
+    check(kvc_save_prompt_cache(path.c_str(), h.data(), (int32_t)h.size(), keys.data(), values.data(),
+                                (int32_t)keys.size(), stream));
+}
+inline std::pair<CacheList, std::map<std::string, std::string>> loadPromptCache(const std::string &path, int device = -1,
+                                                                                 void *stream = nullptr) {
+    int32_t count = 0;
+    size_t need = 0;
+    check(kvc_load_prompt_cache(path.c_str(), device, nullptr, 0, &count, nullptr, 0, &need, stream));
+    std::vector<kvc_cache *> h((size_t)count);
+    std::string buf(need ? need : 1, '\0');
+    check(kvc_load_prompt_cache(path.c_str(), device, h.data(), count, &count, buf.data(), buf.size(), &need, stream));
+    CacheList caches;
+    for (int32_t i = 0; i < count; ++i) caches.push_back(KVCache::wrap(h[(size_t)i]));
+    std::map<std::string, std::string> meta;
+    for (size_t p = 0; p < buf.size() && buf[p] != '\0';) {   // key NUL value NUL ... closed by an empty key
+        const std::string key(buf.c_str() + p);
+        p += key.size() + 1;
+        const std::string value(buf.c_str() + p);
+        p += value.size() + 1;
+        meta[key] = value;
+    }
+    return {std::move(caches), std::move(meta)};
+}
+
+// One cache's share of a speculative verify round (KVCacheRound: beginRound / commit / rollback).
+class StagedRound {
+  public:
+    StagedRound(KVCache &cache, int maxPositions) : stream(cache.stream) {
+        check(kvc_round_begin(cache.handle(), maxPositions, &r_));
+    }
+    ~StagedRound() { if (r_) kvc_round_free(r_); }
+    StagedRound(const StagedRound &) = delete;
+    StagedRound &operator=(const StagedRound &) = delete;
+
+    int64_t offset() const { return kvc_round_offset(r_); }
+    std::pair<kvc_tensor, kvc_tensor> update(const kvc_tensor &keys, const kvc_tensor &values) {
+        kvc_tensor k{}, v{};
+        check(kvc_round_update(r_, &keys, &values, stream, &k, &v));
+        return {k, v};
+    }
+    void attention(const kvc_tensor &queries, const kvc_tensor &keys, const kvc_tensor &values, float scale,
+                   const Mask &mask, const kvc_tensor &out) {
+        const int32_t mode = mask.kind == MaskKind::none ? KVC_MASK_NONE
+                             : mask.kind == MaskKind::causal ? KVC_MASK_CAUSAL : KVC_MASK_ARRAY;
+        check(kvc_round_attention(r_, &queries, &keys, &values, scale, mode,
+                                  mask.kind == MaskKind::array ? &mask.array : nullptr, &out, stream));
+    }
+    void commit(int retain) { check(kvc_round_commit(r_, retain, stream)); }
+    void rollback() { check(kvc_round_rollback(r_, stream)); }
+
+    void *stream = nullptr;
+
+  private:
+    kvc_round *r_ = nullptr;
+};
+
+// rewindLastRound(count) -> positions taken back
+inline int64_t rewindLastRound(KVCache &cache, int64_t count) {
+    int64_t n = 0;
+    check(kvc_rewind_last_round(cache.handle(), count, cache.stream, &n));
+    return n;
 }
 
 }  // namespace kvc::host

@@ -42,3 +42,16 @@ def test_version_and_error_channel(kvc):
 def test_modulemap_names_the_header():
     mm = open(os.path.join(ROOT, "include", "module.modulemap")).read()
     assert 'header "kvcache_b200.h"' in mm
+
+
+def test_cpp_host_mirror_compiles_and_runs_without_a_device(kvc, tmp_path):
+    """host/KVCache.hpp (the C++ mirror of the KVCache protocol surface) compiles against the C header,
+    links the shared library and passes its host-only checks."""
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    lib_dir = os.path.dirname(kvc.LIB_PATH)
+    exe = str(tmp_path / "host_mirror")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", "-Werror", os.path.join(here, "host_mirror_main.cpp"), "-o", exe,
+                    "-L" + lib_dir, "-lkvcache_b200", "-Wl,-rpath," + lib_dir], check=True)
+    out = subprocess.run([exe, str(tmp_path / "mirror.safetensors")], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr

@@ -163,6 +163,27 @@ def test_affine_codes_bit_exact(kvc, oracle, cuda, dtype, bits, D, group):
     _same_state(g, o)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bits,D,group", [(4, 128, 64), (8, 128, 32), (2, 64, 64), (4, 256, 128), (8, 64, 32), (2, 128, 64)])
+def test_affine_codes_bit_exact_prefill_chunk(kvc, oracle, cuda, dtype, bits, D, group):
+    """A prefill-sized chunk (the launcher keeps several rows per warp in flight), an odd-sized one, and
+    a strided (transposed-projection) source that must take the element-wise path."""
+    B, H = 2, 4
+    g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
+    for i, S in enumerate((1100, 3, 1031)):
+        k = seeded((B, H, S, D), 40 + i, dtype, outlier_frac=0.05)
+        v = seeded((B, H, S, D), 50 + i, dtype)
+        kd, vd = k.to(cuda), v.to(cuda)
+        if i == 2:   # [B, S, H, D] storage viewed as [B, H, S, D]
+            kd = kd.transpose(1, 2).contiguous().transpose(1, 2)
+            vd = vd.transpose(1, 2).contiguous().transpose(1, 2)
+        gq = g.update_quantized(kd, vd)
+        oq = o.update_quantized(to_oracle(k), to_oracle(v))
+        for gt, ot in zip(gq[0] + gq[1], oq[0] + oq[1]):
+            assert bits_equal(gt, np.ascontiguousarray(ot))
+    _same_state(g, o)
+
+
 def test_quantized_cache_rejects_what_the_reference_rejects(kvc, cuda):
     q = kvc.QuantizedKVCache()
     x = torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16, device=cuda)

@@ -39,6 +39,21 @@ def test_turbo_encode_bit_exact(kvc, oracle, cuda, dtype, D, bits):
     assert bits_equal(packed, rp), "packed indices differ"
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D,bits", [(128, 3), (128, 4), (64, 2), (256, 4), (32, 3)])
+def test_turbo_encode_bit_exact_many_rows(kvc, oracle, cuda, dtype, D, bits):
+    """A prefill-sized row count (the launcher keeps several rows per warp in flight) plus a row count
+    that leaves the last warp half empty; unsorted boundaries take the counting path."""
+    signs = oracle.wht_signs(D, 7)
+    bounds = oracle.boundaries_of(np.array(kvc.turbo_codebook(D, bits)[0], dtype=np.float32))
+    for rows, bnd in ((8192 + 5, bounds), (9001, bounds[::-1].copy())):
+        x = seeded((rows, D), rows + D + bits, dtype, outlier_frac=0.02)
+        packed, norms = kvc.turbo_encode(x.to(cuda), signs, bnd, bits)
+        rp, rn = oracle.turbo_encode(to_oracle(x), signs, bnd, bits)
+        assert bits_equal(norms, rn), "norms differ"
+        assert bits_equal(packed, rp), "packed indices differ"
+
+
 def _pair(kvc, oracle, **kw):
     g = kvc.TurboQuantKVCache(**kw)
     kb = kw.get("key_bits", kw.get("bits", 4))
