@@ -77,6 +77,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // kernel before it on the stream is still running; everything it reads from global memory
 // must come after pdl_wait(), which returns once that kernel has completed and flushed.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream (if it was launched with launch_pdl) be scheduled as soon as
+// every CTA of this one has issued it or exited. Issued only AFTER pdl_wait(): a kernel that starts
+// early then knows that everything up to the kernel before its predecessor has completed.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }

@@ -69,6 +69,7 @@ struct DecodeParams {
     int64_t kv_sb, kv_sh, kv_st;
     // fused append: the new rows [B, Hkv, D] of this step (null = the cache already holds them)
     const void *new_k, *new_v;
+    int32_t early_tiles;  // flat kernel: the stored rows may be streamed before the preceding kernel has finished
     int64_t nk_sb, nk_sh, nv_sb, nv_sh;  // element strides
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
@@ -378,17 +379,45 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
+    // Everything read below was written by earlier kernels on the stream, so it comes after the wait
+    // on the preceding kernel. One exception, early_tiles: the producer streams its first tiles of
+    // stored rows before that wait. The host vouches that the preceding kernel does not write them (it
+    // is a layer of the same batched call, working on another cache), and every kernel before that one
+    // has completed, because kernels release their successor only after their own wait.
+    const bool early = p.early_tiles != 0 && warp == CONSUMER_WARPS;
+    if (!early) {
+        pdl_wait();
+        pdl_trigger();
+    }
 
     bool ok = true;
     if (warp == CONSUMER_WARPS) {
         // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
             int it = 0, sg = 0;
+            bool waited = !early;
             for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 const int unit = (int)(x / tiles), t0 = (int)(x % tiles);
                 const int n = (int)min((int64_t)(tiles - t0), x_hi - x);
                 const int hk = unit % p.Hkv, b = unit / p.Hkv;
+                int j_first = 0;
+                if (!waited) {
+                    // the ring is empty: up to NSTAGE tiles go out before the wait
+                    for (; j_first < n && j_first < NSTAGE; ++j_first, ++it) {
+                        unsigned char *kt = stages + (size_t)it * 2 * TILE_BYTES;
+                        unsigned char *vt = kt + TILE_BYTES;
+                        mbar_expect_tx(&full[it], 2 * TILE_BYTES);
+                        const int tok = (t0 + j_first) * TILE_T;
+#pragma unroll
+                        for (int bx = 0; bx < BOXES; ++bx) {
+                            tma_load_4d(kt + bx * BOX_BYTES, &kmap, &full[it], bx * 64, tok, hk, b);
+                            tma_load_4d(vt + bx * BOX_BYTES, &vmap, &full[it], bx * 64, tok, hk, b);
+                        }
+                    }
+                    pdl_wait();
+                    pdl_trigger();
+                    waited = true;
+                }
                 if (p.q_bulk) {
                     const int qb = sg & 1;
                     if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
@@ -397,7 +426,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                     bulk_load(qbuf + (size_t)qb * q_bytes, (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh, q_bytes,
                               &qfull[qb]);
                 }
-                for (int j = 0; j < n && ok; ++j, ++it) {
+                for (int j = j_first; j < n && ok; ++j, ++it) {
                     const int s = it % NSTAGE;
                     if (it >= NSTAGE) {
                         // measurement aid (debug_skip & 4): the producer alone recycles the ring
@@ -1169,6 +1198,17 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.k_base = (unsigned char *)a.k.data; p.v_base = (unsigned char *)a.v.data;
             p.kv_sb = a.k.sb * 2; p.kv_sh = a.k.sh * 2; p.kv_st = a.k.st * 2;
             p.new_k = a.new_k; p.new_v = a.new_v;
+            {
+                // early tiles: fused append only (the kernel's tiles end before the row it writes), the
+                // caller's word on the preceding launch, and that launch being a kernel that released
+                // this one only after its own wait. KVC_EARLY_TILES=0 turns it off.
+                static const bool early_off = [] {
+                    const char *e = std::getenv("KVC_EARLY_TILES");
+                    return e && e[0] == '0';
+                }();
+                p.early_tiles = (!early_off && a.new_k && a.stored_rows_settled && g_last_chained_launch == g_launch_count &&
+                                 p.debug_skip == 0) ? 1 : 0;
+            }
             p.nk_sb = a.nk_sb; p.nk_sh = a.nk_sh; p.nv_sb = a.nv_sb; p.nv_sh = a.nv_sh;
             p.causal_offset = a.mask.causal_offset;
             p.scale_log2 = a.scale * 1.4426950408889634f;
@@ -1188,6 +1228,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
                 else KVC_FLAT(__half, 256, 3);
             }
 #undef KVC_FLAT
+            g_last_chained_launch = g_launch_count;
             return 1;
         }
     }

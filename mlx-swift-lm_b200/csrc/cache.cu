@@ -11,6 +11,11 @@
 
 namespace kvc {
 
+// Set by the batched entry points around each layer's call: the cache of the layer launched just
+// before on the same stream (nullptr outside a batched call or for its first layer).
+static thread_local const kvc_cache *tl_batch_prev = nullptr;
+void set_batch_previous(const kvc_cache *prev) { tl_batch_prev = prev; }
+
 int launch_attention(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
@@ -771,12 +776,16 @@ void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, con
                             "update: keys and values disagree on batch, heads or length");
                 c->restore.valid = false;
                 const int64_t prev = c->offset;
+                const void *k_before = c->k.allocated() ? c->k.view(c->offset).data : nullptr;
                 linear_update(c, k, v, s, /*defer_append=*/true);
                 kvc_tensor ck = c->k.view(c->offset), cv = c->v.view(c->offset);
                 AttnArgs a = make_attn_args(q, out, scale, KVC_MASK_NONE, nullptr, ck.shape[2], Hkv);
                 a.k = raw_source(ck);
                 a.v = raw_source(cv);
                 a.new_k = k.data; a.new_v = v.data;
+                // inside a batched call the launch before this one belongs to the previous layer's cache;
+                // a growth copy in linear_update would be a write to this one
+                a.stored_rows_settled = tl_batch_prev != nullptr && tl_batch_prev != c && k_before == ck.data;
                 a.nk_sb = k.stride[0]; a.nk_sh = k.stride[1];
                 a.nv_sb = v.stride[0]; a.nv_sh = v.stride[1];
                 if (launch_attention_decode(a, s) > 0) return;

@@ -144,4 +144,8 @@ AttnArgs make_attn_args(const kvc_tensor &q, const kvc_tensor &out, float scale,
                         const kvc_tensor *mask, int64_t T, int Hkv);
 KVSource raw_source(const kvc_tensor &t);
 
+// Batched entry points: names the cache whose kernels were launched just before the next
+// cache_attention call on the same stream (nullptr = unknown / none).
+void set_batch_previous(const kvc_cache *prev);
+
 }  // namespace kvc

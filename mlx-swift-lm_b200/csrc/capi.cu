@@ -1061,10 +1061,13 @@ kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kv
         });
     }
     for (int i = 0; i < count; ++i) {
+        // layer i's launches follow layer i - 1's on the stream with nothing in between
+        kvc::set_batch_previous(!host && i > 0 ? caches[i - 1] : nullptr);
         kvc_status st = host ? kvc_attention_host(caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
                                                   &outs[i], stream, 0)
                              : kvc_attention(caches[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr,
                                              &outs[i], stream);
+        kvc::set_batch_previous(nullptr);
         if (st != KVC_OK) return st;
     }
     if (synchronize) {

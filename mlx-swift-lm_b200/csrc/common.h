@@ -123,6 +123,10 @@ struct AttnArgs {
     // written to the cache yet; the kernel scores them from here and stores them at token T - 1 itself.
     const void *new_k = nullptr, *new_v = nullptr;
     int64_t nk_sb = 0, nk_sh = 0, nv_sb = 0, nv_sh = 0;  // element strides (inner stride 1)
+    // The caller vouches that the launch right before this one on the stream (a layer of the same
+    // batched call) does not write the rows of this cache that are already stored, so the kernel may
+    // stream them before that launch has finished.
+    bool stored_rows_settled = false;
     const float *q_signs = nullptr;
     const float *q_calib = nullptr;  // optional per-dim key-calibration scale
     const float *o_signs = nullptr;
@@ -236,6 +240,9 @@ void launch_rolled_mask(uint8_t *out, int64_t size, int64_t window, int64_t shif
 // Count of kernels launched by this library on the calling thread since the
 // last reset (benchmarks report it).
 extern thread_local int64_t g_launch_count;
+// Value of g_launch_count right after the last launch of a kernel that releases its successor only
+// after its own wait on its predecessor (-1: none yet).
+extern thread_local int64_t g_last_chained_launch;
 
 // Event timing of the dominant attention kernel (off unless a benchmark enables it).
 bool timing_enabled();

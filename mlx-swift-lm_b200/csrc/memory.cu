@@ -11,6 +11,7 @@
 namespace kvc {
 
 thread_local int64_t g_launch_count = 0;
+thread_local int64_t g_last_chained_launch = -1;
 
 int current_device() {
     int dev = 0;

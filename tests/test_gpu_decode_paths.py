@@ -155,3 +155,42 @@ def test_fused_append_decode_is_one_launch_and_bit_exact_cache(kvc, oracle, cuda
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), eo, D ** -0.5)
     assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_batched_decode_steps_over_layers(kvc, oracle, cuda, dtype):
+    """Several decode steps of a 5-layer stack through one batched call per step (the layers' kernels
+    follow one another on the stream, each appending its own new row): outputs match the oracle layer
+    by layer and the caches hold the oracle's bytes. Layer 3 shares its cache object with nothing but
+    starts one step late from a shorter prefix, and the prefix of layer 2 ends exactly on its capacity
+    so that its first step re-allocates."""
+    B, Hq, Hkv, D, Lyr = 2, 8, 2, 128, 5
+    scale = D ** -0.5
+    prefix = [700, 1300, 512, 65, 2049]
+    g, o = [], []
+    for i in range(Lyr):
+        gc = kvc.KVCacheSimple(step=256)
+        oc = oracle.KVCacheSimple(step=256)
+        k, v = seeded((B, Hkv, prefix[i], D), 10 + i, dtype), seeded((B, Hkv, prefix[i], D), 20 + i, dtype)
+        gc.update(k.to(cuda), v.to(cuda))
+        oc.update(to_oracle(k), to_oracle(v))
+        g.append(gc)
+        o.append(oc)
+    for step in range(6):
+        qs = [seeded((B, Hq, 1, D), 100 + 10 * step + i, dtype) for i in range(Lyr)]
+        ks = [seeded((B, Hkv, 1, D), 200 + 10 * step + i, dtype) for i in range(Lyr)]
+        vs = [seeded((B, Hkv, 1, D), 300 + 10 * step + i, dtype) for i in range(Lyr)]
+        dq, dk, dv = [t.to(cuda) for t in qs], [t.to(cuda) for t in ks], [t.to(cuda) for t in vs]
+        outs = [torch.empty_like(t) for t in dq]
+        n0 = kvc.launch_count(reset=True)
+        kvc.DecodeStep(g, dq, dk, dv, outs, scale).run(synchronize=True)
+        launches = kvc.launch_count(reset=True)
+        assert Lyr <= launches <= Lyr + 4, launches         # one kernel per layer (append fused in) + growth copies
+        for i in range(Lyr):
+            ref = oracle.attention_with_cache_update(to_oracle(qs[i]), to_oracle(ks[i]), to_oracle(vs[i]), o[i], scale, "none")
+            assert max_abs_diff(outs[i], ref) <= TOL[dtype], (step, i)
+    for gc, oc in zip(g, o):
+        assert gc.offset == oc.offset
+        for a, b in zip(gc.state, oc.state):
+            assert bits_equal(a, np.ascontiguousarray(b))
+    assert kvc.lib().kvc_device_status() == 0
