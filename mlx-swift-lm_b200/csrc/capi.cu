@@ -1033,27 +1033,71 @@ kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kv
             cudaEvent_t start = pipe.events[0], done = pipe.events[1];
             KVC_CUDA(cudaEventRecord(start, s));              // earlier work on `stream` still reads the slabs
             KVC_CUDA(cudaStreamWaitEvent(pipe.h2d, start, 0));
-            for (int i = 0; i < count; ++i) {
-                const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
-                             vb = tensor_bytes_contiguous(v[i]);
-                char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb);
-                KVC_CUDA(cudaMemcpyAsync(dq, q[i].data, qb, cudaMemcpyHostToDevice, pipe.h2d));
-                KVC_CUDA(cudaMemcpyAsync(dk, k[i].data, kb, cudaMemcpyHostToDevice, pipe.h2d));
-                KVC_CUDA(cudaMemcpyAsync(dv, v[i].data, vb, cudaMemcpyHostToDevice, pipe.h2d));
-                KVC_CUDA(cudaEventRecord(pipe.events[2 + 2 * (size_t)i], pipe.h2d));
+            // Layers travel in groups: one event per group tells `stream` that the group's inputs have
+            // arrived, and one tells the output stream that its results are ready. Inside a group the
+            // layers' kernels follow one another with nothing in between, so a layer starts under the
+            // tail of the one before it. Groups are small at both ends (the first kernel waits for
+            // one layer's copies only, the last output copy is one layer's) and up to 8 layers between.
+            std::vector<int> group_end;   // one past the last layer of each group
+            {
+                std::vector<int> front, back;
+                int used = 0;
+                for (int sz = 1; used + sz <= count / 2; sz = std::min(sz * 2, 8)) {
+                    front.push_back(sz);
+                    back.push_back(sz);
+                    used += sz;
+                }
+                int pos = 0;
+                for (int sz : front) group_end.push_back(pos += sz);
+                for (int left = count - 2 * used; left > 0;) {
+                    const int sz = std::min(left, 8);
+                    group_end.push_back(pos += sz);
+                    left -= sz;
+                }
+                for (auto it = back.rbegin(); it != back.rend(); ++it) group_end.push_back(pos += *it);
             }
-            for (int i = 0; i < count; ++i) {
-                const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
-                             vb = tensor_bytes_contiguous(v[i]), ob = tensor_bytes_contiguous(outs[i]);
-                char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb), *dout = dv + al(vb);
-                kvc_tensor tq = q[i], tk = k[i], tv = v[i], to = outs[i];
-                tq.data = dq; tk.data = dk; tv.data = dv; to.data = dout;
-                KVC_CUDA(cudaStreamWaitEvent(s, pipe.events[2 + 2 * (size_t)i], 0));
-                kvc::cache_attention(caches[i], tq, tk, tv, scale, mask_mode, nullptr, to, s);
-                cudaEvent_t out_ready = pipe.events[3 + 2 * (size_t)i];
+            // The host issues a group's input copies one group ahead of its kernels: the copies of
+            // all layers up front would keep the device idle while the host is still queueing them.
+            auto issue_inputs = [&](size_t gi) {
+                if (gi >= group_end.size()) return;
+                for (int i = gi ? group_end[gi - 1] : 0; i < group_end[gi]; ++i) {
+                    const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
+                                 vb = tensor_bytes_contiguous(v[i]);
+                    char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb);
+                    KVC_CUDA(cudaMemcpyAsync(dq, q[i].data, qb, cudaMemcpyHostToDevice, pipe.h2d));
+                    KVC_CUDA(cudaMemcpyAsync(dk, k[i].data, kb, cudaMemcpyHostToDevice, pipe.h2d));
+                    KVC_CUDA(cudaMemcpyAsync(dv, v[i].data, vb, cudaMemcpyHostToDevice, pipe.h2d));
+                }
+                KVC_CUDA(cudaEventRecord(pipe.events[2 + 2 * gi], pipe.h2d));
+            };
+            issue_inputs(0);
+            int first = 0;
+            struct HintReset { ~HintReset() { kvc::set_batch_previous(nullptr); } } hint_reset;
+            first = 0;
+            for (size_t gi = 0; gi < group_end.size(); ++gi) {
+                KVC_CUDA(cudaStreamWaitEvent(s, pipe.events[2 + 2 * gi], 0));
+                for (int i = first; i < group_end[gi]; ++i) {
+                    const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
+                                 vb = tensor_bytes_contiguous(v[i]);
+                    char *dq = slabs[(size_t)i], *dk = dq + al(qb), *dv = dk + al(kb), *dout = dv + al(vb);
+                    kvc_tensor tq = q[i], tk = k[i], tv = v[i], to = outs[i];
+                    tq.data = dq; tk.data = dk; tv.data = dv; to.data = dout;
+                    // layer i's launches follow layer i - 1's on the stream with nothing in between
+                    kvc::set_batch_previous(i > first ? caches[i - 1] : nullptr);
+                    kvc::cache_attention(caches[i], tq, tk, tv, scale, mask_mode, nullptr, to, s);
+                }
+                kvc::set_batch_previous(nullptr);
+                cudaEvent_t out_ready = pipe.events[3 + 2 * gi];
                 KVC_CUDA(cudaEventRecord(out_ready, s));
                 KVC_CUDA(cudaStreamWaitEvent(pipe.d2h, out_ready, 0));
-                KVC_CUDA(cudaMemcpyAsync(outs[i].data, dout, ob, cudaMemcpyDeviceToHost, pipe.d2h));
+                for (int i = first; i < group_end[gi]; ++i) {
+                    const size_t qb = tensor_bytes_contiguous(q[i]), kb = tensor_bytes_contiguous(k[i]),
+                                 vb = tensor_bytes_contiguous(v[i]), ob = tensor_bytes_contiguous(outs[i]);
+                    char *dout = slabs[(size_t)i] + al(qb) + al(kb) + al(vb);
+                    KVC_CUDA(cudaMemcpyAsync(outs[i].data, dout, ob, cudaMemcpyDeviceToHost, pipe.d2h));
+                }
+                first = group_end[gi];
+                issue_inputs(gi + 1);
             }
             KVC_CUDA(cudaEventRecord(done, pipe.d2h));
             KVC_CUDA(cudaStreamWaitEvent(s, done, 0));
