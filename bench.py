@@ -176,6 +176,7 @@ def cpu_decode_step_time(w, budget_s: float, steps: int = 1, warmup: int = 0):
     import kvcache_oracle as orc
 
     orc.build()
+    orc.use_all_host_threads()   # torch.distributed.run hands its workers OMP_NUM_THREADS=1
     B, Hq, Hkv, D, T0 = w["B"], w["Hq"], w["Hkv"], w["D"], w["context"]
     if w["kind"] == "gemma3":
         # per-layer average of what a step reads: 22 wrapped 512-token rings and 4 full-context layers

@@ -451,6 +451,15 @@ void orc_append(const void *src, void *dst, int esize, int B, int H, int S, int 
                (size_t)S * W * esize);
 }
 
+/* Thread count of the following parallel regions (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

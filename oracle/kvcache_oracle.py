@@ -335,6 +335,14 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """Run the C kernels on every hardware thread this process may use, whatever OMP_NUM_THREADS says
+    (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(ctypes.c_int(n))
+    return num_threads()
+
+
 # ---------------------------------------------------------------------------
 # masks (KVCache.swift:253-275)
 # ---------------------------------------------------------------------------
