@@ -1,0 +1,467 @@
+// Prefill / long verify chunks over raw K/V on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// attentionWithCacheUpdate's scaledDotProductAttention call (AttentionUtils.swift:87-93) for a chunk
+// of L query positions per head: one CTA takes 128 consecutive positions of one query head and walks
+// the 128-key tiles it can see.
+//
+//   warp 0      TMA producer: the Q block once, then K and V tiles into a 2-stage ring
+//   warp 1      owns the TMEM allocation; lane 0 issues the MMAs:
+//                 S_j = Q K_j^T          (A = Q, B = K_j, both K-major)      -> TMEM S buffer j % 2
+//                 O_j = P_j V_j          (A = P_j from shared memory, B = V_j MN-major) -> TMEM O buffer j % 2
+//   warps 2..5  softmax: thread = query row = TMEM lane. Two passes over S_j in TMEM (row maximum, then
+//               exponentials), P_j written as the next MMA's A operand in shared memory, O_{j-1} pulled
+//               out of TMEM and folded into the row's register accumulator with the usual rescale.
+//
+// Every O_j is a fresh product (no accumulation in TMEM), so the running-maximum rescale never has to
+// touch TMEM. S_{j+1} is issued before O_j: the tensor cores work on the next scores while the
+// softmax warps are busy with the current ones.
+//
+// Shared-memory operand layout (what TMA's 128-byte swizzle writes): a box is 128 rows x 128 bytes
+// (64 elements), 16-byte chunk c of row r at chunk c ^ (r & 7); a 128 x 128 tile is two boxes.
+// Matrix descriptors: K-major operands advance 32 bytes per 16-element k-step inside the row, 8-row
+// groups are 1024 bytes apart; the MN-major V tile advances 2048 bytes per 16 keys, its two 64-dim
+// halves are 16384 bytes apart (leading offset) and its 8-key groups 1024 bytes (stride offset).
+//
+// Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
+// its TMEM.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <type_traits>
+
+#include "attn_common.cuh"
+#include "common.h"
+
+namespace kvc {
+namespace {
+
+using namespace dev;
+
+constexpr int TC_ROWS = 128;                 // query rows per CTA = TMEM lanes
+constexpr int TC_KEYS = 128;                 // keys per tile
+constexpr int TC_D = 128;
+constexpr int TC_BOX = 128 * 128;            // bytes of one 64-element-wide box of 128 rows
+constexpr int TC_TILE = 2 * TC_BOX;          // 32 KB: a 128 x 128 16-bit tile
+constexpr int TC_STAGES = 2;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_TMEM_COLS = 512;       // S0 | S1 | O0 | O1, 128 fp32 columns each
+
+struct ChunkTcParams {
+    void *out;
+    int64_t o_sb, o_sh, o_sl;
+    int32_t B, Hq, Hkv, L;
+    int64_t T;
+    int32_t row_blocks;
+    int32_t causal;
+    int64_t causal_offset;
+    float scale_log2;
+    int *status;
+};
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // start address, leading and stride byte offsets in 16-byte units; descriptor version 1 (bit 46);
+    // 128-byte swizzle (2 at bits 61..63)
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Arrives on the barrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) { return pack_h2(lo, hi); }
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Barrier slots in shared memory.
+enum : int {
+    BAR_Q = 0,
+    BAR_KV_FULL = 1,                       // [TC_STAGES]
+    BAR_KV_EMPTY = BAR_KV_FULL + TC_STAGES, // [TC_STAGES]
+    BAR_S_FULL = BAR_KV_EMPTY + TC_STAGES,  // [2]
+    BAR_S_EMPTY = BAR_S_FULL + 2,           // [2]
+    BAR_P_FULL = BAR_S_EMPTY + 2,
+    BAR_P_EMPTY = BAR_P_FULL + 1,
+    BAR_O_FULL = BAR_P_EMPTY + 1,           // [2]
+    BAR_O_EMPTY = BAR_O_FULL + 2,           // [2]
+    BAR_COUNT = BAR_O_EMPTY + 2
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                     const __grid_constant__ CUtensorMap vmap, const ChunkTcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char *sq = base;                                  // Q block
+    unsigned char *skv = sq + TC_TILE;                         // ring: stage s = K tile | V tile
+    unsigned char *sp = skv + TC_STAGES * 2 * TC_TILE;         // P tile
+    uint64_t *bars = (uint64_t *)(sp + TC_TILE);
+    uint32_t *tmem_slot = (uint32_t *)(bars + BAR_COUNT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // unit = (batch, KV head, row block, query head of the group): the CTAs that share K/V are neighbours
+    const int rep = p.Hq / p.Hkv;
+    int u = blockIdx.x;
+    const int hr = u % rep; u /= rep;
+    const int rb = u % p.row_blocks; u /= p.row_blocks;
+    const int hk = u % p.Hkv;
+    const int b = u / p.Hkv;
+    const int hq = hk * rep + hr;
+    const int l0 = rb * TC_ROWS;
+    // keys this block can see: up to the last row's limit
+    const int64_t last_l = min((int64_t)p.L - 1, (int64_t)l0 + TC_ROWS - 1);
+    const int64_t keys = p.causal ? min(p.T, p.causal_offset + last_l + 1) : p.T;
+    const int n_tiles = (int)((keys + TC_KEYS - 1) / TC_KEYS);
+
+    if (tid == 0) {
+        mbar_init(&bars[BAR_Q], 1);
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&bars[BAR_KV_FULL + s], 1);
+            mbar_init(&bars[BAR_KV_EMPTY + s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[BAR_S_FULL + s], 1);
+            mbar_init(&bars[BAR_S_EMPTY + s], 128);
+            mbar_init(&bars[BAR_O_FULL + s], 1);
+            mbar_init(&bars[BAR_O_EMPTY + s], 128);
+        }
+        mbar_init(&bars[BAR_P_FULL], 128);
+        mbar_init(&bars[BAR_P_EMPTY], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();  // everything below reads what earlier kernels on the stream wrote
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(&bars[BAR_Q], TC_TILE);
+            tma_load_4d(sq, &qmap, &bars[BAR_Q], 0, l0, hq, b);
+            tma_load_4d(sq + TC_BOX, &qmap, &bars[BAR_Q], 64, l0, hq, b);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % TC_STAGES;
+                if (j >= TC_STAGES) ok = mbar_wait(&bars[BAR_KV_EMPTY + s], ((j / TC_STAGES) - 1) & 1);
+                if (!ok) break;
+                unsigned char *kt = skv + (size_t)s * 2 * TC_TILE, *vt = kt + TC_TILE;
+                mbar_expect_tx(&bars[BAR_KV_FULL + s], 2 * TC_TILE);
+                const int tok = j * TC_KEYS;
+                tma_load_4d(kt, &kmap, &bars[BAR_KV_FULL + s], 0, tok, hk, b);
+                tma_load_4d(kt + TC_BOX, &kmap, &bars[BAR_KV_FULL + s], 64, tok, hk, b);
+                tma_load_4d(vt, &vmap, &bars[BAR_KV_FULL + s], 0, tok, hk, b);
+                tma_load_4d(vt + TC_BOX, &vmap, &bars[BAR_KV_FULL + s], 64, tok, hk, b);
+            }
+            if (!ok) atomicExch(p.status, 21);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulator (bits 4-5 = 1), A and B formats (bits 7-9 and 10-12:
+            // 0 = f16, 1 = bf16), B major at bit 16 (1 = MN-major), N / 8 at bits 17-22, M / 16 at 24-28
+            constexpr uint32_t FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t IDESC_PV = IDESC | (1u << 16);
+            const uint32_t q_addr = smem_u32(sq), p_addr = smem_u32(sp);
+            bool ok = mbar_wait(&bars[BAR_Q], 0);
+            auto issue_s = [&](int j) {
+                const int s = j % TC_STAGES;
+                if (!mbar_wait(&bars[BAR_KV_FULL + s], (j / TC_STAGES) & 1)) return false;
+                if (j >= 2 && !mbar_wait(&bars[BAR_S_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE);
+#pragma unroll
+                for (int ks = 0; ks < TC_D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * TC_BOX + (ks & 3) * 32);
+                    umma_f16(tmem + (uint32_t)(j & 1) * 128u, umma_desc(q_addr + off, 16, 1024), umma_desc(k_addr + off, 16, 1024),
+                             IDESC, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars[BAR_S_FULL + (j & 1)]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = issue_s(j + 1);
+                if (!ok) break;
+                ok = mbar_wait(&bars[BAR_P_FULL], j & 1);
+                if (ok && j >= 2) ok = mbar_wait(&bars[BAR_O_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const int s = j % TC_STAGES;
+                const uint32_t v_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE + TC_TILE);
+#pragma unroll
+                for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
+                    const uint32_t a_off = (uint32_t)((ks >> 2) * TC_BOX + (ks & 3) * 32);
+                    umma_f16(tmem + 256u + (uint32_t)(j & 1) * 128u, umma_desc(p_addr + a_off, 16, 1024),
+                             umma_desc(v_addr + (uint32_t)ks * 2048u, 16384, 1024), IDESC_PV, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars[BAR_O_FULL + (j & 1)]);
+                umma_commit(&bars[BAR_P_EMPTY]);
+                umma_commit(&bars[BAR_KV_EMPTY + s]);
+            }
+            if (!ok) atomicExch(p.status, 22);
+        }
+    } else {
+        // ---------------- softmax: thread = row ----------------
+        const int quarter = warp & 3;                       // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const int64_t l = (int64_t)l0 + row;
+        const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1;   // last visible key
+        const int64_t block_min_limit = p.causal ? min(p.T - 1, p.causal_offset + l0) : p.T - 1;
+        float o_acc[TC_D];
+#pragma unroll
+        for (int i = 0; i < TC_D; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+        bool ok = true;
+        unsigned char *p_row = sp + row * 128;
+        const int sw = row & 7;
+
+        auto fold_o = [&](int j, float alpha) {
+            if (!mbar_wait(&bars[BAR_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                float v[32];
+                tmem_ld32(lane_addr + 256u + (uint32_t)(j & 1) * 128u + cb * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o_acc[cb * 32 + i] = fmaf(o_acc[cb * 32 + i], alpha, v[i]);
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[BAR_O_EMPTY + (j & 1)]);
+            return true;
+        };
+
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!ok) break;
+            ok = mbar_wait(&bars[BAR_S_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
+            const int64_t key0 = (int64_t)j * TC_KEYS;
+            const bool masked = key0 + TC_KEYS - 1 > block_min_limit;   // some row of the block loses keys here
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                float v[32];
+                tmem_ld32(s_addr + cb * 32, v);
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + cb * 32 + i > limit) v[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+            const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+            // the P tile is free once the previous tile's O product has read it
+            if (j >= 1) ok = mbar_wait(&bars[BAR_P_EMPTY], (j - 1) & 1);
+            if (!ok) break;
+            // pass 2: exponentials -> P (A operand of the next MMA) and the row sum
+            float sum = 0.f;
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                float v[32];
+                tmem_ld32(s_addr + cb * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float e = fast_exp2(fmaf(v[i], p.scale_log2, neg_m));
+                    if (masked && key0 + cb * 32 + i > limit) e = 0.f;
+                    v[i] = e;
+                    sum += e;
+                }
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int kc = cb * 4 + c4;   // 16-byte chunk (8 keys) of the row
+                    uint4 w;
+                    w.x = pack_pair<T>(v[c4 * 8 + 0], v[c4 * 8 + 1]);
+                    w.y = pack_pair<T>(v[c4 * 8 + 2], v[c4 * 8 + 3]);
+                    w.z = pack_pair<T>(v[c4 * 8 + 4], v[c4 * 8 + 5]);
+                    w.w = pack_pair<T>(v[c4 * 8 + 6], v[c4 * 8 + 7]);
+                    *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
+                }
+            }
+            // P is visible to the tensor cores (async proxy) before the MMA warp hears about it; the S
+            // buffer is free for tile j + 2
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&bars[BAR_P_FULL]);
+            mbar_arrive(&bars[BAR_S_EMPTY + (j & 1)]);
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+            // the previous tile's product, rescaled from its own maximum to the one before this tile's
+            if (j >= 1) ok = fold_o(j - 1, alpha_prev);
+            alpha_prev = alpha;
+        }
+        if (ok && n_tiles > 0) ok = fold_o(n_tiles - 1, alpha_prev);
+        if (!ok) {
+            atomicExch(p.status, 23);
+        } else if (l < p.L) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T *dst = (T *)p.out + b * p.o_sb + hq * p.o_sh + l * p.o_sl;
+#pragma unroll
+            for (int c8 = 0; c8 < TC_D / 8; ++c8) {
+                uint4 w;
+                w.x = pack_pair<T>(o_acc[c8 * 8 + 0] * inv, o_acc[c8 * 8 + 1] * inv);
+                w.y = pack_pair<T>(o_acc[c8 * 8 + 2] * inv, o_acc[c8 * 8 + 3] * inv);
+                w.z = pack_pair<T>(o_acc[c8 * 8 + 4] * inv, o_acc[c8 * 8 + 5] * inv);
+                w.w = pack_pair<T>(o_acc[c8 * 8 + 6] * inv, o_acc[c8 * 8 + 7] * inv);
+                *(uint4 *)(dst + c8 * 8) = w;
+            }
+        }
+    }
+    // all roles meet here; TMEM goes back whatever happened
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_tc() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)ptr;
+        else (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+// [B, H, rows, D] view, element strides (inner 1): boxes of 128 rows x 64 elements, 128-byte swizzle,
+// rows beyond `rows` read as zero.
+bool make_map_tc(CUtensorMap *map, const void *data, int32_t dtype, int64_t rows, int H, int B, int64_t s_row, int64_t s_h,
+                 int64_t s_b) {
+    EncodeTiledFn fn = encode_tiled_tc();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)TC_D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)(H > 1 ? s_h : s_row * rows) * 2,
+                                   (cuuint64_t)(B > 1 ? s_b : (H > 1 ? s_h * H : s_row * rows)) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == KVC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return fn(map, dt, 4, const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int H, int B) {
+    auto ok = [](int64_t st) { return st > 0 && (st * 2) % 16 == 0; };
+    if (((uintptr_t)data & 15) != 0 || !ok(s_row) || s_row < TC_D) return false;
+    if (H > 1 && !ok(s_h)) return false;
+    if (B > 1 && !ok(s_b)) return false;
+    return true;
+}
+
+template <typename T>
+void launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
+                     cudaStream_t stream) {
+    const size_t smem = (size_t)TC_TILE * (2 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 1024;
+    static bool configured[64] = {false};
+    const int dev = current_device();
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        KVC_CUDA(cudaFuncSetAttribute(attn_chunk_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev] = true;
+    }
+    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
+    ++g_launch_count;
+}
+
+}  // namespace
+
+// Returns 1 when the call was taken (head dim 128, f16 / bf16 raw K and V, no array mask, enough
+// 128-row blocks to fill the part), 0 otherwise. KVC_CHUNK_TC=0 turns the path off.
+int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
+    static const bool off = [] {
+        const char *e = std::getenv("KVC_CHUNK_TC");
+        return e && e[0] == '0';
+    }();
+    if (off) return 0;
+    if (a.D != TC_D || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
+    if (a.k.kind != SRC_RAW || a.v.kind != SRC_RAW || a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib || a.new_k) return 0;
+    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30 || a.L < 64) return 0;
+    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
+    const int64_t row_blocks = ((int64_t)a.L + TC_ROWS - 1) / TC_ROWS;
+    const int64_t ctas = (int64_t)a.B * a.Hq * row_blocks;
+    // a CTA owns an SM (its TMEM and 193 KB of shared memory): fewer blocks than half the part run
+    // better on the split-K kernel
+    if (ctas < sm_count(a.device) / 2 || ctas > (int64_t)1 << 30) return 0;
+    if (!strides_fit(a.q, a.q_sl, a.q_sh, a.q_sb, a.Hq, a.B)) return 0;
+    if (!strides_fit(a.k.data, a.k.st, a.k.sh, a.k.sb, a.Hkv, a.B) || !strides_fit(a.v.data, a.v.st, a.v.sh, a.v.sb, a.Hkv, a.B)) return 0;
+    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
+    int *status = device_status_word(a.device);
+    if (!status) return 0;
+    CUtensorMap qmap, kmap, vmap;
+    if (!make_map_tc(&qmap, a.q, a.q_dtype, a.L, a.Hq, a.B, a.q_sl, a.q_sh, a.q_sb)) return 0;
+    if (!make_map_tc(&kmap, a.k.data, a.k.dtype, a.T, a.Hkv, a.B, a.k.st, a.k.sh, a.k.sb)) return 0;
+    if (!make_map_tc(&vmap, a.v.data, a.v.dtype, a.T, a.Hkv, a.B, a.v.st, a.v.sh, a.v.sb)) return 0;
+    ChunkTcParams p = {};
+    p.out = a.out;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
+    p.row_blocks = (int)row_blocks;
+    p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    p.causal_offset = a.mask.causal_offset;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.status = status;
+    if (const char *e = std::getenv("KVC_TRACE_DISPATCH"))
+        if (e[0] == '1') fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
+    if (a.q_dtype == KVC_BF16) launch_tc_typed<__nv_bfloat16>(qmap, kmap, vmap, p, (int)ctas, stream);
+    else launch_tc_typed<__half>(qmap, kmap, vmap, p, (int)ctas, stream);
+    return 1;
+}
+
+}  // namespace kvc

@@ -11,6 +11,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_affine(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
@@ -23,7 +24,9 @@ bool force_general() {
 
 int launch_attention(const AttnArgs &a, cudaStream_t stream) {
     if (!force_general()) {
-        int n = launch_attention_decode(a, stream);
+        int n = launch_attention_chunk_tc(a, stream);   // long chunks over raw caches: tcgen05 kernel
+        if (n > 0) return n;
+        n = launch_attention_decode(a, stream);
         if (n > 0) return n;
         n = launch_attention_affine(a, stream);
         if (n > 0) return n;
