@@ -8,13 +8,15 @@
 //   warp 1      owns the TMEM allocation; lane 0 issues the MMAs:
 //                 S_j = Q K_j^T          (A = Q, B = K_j, both K-major)      -> TMEM S buffer j % 2
 //                 O_j = P_j V_j          (A = P_j from shared memory, B = V_j MN-major) -> TMEM O buffer j % 2
-//   warps 2..5  softmax: thread = query row = TMEM lane. Two passes over S_j in TMEM (row maximum, then
-//               exponentials), P_j written as the next MMA's A operand in shared memory, O_{j-1} pulled
-//               out of TMEM and folded into the row's register accumulator with the usual rescale.
+//   warps 2..5  softmax: thread = query row = TMEM lane. S_j comes out of TMEM in one round trip (128
+//               registers), row maximum, exponentials, P_j written as the next MMA's A operand in
+//               shared memory; the rescale factor of the tile goes to the correction warps
+//   warps 6..9  correction: thread = query row. O_j comes out of TMEM and is folded into the row's
+//               register accumulator, o = o * alpha_j + O_j; normalisation and the store at the end
 //
 // Every O_j is a fresh product (no accumulation in TMEM), so the running-maximum rescale never has to
 // touch TMEM. S_{j+1} is issued before O_j: the tensor cores work on the next scores while the
-// softmax warps are busy with the current ones.
+// softmax warps are busy with the current ones, and the correction warps trail by one product.
 //
 // Shared-memory operand layout (what TMA's 128-byte swizzle writes): a box is 128 rows x 128 bytes
 // (64 elements), 16-byte chunk c of row r at chunk c ^ (r & 7); a 128 x 128 tile is two boxes.
@@ -44,7 +46,7 @@ constexpr int TC_D = 128;
 constexpr int TC_BOX = 128 * 128;            // bytes of one 64-element-wide box of 128 rows
 constexpr int TC_TILE = 2 * TC_BOX;          // 32 KB: a 128 x 128 16-bit tile
 constexpr int TC_STAGES = 2;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;
 constexpr uint32_t TC_TMEM_COLS = 512;       // S0 | S1 | O0 | O1, 128 fp32 columns each
 
 struct ChunkTcParams {
@@ -97,6 +99,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load without the wait: several can be in flight, tmem_ld_wait() closes them all.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) { return pack_h2(lo, hi); }
 template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
@@ -116,7 +131,10 @@ enum : int {
     BAR_P_EMPTY = BAR_P_FULL + 1,
     BAR_O_FULL = BAR_P_EMPTY + 1,           // [2]
     BAR_O_EMPTY = BAR_O_FULL + 2,           // [2]
-    BAR_COUNT = BAR_O_EMPTY + 2
+    BAR_A_FULL = BAR_O_EMPTY + 2,           // [2] rescale factors of a tile written
+    BAR_A_EMPTY = BAR_A_FULL + 2,           // [2] ... and read
+    BAR_L_FULL = BAR_A_EMPTY + 2,           // row sums written
+    BAR_COUNT = BAR_L_FULL + 1
 };
 
 template <typename T>
@@ -130,6 +148,8 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
     unsigned char *sp = skv + TC_STAGES * 2 * TC_TILE;         // P tile
     uint64_t *bars = (uint64_t *)(sp + TC_TILE);
     uint32_t *tmem_slot = (uint32_t *)(bars + BAR_COUNT);
+    float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128] rescale factor of tile j for each row
+    float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128] final row sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // unit = (batch, KV head, row block, query head of the group): the CTAs that share K/V are neighbours
@@ -158,6 +178,11 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             mbar_init(&bars[BAR_O_FULL + s], 1);
             mbar_init(&bars[BAR_O_EMPTY + s], 128);
         }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[BAR_A_FULL + s], 128);
+            mbar_init(&bars[BAR_A_EMPTY + s], 128);
+        }
+        mbar_init(&bars[BAR_L_FULL], 128);
         mbar_init(&bars[BAR_P_FULL], 128);
         mbar_init(&bars[BAR_P_EMPTY], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -243,7 +268,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             }
             if (!ok) atomicExch(p.status, 22);
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------- softmax: thread = row ----------------
         const int quarter = warp & 3;                       // the TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;
@@ -251,98 +276,107 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
         const int64_t l = (int64_t)l0 + row;
         const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l) : p.T - 1;   // last visible key
         const int64_t block_min_limit = p.causal ? min(p.T - 1, p.causal_offset + l0) : p.T - 1;
-        float o_acc[TC_D];
-#pragma unroll
-        for (int i = 0; i < TC_D; ++i) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         unsigned char *p_row = sp + row * 128;
         const int sw = row & 7;
-
-        auto fold_o = [&](int j, float alpha) {
-            if (!mbar_wait(&bars[BAR_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-                float v[32];
-                tmem_ld32(lane_addr + 256u + (uint32_t)(j & 1) * 128u + cb * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[cb * 32 + i] = fmaf(o_acc[cb * 32 + i], alpha, v[i]);
-            }
-            tc_fence_before();
-            mbar_arrive(&bars[BAR_O_EMPTY + (j & 1)]);
-            return true;
-        };
-
         for (int j = 0; j < n_tiles; ++j) {
-            if (!ok) break;
             ok = mbar_wait(&bars[BAR_S_FULL + (j & 1)], (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
+            uint32_t raw[TC_KEYS];
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) tmem_ld32_issue(s_addr + cb * 32, raw + cb * 32);
+            tmem_ld_wait();
+            // the scores are in registers: the S buffer is free for tile j + 2
+            tc_fence_before();
+            mbar_arrive(&bars[BAR_S_EMPTY + (j & 1)]);
             const int64_t key0 = (int64_t)j * TC_KEYS;
-            const bool masked = key0 + TC_KEYS - 1 > block_min_limit;   // some row of the block loses keys here
-            // pass 1: row maximum
-            float mx = -INFINITY;
+            if (key0 + TC_KEYS - 1 > block_min_limit) {   // some row of the block loses keys in this tile
 #pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-                float v[32];
-                tmem_ld32(s_addr + cb * 32, v);
-                if (masked) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + cb * 32 + i > limit) v[i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < TC_KEYS; ++i)
+                    if (key0 + i > limit) raw[i] = 0xff800000u;   // -inf
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < TC_KEYS; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
             const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+            // hand the tile's rescale factor to the correction warps
+            if (j >= 2) ok = mbar_wait(&bars[BAR_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
+            if (!ok) break;
+            s_alpha[(j & 1) * TC_ROWS + row] = alpha;
+            mbar_arrive(&bars[BAR_A_FULL + (j & 1)]);
             // the P tile is free once the previous tile's O product has read it
             if (j >= 1) ok = mbar_wait(&bars[BAR_P_EMPTY], (j - 1) & 1);
             if (!ok) break;
-            // pass 2: exponentials -> P (A operand of the next MMA) and the row sum
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-                float v[32];
-                tmem_ld32(s_addr + cb * 32, v);
+            for (int kc = 0; kc < TC_KEYS / 8; ++kc) {   // 16-byte chunk (8 keys) of the row
+                float e[8];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float e = fast_exp2(fmaf(v[i], p.scale_log2, neg_m));
-                    if (masked && key0 + cb * 32 + i > limit) e = 0.f;
-                    v[i] = e;
-                    sum += e;
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));   // exp2(-inf) = 0
+                    sum4[i & 3] += e[i];
                 }
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const int kc = cb * 4 + c4;   // 16-byte chunk (8 keys) of the row
-                    uint4 w;
-                    w.x = pack_pair<T>(v[c4 * 8 + 0], v[c4 * 8 + 1]);
-                    w.y = pack_pair<T>(v[c4 * 8 + 2], v[c4 * 8 + 3]);
-                    w.z = pack_pair<T>(v[c4 * 8 + 4], v[c4 * 8 + 5]);
-                    w.w = pack_pair<T>(v[c4 * 8 + 6], v[c4 * 8 + 7]);
-                    *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
-                }
+                uint4 w;
+                w.x = pack_pair<T>(e[0], e[1]);
+                w.y = pack_pair<T>(e[2], e[3]);
+                w.z = pack_pair<T>(e[4], e[5]);
+                w.w = pack_pair<T>(e[6], e[7]);
+                *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
             }
-            // P is visible to the tensor cores (async proxy) before the MMA warp hears about it; the S
-            // buffer is free for tile j + 2
+            // P is visible to the tensor cores (async proxy) before the MMA warp hears about it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
             mbar_arrive(&bars[BAR_P_FULL]);
-            mbar_arrive(&bars[BAR_S_EMPTY + (j & 1)]);
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_run = m_new;
-            // the previous tile's product, rescaled from its own maximum to the one before this tile's
-            if (j >= 1) ok = fold_o(j - 1, alpha_prev);
-            alpha_prev = alpha;
         }
-        if (ok && n_tiles > 0) ok = fold_o(n_tiles - 1, alpha_prev);
-        if (!ok) {
+        if (ok) {
+            s_lsum[row] = l_run;
+            mbar_arrive(&bars[BAR_L_FULL]);
+        } else {
             atomicExch(p.status, 23);
+        }
+    } else {
+        // ---------------- correction: thread = row ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + 256u;
+        const int64_t l = (int64_t)l0 + row;
+        float o_acc[TC_D];
+#pragma unroll
+        for (int i = 0; i < TC_D; ++i) o_acc[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = mbar_wait(&bars[BAR_A_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
+            const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
+            mbar_arrive(&bars[BAR_A_EMPTY + (j & 1)]);
+            ok = mbar_wait(&bars[BAR_O_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t raw[64];
+                tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64, raw);
+                tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64 + 32, raw + 32);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 64; ++i) o_acc[half * 64 + i] = fmaf(o_acc[half * 64 + i], alpha, __uint_as_float(raw[i]));
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[BAR_O_EMPTY + (j & 1)]);
+        }
+        if (ok) ok = mbar_wait(&bars[BAR_L_FULL], 0);
+        if (!ok) {
+            atomicExch(p.status, 24);
         } else if (l < p.L) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const float l_sum = s_lsum[row];
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             T *dst = (T *)p.out + b * p.o_sb + hq * p.o_sh + l * p.o_sl;
 #pragma unroll
             for (int c8 = 0; c8 < TC_D / 8; ++c8) {
@@ -408,7 +442,7 @@ bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int 
 template <typename T>
 void launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
-    const size_t smem = (size_t)TC_TILE * (2 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 1024;
+    const size_t smem = (size_t)TC_TILE * (2 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 3 * TC_ROWS * sizeof(float) + 1024;
     static bool configured[64] = {false};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
