@@ -63,6 +63,10 @@ WORKLOADS["cfg2_profile_2layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"]
 WORKLOADS["cfg4_profile_2layers"] = dict(WORKLOADS["cfg4_quant4_bf16_qwen2_7b"], layers=2)
 WORKLOADS["cfg4_ragged_profile_2layers"] = dict(WORKLOADS["cfg4_ragged_quant4_bf16_qwen2_7b"], layers=2)
 WORKLOADS["cfg5_profile_2layers"] = dict(WORKLOADS["cfg5_turbo_k3v4_llama3_70b"], layers=2)
+# Prefill of the default model shape: one 512-token chunk per layer on top of the 8192-token prefix
+# (attentionWithCacheUpdate with a causal mask), 4 layers so that a capture stays small. A side
+# workload: its metric is prefill tokens/s and its roofline is the tensor-core one.
+WORKLOADS["cfg2_prefill512_4layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=4, prefill=512)
 DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
 
 
@@ -442,12 +446,113 @@ def run_ragged(args, w, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, w, rank, world, local_rank):
+    """One step = a chunk of w["prefill"] new tokens through every layer (append + causal attention over
+    prefix + chunk), then the chunk is trimmed off again so that every step does the same work. Each
+    rank runs its own sequences (no collective)."""
+    import torch
+    import kvcache_b200 as kvc
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (the library has no CPU fallback)"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch_dtype(w["dtype"])
+    B, Hq, Hkv, D, Lyr, L, ctx = w["B"], w["Hq"], w["Hkv"], w["D"], w["layers"], w["prefill"], w["context"]
+    g = torch.Generator(device="cpu").manual_seed(99 + rank)
+    chunk_k = torch.randn((B, Hkv, w["chunk"], D), generator=g).to(dtype).to(dev)
+    chunk_v = torch.randn((B, Hkv, w["chunk"], D), generator=g).to(dtype).to(dev)
+    caches = [make_cache(kvc, w, ctx + L + 8, i) for i in range(Lyr)]
+    for c in caches:
+        fill_cache(kvc, c, w, B, Hkv, chunk_k, chunk_v)
+    qs = [torch.randn((B, Hq, L, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    ks = [torch.randn((B, Hkv, L, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    vs = [torch.randn((B, Hkv, L, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+    outs = [torch.empty_like(q) for q in qs]
+    scale = D ** -0.5
+
+    def one_step():
+        for i, c in enumerate(caches):
+            c.attention(qs[i], ks[i], vs[i], scale, "causal", out=outs[i])
+            c.trim(L)
+
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    kvc.launch_count(reset=True)
+    kvc.timing_enable(True)
+    kvc.timing_read(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        one_step()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    w1 = time.perf_counter()
+    k_ms, k_n = kvc.timing_read(reset=True)
+    kvc.timing_enable(False)
+    launches = kvc.launch_count()
+    ms_total = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    time.sleep(0.15)
+    sampler.stop()
+    # visible (query, key) pairs of one layer call: row l of the chunk sees ctx + l + 1 keys
+    pairs = sum(ctx + l + 1 for l in range(L))
+    flops = 4.0 * B * Hq * pairs * D
+    k_avg_ms = k_ms / max(k_n, 1)
+    achieved = flops / (k_avg_ms * 1e-3) / 1e12 if k_n else None
+    peak, peak_src = 1590.0, "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+    mp = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(mp):
+        try:
+            peak = float(json.load(open(mp))["bf16_tflops"])
+            peak_src = "MEASURED_PEAKS.json bf16_tflops (cuBLAS burst)"
+        except Exception:
+            pass
+    if rank == 0:
+        print(json.dumps({
+            "metric": "kv_cache_prefill_tokens_per_s", "value": world * B * L * args.steps / (ms_total * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": args.workload, "layers": Lyr, "Hq": Hq, "Hkv": Hkv, "D": D, "B": B, "context": ctx,
+                       "chunk": L, "parallelism": "single" if world == 1 else f"sequences x{world}",
+                       "l2": f"per-layer K+V working set {B * Hkv * (ctx + L) * 2 * D * 2 / 1e6:.0f} MB"},
+            "clocks": sampler.summary(w0, w1), "e2e": None, "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "kernel": "attention over the chunk (dominant)", "launch_ms": k_avg_ms, "launches_timed": k_n,
+                         "timing": "CUDA events around each attention launch (kvc_timing)",
+                         "flops_per_launch": flops, "peak_source": peak_src},
+            "cpu_baseline": None}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch
     import kvcache_b200 as kvc
 
     if w.get("ragged"):
         return run_ragged(args, w, rank, world, local_rank)
+    if w.get("prefill"):
+        return run_prefill(args, w, rank, world, local_rank)
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (the library has no CPU fallback)"
     dev = torch.device("cuda", local_rank)

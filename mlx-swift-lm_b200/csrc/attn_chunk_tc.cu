@@ -4,7 +4,7 @@
 // of L query positions per head: one CTA takes 128 consecutive positions of one query head and walks
 // the 128-key tiles it can see.
 //
-//   warp 0      TMA producer: the Q block once, then K and V tiles into a 2-stage ring
+//   warp 0      TMA producer: the Q block once, then K and V tiles into two slots each (K one tile ahead)
 //   warp 1      owns the TMEM allocation; lane 0 issues the MMAs:
 //                 S_j = Q K_j^T          (A = Q, B = K_j, both K-major)      -> TMEM S buffer j % 2
 //                 O_j = P_j V_j          (A = P_j from shared memory, B = V_j MN-major) -> TMEM O buffer j % 2
@@ -123,9 +123,11 @@ template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float l
 // Barrier slots in shared memory.
 enum : int {
     BAR_Q = 0,
-    BAR_KV_FULL = 1,                       // [TC_STAGES]
-    BAR_KV_EMPTY = BAR_KV_FULL + TC_STAGES, // [TC_STAGES]
-    BAR_S_FULL = BAR_KV_EMPTY + TC_STAGES,  // [2]
+    BAR_K_FULL = 1,                         // [TC_STAGES]
+    BAR_K_EMPTY = BAR_K_FULL + TC_STAGES,   // [TC_STAGES] free once the S product has read the tile
+    BAR_V_FULL = BAR_K_EMPTY + TC_STAGES,   // [TC_STAGES]
+    BAR_V_EMPTY = BAR_V_FULL + TC_STAGES,   // [TC_STAGES] free once the O product has read the tile
+    BAR_S_FULL = BAR_V_EMPTY + TC_STAGES,   // [2]
     BAR_S_EMPTY = BAR_S_FULL + 2,           // [2]
     BAR_P_FULL = BAR_S_EMPTY + 2,
     BAR_P_EMPTY = BAR_P_FULL + 1,
@@ -169,8 +171,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
     if (tid == 0) {
         mbar_init(&bars[BAR_Q], 1);
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&bars[BAR_KV_FULL + s], 1);
-            mbar_init(&bars[BAR_KV_EMPTY + s], 1);
+            mbar_init(&bars[BAR_K_FULL + s], 1);
+            mbar_init(&bars[BAR_K_EMPTY + s], 1);
+            mbar_init(&bars[BAR_V_FULL + s], 1);
+            mbar_init(&bars[BAR_V_EMPTY + s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[BAR_S_FULL + s], 1);
@@ -207,17 +211,30 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             mbar_expect_tx(&bars[BAR_Q], TC_TILE);
             tma_load_4d(sq, &qmap, &bars[BAR_Q], 0, l0, hq, b);
             tma_load_4d(sq + TC_BOX, &qmap, &bars[BAR_Q], 64, l0, hq, b);
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            // A K slot is free as soon as its score product is done, a V slot only after the output
+            // product one tile later: K runs one tile ahead of V so that neither waits for the other.
+            auto load_k = [&](int j) {
                 const int s = j % TC_STAGES;
-                if (j >= TC_STAGES) ok = mbar_wait(&bars[BAR_KV_EMPTY + s], ((j / TC_STAGES) - 1) & 1);
-                if (!ok) break;
-                unsigned char *kt = skv + (size_t)s * 2 * TC_TILE, *vt = kt + TC_TILE;
-                mbar_expect_tx(&bars[BAR_KV_FULL + s], 2 * TC_TILE);
-                const int tok = j * TC_KEYS;
-                tma_load_4d(kt, &kmap, &bars[BAR_KV_FULL + s], 0, tok, hk, b);
-                tma_load_4d(kt + TC_BOX, &kmap, &bars[BAR_KV_FULL + s], 64, tok, hk, b);
-                tma_load_4d(vt, &vmap, &bars[BAR_KV_FULL + s], 0, tok, hk, b);
-                tma_load_4d(vt + TC_BOX, &vmap, &bars[BAR_KV_FULL + s], 64, tok, hk, b);
+                if (j >= TC_STAGES && !mbar_wait(&bars[BAR_K_EMPTY + s], ((j / TC_STAGES) - 1) & 1)) return false;
+                unsigned char *kt = skv + (size_t)s * 2 * TC_TILE;
+                mbar_expect_tx(&bars[BAR_K_FULL + s], TC_TILE);
+                tma_load_4d(kt, &kmap, &bars[BAR_K_FULL + s], 0, j * TC_KEYS, hk, b);
+                tma_load_4d(kt + TC_BOX, &kmap, &bars[BAR_K_FULL + s], 64, j * TC_KEYS, hk, b);
+                return true;
+            };
+            auto load_v = [&](int j) {
+                const int s = j % TC_STAGES;
+                if (j >= TC_STAGES && !mbar_wait(&bars[BAR_V_EMPTY + s], ((j / TC_STAGES) - 1) & 1)) return false;
+                unsigned char *vt = skv + (size_t)s * 2 * TC_TILE + TC_TILE;
+                mbar_expect_tx(&bars[BAR_V_FULL + s], TC_TILE);
+                tma_load_4d(vt, &vmap, &bars[BAR_V_FULL + s], 0, j * TC_KEYS, hk, b);
+                tma_load_4d(vt + TC_BOX, &vmap, &bars[BAR_V_FULL + s], 64, j * TC_KEYS, hk, b);
+                return true;
+            };
+            if (n_tiles > 0) ok = load_k(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = load_k(j + 1);
+                if (ok) ok = load_v(j);
             }
             if (!ok) atomicExch(p.status, 21);
         }
@@ -233,7 +250,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             bool ok = mbar_wait(&bars[BAR_Q], 0);
             auto issue_s = [&](int j) {
                 const int s = j % TC_STAGES;
-                if (!mbar_wait(&bars[BAR_KV_FULL + s], (j / TC_STAGES) & 1)) return false;
+                if (!mbar_wait(&bars[BAR_K_FULL + s], (j / TC_STAGES) & 1)) return false;
                 if (j >= 2 && !mbar_wait(&bars[BAR_S_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE);
@@ -244,17 +261,19 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                              IDESC, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&bars[BAR_S_FULL + (j & 1)]);
+                umma_commit(&bars[BAR_K_EMPTY + s]);
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) ok = issue_s(j + 1);
                 if (!ok) break;
-                ok = mbar_wait(&bars[BAR_P_FULL], j & 1);
+                const int s = j % TC_STAGES;
+                ok = mbar_wait(&bars[BAR_V_FULL + s], (j / TC_STAGES) & 1);
+                if (ok) ok = mbar_wait(&bars[BAR_P_FULL], j & 1);
                 if (ok && j >= 2) ok = mbar_wait(&bars[BAR_O_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const int s = j % TC_STAGES;
                 const uint32_t v_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE + TC_TILE);
 #pragma unroll
                 for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
@@ -264,7 +283,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 }
                 umma_commit(&bars[BAR_O_FULL + (j & 1)]);
                 umma_commit(&bars[BAR_P_EMPTY]);
-                umma_commit(&bars[BAR_KV_EMPTY + s]);
+                umma_commit(&bars[BAR_V_EMPTY + s]);
             }
             if (!ok) atomicExch(p.status, 22);
         }
@@ -449,7 +468,9 @@ void launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
         KVC_CUDA(cudaFuncSetAttribute(attn_chunk_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev] = true;
     }
+    KernelTimer timer(stream);
     KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
+    timer.stop();
     ++g_launch_count;
 }
 
