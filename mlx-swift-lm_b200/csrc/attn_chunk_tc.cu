@@ -10,7 +10,8 @@
 //                 O_j = P_j V_j          (A = P_j from shared memory, B = V_j MN-major) -> TMEM O buffer j % 2
 //   warps 2..5  softmax: thread = query row = TMEM lane. S_j comes out of TMEM in one round trip (128
 //               registers), row maximum, exponentials, P_j written as the next MMA's A operand in
-//               shared memory; the rescale factor of the tile goes to the correction warps
+//               shared memory (two P tiles, so that tile j + 1 never waits for O_j to have read
+//               P_j); the rescale factor of the tile goes to the correction warps
 //   warps 6..9  correction: thread = query row. O_j comes out of TMEM and is folded into the row's
 //               register accumulator, o = o * alpha_j + O_j; normalisation and the store at the end
 //
@@ -129,9 +130,9 @@ enum : int {
     BAR_V_EMPTY = BAR_V_FULL + TC_STAGES,   // [TC_STAGES] free once the O product has read the tile
     BAR_S_FULL = BAR_V_EMPTY + TC_STAGES,   // [2]
     BAR_S_EMPTY = BAR_S_FULL + 2,           // [2]
-    BAR_P_FULL = BAR_S_EMPTY + 2,
-    BAR_P_EMPTY = BAR_P_FULL + 1,
-    BAR_O_FULL = BAR_P_EMPTY + 1,           // [2]
+    BAR_P_FULL = BAR_S_EMPTY + 2,           // [2]
+    BAR_P_EMPTY = BAR_P_FULL + 2,           // [2]
+    BAR_O_FULL = BAR_P_EMPTY + 2,           // [2]
     BAR_O_EMPTY = BAR_O_FULL + 2,           // [2]
     BAR_A_FULL = BAR_O_EMPTY + 2,           // [2] rescale factors of a tile written
     BAR_A_EMPTY = BAR_A_FULL + 2,           // [2] ... and read
@@ -147,8 +148,8 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q block
     unsigned char *skv = sq + TC_TILE;                         // ring: stage s = K tile | V tile
-    unsigned char *sp = skv + TC_STAGES * 2 * TC_TILE;         // P tile
-    uint64_t *bars = (uint64_t *)(sp + TC_TILE);
+    unsigned char *sp = skv + TC_STAGES * 2 * TC_TILE;         // two P tiles
+    uint64_t *bars = (uint64_t *)(sp + 2 * TC_TILE);
     uint32_t *tmem_slot = (uint32_t *)(bars + BAR_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128] rescale factor of tile j for each row
     float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128] final row sums
@@ -187,8 +188,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             mbar_init(&bars[BAR_A_EMPTY + s], 128);
         }
         mbar_init(&bars[BAR_L_FULL], 128);
-        mbar_init(&bars[BAR_P_FULL], 128);
-        mbar_init(&bars[BAR_P_EMPTY], 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[BAR_P_FULL + s], 128);
+            mbar_init(&bars[BAR_P_EMPTY + s], 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -246,19 +249,24 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             constexpr uint32_t FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             constexpr uint32_t IDESC_PV = IDESC | (1u << 16);
-            const uint32_t q_addr = smem_u32(sq), p_addr = smem_u32(sp);
+            // Descriptors differ only in the start-address field (16-byte units): a box is 1024 units, a
+            // k-step inside a box row 2, 16 keys of the MN-major V tile 128.
+            const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
+            const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
+            const uint64_t v_desc = umma_desc(smem_u32(skv) + TC_TILE, 16384, 1024);
+            const uint64_t p_desc = umma_desc(smem_u32(sp), 16, 1024);
             bool ok = mbar_wait(&bars[BAR_Q], 0);
             auto issue_s = [&](int j) {
                 const int s = j % TC_STAGES;
                 if (!mbar_wait(&bars[BAR_K_FULL + s], (j / TC_STAGES) & 1)) return false;
                 if (j >= 2 && !mbar_wait(&bars[BAR_S_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE);
+                const uint64_t kd = k_desc + (uint64_t)(s * (2 * TC_TILE / 16));
+                const uint32_t d_addr = tmem + (uint32_t)(j & 1) * 128u;
 #pragma unroll
                 for (int ks = 0; ks < TC_D / 16; ++ks) {
-                    const uint32_t off = (uint32_t)((ks >> 2) * TC_BOX + (ks & 3) * 32);
-                    umma_f16(tmem + (uint32_t)(j & 1) * 128u, umma_desc(q_addr + off, 16, 1024), umma_desc(k_addr + off, 16, 1024),
-                             IDESC, ks > 0 ? 1u : 0u);
+                    const uint64_t off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
+                    umma_f16(d_addr, q_desc + off, kd + off, IDESC, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&bars[BAR_S_FULL + (j & 1)]);
                 umma_commit(&bars[BAR_K_EMPTY + s]);
@@ -270,19 +278,20 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 if (!ok) break;
                 const int s = j % TC_STAGES;
                 ok = mbar_wait(&bars[BAR_V_FULL + s], (j / TC_STAGES) & 1);
-                if (ok) ok = mbar_wait(&bars[BAR_P_FULL], j & 1);
+                if (ok) ok = mbar_wait(&bars[BAR_P_FULL + (j & 1)], (j >> 1) & 1);
                 if (ok && j >= 2) ok = mbar_wait(&bars[BAR_O_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(skv + (size_t)s * 2 * TC_TILE + TC_TILE);
+                const uint64_t vd = v_desc + (uint64_t)(s * (2 * TC_TILE / 16));
+                const uint64_t pd = p_desc + (uint64_t)((j & 1) * (TC_TILE / 16));
+                const uint32_t o_addr = tmem + 256u + (uint32_t)(j & 1) * 128u;
 #pragma unroll
                 for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
-                    const uint32_t a_off = (uint32_t)((ks >> 2) * TC_BOX + (ks & 3) * 32);
-                    umma_f16(tmem + 256u + (uint32_t)(j & 1) * 128u, umma_desc(p_addr + a_off, 16, 1024),
-                             umma_desc(v_addr + (uint32_t)ks * 2048u, 16384, 1024), IDESC_PV, ks > 0 ? 1u : 0u);
+                    const uint64_t a_off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
+                    umma_f16(o_addr, pd + a_off, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&bars[BAR_O_FULL + (j & 1)]);
-                umma_commit(&bars[BAR_P_EMPTY]);
+                umma_commit(&bars[BAR_P_EMPTY + (j & 1)]);
                 umma_commit(&bars[BAR_V_EMPTY + s]);
             }
             if (!ok) atomicExch(p.status, 22);
@@ -329,9 +338,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             if (!ok) break;
             s_alpha[(j & 1) * TC_ROWS + row] = alpha;
             mbar_arrive(&bars[BAR_A_FULL + (j & 1)]);
-            // the P tile is free once the previous tile's O product has read it
-            if (j >= 1) ok = mbar_wait(&bars[BAR_P_EMPTY], (j - 1) & 1);
+            // this P tile is free once the O product of two tiles ago has read it
+            if (j >= 2) ok = mbar_wait(&bars[BAR_P_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
             if (!ok) break;
+            unsigned char *p_dst = p_row + (j & 1) * TC_TILE;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int kc = 0; kc < TC_KEYS / 8; ++kc) {   // 16-byte chunk (8 keys) of the row
@@ -346,11 +356,11 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 w.y = pack_pair<T>(e[2], e[3]);
                 w.z = pack_pair<T>(e[4], e[5]);
                 w.w = pack_pair<T>(e[6], e[7]);
-                *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
+                *(uint4 *)(p_dst + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
             }
             // P is visible to the tensor cores (async proxy) before the MMA warp hears about it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bars[BAR_P_FULL]);
+            mbar_arrive(&bars[BAR_P_FULL + (j & 1)]);
             l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_run = m_new;
         }
@@ -461,7 +471,7 @@ bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int 
 template <typename T>
 void launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
-    const size_t smem = (size_t)TC_TILE * (2 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 3 * TC_ROWS * sizeof(float) + 1024;
+    const size_t smem = (size_t)TC_TILE * (3 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 3 * TC_ROWS * sizeof(float) + 1024;
     static bool configured[64] = {false};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
