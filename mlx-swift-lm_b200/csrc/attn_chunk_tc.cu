@@ -159,7 +159,8 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
     const int rep = p.Hq / p.Hkv;
     int u = blockIdx.x;
     const int hr = u % rep; u /= rep;
-    const int rb = u % p.row_blocks; u /= p.row_blocks;
+    // with a causal mask the late row blocks see the most keys: they go first, the short ones fill the tail
+    const int rb = p.row_blocks - 1 - (u % p.row_blocks); u /= p.row_blocks;
     const int hk = u % p.Hkv;
     const int b = u / p.Hkv;
     const int hq = hk * rep + hr;
@@ -468,20 +469,26 @@ bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int 
     return true;
 }
 
+// Returns false when the device does not grant the kernel its shared memory (the caller falls back to
+// the mma.sync chunk kernel).
 template <typename T>
-void launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
+bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
     const size_t smem = (size_t)TC_TILE * (3 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 3 * TC_ROWS * sizeof(float) + 1024;
-    static bool configured[64] = {false};
+    static int configured[64] = {0};   // 0 = not yet, 1 = ready, -1 = refused
     const int dev = current_device();
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        KVC_CUDA(cudaFuncSetAttribute(attn_chunk_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev] = true;
+    if (dev < 0 || dev >= 64) return false;
+    if (configured[dev] == 0) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        configured[dev] = e == cudaSuccess ? 1 : -1;
     }
+    if (configured[dev] < 0) return false;
     KernelTimer timer(stream);
     KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
     ++g_launch_count;
+    return true;
 }
 
 }  // namespace
@@ -522,11 +529,12 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = status;
-    if (const char *e = std::getenv("KVC_TRACE_DISPATCH"))
-        if (e[0] == '1') fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
-    if (a.q_dtype == KVC_BF16) launch_tc_typed<__nv_bfloat16>(qmap, kmap, vmap, p, (int)ctas, stream);
-    else launch_tc_typed<__half>(qmap, kmap, vmap, p, (int)ctas, stream);
-    return 1;
+    const bool taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16>(qmap, kmap, vmap, p, (int)ctas, stream)
+                                             : launch_tc_typed<__half>(qmap, kmap, vmap, p, (int)ctas, stream);
+    if (taken)
+        if (const char *e = std::getenv("KVC_TRACE_DISPATCH"))
+            if (e[0] == '1') fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
+    return taken ? 1 : 0;
 }
 
 }  // namespace kvc
