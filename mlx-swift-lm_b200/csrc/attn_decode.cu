@@ -70,6 +70,7 @@ struct DecodeParams {
     // fused append: the new rows [B, Hkv, D] of this step (null = the cache already holds them)
     const void *new_k, *new_v;
     int32_t early_tiles;  // flat kernel: the stored rows may be streamed before the preceding kernel has finished
+    int64_t new_slot;     // flat kernel, fused append: token index the new row is stored at (T - 1, or a ring slot)
     int64_t nk_sb, nk_sh, nv_sb, nv_sh;  // element strides
     int64_t causal_offset;
     float scale_log2;  // scale * log2(e)
@@ -463,7 +464,11 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     // Fused append: token T - 1 is not in the cache yet; the tiles are masked up to T - 2 and the
     // new row is scored from its source by warp 0 of the CTA that owns the unit's last tile.
     const bool fused = p.new_k != nullptr;
-    const int64_t t_cached = p.T - (fused ? 2 : 1);
+    // Appending at the end: the tiles are simply cut one token short. Replacing a row inside a
+    // wrapped ring: every token is visible except that slot, which still holds the row it loses.
+    const bool ring = fused && p.new_slot != p.T - 1;
+    const int64_t t_cached = p.T - ((fused && !ring) ? 2 : 1);
+    const int64_t hole = ring ? p.new_slot : -1;
     int64_t row_limit[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -582,7 +587,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                     const int half = e >> 1;
                     const int64_t t = t_blk + jj * 8 + 2 * c + (e & 1);
                     float v = sc[jj][e] * p.scale_log2;
-                    v = (t <= row_limit[half]) ? v : -INFINITY;
+                    v = (t <= row_limit[half] && t != hole) ? v : -INFINITY;
                     sc[jj][e] = v;
                     tmax[half] = fmaxf(tmax[half], v);
                 }
@@ -676,7 +681,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                 o_acc[nt][3] = o_acc[nt][3] * alpha[1] + pn[1] * vv.y;
             }
             // the append itself: rows of D elements, 16 bytes per lane
-            const int64_t row_off = b * p.kv_sb + hk * p.kv_sh + (p.T - 1) * p.kv_st;
+            const int64_t row_off = b * p.kv_sb + hk * p.kv_sh + p.new_slot * p.kv_st;
             constexpr int CHUNKS = D * 2 / 16;
             for (int i = lane; i < 2 * CHUNKS; i += 32) {
                 const bool is_v = i >= CHUNKS;
@@ -1198,6 +1203,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.k_base = (unsigned char *)a.k.data; p.v_base = (unsigned char *)a.v.data;
             p.kv_sb = a.k.sb * 2; p.kv_sh = a.k.sh * 2; p.kv_st = a.k.st * 2;
             p.new_k = a.new_k; p.new_v = a.new_v;
+            p.new_slot = (a.new_slot >= 0 && a.new_slot < a.T) ? a.new_slot : a.T - 1;
             {
                 // early tiles: fused append only (the kernel's tiles end before the row it writes), the
                 // caller's word on the preceding launch, and that launch being a kernel that released

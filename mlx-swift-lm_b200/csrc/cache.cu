@@ -277,8 +277,9 @@ static void linear_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v
 }
 
 // RotatingKVCache.updateInPlace (KVCache.swift:684-740), S == 1.
+// With `slot` the new row is NOT written: the caller (the fused decode kernel) stores it at *slot.
 static void rotating_update_in_place(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v,
-                                     cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov) {
+                                     cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov, int64_t *slot = nullptr) {
     const int64_t max_size = c->cfg.max_size, keep = c->cfg.keep;
     const int64_t prev = c->offset;
     if (!c->k.allocated() || (prev >= c->len && c->len < max_size)) {
@@ -312,7 +313,8 @@ static void rotating_update_in_place(kvc_cache *c, const kvc_tensor &k, const kv
     if (c->idx == max_size) c->idx = keep;
     if (c->idx < 0 || c->idx + 1 > c->len)
         fail(KVC_ERR_INVALID_STATE, "rotating cache: ring index outside the buffer");
-    append_pair(c->k, c->v, k, v, c->idx, s);
+    if (slot) *slot = c->idx;
+    else append_pair(c->k, c->v, k, v, c->idx, s);
     c->offset += 1;
     c->idx += 1;
     const int64_t rows = c->offset < max_size ? std::min(c->offset, c->len) : c->len;
@@ -791,6 +793,37 @@ void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, con
                 if (launch_attention_decode(a, s) > 0) return;
                 append_pair(c->k, c->v, k, v, prev, s);
                 a.new_k = a.new_v = nullptr;
+                launch_attention(a, s);
+                return;
+            }
+            // The same for a RotatingKVCache's single-token update (updateInPlace): the kernel writes
+            // the row into the ring slot and leaves the row it replaces out of the scores.
+            if (!fuse_off && c->cfg.kind == KVC_KIND_ROTATING && k.shape[2] == 1 && q.shape[2] == 1 && !c->open_round &&
+                mask_mode == KVC_MASK_NONE && k.stride[3] == 1 && v.stride[3] == 1 && k.ndim == 4 && v.ndim == 4 &&
+                (k.dtype == KVC_BF16 || k.dtype == KVC_F16) && k.dtype == v.dtype && k.shape[0] == v.shape[0] &&
+                k.shape[1] == v.shape[1] && v.shape[2] == 1) {
+                check_new_rows(c, c->k, c->v, k, v);
+                c->restore.valid = false;
+                const int64_t launches_before = g_launch_count;
+                const void *k_before = c->k.allocated() ? c->k.view(1).data : nullptr;
+                kvc_tensor ck, cv;
+                int64_t slot = -1;
+                rotating_update_in_place(c, k, v, s, &ck, &cv, &slot);
+                AttnArgs a = make_attn_args(q, out, scale, KVC_MASK_NONE, nullptr, ck.shape[2], Hkv);
+                a.k = raw_source(ck);
+                a.v = raw_source(cv);
+                a.new_k = k.data; a.new_v = v.data;
+                a.new_slot = slot;
+                a.nk_sb = k.stride[0]; a.nk_sh = k.stride[1];
+                a.nv_sb = v.stride[0]; a.nv_sh = v.stride[1];
+                // no growth copy and no ring rebuild in this call: the stored rows are as the last step left them
+                a.stored_rows_settled = tl_batch_prev != nullptr && tl_batch_prev != c && k_before == ck.data &&
+                                        launches_before == g_launch_count;
+                if (slot >= 0 && slot < ck.shape[2] && launch_attention_decode(a, s) > 0) return;
+                append_pair(c->k, c->v, k, v, slot, s);
+                a.new_k = a.new_v = nullptr;
+                a.new_slot = -1;
+                a.stored_rows_settled = false;
                 launch_attention(a, s);
                 return;
             }

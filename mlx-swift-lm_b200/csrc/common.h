@@ -123,6 +123,9 @@ struct AttnArgs {
     // written to the cache yet; the kernel scores them from here and stores them at token T - 1 itself.
     const void *new_k = nullptr, *new_v = nullptr;
     int64_t nk_sb = 0, nk_sh = 0, nv_sb = 0, nv_sh = 0;  // element strides (inner stride 1)
+    // Token index the new row is stored at: T - 1 (append at the end) unless the cache is a wrapped
+    // ring, where it replaces the oldest row somewhere in the middle; that row is not attended.
+    int64_t new_slot = -1;
     // The caller vouches that the launch right before this one on the stream (a layer of the same
     // batched call) does not write the rows of this cache that are already stored, so the kernel may
     // stream them before that launch has finished.

@@ -232,3 +232,34 @@ def test_tensor_core_chunk_through_the_cache(kvc, oracle, cuda):
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5, "causal")
         assert max_abs_diff(out, ref) <= TOL[torch.bfloat16]
     assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("D,keep,max_size,prefill", [(128, 0, 96, 70), (128, 4, 80, 200), (256, 0, 64, 10), (64, 3, 130, 129)])
+def test_rotating_ring_decode_appends_inside_the_attention_kernel(kvc, oracle, cuda, D, keep, max_size, prefill):
+    """Single-token steps on a RotatingKVCache (updateInPlace, KVCache.swift:684-740) through
+    attentionWithCacheUpdate: while the buffer grows the row lands at the end, once the ring has
+    wrapped it replaces the oldest row in the middle of the buffer. One launch per step; outputs and
+    the physical ring match the oracle at every step."""
+    B, Hq, Hkv = 2, 4, 2
+    dtype = torch.bfloat16
+    scale = D ** -0.5
+    g, o = kvc.RotatingKVCache(max_size, keep=keep, step=32), oracle.RotatingKVCache(max_size, keep=keep, step=32)
+    k, v = seeded((B, Hkv, prefill, D), 1, dtype), seeded((B, Hkv, prefill, D), 2, dtype)
+    q = seeded((B, Hq, prefill, D), 3, dtype)
+    kvc.attention_with_cache_update(q.to(cuda), k.to(cuda), v.to(cuda), g, scale, "causal")
+    oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    fused_steps = 0
+    for step in range(150):
+        k, v = seeded((B, Hkv, 1, D), 10 + 3 * step, dtype), seeded((B, Hkv, 1, D), 11 + 3 * step, dtype)
+        q = seeded((B, Hq, 1, D), 12 + 3 * step, dtype)
+        kvc.launch_count(reset=True)
+        out = kvc.attention_with_cache_update(q.to(cuda), k.to(cuda), v.to(cuda), g, scale, "none")
+        fused_steps += kvc.launch_count(reset=True) == 1
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "none")
+        assert max_abs_diff(out, ref) <= TOL[dtype], step
+        assert g.offset == o.offset and list(g.meta_state) == list(o.meta_state), step
+        if step % 37 == 0 or step == 149:
+            for a, b in zip(g.state, o.state):
+                assert bits_equal(a, np.ascontiguousarray(b)), step
+    assert fused_steps >= 140        # growth and the one ring rebuild after the prefill cost extra launches
+    assert kvc.lib().kvc_device_status() == 0
