@@ -32,7 +32,9 @@ def parse_codebooks(swift_path: str):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of the mlx-swift-lm checkout>")
+    ref = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     table = parse_codebooks(os.path.join(ref, "Libraries/MLXLMCommon/TurboQuantKVCache.swift"))
     for dim, per_bits in table.items():
