@@ -68,6 +68,16 @@ WORKLOADS["cfg5_profile_2layers"] = dict(WORKLOADS["cfg5_turbo_k3v4_llama3_70b"]
 # workload: its metric is prefill tokens/s and its roofline is the tensor-core one.
 WORKLOADS["cfg2_prefill512_4layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=4, prefill=512)
 DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (taken on the 2-layer variants: a launch is the same size)
+NCU_TRAFFIC_BYTES = {
+    "cfg2_simple_bf16_llama3_8b": (268.8e6 + 5.0e6, "profiles/attn_decode_flat_bf16_cfg2_llama3_8b.md"),
+    "cfg4_quant4_bf16_qwen2_7b": (322.8e6 + 4.4e6, "profiles/attn_affine_decode8_cfg4_qwen2_7b.md"),
+    "cfg5_turbo_k3v4_llama3_70b": (505.4e6 + 4.3e6, "profiles/attn_turbo_decode8_cfg5_llama3_70b.md"),
+}
+for _k in ("cfg2", "cfg4", "cfg5"):
+    _full = [n for n in NCU_TRAFFIC_BYTES if n.startswith(_k)][0]
+    NCU_TRAFFIC_BYTES[_k + "_profile_2layers"] = NCU_TRAFFIC_BYTES[_full]
 
 
 def bytes_per_token_head(w) -> float:
@@ -404,8 +414,10 @@ def run_ragged(args, w, rank, world, local_rank):
         except Exception:
             pass
     achieved = alg_bytes / (k_avg_ms * 1e-3) / 1e9 if k_n else None
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "frac": (achieved / peak) if achieved else None, "traffic": traffic[0] if traffic else None,
+                "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, " + traffic[1]) if traffic else None,
                 "kernel": "var-len attention (dominant)", "launch_ms": k_avg_ms, "launches_timed": k_n,
                 "algorithmic_bytes_per_launch": alg_bytes, "peak_source": peak_src}
 
