@@ -7,6 +7,7 @@
 // Not compiled in this repository's build image (no Swift toolchain); the C ABI
 // underneath is what the test-suite exercises.
 import CKVCacheB200
+import Foundation
 
 /// What the wrapper needs from an array type: a device pointer, a dtype, a shape
 /// and element strides. `MLXArray` on a CUDA backend provides all four.
@@ -297,4 +298,63 @@ public func attentionWithCacheUpdateVarlenB200<A: DeviceArray>(
     var q = queries.map(describe), k = keys.map(describe), v = values.map(describe), o = outs.map(describe)
     let status = kvc_attention_varlen(&handles, Int32(handles.count), &q, &k, &v, scale, &o, stream)
     precondition(status == KVC_OK, String(cString: kvc_last_error_message()))
+}
+
+/// maybeAffineQuantizeKVCache (KVCache.swift:2500-2520) over a flat layer list.
+@discardableResult
+public func maybeAffineQuantizeKVCacheB200<A: DeviceArray>(
+    cache: inout [B200KVCache<A>], bits: Int, groupSize: Int, compressionStart: Int, stream: UnsafeMutableRawPointer? = nil
+) -> Bool {
+    var handles: [OpaquePointer?] = cache.map { $0.handle }
+    var complete: Int32 = 0
+    let status = handles.withUnsafeMutableBufferPointer {
+        kvc_maybe_affine_quantize($0.baseAddress, Int32($0.count), Int32(bits), Int32(groupSize), Int64(compressionStart), stream, &complete)
+    }
+    precondition(status == KVC_OK, String(cString: kvc_last_error_message()))
+    for i in cache.indices where handles[i] != cache[i].handle {
+        cache[i].forgetHandle()     // already freed by the library
+        cache[i] = B200KVCache<A>.wrap(adopting: handles[i]!)
+    }
+    return complete != 0
+}
+
+/// savePromptCache(url:cache:metadata:) (KVCache.swift:1797-1846) for caches held by the library. Model
+/// state (`LMOutput.State`) is not a cache matter: callers that have one keep using the reference's
+/// writer on `state` / `metaState`, which this wrapper exposes unchanged.
+public func savePromptCacheB200<A: DeviceArray>(
+    url: URL, cache: [B200KVCache<A>], metadata: [String: String] = [:], stream: UnsafeMutableRawPointer? = nil
+) throws {
+    var handles: [OpaquePointer?] = cache.map { $0.handle }
+    let keys = metadata.keys.sorted()
+    var cKeys: [UnsafePointer<CChar>?] = keys.map { UnsafePointer(strdup($0)) }
+    var cValues: [UnsafePointer<CChar>?] = keys.map { UnsafePointer(strdup(metadata[$0]!)) }
+    defer {
+        for p in cKeys + cValues { free(UnsafeMutablePointer(mutating: p)) }
+    }
+    try check(kvc_save_prompt_cache(url.path, &handles, Int32(handles.count), &cKeys, &cValues, Int32(keys.count), stream))
+}
+
+/// loadPromptCache(url:) (KVCache.swift:1859-1871, restoreCacheFromMetaState :2031-2138). Files that
+/// carry model state or cache classes outside this library make the call throw with the reference's
+/// message; the caller then falls back to the reference's loader.
+public func loadPromptCacheB200<A: DeviceArray>(
+    url: URL, device: Int32 = -1, stream: UnsafeMutableRawPointer? = nil
+) throws -> ([B200KVCache<A>], [String: String]) {
+    var count: Int32 = 0
+    var need = 0
+    try check(kvc_load_prompt_cache(url.path, device, nil, 0, &count, nil, 0, &need, stream))
+    var handles = [OpaquePointer?](repeating: nil, count: Int(count))
+    var buffer = [CChar](repeating: 0, count: max(need, 1))
+    try check(kvc_load_prompt_cache(url.path, device, &handles, count, &count, &buffer, buffer.count, &need, stream))
+    // key NUL value NUL ... closed by an empty key
+    var metadata: [String: String] = [:]
+    var pos = 0
+    while pos < buffer.count, buffer[pos] != 0 {
+        let key = String(cString: Array(buffer[pos...]))
+        pos += key.utf8.count + 1
+        let value = String(cString: Array(buffer[pos...]))
+        pos += value.utf8.count + 1
+        metadata[key] = value
+    }
+    return (handles.prefix(Int(count)).map { B200KVCache<A>.wrap(adopting: $0!) }, metadata)
 }
