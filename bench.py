@@ -690,8 +690,10 @@ def run_ours(args, w, rank, world, local_rank):
             peak_src = "MEASURED_PEAKS.json hbm_gbs (measured copy)"
         except Exception:
             pass
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "frac": (achieved / peak) if achieved else None, "traffic": traffic[0] if traffic else None,
+                "traffic_source": ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, " + traffic[1]) if traffic else None,
                 "kernel": "attention (dominant)", "launch_ms": k_avg_ms, "launches_timed": k_n,
                 "timing": ("CUDA events around %d back-to-back steps of one launch per layer" % rsteps) if only_attention
                           else "CUDA events around each attention launch (kvc_timing)",
