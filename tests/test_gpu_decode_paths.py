@@ -202,6 +202,9 @@ def test_batched_decode_steps_over_layers(kvc, oracle, cuda, dtype):
     (1, 16, 4, 600, 600, "causal"),      # chunk from an empty cache, last row block partial, T not a tile multiple
     (1, 8, 8, 1300, 1300, "none"),       # no mask: only the ragged last key tile is masked
     (4, 8, 1, 384, 3000, "causal"),      # long prefix: 24 key tiles per block, multi-query
+    (4, 32, 8, 100, 100, "causal"),      # one partial row block and one partial key tile per CTA
+    (2, 64, 8, 64, 5001, "none"),        # the shortest chunk the kernel takes, ragged last key tile
+    (5, 16, 16, 129, 257, "causal"),     # one row past a block, one key past a tile
 ])
 def test_tensor_core_chunk_kernel_matches_oracle(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, T, mask):
     """Long chunks over raw K/V at head dim 128 run on the tcgen05 kernel (128 query rows per CTA)."""
