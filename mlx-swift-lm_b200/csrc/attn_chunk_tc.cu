@@ -20,7 +20,8 @@
 // softmax warps are busy with the current ones, and the correction warps trail by one product.
 //
 // Shared-memory operand layout (what TMA's 128-byte swizzle writes): a box is 128 rows x 128 bytes
-// (64 elements), 16-byte chunk c of row r at chunk c ^ (r & 7); a 128 x 128 tile is two boxes.
+// (64 elements), 16-byte chunk c of row r at chunk c ^ (r & 7); a 128 x 128 tile is two boxes (Q, K and
+// V tiles at head dim 64 are one box, the O product then has 64 columns).
 // Matrix descriptors: K-major operands advance 32 bytes per 16-element k-step inside the row, 8-row
 // groups are 1024 bytes apart; the MN-major V tile advances 2048 bytes per 16 keys, its two 64-dim
 // halves are 16384 bytes apart (leading offset) and its 8-key groups 1024 bytes (stride offset).
@@ -43,9 +44,8 @@ using namespace dev;
 
 constexpr int TC_ROWS = 128;                 // query rows per CTA = TMEM lanes
 constexpr int TC_KEYS = 128;                 // keys per tile
-constexpr int TC_D = 128;
 constexpr int TC_BOX = 128 * 128;            // bytes of one 64-element-wide box of 128 rows
-constexpr int TC_TILE = 2 * TC_BOX;          // 32 KB: a 128 x 128 16-bit tile
+constexpr int TC_TILE = 2 * TC_BOX;          // 32 KB: a 128 x 128 16-bit tile (P; Q, K and V at head dim 128)
 constexpr int TC_STAGES = 2;
 constexpr int TC_THREADS = 320;
 constexpr uint32_t TC_TMEM_COLS = 512;       // S0 | S1 | O0 | O1, 128 fp32 columns each
@@ -140,15 +140,17 @@ enum : int {
     BAR_COUNT = BAR_L_FULL + 1
 };
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                      const __grid_constant__ CUtensorMap vmap, const ChunkTcParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int NBOX = D / 64;                               // boxes of 64 head dims per Q / K / V tile
+    constexpr int QKV_TILE = NBOX * TC_BOX;                    // bytes of a 128-row tile of D head dims
     unsigned char *sq = base;                                  // Q block
-    unsigned char *skv = sq + TC_TILE;                         // ring: stage s = K tile | V tile
-    unsigned char *sp = skv + TC_STAGES * 2 * TC_TILE;         // two P tiles
+    unsigned char *skv = sq + QKV_TILE;                        // ring: stage s = K tile | V tile
+    unsigned char *sp = skv + TC_STAGES * 2 * QKV_TILE;        // two P tiles
     uint64_t *bars = (uint64_t *)(sp + 2 * TC_TILE);
     uint32_t *tmem_slot = (uint32_t *)(bars + BAR_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128] rescale factor of tile j for each row
@@ -212,27 +214,27 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
         // ---------------- producer ----------------
         if (lane == 0) {
             bool ok = true;
-            mbar_expect_tx(&bars[BAR_Q], TC_TILE);
-            tma_load_4d(sq, &qmap, &bars[BAR_Q], 0, l0, hq, b);
-            tma_load_4d(sq + TC_BOX, &qmap, &bars[BAR_Q], 64, l0, hq, b);
+            mbar_expect_tx(&bars[BAR_Q], QKV_TILE);
+#pragma unroll
+            for (int bx = 0; bx < NBOX; ++bx) tma_load_4d(sq + bx * TC_BOX, &qmap, &bars[BAR_Q], bx * 64, l0, hq, b);
             // A K slot is free as soon as its score product is done, a V slot only after the output
             // product one tile later: K runs one tile ahead of V so that neither waits for the other.
             auto load_k = [&](int j) {
                 const int s = j % TC_STAGES;
                 if (j >= TC_STAGES && !mbar_wait(&bars[BAR_K_EMPTY + s], ((j / TC_STAGES) - 1) & 1)) return false;
-                unsigned char *kt = skv + (size_t)s * 2 * TC_TILE;
-                mbar_expect_tx(&bars[BAR_K_FULL + s], TC_TILE);
-                tma_load_4d(kt, &kmap, &bars[BAR_K_FULL + s], 0, j * TC_KEYS, hk, b);
-                tma_load_4d(kt + TC_BOX, &kmap, &bars[BAR_K_FULL + s], 64, j * TC_KEYS, hk, b);
+                unsigned char *kt = skv + (size_t)s * 2 * QKV_TILE;
+                mbar_expect_tx(&bars[BAR_K_FULL + s], QKV_TILE);
+#pragma unroll
+                for (int bx = 0; bx < NBOX; ++bx) tma_load_4d(kt + bx * TC_BOX, &kmap, &bars[BAR_K_FULL + s], bx * 64, j * TC_KEYS, hk, b);
                 return true;
             };
             auto load_v = [&](int j) {
                 const int s = j % TC_STAGES;
                 if (j >= TC_STAGES && !mbar_wait(&bars[BAR_V_EMPTY + s], ((j / TC_STAGES) - 1) & 1)) return false;
-                unsigned char *vt = skv + (size_t)s * 2 * TC_TILE + TC_TILE;
-                mbar_expect_tx(&bars[BAR_V_FULL + s], TC_TILE);
-                tma_load_4d(vt, &vmap, &bars[BAR_V_FULL + s], 0, j * TC_KEYS, hk, b);
-                tma_load_4d(vt + TC_BOX, &vmap, &bars[BAR_V_FULL + s], 64, j * TC_KEYS, hk, b);
+                unsigned char *vt = skv + (size_t)s * 2 * QKV_TILE + QKV_TILE;
+                mbar_expect_tx(&bars[BAR_V_FULL + s], QKV_TILE);
+#pragma unroll
+                for (int bx = 0; bx < NBOX; ++bx) tma_load_4d(vt + bx * TC_BOX, &vmap, &bars[BAR_V_FULL + s], bx * 64, j * TC_KEYS, hk, b);
                 return true;
             };
             if (n_tiles > 0) ok = load_k(0);
@@ -249,12 +251,13 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             // 0 = f16, 1 = bf16), B major at bit 16 (1 = MN-major), N / 8 at bits 17-22, M / 16 at 24-28
             constexpr uint32_t FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            constexpr uint32_t IDESC_PV = IDESC | (1u << 16);
+            // the O product has N = D columns
+            constexpr uint32_t IDESC_PV = (1u << 4) | (FMT << 7) | (FMT << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
             // Descriptors differ only in the start-address field (16-byte units): a box is 1024 units, a
             // k-step inside a box row 2, 16 keys of the MN-major V tile 128.
             const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
             const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
-            const uint64_t v_desc = umma_desc(smem_u32(skv) + TC_TILE, 16384, 1024);
+            const uint64_t v_desc = umma_desc(smem_u32(skv) + QKV_TILE, 16384, 1024);
             const uint64_t p_desc = umma_desc(smem_u32(sp), 16, 1024);
             bool ok = mbar_wait(&bars[BAR_Q], 0);
             auto issue_s = [&](int j) {
@@ -262,10 +265,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 if (!mbar_wait(&bars[BAR_K_FULL + s], (j / TC_STAGES) & 1)) return false;
                 if (j >= 2 && !mbar_wait(&bars[BAR_S_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
                 tc_fence_after();
-                const uint64_t kd = k_desc + (uint64_t)(s * (2 * TC_TILE / 16));
+                const uint64_t kd = k_desc + (uint64_t)(s * (2 * QKV_TILE / 16));
                 const uint32_t d_addr = tmem + (uint32_t)(j & 1) * 128u;
 #pragma unroll
-                for (int ks = 0; ks < TC_D / 16; ++ks) {
+                for (int ks = 0; ks < D / 16; ++ks) {
                     const uint64_t off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
                     umma_f16(d_addr, q_desc + off, kd + off, IDESC, ks > 0 ? 1u : 0u);
                 }
@@ -283,7 +286,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 if (ok && j >= 2) ok = mbar_wait(&bars[BAR_O_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t vd = v_desc + (uint64_t)(s * (2 * TC_TILE / 16));
+                const uint64_t vd = v_desc + (uint64_t)(s * (2 * QKV_TILE / 16));
                 const uint64_t pd = p_desc + (uint64_t)((j & 1) * (TC_TILE / 16));
                 const uint32_t o_addr = tmem + 256u + (uint32_t)(j & 1) * 128u;
 #pragma unroll
@@ -377,9 +380,9 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + 256u;
         const int64_t l = (int64_t)l0 + row;
-        float o_acc[TC_D];
+        float o_acc[D];
 #pragma unroll
-        for (int i = 0; i < TC_D; ++i) o_acc[i] = 0.f;
+        for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             ok = mbar_wait(&bars[BAR_A_FULL + (j & 1)], (j >> 1) & 1);
@@ -390,7 +393,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            for (int half = 0; half < D / 64; ++half) {
                 uint32_t raw[64];
                 tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64, raw);
                 tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64 + 32, raw + 32);
@@ -409,7 +412,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             T *dst = (T *)p.out + b * p.o_sb + hq * p.o_sh + l * p.o_sl;
 #pragma unroll
-            for (int c8 = 0; c8 < TC_D / 8; ++c8) {
+            for (int c8 = 0; c8 < D / 8; ++c8) {
                 uint4 w;
                 w.x = pack_pair<T>(o_acc[c8 * 8 + 0] * inv, o_acc[c8 * 8 + 1] * inv);
                 w.y = pack_pair<T>(o_acc[c8 * 8 + 2] * inv, o_acc[c8 * 8 + 3] * inv);
@@ -447,11 +450,11 @@ EncodeTiledFn encode_tiled_tc() {
 
 // [B, H, rows, D] view, element strides (inner 1): boxes of 128 rows x 64 elements, 128-byte swizzle,
 // rows beyond `rows` read as zero.
-bool make_map_tc(CUtensorMap *map, const void *data, int32_t dtype, int64_t rows, int H, int B, int64_t s_row, int64_t s_h,
-                 int64_t s_b) {
+bool make_map_tc(CUtensorMap *map, const void *data, int32_t dtype, int D, int64_t rows, int H, int B, int64_t s_row,
+                 int64_t s_h, int64_t s_b) {
     EncodeTiledFn fn = encode_tiled_tc();
     if (!fn) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)TC_D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
     const cuuint64_t strides[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)(H > 1 ? s_h : s_row * rows) * 2,
                                    (cuuint64_t)(B > 1 ? s_b : (H > 1 ? s_h * H : s_row * rows)) * 2};
     const cuuint32_t box[4] = {64, 128, 1, 1};
@@ -461,9 +464,9 @@ bool make_map_tc(CUtensorMap *map, const void *data, int32_t dtype, int64_t rows
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int H, int B) {
+bool strides_fit(const void *data, int D, int64_t s_row, int64_t s_h, int64_t s_b, int H, int B) {
     auto ok = [](int64_t st) { return st > 0 && (st * 2) % 16 == 0; };
-    if (((uintptr_t)data & 15) != 0 || !ok(s_row) || s_row < TC_D) return false;
+    if (((uintptr_t)data & 15) != 0 || !ok(s_row) || s_row < D) return false;
     if (H > 1 && !ok(s_h)) return false;
     if (B > 1 && !ok(s_b)) return false;
     return true;
@@ -471,21 +474,22 @@ bool strides_fit(const void *data, int64_t s_row, int64_t s_h, int64_t s_b, int 
 
 // Returns false when the device does not grant the kernel its shared memory (the caller falls back to
 // the mma.sync chunk kernel).
-template <typename T>
+template <typename T, int D>
 bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
-    const size_t smem = (size_t)TC_TILE * (3 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 + 3 * TC_ROWS * sizeof(float) + 1024;
+    const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + 2 * (size_t)TC_TILE + BAR_COUNT * sizeof(uint64_t) + 64 +
+                        3 * TC_ROWS * sizeof(float) + 1024;
     static int configured[64] = {0};   // 0 = not yet, 1 = ready, -1 = refused
     const int dev = current_device();
     if (dev < 0 || dev >= 64) return false;
     if (configured[dev] == 0) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
         configured[dev] = e == cudaSuccess ? 1 : -1;
     }
     if (configured[dev] < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
+    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
     ++g_launch_count;
     return true;
@@ -493,7 +497,7 @@ bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
 
 }  // namespace
 
-// Returns 1 when the call was taken (head dim 128, f16 / bf16 raw K and V, no array mask, enough
+// Returns 1 when the call was taken (head dim 64 or 128, f16 / bf16 raw K and V, no array mask, enough
 // 128-row blocks to fill the part), 0 otherwise. KVC_CHUNK_TC=0 turns the path off.
 int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     static const bool off = [] {
@@ -501,7 +505,7 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
         return e && e[0] == '0';
     }();
     if (off) return 0;
-    if (a.D != TC_D || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
+    if ((a.D != 128 && a.D != 64) || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
     if (a.k.kind != SRC_RAW || a.v.kind != SRC_RAW || a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
     if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib || a.new_k) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30 || a.L < 64) return 0;
@@ -511,15 +515,16 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     // a CTA owns an SM (its TMEM and 193 KB of shared memory): fewer blocks than half the part run
     // better on the split-K kernel
     if (ctas < sm_count(a.device) / 2 || ctas > (int64_t)1 << 30) return 0;
-    if (!strides_fit(a.q, a.q_sl, a.q_sh, a.q_sb, a.Hq, a.B)) return 0;
-    if (!strides_fit(a.k.data, a.k.st, a.k.sh, a.k.sb, a.Hkv, a.B) || !strides_fit(a.v.data, a.v.st, a.v.sh, a.v.sb, a.Hkv, a.B)) return 0;
+    if (!strides_fit(a.q, a.D, a.q_sl, a.q_sh, a.q_sb, a.Hq, a.B)) return 0;
+    if (!strides_fit(a.k.data, a.D, a.k.st, a.k.sh, a.k.sb, a.Hkv, a.B) || !strides_fit(a.v.data, a.D, a.v.st, a.v.sh, a.v.sb, a.Hkv, a.B))
+        return 0;
     if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
     int *status = device_status_word(a.device);
     if (!status) return 0;
     CUtensorMap qmap, kmap, vmap;
-    if (!make_map_tc(&qmap, a.q, a.q_dtype, a.L, a.Hq, a.B, a.q_sl, a.q_sh, a.q_sb)) return 0;
-    if (!make_map_tc(&kmap, a.k.data, a.k.dtype, a.T, a.Hkv, a.B, a.k.st, a.k.sh, a.k.sb)) return 0;
-    if (!make_map_tc(&vmap, a.v.data, a.v.dtype, a.T, a.Hkv, a.B, a.v.st, a.v.sh, a.v.sb)) return 0;
+    if (!make_map_tc(&qmap, a.q, a.q_dtype, a.D, a.L, a.Hq, a.B, a.q_sl, a.q_sh, a.q_sb)) return 0;
+    if (!make_map_tc(&kmap, a.k.data, a.k.dtype, a.D, a.T, a.Hkv, a.B, a.k.st, a.k.sh, a.k.sb)) return 0;
+    if (!make_map_tc(&vmap, a.v.data, a.v.dtype, a.D, a.T, a.Hkv, a.B, a.v.st, a.v.sh, a.v.sb)) return 0;
     ChunkTcParams p = {};
     p.out = a.out;
     p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
@@ -529,8 +534,13 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = status;
-    const bool taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16>(qmap, kmap, vmap, p, (int)ctas, stream)
-                                             : launch_tc_typed<__half>(qmap, kmap, vmap, p, (int)ctas, stream);
+    bool taken;
+    if (a.D == 128)
+        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 128>(qmap, kmap, vmap, p, (int)ctas, stream)
+                                      : launch_tc_typed<__half, 128>(qmap, kmap, vmap, p, (int)ctas, stream);
+    else
+        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 64>(qmap, kmap, vmap, p, (int)ctas, stream)
+                                      : launch_tc_typed<__half, 64>(qmap, kmap, vmap, p, (int)ctas, stream);
     if (taken)
         if (const char *e = std::getenv("KVC_TRACE_DISPATCH"))
             if (e[0] == '1') fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);

@@ -222,6 +222,26 @@ def test_tensor_core_chunk_kernel_matches_oracle(kvc, oracle, cuda, capfd, monke
     assert kvc.lib().kvc_device_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,L,T,mask", [
+    (2, 32, 8, 300, 777, "causal"),
+    (1, 32, 8, 512, 512, "causal"),
+    (5, 16, 2, 128, 1000, "none"),
+])
+def test_tensor_core_chunk_kernel_head_dim_64(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, T, mask):
+    """The same kernel at head dim 64 (one 64-element box per Q / K / V tile, 64 output columns)."""
+    D = 64
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    q = seeded((B, Hq, L, D), 4, dtype)
+    k, v = seeded((B, Hkv, T, D), 5, dtype), seeded((B, Hkv, T, D), 6, dtype)
+    out = kvc.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, mask)
+    torch.cuda.synchronize()
+    assert "chunk_tc" in capfd.readouterr().err
+    ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), D ** -0.5, mask)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
 def test_tensor_core_chunk_through_the_cache(kvc, oracle, cuda):
     """A 512-token prefill chunk on top of a stored prefix through attentionWithCacheUpdate, strided
     (transposed-projection) queries included; the same call with the kernel switched off agrees."""
