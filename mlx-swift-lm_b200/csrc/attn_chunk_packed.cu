@@ -53,6 +53,7 @@ struct ChunkPackedParams {
     int64_t kc_sb, kc_sh, vc_sb, vc_sh;  // word strides of the code / index arrays
     int64_t kg_sb, kg_sh, vg_sb, vg_sh;  // element strides of scales/biases or norms
     const float *q_signs, *o_signs;      // turbo
+    const float *q_calib;                // turbo: optional key-calibration scale folded into the rotated query
     float kcb[16], vcb[16];              // turbo centroids
     float *o_part;
     float2 *ml_part;
@@ -455,6 +456,10 @@ attn_chunk_packed_kernel(const __grid_constant__ ChunkPackedParams p) {
                     qs[rr * D + i1] = xa - ya;
                 }
             }
+            if (p.q_calib) {
+                consumer_bar<CP_WARPS>();
+                for (int i = tid; i < 64 * D; i += CP_CONSUMERS) qs[i] *= p.q_calib[i % D];
+            }
         }
         consumer_bar<CP_WARPS>();
     }
@@ -693,18 +698,14 @@ bool chunk_turbo_fits(const KVSource &s, int64_t T) {
 // Returns the number of kernels launched, or 0 when the call does not fit this path.
 // KVC_TRACE_DISPATCH=1 prints which check sent a call to another kernel.
 static int chunk_reject(int reason) {
-    static const bool trace = [] {
-        const char *e = std::getenv("KVC_TRACE_DISPATCH");
-        return e && e[0] == '1';
-    }();
-    if (trace) fprintf(stderr, "[kvc] chunk_packed: not taken (check %d)\n", reason);
+    if (trace_dispatch()) fprintf(stderr, "[kvc] chunk_packed: not taken (check %d)\n", reason);
     return 0;
 }
 
 int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return chunk_reject(1);
     if (a.D != CP_D) return chunk_reject(2);
-    if (a.mask.mode == KVC_MASK_ARRAY || a.q_calib) return chunk_reject(3);
+    if (a.mask.mode == KVC_MASK_ARRAY) return chunk_reject(3);
     if (a.Hkv <= 0 || a.Hq % a.Hkv) return chunk_reject(4);
     if (a.T < 1 || a.T > (int64_t)1 << 30) return chunk_reject(5);
     const int rep = a.Hq / a.Hkv;
@@ -714,7 +715,7 @@ int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream) {
     const bool turbo = a.k.kind == SRC_TURBO && a.v.kind == SRC_TURBO;
     if (!affine && !turbo) return chunk_reject(7);
     if (affine) {
-        if (a.q_signs || a.o_signs) return chunk_reject(8);
+        if (a.q_signs || a.o_signs || a.q_calib) return chunk_reject(8);
         if (a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return chunk_reject(9);
         if (a.k.bits != a.v.bits || a.k.group != a.v.group) return chunk_reject(10);
         if (!chunk_affine_fits(a.k, a.T) || !chunk_affine_fits(a.v, a.T)) return chunk_reject(11);
@@ -767,7 +768,7 @@ int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream) {
     p.kn = a.k.norms; p.vn = a.v.norms;
     p.kc_sb = a.k.sb; p.kc_sh = a.k.sh; p.vc_sb = a.v.sb; p.vc_sh = a.v.sh;
     p.kg_sb = a.k.gsb; p.kg_sh = a.k.gsh; p.vg_sb = a.v.gsb; p.vg_sh = a.v.gsh;
-    p.q_signs = a.q_signs; p.o_signs = a.o_signs;
+    p.q_signs = a.q_signs; p.o_signs = a.o_signs; p.q_calib = a.q_calib;
     for (int i = 0; i < 16; ++i) {
         p.kcb[i] = a.k.codebook[i];
         p.vcb[i] = a.v.codebook[i];

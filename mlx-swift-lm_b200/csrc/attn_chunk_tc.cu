@@ -28,6 +28,7 @@
 //
 // Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
 // its TMEM.
+#include <atomic>
 #include <cuda.h>
 
 #include <cstdlib>
@@ -479,15 +480,19 @@ bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
                      cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + 2 * (size_t)TC_TILE + BAR_COUNT * sizeof(uint64_t) + 64 +
                         3 * TC_ROWS * sizeof(float) + 1024;
-    static int configured[64] = {0};   // 0 = not yet, 1 = ready, -1 = refused
+    // 0 = not yet, 1 = ready, -1 = refused; distinct handles may call from distinct host threads
+    static std::atomic<int> configured[64];
     const int dev = current_device();
     if (dev < 0 || dev >= 64) return false;
-    if (configured[dev] == 0) {
+    int state = configured[dev].load(std::memory_order_acquire);
+    if (state == 0) {
+        // setting the attribute twice from two racing threads is harmless; the result is the same
         const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
-        configured[dev] = e == cudaSuccess ? 1 : -1;
+        state = e == cudaSuccess ? 1 : -1;
+        configured[dev].store(state, std::memory_order_release);
     }
-    if (configured[dev] < 0) return false;
+    if (state < 0) return false;
     KernelTimer timer(stream);
     KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
@@ -541,9 +546,7 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     else
         taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 64>(qmap, kmap, vmap, p, (int)ctas, stream)
                                       : launch_tc_typed<__half, 64>(qmap, kmap, vmap, p, (int)ctas, stream);
-    if (taken)
-        if (const char *e = std::getenv("KVC_TRACE_DISPATCH"))
-            if (e[0] == '1') fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
+    if (taken && trace_dispatch()) fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
     return taken ? 1 : 0;
 }
 

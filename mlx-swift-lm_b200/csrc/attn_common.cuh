@@ -10,7 +10,37 @@
 
 #include <cuda.h>
 
+// Measurement aids (switching consumer work off piece by piece to time the producer alone) exist
+// only in a build made with -DKVC_MEASURE_AIDS, which the shipped build never sets: without the
+// flag the skip bits are the constant 0, the branches on them compile away and no environment
+// variable is read.
+#ifdef KVC_MEASURE_AIDS
+#define KVC_SKIP_BITS(p) ((p).debug_skip)
+#else
+#define KVC_SKIP_BITS(p) 0
+#endif
+
 namespace kvc {
+
+inline int measure_skip_bits() {
+#ifdef KVC_MEASURE_AIDS
+    static const int bits = [] {
+        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
+        return e ? std::atoi(e) : 0;
+    }();
+    return bits;
+#else
+    return 0;
+#endif
+}
+
+// KVC_TRACE_DISPATCH=1 makes the chunk paths say on stderr which kernel took a call. Read at each
+// use (tests switch it on inside a running process); only chunk launches consult it, never decode.
+inline bool trace_dispatch() {
+    const char *e = std::getenv("KVC_TRACE_DISPATCH");
+    return e && e[0] == '1';
+}
+
 namespace dev {
 
 constexpr uint32_t SPIN_LIMIT = 1u << 24;

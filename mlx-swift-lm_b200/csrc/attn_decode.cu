@@ -193,7 +193,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
             const int s = it % NSTAGE;
             ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
             if (!ok) break;
-            if (p.debug_skip) {
+            if (KVC_SKIP_BITS(p)) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -431,7 +431,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                     const int s = it % NSTAGE;
                     if (it >= NSTAGE) {
                         // measurement aid (debug_skip & 4): the producer alone recycles the ring
-                        if (p.debug_skip & 4) ok = mbar_wait(&full[s], ((it / NSTAGE) - 1) & 1);
+                        if (KVC_SKIP_BITS(p) & 4) ok = mbar_wait(&full[s], ((it / NSTAGE) - 1) & 1);
                         else ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
                     }
                     if (!ok) break;
@@ -439,7 +439,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
                     unsigned char *vt = kt + TILE_BYTES;
                     mbar_expect_tx(&full[s], 2 * TILE_BYTES);
                     const int tok = (t0 + j) * TILE_T;
-                    if (p.debug_skip & 2) {
+                    if (KVC_SKIP_BITS(p) & 2) {
                         const int64_t off = b * p.kv_sb + hk * p.kv_sh + (int64_t)tok * p.kv_st;
                         bulk_load(kt, p.k_base + off, TILE_BYTES, &full[s]);
                         bulk_load(vt, p.v_base + off, TILE_BYTES, &full[s]);
@@ -459,7 +459,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     }
 
     // ---------------- consumers ----------------
-    if (p.debug_skip & 8) return;  // measurement aid: no consumer work at all (with 4: producer-only streaming)
+    if (KVC_SKIP_BITS(p) & 8) return;  // measurement aid: no consumer work at all (with 4: producer-only streaming)
     const int g = lane >> 2, c = lane & 3;
     // Fused append: token T - 1 is not in the cache yet; the tiles are masked up to T - 2 and the
     // new row is scored from its source by warp 0 of the CTA that owns the unit's last tile.
@@ -533,7 +533,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             for (int half = 0; half < 2; ++half) {
                 const int r = g + 8 * half;
                 uint32_t w0 = 0, w1 = 0;
-                if (r < R && !(p.debug_skip & 32)) {
+                if (r < R && !(KVC_SKIP_BITS(p) & 32)) {
                     const int hq = hk * rep + r / p.L, l = r % p.L;
                     const T *qp = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + d0;
                     w0 = *(const uint32_t *)qp;
@@ -549,14 +549,14 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
         for (int j = 0; j < n; ++j, ++it) {
-            if (!ok || (p.debug_skip & 4)) continue;  // a wait ran out earlier: walk on to the barriers below
+            if (!ok || (KVC_SKIP_BITS(p) & 4)) continue;  // a wait ran out earlier: walk on to the barriers below
             const int s = it % NSTAGE;
             ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
             if (!ok) {
                 if (lane == 0) atomicExch(p.status, 10);
                 continue;
             }
-            if (p.debug_skip & 1) {
+            if (KVC_SKIP_BITS(p) & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -643,7 +643,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             if (lane == 0) mbar_arrive(&empty[s]);
         }
 
-        if (fused && warp == 0 && t0 + n == tiles && !(p.debug_skip & 32)) {
+        if (fused && warp == 0 && t0 + n == tiles && !(KVC_SKIP_BITS(p) & 32)) {
             // ---- the step's new token: score q . k_new, fold it into this warp's state, store the rows ----
             const T *kn = (const T *)p.new_k + b * p.nk_sb + hk * p.nk_sh;
             const T *vn = (const T *)p.new_v + b * p.nv_sb + hk * p.nv_sh;
@@ -718,7 +718,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
         u.o_signs = nullptr;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
-        if (!(p.debug_skip & 16))
+        if (!(KVC_SKIP_BITS(p) & 16))
             segment_epilogue<D, CONSUMER_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R);
         x += n;
     }
@@ -1196,10 +1196,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
             p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
             p.splits = 1; p.tiles_base = 0; p.tiles_rem = 0; p.row_blocks = 1;
             p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
-            {
-                const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-                p.debug_skip = e ? std::atoi(e) : 0;
-            }
+            p.debug_skip = measure_skip_bits();
             p.k_base = (unsigned char *)a.k.data; p.v_base = (unsigned char *)a.v.data;
             p.kv_sb = a.k.sb * 2; p.kv_sh = a.k.sh * 2; p.kv_st = a.k.st * 2;
             p.new_k = a.new_k; p.new_v = a.new_v;
@@ -1213,7 +1210,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
                     return e && e[0] == '0';
                 }();
                 p.early_tiles = (!early_off && a.new_k && a.stored_rows_settled && g_last_chained_launch == g_launch_count &&
-                                 p.debug_skip == 0) ? 1 : 0;
+                                 KVC_SKIP_BITS(p) == 0) ? 1 : 0;
             }
             p.nk_sb = a.nk_sb; p.nk_sh = a.nk_sh; p.nv_sb = a.nv_sb; p.nv_sh = a.nv_sh;
             p.causal_offset = a.mask.causal_offset;
@@ -1275,10 +1272,7 @@ int launch_attention_decode(const AttnArgs &a, cudaStream_t stream) {
     p.tiles_base = (int)(tiles / splits);
     p.tiles_rem = (int)(tiles % splits);
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
-    {
-        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-        p.debug_skip = (e && e[0] == '1') ? 1 : 0;
-    }
+    p.debug_skip = measure_skip_bits();
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.row_blocks = (int)row_blocks;

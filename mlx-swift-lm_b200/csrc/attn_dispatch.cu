@@ -14,11 +14,14 @@ int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
-// KVC_ATTENTION_PATH=general forces the general kernel (used by tests that
-// compare the two paths on the device).
+// KVC_ATTENTION_PATH=general forces the general kernel (read once per process; used by
+// tests that compare the two paths on the device from child processes).
 bool force_general() {
-    const char *e = std::getenv("KVC_ATTENTION_PATH");
-    return e && e[0] == 'g';
+    static const bool forced = [] {
+        const char *e = std::getenv("KVC_ATTENTION_PATH");
+        return e && e[0] == 'g';
+    }();
+    return forced;
 }
 }  // namespace
 

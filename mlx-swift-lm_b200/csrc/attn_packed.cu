@@ -845,7 +845,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
                 if (lane == 0) atomicExch(p.status, 6);
                 continue;
             }
-            if (p.debug_skip & 1) {
+            if (KVC_SKIP_BITS(p) & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -858,9 +858,9 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
             const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
             const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
             const int t_blk = (tile_begin + jt) * PK_TILE + blk * 16;
-            if (p.debug_skip & 6) {
+            if (KVC_SKIP_BITS(p) & 6) {
                 // measurement aid (results are meaningless): 2 = only the K half, 4 = only the V half
-                if (p.debug_skip & 2) {
+                if (KVC_SKIP_BITS(p) & 2) {
 #pragma unroll
                     for (int gr = 0; gr < G; ++gr) {
                         uint32_t wa[WPL], wb[WPL];
@@ -878,7 +878,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
                         }
                     }
                 }
-                if (p.debug_skip & 4) {
+                if (KVC_SKIP_BITS(p) & 4) {
                     const uint32_t v_row = smem_u32(vct + v_off);
 #pragma unroll
                     for (int cp = 0; cp < CH / 2; ++cp) {
@@ -1312,10 +1312,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     p.tiles_base = (int)(tiles / splits);
     p.tiles_rem = (int)(tiles % splits);
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
-    {
-        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-        p.debug_skip = e ? std::atoi(e) : 0;
-    }
+    p.debug_skip = measure_skip_bits();
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.flat.tiles = (int)tiles;

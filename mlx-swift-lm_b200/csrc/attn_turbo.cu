@@ -52,6 +52,7 @@ struct TurboParams {
     int64_t kp_sb, kp_sh, vp_sb, vp_sh;  // word strides (token stride = words per row)
     int64_t kn_sb, kn_sh, vn_sb, vn_sh;  // element strides (token stride = 1)
     const float *q_signs, *o_signs;      // [D] each
+    const float *q_calib;                // optional [D]: key-calibration scale folded into the rotated query
     float kcb[16], vcb[16];              // centroids
     float *o_part;
     float2 *ml_part;
@@ -250,6 +251,10 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
                 qrot[r * D + i1] = xa - ya;
             }
         }
+        if (p.q_calib) {
+            consumer_bar<TQ_WARPS>();
+            for (int i = tid; i < 8 * D; i += CT) qrot[i] *= p.q_calib[i % D];
+        }
         consumer_bar<TQ_WARPS>();
         float m_run[2], l_run[2] = {0.f, 0.f};
         float o_acc[8][4];
@@ -292,7 +297,7 @@ attn_turbo_decode8_kernel(const __grid_constant__ TurboParams p) {
                 if (lane == 0) atomicExch(p.status, 8);
                 continue;
             }
-            if (p.debug_skip & 1) {
+            if (KVC_SKIP_BITS(p) & 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 continue;
@@ -492,7 +497,7 @@ bool turbo_source_fits(const KVSource &s, int D, int64_t T) {
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
     if (a.D != TQ_D) return 0;
-    if (a.mask.mode == KVC_MASK_ARRAY || a.q_calib || !a.q_signs || !a.o_signs) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || !a.q_signs || !a.o_signs) return 0;
     if (a.k.kind != SRC_TURBO || a.v.kind != SRC_TURBO) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv) return 0;
     const int rep = a.Hq / a.Hkv;
@@ -544,7 +549,7 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     p.kn = a.k.norms; p.vn = a.v.norms;
     p.kp_sb = a.k.sb; p.kp_sh = a.k.sh; p.vp_sb = a.v.sb; p.vp_sh = a.v.sh;
     p.kn_sb = a.k.gsb; p.kn_sh = a.k.gsh; p.vn_sb = a.v.gsb; p.vn_sh = a.v.gsh;
-    p.q_signs = a.q_signs; p.o_signs = a.o_signs;
+    p.q_signs = a.q_signs; p.o_signs = a.o_signs; p.q_calib = a.q_calib;
     for (int i = 0; i < 16; ++i) {
         p.kcb[i] = a.k.codebook[i];
         p.vcb[i] = a.v.codebook[i];
@@ -557,10 +562,7 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     p.tiles_base = (int)(tiles / splits);
     p.tiles_rem = (int)(tiles % splits);
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
-    {
-        const char *e = std::getenv("KVC_DECODE_DEBUG_SKIP");
-        p.debug_skip = e ? std::atoi(e) : 0;
-    }
+    p.debug_skip = measure_skip_bits();
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.flat = plan;

@@ -4,6 +4,7 @@
 #include "cache.h"
 
 #include <algorithm>
+#include <limits>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -231,6 +232,7 @@ kvc_cache::~kvc_cache() {
         if (stage[i]) kvc::dev_free(stage[i], s);
     if (kcodec.signs_dev) kvc::dev_free(kcodec.signs_dev, s);
     if (vcodec.signs_dev) kvc::dev_free(vcodec.signs_dev, s);
+    if (kcodec.calib_dev) kvc::dev_free(kcodec.calib_dev, s);
 }
 
 namespace kvc {
@@ -579,7 +581,59 @@ static TurboEncodeArgs turbo_args(const kvc_tensor &x, Array4 &packed, Array4 &n
     a.B = (int)x.shape[0]; a.H = (int)x.shape[1]; a.S = (int)x.shape[2]; a.D = (int)x.shape[3];
     a.bits = codec.bits; a.pos = pos; a.signs = codec.signs_dev;
     for (size_t i = 0; i < codec.boundaries.size() && i < 15; ++i) a.boundaries[i] = codec.boundaries[i];
+    if (codec.calib_dev) {
+        a.calib = codec.calib_dev;
+        for (size_t i = 0; i < codec.centroids.size() && i < 16; ++i) a.centroids[i] = codec.centroids[i];
+    }
     return a;
+}
+
+static void set_key_calibration(kvc_cache *c, const std::vector<float> &scale, cudaStream_t s) {
+    TurboCodec &codec = c->kcodec;
+    if (codec.calib_dev) { dev_free(codec.calib_dev, s); codec.calib_dev = nullptr; }
+    codec.calib = scale;
+    if (scale.empty()) return;
+    codec.calib_dev = (float *)dev_alloc(scale.size() * sizeof(float), s);
+    KVC_CUDA(cudaMemcpyAsync(codec.calib_dev, codec.calib.data(), scale.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+}
+
+// computeKeyCalibrationScale (TurboQuantKVCache.swift:867-886): per-dimension standard deviation of
+// the rotated unit keys over every cached (batch, head, token), divided by its mean over the
+// dimensions, clamped to [0.25, 4]; none when fewer than 32 rows or when no dimension is 10 % off 1.
+// The two moments are accumulated on the device as fixed-point integers (order-free, so a CPU
+// restatement reaches the same bits), the rest is a handful of host operations per dimension. The
+// host reads the sums back, so this call waits for the stream like the reference's eval/item does.
+static std::vector<float> compute_key_calibration(kvc_cache *c, const kvc_tensor &keys, cudaStream_t s) {
+    const int D = (int)keys.shape[3];
+    const int64_t rows = keys.shape[0] * keys.shape[1] * keys.shape[2];
+    if (rows < 32) return {};
+    Array4 dummy_p, dummy_n;
+    TurboEncodeArgs a = turbo_args(keys, dummy_p, dummy_n, c->kcodec, 0);
+    a.calib = nullptr;
+    long long *sums = (long long *)dev_alloc((size_t)2 * D * sizeof(long long), s);
+    KVC_CUDA(cudaMemsetAsync(sums, 0, (size_t)2 * D * sizeof(long long), s));
+    launch_turbo_calib_stats(a, sums, s);
+    std::vector<long long> host(2 * D);
+    KVC_CUDA(cudaMemcpyAsync(host.data(), sums, host.size() * sizeof(long long), cudaMemcpyDeviceToHost, s));
+    KVC_CUDA(cudaStreamSynchronize(s));
+    dev_free(sums, s);
+    std::vector<float> sd(D);
+    double sd_sum = 0.0;
+    for (int d = 0; d < D; ++d) {
+        const double mean = (double)host[d] / 1073741824.0 / (double)rows;
+        const double ex2 = (double)host[D + d] / 68719476736.0 / (double)rows;
+        const double var = std::max(ex2 - mean * mean, 0.0);
+        sd[d] = (float)std::sqrt(var);
+        sd_sum += (double)sd[d];
+    }
+    const float mean_sd = std::max((float)(sd_sum / (double)D), 1e-8f);
+    float max_dev = 0.0f;
+    for (int d = 0; d < D; ++d) {
+        sd[d] = std::min(std::max(sd[d] / mean_sd, 0.25f), 4.0f);
+        max_dev = std::max(max_dev, std::fabs(sd[d] - 1.0f));
+    }
+    if (!(max_dev >= 0.1f)) return {};
+    return sd;
 }
 
 static int turbo_pw(int count, int bits) { return (count * bits + 31) / 32; }
@@ -664,6 +718,9 @@ static void turbo_compress_raw(kvc_cache *c, cudaStream_t s) {
         else launch_affine_quantize(quant_args(vt, c->vq, c->vs, c->vb, c->key_group, c->value_bits, 0), s);
         c->v.release(s);
     } else {
+        // standard mode: the calibration scale is derived once from the whole raw key cache and
+        // reused by every later encode on this cache (TurboQuantKVCache.swift:960-962)
+        if (!c->affine_key) set_key_calibration(c, compute_key_calibration(c, kt, s), s);
         turbo_encode_rows(c, kt, vt, 0, s);
         c->k.release(s);
         c->v.release(s);
@@ -716,6 +773,7 @@ static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const 
     } else {
         a.k = turbo_source(c->kp, c->kn, c->kcodec);
         a.q_signs = c->kcodec.signs_dev;
+        a.q_calib = c->kcodec.calib_dev;   // folded into the rotated query (TurboQuantKVCache.swift:1348-1352)
     }
     if (c->affine_value) {
         a.v = affine_source(c->vq.view(T), c->vs.view(T), c->vb.view(T), c->key_group, c->value_bits);
@@ -935,6 +993,7 @@ int64_t cache_trim(kvc_cache *c, int64_t n) {
                 for (Array4 *a : {&c->k, &c->v, &c->kp, &c->kn, &c->vp, &c->vn, &c->kq, &c->ks, &c->kb,
                                   &c->vq, &c->vs, &c->vb})
                     a->release(s);
+                set_key_calibration(c, {}, s);   // keyCalibScale = nil (:1598)
                 c->compressed = false;
             }
             return t;
@@ -966,7 +1025,7 @@ int cache_state_count(const kvc_cache *c) {
             if (c->affine_value) return c->raw_key ? 4 : (c->affine_key ? 6 : 5);
             if (c->affine_key) return 5;
             if (c->raw_key) return 3;
-            return 4;
+            return c->kcodec.calib_dev ? 5 : 4;
         default: return 0;
     }
 }
@@ -993,6 +1052,13 @@ kvc_tensor cache_state_get(kvc_cache *c, int index) {
             else { st.push_back(c->kp.view(c->offset)); st.push_back(view3(c->kn, c->offset)); }
             if (c->affine_value) { st.push_back(c->vq.view(c->offset)); st.push_back(c->vs.view(c->offset)); st.push_back(c->vb.view(c->offset)); }
             else { st.push_back(c->vp.view(c->offset)); st.push_back(view3(c->vn, c->offset)); }
+            if (!c->affine_key && !c->raw_key && !c->affine_value && c->kcodec.calib_dev) {
+                // fifth array of the standard state: the calibration scale, shape [D] (:1509-1511)
+                kvc_tensor t{};
+                t.data = c->kcodec.calib_dev; t.dtype = KVC_F32; t.ndim = 1;
+                t.shape[0] = (int64_t)c->kcodec.calib.size(); t.stride[0] = 1;
+                st.push_back(t);
+            }
             return st[index];
         }
         default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
@@ -1059,7 +1125,17 @@ void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStre
                 adopt(c->vq, arrays[2], s); adopt(c->vs, arrays[3], s); adopt(c->vb, arrays[4], s);
                 c->compressed = true;
             } else if (!c->affine_key && !c->raw_key && count == 5) {
-                fail(KVC_ERR_UNSUPPORTED, "TurboQuant state with a key-calibration scale is not built");
+                // [keyPacked, keyNorms, valPacked, valNorms, keyCalibScale] (:1539-1550)
+                const kvc_tensor &cs = arrays[4];
+                KVC_REQUIRE(cs.ndim == 1 && cs.dtype == KVC_F32 && cs.stride[0] == 1 && cs.shape[0] > 0 && cs.shape[0] <= 1024,
+                            "TurboQuantKVCache state: the key-calibration scale must be a contiguous float32 [D] array");
+                std::vector<float> scale((size_t)cs.shape[0]);
+                KVC_CUDA(cudaMemcpyAsync(scale.data(), cs.data, scale.size() * sizeof(float), cudaMemcpyDeviceToHost, s));
+                KVC_CUDA(cudaStreamSynchronize(s));
+                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
+                adopt(c->vp, arrays[2], s); adopt(c->vn, arrays[3], s);
+                set_key_calibration(c, scale, s);
+                c->compressed = true;
             } else if (count == 4 && !c->affine_value) {
                 adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
                 adopt(c->vp, arrays[2], s); adopt(c->vn, arrays[3], s);
@@ -1173,6 +1249,7 @@ kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
     clone_array(c->vq, n->vq, rows, s); clone_array(c->vs, n->vs, rows, s); clone_array(c->vb, n->vb, rows, s);
     clone_array(c->kp, n->kp, rows, s); clone_array(c->kn, n->kn, rows, s);
     clone_array(c->vp, n->vp, rows, s); clone_array(c->vn, n->vn, rows, s);
+    if (!c->kcodec.calib.empty()) set_key_calibration(n.get(), c->kcodec.calib, s);
     return n.release();
 }
 
@@ -1332,48 +1409,83 @@ void cache_make_mask(const kvc_cache *c, int n, int64_t window, bool return_arra
 // ---------------------------------------------------------------------
 // TurboQuant codebooks and sign vectors
 // ---------------------------------------------------------------------
+namespace {
+// The Lloyd-Max centroids the reference ships as data for its common (head dim, bits) pairs
+// (TurboQuantCodebook.precomputed, TurboQuantKVCache.swift:57-94). The reference reads this
+// table before it falls back to its generator (codebook(dim:bits:), :134-147), and the values
+// are not exactly symmetric, so packed codes only match the reference's when the very same
+// numbers set the boundaries.
+struct ShippedCentroids {
+    int dim, bits;
+    float c[16];
+};
+const ShippedCentroids kShippedCentroids[] = {
+    {64, 2, {-0.18745463f, -0.05649366f, 0.05649367f, 0.18745449f}},
+    {64, 3, {-0.26375133f, -0.16599470f, -0.09368263f, -0.03040462f, 0.03040464f, 0.09368261f, 0.16599482f, 0.26375186f}},
+    {64, 4, {-0.32913971f, -0.25096416f, -0.19681059f, -0.15295772f, -0.11478586f, -0.08000945f, -0.04726735f, -0.01563822f, 0.01563822f, 0.04723797f, 0.07994876f, 0.11472529f, 0.15289739f, 0.19675052f, 0.25090477f, 0.32908401f}},
+    {128, 2, {-0.13302007f, -0.03998107f, 0.03998102f, 0.13302033f}},
+    {128, 3, {-0.18828832f, -0.11801215f, -0.06648001f, -0.02156330f, 0.02156329f, 0.06648005f, 0.11801218f, 0.18828897f}},
+    {128, 4, {-0.23639172f, -0.17934021f, -0.14023653f, -0.10881814f, -0.08157559f, -0.05678632f, -0.03350975f, -0.01108178f, 0.01108178f, 0.03350975f, 0.05678631f, 0.08157560f, 0.10881804f, 0.14023650f, 0.17934017f, 0.23639278f}},
+    {256, 2, {-0.09420358f, -0.02827190f, 0.02827190f, 0.09420330f}},
+    {256, 3, {-0.13371243f, -0.08361249f, -0.04704370f, -0.01524900f, 0.01524901f, 0.04704368f, 0.08361248f, 0.13371260f}},
+    {256, 4, {-0.16852295f, -0.12754069f, -0.09961203f, -0.07719406f, -0.05781249f, -0.04021866f, -0.02370371f, -0.00783269f, 0.00783269f, 0.02370371f, 0.04021868f, 0.05781246f, 0.07719407f, 0.09961203f, 0.12754090f, 0.16852276f}},
+};
+}  // namespace
+
 void turbo_codebook(int dim, int bits, std::vector<float> &centroids, std::vector<float> &bounds) {
-    // Lloyd-Max quantiser for one coordinate of a random unit vector in R^dim,
-    // density proportional to (1 - x^2)^((dim-3)/2) on [-1, 1]: weighted k-means
-    // on a 32768-point grid, 100 sweeps from quantile initialisation, the same
-    // procedure TurboQuantCodebook.generateCentroids (TurboQuantKVCache.swift:174-233)
-    // runs; carried out here in double precision.
     const int levels = 1 << bits;
-    const int grid_n = 32768;
-    std::vector<double> grid(grid_n), w(grid_n);
-    const double expo = (dim - 3) / 2.0;
-    double total = 0;
-    for (int i = 0; i < grid_n; ++i) {
-        const double x = -1.0 + 2.0 * i / (grid_n - 1);
-        grid[i] = x;
-        w[i] = std::pow(std::max(1.0 - x * x, 1e-30), expo);
-        total += w[i];
-    }
-    std::vector<double> cen(levels, 0.0);
-    {
-        double cum = 0;
-        int ci = 0;
-        for (int i = 0; i < grid_n && ci < levels; ++i) {
-            cum += w[i];
-            while (ci < levels && cum >= (ci + 0.5) / levels * total) cen[ci++] = grid[i];
+    centroids.assign(levels, 0.0f);
+    bool found = false;
+    for (const ShippedCentroids &e : kShippedCentroids)
+        if (e.dim == dim && e.bits == bits) {
+            for (int k = 0; k < levels; ++k) centroids[k] = e.c[k];
+            found = true;
         }
-        const double sigma = 1.0 / std::sqrt((double)dim);
-        while (ci < levels) { cen[ci] = (ci ? cen[ci - 1] : 0.0) + sigma; ++ci; }
-    }
-    for (int it = 0; it < 100; ++it) {
-        std::vector<double> sums(levels, 0.0), cnt(levels, 0.0);
-        int j = 0;
+    if (!found) {
+        // Any other pair: the Lloyd-Max quantiser for one coordinate of a random unit vector in
+        // R^dim (density proportional to (1 - x^2)^((dim-3)/2) on [-1, 1]) by weighted k-means on
+        // a 32768-point grid, 100 sweeps from a quantile start, in single precision and in the
+        // order of operations of TurboQuantCodebook.generateCentroids (TurboQuantKVCache.swift:174-233),
+        // so that the same host produces the same floats.
+        const int grid_n = 32768;
+        std::vector<float> grid(grid_n), w(grid_n);
+        const float expo = (float)(dim - 3) / 2.0f;
+        float total = 0.0f;
         for (int i = 0; i < grid_n; ++i) {
-            while (j + 1 < levels && std::fabs(grid[i] - cen[j + 1]) < std::fabs(grid[i] - cen[j])) ++j;
-            sums[j] += grid[i] * w[i];
-            cnt[j] += w[i];
+            const float x = -1.0f + 2.0f * (float)i / (float)(grid_n - 1);
+            grid[i] = x;
+            w[i] = std::pow(std::max(1.0f - x * x, 1e-30f), expo);
+            total += w[i];
         }
-        for (int k = 0; k < levels; ++k)
-            if (cnt[k] > 0) cen[k] = sums[k] / cnt[k];
+        std::vector<float> cen(levels, 0.0f);
+        int filled = 0;
+        float cum = 0.0f;
+        for (int i = 0; i < grid_n; ++i) {
+            cum += w[i];
+            if (filled < levels && cum >= ((float)filled + 0.5f) / (float)levels * total) cen[filled++] = grid[i];
+        }
+        const float sigma = 1.0f / std::sqrt((float)dim);
+        for (; filled < levels; ++filled) cen[filled] = (filled ? cen[filled - 1] : 0.0f) + sigma;
+        std::vector<float> sums(levels), cnt(levels);
+        for (int it = 0; it < 100; ++it) {
+            std::fill(sums.begin(), sums.end(), 0.0f);
+            std::fill(cnt.begin(), cnt.end(), 0.0f);
+            for (int i = 0; i < grid_n; ++i) {
+                int best = 0;
+                float best_d = std::numeric_limits<float>::infinity();
+                for (int j = 0; j < levels; ++j) {
+                    const float d = std::fabs(grid[i] - cen[j]);
+                    if (d < best_d) { best_d = d; best = j; }
+                }
+                sums[best] += grid[i] * w[i];
+                cnt[best] += w[i];
+            }
+            for (int j = 0; j < levels; ++j)
+                if (cnt[j] > 0.0f) cen[j] = sums[j] / cnt[j];
+        }
         std::sort(cen.begin(), cen.end());
+        centroids = cen;
     }
-    centroids.resize(levels);
-    for (int k = 0; k < levels; ++k) centroids[k] = (float)cen[k];
     bounds.resize(levels - 1);
     for (int k = 0; k + 1 < levels; ++k) bounds[k] = (centroids[k] + centroids[k + 1]) / 2.0f;
 }

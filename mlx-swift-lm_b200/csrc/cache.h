@@ -35,6 +35,10 @@ struct TurboCodec {
     int dim = 0, bits = 0;
     std::vector<float> centroids, boundaries, signs;
     float *signs_dev = nullptr;
+    // Key-calibration scale (keys only; empty = none): TurboQuantKVCache.keyCalibScale
+    // (TurboQuantKVCache.swift:688, computed at :867-886).
+    std::vector<float> calib;
+    float *calib_dev = nullptr;
 };
 
 struct RestorePoint {

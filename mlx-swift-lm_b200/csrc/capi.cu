@@ -556,6 +556,21 @@ kvc_status kvc_state_export(kvc_cache *c, int32_t index, void *host_dst, size_t 
         cudaStream_t s = as_stream(stream);
         kvc_tensor t = kvc::cache_state_get(c, index);
         const int nd = t.ndim;
+        if (nd < 3) {
+            // a plain vector (the TurboQuant key-calibration scale): one contiguous copy
+            int64_t count = 1;
+            for (int i = 0; i < nd; ++i) count *= t.shape[i];
+            const size_t bytes = (size_t)count * kvc::dtype_size(t.dtype);
+            if (out_desc) {
+                *out_desc = t;
+                out_desc->data = host_dst;
+            }
+            if (!host_dst) return;
+            KVC_REQUIRE(host_bytes >= bytes, "kvc_state_export: destination too small");
+            KVC_CUDA(cudaMemcpyAsync(host_dst, t.data, bytes, cudaMemcpyDeviceToHost, s));
+            KVC_CUDA(cudaStreamSynchronize(s));
+            return;
+        }
         const int64_t W = nd == 4 ? t.shape[3] : 1;
         const size_t es = kvc::dtype_size(t.dtype);
         const size_t need = (size_t)(t.shape[0] * t.shape[1] * t.shape[2] * W) * es;

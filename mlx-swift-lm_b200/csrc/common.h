@@ -228,8 +228,18 @@ struct TurboEncodeArgs {
     int64_t pos = 0;
     const float *signs = nullptr;       // device [D]
     float boundaries[15] = {0};         // 2^bits - 1 used
+    // Key calibration (TurboQuantKVCache.swift:867-886): when `calib` (device [D]) is set, the rotated
+    // row is divided by it before the boundary search and the stored norm becomes
+    // norm / ||centroids[idx] * calib|| (fusedQuantizePackScaled, TurboQuantKernels.swift:354-411).
+    const float *calib = nullptr;
+    float centroids[16] = {0};          // 2^bits used, only read with `calib`
 };
 void launch_turbo_encode(const TurboEncodeArgs &a, cudaStream_t stream);
+// Per-dimension fixed-point sums of the rotated unit rows of `a.src` for the calibration scale:
+// sums[d] += rint(r * 2^30), sums[D + d] += rint(r * r * 2^36) with r the value the encode kernel
+// quantises; integer accumulation makes the result independent of the order of the rows.
+// `sums` is a device array of 2 * D int64, zeroed by the caller.
+void launch_turbo_calib_stats(const TurboEncodeArgs &a, long long *sums, cudaStream_t stream);
 void launch_turbo_encode2(const TurboEncodeArgs &k, const TurboEncodeArgs *v, cudaStream_t stream);
 
 // Attention: returns the number of kernels launched.

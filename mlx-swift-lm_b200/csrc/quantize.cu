@@ -542,22 +542,111 @@ __global__ void turbo_encode_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, int6
     __syncwarp();
     const int levels_m1 = (1 << a.bits) - 1;
     const uint32_t mask = (uint32_t)levels_m1;
+    float recon_sq = 0.f;  // calibrated rows: squared norm of centroid * scale, same reduction tree as the norm
 #pragma unroll
     for (int i = 0; i < E; ++i) {
-        const float rotated = __fmul_rn(v[i], inv_sqrt_dim);
+        float rotated = __fmul_rn(v[i], inv_sqrt_dim);
+        float cal = 1.f;
+        if (a.calib) {
+            cal = a.calib[lane * E + i];
+            rotated = __fdiv_rn(rotated, cal);
+        }
         uint32_t idx = 0;
         for (int bd = 0; bd < levels_m1; ++bd) idx += (rotated > a.boundaries[bd]) ? 1u : 0u;
         idx &= mask;
+        if (a.calib) {
+            const float cv = __fmul_rn(a.centroids[idx], cal);
+            const float sqv = __fmul_rn(cv, cv);
+            recon_sq = i == 0 ? sqv : __fadd_rn(recon_sq, sqv);
+        }
         const int bit = (lane * E + i) * a.bits;
         const int w = bit >> 5, sh = bit & 31;
         atomicOr(&words[w], idx << sh);
         if (sh + a.bits > 32) atomicOr(&words[w + 1], idx >> (32 - sh));
     }
+    float stored = norm;
+    if (a.calib) {
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) recon_sq = __fadd_rn(recon_sq, __shfl_xor_sync(0xffffffffu, recon_sq, m));
+        const float recon = __fsqrt_rn(recon_sq);
+        if (recon > 1e-8f) stored = __fdiv_rn(norm, recon);
+    }
     __syncwarp();
     const int64_t t = a.pos + s;
     uint32_t *dst = a.packed + b * a.p_sb + h * a.p_sh + t * a.p_st;
     for (int w = lane; w < pw; w += 32) dst[w] = words[w];
-    if (lane == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = norm;
+    if (lane == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = stored;
+}
+
+// Fixed-point per-dimension sums of the rotated unit rows (see launch_turbo_calib_stats). One warp per
+// row at a time, rows strided over the grid; a block folds its warps in shared memory and adds once
+// per dimension to the global sums. The rotated values are computed exactly as turbo_encode_kernel
+// computes the ones it quantises.
+template <typename T, int E>
+__global__ void __launch_bounds__(256)
+turbo_calib_stats_kernel(TurboEncodeArgs a, int64_t total_rows, float inv_sqrt_dim, unsigned long long *sums) {
+    constexpr int D = E * 32;
+    __shared__ unsigned long long s_sum[2 * D];
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) s_sum[i] = 0ull;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    long long acc1[E], acc2[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) { acc1[i] = 0; acc2[i] = 0; }
+    for (int64_t row = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); row < total_rows; row += (int64_t)gridDim.x * warps) {
+        int64_t r = row;
+        const int s = (int)(r % a.S);
+        r /= a.S;
+        const int h = (int)(r % a.H);
+        const int b = (int)(r / a.H);
+        const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
+        float v[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_float<T>(src[(int64_t)(lane * E + i) * a.s_sd]);
+        float sq = __fmul_rn(v[0], v[0]);
+#pragma unroll
+        for (int i = 1; i < E; ++i) sq = __fadd_rn(sq, __fmul_rn(v[i], v[i]));
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, m));
+        const float norm = __fsqrt_rn(sq);
+        const float inv_norm = (norm > 1e-8f) ? __fdiv_rn(1.0f, norm) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = __fmul_rn(v[i], __fmul_rn(inv_norm, a.signs[lane * E + i]));
+#pragma unroll
+        for (int st = 1; st < E; st <<= 1) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                if ((i & st) == 0) {
+                    const float lo = v[i], hi = v[i + st];
+                    v[i] = __fadd_rn(lo, hi);
+                    v[i + st] = __fsub_rn(lo, hi);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], m);
+                v[i] = (lane & m) ? __fsub_rn(other, v[i]) : __fadd_rn(other, v[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const float rot = __fmul_rn(v[i], inv_sqrt_dim);
+            acc1[i] += __float2ll_rn(__fmul_rn(rot, 1073741824.0f));                       // 2^30
+            acc2[i] += __float2ll_rn(__fmul_rn(__fmul_rn(rot, rot), 68719476736.0f));      // 2^36
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        atomicAdd(&s_sum[lane * E + i], (unsigned long long)acc1[i]);
+        atomicAdd(&s_sum[D + lane * E + i], (unsigned long long)acc2[i]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x)
+        if (s_sum[i]) atomicAdd(&sums[i], s_sum[i]);
 }
 
 // E consecutive elements of a contiguous row in as few loads as their size allows.
@@ -746,7 +835,8 @@ void turbo_dispatch(const TurboEncodeArgs &k, const TurboEncodeArgs &v, bool hav
         return true;
     };
     const bool same_dims = !have_v || (k.B == v.B && k.H == v.H && k.S == v.S);
-    if (E <= 8 && same_dims && vec_ok(k) && (!have_v || vec_ok(v)) && k.H <= 65535 && 2 * (int64_t)k.B <= 65535) {
+    const bool calibrated = k.calib || (have_v && v.calib);   // calibrated rows take the generic kernel
+    if (!calibrated && E <= 8 && same_dims && vec_ok(k) && (!have_v || vec_ok(v)) && k.H <= 65535 && 2 * (int64_t)k.B <= 65535) {
         const int sorted = ascending(k) && (!have_v || ascending(v)) ? 1 : 0;
         const bool deep = k.S >= 16;
         const int rpw = deep ? 2 : 1;
@@ -806,6 +896,35 @@ void launch_turbo_encode2(const TurboEncodeArgs &k, const TurboEncodeArgs *v, cu
 
 void launch_turbo_encode(const TurboEncodeArgs &a, cudaStream_t stream) {
     launch_turbo_encode2(a, nullptr, stream);
+}
+
+void launch_turbo_calib_stats(const TurboEncodeArgs &a, long long *sums, cudaStream_t stream) {
+    const int64_t rows = (int64_t)a.B * a.H * a.S;
+    if (rows == 0) return;
+    KVC_REQUIRE(a.D >= 32 && a.D <= 1024 && (a.D & (a.D - 1)) == 0,
+                "key calibration (Walsh-Hadamard path) needs a power-of-two head dim in [32, 1024]");
+    const float inv_sqrt_dim = 1.0f / sqrtf((float)a.D);
+    const int warps = 8;
+    const unsigned blocks = (unsigned)std::min<int64_t>((rows + warps - 1) / warps, (int64_t)sm_count(current_device()) * 8);
+    unsigned long long *out = reinterpret_cast<unsigned long long *>(sums);
+#define KVC_CS(TT)                                                                                                \
+    switch (a.D / 32) {                                                                                           \
+        case 1: turbo_calib_stats_kernel<TT, 1><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+        case 2: turbo_calib_stats_kernel<TT, 2><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+        case 4: turbo_calib_stats_kernel<TT, 4><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+        case 8: turbo_calib_stats_kernel<TT, 8><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+        case 16: turbo_calib_stats_kernel<TT, 16><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+        default: turbo_calib_stats_kernel<TT, 32><<<blocks, warps * 32, 0, stream>>>(a, rows, inv_sqrt_dim, out); break; \
+    }
+    switch (a.dtype) {
+        case KVC_F32: KVC_CS(float) break;
+        case KVC_F16: KVC_CS(__half) break;
+        case KVC_BF16: KVC_CS(__nv_bfloat16) break;
+        default: fail(KVC_ERR_INVALID_ARG, "key calibration needs a floating dtype");
+    }
+#undef KVC_CS
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
 }
 
 }  // namespace kvc

@@ -24,6 +24,8 @@
  *   orc_pack / orc_unpack  TurboQuantPacking, TurboQuantKVCache.swift:351-424
  *   orc_fwht               whtButterfly, TurboQuantKVCache.swift:302-325
  *   orc_codebook           TurboQuantCodebook.generateCentroids, :174-233
+ *   orc_turbo_encode_scaled / orc_turbo_calib_sums   key calibration, :867-886,
+ *                          TurboQuantKernels.swift:354-411
  *   orc_attention          quantizedScaledDotProductAttention KVCache.swift:2351-2447,
  *                          MLXFast.scaledDotProductAttention as called at
  *                          AttentionUtils.swift:86-93, and the turbo flash kernels
@@ -241,6 +243,73 @@ void orc_turbo_encode(const void *x, int dtype, int64_t rows, int D, const float
         }
         orc_pack(idx, 1, D, bits, packed + r * pw);
         norms[r] = norm;
+    }
+}
+
+/* Calibrated encode: the row is rotated as above, divided by the per-dimension
+ * calibration scale before the boundary count, and the stored norm is the raw
+ * norm over the norm of (centroid[idx] * scale)
+ * (fusedQuantizePackScaled, TurboQuantKernels.swift:354-411; MSECodec.encode
+ * with a scale, TurboQuantKVCache.swift:527-544). The reconstruction norm uses
+ * the same reduction tree as the row norm. */
+void orc_turbo_encode_scaled(const void *x, int dtype, int64_t rows, int D, const float *signs,
+                             const float *boundaries, const float *centroids, const float *scale,
+                             int bits, uint32_t *packed, float *norms) {
+    const int pw = orc_packed_width(D, bits);
+    const int nb = (1 << bits) - 1;
+    const float inv_sqrt_dim = 1.0f / sqrtf((float)D);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float v[1024], recon[1024];
+        uint32_t idx[1024];
+        for (int d = 0; d < D; ++d) v[d] = ld(x, dtype, r * D + d);
+        const float norm = sqrtf(sum_squares_tree(v, D));
+        const float inv_norm = norm > 1e-8f ? 1.0f / norm : 0.0f;
+        for (int d = 0; d < D; ++d) v[d] = v[d] * (inv_norm * signs[d]);
+        fwht_row(v, D);
+        for (int d = 0; d < D; ++d) {
+            const float rotated = v[d] * inv_sqrt_dim;
+            const float calibrated = rotated / scale[d];
+            uint32_t k = 0;
+            for (int b = 0; b < nb; ++b) k += calibrated > boundaries[b] ? 1u : 0u;
+            idx[d] = k;
+            recon[d] = centroids[k] * scale[d];
+        }
+        orc_pack(idx, 1, D, bits, packed + r * pw);
+        const float recon_norm = sqrtf(sum_squares_tree(recon, D));
+        norms[r] = recon_norm > 1e-8f ? norm / recon_norm : norm;
+    }
+}
+
+/* First and second moments of the rotated unit rows per dimension, as
+ * fixed-point integers (value * 2^30 and square * 2^36, each rounded to
+ * nearest): the statistic under computeKeyCalibrationScale
+ * (TurboQuantKVCache.swift:867-886). Integer sums do not depend on the order of
+ * the rows. sums[0..D) first moments, sums[D..2D) second moments. */
+void orc_turbo_calib_sums(const void *x, int dtype, int64_t rows, int D, const float *signs, int64_t *sums) {
+    const float inv_sqrt_dim = 1.0f / sqrtf((float)D);
+    memset(sums, 0, sizeof(int64_t) * 2 * (size_t)D);
+#pragma omp parallel
+    {
+        int64_t *local = (int64_t *)calloc(2 * (size_t)D, sizeof(int64_t));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            float v[1024];
+            for (int d = 0; d < D; ++d) v[d] = ld(x, dtype, r * D + d);
+            const float norm = sqrtf(sum_squares_tree(v, D));
+            const float inv_norm = norm > 1e-8f ? 1.0f / norm : 0.0f;
+            for (int d = 0; d < D; ++d) v[d] = v[d] * (inv_norm * signs[d]);
+            fwht_row(v, D);
+            for (int d = 0; d < D; ++d) {
+                const float rot = v[d] * inv_sqrt_dim;
+                const float sq = rot * rot;
+                local[d] += (int64_t)llrintf(rot * 1073741824.0f);
+                local[D + d] += (int64_t)llrintf(sq * 68719476736.0f);
+            }
+        }
+#pragma omp critical
+        for (int d = 0; d < 2 * D; ++d) sums[d] += local[d];
+        free(local);
     }
 }
 

@@ -165,9 +165,34 @@ def fwht(x: np.ndarray) -> np.ndarray:
 
 
 def generate_centroids(dim: int, bits: int) -> np.ndarray:
+    """TurboQuantCodebook.generateCentroids (TurboQuantKVCache.swift:174-233)."""
     out = np.zeros(1 << bits, dtype=np.float32)
     lib().orc_codebook(dim, bits, _p(out))
     return out
+
+
+_SHIPPED_CENTROIDS = None
+
+
+def shipped_centroids() -> dict:
+    """The centroid table the reference ships as data (TurboQuantKVCache.swift:57-94), read from the
+    fixture that tests/golden/make_golden.py parsed out of the Swift source."""
+    global _SHIPPED_CENTROIDS
+    if _SHIPPED_CENTROIDS is None:
+        import json
+        path = os.path.join(_HERE, "..", "tests", "golden", "turbo_codebooks.json")
+        raw = json.load(open(path))["centroids"]
+        _SHIPPED_CENTROIDS = {(int(d), int(b)): np.array(v, dtype=np.float32)
+                              for d, per in raw.items() for b, v in per.items()}
+    return _SHIPPED_CENTROIDS
+
+
+def codebook(dim: int, bits: int) -> np.ndarray:
+    """TurboQuantCodebook.codebook(dim:bits:) (:130-147): the shipped table first, else the generator."""
+    table = shipped_centroids()
+    if (dim, bits) in table:
+        return table[(dim, bits)].copy()
+    return generate_centroids(dim, bits)
 
 
 def boundaries_of(centroids: np.ndarray) -> np.ndarray:
@@ -203,6 +228,51 @@ def turbo_encode(x: np.ndarray, signs: np.ndarray, boundaries: np.ndarray, bits:
         lib().orc_turbo_encode(_p(x), dtype_code(x), ctypes.c_int64(rows), D, _p(signs), _p(boundaries), bits,
                                _p(packed), _p(norms))
     return packed, norms
+
+
+def turbo_encode_scaled(x: np.ndarray, signs: np.ndarray, boundaries: np.ndarray, centroids: np.ndarray,
+                        scale: np.ndarray, bits: int):
+    """Calibrated encode (fusedEncodeDispatchScaled, TurboQuantKVCache.swift:787-796): rotated / scale is
+    quantised and the stored norm is corrected by the norm of the scaled reconstruction."""
+    x = np.ascontiguousarray(x)
+    D = x.shape[-1]
+    rows = int(np.prod(x.shape[:-1], dtype=np.int64))
+    packed = np.zeros(x.shape[:-1] + (packed_width(D, bits),), dtype=np.uint32)
+    norms = np.zeros(x.shape[:-1], dtype=np.float32)
+    signs = np.ascontiguousarray(signs, dtype=np.float32)
+    boundaries = np.ascontiguousarray(boundaries, dtype=np.float32)
+    centroids = np.ascontiguousarray(centroids, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    if rows:
+        lib().orc_turbo_encode_scaled(_p(x), dtype_code(x), ctypes.c_int64(rows), D, _p(signs), _p(boundaries),
+                                      _p(centroids), _p(scale), bits, _p(packed), _p(norms))
+    return packed, norms
+
+
+def key_calibration_scale(all_keys: np.ndarray, signs: np.ndarray) -> Optional[np.ndarray]:
+    """computeKeyCalibrationScale (TurboQuantKVCache.swift:867-886): per-dimension standard deviation of the
+    rotated unit keys pooled over (batch, head, token), divided by its mean over the dimensions, clamped to
+    [0.25, 4]; None with fewer than 32 rows or when every dimension is within 10 % of 1.
+
+    MLX's `std` reduction order is not available here, so the two moments are accumulated as fixed-point
+    integers (exact, order-free) and turned into the population standard deviation in float64; the clamp
+    and the deviation test follow the Swift lines in float32."""
+    x = np.ascontiguousarray(all_keys)
+    D = x.shape[-1]
+    rows = int(np.prod(x.shape[:-1], dtype=np.int64))
+    if rows < 32:
+        return None
+    sums = np.zeros(2 * D, dtype=np.int64)
+    lib().orc_turbo_calib_sums(_p(x), dtype_code(x), ctypes.c_int64(rows), D,
+                               _p(np.ascontiguousarray(signs, dtype=np.float32)), _p(sums))
+    mean = sums[:D].astype(np.float64) / 1073741824.0 / float(rows)
+    ex2 = sums[D:].astype(np.float64) / 68719476736.0 / float(rows)
+    sd = np.sqrt(np.maximum(ex2 - mean * mean, 0.0)).astype(np.float32)
+    mean_sd = np.float32(max(np.float32(np.sum(sd.astype(np.float64)) / float(D)), np.float32(1e-8)))
+    clamped = np.minimum(np.maximum(sd / mean_sd, np.float32(0.25)), np.float32(4.0)).astype(np.float32)
+    if not float(np.max(np.abs(clamped - np.float32(1.0)))) >= 0.1:
+        return None
+    return clamped
 
 
 class _Source(ctypes.Structure):
@@ -752,12 +822,14 @@ class MSECodec:
 
     def __post_init__(self):
         if self.codebook is None:
-            self.codebook = generate_centroids(self.dim, self.bits)
+            self.codebook = codebook(self.dim, self.bits)
         if self.signs is None:
             self.signs = wht_signs(self.dim, self.seed)
         self.boundaries = boundaries_of(self.codebook)
 
-    def encode(self, x: np.ndarray):
+    def encode(self, x: np.ndarray, scale: Optional[np.ndarray] = None):
+        if scale is not None:
+            return turbo_encode_scaled(x, self.signs, self.boundaries, self.codebook, scale, self.bits)
         return turbo_encode(x, self.signs, self.boundaries, self.bits)
 
     def rotate(self, x_f32: np.ndarray) -> np.ndarray:
@@ -800,6 +872,7 @@ class TurboQuantKVCache(BaseKVCache):
         self.is_compressed = False
         self.key_codec: Optional[MSECodec] = None
         self.value_codec: Optional[MSECodec] = None
+        self.key_calib_scale: Optional[np.ndarray] = None
         self._kcb, self._vcb = key_codebook, value_codebook
 
     def _ensure_codecs(self, head_dim: int):
@@ -871,7 +944,7 @@ class TurboQuantKVCache(BaseKVCache):
             self.raw_keys = self._grow(self.raw_keys, end, (B, H, D), keys.dtype)
             self.raw_keys[:, :, prev:end] = keys
         else:
-            kp, kn = self.key_codec.encode(keys)
+            kp, kn = self.key_codec.encode(keys, self.key_calib_scale)
             self.key_packed = self._grow(self.key_packed, end, (B, H, kp.shape[-1]), np.uint32)
             self.key_norms = self._grow(self.key_norms, end, (B, H), np.float32)
             self.key_packed[:, :, prev:end] = kp
@@ -886,6 +959,9 @@ class TurboQuantKVCache(BaseKVCache):
             self.key_group_size = resolved_group_size(self.key_group_size, ak.shape[-1], ak.shape[-1])
         keep_raw = self.raw_keys if self.raw_key_mode else None
         self.raw_keys = None if not self.raw_key_mode else keep_raw
+        if not self.raw_key_mode and not self.affine_key_mode:
+            # computed once from the whole raw key cache, reused by every later encode (:960-962)
+            self.key_calib_scale = key_calibration_scale(ak, self.key_codec.signs)
         self._encode_rows(ak, av, 0)
         self.raw_values = None
         self.is_compressed = True
@@ -918,6 +994,8 @@ class TurboQuantKVCache(BaseKVCache):
         else:
             ks = TurboSource(self.key_packed[:, :, :T], self.key_norms[:, :, :T], self.key_codec.codebook, self.key_bits)
             kw["q_signs"] = self.key_codec.signs
+            if self.key_calib_scale is not None:
+                kw["q_calib"] = self.key_calib_scale    # folded into the rotated query (:1348-1352)
         if self.affine_values:
             vs = AffineSource(*(a[:, :, :T] for a in self.aff_val), self.key_group_size, self.value_bits)
         else:
@@ -942,6 +1020,9 @@ class TurboQuantKVCache(BaseKVCache):
                 out += [a[:, :, :o] for a in self.aff_val]
             else:
                 out += [self.val_packed[:, :, :o], self.val_norms[:, :, :o]]
+            if (self.key_calib_scale is not None and not self.affine_key_mode and not self.raw_key_mode
+                    and not self.affine_values):
+                out.append(self.key_calib_scale)        # fifth array of the standard state (:1509-1511)
             return out
         if self.raw_keys is None or o <= 0:
             return []
@@ -964,6 +1045,7 @@ class TurboQuantKVCache(BaseKVCache):
             self.raw_keys = self.raw_values = None
             self.key_packed = self.key_norms = self.val_packed = self.val_norms = None
             self.aff_key = self.aff_val = None
+            self.key_calib_scale = None
             self.is_compressed = False
         return t
 

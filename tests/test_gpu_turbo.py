@@ -14,8 +14,10 @@ def test_library_codebook_and_signs_match_the_oracle(kvc, oracle):
     for dim in (64, 128, 256):
         for bits in (2, 3, 4):
             c, b = kvc.turbo_codebook(dim, bits)
-            ref = oracle.generate_centroids(dim, bits)
-            assert np.max(np.abs(np.array(c, dtype=np.float32) - ref)) < 2e-4
+            # the shipped table (TurboQuantKVCache.swift:57-94) is the default on both sides ...
+            assert np.array_equal(np.array(c, dtype=np.float32), oracle.codebook(dim, bits))
+            # ... and the generator lands within the table's own asymmetry of it
+            assert np.max(np.abs(np.array(c, dtype=np.float32) - oracle.generate_centroids(dim, bits))) < 2e-4
             assert len(b) == (1 << bits) - 1 and all(b[i] < b[i + 1] for i in range(len(b) - 1))
         assert np.array_equal(np.array(kvc.turbo_signs(dim, 42), dtype=np.float32), oracle.wht_signs(dim, 42))
     assert kvc.turbo_packed_width(128, 3) == 12 and kvc.turbo_packed_width(128, 4) == 16
@@ -24,14 +26,23 @@ def test_library_codebook_and_signs_match_the_oracle(kvc, oracle):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("D", [32, 64, 128, 256, 512])
 @pytest.mark.parametrize("bits", [2, 3, 4])
-def test_turbo_encode_bit_exact(kvc, oracle, cuda, dtype, D, bits):
+@pytest.mark.parametrize("table", ["golden", "generated"])
+def test_turbo_encode_bit_exact(kvc, oracle, cuda, dtype, D, bits, table):
+    """Boundaries from the reference's shipped centroid table (the fixture under tests/golden, where it has
+    the pair) and from the generator; either way the oracle computes its own boundaries, the library is
+    only handed the same floats."""
     rows = 517
     x = seeded((rows, D), D + bits, dtype, outlier_frac=0.02)
     x[3] = 0                      # zero row: norm floor
     x[4] = x[4].abs()             # one-sided row
     x[5, 1:] = 0                  # a single spike
     signs = oracle.wht_signs(D, 42)
-    cb = np.array(kvc.turbo_codebook(D, bits)[0], dtype=np.float32)
+    if table == "golden":
+        if (D, bits) not in oracle.shipped_centroids():
+            pytest.skip("the reference ships no table for this pair")
+        cb = oracle.shipped_centroids()[(D, bits)]
+    else:
+        cb = oracle.generate_centroids(D, bits)
     bounds = oracle.boundaries_of(cb)
     packed, norms = kvc.turbo_encode(x.to(cuda), signs, bounds, bits)
     rp, rn = oracle.turbo_encode(to_oracle(x), signs, bounds, bits)
@@ -69,9 +80,7 @@ def _pair(kvc, oracle, **kw):
 def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
     B, Hq, Hkv, D, P = 2, 8, 2, 128, 250
     g = kvc.TurboQuantKVCache(**kw)
-    kcb = np.array(kvc.turbo_codebook(D, kw.get("key_bits", kw["bits"]))[0], dtype=np.float32) if kw.get("key_bits", kw["bits"]) in (1, 2, 3, 4) else None
-    vcb = np.array(kvc.turbo_codebook(D, kw.get("value_bits", kw["bits"]))[0], dtype=np.float32) if not kw.get("affine_values") else None
-    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    o = oracle.TurboQuantKVCache(**kw)      # default codecs on both sides: the reference's shipped centroid table
     scale = D ** -0.5
     q, k, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype), seeded((B, Hkv, P, D), 3, dtype)
     out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")      # raw prefill + plain SDPA
@@ -108,8 +117,7 @@ def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
 def test_turbo_starts_compressed_when_first_call_is_decode(kvc, oracle, cuda):
     B, Hq, Hkv, D = 1, 4, 1, 64
     g = kvc.TurboQuantKVCache(bits=4)
-    cb = np.array(kvc.turbo_codebook(D, 4)[0], dtype=np.float32)
-    o = oracle.TurboQuantKVCache(bits=4, key_codebook=cb, value_codebook=cb)
+    o = oracle.TurboQuantKVCache(bits=4)
     for step in range(5):
         q, k, v = seeded((B, Hq, 1, D), step, torch.float32), seeded((B, Hkv, 1, D), 50 + step, torch.float32), seeded((B, Hkv, 1, D), 70 + step, torch.float32)
         out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), 0.125)
@@ -134,9 +142,7 @@ def test_chunked_compressed_append_matches_oracle(kvc, oracle, cuda, kw):
     B, Hq, Hkv, D = 2, 8, 2, 128
     dtype = torch.bfloat16
     g = kvc.TurboQuantKVCache(reserve_tokens=700, **kw)
-    kcb = np.array(kvc.turbo_codebook(D, kw.get("key_bits", kw["bits"]))[0], dtype=np.float32)
-    vcb = np.array(kvc.turbo_codebook(D, kw.get("value_bits", kw["bits"]))[0], dtype=np.float32)
-    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    o = oracle.TurboQuantKVCache(**kw)
     for i, n in enumerate([256, 100, 1, 243]):
         k, v = seeded((B, Hkv, n, D), 2 * i, dtype), seeded((B, Hkv, n, D), 2 * i + 1, dtype)
         g.encode_new_token(k.to(cuda), v.to(cuda))
@@ -147,4 +153,99 @@ def test_chunked_compressed_append_matches_oracle(kvc, oracle, cuda, kw):
     q, k, v = seeded((B, Hq, 1, D), 50, dtype), seeded((B, Hkv, 1, D), 51, dtype), seeded((B, Hkv, 1, D), 52, dtype)
     out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5)
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+
+
+def _correlated_keys(shape, seed, dtype, rank=6, noise=0.25):
+    """Keys whose channels are correlated (a low-rank mix plus noise): after the rotation the spread differs
+    from one coordinate to the next, which is what makes computeKeyCalibrationScale return a scale."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    D = shape[-1]
+    mix = torch.randn((rank, D), generator=torch.Generator(device="cpu").manual_seed(1234), dtype=torch.float32)
+    z = torch.randn(shape[:-1] + (rank,), generator=g, dtype=torch.float32)
+    return (z @ mix + noise * torch.randn(shape, generator=g, dtype=torch.float32)).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kw", [dict(bits=4), dict(bits=4, key_bits=3, value_bits=4)], ids=["turbo4", "k3v4"])
+def test_key_calibration_matches_oracle(kvc, oracle, cuda, tmp_path, dtype, kw):
+    """Raw prefill of correlated keys, then decode: the raw-to-compressed transition derives the per-dimension
+    calibration scale (TurboQuantKVCache.swift:867-886, :960-970), keys are encoded through the scaled codec
+    (TurboQuantKernels.swift:354-411), the scale is folded into the rotated query (:1348-1352) and becomes the
+    fifth state array (:1509-1511). Scale, indices and norms are bit-exact against the oracle, outputs in
+    tolerance on the decode kernel, the verify-chunk kernel and the general kernel (array mask)."""
+    B, Hq, Hkv, D, P = 2, 8, 2, 128, 300
+    scale = D ** -0.5
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    q, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 3, dtype)
+    k = _correlated_keys((B, Hkv, P, D), 2, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    for step in range(8):
+        q, v = seeded((B, Hq, 1, D), 10 + 3 * step, dtype), seeded((B, Hkv, 1, D), 12 + 3 * step, dtype)
+        k = _correlated_keys((B, Hkv, 1, D), 11 + 3 * step, dtype)
+        out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"decode step {step}"
+    assert o.key_calib_scale is not None, "the oracle did not calibrate: the inputs are not anisotropic enough"
+    gs, os_ = g.state, o.state
+    assert len(gs) == len(os_) == 5
+    for a, b in zip(gs, os_):
+        assert tuple(a.shape) == tuple(b.shape) and bits_equal(a, np.ascontiguousarray(b))
+    L = 6
+    q, v = seeded((B, Hq, L, D), 90, dtype), seeded((B, Hkv, L, D), 92, dtype)
+    k = _correlated_keys((B, Hkv, L, D), 91, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype], "verify chunk"
+    mask = torch.ones((1, 1, 1, g.offset + 1), dtype=torch.bool)
+    mask[..., ::3] = False
+    q, v = seeded((B, Hq, 1, D), 95, dtype), seeded((B, Hkv, 1, D), 97, dtype)
+    k = _correlated_keys((B, Hkv, 1, D), 96, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, mask.to(cuda))
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, mask.numpy())
+    assert max_abs_diff(out, ref) <= TOL[dtype], "array mask"
+    # the five-array state survives copy() and a prompt-cache file, and decode continues identically
+    c2 = g.copy()
+    path = str(tmp_path / "calibrated.safetensors")
+    kvc.save_prompt_cache(path, [g])
+    loaded, _ = kvc.load_prompt_cache(path)
+    q, v = seeded((B, Hq, 1, D), 98, dtype), seeded((B, Hkv, 1, D), 99, dtype)
+    k = _correlated_keys((B, Hkv, 1, D), 100, dtype)
+    outs = [c.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale) for c in (g, c2, loaded[0])]
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+    assert max_abs_diff(outs[0], ref) <= TOL[dtype]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for c in (c2, loaded[0]):
+        assert len(c.state) == 5
+        for a, b in zip(c.state, o.state):
+            assert bits_equal(a, np.ascontiguousarray(b))
+    assert g.trim(10_000) == o.trim(10_000) and g.state == [] and not g.is_compressed
+    # a fresh sequence of isotropic keys on the same object: the scale is gone and none is derived
+    q, k, v = seeded((B, Hq, 40, D), 101, dtype), seeded((B, Hkv, 40, D), 102, dtype), seeded((B, Hkv, 40, D), 103, dtype)
+    g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    q, k, v = seeded((B, Hq, 1, D), 104, dtype), seeded((B, Hkv, 1, D), 105, dtype), seeded((B, Hkv, 1, D), 106, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale)
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+    assert o.key_calib_scale is None and len(g.state) == 4 and max_abs_diff(out, ref) <= TOL[dtype]
+
+
+def test_outlier_channels_do_not_calibrate(kvc, oracle, cuda):
+    """Independent channels, a few of them 20 times larger: the rotation spreads each channel over every
+    coordinate, the deviation stays under 10 % and both sides keep the plain four-array state."""
+    B, Hq, Hkv, D, P = 1, 8, 2, 128, 200
+    dtype = torch.bfloat16
+    g, o = kvc.TurboQuantKVCache(bits=4), oracle.TurboQuantKVCache(bits=4)
+    q, k, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype, outlier_frac=0.02), seeded((B, Hkv, P, D), 3, dtype)
+    g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, "causal")
+    oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5, "causal")
+    q, k, v = seeded((B, Hq, 1, D), 4, dtype), seeded((B, Hkv, 1, D), 5, dtype, outlier_frac=0.02), seeded((B, Hkv, 1, D), 6, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5)
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5)
+    assert o.key_calib_scale is None and len(g.state) == len(o.state) == 4
+    for a, b in zip(g.state, o.state):
+        assert bits_equal(a, np.ascontiguousarray(b))
     assert max_abs_diff(out, ref) <= TOL[dtype]

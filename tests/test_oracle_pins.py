@@ -70,6 +70,81 @@ def test_codebook_matches_reference_table(oracle):
     assert worst < 2e-4, worst
 
 
+def test_default_codebook_is_the_reference_table(oracle, kvc):
+    """TurboQuantCodebook.codebook(dim:bits:) reads the shipped table first (TurboQuantKVCache.swift:134-147):
+    for its nine (head dim, bits) pairs both the oracle's and the library's default centroids are those
+    floats exactly, and the boundaries are the float32 midpoints (:164-167)."""
+    table = json.load(open(os.path.join(GOLDEN, "turbo_codebooks.json")))["centroids"]
+    assert sorted(table) == ["128", "256", "64"]
+    for dim, per_bits in table.items():
+        assert sorted(per_bits) == ["2", "3", "4"]
+        for bits, vals in per_bits.items():
+            want = np.array(vals, dtype=np.float32)
+            assert np.array_equal(oracle.codebook(int(dim), int(bits)), want)
+            assert np.array_equal(oracle.MSECodec(int(dim), int(bits)).codebook, want)
+            c, b = kvc.turbo_codebook(int(dim), int(bits))      # host-side table lookup, no device needed
+            assert np.array_equal(np.array(c, dtype=np.float32), want)
+            assert np.array_equal(np.array(b, dtype=np.float32), ((want[:-1] + want[1:]) / np.float32(2.0)))
+
+
+@pytest.mark.parametrize("dim,bits", [(32, 4), (512, 3), (1024, 2), (128, 1)])
+def test_generated_codebooks_agree_between_library_and_oracle(oracle, kvc, dim, bits):
+    """Pairs outside the table come from the generator (:174-233): the library's single-precision k-means
+    and the oracle's restatement produce the same floats on the same host."""
+    c, _ = kvc.turbo_codebook(dim, bits)
+    assert np.array_equal(np.array(c, dtype=np.float32), oracle.generate_centroids(dim, bits))
+
+
+def test_key_calibration_decision(oracle):
+    """computeKeyCalibrationScale (TurboQuantKVCache.swift:867-886): nil for fewer than 32 rows and for keys
+    whose rotated coordinates all have the same spread (independent channels, outlier channels included:
+    the Walsh-Hadamard rotation spreads every channel evenly); a clamped, mean-normalised scale for keys
+    with correlated channels."""
+    rng = np.random.default_rng(7)
+    D = 128
+    signs = oracle.wht_signs(D, 42)
+    iid = rng.standard_normal((2, 2, 200, D)).astype(np.float32)
+    assert oracle.key_calibration_scale(iid, signs) is None
+    out = iid.copy()
+    out[..., [3, 90]] *= 20.0
+    assert oracle.key_calibration_scale(out, signs) is None
+    mix = rng.standard_normal((6, D)).astype(np.float32)
+    low = (rng.standard_normal((2, 2, 200, 6)).astype(np.float32) @ mix + 0.25 * iid).astype(np.float32)
+    assert oracle.key_calibration_scale(low[:, :1, :7], signs) is None            # 14 rows < 32
+    s = oracle.key_calibration_scale(low, signs)
+    assert s is not None and s.shape == (D,) and s.dtype == np.float32
+    assert s.min() >= 0.25 and s.max() <= 4.0 and abs(float(s.mean()) - 1.0) < 0.05
+    assert float(np.max(np.abs(s - 1.0))) >= 0.1
+    # the statistic is the population std of the rotated unit rows, up to the fixed-point grid
+    unit = low / np.maximum(np.sqrt((low * low).sum(-1, keepdims=True)), 1e-8)
+    rot = oracle.MSECodec(D, 3).rotate(unit).reshape(-1, D).astype(np.float64)
+    sd = rot.std(axis=0)
+    want = np.clip(sd / sd.mean(), 0.25, 4.0)
+    assert np.max(np.abs(want - s)) < 1e-5
+
+
+def test_calibrated_encode_follows_the_scaled_codec(oracle):
+    """MSECodec.encode(_:scale:) (TurboQuantKVCache.swift:527-544): indices of rotated / scale, stored norm =
+    raw norm / ||codebook[idx] * scale||; decode(scale:) (:573-588) undoes it."""
+    rng = np.random.default_rng(8)
+    D, bits = 64, 4
+    codec = oracle.MSECodec(D, bits, seed=5)
+    x = rng.standard_normal((1, 2, 40, D)).astype(np.float32)
+    scale = np.clip(1.0 + 0.6 * rng.standard_normal(D), 0.25, 4.0).astype(np.float32)
+    packed, norms = codec.encode(x, scale)
+    raw = np.sqrt((x * x).sum(-1))
+    rot = codec.rotate(x / np.maximum(raw, 1e-8)[..., None])
+    idx = oracle.unpack_low_bit(packed, bits, D)
+    want = (rot / scale > codec.boundaries[:, None, None, None, None]).sum(0)
+    assert (idx != want).mean() < 2e-3          # only values within rounding of a boundary may differ
+    recon = codec.codebook[idx] * scale
+    assert np.allclose(norms, raw / np.sqrt((recon * recon).sum(-1)), rtol=1e-5)
+    # reconstruction quality: decode with the scale folded back in
+    approx = oracle.fwht(recon) * np.float32(1.0 / np.sqrt(D)) * codec.signs * norms[..., None]
+    cos = (approx * x).sum(-1) / (np.sqrt((approx * approx).sum(-1)) * raw)
+    assert cos.min() > 0.85 and cos.mean() > 0.95    # an arbitrary scale on isotropic rows costs some accuracy
+
+
 def test_group_size_resolution(oracle):
     # KVCacheTests.swift:477-484 (D = 32 falls back 64 -> 32) and KVCache.swift:902-920
     assert oracle.resolved_group_size(64, 32, 32) == 32
