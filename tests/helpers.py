@@ -55,3 +55,27 @@ def bits_equal(gpu: torch.Tensor, ref: np.ndarray) -> bool:
 
 
 TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def store_ulp(x: np.ndarray, dtype) -> np.ndarray:
+    """Spacing of `dtype` (bf16: 8 significand bits, f16: 11) at the magnitude of x; 0 for float32."""
+    if dtype == torch.float32:
+        return np.zeros_like(x, dtype=np.float32)
+    sig = 8 if dtype == torch.bfloat16 else 11
+    mag = np.maximum(np.abs(x.astype(np.float32)), np.float32(2.0 ** -14))
+    return np.exp2(np.floor(np.log2(mag)) - (sig - 1)).astype(np.float32)
+
+
+def worst_excess(gpu: torch.Tensor, ref: np.ndarray, dtype) -> float:
+    """Largest amount by which |gpu - ref| exceeds the stated absolute tolerance plus the store rounding.
+
+    The tolerance (2e-2 for bf16 / f16, 1e-4 for f32) bounds the error of the arithmetic. Both results are
+    then rounded to `dtype`, which moves each of them by up to half a spacing: two results whose unrounded
+    values differ by less than the tolerance may land one spacing further apart. Below magnitude 1 a bf16
+    spacing (<= 2^-8) is well inside 2e-2 and was always absorbed by it; with x20 outlier channels outputs
+    reach ~10, where one spacing is 2^-4, so the bound is stated per element: TOL + spacing(max(|gpu|, |ref|)).
+    Returns <= 0 when every element is inside."""
+    g = gpu.detach().float().cpu().numpy()
+    r = oracle_f32(ref)
+    bound = np.float32(TOL[dtype]) + store_ulp(np.maximum(np.abs(g), np.abs(r)), dtype)
+    return float(np.max(np.abs(g - r) - bound)) if g.size else 0.0

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, bits_equal, max_abs_diff, oracle_f32, seeded, to_oracle
+from helpers import TOL, bits_equal, max_abs_diff, oracle_f32, seeded, to_oracle, worst_excess
 
 pytestmark = pytest.mark.gpu
 
@@ -32,11 +32,9 @@ def test_affine_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hk
         k1, v1 = seeded((B, Hkv, 1, D), 20 + step, dtype), seeded((B, Hkv, 1, D), 30 + step, dtype)
         out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), scale)
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, scale)
-        # the x20 outlier channels of V make some outputs larger than 1: the tolerance is the
-        # stated one at unit scale and grows with the output magnitude (one bf16 ulp at |x| is
-        # x * 2^-8, so equal float results can still round one ulp apart)
-        biggest = float(np.abs(oracle_f32(ref)).max())
-        assert max_abs_diff(out, ref) <= TOL[dtype] * max(1.0, biggest), f"step {step}"
+        # the x20 outlier channels of V make some outputs larger than 1: the stated absolute
+        # tolerance on the arithmetic plus one spacing of the 16-bit store (helpers.worst_excess)
+        assert worst_excess(out, ref, dtype) <= 0, f"step {step}"
     assert kvc.lib().kvc_device_status() == 0
     for a, b in zip(g.state, o.state):
         assert bits_equal(a, np.ascontiguousarray(b))
@@ -68,9 +66,8 @@ def test_affine_kernel_with_large_queries_and_scales(kvc, oracle, cuda):
     k1, v1 = seeded((B, Hkv, 1, D), 4, torch.bfloat16), seeded((B, Hkv, 1, D), 5, torch.bfloat16)
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
-    biggest = float(np.abs(oracle_f32(ref)).max())
-    # outlier channels make outputs larger than 1; one bf16 ulp at |x| is x * 2^-8
-    assert max_abs_diff(out, ref) <= 2e-2 * max(1.0, biggest)
+    # outlier channels make outputs larger than 1: stated tolerance plus one spacing of the bf16 store
+    assert worst_excess(out, ref, torch.bfloat16) <= 0
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -86,9 +83,7 @@ def test_turbo_decode_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv
     D = 128
     kw = dict(bits=max(kb, vb), key_bits=kb, value_bits=vb)
     g = kvc.TurboQuantKVCache(**kw)
-    kcb = np.array(kvc.turbo_codebook(D, kb)[0], dtype=np.float32)
-    vcb = np.array(kvc.turbo_codebook(D, vb)[0], dtype=np.float32)
-    o = oracle.TurboQuantKVCache(key_codebook=kcb, value_codebook=vcb, **kw)
+    o = oracle.TurboQuantKVCache(**kw)
     k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
     g.encode_new_token(k.to(cuda), v.to(cuda))
     o.encode_new_token(to_oracle(k), to_oracle(v))
@@ -111,8 +106,7 @@ def test_turbo_kernel_small_causal_chunk(kvc, oracle, cuda):
     B, Hq, Hkv, D, L = 2, 4, 2, 128, 4     # 2 query heads per KV head x 4 positions = 8 rows
     kw = dict(bits=4, key_bits=3, value_bits=4)
     g = kvc.TurboQuantKVCache(**kw)
-    o = oracle.TurboQuantKVCache(key_codebook=np.array(kvc.turbo_codebook(D, 3)[0], dtype=np.float32),
-                                 value_codebook=np.array(kvc.turbo_codebook(D, 4)[0], dtype=np.float32), **kw)
+    o = oracle.TurboQuantKVCache(**kw)
     k, v = seeded((B, Hkv, 500, D), 1, torch.bfloat16), seeded((B, Hkv, 500, D), 2, torch.bfloat16)
     g.encode_new_token(k.to(cuda), v.to(cuda))
     o.encode_new_token(to_oracle(k), to_oracle(v))
@@ -163,8 +157,7 @@ def test_turbo_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv,
     D = 128
     kw = dict(bits=max(kb, vb), key_bits=kb, value_bits=vb)
     g = kvc.TurboQuantKVCache(reserve_tokens=P + L, **kw)
-    o = oracle.TurboQuantKVCache(key_codebook=np.array(kvc.turbo_codebook(D, kb)[0], dtype=np.float32),
-                                 value_codebook=np.array(kvc.turbo_codebook(D, vb)[0], dtype=np.float32), **kw)
+    o = oracle.TurboQuantKVCache(**kw)
     k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
     g.encode_new_token(k.to(cuda), v.to(cuda))
     o.encode_new_token(to_oracle(k), to_oracle(v))
