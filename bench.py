@@ -9,12 +9,17 @@ of the dominant attention kernel against the measured copy peak.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Under torchrun (N > 1) the default partition is by sequence: caches of different
-sequences never exchange data, so every rank serves its own batch of B
-sequences with no data-path collective and the job's value is the sum over
-ranks ("weak" scaling). `--parallel heads` instead shards the KV heads of ONE
-batch across ranks and ends every layer with an all-gather of the attention
-outputs (total work fixed, "strong" scaling).
+The default workload is the TurboQuant cache at the Llama-3-70B attention shape
+(80 layers, 64 query heads, 8 KV heads, head dim 128, batch 16, context 32768,
+3-bit keys / 4-bit values): the largest configuration that fits one GPU. The
+same line also carries a speculative verify leg (6 query rows per sequence:
+5 draft tokens + the bonus token, causal, trimmed off again after the round).
+
+Under torchrun (N > 1) the default partition shards the KV heads of ONE batch
+across the ranks (the batch where the heads do not divide) and ends every layer
+with an exchange of the attention outputs: total work is fixed ("strong"
+scaling). `--parallel sequences` instead gives every rank its own batch of B
+sequences with no data-path collective ("weak" scaling).
 Inputs are synthetic (seeded N(0,1)); no dataset is involved.
 """
 from __future__ import annotations
@@ -67,7 +72,9 @@ WORKLOADS["cfg5_profile_2layers"] = dict(WORKLOADS["cfg5_turbo_k3v4_llama3_70b"]
 # (attentionWithCacheUpdate with a causal mask), 4 layers so that a capture stays small. A side
 # workload: its metric is prefill tokens/s and its roofline is the tensor-core one.
 WORKLOADS["cfg2_prefill512_4layers"] = dict(WORKLOADS["cfg2_simple_bf16_llama3_8b"], layers=4, prefill=512)
-DEFAULT_WORKLOAD = "cfg2_simple_bf16_llama3_8b"
+DEFAULT_WORKLOAD = "cfg5_turbo_k3v4_llama3_70b"
+VERIFY_ROWS = 6   # 5 draft tokens + 1 bonus token per speculative round (Evaluate.swift:1205-1208)
+MIN_TIMED_S = 0.5  # the timed region is repeated (whole passes of K steps) until it covers this much
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (taken on the 2-layer variants: a launch is the same size)
 NCU_TRAFFIC_BYTES = {
@@ -115,9 +122,23 @@ def partition(w, world: int, mode: str):
         return dict(shard_axis=1, B_local=B, Hkv_local=Hkv // world, Hq_local=Hq // world, B_global=B,
                     scaling="strong", parallelism=f"kv-head x{world} + all-gather", collective=True)
     if B % world:
-        raise ValueError("neither the KV heads nor the batch divide across the ranks")
+        # neither axis divides: independent sequences per rank
+        return partition(w, world, "sequences")
     return dict(shard_axis=0, B_local=B // world, Hkv_local=Hkv, Hq_local=Hq, B_global=B, scaling="strong",
                 parallelism=f"batch x{world} + all-gather", collective=True)
+
+
+def job_config(args, w, world):
+    """The `config` object of the JSON line: the workload and how it is laid over the ranks. Both arms
+    (this library and the CPU reference) print the same object for the same command line."""
+    part = partition(w, world, args.parallel)
+    ctx0 = w["context"] + max(args.warmup, 3)
+    per_layer = part["B_local"] * part["Hkv_local"] * ctx0 * bytes_per_token_head(w)
+    cfg = {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D")}, "B": part["B_global"],
+           "context_start": ctx0, "parallelism": part["parallelism"], "verify_rows": VERIFY_ROWS,
+           "l2": "inputs larger than L2 (per-layer K+V working set per GPU "
+                 f"{per_layer / 1e6:.0f} MB; all layers {w['layers'] * per_layer / 1e9:.2f} GB per step)"}
+    return cfg, part
 
 
 def torch_dtype(name):
@@ -279,15 +300,18 @@ def cpu_decode_step_time(w, budget_s: float, steps: int = 1, warmup: int = 0):
 
 
 def run_reference(args, w, rank, world):
+    """The reference arm: the CPU restatement of the reference path (MLX itself cannot run on this box) on
+    all host cores, rank 0 only, on the same job (same global batch at every N) and the same `config`."""
     if rank != 0:
         return
-    sec, info = cpu_decode_step_time(w, budget_s=90.0, steps=max(1, args.steps), warmup=min(args.warmup, 1))
-    value = w["B"] / sec
+    cfg, part = job_config(args, w, world)
+    wj = dict(w, B=part["B_global"])
+    sec, info = cpu_decode_step_time(wj, budget_s=90.0, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    value = part["B_global"] / sec
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": part["scaling"],
             "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "impl": "reference",
-            "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D", "B", "context")},
-                       "timing": "CPU restatement of the reference path (MLX itself is unavailable on this box)"},
+            "config": cfg,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -577,11 +601,11 @@ def run_ours(args, w, rank, world, local_rank):
 
     dtype = torch_dtype(w["dtype"])
     Hq, D, Lyr = w["Hq"], w["D"], w["layers"]
-    part = partition(w, world, args.parallel)
+    cfg, part = job_config(args, w, world)
     shard_axis, Bl, Hkvl, Hql = part["shard_axis"], part["B_local"], part["Hkv_local"], part["Hq_local"]
     B, parallelism = part["B_global"], part["parallelism"]
     steps, warmup = args.steps, args.warmup
-    total_steps = warmup + steps * 2 + 64
+    total_steps = warmup + steps * 21 + 64 + VERIFY_ROWS   # timed passes, roofline pass, end-to-end passes
     reserve = w["context"] + total_steps + 8
 
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -626,6 +650,18 @@ def run_ours(args, w, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_pass(fn, n):
+        """Exactly n calls of fn between two events, a barrier and a device sync on both sides; the
+        time is the maximum over the ranks."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
     for _ in range(warmup):
         one_step()
     sampler = ClockSampler(local_rank)
@@ -634,21 +670,50 @@ def run_ours(args, w, rank, world, local_rank):
     barrier()
     ctx0 = caches[0].offset
     kvc.launch_count(reset=True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0 = time.perf_counter()
-    e0.record()
-    for _ in range(steps):
-        one_step()
-    e1.record()
-    barrier()
-    w1 = time.perf_counter()
+    # The timed region is whole passes of exactly `steps` steps, repeated until it covers MIN_TIMED_S
+    # (at most 10 passes); the reported time is the median pass. Every rank takes the same count.
+    pass_ms = [timed_pass(one_step, steps)]
     launches = kvc.launch_count()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    while sum(pass_ms) < MIN_TIMED_S * 1e3 and len(pass_ms) < 10:
+        pass_ms.append(timed_pass(one_step, steps))
+    w1 = time.perf_counter()
+    ms_total = statistics.median(pass_ms)
     ms_per_step = ms_total / steps
     value = B * steps / (ms_total * 1e-3)
     time.sleep(0.15)
     sampler.stop()
     clocks = sampler.summary(w0, w1)
+
+    # speculative verify leg: every layer appends VERIFY_ROWS rows and attends with a causal mask, then
+    # the rows are trimmed off again (all rejected), so that every round does the same work
+    verify = None
+    if VERIFY_ROWS and w["kind"] in ("simple", "quantized", "turbo"):
+        Lv = VERIFY_ROWS
+        vq = [torch.randn((Bl, Hql, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+        vk = [torch.randn((Bl, Hkvl, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+        vv = [torch.randn((Bl, Hkvl, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
+        if comm is not None:
+            vo = [torch.empty((B, Hq, Lv, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+        else:
+            vo = [torch.empty((Bl, Hql, Lv, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+        vstep = kvc.DecodeStep(caches, vq, vk, vv, vo, scale, mask="causal")
+
+        def one_round():
+            if comm is not None:
+                vstep.run_sharded(comm, shard_axis)
+            else:
+                vstep.run()
+            kvc.trim_prompt_cache(caches, Lv)
+
+        for _ in range(3):
+            one_round()
+        rounds = max(2, min(steps, 16))
+        v_ms = timed_pass(one_round, rounds) / rounds
+        verify = {"rows": Lv, "ms_per_round": v_ms, "tokens_per_s_if_all_accepted": B * Lv / (v_ms * 1e-3),
+                  "vs_decode_step": v_ms / ms_per_step,
+                  "note": "one round = append 6 rows + causal attention in every layer, then trim(6)"}
+        del vq, vk, vv, vo, vstep
 
     # roofline pass: bracket the dominant attention kernel with events
     # The dominant kernel's launch duration. When a step is nothing but that kernel (one launch per
@@ -656,7 +721,7 @@ def run_ours(args, w, rank, world, local_rank):
     # it directly; otherwise the library brackets each attention launch with its own events.
     rsteps = min(steps, 16)
     ctx_r0 = caches[0].offset
-    only_attention = launches == steps * Lyr
+    only_attention = launches == steps * Lyr and comm is None
     if only_attention:
         r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -714,6 +779,17 @@ def run_ours(args, w, rank, world, local_rank):
         _ = float(ho[-1][0, 0, 0, 0])  # the step's result is read on the host
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_repeats = 1
+    while e2e_s * e2e_repeats < MIN_TIMED_S and e2e_repeats < 10:
+        # same rule as the device-timed region: whole passes of `steps` steps, the last pass is reported
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            hstep.run(synchronize=True)
+            _ = float(ho[-1][0, 0, 0, 0])
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        e2e_repeats += 1
     h2d = world * Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es  # summed over ranks
     d2h = world * Lyr * Bl * Hql * D * es
     e2e = {"value": B * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -722,20 +798,17 @@ def run_ours(args, w, rank, world, local_rank):
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sec, info = cpu_decode_step_time(w, budget_s=15.0, steps=1, warmup=0)
+        sec, info = cpu_decode_step_time(w, budget_s=20.0, steps=3, warmup=0)
         cpu_baseline = {"value": B / sec, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]}
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": part["scaling"], "vs_baseline": None,
-                "dtype": w["dtype"], "data": "synthetic",
-                "config": {"workload": args.workload, **{k: w[k] for k in ("layers", "Hq", "Hkv", "D")}, "B": B,
-                           "context_start": ctx0, "parallelism": parallelism,
-                           "l2": "inputs larger than L2 (per-layer K+V working set "
-                                 f"{Bl * Hkvl * ctx0 * bytes_per_token_head(w) / 1e6:.0f} MB; all layers "
-                                 f"{Lyr * Bl * Hkvl * ctx0 * bytes_per_token_head(w) / 1e9:.2f} GB per step)"},
+                "dtype": w["dtype"], "data": "synthetic", "config": cfg,
+                "timed_passes": {"count": len(pass_ms), "ms": pass_ms, "reported": "median",
+                                 "context_at_first_timed_step": ctx0},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
-                "cpu_baseline": cpu_baseline}
+                "verify": verify, "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -750,8 +823,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--parallel", default="sequences", choices=["sequences", "heads"],
-                    help="N>1 partition: independent sequences per rank (weak) or KV heads of one batch (strong)")
+    ap.add_argument("--parallel", default="heads", choices=["sequences", "heads"],
+                    help="N>1 partition: KV heads of one batch + per-layer output exchange (strong, default) or "
+                         "independent sequences per rank (weak)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

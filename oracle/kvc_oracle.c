@@ -424,7 +424,107 @@ static void load_row(const orc_source *s, int b, int h, int64_t t, int D, float 
         for (int d = 0; d < D; ++d) dst[d] = bf16_to_f32(p[d]);
         return;
     }
+    if (s->kind == SRC_TURBO) {
+        /* one pass over the row's bit stream instead of a word lookup per element (same values) */
+        const uint32_t *row = (const uint32_t *)s->data + b * s->sb + h * s->sh + t * s->st;
+        const float norm = s->norms[b * s->gsb + h * s->gsh + t * s->gst];
+        const int bits = s->bits;
+        const uint32_t mask = (1u << bits) - 1u;
+        uint64_t buf = 0;
+        int have = 0, wi = 0;
+        for (int d = 0; d < D; ++d) {
+            if (have < bits) { buf |= (uint64_t)row[wi++] << have; have += 32; }
+            dst[d] = s->codebook[(uint32_t)buf & mask] * norm;
+            buf >>= bits;
+            have -= bits;
+        }
+        return;
+    }
     for (int d = 0; d < D; ++d) dst[d] = src_elem(s, b, h, t, d);
+}
+
+/* The timed baseline's form of the same attention (float accumulation, no array mask): one pass per
+ * (batch, KV head) that decodes every cached K and V row once and serves all the query rows of the
+ * head group from it, the way the reference's kernels share a KV head between its query heads
+ * (TurboQuantKernels.swift:424-542) instead of decoding the row again for every query head. */
+static void attention_grouped(const orc_attn *a) {
+    const int D = a->D, L = a->L;
+    const int rep = a->Hq / a->Hkv;
+    const int R = rep * L;
+    const int64_t T = a->T;
+    const int64_t units = (int64_t)a->B * a->Hkv;
+#pragma omp parallel
+    {
+        float *kv = (float *)malloc(sizeof(float) * D);
+        float *qv = (float *)malloc(sizeof(float) * (size_t)R * D);
+        float *acc = (float *)malloc(sizeof(float) * (size_t)R * D);
+        float *sc = (float *)malloc(sizeof(float) * (size_t)R * (size_t)(T > 0 ? T : 1));
+        float *mx = (float *)malloc(sizeof(float) * R);
+        float *lsum = (float *)malloc(sizeof(float) * R);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t u = 0; u < units; ++u) {
+            const int hk = (int)(u % a->Hkv), b = (int)(u / a->Hkv);
+            for (int r = 0; r < R; ++r) {
+                const int hq = hk * rep + r / L, l = r % L;
+                const int64_t qbase = (((int64_t)b * a->Hq + hq) * L + l) * D;
+                float *q = qv + (size_t)r * D;
+                for (int d = 0; d < D; ++d) q[d] = ld(a->q, a->q_dtype, qbase + d);
+                if (a->q_signs) {
+                    for (int d = 0; d < D; ++d) q[d] *= a->q_signs[d];
+                    fwht_row(q, D);
+                    const float f = 1.0f / sqrtf((float)D);
+                    for (int d = 0; d < D; ++d) {
+                        q[d] = q[d] * f * a->scale;
+                        if (a->q_calib) q[d] *= a->q_calib[d];
+                    }
+                } else {
+                    for (int d = 0; d < D; ++d) q[d] *= a->scale;
+                }
+                mx[r] = -INFINITY;
+                lsum[r] = 0.f;
+                for (int d = 0; d < D; ++d) acc[(size_t)r * D + d] = 0.f;
+            }
+            for (int64_t t = 0; t < T; ++t) {
+                load_row(&a->k, b, hk, t, D, kv);
+                for (int r = 0; r < R; ++r) {
+                    const int l = r % L;
+                    float s2 = -INFINITY;
+                    if (a->mask_mode != MASK_CAUSAL || t <= a->causal_offset + l) {
+                        const float *q = qv + (size_t)r * D;
+                        s2 = 0.f;
+                        for (int d = 0; d < D; ++d) s2 += q[d] * kv[d];
+                        if (s2 > mx[r]) mx[r] = s2;
+                    }
+                    sc[(size_t)r * T + t] = s2;
+                }
+            }
+            for (int64_t t = 0; t < T; ++t) {
+                load_row(&a->v, b, hk, t, D, kv);
+                for (int r = 0; r < R; ++r) {
+                    const float s2 = sc[(size_t)r * T + t];
+                    if (s2 == -INFINITY) continue;
+                    const float p = expf(s2 - mx[r]);
+                    lsum[r] += p;
+                    float *o = acc + (size_t)r * D;
+                    for (int d = 0; d < D; ++d) o[d] += p * kv[d];
+                }
+            }
+            for (int r = 0; r < R; ++r) {
+                const int hq = hk * rep + r / L, l = r % L;
+                const int64_t qbase = (((int64_t)b * a->Hq + hq) * L + l) * D;
+                float *o = acc + (size_t)r * D;
+                const float inv = lsum[r] > 0.f ? 1.0f / lsum[r] : 0.f;
+                for (int d = 0; d < D; ++d) o[d] *= inv;
+                if (a->o_signs) {
+                    fwht_row(o, D);
+                    const float f = 1.0f / sqrtf((float)D);
+                    for (int d = 0; d < D; ++d) o[d] = o[d] * f * a->o_signs[d];
+                }
+                for (int d = 0; d < D; ++d) st(a->out, a->q_dtype, qbase + d, o[d]);
+            }
+        }
+        free(kv); free(qv); free(acc); free(sc); free(mx); free(lsum);
+    }
 }
 
 void orc_attention(const orc_attn *a) {
@@ -432,6 +532,10 @@ void orc_attention(const orc_attn *a) {
     const int rep = a->Hq / a->Hkv;
     const int64_t T = a->T;
     const int64_t work = (int64_t)a->B * a->Hq * L;
+    if (!a->precise && a->mask_mode != MASK_ARRAY) {
+        attention_grouped(a);
+        return;
+    }
 #pragma omp parallel
     {
         float *kv = (float *)malloc(sizeof(float) * D);

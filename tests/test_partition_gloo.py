@@ -41,8 +41,9 @@ def test_partition_covers_every_unit_once():
             assert p["Hq_local"] * W["Hkv"] == p["Hkv_local"] * W["Hq"]
     odd = dict(W, Hkv=3, Hq=6)
     assert bench.partition(odd, 2, "heads")["shard_axis"] == 0      # falls back to the batch
-    with pytest.raises(ValueError):
-        bench.partition(dict(odd, B=3), 2, "heads")
+    # neither the heads nor the batch divide: every rank keeps whole sequences, nothing is exchanged
+    none = bench.partition(dict(odd, B=3), 2, "heads")
+    assert not none["collective"] and none["scaling"] == "weak" and none["B_global"] == 6
 
 
 def _rank_main(rank, world, port, mode, q_out):
