@@ -337,7 +337,9 @@ __device__ __forceinline__ void consumer_bar() {
 // segment's partial, takes a ticket and, in the CTA that completes the unit, merges all
 // partials (log-sum-exp) and writes the output rows (through signs * H(.) / sqrt(D) when
 // o_signs is set). `work` holds red_rows * D floats when o_signs is set and is unused otherwise.
-template <int D, int NW>
+// NBUF (default NW) is the number of warps that wrote cross-warp buffers: a kernel that has already
+// folded its NW warps down to NBUF of them passes the smaller count, all NW warps still take part.
+template <int D, int NW, int NBUF = NW>
 __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const float *red_o, const float *red_ml,
                                  int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R,
                                  int64_t x_unit = -1, int unit_tiles = 0) {
@@ -357,10 +359,10 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
         const int r = i / D, d = i % D;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) m = fmaxf(m, red_ml[(w * f.red_rows + r) * 2]);
+        for (int w = 0; w < NBUF; ++w) m = fmaxf(m, red_ml[(w * f.red_rows + r) * 2]);
         float o = 0.f, l = 0.f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
+        for (int w = 0; w < NBUF; ++w) {
             const float mw = red_ml[(w * f.red_rows + r) * 2];
             const float fw = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
             o += red_o[(w * f.red_rows + r) * red_stride + d] * fw;

@@ -493,6 +493,8 @@ bool turbo_source_fits(const KVSource &s, int D, int64_t T) {
 
 }  // namespace
 
+int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream);   // attn_turbo_v4.cu: 4-bit values
+
 // Returns the number of kernels launched, or 0 when the call does not fit this path.
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
@@ -508,6 +510,10 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     const bool known = (kb == 4 && vb == 4) || (kb == 4 && vb == 2) || (kb == 3 && vb == 3) || (kb == 2 && vb == 2) ||
                        (kb == 3 && vb == 4);
     if (!known) return 0;
+    if (vb == 4) {
+        const int n = launch_attention_turbo_v4(a, stream);
+        if (n > 0) return n;
+    }
     const int64_t bh = (int64_t)a.B * a.Hkv;
     if (bh * (int64_t)sizeof(int) > TQ_COUNTER_BYTES) return 0;
     int *status = device_status_word(a.device);

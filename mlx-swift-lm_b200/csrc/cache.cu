@@ -177,9 +177,9 @@ void check_new_rows(const kvc_cache *c, const Array4 &ka, const Array4 &va, cons
 // Array4
 // ---------------------------------------------------------------------
 void Array4::alloc(int64_t b, int64_t h, int64_t c, int64_t w, int32_t dt, cudaStream_t s) {
-    // capacity in whole 64-token tiles: the TMA-staged attention kernels copy full
-    // tiles, and a tile must never reach past the (batch, head) slab
-    B = b; H = h; cap = round_up(std::max<int64_t>(c, 1), 64); W = w; dtype = dt;
+    // capacity in whole 256-token steps (the reference's allocation step): the TMA-staged attention
+    // kernels copy full stages of up to 256 tokens, and a stage must never reach past the (batch, head) slab
+    B = b; H = h; cap = round_up(std::max<int64_t>(c, 1), 256); W = w; dtype = dt;
     ptr = dev_alloc(bytes(), s);
     KVC_CUDA(cudaMemsetAsync(ptr, 0, bytes(), s));
 }
@@ -708,7 +708,8 @@ static void turbo_compress_raw(kvc_cache *c, cudaStream_t s) {
     const int D = (int)c->k.W;
     KVC_REQUIRE(c->v.W == c->k.W, "TurboQuant: key and value head dims must match");
     ensure_codecs(c, D, s);
-    const int64_t cap = std::max<int64_t>(std::max<int64_t>(c->cfg.reserve_tokens, c->k.cap), round_up(c->offset, 256));
+    // whole 256-row steps, like the reference's allocations: the decode kernels stream whole stages
+    const int64_t cap = round_up(std::max<int64_t>(std::max<int64_t>(c->cfg.reserve_tokens, c->k.cap), round_up(c->offset, 256)), 256);
     turbo_alloc_compressed(c, c->k.B, c->k.H, D, c->k.dtype, cap, s);
     kvc_tensor kt = c->k.view(c->offset), vt = c->v.view(c->offset);
     if (c->raw_key) {
@@ -743,7 +744,7 @@ void cache_turbo_encode_new_token(kvc_cache *c, const kvc_tensor &k, const kvc_t
     const int64_t S = k.shape[2], prev = c->offset;
     if (!c->compressed) {
         // nothing was cached yet: start directly in the compressed phase
-        const int64_t cap = std::max<int64_t>(c->cfg.reserve_tokens, round_up(std::max<int64_t>(S, 1), 256));
+        const int64_t cap = round_up(std::max<int64_t>(c->cfg.reserve_tokens, round_up(std::max<int64_t>(S, 1), 256)), 256);
         turbo_alloc_compressed(c, k.shape[0], k.shape[1], D, k.dtype, cap, s);
         if (c->raw_key) c->k.alloc(k.shape[0], k.shape[1], cap, D, k.dtype, s);
         c->compressed = true;
@@ -1066,12 +1067,13 @@ kvc_tensor cache_state_get(kvc_cache *c, int index) {
 }
 
 // Copy a strided [B, H, T, W] (or [B, H, T]) device tensor into a fresh array.
-static void adopt(Array4 &dst, const kvc_tensor &t, cudaStream_t s) {
+// `step` > 1 rounds the capacity up to whole steps (the rows beyond the copied ones stay unused).
+static void adopt(Array4 &dst, const kvc_tensor &t, cudaStream_t s, int64_t step = 1) {
     kvc_tensor x = t;
     if (x.ndim == 3) { x.ndim = 4; x.shape[3] = 1; x.stride[3] = 1; }
     require4(x, "state array");
     dst.release(s);
-    dst.alloc(x.shape[0], x.shape[1], std::max<int64_t>(x.shape[2], 1), x.shape[3], x.dtype, s);
+    dst.alloc(x.shape[0], x.shape[1], round_up(std::max<int64_t>(x.shape[2], 1), step), x.shape[3], x.dtype, s);
     if (x.shape[2] == 0) return;
     AppendArgs a;
     a.k_src = x.data; a.v_src = x.data;
@@ -1115,13 +1117,13 @@ void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStre
                 a->release(s);
             if (c->affine_key && count == 5 && !c->affine_value) {
                 adopt(c->kq, arrays[0], s); adopt(c->ks, arrays[1], s); adopt(c->kb, arrays[2], s);
-                adopt(c->vp, arrays[3], s); adopt(c->vn, arrays[4], s);
+                adopt(c->vp, arrays[3], s, 256); adopt(c->vn, arrays[4], s, 256);
                 c->compressed = true;
             } else if (c->raw_key && count == 3 && !c->affine_value) {
-                adopt(c->k, arrays[0], s); adopt(c->vp, arrays[1], s); adopt(c->vn, arrays[2], s);
+                adopt(c->k, arrays[0], s); adopt(c->vp, arrays[1], s, 256); adopt(c->vn, arrays[2], s, 256);
                 c->compressed = true;
             } else if (!c->affine_key && !c->raw_key && c->affine_value && count == 5) {
-                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
+                adopt(c->kp, arrays[0], s, 256); adopt(c->kn, arrays[1], s, 256);
                 adopt(c->vq, arrays[2], s); adopt(c->vs, arrays[3], s); adopt(c->vb, arrays[4], s);
                 c->compressed = true;
             } else if (!c->affine_key && !c->raw_key && count == 5) {
@@ -1132,13 +1134,13 @@ void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStre
                 std::vector<float> scale((size_t)cs.shape[0]);
                 KVC_CUDA(cudaMemcpyAsync(scale.data(), cs.data, scale.size() * sizeof(float), cudaMemcpyDeviceToHost, s));
                 KVC_CUDA(cudaStreamSynchronize(s));
-                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
-                adopt(c->vp, arrays[2], s); adopt(c->vn, arrays[3], s);
+                adopt(c->kp, arrays[0], s, 256); adopt(c->kn, arrays[1], s, 256);
+                adopt(c->vp, arrays[2], s, 256); adopt(c->vn, arrays[3], s, 256);
                 set_key_calibration(c, scale, s);
                 c->compressed = true;
             } else if (count == 4 && !c->affine_value) {
-                adopt(c->kp, arrays[0], s); adopt(c->kn, arrays[1], s);
-                adopt(c->vp, arrays[2], s); adopt(c->vn, arrays[3], s);
+                adopt(c->kp, arrays[0], s, 256); adopt(c->kn, arrays[1], s, 256);
+                adopt(c->vp, arrays[2], s, 256); adopt(c->vn, arrays[3], s, 256);
                 c->compressed = true;
             } else if (count == 2) {
                 adopt(c->k, arrays[0], s); adopt(c->v, arrays[1], s);
@@ -1219,9 +1221,9 @@ void cache_set_meta_state(kvc_cache *c, const std::vector<std::string> &m) {
 // ---------------------------------------------------------------------
 // copy / conversions
 // ---------------------------------------------------------------------
-static void clone_array(const Array4 &src, Array4 &dst, int64_t rows, cudaStream_t s) {
+static void clone_array(const Array4 &src, Array4 &dst, int64_t rows, cudaStream_t s, int64_t step = 1) {
     if (!src.allocated()) return;
-    dst.alloc(src.B, src.H, std::max<int64_t>(rows, 1), src.W, src.dtype, s);
+    dst.alloc(src.B, src.H, round_up(std::max<int64_t>(rows, 1), step), src.W, src.dtype, s);
     copy_rows(src, 0, dst, 0, std::min(rows, src.cap), s);
 }
 
@@ -1247,8 +1249,9 @@ kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
     clone_array(c->k, n->k, rows, s); clone_array(c->v, n->v, rows, s);
     clone_array(c->kq, n->kq, rows, s); clone_array(c->ks, n->ks, rows, s); clone_array(c->kb, n->kb, rows, s);
     clone_array(c->vq, n->vq, rows, s); clone_array(c->vs, n->vs, rows, s); clone_array(c->vb, n->vb, rows, s);
-    clone_array(c->kp, n->kp, rows, s); clone_array(c->kn, n->kn, rows, s);
-    clone_array(c->vp, n->vp, rows, s); clone_array(c->vn, n->vn, rows, s);
+    // packed TurboQuant arrays in whole 256-row steps (what the reference allocates; the decode kernels stream whole stages)
+    clone_array(c->kp, n->kp, rows, s, 256); clone_array(c->kn, n->kn, rows, s, 256);
+    clone_array(c->vp, n->vp, rows, s, 256); clone_array(c->vn, n->vn, rows, s, 256);
     if (!c->kcodec.calib.empty()) set_key_calibration(n.get(), c->kcodec.calib, s);
     return n.release();
 }
