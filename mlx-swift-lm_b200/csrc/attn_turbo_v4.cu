@@ -104,9 +104,19 @@ __device__ __forceinline__ void lds_words(uint32_t addr, uint32_t (&dst)[N]) {
     } else if constexpr (N == 2) {
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dst[0]), "=r"(dst[1]) : "r"(addr));
     } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dst[i]) : "r"(addr + 4 * i));
+        static_assert(N == 3, "word loads are written for 2, 3 or 4 words");
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dst[0]) : "r"(addr));
+        asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(dst[1]) : "r"(addr));
+        asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(dst[2]) : "r"(addr));
     }
+}
+
+// The 8x8 b16 transpose without `volatile`: every lane of the warp reaches it (it is never under a
+// divergent branch here) and it has no side effect, so the compiler may schedule it among the lookups.
+__device__ __forceinline__ uint32_t movmatrix_free(uint32_t x) {
+    uint32_t r;
+    asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
 }
 
 // Address of value-table entry `byte BYTE of x` for this lane: one byte permute. `lane_const`
@@ -377,12 +387,25 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
                            vnt_a = st_a + K_TILE + V_TILE + N_TILE;
             const int t_blk = (tile_begin + jt) * V4_TILE + wq * 16;
 
+            // ---- everything this block reads from the stage, up front: the loads are the only ordered
+            // (volatile) operations of the block, what follows is free to be scheduled around them ----
+            uint32_t wa[KB], wb[KB];
+            uint32_t va[2], vb4[2], vc[2], vd[2];
+            lds_words<KB>(kpt_a + (uint32_t)(tl0 * KW + c * KB) * 4u, wa);
+            lds_words<KB>(kpt_a + (uint32_t)(tl1 * KW + c * KB) * 4u, wb);
+            const float kn0 = lds_f32(knt_a + 4u * tl0), kn1 = lds_f32(knt_a + 4u * tl1);
+            const float vn0 = lds_f32(vnt_a + 4u * tl0), vn1 = lds_f32(vnt_a + 4u * tl1);
+            {
+                const uint32_t v_a = vpt_a + (uint32_t)(tv * V4_VW + 2 * g) * 4u;
+                lds_words<2>(v_a, va);
+                lds_words<2>(v_a + 4 * V4_VW * 4, vb4);
+                lds_words<2>(v_a + 8 * V4_VW * 4, vc);
+                lds_words<2>(v_a + 12 * V4_VW * 4, vd);
+            }
             // ---- S^T = centroids[idx_k] . Q'^T, two accumulator chains ----
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#ifndef KVC_V4_MEASURE_NO_K
             {
-                uint32_t wa[KB], wb[KB];
-                lds_words<KB>(kpt_a + (uint32_t)(tl0 * KW + c * KB) * 4u, wa);
-                lds_words<KB>(kpt_a + (uint32_t)(tl1 * KW + c * KB) * 4u, wb);
 #pragma unroll
                 for (int m = 0; m < 8; ++m) {
                     uint32_t a[4];
@@ -393,9 +416,10 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
                     mma_f16(acc[m & 1], a, qb[m][0], qb[m][1]);
                 }
             }
+#endif
             float sc[4];
             {
-                const float n0 = lds_f32(knt_a + 4u * tl0), n1 = lds_f32(knt_a + 4u * tl1);
+                const float n0 = kn0, n1 = kn1;
                 sc[0] = n0 * (acc[0][0] + acc[1][0]);
                 sc[1] = n0 * (acc[0][1] + acc[1][1]);
                 sc[2] = n1 * (acc[0][2] + acc[1][2]);
@@ -442,21 +466,15 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
             // query row g and the k slots (2c, 2c+1), i.e. the tokens (c, c + 4) [+ 8 in the second register] ----
             uint32_t pb[2];
             {
-                const float n0 = lds_f32(vnt_a + 4u * tl0), n1 = lds_f32(vnt_a + 4u * tl1);
-                pb[0] = movmatrix_trans(pack_h2(pr[0] * n0, pr[1] * n0));
-                pb[1] = movmatrix_trans(pack_h2(pr[2] * n1, pr[3] * n1));
+                pb[0] = movmatrix_free(pack_h2(pr[0] * vn0, pr[1] * vn0));
+                pb[1] = movmatrix_free(pack_h2(pr[2] * vn1, pr[3] * vn1));
             }
+#ifndef KVC_V4_MEASURE_NO_V
             // ---- O^T += centroids[idx_v]^T . P'^T ----
             // The lane owns dims 16g .. 16g+15 of its four tokens. For word w and byte b of the
             // interleaved registers, output tile mt = 4w + b has row g = dim 16g + 2mt (even nibbles)
             // and row g + 8 = dim 16g + 2mt + 1 (odd nibbles).
             {
-                uint32_t va[2], vb4[2], vc[2], vd[2];
-                const uint32_t v_a = vpt_a + (uint32_t)(tv * V4_VW + 2 * g) * 4u;
-                lds_words<2>(v_a, va);
-                lds_words<2>(v_a + 4 * V4_VW * 4, vb4);
-                lds_words<2>(v_a + 8 * V4_VW * 4, vc);
-                lds_words<2>(v_a + 12 * V4_VW * 4, vd);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     const uint32_t lo_ab = (va[w] & 0x0F0F0F0Fu) | ((vb4[w] << 4) & 0xF0F0F0F0u);
@@ -477,6 +495,9 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
 #undef KVC_V4_TILE
                 }
             }
+#else
+            o_acc[0][0] += __uint_as_float(pb[0]) + __uint_as_float(pb[1]);
+#endif
             __syncwarp();
             if (lane == 0 && !(KVC_SKIP_BITS(p) & 2)) mbar_arrive(&empty[s]);
         }
