@@ -627,7 +627,13 @@ def run_ours(args, w, rank, world, local_rank):
         uid = [kvc.Comm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         comm = kvc.Comm(rank, world, uid[0])
-        outs = [torch.empty((B, Hq, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
+        # gathered outputs in symmetric memory: the per-layer exchange runs as peer stores over NVLink
+        # (--exchange nccl keeps them in ordinary memory: ncclAllGather + re-ordering kernel)
+        if args.exchange == "peer":
+            all_outs = comm.symm_empty((Lyr, B, Hq, 1, D), dtype, dev)
+            outs = [all_outs[i] for i in range(Lyr)]
+        else:
+            outs = [torch.empty((B, Hq, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
     else:
         outs = [torch.empty((Bl, Hql, 1, D), dtype=dtype, device=dev) for _ in range(Lyr)]
     step = kvc.DecodeStep(caches, qs, ks, vs, outs, scale)
@@ -693,7 +699,10 @@ def run_ours(args, w, rank, world, local_rank):
         vq = [torch.randn((Bl, Hql, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
         vk = [torch.randn((Bl, Hkvl, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
         vv = [torch.randn((Bl, Hkvl, Lv, D), generator=g).to(dtype).to(dev) for _ in range(Lyr)]
-        if comm is not None:
+        if comm is not None and args.exchange == "peer":
+            all_vo = comm.symm_empty((Lyr, B, Hq, Lv, D), dtype, dev)
+            vo = [all_vo[i] for i in range(Lyr)]
+        elif comm is not None:
             vo = [torch.empty((B, Hq, Lv, D), dtype=dtype, device=dev) for _ in range(Lyr)]
         else:
             vo = [torch.empty((Bl, Hql, Lv, D), dtype=dtype, device=dev) for _ in range(Lyr)]
@@ -769,14 +778,34 @@ def run_ours(args, w, rank, world, local_rank):
     hk = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).pin_memory() for _ in range(Lyr)]
     hv = [torch.randn((Bl, Hkvl, 1, D), generator=g).to(dtype).pin_memory() for _ in range(Lyr)]
     ho = [torch.empty((Bl, Hql, 1, D), dtype=dtype).pin_memory() for _ in range(Lyr)]
-    hstep = kvc.DecodeStep(caches, hq, hk, hv, ho, scale, host=True)
+    if comm is None:
+        hstep = kvc.DecodeStep(caches, hq, hk, hv, ho, scale, host=True)
+
+        def e2e_step():
+            hstep.run(synchronize=True)
+            return float(ho[-1][0, 0, 0, 0])  # the step's result is read on the host
+    else:
+        # sharded: this rank's inputs travel host -> device, the sharded step (attention + exchange per
+        # layer) runs, and the GATHERED outputs of every layer travel back to this rank's host
+        hfull = [torch.empty((B, Hq, 1, D), dtype=dtype).pin_memory() for _ in range(Lyr)]
+
+        def e2e_step():
+            for i in range(Lyr):
+                qs[i].copy_(hq[i], non_blocking=True)
+                ks[i].copy_(hk[i], non_blocking=True)
+                vs[i].copy_(hv[i], non_blocking=True)
+            step.run_sharded(comm, shard_axis)
+            for i in range(Lyr):
+                hfull[i].copy_(outs[i], non_blocking=True)
+            torch.cuda.synchronize()
+            return float(hfull[-1][0, 0, 0, 0])
+
     for _ in range(min(warmup, 3)):
-        hstep.run(synchronize=True)
+        e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
-        hstep.run(synchronize=True)
-        _ = float(ho[-1][0, 0, 0, 0])  # the step's result is read on the host
+        e2e_step()
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     e2e_repeats = 1
@@ -785,16 +814,19 @@ def run_ours(args, w, rank, world, local_rank):
         barrier()
         t0 = time.perf_counter()
         for _ in range(steps):
-            hstep.run(synchronize=True)
-            _ = float(ho[-1][0, 0, 0, 0])
+            e2e_step()
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e_repeats += 1
     h2d = world * Lyr * (Bl * Hql * D + 2 * Bl * Hkvl * D) * es  # summed over ranks
-    d2h = world * Lyr * Bl * Hql * D * es
+    d2h = world * Lyr * (B * Hq if comm is not None else Bl * Hql) * D * es
     e2e = {"value": B * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "note": "kvc_attention_batch with pinned host q/k/v in and outputs out for every layer (copies run on side streams ahead of / behind the layer kernels), one stream sync per step, result read on the host"
-                   + ("; every rank runs its own shard, bytes summed over ranks, time is the max" if world > 1 else "")}
+           "note": ("kvc_attention_batch with pinned host q/k/v in and outputs out for every layer (copies run on side "
+                    "streams ahead of / behind the layer kernels), one stream sync per step, result read on the host"
+                    if comm is None else
+                    "per rank: pinned host q/k/v of its shard -> device, the sharded step (attention + output exchange per "
+                    "layer), the gathered outputs of every layer -> pinned host, one sync per step")
+                   + ("; bytes summed over ranks, time is the max over ranks" if world > 1 else "")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -823,6 +855,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="per-layer output exchange of the sharded partition: peer stores into symmetric memory "
+                         "(default) or ncclAllGather")
     ap.add_argument("--parallel", default="heads", choices=["sequences", "heads"],
                     help="N>1 partition: KV heads of one batch + per-layer output exchange (strong, default) or "
                          "independent sequences per rank (weak)")

@@ -473,6 +473,25 @@ kvc_status kvc_comm_init(int32_t rank, int32_t world, const uint8_t id[KVC_UNIQU
 void       kvc_comm_free(kvc_comm *comm);
 int32_t    kvc_comm_rank(const kvc_comm *comm);
 int32_t    kvc_comm_world(const kvc_comm *comm);
+/* Symmetric memory for the gathered attention outputs. Collective over the
+ * communicator (every rank calls it with the same size, in the same order):
+ * allocates `bytes` on this rank, maps every peer's allocation of the same
+ * call through CUDA IPC and returns this rank's pointer. When the `out_full`
+ * of kvc_attention_sharded lies inside such memory, the per-layer exchange is
+ * done with peer stores instead of ncclAllGather: every rank's attention
+ * kernel writes its slice into its own copy in the final layout, one kernel
+ * pushes the slice into every peer's copy with plain 16-byte stores over
+ * NVLink, releases an arrival counter in the peer's memory and waits until
+ * every peer's slice has arrived (bounded: a wait that runs out stores code
+ * 41 in the status word read by kvc_device_status and the kernel returns).
+ * A gathered buffer may be written again only after at least one other
+ * exchange on the same communicator has completed in between (consecutive
+ * layers of a model satisfy this). Freed with the communicator.
+ * No counterpart in the reference (it has no multi-device path). */
+kvc_status kvc_comm_symm_alloc(kvc_comm *comm, size_t bytes, void *stream, void **out_ptr);
+/* Iterations of the bounded arrival wait (default 2^26, each at least 64 ns). */
+kvc_status kvc_comm_set_wait_limit(kvc_comm *comm, uint32_t iterations);
+
 /* This rank attends over its own shard (cache holds Hkv/world heads, queries
  * carry the matching Hq/world heads) and the per-layer outputs are
  * all-gathered along the head axis into out_full [B, Hq, L, D] on every rank.
@@ -515,6 +534,15 @@ kvc_status kvc_attention_batch(kvc_cache *const *caches, int32_t count, const kv
  * ran out; -1 = the word could not be read. The affected call's output is
  * undefined when the status is non-zero (KVC_ERR_TIMEOUT territory). */
 int32_t    kvc_device_status(void);
+/* Clears the status word of the current device (after the caller has dealt
+ * with a reported timeout). */
+kvc_status kvc_device_status_reset(void);
+/* Launches a one-thread kernel whose bounded wait can never be satisfied: it
+ * polls a word that stays zero `iterations` times (<= 2^24, each at least 32 ns),
+ * then stores code 40 in the status word and returns. Lets a host check the
+ * timeout reporting path without any fault or hang on the device. No
+ * counterpart in the reference. */
+kvc_status kvc_device_wait_probe(uint32_t iterations, void *stream);
 
 /* Event timing of the dominant attention kernel. While enabled, every
  * attention call brackets its main kernel (not the merge or append kernels)

@@ -1144,6 +1144,22 @@ int32_t kvc_device_status(void) {
     return kvc::device_status(dev);
 }
 
+kvc_status kvc_device_status_reset(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || !kvc::device_status_reset(dev)) {
+        (void)cudaGetLastError();
+        return set_error(KVC_ERR_CUDA, "kvc_device_status_reset: the status word could not be cleared");
+    }
+    return KVC_OK;
+}
+
+kvc_status kvc_device_wait_probe(uint32_t iterations, void *stream) {
+    return guarded([&] {
+        KVC_REQUIRE(iterations > 0 && iterations <= (1u << 24), "kvc_device_wait_probe: iterations must be in [1, 2^24]");
+        kvc::device_wait_probe(kvc::current_device(), iterations, as_stream(stream));
+    });
+}
+
 void kvc_timing_enable(int32_t on) { kvc::timing_set(on != 0); }
 
 kvc_status kvc_timing_read(double *total_ms, int64_t *launches, int32_t reset) {

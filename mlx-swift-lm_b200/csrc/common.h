@@ -70,6 +70,8 @@ int current_device();
 int sm_count(int device);
 int *device_status_word(int device);  // shared by all kernels with bounded waits
 int device_status(int device);        // reads it (0 = no wait ever ran out)
+bool device_status_reset(int device);  // clears it
+void device_wait_probe(int device, uint32_t iterations, cudaStream_t stream);  // a wait that runs out on purpose
 
 // ---------------------------------------------------------------------
 // kernel launch descriptors

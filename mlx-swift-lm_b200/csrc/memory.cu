@@ -209,6 +209,40 @@ int *device_status_word(int device) {
     return words[device];
 }
 
+bool device_status_reset(int device) {
+    int *w = device_status_word(device);
+    if (!w) return false;
+    if (cudaMemset(w, 0, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
+namespace {
+// A wait that nothing ever satisfies: spins `iterations` times on a word that stays zero, then
+// reports through the status word and returns, exactly as the kernels' bounded waits do.
+__global__ void wait_probe_kernel(const volatile int *never_set, uint32_t iterations, int *status) {
+    bool ok = false;
+    for (uint32_t i = 0; i < iterations; ++i) {
+        if (*never_set != 0) { ok = true; break; }
+        __nanosleep(32);
+    }
+    if (!ok) atomicExch(status, 40);
+}
+}  // namespace
+
+void device_wait_probe(int device, uint32_t iterations, cudaStream_t stream) {
+    int *status = device_status_word(device);
+    if (!status) fail(KVC_ERR_CUDA, "no status word on this device");
+    int *zero = (int *)dev_alloc(sizeof(int), stream);
+    KVC_CUDA(cudaMemsetAsync(zero, 0, sizeof(int), stream));
+    wait_probe_kernel<<<1, 1, 0, stream>>>(zero, iterations, status);
+    KVC_CUDA(cudaGetLastError());
+    dev_free(zero, stream);
+    ++g_launch_count;
+}
+
 int device_status(int device) {
     int *w = device_status_word(device);
     if (!w) return 0;

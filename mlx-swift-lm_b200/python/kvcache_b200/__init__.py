@@ -151,10 +151,13 @@ _lib.kvc_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctyp
 _lib.kvc_can_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32]
 _lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
 _lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
+_lib.kvc_comm_symm_alloc.argtypes = [_vp, ctypes.c_size_t, _vp, ctypes.POINTER(_vp)]
+_lib.kvc_comm_set_wait_limit.argtypes = [_vp, ctypes.c_uint32]
 _lib.kvc_attention_batch.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP, ctypes.c_float,
                                      ctypes.c_int32, _TP, _vp, ctypes.c_int32, ctypes.c_int32]
 _lib.kvc_attention_sharded_batch.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP,
                                              ctypes.c_float, ctypes.c_int32, _TP, ctypes.c_int32, _vp]
+_lib.kvc_device_wait_probe.argtypes = [ctypes.c_uint32, _vp]
 _lib.kvc_timing_enable.argtypes = [ctypes.c_int32]
 _lib.kvc_timing_enable.restype = None
 _lib.kvc_timing_read.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int64), ctypes.c_int32]
@@ -733,6 +736,20 @@ class DecodeStep:
                                                self.mode, self.o, shard_axis, _stream_ptr(stream)))
 
 
+def device_status() -> int:
+    """0 unless a bounded device-side wait has run out since the last reset (kvc_device_status)."""
+    return int(_lib.kvc_device_status())
+
+
+def device_status_reset() -> None:
+    check(_lib.kvc_device_status_reset())
+
+
+def device_wait_probe(iterations: int = 1 << 12, stream=None) -> None:
+    """A kernel whose bounded wait runs out on purpose (kvc_device_wait_probe)."""
+    check(_lib.kvc_device_wait_probe(iterations, _stream_ptr(stream)))
+
+
 def timing_enable(on: bool) -> None:
     _lib.kvc_timing_enable(1 if on else 0)
 
@@ -775,6 +792,22 @@ class Comm:
         if h:
             _lib.kvc_comm_free(h)
             self._h = None
+
+    def symm_empty(self, shape, dtype, device, stream=None):
+        """A tensor of `shape` in symmetric memory (kvc_comm_symm_alloc; collective: every rank makes the
+        same call). Gathered outputs placed in such tensors are exchanged with peer stores over NVLink
+        instead of ncclAllGather. The memory belongs to the communicator and lives as long as it does."""
+        torch = _torch()
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        ptr = ctypes.c_void_p()
+        check(_lib.kvc_comm_symm_alloc(self._h, nbytes, _stream_ptr(stream), ctypes.byref(ptr)))
+        return _from_pointer(int(ptr.value), nbytes, dtype, device).view(*shape)
+
+    def set_wait_limit(self, iterations: int) -> None:
+        check(_lib.kvc_comm_set_wait_limit(self._h, iterations))
 
     def attention_sharded(self, cache: KVCache, queries, keys, values, scale, out_full, mask="none",
                           shard_axis: int = 1, stream=None):

@@ -286,3 +286,19 @@ def test_rotating_ring_decode_appends_inside_the_attention_kernel(kvc, oracle, c
                 assert bits_equal(a, np.ascontiguousarray(b)), step
     assert fused_steps >= 140        # growth and the one ring rebuild after the prefill cost extra launches
     assert kvc.lib().kvc_device_status() == 0
+
+
+def test_bounded_wait_reports_through_the_status_word(kvc, cuda):
+    """Every device-side wait in the library is bounded; one that runs out stores a code in the
+    per-device status word and the kernel returns. The probe kernel waits on a word nothing ever
+    sets: the status reads 40 afterwards, the context stays usable, and a reset clears the word."""
+    assert kvc.device_status() == 0
+    kvc.device_wait_probe(1 << 10)
+    torch.cuda.synchronize()
+    assert kvc.device_status() == 40
+    kvc.device_status_reset()
+    assert kvc.device_status() == 0
+    q = seeded((1, 8, 1, 128), 1, torch.bfloat16).to(cuda)
+    k = seeded((1, 2, 300, 128), 2, torch.bfloat16).to(cuda)
+    out = kvc.scaled_dot_product_attention(q, k, k, 0.09)       # the device still answers
+    assert torch.isfinite(out.float()).all() and kvc.device_status() == 0
