@@ -13,7 +13,7 @@ passes when run alone in a fresh process.
 import pytest
 import torch
 
-from helpers import TOL, seeded
+from helpers import TOL, max_abs_diff, seeded, to_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -40,6 +40,38 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row(kvc, cuda, 
     got, want = _pair(kvc, cuda, dtype, B=2, Hq=8, Hkv=2, L=1, T=2999, D=128, seed=11, mask="none")
     assert float((got.float() - want.float()).abs().max()) <= TOL[dtype]
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_no_alloc_entry_point_matches_the_oracle(kvc, oracle, cuda, dtype):
+    """The same two-calls-in-a-row pattern against the CPU oracle (not only against the library's
+    other entry point, which shares its authors)."""
+    for B, Hq, Hkv, L, T, D, seed, mask in ((2, 8, 2, 1, 1500, 128, 21, "none"), (1, 4, 2, 5, 90, 64, 27, "causal")):
+        q, k, v = seeded((B, Hq, L, D), seed, dtype), seeded((B, Hkv, T, D), seed + 1, dtype), seeded((B, Hkv, T, D), seed + 2, dtype)
+        dq, dk, dv = q.to(cuda), k.to(cuda), v.to(cuda)
+        got = kvc.scaled_dot_product_attention_noalloc(dq, dk, dv, D ** -0.5, mask, out=torch.empty_like(dq))
+        ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), D ** -0.5, mask)
+        assert max_abs_diff(got, ref) <= TOL[dtype]
+
+
+def test_no_alloc_entry_point_allocates_nothing(kvc, cuda):
+    """What the name promises: with inputs and output already on the device and one warm-up call
+    behind it (the first call on a device looks up the address of the fixed array), further calls
+    change neither the driver's free-memory figure nor the memory PyTorch's allocator holds."""
+    q = seeded((2, 8, 1, 128), 31, torch.bfloat16).to(cuda)
+    k = seeded((2, 2, 2500, 128), 32, torch.bfloat16).to(cuda)
+    v = seeded((2, 2, 2500, 128), 33, torch.bfloat16).to(cuda)
+    out = torch.empty_like(q)
+    kvc.scaled_dot_product_attention_noalloc(q, k, v, 0.09, out=out)     # warm-up: symbol lookup
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    held0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(5):
+        kvc.scaled_dot_product_attention_noalloc(q, k, v, 0.09, out=out)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the driver's free memory moved during no-alloc calls"
+    assert torch.cuda.memory_allocated() == held0 and torch.cuda.memory_reserved() == reserved0
 
 
 def test_no_alloc_entry_point_rejects_what_does_not_fit(kvc, cuda):
