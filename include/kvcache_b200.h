@@ -112,7 +112,9 @@ typedef enum {
     KVC_KIND_SIMPLE = 0,     /* KVCacheSimple        KVCache.swift:391-538  */
     KVC_KIND_ROTATING = 1,   /* RotatingKVCache      KVCache.swift:541-900  */
     KVC_KIND_QUANTIZED = 2,  /* QuantizedKVCache     KVCache.swift:923-1210 */
-    KVC_KIND_TURBO = 3       /* TurboQuantKVCache    TurboQuantKVCache.swift:633-1604 */
+    KVC_KIND_TURBO = 3,      /* TurboQuantKVCache    TurboQuantKVCache.swift:633-1604 */
+    KVC_KIND_CHUNKED = 4,    /* ChunkedKVCache       KVCache.swift:1213-1304 (chunkSize travels in max_size, <= 0 = nil) */
+    KVC_KIND_LIST = 5        /* CacheList            KVCache.swift:1556-1726 (made by kvc_list_create) */
 } kvc_kind;
 
 /* Construction parameters; one struct for the four initialisers
@@ -148,6 +150,35 @@ typedef struct kvc_config {
 void       kvc_config_default(kvc_config *cfg, int32_t kind);
 kvc_status kvc_create(const kvc_config *cfg, kvc_cache **out);
 void       kvc_free(kvc_cache *cache);
+
+/* CacheList(caches...)  KVCache.swift:1556-1568. The list takes ownership of the
+ * children (freeing the list frees them; do not free them yourself). Children
+ * may be lists. update / attention on the list itself are refused like the
+ * reference's fatalError (:1576-1578): work goes through kvc_list_child. */
+kvc_status kvc_list_create(kvc_cache *const *children, int32_t count, kvc_cache **out);
+int32_t    kvc_list_count(const kvc_cache *list);
+/* subscript(index:) :1572-1574: borrowed handle, valid while the list lives. */
+kvc_cache *kvc_list_child(const kvc_cache *list, int32_t index);
+
+/* ChunkedKVCache.maybeTrimFront()  KVCache.swift:1222-1232: once the buffer holds
+ * chunkSize rows or more, drops everything but its last chunkSize rows and advances
+ * startPosition. kvc_start_position returns that counter (0 for other kinds). */
+kvc_status kvc_maybe_trim_front(kvc_cache *cache, void *stream);
+int64_t    kvc_start_position(const kvc_cache *cache);
+
+/* prepare(lengths:) / finalize()  KVCache.swift:97-103. For every cache kind of this
+ * library they are the reference's empty defaults (BaseKVCache :229-233; only the
+ * state-space ArraysCache keeps the lengths); a CacheList forwards to its children
+ * (:1633-1643). Provided so that callers written against the protocol link. */
+kvc_status kvc_prepare(kvc_cache *cache, const int32_t *lengths, int32_t count);
+kvc_status kvc_finalize(kvc_cache *cache);
+
+/* createCausalMask(n:offset:windowSize:lengths:)  KVCache.swift:253-275. Writes the boolean
+ * mask (one byte per element) for `n` query rows at `offset`: [n, offset + n] without
+ * lengths, [batch, 1, n, offset + n] with `lengths` (device int32 [batch]: row b also
+ * requires key index < lengths[b]). window_size < 0 means nil. */
+kvc_status kvc_create_causal_mask(int32_t n, int64_t offset, int64_t window_size, const int32_t *lengths_dev,
+                                  int32_t batch, void *out_mask, void *stream);
 
 /* KVCache.offset / maxSize (-1 when nil) / kind. `offset` is a settable
  * property in the reference (BaseKVCache.offset, KVCache.swift:185); setting

@@ -110,6 +110,22 @@ __global__ void causal_mask_kernel(uint8_t *out, int64_t n, int64_t offset, int6
     out[i] = keep ? 1 : 0;
 }
 
+// The same mask per batch entry with prepared lengths: entry b also requires col < lengths[b]
+// (createCausalMask's `lengths` argument, KVCache.swift:268-271). out: [batch, 1, n, offset + n].
+__global__ void causal_mask_lengths_kernel(uint8_t *out, int64_t n, int64_t offset, int64_t window,
+                                           const int32_t *lengths, int64_t total) {
+    const int64_t cols = offset + n;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int64_t b = i / (n * cols), j = i % (n * cols);
+    const int64_t r = offset + j / cols;
+    const int64_t c = j % cols;
+    bool keep = r >= c;
+    if (window >= 0) keep = keep && (r < c + window);
+    keep = keep && (c < (int64_t)lengths[b]);
+    out[i] = keep ? 1 : 0;
+}
+
 __global__ void rolled_mask_kernel(uint8_t *out, int64_t size, int64_t window, int64_t shift) {
     // RotatingKVCache.makeMask single-token branch (KVCache.swift:861-865):
     // mask[i] = i >= size - window, rolled right by `shift`.
@@ -194,6 +210,15 @@ void launch_causal_mask(uint8_t *out, int64_t n, int64_t offset, int64_t window,
     const int64_t total = n * (offset + n);
     if (total <= 0) return;
     causal_mask_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out, n, offset, window);
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+void launch_causal_mask_lengths(uint8_t *out, int64_t n, int64_t offset, int64_t window, const int32_t *lengths,
+                                int64_t batch, cudaStream_t s) {
+    const int64_t total = batch * n * (offset + n);
+    if (total <= 0) return;
+    causal_mask_lengths_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out, n, offset, window, lengths, total);
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
 }

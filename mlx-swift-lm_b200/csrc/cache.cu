@@ -233,6 +233,7 @@ kvc_cache::~kvc_cache() {
     if (kcodec.signs_dev) kvc::dev_free(kcodec.signs_dev, s);
     if (vcodec.signs_dev) kvc::dev_free(vcodec.signs_dev, s);
     if (kcodec.calib_dev) kvc::dev_free(kcodec.calib_dev, s);
+    for (kvc_cache *child : children) delete child;
 }
 
 namespace kvc {
@@ -360,6 +361,59 @@ static void rotating_update_concat(kvc_cache *c, const kvc_tensor &k, const kvc_
     if (ov) *ov = c->v.view(c->len);
 }
 
+// ChunkedKVCache.update (KVCache.swift:1234-1269). `len` follows the reference's buffer length
+// keys.dim(2) (whole `step`s of zero rows are appended when the new rows do not fit; a buffer whose
+// fill is not a multiple of `step` is first cut back to its fill), because maybeTrimFront and the
+// state getter work on that length, zero padding included.
+static void chunked_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s) {
+    const int64_t S = k.shape[2];
+    const int64_t step = std::max<int32_t>(c->cfg.step, 1);
+    const int64_t prev = c->offset - c->start_position;
+    if (prev < 0) fail(KVC_ERR_INVALID_STATE, "chunked cache: offset is before startPosition");
+    if (!c->k.allocated() || prev + S > c->len) {
+        const int64_t n_steps = (step + S - 1) / step;
+        if (!c->k.allocated()) {
+            c->len = n_steps * step;
+            c->k.alloc(k.shape[0], k.shape[1], c->len, k.shape[3], k.dtype, s);
+            c->v.alloc(v.shape[0], v.shape[1], c->len, v.shape[3], v.dtype, s);
+        } else {
+            int64_t kept = c->len;
+            if (prev % step != 0) kept = prev;          // currentKeys[..<prev]
+            const int64_t new_len = kept + n_steps * step;
+            c->k.ensure(new_len, kept, step, s);
+            c->v.ensure(new_len, kept, step, s);
+            zero_rows(c->k, kept, new_len - kept, s);    // the appended rows are zeros in the reference
+            zero_rows(c->v, kept, new_len - kept, s);
+            c->len = new_len;
+        }
+    }
+    KVC_REQUIRE(k.shape[0] == c->k.B && k.shape[1] == c->k.H && k.shape[3] == c->k.W && v.shape[3] == c->v.W &&
+                    k.dtype == c->k.dtype,
+                "update: new keys/values do not match the cached shape or dtype");
+    if (S > 0) append_pair(c->k, c->v, k, v, prev, s);
+    c->offset += S;
+}
+
+// ChunkedKVCache.maybeTrimFront (KVCache.swift:1222-1232).
+void cache_maybe_trim_front(kvc_cache *c, cudaStream_t s) {
+    KVC_REQUIRE(c->cfg.kind == KVC_KIND_CHUNKED, "maybeTrimFront needs a ChunkedKVCache");
+    const int64_t chunk = c->cfg.max_size;
+    if (!c->k.allocated() || chunk <= 0 || c->len < chunk) return;
+    const int64_t drop = c->len - chunk;
+    c->start_position += drop;
+    if (drop > 0) {
+        std::vector<GatherSeg> keep;
+        seg_push(keep, drop, chunk);
+        ensure_like(c->k_alt, c->k, std::max<int64_t>(chunk, c->k.cap), s);
+        ensure_like(c->v_alt, c->v, std::max<int64_t>(chunk, c->v.cap), s);
+        gather_rows(c->k, c->k_alt, keep, s);
+        gather_rows(c->v, c->v_alt, keep, s);
+        std::swap(c->k, c->k_alt);
+        std::swap(c->v, c->v_alt);
+    }
+    c->len = chunk;
+}
+
 void cache_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
                   kvc_tensor *out_k, kvc_tensor *out_v) {
     require4(k, "keys");
@@ -390,6 +444,16 @@ void cache_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaSt
         case KVC_KIND_QUANTIZED:
             // KVCache.swift:1106-1110
             fail(KVC_ERR_INVALID_STATE, "`update` was called on `QuantizedKVCache`. Use `updateQuantized` instead.");
+        case KVC_KIND_CHUNKED: {
+            chunked_update(c, k, v, s);
+            const int64_t end = c->offset - c->start_position;
+            if (out_k) *out_k = c->k.view(end);
+            if (out_v) *out_v = c->v.view(end);
+            return;
+        }
+        case KVC_KIND_LIST:
+            // KVCache.swift:1576-1578
+            fail(KVC_ERR_INVALID_STATE, "CacheList should not use update(keys:values:) - use subscript access instead");
         default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
     }
 }
@@ -999,6 +1063,18 @@ int64_t cache_trim(kvc_cache *c, int64_t n) {
             }
             return t;
         }
+        case KVC_KIND_CHUNKED: {
+            // KVCache.swift:1271-1276
+            const int64_t t = std::min(c->offset - c->start_position, n);
+            c->offset -= t;
+            return t;
+        }
+        case KVC_KIND_LIST: {
+            // KVCache.swift:1653-1660: every child trims, the last child's count is returned
+            int64_t result = 0;
+            for (kvc_cache *child : c->children) result = cache_trim(child, n);
+            return result;
+        }
         default: {
             const int64_t t = std::min(c->offset, std::max<int64_t>(n, 0));
             c->offset -= t;
@@ -1009,7 +1085,25 @@ int64_t cache_trim(kvc_cache *c, int64_t n) {
 
 bool cache_is_trimmable_after(const kvc_cache *c, int64_t positions) {
     if (c->cfg.kind == KVC_KIND_ROTATING) return c->offset + positions < c->cfg.max_size;  // KVCache.swift:821-823
+    if (c->cfg.kind == KVC_KIND_LIST) {  // KVCache.swift:1645-1651
+        for (const kvc_cache *child : c->children)
+            if (!cache_is_trimmable_after(child, positions)) return false;
+        return true;
+    }
     return true;
+}
+
+const char *cache_class_name(const kvc_cache *c) {
+    // cacheClassName (KVCache.swift:1739-1751)
+    switch (c->cfg.kind) {
+        case KVC_KIND_SIMPLE: return "KVCache";
+        case KVC_KIND_ROTATING: return "RotatingKVCache";
+        case KVC_KIND_QUANTIZED: return "QuantizedKVCache";
+        case KVC_KIND_TURBO: return "TurboQuantKVCache";
+        case KVC_KIND_CHUNKED: return "ChunkedKVCache";
+        case KVC_KIND_LIST: return "CacheList";
+        default: return "KVCache";
+    }
 }
 
 // ---------------------------------------------------------------------
@@ -1017,6 +1111,12 @@ bool cache_is_trimmable_after(const kvc_cache *c, int64_t positions) {
 // ---------------------------------------------------------------------
 int cache_state_count(const kvc_cache *c) {
     switch (c->cfg.kind) {
+        case KVC_KIND_LIST: {
+            int n = 0;
+            for (const kvc_cache *child : c->children) n += cache_state_count(child);
+            return n;
+        }
+        case KVC_KIND_CHUNKED:
         case KVC_KIND_SIMPLE:
         case KVC_KIND_ROTATING: return c->k.allocated() ? 2 : 0;
         case KVC_KIND_QUANTIZED: return c->kq.allocated() ? 6 : 0;
@@ -1035,6 +1135,19 @@ kvc_tensor cache_state_get(kvc_cache *c, int index) {
     const int n = cache_state_count(c);
     if (index < 0 || index >= n) fail(KVC_ERR_INVALID_ARG, "state index out of range");
     switch (c->cfg.kind) {
+        case KVC_KIND_LIST: {
+            // state = caches.flatMap { $0.state } (KVCache.swift:1580-1581)
+            for (kvc_cache *child : c->children) {
+                const int m = cache_state_count(child);
+                if (index < m) return cache_state_get(child, index);
+                index -= m;
+            }
+            fail(KVC_ERR_INTERNAL, "CacheList state index");
+        }
+        case KVC_KIND_CHUNKED:
+            // the inherited getter slices [..<offset] with the ABSOLUTE offset (KVCache.swift:449-459); a slice
+            // past the end of the buffer clamps to it, zero padding rows included
+            return (index == 0 ? c->k : c->v).view(std::min(c->offset, c->len));
         case KVC_KIND_SIMPLE: return (index == 0 ? c->k : c->v).view(c->offset);
         case KVC_KIND_ROTATING: {
             // KVCache.swift:752-763: rows [0, offset) while the buffer is longer, else the whole ring
@@ -1092,6 +1205,24 @@ void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStre
     if (c->open_round) fail(KVC_ERR_INVALID_STATE, "state: a staged round is open on this cache");
     c->restore.valid = false;
     switch (c->cfg.kind) {
+        case KVC_KIND_LIST: {
+            // KVCache.swift:1582-1590: every child takes as many arrays as its state currently has
+            int start = 0;
+            for (kvc_cache *child : c->children) {
+                const int m = cache_state_count(child);
+                KVC_REQUIRE(start + m <= count, "CacheList state: too few arrays for the children's current state counts");
+                cache_state_set(child, arrays + start, m, s);
+                start += m;
+            }
+            return;
+        }
+        case KVC_KIND_CHUNKED:
+            KVC_REQUIRE(count == 2, "KVCacheSimple state must have exactly 2 arrays (keys, values)");
+            adopt(c->k, arrays[0], s);
+            adopt(c->v, arrays[1], s);
+            c->offset = arrays[0].shape[2];
+            c->len = arrays[0].shape[2];
+            return;
         case KVC_KIND_SIMPLE:
             KVC_REQUIRE(count == 2, "KVCacheSimple state must have exactly 2 arrays (keys, values)");
             adopt(c->k, arrays[0], s);
@@ -1165,6 +1296,19 @@ std::vector<std::string> cache_meta_state(const kvc_cache *c) {
             return {S(c->cfg.step), S(c->offset), S(c->group_size), S(c->bits)};
         case KVC_KIND_TURBO:  // TurboQuantKVCache.swift:1570-1573
             return {S(c->offset), S(c->cfg.bits), S(c->key_bits), S(c->value_bits), std::to_string(c->cfg.seed)};
+        case KVC_KIND_CHUNKED:  // KVCache.swift:1289-1293
+            return {c->cfg.max_size > 0 ? S(c->cfg.max_size) : std::string("None"), S(c->start_position)};
+        case KVC_KIND_LIST: {   // KVCache.swift:1673-1685: [childCount, (className, stateCount, metaCount, meta...)*]
+            std::vector<std::string> out{S((int64_t)c->children.size())};
+            for (const kvc_cache *child : c->children) {
+                const std::vector<std::string> meta = cache_meta_state(child);
+                out.push_back(cache_class_name(child));
+                out.push_back(S(cache_state_count(child)));
+                out.push_back(S((int64_t)meta.size()));
+                out.insert(out.end(), meta.begin(), meta.end());
+            }
+            return out;
+        }
         default: return {};
     }
 }
@@ -1214,6 +1358,19 @@ void cache_set_meta_state(kvc_cache *c, const std::vector<std::string> &m) {
             if (m.size() >= 5 && parse_int(m[0], off)) c->offset = off;  // TurboQuantKVCache.swift:1574-1579
             return;
         }
+        case KVC_KIND_CHUNKED: {
+            // KVCache.swift:1294-1303
+            KVC_REQUIRE(m.size() == 2, "ChunkedKVCache metaState must have exactly 2 values");
+            int64_t v = 0;
+            if (m[0] == "None") c->cfg.max_size = -1;
+            else if (parse_int(m[0], v)) c->cfg.max_size = (int32_t)v;
+            else c->cfg.max_size = -1;   // Int(newValue[0]) gives nil
+            c->start_position = parse_int(m[1], v) ? v : 0;
+            return;
+        }
+        case KVC_KIND_LIST:
+            // KVCache.swift:1686-1689
+            fail(KVC_ERR_INVALID_STATE, "CacheList.metaState should not be set directly. Use CacheList.fromState() instead");
         default: fail(KVC_ERR_INVALID_ARG, "unknown cache kind");
     }
 }
@@ -1231,6 +1388,13 @@ kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
     // copy() (KVCache.swift:525-533, :877-885, :1177-1185): the new object adopts
     // the `state` arrays and the metaState.
     std::unique_ptr<kvc_cache> n(new kvc_cache());
+    if (c->cfg.kind == KVC_KIND_LIST) {
+        // KVCache.swift:1592-1596
+        n->cfg = c->cfg;
+        n->device = c->device;
+        for (const kvc_cache *child : c->children) n->children.push_back(cache_copy(child, s));
+        return n.release();
+    }
     n->cfg = c->cfg;
     n->cfg.reserve_tokens = 0;
     n->device = c->device;
@@ -1242,6 +1406,14 @@ kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
     n->raw_key = c->raw_key; n->affine_key = c->affine_key; n->affine_value = c->affine_value;
     n->user_kc = c->user_kc; n->user_vc = c->user_vc; n->user_ks = c->user_ks; n->user_vs = c->user_vs;
     int64_t rows = c->offset;
+    if (c->cfg.kind == KVC_KIND_CHUNKED) {
+        // KVCache.swift:1278-1287: the copy adopts `state` (rows up to the absolute offset, clamped to the
+        // buffer) and then the metaState; its offset becomes the adopted row count
+        rows = c->k.allocated() ? std::min(c->offset, c->len) : 0;
+        n->offset = c->k.allocated() ? rows : 0;
+        n->len = rows;
+        n->start_position = c->start_position;
+    }
     if (c->cfg.kind == KVC_KIND_ROTATING) {
         rows = c->offset < c->len ? std::max<int64_t>(c->offset, 0) : c->len;
         n->len = c->k.allocated() ? rows : 0;

@@ -67,6 +67,10 @@ struct kvc_cache {
     int64_t len = 0;   // the reference's keys.dim(2)
     int64_t idx = 0;
     std::string origin = "modelNative";
+    // chunked: ChunkedKVCache.startPosition (KVCache.swift:1215); `len` is the reference's keys.dim(2)
+    int64_t start_position = 0;
+    // list: CacheList children (owned)
+    std::vector<kvc_cache *> children;
     kvc::Array4 k_alt, v_alt;       // ping-pong target for re-order / trim
     kvc::Array4 k_view, v_view;     // scratch for logical views
     kvc::RestorePoint restore;
@@ -136,6 +140,8 @@ kvc_cache *cache_to_unquantized(const kvc_cache *c, cudaStream_t s);
 void cache_turbo_encode_new_token(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s);
 kvc_cache *cache_to_turbo(const kvc_cache *c, int kb, int vb, int kg, cudaStream_t s);
 void cache_logical_view(kvc_cache *c, int64_t tail, cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov);
+void cache_maybe_trim_front(kvc_cache *c, cudaStream_t s);
+const char *cache_class_name(const kvc_cache *c);
 void cache_make_mask(const kvc_cache *c, int n, int64_t window, bool return_array, int32_t *mode,
                      int64_t *rows, int64_t *cols, void *out_mask, cudaStream_t s);
 int resolved_group_size(int requested, int kd, int vd);  // 0 when none fits

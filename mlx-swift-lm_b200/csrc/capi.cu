@@ -151,7 +151,8 @@ kvc_status kvc_create(const kvc_config *cfg, kvc_cache **out) {
     if (!cfg || !out) return set_error(KVC_ERR_INVALID_ARG, "kvc_create: null argument");
     *out = nullptr;
     return guarded([&] {
-        KVC_REQUIRE(cfg->kind >= KVC_KIND_SIMPLE && cfg->kind <= KVC_KIND_TURBO, "kvc_create: unknown kind");
+        KVC_REQUIRE(cfg->kind >= KVC_KIND_SIMPLE && cfg->kind <= KVC_KIND_CHUNKED,
+                    "kvc_create: unknown kind (a CacheList is made by kvc_list_create)");
         KVC_REQUIRE(cfg->step > 0, "kvc_create: step must be positive");
         std::unique_ptr<kvc_cache> c(new kvc_cache());
         c->cfg = *cfg;
@@ -192,6 +193,71 @@ void kvc_free(kvc_cache *cache) {
         delete cache;
     } catch (...) {
     }
+}
+
+kvc_status kvc_list_create(kvc_cache *const *children, int32_t count, kvc_cache **out) {
+    if (!out || (count > 0 && !children)) return set_error(KVC_ERR_INVALID_ARG, "kvc_list_create: null argument");
+    *out = nullptr;
+    return guarded([&] {
+        KVC_REQUIRE(count >= 0, "kvc_list_create: negative count");
+        for (int i = 0; i < count; ++i) {
+            KVC_REQUIRE(children[i] != nullptr, "kvc_list_create: null child");
+            for (int j = 0; j < i; ++j) KVC_REQUIRE(children[i] != children[j], "kvc_list_create: a child appears twice");
+        }
+        std::unique_ptr<kvc_cache> c(new kvc_cache());
+        kvc_config_default(&c->cfg, KVC_KIND_LIST);
+        c->device = count > 0 ? children[0]->device : -1;
+        c->children.assign(children, children + count);
+        *out = c.release();
+    });
+}
+
+int32_t kvc_list_count(const kvc_cache *list) {
+    return (list && list->cfg.kind == KVC_KIND_LIST) ? (int32_t)list->children.size() : -1;
+}
+
+kvc_cache *kvc_list_child(const kvc_cache *list, int32_t index) {
+    if (!list || list->cfg.kind != KVC_KIND_LIST || index < 0 || index >= (int32_t)list->children.size()) return nullptr;
+    return list->children[(size_t)index];
+}
+
+kvc_status kvc_maybe_trim_front(kvc_cache *c, void *stream) {
+    KVC_CHECK_HANDLE(c);
+    return guarded([&] {
+        DeviceGuard dg(c->device);
+        kvc::cache_maybe_trim_front(c, as_stream(stream));
+    });
+}
+
+int64_t kvc_start_position(const kvc_cache *c) { return (c && c->cfg.kind == KVC_KIND_CHUNKED) ? c->start_position : 0; }
+
+kvc_status kvc_prepare(kvc_cache *c, const int32_t *lengths, int32_t count) {
+    KVC_CHECK_HANDLE(c);
+    (void)lengths; (void)count;   // BaseKVCache.prepare(lengths:) is empty for these cache kinds (KVCache.swift:229-231)
+    if (c->cfg.kind == KVC_KIND_LIST)
+        for (kvc_cache *child : c->children) (void)kvc_prepare(child, lengths, count);
+    return KVC_OK;
+}
+
+kvc_status kvc_finalize(kvc_cache *c) {
+    KVC_CHECK_HANDLE(c);
+    if (c->cfg.kind == KVC_KIND_LIST)
+        for (kvc_cache *child : c->children) (void)kvc_finalize(child);
+    return KVC_OK;
+}
+
+kvc_status kvc_create_causal_mask(int32_t n, int64_t offset, int64_t window_size, const int32_t *lengths_dev, int32_t batch,
+                                  void *out_mask, void *stream) {
+    if (!out_mask) return set_error(KVC_ERR_INVALID_ARG, "kvc_create_causal_mask: null output");
+    return guarded([&] {
+        KVC_REQUIRE(n >= 0 && offset >= 0, "kvc_create_causal_mask: negative size");
+        if (lengths_dev) {
+            KVC_REQUIRE(batch > 0, "kvc_create_causal_mask: lengths need a batch size");
+            kvc::launch_causal_mask_lengths((uint8_t *)out_mask, n, offset, window_size, lengths_dev, batch, as_stream(stream));
+        } else {
+            kvc::launch_causal_mask((uint8_t *)out_mask, n, offset, window_size, as_stream(stream));
+        }
+    });
 }
 
 int64_t kvc_offset(const kvc_cache *c) { return c ? c->offset : -1; }

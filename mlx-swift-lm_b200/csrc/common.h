@@ -251,6 +251,8 @@ int launch_attention(const AttnArgs &a, cudaStream_t stream);
 // rolled single-token window mask of a wrapped rotating cache.
 void launch_causal_mask(uint8_t *out, int64_t n, int64_t offset, int64_t window, cudaStream_t s);
 void launch_rolled_mask(uint8_t *out, int64_t size, int64_t window, int64_t shift, cudaStream_t s);
+void launch_causal_mask_lengths(uint8_t *out, int64_t n, int64_t offset, int64_t window, const int32_t *lengths,
+                                int64_t batch, cudaStream_t s);
 
 // Count of kernels launched by this library on the calling thread since the
 // last reset (benchmarks report it).

@@ -175,6 +175,8 @@ const char *class_name(int32_t kind) {
         case KVC_KIND_ROTATING: return "RotatingKVCache";
         case KVC_KIND_QUANTIZED: return "QuantizedKVCache";
         case KVC_KIND_TURBO: return "TurboQuantKVCache";
+        case KVC_KIND_CHUNKED: return "ChunkedKVCache";
+        case KVC_KIND_LIST: return "CacheList";
         default: fail(KVC_ERR_UNSUPPORTED, "prompt cache: unknown cache kind");
     }
 }
@@ -206,6 +208,95 @@ struct FileCloser {
     FILE *f;
     ~FileCloser() { if (f) std::fclose(f); }
 };
+
+// restoreCacheFromMetaState (KVCache.swift:2031-2138): a cache of class `cls` from its state arrays
+// (device tensors, copied) and metaState strings. CacheList recurses (CacheList.fromState :1689-1725).
+kvc_cache *restore_cache(const std::string &cls, const std::vector<kvc_tensor> &tens, const std::vector<std::string> &ms,
+                         int device, cudaStream_t s) {
+    auto require_counts = [&](const char *name, std::initializer_list<size_t> sc, std::initializer_list<size_t> mc) {
+        bool s_ok = false, m_ok = false;
+        for (size_t x : sc) s_ok = s_ok || tens.size() == x;
+        for (size_t x : mc) m_ok = m_ok || ms.size() == x;
+        if (!s_ok) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: ") + name + " has " + std::to_string(tens.size()) + " state arrays.");
+        for (const kvc_tensor &t : tens)
+            if (t.ndim != 4) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: invalid ") + name + " state shape.");
+        if (!m_ok) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: ") + name + " has " + std::to_string(ms.size()) + " metadata entries.");
+    };
+    if (cls.rfind("__mlx_lm_state", 0) == 0) fail(KVC_ERR_UNSUPPORTED, "Prompt cache contains model state; this library restores caches only");
+    if (cls == "CacheList") {
+        if (ms.empty()) fail(KVC_ERR_INVALID_ARG, "CacheList metaState missing child count");
+        const int64_t child_count = parse_int(ms[0], "CacheList");
+        std::vector<kvc_cache *> children;
+        struct Guard { std::vector<kvc_cache *> &v; bool armed = true; ~Guard() { if (armed) for (kvc_cache *c : v) kvc_free(c); } } guard{children};
+        size_t mi = 1, si = 0;
+        for (int64_t k = 0; k < child_count; ++k) {
+            if (mi + 2 >= ms.size()) fail(KVC_ERR_INVALID_ARG, "CacheList metaState truncated");
+            const std::string child_cls = ms[mi];
+            const int64_t state_count = parse_int(ms[mi + 1], "CacheList");
+            const int64_t meta_count = parse_int(ms[mi + 2], "CacheList");
+            mi += 3;
+            std::vector<std::string> child_meta;
+            for (int64_t j = 0; j < meta_count && mi + (size_t)j < ms.size(); ++j) child_meta.push_back(ms[mi + (size_t)j]);
+            mi += (size_t)meta_count;
+            std::vector<kvc_tensor> child_state;
+            for (int64_t j = 0; j < state_count && si + (size_t)j < tens.size(); ++j) child_state.push_back(tens[si + (size_t)j]);
+            si += (size_t)state_count;
+            children.push_back(restore_cache(child_cls, child_state, child_meta, device, s));
+        }
+        kvc_cache *list = nullptr;
+        must(kvc_list_create(children.data(), (int32_t)children.size(), &list));
+        guard.armed = false;   // the list owns them now
+        return list;
+    }
+    kvc_config cfg;
+    bool set_meta = true;
+    if (cls == "KVCache" || cls == "KVCacheSimple") {
+        require_counts("KVCacheSimple", {0, 2}, {1});
+        if (!ms[0].empty()) fail(KVC_ERR_INVALID_ARG, "Corrupt prompt cache: KVCacheSimple metadata must contain its single empty placeholder.");
+        kvc_config_default(&cfg, KVC_KIND_SIMPLE);
+        set_meta = false;
+    } else if (cls == "RotatingKVCache") {
+        require_counts("RotatingKVCache", {0, 2}, {5, 6});
+        for (int j = 0; j < 5; ++j) (void)parse_int(ms[(size_t)j], "RotatingKVCache");
+        kvc_config_default(&cfg, KVC_KIND_ROTATING);
+        cfg.max_size = parse_int(ms[1], "RotatingKVCache");
+    } else if (cls == "QuantizedKVCache") {
+        require_counts("QuantizedKVCache", {0, 4, 6}, {4});
+        for (const std::string &m : ms) (void)parse_int(m, "QuantizedKVCache");
+        kvc_config_default(&cfg, KVC_KIND_QUANTIZED);
+        cfg.group_size = (int32_t)parse_int(ms[2], "QuantizedKVCache");
+        cfg.bits = (int32_t)parse_int(ms[3], "QuantizedKVCache");
+    } else if (cls == "ChunkedKVCache") {
+        require_counts("ChunkedKVCache", {0, 2}, {2});
+        kvc_config_default(&cfg, KVC_KIND_CHUNKED);
+        cfg.max_size = ms[0] == "None" ? -1 : (int32_t)parse_int(ms[0], "ChunkedKVCache");
+        (void)parse_int(ms[1], "ChunkedKVCache");
+    } else if (cls == "TurboQuantKVCache") {
+        if (ms.size() < 5) fail(KVC_ERR_INVALID_ARG, "Invalid TurboQuantKVCache metaState");
+        kvc_config_default(&cfg, KVC_KIND_TURBO);
+        cfg.bits = (int32_t)parse_int(ms[1], "TurboQuantKVCache");
+        cfg.key_bits = (int32_t)parse_int(ms[2], "TurboQuantKVCache");
+        cfg.value_bits = (int32_t)parse_int(ms[3], "TurboQuantKVCache");
+        cfg.seed = (uint64_t)std::strtoull(ms[4].c_str(), nullptr, 10);
+    } else {
+        fail(KVC_ERR_UNSUPPORTED, "Unknown cache class: " + cls);
+    }
+    cfg.device = device;
+    kvc_cache *c = nullptr;
+    must(kvc_create(&cfg, &c));
+    struct One { kvc_cache *c; bool armed = true; ~One() { if (armed) kvc_free(c); } } one{c};
+    if (!tens.empty()) must(kvc_state_set(c, tens.data(), (int32_t)tens.size(), (void *)s));
+    if (set_meta) {
+        std::string joined;
+        for (size_t j = 0; j < ms.size(); ++j) {
+            if (j) joined += '\n';
+            joined += ms[j];
+        }
+        must(kvc_set_meta_state(c, joined.c_str()));
+    }
+    one.armed = false;
+    return c;
+}
 
 }  // namespace
 
@@ -354,90 +445,40 @@ void load_prompt_cache(const char *path, int device, std::vector<kvc_cache *> &o
         for (size_t j = 0; j < tens.size(); ++j)
             if (tens[j].j != (int)j) fail(KVC_ERR_INVALID_ARG, "Corrupt prompt cache: state arrays are not contiguous");
         const std::vector<std::string> &ms = meta_state[i];
-        auto require_counts = [&](const char *name, std::initializer_list<size_t> sc, std::initializer_list<size_t> mc) {
-            bool s_ok = false, m_ok = false;
-            for (size_t x : sc) s_ok = s_ok || tens.size() == x;
-            for (size_t x : mc) m_ok = m_ok || ms.size() == x;
-            if (!s_ok) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: ") + name + " has " + std::to_string(tens.size()) + " state arrays.");
-            for (const Ten &t : tens)
-                if (t.shape.size() != 4) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: invalid ") + name + " state shape.");
-            if (!m_ok) fail(KVC_ERR_INVALID_ARG, std::string("Corrupt prompt cache: ") + name + " has " + std::to_string(ms.size()) + " metadata entries.");
-        };
-        kvc_config cfg;
-        bool set_meta = true;
-        if (cls == "KVCache" || cls == "KVCacheSimple") {
-            require_counts("KVCacheSimple", {0, 2}, {1});
-            if (!ms[0].empty()) fail(KVC_ERR_INVALID_ARG, "Corrupt prompt cache: KVCacheSimple metadata must contain its single empty placeholder.");
-            kvc_config_default(&cfg, KVC_KIND_SIMPLE);
-            set_meta = false;
-        } else if (cls == "RotatingKVCache") {
-            require_counts("RotatingKVCache", {0, 2}, {5, 6});
-            for (int j = 0; j < 5; ++j) (void)parse_int(ms[(size_t)j], "RotatingKVCache");
-            kvc_config_default(&cfg, KVC_KIND_ROTATING);
-            cfg.max_size = parse_int(ms[1], "RotatingKVCache");
-        } else if (cls == "QuantizedKVCache") {
-            require_counts("QuantizedKVCache", {0, 4, 6}, {4});
-            for (const std::string &m : ms) (void)parse_int(m, "QuantizedKVCache");
-            kvc_config_default(&cfg, KVC_KIND_QUANTIZED);
-            cfg.group_size = (int32_t)parse_int(ms[2], "QuantizedKVCache");
-            cfg.bits = (int32_t)parse_int(ms[3], "QuantizedKVCache");
-        } else if (cls == "TurboQuantKVCache") {
-            if (ms.size() < 5) fail(KVC_ERR_INVALID_ARG, "Invalid TurboQuantKVCache metaState");
-            kvc_config_default(&cfg, KVC_KIND_TURBO);
-            cfg.bits = (int32_t)parse_int(ms[1], "TurboQuantKVCache");
-            cfg.key_bits = (int32_t)parse_int(ms[2], "TurboQuantKVCache");
-            cfg.value_bits = (int32_t)parse_int(ms[3], "TurboQuantKVCache");
-            cfg.seed = (uint64_t)std::strtoull(ms[4].c_str(), nullptr, 10);
-        } else {
-            fail(KVC_ERR_UNSUPPORTED, "Unknown cache class: " + cls);
-        }
-        cfg.device = device;
-        kvc_cache *c = nullptr;
-        must(kvc_create(&cfg, &c));
-        out.push_back(c);
-        if (!tens.empty()) {
-            std::vector<void *> dev_bufs;
-            std::vector<kvc_tensor> descs;
-            struct Free { std::vector<void *> &b; ~Free() { for (void *p : b) cudaFree(p); } } freer{dev_bufs};
-            for (const Ten &t : tens) {
-                kvc_tensor d = {};
-                d.dtype = t.dtype;
-                d.ndim = (int32_t)t.shape.size();
-                if (d.ndim < 1 || d.ndim > 5) fail(KVC_ERR_INVALID_ARG, "prompt cache: tensor rank out of range");
-                size_t elems = 1;
-                for (int k = 0; k < d.ndim; ++k) {
-                    d.shape[k] = t.shape[(size_t)k];
-                    elems *= (size_t)t.shape[(size_t)k];
-                }
-                int64_t stride = 1;
-                for (int k = d.ndim - 1; k >= 0; --k) {
-                    d.stride[k] = stride;
-                    stride *= d.shape[k];
-                }
-                const size_t bytes = elems * dtype_size(t.dtype);
-                if (t.b < t.a || t.b - t.a != bytes) fail(KVC_ERR_INVALID_ARG, "Corrupt prompt cache: tensor size does not match its shape");
-                std::vector<char> host(bytes);
-                if (std::fseek(fc.f, (long)(8 + hlen + t.a), SEEK_SET) != 0 || (bytes && std::fread(host.data(), 1, bytes, fc.f) != bytes))
-                    fail(KVC_ERR_INVALID_ARG, "prompt cache: truncated tensor data");
-                void *dp = nullptr;
-                KVC_CUDA(cudaMalloc(&dp, bytes ? bytes : 16));
-                dev_bufs.push_back(dp);
-                KVC_CUDA(cudaMemcpyAsync(dp, host.data(), bytes, cudaMemcpyHostToDevice, s));
-                KVC_CUDA(cudaStreamSynchronize(s));   // `host` goes out of scope
-                d.data = dp;
-                descs.push_back(d);
+        // the entry's arrays, on the device for the duration of the restore
+        std::vector<void *> dev_bufs;
+        std::vector<kvc_tensor> descs;
+        struct Free { std::vector<void *> &b; ~Free() { for (void *p : b) cudaFree(p); } } freer{dev_bufs};
+        for (const Ten &t : tens) {
+            kvc_tensor d = {};
+            d.dtype = t.dtype;
+            d.ndim = (int32_t)t.shape.size();
+            if (d.ndim < 1 || d.ndim > 5) fail(KVC_ERR_INVALID_ARG, "prompt cache: tensor rank out of range");
+            size_t elems = 1;
+            for (int k = 0; k < d.ndim; ++k) {
+                d.shape[k] = t.shape[(size_t)k];
+                elems *= (size_t)t.shape[(size_t)k];
             }
-            must(kvc_state_set(c, descs.data(), (int32_t)descs.size(), (void *)s));
-            KVC_CUDA(cudaStreamSynchronize(s));
-        }
-        if (set_meta) {
-            std::string joined;
-            for (size_t j = 0; j < ms.size(); ++j) {
-                if (j) joined += '\n';
-                joined += ms[j];
+            int64_t stride = 1;
+            for (int k = d.ndim - 1; k >= 0; --k) {
+                d.stride[k] = stride;
+                stride *= d.shape[k];
             }
-            must(kvc_set_meta_state(c, joined.c_str()));
+            const size_t bytes = elems * dtype_size(t.dtype);
+            if (t.b < t.a || t.b - t.a != bytes) fail(KVC_ERR_INVALID_ARG, "Corrupt prompt cache: tensor size does not match its shape");
+            std::vector<char> host(bytes);
+            if (std::fseek(fc.f, (long)(8 + hlen + t.a), SEEK_SET) != 0 || (bytes && std::fread(host.data(), 1, bytes, fc.f) != bytes))
+                fail(KVC_ERR_INVALID_ARG, "prompt cache: truncated tensor data");
+            void *dp = nullptr;
+            KVC_CUDA(cudaMalloc(&dp, bytes ? bytes : 16));
+            dev_bufs.push_back(dp);
+            KVC_CUDA(cudaMemcpyAsync(dp, host.data(), bytes, cudaMemcpyHostToDevice, s));
+            KVC_CUDA(cudaStreamSynchronize(s));   // `host` goes out of scope
+            d.data = dp;
+            descs.push_back(d);
         }
+        out.push_back(restore_cache(cls, descs, ms, device, s));
+        if (!descs.empty()) KVC_CUDA(cudaStreamSynchronize(s));   // the staging buffers are freed at the end of the iteration
     }
     cleanup.armed = false;
 }

@@ -27,7 +27,7 @@ _lib = ctypes.CDLL(LIB_PATH)
 
 KVC_MAX_DIMS = 5
 F32, F16, BF16, U32, BOOL = 0, 1, 2, 3, 4
-KIND_SIMPLE, KIND_ROTATING, KIND_QUANTIZED, KIND_TURBO = 0, 1, 2, 3
+KIND_SIMPLE, KIND_ROTATING, KIND_QUANTIZED, KIND_TURBO, KIND_CHUNKED, KIND_LIST = 0, 1, 2, 3, 4, 5
 MASK_NONE, MASK_CAUSAL, MASK_ARRAY = 0, 1, 2
 
 OK = 0
@@ -149,6 +149,16 @@ _lib.kvc_turbo_set_codec.argtypes = [_vp] + [ctypes.POINTER(ctypes.c_float)] * 4
 _lib.kvc_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int64,
                                        ctypes.POINTER(ctypes.c_int64)]
 _lib.kvc_can_trim_prompt_cache.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32]
+_lib.kvc_list_create.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.POINTER(_vp)]
+_lib.kvc_list_count.argtypes = [_vp]
+_lib.kvc_list_child.argtypes = [_vp, ctypes.c_int32]
+_lib.kvc_list_child.restype = _vp
+_lib.kvc_maybe_trim_front.argtypes = [_vp, _vp]
+_lib.kvc_start_position.argtypes = [_vp]
+_lib.kvc_start_position.restype = ctypes.c_int64
+_lib.kvc_prepare.argtypes = [_vp, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]
+_lib.kvc_finalize.argtypes = [_vp]
+_lib.kvc_create_causal_mask.argtypes = [ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int32, _vp, _vp]
 _lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
 _lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
 _lib.kvc_comm_symm_alloc.argtypes = [_vp, ctypes.c_size_t, _vp, ctypes.POINTER(_vp)]
@@ -320,6 +330,15 @@ class KVCache:
         m = int(_lib.kvc_max_size(self._h))
         return None if m < 0 else m
 
+    def prepare(self, lengths=None) -> None:
+        """prepare(lengths:): the reference's empty default for these cache kinds (KVCache.swift:229-231)."""
+        n = 0 if lengths is None else len(lengths)
+        arr = (ctypes.c_int32 * max(n, 1))(*(list(lengths) if lengths is not None else []))
+        check(_lib.kvc_prepare(self._h, arr, n))
+
+    def finalize(self) -> None:
+        check(_lib.kvc_finalize(self._h))
+
     def update(self, keys, values, stream=None):
         ok, ov = Tensor(), Tensor()
         tk, tv = as_tensor(keys), as_tensor(values)
@@ -460,6 +479,47 @@ class KVCacheSimple(KVCache):
         return new
 
 
+class ChunkedKVCache(KVCache):
+    """ChunkedKVCache(chunkSize:) (KVCache.swift:1213-1304)."""
+
+    def __init__(self, chunk_size: Optional[int] = None, step: int = 256):
+        super().__init__(self._create(self._config(KIND_CHUNKED, max_size=-1 if chunk_size is None else chunk_size,
+                                                   step=step)))
+
+    def maybe_trim_front(self, stream=None) -> None:
+        check(_lib.kvc_maybe_trim_front(self._h, _stream_ptr(stream)))
+
+    @property
+    def start_position(self) -> int:
+        return int(_lib.kvc_start_position(self._h))
+
+
+class CacheList(KVCache):
+    """CacheList(caches...) (KVCache.swift:1556-1726). The list owns its children: the Python objects
+    passed in give their handles up and must not be used afterwards; use list[i]."""
+
+    def __init__(self, *caches: "KVCache"):
+        n = len(caches)
+        arr = (_vp * max(n, 1))(*[c._h for c in caches])
+        h = ctypes.c_void_p()
+        check(_lib.kvc_list_create(arr, n, ctypes.byref(h)))
+        dev = None
+        for c in caches:
+            dev = dev or c._device
+            c._h = None                      # ownership moved into the list
+        super().__init__(h.value, dev)
+        self._kinds = [type(c) for c in caches]
+
+    def __len__(self) -> int:
+        return int(_lib.kvc_list_count(self._h))
+
+    def __getitem__(self, i: int) -> "KVCache":
+        h = _lib.kvc_list_child(self._h, i)
+        if not h:
+            raise IndexError(i)
+        return _borrowed(h, self._device, self)
+
+
 class RotatingKVCache(KVCache):
     def __init__(self, max_size: int, keep: int = 0, step: int = 256):
         super().__init__(self._create(self._config(KIND_ROTATING, max_size=max_size, keep=keep, step=step)))
@@ -590,6 +650,36 @@ class StagedRound:
 # ---------------------------------------------------------------------------
 # free functions
 # ---------------------------------------------------------------------------
+
+def _borrowed(handle: int, device, owner) -> "KVCache":
+    """A view object on a handle owned by something else (a CacheList child): never frees it."""
+    kind = int(_lib.kvc_kind_of(ctypes.c_void_p(handle)))
+    cls = {KIND_SIMPLE: KVCacheSimple, KIND_ROTATING: RotatingKVCache, KIND_QUANTIZED: QuantizedKVCache,
+           KIND_TURBO: TurboQuantKVCache, KIND_CHUNKED: ChunkedKVCache, KIND_LIST: CacheList}.get(kind, KVCache)
+    obj = object.__new__(cls)
+    KVCache.__init__(obj, handle, device)
+    obj._owner = owner          # keeps the owning list alive
+    obj.__class__ = type("Borrowed" + cls.__name__, (cls,), {"__del__": lambda self: None})
+    return obj
+
+
+def create_causal_mask(n: int, offset: int, window_size: Optional[int] = None, lengths=None, device=None, stream=None):
+    """createCausalMask(n:offset:windowSize:lengths:) (KVCache.swift:253-275) as a bool tensor on the device:
+    [n, offset + n], or [B, 1, n, offset + n] when `lengths` (a sequence of B ints or an int32 device tensor) is given."""
+    torch = _torch()
+    dev = device if device is not None else torch.device("cuda")
+    ws = -1 if window_size is None else window_size
+    if lengths is None:
+        out = torch.empty((n, offset + n), dtype=torch.uint8, device=dev)
+        check(_lib.kvc_create_causal_mask(n, offset, ws, None, 0, out.data_ptr(), _stream_ptr(stream)))
+        return out.bool()
+    ln = lengths if hasattr(lengths, "data_ptr") else torch.tensor(list(lengths), dtype=torch.int32, device=dev)
+    ln = ln.to(dtype=torch.int32, device=dev).contiguous()
+    B = int(ln.numel())
+    out = torch.empty((B, 1, n, offset + n), dtype=torch.uint8, device=dev)
+    check(_lib.kvc_create_causal_mask(n, offset, ws, ln.data_ptr(), B, out.data_ptr(), _stream_ptr(stream)))
+    return out.bool()
+
 
 def attention_with_cache_update(queries, keys, values, cache: Optional[KVCache], scale: float, mask="none"):
     """attentionWithCacheUpdate(queries:keys:values:cache:scale:mask:)."""
@@ -925,7 +1015,7 @@ def load_prompt_cache(path: str, device: int = -1, stream=None):
         h = int(ctypes.cast(arr[i], ctypes.c_void_p).value)
         kind = int(_lib.kvc_kind_of(ctypes.c_void_p(h)))
         cls = {KIND_SIMPLE: KVCacheSimple, KIND_ROTATING: RotatingKVCache, KIND_QUANTIZED: QuantizedKVCache,
-               KIND_TURBO: TurboQuantKVCache}[kind]
+               KIND_TURBO: TurboQuantKVCache, KIND_CHUNKED: ChunkedKVCache, KIND_LIST: CacheList}[kind]
         obj = cls.__new__(cls)
         KVCache.__init__(obj, h, torch_dev)
         caches.append(obj)

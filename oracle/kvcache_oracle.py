@@ -417,12 +417,18 @@ def use_all_host_threads() -> int:
 # masks (KVCache.swift:253-275)
 # ---------------------------------------------------------------------------
 
-def create_causal_mask(n: int, offset: int, window_size: Optional[int] = None) -> np.ndarray:
-    rinds = np.arange(offset + n, dtype=np.int64)[None, :]
-    linds = np.arange(offset, offset + n, dtype=np.int64)[:, None]
+def create_causal_mask(n: int, offset: int, window_size: Optional[int] = None, lengths=None) -> np.ndarray:
+    """createCausalMask (KVCache.swift:253-275): [n, offset + n] bool, or [B, 1, n, offset + n] with `lengths`."""
+    rinds = np.arange(offset + n, dtype=np.int32)
+    linds = np.arange(offset, offset + n, dtype=np.int32) if offset != 0 else rinds
+    linds = linds[:, None]
+    rinds = rinds[None]
     mask = linds >= rinds
     if window_size is not None:
         mask = mask & (linds < rinds + window_size)
+    if lengths is not None:
+        ln = np.asarray(lengths, dtype=np.int32)[:, None, None, None]
+        mask = mask & (rinds < ln)
     return mask
 
 
@@ -538,6 +544,127 @@ class KVCacheSimple(BaseKVCache):
         q = QuantizedKVCache(group_size=group_size, bits=bits)
         q.offset = self.offset
         return q
+
+
+class ChunkedKVCache(KVCacheSimple):
+    """ChunkedKVCache (KVCache.swift:1213-1304): a KVCacheSimple whose front can be dropped."""
+
+    def __init__(self, chunk_size: Optional[int] = None, step: int = 256):
+        super().__init__(step)
+        self.chunk_size = chunk_size
+        self.start_position = 0
+
+    def maybe_trim_front(self):
+        if self.keys is None or self.chunk_size is None or self.keys.shape[2] < self.chunk_size:
+            return
+        self.start_position += self.keys.shape[2] - self.chunk_size
+        self.keys = self.keys[:, :, -self.chunk_size:]
+        self.values = self.values[:, :, -self.chunk_size:]
+
+    def update(self, keys, values):
+        prev = self.offset - self.start_position
+        S = keys.shape[2]
+        if self.keys is None or prev + S > self.keys.shape[2]:
+            B, H, _, kd = keys.shape
+            n_steps = (self.step + S - 1) // self.step
+            new_k = _zeros((B, H, n_steps * self.step, kd), keys)
+            new_v = _zeros((B, H, n_steps * self.step, values.shape[3]), values)
+            if self.keys is not None:
+                ck, cv = self.keys, self.values
+                if prev % self.step != 0:
+                    ck, cv = ck[:, :, :prev], cv[:, :, :prev]
+                self.keys = np.concatenate([ck, new_k], axis=2)
+                self.values = np.concatenate([cv, new_v], axis=2)
+            else:
+                self.keys, self.values = new_k, new_v
+        self.offset += S
+        end = self.offset - self.start_position
+        self.keys[:, :, prev:end] = keys
+        self.values[:, :, prev:end] = values
+        return self.keys[:, :, :end], self.values[:, :, :end]
+
+    def trim(self, n: int) -> int:
+        t = min(self.offset - self.start_position, n)
+        self.offset -= t
+        return t
+
+    @property
+    def meta_state(self) -> List[str]:
+        return ["None" if self.chunk_size is None else str(self.chunk_size), str(self.start_position)]
+
+    @meta_state.setter
+    def meta_state(self, m: Sequence[str]):
+        assert len(m) == 2, "ChunkedKVCache metaState must have exactly 2 values"
+        self.chunk_size = None if m[0] == "None" else int(m[0])
+        self.start_position = int(m[1])
+
+    def copy(self) -> "ChunkedKVCache":
+        new = ChunkedKVCache(self.chunk_size, self.step)
+        s = self.state
+        if s:
+            new.state = [a.copy() for a in s]
+        new.meta_state = self.meta_state
+        return new
+
+
+class CacheList(BaseKVCache):
+    """CacheList (KVCache.swift:1556-1726): a composite of child caches."""
+
+    def __init__(self, *caches):
+        super().__init__()
+        self.caches = list(caches)
+
+    def __getitem__(self, i):
+        return self.caches[i]
+
+    def update(self, keys, values):
+        raise RuntimeError("CacheList should not use update(keys:values:) - use subscript access instead")
+
+    @property
+    def state(self) -> List[np.ndarray]:
+        return [a for c in self.caches for a in c.state]
+
+    @state.setter
+    def state(self, arrays):
+        lengths = [len(c.state) for c in self.caches]
+        start = 0
+        for c, n in zip(self.caches, lengths):
+            c.state = list(arrays[start:start + n])
+            start += n
+
+    def copy(self) -> "CacheList":
+        return CacheList(*[c.copy() for c in self.caches])
+
+    @property
+    def is_trimmable(self) -> bool:
+        return self.is_trimmable_after(0)
+
+    def is_trimmable_after(self, positions: int) -> bool:
+        return all(c.is_trimmable_after(positions) for c in self.caches)
+
+    def trim(self, n: int) -> int:
+        result = 0
+        for c in self.caches:
+            result = c.trim(n)
+        return result
+
+    @property
+    def meta_state(self) -> List[str]:
+        out = [str(len(self.caches))]
+        for c in self.caches:
+            meta = list(c.meta_state)
+            out += [class_name(c), str(len(c.state)), str(len(meta))] + meta
+        return out
+
+
+def class_name(cache) -> str:
+    """cacheClassName (KVCache.swift:1739-1751)."""
+    for cls, name in ((ChunkedKVCache, "ChunkedKVCache"), (RotatingKVCache, "RotatingKVCache"),
+                      (QuantizedKVCache, "QuantizedKVCache"), (TurboQuantKVCache, "TurboQuantKVCache"),
+                      (KVCacheSimple, "KVCache"), (CacheList, "CacheList")):
+        if isinstance(cache, cls):
+            return name
+    return "KVCache"
 
 
 class RotatingKVCache(BaseKVCache):
