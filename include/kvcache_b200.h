@@ -395,6 +395,63 @@ kvc_status kvc_rewind_last_round(kvc_cache *cache, int64_t count, void *stream,
 void       kvc_round_free(kvc_round *round);
 
 /* ------------------------------------------------------------------ */
+/* the caller's step around the cache: rotary positions at the cache     */
+/* offset, speculative rounds over a layer list                          */
+/* ------------------------------------------------------------------ */
+
+/* Parameters of the rotary embedding the models construct (MLXNN.RoPE as used at
+ * MLXLLM/Models/Llama.swift:36-41): the first `dims` features of every head are rotated,
+ * pairs (i, i + dims/2) or, when `traditional`, (2i, 2i+1); angle of pair i at position p is
+ * p * scale * base^(-2i/dims). */
+typedef struct kvc_rope_config {
+    int32_t dims;         /* rotated features per head (even, <= head dim) */
+    int32_t traditional;  /* 1 = interleaved pairs */
+    float   base;         /* 10000 */
+    float   scale;        /* 1 */
+} kvc_rope_config;
+
+/* applyRotaryPosition(rope, to: x, offset:)  MLXLMCommon/RoPEApplication.swift:58-69.
+ * x, out: [B, H, L, D] (inner stride 1; out may alias x). Row l gets position offset + l. */
+kvc_status kvc_rope(const kvc_tensor *x, int64_t offset, const kvc_rope_config *rope,
+                    const kvc_tensor *out, void *stream);
+
+/* The attention block's cache step as the models write it (MLXLLM/Models/Llama.swift:58-69):
+ *   offset  = cache.ropeOffset            (the cache offset; 0 without a cache)
+ *   queries = applyRotaryPosition(rope, to: queries, offset: offset)
+ *   keys    = applyRotaryPosition(rope, to: keys,    offset: offset)
+ *   out     = attentionWithCacheUpdate(queries, keys, values, cache, scale, mask)
+ * Queries and keys are rotated by ONE launch into buffers the handle keeps, then the
+ * fused update + attention runs on them; the inputs are not modified. */
+kvc_status kvc_attention_rope(kvc_cache *cache, const kvc_tensor *queries, const kvc_tensor *keys,
+                              const kvc_tensor *values, const kvc_rope_config *rope, float scale,
+                              int32_t mask_mode, const kvc_tensor *mask, const kvc_tensor *out,
+                              void *stream);
+
+/* A speculative round over the layer list of a model (KVCacheStorage.beginRound / commit,
+ * KVCachePlan.swift:219-300, as driven by the speculative iterators, Evaluate.swift:1179-1286).
+ * kvc_storage_begin_round opens one staged round per cache, all or nothing: when any
+ * cache refuses (it could not be rewound after `max_positions` more tokens) nothing is
+ * opened and KVC_ERR_NOT_TRIMMABLE comes back, so the caller can fall back to unstaged
+ * decoding like the reference does (:219-228). out_rounds receives `count` handles.
+ * kvc_storage_round_attention runs the verify pass of every layer (queries[i] etc. belong
+ * to caches[i]'s round) on `stream`. kvc_storage_commit keeps the first `retaining`
+ * positions the round wrote in every cache, drops the rest and frees the rounds
+ * (retaining 0 = rollback). */
+kvc_status kvc_storage_begin_round(kvc_cache *const *caches, int32_t count, int32_t max_positions,
+                                   kvc_round **out_rounds);
+kvc_status kvc_storage_round_attention(kvc_round *const *rounds, int32_t count, const kvc_tensor *queries,
+                                       const kvc_tensor *keys, const kvc_tensor *values, float scale,
+                                       int32_t mask_mode, const kvc_tensor *outs, void *stream);
+kvc_status kvc_storage_commit(kvc_round **rounds, int32_t count, int32_t retaining, void *stream);
+
+/* The rewind at the end of speculateRound without staged rounds (Evaluate.swift:1262-1264):
+ * the main model's caches give back num_draft - accepted positions, the draft model's
+ * max(num_draft - accepted - 1, 0); both through trimPromptCache (all or nothing).
+ * is_draft selects the rule; *out_trimmed receives the positions actually trimmed. */
+kvc_status kvc_speculate_rewind(kvc_cache *const *caches, int32_t count, int32_t num_draft,
+                                int32_t accepted, int32_t is_draft, int64_t *out_trimmed);
+
+/* ------------------------------------------------------------------ */
 /* TurboQuant codec pieces (TurboQuantKVCache.swift:47-621,            */
 /* TurboQuantKernels.swift:224-342, :354-411)                          */
 /* ------------------------------------------------------------------ */

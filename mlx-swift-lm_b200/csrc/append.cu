@@ -9,6 +9,15 @@ namespace kvc {
 
 namespace {
 
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
 template <typename V>
 __global__ void append_kernel(AppendArgs a, int64_t k_units, int64_t total_units,
                               int k_upr, int v_upr /* units per row */) {
@@ -64,6 +73,47 @@ __global__ void append_strided_kernel(AppendArgs a, int64_t k_elems, int64_t tot
         const E *src = (const E *)a.v_src + b * a.vs_sb + h * a.vs_sh + s * a.vs_ss + d * a.vs_sd;
         E *dst = (E *)a.v_dst + b * a.vd_sb + h * a.vd_sh + (a.pos + s) * a.vd_st + d;
         *dst = *src;
+    }
+}
+
+// Rotary positions for queries and keys in one launch (applyRotaryPosition,
+// MLXLMCommon/RoPEApplication.swift:58-69; the rotation itself is MLX's published RoPE: pair i of a
+// head at position p turns by p * scale * base^(-2i/dims)). One thread per (row, pair); features past
+// `dims` are copied. Arithmetic in float32, results rounded to the element type.
+template <typename T>
+__global__ void rope_kernel(RopeArgs a, int64_t q_items, int64_t total_items) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total_items) return;
+    const bool is_k = i >= q_items;
+    if (is_k) i -= q_items;
+    const RopeTensor &t = is_k ? a.k : a.q;
+    const int half = a.D / 2;            // items per row: D / 2 (rotated pairs first, then pass-through pairs)
+    const int p = (int)(i % half);
+    int64_t row = i / half;
+    const int l = (int)(row % t.L);
+    row /= t.L;
+    const int h = (int)(row % t.H);
+    const int b = (int)(row / t.H);
+    const T *src = (const T *)t.src + b * t.s_sb + h * t.s_sh + l * t.s_sl;
+    T *dst = (T *)t.dst + b * t.d_sb + h * t.d_sh + l * t.d_sl;
+    const int rp = a.dims / 2;           // rotated pairs
+    if (p < rp) {
+        const int i0 = a.traditional ? 2 * p : p, i1 = a.traditional ? 2 * p + 1 : p + rp;
+        const float x0 = to_float<T>(src[i0]), x1 = to_float<T>(src[i1]);
+        // the frequency in double precision, rounded once: at positions in the tens of thousands a float32
+        // exp2 would already move the angle by 1e-3
+        const float inv_freq = (float)exp2(-(double)p * a.log2_base_over_half);
+        const float theta = __fmul_rn(__fmul_rn((float)(a.offset + l), a.scale), inv_freq);
+        float sn, cs;
+        sincosf(theta, &sn, &cs);
+        dst[i0] = from_float<T>(x0 * cs - x1 * sn);
+        dst[i1] = from_float<T>(x0 * sn + x1 * cs);
+    } else {
+        // the features past `dims`, two per item
+        const int j = a.dims + 2 * (p - rp);
+        dst[j] = src[j];
+        if (j + 1 < a.D) dst[j + 1] = src[j + 1];
     }
 }
 
@@ -201,6 +251,24 @@ void launch_gather(const GatherArgs &a, cudaStream_t stream) {
             a, total, upr, rows_per_bh);
     } else {
         fail(KVC_ERR_INVALID_ARG, "gather: unsupported row layout");
+    }
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
+void launch_rope(const RopeArgs &a, cudaStream_t s) {
+    KVC_REQUIRE(a.dims >= 2 && a.dims % 2 == 0 && a.dims <= a.D && a.D % 2 == 0, "rope: dims must be even and at most the head dim");
+    const int half = a.D / 2;
+    const int64_t q_items = a.q.src ? (int64_t)a.q.B * a.q.H * a.q.L * half : 0;
+    const int64_t k_items = a.k.src ? (int64_t)a.k.B * a.k.H * a.k.L * half : 0;
+    const int64_t total = q_items + k_items;
+    if (total <= 0) return;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    switch (a.dtype) {
+        case KVC_F32: rope_kernel<float><<<blocks, 256, 0, s>>>(a, q_items, total); break;
+        case KVC_F16: rope_kernel<__half><<<blocks, 256, 0, s>>>(a, q_items, total); break;
+        case KVC_BF16: rope_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(a, q_items, total); break;
+        default: fail(KVC_ERR_INVALID_ARG, "rope needs a floating dtype");
     }
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;

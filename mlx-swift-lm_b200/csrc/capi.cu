@@ -9,6 +9,7 @@
 #include <vector>
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <memory>
 #include <sstream>
@@ -1208,6 +1209,144 @@ int32_t kvc_device_status(void) {
         return -1;
     }
     return kvc::device_status(dev);
+}
+
+// ---------------------------------------------------------------------
+// rotary positions at the cache offset; speculative rounds over a layer list
+// ---------------------------------------------------------------------
+namespace {
+kvc::RopeTensor rope_tensor(const kvc_tensor &x, void *dst, int64_t d_sb, int64_t d_sh, int64_t d_sl) {
+    kvc::RopeTensor t;
+    t.src = x.data; t.dst = dst;
+    t.s_sb = x.stride[0]; t.s_sh = x.stride[1]; t.s_sl = x.stride[2];
+    t.d_sb = d_sb; t.d_sh = d_sh; t.d_sl = d_sl;
+    t.B = (int32_t)x.shape[0]; t.H = (int32_t)x.shape[1]; t.L = (int32_t)x.shape[2];
+    return t;
+}
+
+void rope_check(const kvc_tensor &x, const kvc_rope_config &r, const char *what) {
+    KVC_REQUIRE(x.ndim == 4 && x.stride[3] == 1, std::string(what) + ": tensors must be [B, H, L, D] with inner stride 1");
+    KVC_REQUIRE(x.dtype == KVC_F32 || x.dtype == KVC_F16 || x.dtype == KVC_BF16, std::string(what) + ": floating dtype needed");
+    KVC_REQUIRE(r.dims >= 2 && r.dims % 2 == 0 && r.dims <= x.shape[3] && x.shape[3] % 2 == 0,
+                std::string(what) + ": rope dims must be even and at most the head dim");
+    KVC_REQUIRE(r.base > 0.f, std::string(what) + ": rope base must be positive");
+}
+
+kvc::RopeArgs rope_args(const kvc_rope_config &r, int32_t dtype, int D, int64_t offset) {
+    kvc::RopeArgs a;
+    a.dtype = dtype; a.D = D; a.dims = r.dims; a.traditional = r.traditional ? 1 : 0;
+    a.log2_base_over_half = std::log2((double)r.base) / (double)(r.dims / 2);
+    a.scale = r.scale;
+    a.offset = offset;
+    return a;
+}
+}  // namespace
+
+kvc_status kvc_rope(const kvc_tensor *x, int64_t offset, const kvc_rope_config *rope, const kvc_tensor *out, void *stream) {
+    if (!x || !rope || !out) return set_error(KVC_ERR_INVALID_ARG, "kvc_rope: null argument");
+    return guarded([&] {
+        rope_check(*x, *rope, "kvc_rope");
+        KVC_REQUIRE(out->ndim == 4 && out->stride[3] == 1 && out->dtype == x->dtype, "kvc_rope: out must match x");
+        for (int i = 0; i < 4; ++i) KVC_REQUIRE(out->shape[i] == x->shape[i], "kvc_rope: out must match x");
+        kvc::RopeArgs a = rope_args(*rope, x->dtype, (int)x->shape[3], offset);
+        a.q = rope_tensor(*x, out->data, out->stride[0], out->stride[1], out->stride[2]);
+        kvc::launch_rope(a, as_stream(stream));
+    });
+}
+
+kvc_status kvc_attention_rope(kvc_cache *cache, const kvc_tensor *q, const kvc_tensor *k, const kvc_tensor *v,
+                              const kvc_rope_config *rope, float scale, int32_t mask_mode, const kvc_tensor *mask,
+                              const kvc_tensor *out, void *stream) {
+    if (!q || !k || !v || !rope || !out) return set_error(KVC_ERR_INVALID_ARG, "kvc_attention_rope: null argument");
+    return guarded([&] {
+        cudaStream_t s = as_stream(stream);
+        rope_check(*q, *rope, "kvc_attention_rope");
+        rope_check(*k, *rope, "kvc_attention_rope");
+        KVC_REQUIRE(q->dtype == k->dtype && q->shape[3] == k->shape[3] && q->shape[2] == k->shape[2] && q->shape[0] == k->shape[0],
+                    "kvc_attention_rope: queries and keys disagree");
+        DeviceGuard dg(cache ? cache->device : -1);
+        // cache?.ropeOffset: the scalar cache offset (KVCache.swift:107-109), 0 without a cache
+        const int64_t offset = cache ? cache->offset : 0;
+        const size_t es = kvc::dtype_size(q->dtype);
+        const int64_t D = q->shape[3], L = q->shape[2];
+        const size_t qn = (size_t)(q->shape[0] * q->shape[1] * L * D), kn = (size_t)(k->shape[0] * k->shape[1] * L * D);
+        char *buf = (char *)kvc::dev_alloc((qn + kn) * es + 256, s);
+        struct Free { char *p; cudaStream_t s; ~Free() { kvc::dev_free(p, s); } } freer{buf, s};
+        kvc_tensor rq = *q, rk = *k;
+        rq.data = buf;
+        rk.data = buf + ((qn * es + 255) / 256) * 256;
+        for (kvc_tensor *t : {&rq, &rk}) {
+            t->stride[3] = 1; t->stride[2] = D; t->stride[1] = L * D; t->stride[0] = t->shape[1] * L * D;
+        }
+        kvc::RopeArgs a = rope_args(*rope, q->dtype, (int)D, offset);
+        a.q = rope_tensor(*q, rq.data, rq.stride[0], rq.stride[1], rq.stride[2]);
+        a.k = rope_tensor(*k, rk.data, rk.stride[0], rk.stride[1], rk.stride[2]);
+        kvc::launch_rope(a, s);
+        if (cache) {
+            kvc::cache_attention(cache, rq, rk, *v, scale, mask_mode, mask, *out, s);
+        } else {
+            // attentionWithCacheUpdate without a cache: plain SDPA (AttentionUtils.swift:46-52)
+            kvc_status st = kvc_sdpa(&rq, &rk, v, scale, mask_mode, mask, out, stream);
+            if (st != KVC_OK) kvc::fail(st, kvc_last_error_message());
+        }
+    });
+}
+
+kvc_status kvc_storage_begin_round(kvc_cache *const *caches, int32_t count, int32_t max_positions, kvc_round **out_rounds) {
+    if (!caches || !out_rounds || count <= 0) return set_error(KVC_ERR_INVALID_ARG, "kvc_storage_begin_round: bad argument");
+    for (int i = 0; i < count; ++i) out_rounds[i] = nullptr;
+    for (int i = 0; i < count; ++i) {
+        // nested lists expand to more leaves than slots and are refused (KVCachePlan.swift:226-231)
+        kvc_status st = (caches[i] && caches[i]->cfg.kind == KVC_KIND_LIST)
+                            ? set_error(KVC_ERR_NOT_TRIMMABLE, "a CacheList entry cannot take part in a staged round")
+                            : kvc_round_begin(caches[i], max_positions, &out_rounds[i]);
+        if (st != KVC_OK) {
+            // all or nothing: close what was opened (nothing has been written through them yet)
+            const std::string msg = kvc_last_error_message() ? kvc_last_error_message() : "";
+            for (int j = 0; j < i; ++j) {
+                (void)kvc_round_rollback(out_rounds[j], nullptr);
+                kvc_round_free(out_rounds[j]);
+                out_rounds[j] = nullptr;
+            }
+            return set_error(st, msg.c_str());
+        }
+    }
+    return KVC_OK;
+}
+
+kvc_status kvc_storage_round_attention(kvc_round *const *rounds, int32_t count, const kvc_tensor *q, const kvc_tensor *k,
+                                       const kvc_tensor *v, float scale, int32_t mask_mode, const kvc_tensor *outs, void *stream) {
+    if (!rounds || !q || !k || !v || !outs) return set_error(KVC_ERR_INVALID_ARG, "kvc_storage_round_attention: null argument");
+    for (int i = 0; i < count; ++i) {
+        kvc_status st = kvc_round_attention(rounds[i], &q[i], &k[i], &v[i], scale, mask_mode, nullptr, &outs[i], stream);
+        if (st != KVC_OK) return st;
+    }
+    return KVC_OK;
+}
+
+kvc_status kvc_storage_commit(kvc_round **rounds, int32_t count, int32_t retaining, void *stream) {
+    if (!rounds) return set_error(KVC_ERR_INVALID_ARG, "kvc_storage_commit: null argument");
+    kvc_status first = KVC_OK;
+    for (int i = 0; i < count; ++i) {
+        if (!rounds[i]) continue;
+        kvc_status st = kvc_round_commit(rounds[i], retaining, stream);
+        if (st != KVC_OK && first == KVC_OK) first = st;
+        kvc_round_free(rounds[i]);
+        rounds[i] = nullptr;
+    }
+    return first;
+}
+
+kvc_status kvc_speculate_rewind(kvc_cache *const *caches, int32_t count, int32_t num_draft, int32_t accepted, int32_t is_draft,
+                                int64_t *out_trimmed) {
+    if (!caches || num_draft < 0 || accepted < 0 || accepted > num_draft)
+        return set_error(KVC_ERR_INVALID_ARG, "kvc_speculate_rewind: need 0 <= accepted <= num_draft");
+    // Evaluate.swift:1262-1264
+    const int64_t n = is_draft ? std::max(num_draft - accepted - 1, 0) : num_draft - accepted;
+    int64_t trimmed = 0;
+    kvc_status st = n > 0 ? kvc_trim_prompt_cache(caches, count, n, &trimmed) : KVC_OK;
+    if (out_trimmed) *out_trimmed = trimmed;
+    return st;
 }
 
 kvc_status kvc_device_status_reset(void) {

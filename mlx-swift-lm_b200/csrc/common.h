@@ -168,6 +168,24 @@ struct GatherArgs {
     int64_t dst_start = 0;                 // first destination token
 };
 
+// Rotary positions for a query tensor and a key tensor [B, H, L, D] in one launch (either may be absent).
+struct RopeTensor {
+    const void *src = nullptr;
+    void *dst = nullptr;
+    int64_t s_sb = 0, s_sh = 0, s_sl = 0;   // element strides (inner stride 1)
+    int64_t d_sb = 0, d_sh = 0, d_sl = 0;
+    int32_t B = 0, H = 0, L = 0;
+};
+struct RopeArgs {
+    RopeTensor q, k;
+    int32_t dtype = KVC_BF16;
+    int32_t D = 0, dims = 0, traditional = 0;
+    double log2_base_over_half = 0.0;  // log2(base) / (dims / 2)
+    float scale = 1.f;
+    int64_t offset = 0;
+};
+void launch_rope(const RopeArgs &a, cudaStream_t stream);
+
 void launch_append(const AppendArgs &a, cudaStream_t stream);
 void launch_gather(const GatherArgs &a, cudaStream_t stream);
 

@@ -159,6 +159,20 @@ _lib.kvc_start_position.restype = ctypes.c_int64
 _lib.kvc_prepare.argtypes = [_vp, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]
 _lib.kvc_finalize.argtypes = [_vp]
 _lib.kvc_create_causal_mask.argtypes = [ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, _vp, ctypes.c_int32, _vp, _vp]
+class RopeConfig(ctypes.Structure):
+    _fields_ = [("dims", ctypes.c_int32), ("traditional", ctypes.c_int32), ("base", ctypes.c_float),
+                ("scale", ctypes.c_float)]
+
+
+_lib.kvc_rope.argtypes = [_TP, ctypes.c_int64, ctypes.POINTER(RopeConfig), _TP, _vp]
+_lib.kvc_attention_rope.argtypes = [_vp, _TP, _TP, _TP, ctypes.POINTER(RopeConfig), ctypes.c_float, ctypes.c_int32,
+                                    _TP, _TP, _vp]
+_lib.kvc_storage_begin_round.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_vp)]
+_lib.kvc_storage_round_attention.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, _TP, _TP, _TP, ctypes.c_float,
+                                             ctypes.c_int32, _TP, _vp]
+_lib.kvc_storage_commit.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, _vp]
+_lib.kvc_speculate_rewind.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                      ctypes.c_int32, ctypes.POINTER(ctypes.c_int64)]
 _lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
 _lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
 _lib.kvc_comm_symm_alloc.argtypes = [_vp, ctypes.c_size_t, _vp, ctypes.POINTER(_vp)]
@@ -838,6 +852,82 @@ def device_status_reset() -> None:
 def device_wait_probe(iterations: int = 1 << 12, stream=None) -> None:
     """A kernel whose bounded wait runs out on purpose (kvc_device_wait_probe)."""
     check(_lib.kvc_device_wait_probe(iterations, _stream_ptr(stream)))
+
+
+def rope(x, offset: int, dims: int, traditional: bool = False, base: float = 10000.0, scale: float = 1.0, out=None,
+         stream=None):
+    """applyRotaryPosition(rope, to: x, offset:) for x [B, H, L, D] on the device."""
+    torch = _torch()
+    if out is None:
+        out = torch.empty_like(x)
+    cfg = RopeConfig(dims, int(traditional), base, scale)
+    tx, to = as_tensor(x), as_tensor(out)
+    check(_lib.kvc_rope(ctypes.byref(tx), offset, ctypes.byref(cfg), ctypes.byref(to), _stream_ptr(stream)))
+    return out
+
+
+def attention_rope(queries, keys, values, cache: Optional["KVCache"], rope_cfg: dict, scale: float, mask="none", out=None,
+                   stream=None):
+    """The attention block's cache step (Llama.swift:58-69): rotary positions at cache.ropeOffset for queries
+    and keys, then attentionWithCacheUpdate."""
+    torch = _torch()
+    if out is None:
+        out = torch.empty(queries.shape, dtype=queries.dtype, device=queries.device)
+    cfg = RopeConfig(rope_cfg["dims"], int(rope_cfg.get("traditional", False)), rope_cfg.get("base", 10000.0),
+                     rope_cfg.get("scale", 1.0))
+    mode, mptr, _keep = _mask_args(mask)
+    tq, tk, tv, to = as_tensor(queries), as_tensor(keys), as_tensor(values), as_tensor(out)
+    check(_lib.kvc_attention_rope(cache._h if cache is not None else None, ctypes.byref(tq), ctypes.byref(tk),
+                                  ctypes.byref(tv), ctypes.byref(cfg), ctypes.c_float(scale), mode, mptr, ctypes.byref(to),
+                                  _stream_ptr(stream)))
+    return out
+
+
+class StorageRound:
+    """A staged speculative round over the layer list of a model (KVCacheStorage.beginRound / commit,
+    KVCachePlan.swift:219-300). Opening is all or nothing; `attention` runs the verify pass of every layer;
+    `commit(retaining)` keeps that many of the written positions in every cache (0 = rollback)."""
+
+    def __init__(self, caches: Sequence["KVCache"], max_positions: int):
+        self.caches = list(caches)
+        n = len(self.caches)
+        arr = (_vp * n)(*[c._h for c in self.caches])
+        self._rounds = (_vp * n)()
+        self._n = n
+        check(_lib.kvc_storage_begin_round(arr, n, max_positions, self._rounds))
+        self._open = True
+
+    def attention(self, queries, keys, values, scale: float, outs, mask: str = "causal", stream=None):
+        n = self._n
+        q = (Tensor * n)(*[as_tensor(t) for t in queries])
+        k = (Tensor * n)(*[as_tensor(t) for t in keys])
+        v = (Tensor * n)(*[as_tensor(t) for t in values])
+        o = (Tensor * n)(*[as_tensor(t) for t in outs])
+        mode = {"none": MASK_NONE, "causal": MASK_CAUSAL}[mask]
+        check(_lib.kvc_storage_round_attention(self._rounds, n, q, k, v, ctypes.c_float(scale), mode, o, _stream_ptr(stream)))
+        return outs
+
+    def commit(self, retaining: int, stream=None) -> None:
+        if self._open:
+            self._open = False
+            check(_lib.kvc_storage_commit(self._rounds, self._n, retaining, _stream_ptr(stream)))
+
+    def rollback(self, stream=None) -> None:
+        self.commit(0, stream)
+
+    def __del__(self):
+        try:
+            self.commit(0)
+        except Exception:
+            pass
+
+
+def speculate_rewind(caches: Sequence["KVCache"], num_draft: int, accepted: int, is_draft: bool = False) -> int:
+    """The rewind at the end of speculateRound (Evaluate.swift:1262-1264)."""
+    arr = (_vp * len(caches))(*[c._h for c in caches])
+    out = ctypes.c_int64()
+    check(_lib.kvc_speculate_rewind(arr, len(caches), num_draft, accepted, int(is_draft), ctypes.byref(out)))
+    return int(out.value)
 
 
 def timing_enable(on: bool) -> None:

@@ -1195,6 +1195,42 @@ def attention_with_cache_update(q, keys, values, cache, scale, mask="none", prec
 # staged rounds (RotatingStagedKVCache.swift, KVCacheRound.swift, KVCachePlan.swift:219-347)
 # ---------------------------------------------------------------------------
 
+def rope(x: np.ndarray, offset: int, dims: int, traditional: bool = False, base: float = 10000.0,
+         scale: float = 1.0) -> np.ndarray:
+    """applyRotaryPosition(rope, to: x, offset:) (MLXLMCommon/RoPEApplication.swift:58-69) for x [B, H, L, D] in
+    storage dtype. The rotation is MLX's published RoPE (un-vendored mlx-swift: parity unpinned): pair i of a
+    head at position p = offset + l turns by p * scale * base^(-2i/dims); pairs are (i, i + dims/2), or
+    (2i, 2i+1) when `traditional`; features past `dims` pass through. Float32 arithmetic."""
+    code = dtype_code(x)
+    xf = to_f32(x).copy()
+    B, H, L, D = xf.shape
+    half = dims // 2
+    inv_freq = np.exp2(-np.arange(half, dtype=np.float64) * (np.log2(np.float64(np.float32(base))) / half)).astype(np.float32)
+    pos = (np.arange(L, dtype=np.float32) + np.float32(offset)) * np.float32(scale)
+    theta = (pos[:, None] * inv_freq[None, :]).astype(np.float32)
+    cs, sn = np.cos(theta).astype(np.float32), np.sin(theta).astype(np.float32)
+    if traditional:
+        x0, x1 = xf[..., 0:dims:2].copy(), xf[..., 1:dims:2].copy()
+        xf[..., 0:dims:2] = x0 * cs - x1 * sn
+        xf[..., 1:dims:2] = x0 * sn + x1 * cs
+    else:
+        x0, x1 = xf[..., :half].copy(), xf[..., half:dims].copy()
+        xf[..., :half] = x0 * cs - x1 * sn
+        xf[..., half:dims] = x0 * sn + x1 * cs
+    return from_f32(xf, code)
+
+
+def attention_rope(q, keys, values, cache, rope_cfg: dict, scale, mask="none", precise=True):
+    """The attention block's cache step (MLXLLM/Models/Llama.swift:58-69): rotate q and k at the cache's
+    ropeOffset (its offset; 0 without a cache), then attentionWithCacheUpdate."""
+    offset = cache.offset if cache is not None else 0
+    rq = rope(q, offset, **rope_cfg)
+    rk = rope(keys, offset, **rope_cfg)
+    if cache is None:
+        return sdpa(rq, rk, values, scale, mask, precise=precise)
+    return attention_with_cache_update(rq, rk, values, cache, scale, mask, precise=precise)
+
+
 class StagedRound:
     """One cache's share of a speculative round."""
 
