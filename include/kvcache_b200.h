@@ -468,6 +468,15 @@ kvc_status kvc_turbo_signs(int32_t dim, uint64_t seed, float *signs);
 kvc_status kvc_turbo_set_codec(kvc_cache *cache, const float *key_centroids,
                                const float *value_centroids, const float *key_signs,
                                const float *value_signs, int32_t dim);
+/* The dense random rotation the codec uses for head dims that are not powers of two
+ * (TurboQuantRotation.rotationMatrix, TurboQuantKVCache.swift:246-259): QR of a seeded Gaussian
+ * matrix, sign-corrected; host array, row-major [dim, dim]. The reference draws it from MLXRandom
+ * and factors it with MLX's QR (not reproducible outside MLX); this library's generator is its own
+ * (splitmix64 + Box-Muller, Householder QR in double precision). kvc_turbo_set_rotation hands a
+ * cache the matrices a host already holds (before the first encode); NULL keeps the default. */
+kvc_status kvc_turbo_rotation(int32_t dim, uint64_t seed, float *rotation);
+kvc_status kvc_turbo_set_rotation(kvc_cache *cache, const float *key_rotation,
+                                  const float *value_rotation, int32_t dim);
 /* Fused WHT encode of rows [rows, D] -> packed [rows, PW] u32 + raw norms f32
  * (fusedEncodeWHT, TurboQuantKernels.swift:224-342 / :1672-1719). signs_dev is
  * a device array [D]; boundaries_host a host array [2^bits - 1]. */

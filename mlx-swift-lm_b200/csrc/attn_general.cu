@@ -136,9 +136,34 @@ attn_general_partial(const __grid_constant__ AttnArgs a, float *o_part, float2 *
             const int hq = hk * rep + ri / a.L, l = ri % a.L;
             qv = ld_elem(a.q, a.q_dtype, b * a.q_sb + hq * a.q_sh + l * a.q_sl + d);
             if (a.q_signs) qv *= a.q_signs[d];
-            else qv *= a.scale;
+            else if (!a.q_rot) qv *= a.scale;
         }
         Qs[r * D + d] = qv;
+    }
+    if (a.q_rot) {
+        // dense rotation: q'[d] = sum_j Pi[d][j] q[j], then the scale (and calibration); two dims per thread
+        __syncthreads();
+        float rq[G_RC][2];
+#pragma unroll
+        for (int r = 0; r < G_RC; ++r) rq[r][0] = rq[r][1] = 0.f;
+        for (int dd = 0; dd < 2; ++dd) {
+            const int d = tid + dd * G_THREADS;
+            if (d >= D) continue;
+            const float *rot = a.q_rot + (int64_t)d * D;
+            for (int j = 0; j < D; ++j) {
+                const float m = rot[j];
+#pragma unroll
+                for (int r = 0; r < G_RC; ++r) rq[r][dd] = fmaf(m, Qs[r * D + j], rq[r][dd]);
+            }
+        }
+        __syncthreads();
+        for (int dd = 0; dd < 2; ++dd) {
+            const int d = tid + dd * G_THREADS;
+            if (d >= D) continue;
+            const float f = a.scale * (a.q_calib ? a.q_calib[d] : 1.f);
+#pragma unroll
+            for (int r = 0; r < G_RC; ++r) Qs[r * D + d] = rq[r][dd] * f;
+        }
     }
     if (a.q_signs) {
         smem_fwht(Qs, G_RC, D, D);
@@ -270,7 +295,7 @@ attn_general_partial(const __grid_constant__ AttnArgs a, float *o_part, float2 *
 // is rotated back: out = signs * H(o) / sqrt(D).
 __global__ void attn_merge_kernel(const float *o_part, const float2 *ml_part, int splits, int D,
                                   void *out, int32_t out_dtype, int Hq, int L, int64_t o_sb,
-                                  int64_t o_sh, int64_t o_sl, const float *o_signs) {
+                                  int64_t o_sh, int64_t o_sl, const float *o_signs, const float *o_rot) {
     extern __shared__ float sm[];  // [D] when rotating
     const int64_t qrow = blockIdx.x;
     const int l = (int)(qrow % L);
@@ -292,8 +317,18 @@ __global__ void attn_merge_kernel(const float *o_part, const float2 *ml_part, in
                 o = fmaf(o_part[(qrow * splits + s) * D + d], expf(ml.x - m), o);
         }
         o *= inv_l;
-        if (o_signs) sm[d] = o;
+        if (o_signs || o_rot) sm[d] = o;
         else st_elem(out, out_dtype, b * o_sb + hq * o_sh + l * o_sl + d, o);
+    }
+    if (o_rot) {
+        // dense inverse rotation: out[j] = sum_d o'[d] Pi[d][j]
+        __syncthreads();
+        for (int j = threadIdx.x; j < D; j += blockDim.x) {
+            float acc = 0.f;
+            for (int d = 0; d < D; ++d) acc = fmaf(sm[d], o_rot[(int64_t)d * D + j], acc);
+            st_elem(out, out_dtype, b * o_sb + hq * o_sh + l * o_sl + j, acc);
+        }
+        return;
     }
     if (o_signs) {
         smem_fwht(sm, 1, D, D);
@@ -309,9 +344,9 @@ void launch_merge(const float *o_part, const float2 *ml_part, int splits, const 
                   cudaStream_t stream) {
     const int64_t qrows = (int64_t)a.B * a.Hq * a.L;
     const int threads = std::min(256, std::max(32, ((a.D + 31) / 32) * 32));
-    const size_t smem = a.o_signs ? (size_t)a.D * sizeof(float) : 0;
+    const size_t smem = (a.o_signs || a.o_rot) ? (size_t)a.D * sizeof(float) : 0;
     attn_merge_kernel<<<(unsigned)qrows, threads, smem, stream>>>(
-        o_part, ml_part, splits, a.D, a.out, a.q_dtype, a.Hq, a.L, a.o_sb, a.o_sh, a.o_sl, a.o_signs);
+        o_part, ml_part, splits, a.D, a.out, a.q_dtype, a.Hq, a.L, a.o_sb, a.o_sh, a.o_sl, a.o_signs, a.o_rot);
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
 }

@@ -221,6 +221,67 @@ static kvc_tensor view3(const Array4 &a, int64_t tokens) {
     return t;
 }
 
+
+void turbo_rotation(int dim, uint64_t seed, std::vector<float> &rotation) {
+    // TurboQuantRotation.rotationMatrix (TurboQuantKVCache.swift:246-259): QR of a seeded Gaussian matrix,
+    // the columns of Q flipped by the signs of R's diagonal. The reference draws the matrix from MLXRandom
+    // and factors it with MLX's QR, neither of which is reproducible outside MLX; this library defines its
+    // own: Box-Muller normals from the splitmix64 stream seeded with `seed` (row-major fill), Householder QR
+    // in double precision, result rounded to float32.
+    const int n = dim;
+    std::vector<double> a((size_t)n * n);
+    uint64_t x = seed;
+    auto next_u = [&]() {
+        x += 0x9E3779B97F4A7C15ull;
+        uint64_t z = x;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z = z ^ (z >> 31);
+        return ((double)(z >> 11) + 0.5) / 9007199254740992.0;   // (0, 1)
+    };
+    for (size_t i = 0; i < a.size(); i += 2) {
+        const double u1 = next_u(), u2 = next_u();
+        const double r = std::sqrt(-2.0 * std::log(u1)), t = 6.283185307179586476925286766559 * u2;
+        a[i] = r * std::cos(t);
+        if (i + 1 < a.size()) a[i + 1] = r * std::sin(t);
+    }
+    // Householder: A = Q R; accumulate Q explicitly
+    std::vector<double> q((size_t)n * n, 0.0), v(n);
+    for (int i = 0; i < n; ++i) q[(size_t)i * n + i] = 1.0;
+    std::vector<double> rdiag(n, 0.0);
+    for (int k = 0; k < n; ++k) {
+        double norm = 0.0;
+        for (int i = k; i < n; ++i) norm += a[(size_t)i * n + k] * a[(size_t)i * n + k];
+        norm = std::sqrt(norm);
+        const double akk = a[(size_t)k * n + k];
+        const double alpha = akk > 0 ? -norm : norm;
+        for (int i = 0; i < n; ++i) v[i] = 0.0;
+        for (int i = k; i < n; ++i) v[i] = a[(size_t)i * n + k];
+        v[k] -= alpha;
+        double vnorm2 = 0.0;
+        for (int i = k; i < n; ++i) vnorm2 += v[i] * v[i];
+        if (vnorm2 > 0.0) {
+            for (int j = 0; j < n; ++j) {      // A <- (I - 2 v v^T / v^T v) A
+                double dot = 0.0;
+                for (int i = k; i < n; ++i) dot += v[i] * a[(size_t)i * n + j];
+                const double f = 2.0 * dot / vnorm2;
+                for (int i = k; i < n; ++i) a[(size_t)i * n + j] -= f * v[i];
+            }
+            for (int i = 0; i < n; ++i) {      // Q <- Q (I - 2 v v^T / v^T v)
+                double dot = 0.0;
+                for (int j = k; j < n; ++j) dot += q[(size_t)i * n + j] * v[j];
+                const double f = 2.0 * dot / vnorm2;
+                for (int j = k; j < n; ++j) q[(size_t)i * n + j] -= f * v[j];
+            }
+        }
+        rdiag[k] = a[(size_t)k * n + k];
+    }
+    rotation.resize((size_t)n * n);
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < n; ++j)
+            rotation[(size_t)i * n + j] = (float)(q[(size_t)i * n + j] * (rdiag[j] < 0 ? -1.0 : 1.0));
+}
+
 }  // namespace kvc
 
 kvc_cache::~kvc_cache() {
@@ -233,6 +294,8 @@ kvc_cache::~kvc_cache() {
     if (kcodec.signs_dev) kvc::dev_free(kcodec.signs_dev, s);
     if (vcodec.signs_dev) kvc::dev_free(vcodec.signs_dev, s);
     if (kcodec.calib_dev) kvc::dev_free(kcodec.calib_dev, s);
+    if (kcodec.rotation_dev) kvc::dev_free(kcodec.rotation_dev, s);
+    if (vcodec.rotation_dev) kvc::dev_free(vcodec.rotation_dev, s);
     for (kvc_cache *child : children) delete child;
 }
 
@@ -604,12 +667,16 @@ static void upload_signs(TurboCodec &codec, cudaStream_t s) {
 
 void ensure_codecs(kvc_cache *c, int head_dim, cudaStream_t s) {
     // TurboQuantKVCache.ensureCodecs (TurboQuantKVCache.swift:753-759): key codec
-    // seeded with `seed`, value codec with `seed + 1`.
+    // seeded with `seed`, value codec with `seed + 1`. MSECodec.init (:459-486): the randomised
+    // Walsh-Hadamard rotation for power-of-two head dims up to 1024, a dense random rotation otherwise.
     if (c->codec_ready && c->vcodec.dim == head_dim) return;
-    KVC_REQUIRE(head_dim >= 32 && head_dim <= 1024 && (head_dim & (head_dim - 1)) == 0,
-                "TurboQuant: only the Walsh-Hadamard path (power-of-two head dim in [32, 1024]) is built");
+    KVC_REQUIRE(head_dim >= 2 && head_dim <= 1024, "TurboQuant: head dim must be in [2, 1024]");
+    const bool wht = (head_dim & (head_dim - 1)) == 0;
+    if (wht && head_dim < 32)
+        fail(KVC_ERR_UNSUPPORTED, "TurboQuant: power-of-two head dims below 32 (Walsh-Hadamard over less than a warp) are not built");
+    if (!wht) KVC_REQUIRE(head_dim <= 256, "TurboQuant: the dense-rotation path is built for head dims up to 256");
     auto build = [&](TurboCodec &codec, int bits, uint64_t seed, const std::vector<float> &uc,
-                     const std::vector<float> &us) {
+                     const std::vector<float> &us, const std::vector<float> &ur) {
         codec.dim = head_dim;
         codec.bits = bits;
         if (!uc.empty()) {
@@ -620,16 +687,29 @@ void ensure_codecs(kvc_cache *c, int head_dim, cudaStream_t s) {
         } else {
             turbo_codebook(head_dim, bits, codec.centroids, codec.boundaries);
         }
-        if (!us.empty()) {
-            KVC_REQUIRE((int)us.size() == head_dim, "TurboQuant: sign override has the wrong length");
-            codec.signs = us;
+        if (wht) {
+            if (!us.empty()) {
+                KVC_REQUIRE((int)us.size() == head_dim, "TurboQuant: sign override has the wrong length");
+                codec.signs = us;
+            } else {
+                turbo_signs(head_dim, seed, codec.signs);
+            }
+            upload_signs(codec, s);
         } else {
-            turbo_signs(head_dim, seed, codec.signs);
+            if (!ur.empty()) {
+                KVC_REQUIRE((int64_t)ur.size() == (int64_t)head_dim * head_dim, "TurboQuant: rotation override has the wrong size");
+                codec.rotation = ur;
+            } else {
+                turbo_rotation(head_dim, seed, codec.rotation);
+            }
+            if (codec.rotation_dev) dev_free(codec.rotation_dev, s);
+            codec.rotation_dev = (float *)dev_alloc(codec.rotation.size() * sizeof(float), s);
+            KVC_CUDA(cudaMemcpyAsync(codec.rotation_dev, codec.rotation.data(), codec.rotation.size() * sizeof(float),
+                                     cudaMemcpyHostToDevice, s));
         }
-        upload_signs(codec, s);
     };
-    if (!c->raw_key && !c->affine_key) build(c->kcodec, c->key_bits, c->cfg.seed, c->user_kc, c->user_ks);
-    if (!c->affine_value) build(c->vcodec, c->value_bits, c->cfg.seed + 1, c->user_vc, c->user_vs);
+    if (!c->raw_key && !c->affine_key) build(c->kcodec, c->key_bits, c->cfg.seed, c->user_kc, c->user_ks, c->user_kr);
+    if (!c->affine_value) build(c->vcodec, c->value_bits, c->cfg.seed + 1, c->user_vc, c->user_vs, c->user_vr);
     else c->vcodec.dim = head_dim;
     c->codec_ready = true;
 }
@@ -645,10 +725,10 @@ static TurboEncodeArgs turbo_args(const kvc_tensor &x, Array4 &packed, Array4 &n
     a.B = (int)x.shape[0]; a.H = (int)x.shape[1]; a.S = (int)x.shape[2]; a.D = (int)x.shape[3];
     a.bits = codec.bits; a.pos = pos; a.signs = codec.signs_dev;
     for (size_t i = 0; i < codec.boundaries.size() && i < 15; ++i) a.boundaries[i] = codec.boundaries[i];
-    if (codec.calib_dev) {
-        a.calib = codec.calib_dev;
+    a.calib = codec.calib_dev;
+    a.rotation = codec.rotation_dev;
+    if (a.calib || a.rotation)
         for (size_t i = 0; i < codec.centroids.size() && i < 16; ++i) a.centroids[i] = codec.centroids[i];
-    }
     return a;
 }
 
@@ -673,7 +753,7 @@ static std::vector<float> compute_key_calibration(kvc_cache *c, const kvc_tensor
     if (rows < 32) return {};
     Array4 dummy_p, dummy_n;
     TurboEncodeArgs a = turbo_args(keys, dummy_p, dummy_n, c->kcodec, 0);
-    a.calib = nullptr;
+    a.calib = nullptr;   // the statistic is taken on the uncalibrated rotation
     long long *sums = (long long *)dev_alloc((size_t)2 * D * sizeof(long long), s);
     KVC_CUDA(cudaMemsetAsync(sums, 0, (size_t)2 * D * sizeof(long long), s));
     launch_turbo_calib_stats(a, sums, s);
@@ -837,14 +917,16 @@ static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const 
         a.k = affine_source(c->kq.view(T), c->ks.view(T), c->kb.view(T), c->key_group, 8);
     } else {
         a.k = turbo_source(c->kp, c->kn, c->kcodec);
-        a.q_signs = c->kcodec.signs_dev;
+        a.q_signs = c->kcodec.rotation_dev ? nullptr : c->kcodec.signs_dev;
+        a.q_rot = c->kcodec.rotation_dev;
         a.q_calib = c->kcodec.calib_dev;   // folded into the rotated query (TurboQuantKVCache.swift:1348-1352)
     }
     if (c->affine_value) {
         a.v = affine_source(c->vq.view(T), c->vs.view(T), c->vb.view(T), c->key_group, c->value_bits);
     } else {
         a.v = turbo_source(c->vp, c->vn, c->vcodec);
-        a.o_signs = c->vcodec.signs_dev;
+        a.o_signs = c->vcodec.rotation_dev ? nullptr : c->vcodec.signs_dev;
+        a.o_rot = c->vcodec.rotation_dev;
     }
     launch_attention(a, s);
 }
@@ -1405,6 +1487,7 @@ kvc_cache *cache_copy(const kvc_cache *c, cudaStream_t s) {
     n->key_bits = c->key_bits; n->value_bits = c->value_bits; n->key_group = c->key_group;
     n->raw_key = c->raw_key; n->affine_key = c->affine_key; n->affine_value = c->affine_value;
     n->user_kc = c->user_kc; n->user_vc = c->user_vc; n->user_ks = c->user_ks; n->user_vs = c->user_vs;
+    n->user_kr = c->user_kr; n->user_vr = c->user_vr;
     int64_t rows = c->offset;
     if (c->cfg.kind == KVC_KIND_CHUNKED) {
         // KVCache.swift:1278-1287: the copy adopts `state` (rows up to the absolute offset, clamped to the

@@ -39,6 +39,10 @@ struct TurboCodec {
     // (TurboQuantKVCache.swift:688, computed at :867-886).
     std::vector<float> calib;
     float *calib_dev = nullptr;
+    // Dense rotation Pi, row-major [dim, dim], for head dims that are not powers of two
+    // (TurboQuantRotation.rotationMatrix, TurboQuantKVCache.swift:246-259); empty on the Walsh-Hadamard path.
+    std::vector<float> rotation;
+    float *rotation_dev = nullptr;
 };
 
 struct RestorePoint {
@@ -89,6 +93,7 @@ struct kvc_cache {
     kvc::TurboCodec kcodec, vcodec;
     bool codec_ready = false;
     std::vector<float> user_kc, user_vc, user_ks, user_vs;  // overrides
+    std::vector<float> user_kr, user_vr;                    // dense-rotation overrides [D * D]
 
     // host-call staging
     void *stage[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -148,6 +153,7 @@ int resolved_group_size(int requested, int kd, int vd);  // 0 when none fits
 void ensure_codecs(kvc_cache *c, int head_dim, cudaStream_t s);
 void turbo_codebook(int dim, int bits, std::vector<float> &centroids, std::vector<float> &bounds);
 void turbo_signs(int dim, uint64_t seed, std::vector<float> &signs);
+void turbo_rotation(int dim, uint64_t seed, std::vector<float> &rotation);   // row-major [dim, dim]
 
 // attention over explicit tensors
 AttnArgs make_attn_args(const kvc_tensor &q, const kvc_tensor &out, float scale, int32_t mask_mode,

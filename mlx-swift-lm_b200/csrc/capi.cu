@@ -1041,6 +1041,27 @@ kvc_status kvc_turbo_set_codec(kvc_cache *c, const float *key_centroids, const f
     });
 }
 
+kvc_status kvc_turbo_rotation(int32_t dim, uint64_t seed, float *rotation) {
+    return guarded([&] {
+        KVC_REQUIRE(dim >= 2 && dim <= 1024 && rotation, "kvc_turbo_rotation: bad arguments");
+        std::vector<float> r;
+        kvc::turbo_rotation(dim, seed, r);
+        std::memcpy(rotation, r.data(), r.size() * sizeof(float));
+    });
+}
+
+kvc_status kvc_turbo_set_rotation(kvc_cache *c, const float *key_rotation, const float *value_rotation, int32_t dim) {
+    KVC_CHECK_HANDLE(c);
+    return guarded([&] {
+        KVC_REQUIRE(c->cfg.kind == KVC_KIND_TURBO, "kvc_turbo_set_rotation needs a TurboQuantKVCache");
+        if (c->codec_ready) kvc::fail(KVC_ERR_INVALID_STATE, "kvc_turbo_set_rotation: the codec is already in use");
+        KVC_REQUIRE(dim >= 2 && dim <= 1024, "kvc_turbo_set_rotation: bad dim");
+        const size_t n = (size_t)dim * dim;
+        if (key_rotation) c->user_kr.assign(key_rotation, key_rotation + n);
+        if (value_rotation) c->user_vr.assign(value_rotation, value_rotation + n);
+    });
+}
+
 kvc_status kvc_turbo_encode(const kvc_tensor *rows, const float *signs_dev, const float *boundaries_host,
                             int32_t bits, const kvc_tensor *packed, const kvc_tensor *norms, void *stream) {
     if (!rows || !signs_dev || !boundaries_host || !packed || !norms)

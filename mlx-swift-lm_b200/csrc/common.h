@@ -134,6 +134,11 @@ struct AttnArgs {
     bool stored_rows_settled = false;
     const float *q_signs = nullptr;
     const float *q_calib = nullptr;  // optional per-dim key-calibration scale
+    // Dense rotations for head dims that are not powers of two (row-major [D, D] device matrices Pi):
+    // queries go through q' = Pi_k q, merged outputs through out = o' Pi_v (TurboQuantKVCache.swift:601-603,
+    // :1335-1338). Set instead of q_signs / o_signs.
+    const float *q_rot = nullptr;
+    const float *o_rot = nullptr;
     const float *o_signs = nullptr;
     int device = 0;
 };
@@ -252,7 +257,10 @@ struct TurboEncodeArgs {
     // row is divided by it before the boundary search and the stored norm becomes
     // norm / ||centroids[idx] * calib|| (fusedQuantizePackScaled, TurboQuantKernels.swift:354-411).
     const float *calib = nullptr;
-    float centroids[16] = {0};          // 2^bits used, only read with `calib`
+    float centroids[16] = {0};          // 2^bits used, read with `calib` and on the dense path
+    // Dense rotation (head dims that are not powers of two, fusedEncodeSource, TurboQuantKernels.swift:103-204):
+    // row-major [D, D] device matrix Pi, rotated = Pi * unit; the stored norm is norm / ||centroids[idx]||.
+    const float *rotation = nullptr;
 };
 void launch_turbo_encode(const TurboEncodeArgs &a, cudaStream_t stream);
 // Per-dimension fixed-point sums of the rotated unit rows of `a.src` for the calibration scale:

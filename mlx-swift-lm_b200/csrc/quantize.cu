@@ -578,6 +578,137 @@ __global__ void turbo_encode_kernel(TurboEncodeArgs ka, TurboEncodeArgs va, int6
     if (lane == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = stored;
 }
 
+// Dense-rotation encode for head dims that are not powers of two (fusedEncodeSource,
+// TurboQuantKernels.swift:103-204): one block per row, thread d owns dimension d. Norm over the fixed tree
+// (32 lanes x ceil(D/32) contiguous elements, then the xor butterfly), rotated[d] = sum_j Pi[d][j] * unit[j]
+// accumulated left to right with separate multiply and add, boundary count, packing, and the norm
+// correction norm / ||centroids[idx]|| over the same tree. With `calib` the rotated value is divided by
+// the scale first and the correction uses centroids[idx] * scale (TurboQuantKernels.swift:354-411).
+template <typename T>
+__global__ void turbo_encode_dense_kernel(TurboEncodeArgs a, int64_t total_rows) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    extern __shared__ float s_f[];           // [D] unit row, [D] tree scratch, then the packed words
+    const int D = a.D;
+    float *unit = s_f;
+    float *tree = s_f + D;
+    uint32_t *words = (uint32_t *)(s_f + 2 * D + 1);   // tree has one slot past the row
+    const int d = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    if (row >= total_rows) return;
+    int64_t r = row;
+    const int s = (int)(r % a.S);
+    r /= a.S;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
+    const int E = (D + 31) / 32;
+    const float val = d < D ? to_float<T>(src[(int64_t)d * a.s_sd]) : 0.f;
+
+    // sum over the fixed tree of a per-dimension quantity held in `tree`
+    auto tree_sum = [&](float mine) -> float {
+        if (d < D) tree[d] = mine;
+        __syncthreads();
+        float lane_sum = 0.f;
+        if (d < 32) {
+            bool first = true;
+            for (int i = 0; i < E; ++i) {
+                const int idx = d * E + i;
+                const float x = idx < D ? tree[idx] : 0.f;
+                lane_sum = first ? x : __fadd_rn(lane_sum, x);
+                first = false;
+            }
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) lane_sum = __fadd_rn(lane_sum, __shfl_xor_sync(0xffffffffu, lane_sum, m));
+            if (d == 0) tree[D] = lane_sum;      // one slot past the row
+        }
+        __syncthreads();
+        const float total = tree[D];
+        __syncthreads();
+        return total;
+    };
+
+    const float norm = __fsqrt_rn(tree_sum(__fmul_rn(val, val)));
+    const float inv_norm = (norm > 1e-8f) ? __fdiv_rn(1.0f, norm) : 0.0f;
+    if (d < D) unit[d] = __fmul_rn(val, inv_norm);
+    const int pw = (D * a.bits + 31) / 32;
+    for (int w = d; w < pw; w += blockDim.x) words[w] = 0;
+    __syncthreads();
+    uint32_t idx = 0;
+    float recon = 0.f;
+    if (d < D) {
+        const float *rot = a.rotation + (int64_t)d * D;
+        float acc = 0.f;
+        for (int j = 0; j < D; ++j) acc = __fadd_rn(acc, __fmul_rn(rot[j], unit[j]));
+        float cal = 1.f;
+        if (a.calib) {
+            cal = a.calib[d];
+            acc = __fdiv_rn(acc, cal);
+        }
+        const int levels_m1 = (1 << a.bits) - 1;
+        for (int bd = 0; bd < levels_m1; ++bd) idx += (acc > a.boundaries[bd]) ? 1u : 0u;
+        idx &= (uint32_t)levels_m1;
+        const float cv = a.calib ? __fmul_rn(a.centroids[idx], cal) : a.centroids[idx];
+        recon = __fmul_rn(cv, cv);
+        const int bit = d * a.bits;
+        const int w = bit >> 5, sh = bit & 31;
+        atomicOr(&words[w], idx << sh);
+        if (sh + a.bits > 32) atomicOr(&words[w + 1], idx >> (32 - sh));
+    }
+    const float recon_norm = __fsqrt_rn(tree_sum(recon));
+    const int64_t t = a.pos + s;
+    uint32_t *dst = a.packed + b * a.p_sb + h * a.p_sh + t * a.p_st;
+    for (int w = d; w < pw; w += blockDim.x) dst[w] = words[w];
+    if (d == 0) a.norms[b * a.n_sb + h * a.n_sh + t * a.n_st] = (recon_norm > 1e-8f) ? __fdiv_rn(norm, recon_norm) : norm;
+}
+
+// The calibration statistic on the dense path: thread d of a row's block adds its rotated value (computed
+// exactly as turbo_encode_dense_kernel computes it) to the fixed-point sums of dimension d.
+template <typename T>
+__global__ void turbo_calib_stats_dense_kernel(TurboEncodeArgs a, int64_t total_rows, unsigned long long *sums) {
+    extern __shared__ float s_f[];           // [D] unit row, [D + 1] tree scratch
+    const int D = a.D;
+    float *unit = s_f;
+    float *tree = s_f + D;
+    const int d = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    if (row >= total_rows) return;
+    int64_t r = row;
+    const int s = (int)(r % a.S);
+    r /= a.S;
+    const int h = (int)(r % a.H);
+    const int b = (int)(r / a.H);
+    const T *src = (const T *)a.src + b * a.s_sb + h * a.s_sh + s * a.s_ss;
+    const int E = (D + 31) / 32;
+    const float val = d < D ? to_float<T>(src[(int64_t)d * a.s_sd]) : 0.f;
+    if (d < D) tree[d] = __fmul_rn(val, val);
+    __syncthreads();
+    if (d < 32) {
+        float lane_sum = 0.f;
+        bool first = true;
+        for (int i = 0; i < E; ++i) {
+            const int idx = d * E + i;
+            const float x = idx < D ? tree[idx] : 0.f;
+            lane_sum = first ? x : __fadd_rn(lane_sum, x);
+            first = false;
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) lane_sum = __fadd_rn(lane_sum, __shfl_xor_sync(0xffffffffu, lane_sum, m));
+        if (d == 0) tree[D] = lane_sum;
+    }
+    __syncthreads();
+    const float norm = __fsqrt_rn(tree[D]);
+    const float inv_norm = (norm > 1e-8f) ? __fdiv_rn(1.0f, norm) : 0.0f;
+    if (d < D) unit[d] = __fmul_rn(val, inv_norm);
+    __syncthreads();
+    if (d < D) {
+        const float *rot = a.rotation + (int64_t)d * D;
+        float acc = 0.f;
+        for (int j = 0; j < D; ++j) acc = __fadd_rn(acc, __fmul_rn(rot[j], unit[j]));
+        atomicAdd(&sums[d], (unsigned long long)__float2ll_rn(__fmul_rn(acc, 1073741824.0f)));
+        atomicAdd(&sums[D + d], (unsigned long long)__float2ll_rn(__fmul_rn(__fmul_rn(acc, acc), 68719476736.0f)));
+    }
+}
+
 // Fixed-point per-dimension sums of the rotated unit rows (see launch_turbo_calib_stats). One warp per
 // row at a time, rows strided over the grid; a block folds its warps in shared memory and adds once
 // per dimension to the global sums. The rotated values are computed exactly as turbo_encode_kernel
@@ -876,8 +1007,32 @@ void turbo_dispatch(const TurboEncodeArgs &k, const TurboEncodeArgs &v, bool hav
 
 }  // namespace
 
+static void launch_turbo_encode_dense(const TurboEncodeArgs &a, cudaStream_t stream) {
+    const int64_t rows = (int64_t)a.B * a.H * a.S;
+    if (rows == 0) return;
+    KVC_REQUIRE(a.bits >= 1 && a.bits <= 4, "turbo encode supports 1..4 bits");
+    KVC_REQUIRE(a.D >= 2 && a.D <= 1024, "turbo encode (dense rotation) supports head dims up to 1024");
+    const int threads = std::max(32, ((a.D + 31) / 32) * 32);
+    const size_t smem = (size_t)(2 * a.D + 1) * sizeof(float) + (size_t)((a.D * a.bits + 31) / 32 + 1) * sizeof(uint32_t);
+    switch (a.dtype) {
+        case KVC_F32: turbo_encode_dense_kernel<float><<<(unsigned)rows, threads, smem, stream>>>(a, rows); break;
+        case KVC_F16: turbo_encode_dense_kernel<__half><<<(unsigned)rows, threads, smem, stream>>>(a, rows); break;
+        case KVC_BF16: turbo_encode_dense_kernel<__nv_bfloat16><<<(unsigned)rows, threads, smem, stream>>>(a, rows); break;
+        default: fail(KVC_ERR_INVALID_ARG, "turbo encode needs a floating dtype");
+    }
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+}
+
 void launch_turbo_encode2(const TurboEncodeArgs &k, const TurboEncodeArgs *v, cudaStream_t stream) {
     if ((int64_t)k.B * k.H * k.S == 0) return;
+    if (k.rotation || (v && v->rotation)) {
+        // dense rotations: one launch per tensor
+        KVC_REQUIRE(k.rotation && (!v || v->rotation), "turbo encode: keys and values must both use the dense rotation");
+        launch_turbo_encode_dense(k, stream);
+        if (v) launch_turbo_encode_dense(*v, stream);
+        return;
+    }
     KVC_REQUIRE(k.bits >= 1 && k.bits <= 4, "turbo encode supports 1..4 bits");
     KVC_REQUIRE(k.D >= 32 && k.D <= 1024 && (k.D & (k.D - 1)) == 0,
                 "turbo encode (Walsh-Hadamard path) needs a power-of-two head dim in [32, 1024]");
@@ -901,6 +1056,20 @@ void launch_turbo_encode(const TurboEncodeArgs &a, cudaStream_t stream) {
 void launch_turbo_calib_stats(const TurboEncodeArgs &a, long long *sums, cudaStream_t stream) {
     const int64_t rows = (int64_t)a.B * a.H * a.S;
     if (rows == 0) return;
+    if (a.rotation) {
+        const int threads = std::max(32, ((a.D + 31) / 32) * 32);
+        const size_t smem = (size_t)(2 * a.D + 1) * sizeof(float);
+        unsigned long long *o = reinterpret_cast<unsigned long long *>(sums);
+        switch (a.dtype) {
+            case KVC_F32: turbo_calib_stats_dense_kernel<float><<<(unsigned)rows, threads, smem, stream>>>(a, rows, o); break;
+            case KVC_F16: turbo_calib_stats_dense_kernel<__half><<<(unsigned)rows, threads, smem, stream>>>(a, rows, o); break;
+            case KVC_BF16: turbo_calib_stats_dense_kernel<__nv_bfloat16><<<(unsigned)rows, threads, smem, stream>>>(a, rows, o); break;
+            default: fail(KVC_ERR_INVALID_ARG, "key calibration needs a floating dtype");
+        }
+        KVC_CUDA(cudaGetLastError());
+        ++g_launch_count;
+        return;
+    }
     KVC_REQUIRE(a.D >= 32 && a.D <= 1024 && (a.D & (a.D - 1)) == 0,
                 "key calibration (Walsh-Hadamard path) needs a power-of-two head dim in [32, 1024]");
     const float inv_sqrt_dim = 1.0f / sqrtf((float)a.D);

@@ -173,6 +173,8 @@ _lib.kvc_storage_round_attention.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32
 _lib.kvc_storage_commit.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, _vp]
 _lib.kvc_speculate_rewind.argtypes = [ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                       ctypes.c_int32, ctypes.POINTER(ctypes.c_int64)]
+_lib.kvc_turbo_rotation.argtypes = [ctypes.c_int32, ctypes.c_uint64, ctypes.POINTER(ctypes.c_float)]
+_lib.kvc_turbo_set_rotation.argtypes = [_vp, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.c_int32]
 _lib.kvc_comm_init.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p, ctypes.POINTER(_vp)]
 _lib.kvc_comm_unique_id.argtypes = [ctypes.c_char_p]
 _lib.kvc_comm_symm_alloc.argtypes = [_vp, ctypes.c_size_t, _vp, ctypes.POINTER(_vp)]
@@ -609,6 +611,18 @@ class TurboQuantKVCache(KVCache):
         check(_lib.kvc_turbo_set_codec(self._h, arr(key_centroids), arr(value_centroids), arr(key_signs),
                                        arr(value_signs), dim))
 
+    def set_rotation(self, key_rotation=None, value_rotation=None, dim=0):
+        """Hand the cache the dense rotations a host already holds (row-major [dim, dim]); None keeps the default."""
+        import numpy as _np
+
+        def arr(x):
+            if x is None:
+                return None
+            a = _np.ascontiguousarray(x, dtype=_np.float32).reshape(-1)
+            return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), a
+        k, v = arr(key_rotation), arr(value_rotation)
+        check(_lib.kvc_turbo_set_rotation(self._h, k[0] if k else None, v[0] if v else None, dim))
+
     def encode_new_token(self, keys, values, stream=None):
         """Compressed-domain append of keys/values [B, H, S, D] (encodeNewToken); no attention."""
         tk, tv = as_tensor(keys), as_tensor(values)
@@ -781,6 +795,14 @@ def turbo_signs(dim: int, seed: int) -> List[float]:
     s = (ctypes.c_float * dim)()
     check(_lib.kvc_turbo_signs(dim, seed, s))
     return list(s)
+
+
+def turbo_rotation(dim: int, seed: int):
+    """The library's seeded dense rotation for head dims that are not powers of two, as a numpy [dim, dim] array."""
+    import numpy as _np
+    out = _np.zeros((dim, dim), dtype=_np.float32)
+    check(_lib.kvc_turbo_rotation(dim, seed, out.ctypes.data_as(ctypes.POINTER(ctypes.c_float))))
+    return out
 
 
 def turbo_packed_width(count: int, bits: int) -> int:

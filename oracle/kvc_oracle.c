@@ -281,6 +281,68 @@ void orc_turbo_encode_scaled(const void *x, int dtype, int64_t rows, int D, cons
     }
 }
 
+/* Dense-rotation encode for head dims that are not powers of two (fusedEncodeSource,
+ * TurboQuantKernels.swift:103-204; MSECodec.encode dense branch, TurboQuantKVCache.swift:549-554):
+ * rotated[d] = sum_j Pi[d][j] * unit[j] (left to right, separate multiply and add), boundary count,
+ * stored norm = norm / ||centroids[idx]|| (norm itself when that is <= 1e-8). With `scale` the rotated
+ * value is divided by it first and the correction uses centroids[idx] * scale. `scale` may be NULL. */
+void orc_turbo_encode_dense(const void *x, int dtype, int64_t rows, int D, const float *rotation,
+                            const float *boundaries, const float *centroids, const float *scale, int bits,
+                            uint32_t *packed, float *norms) {
+    const int pw = orc_packed_width(D, bits);
+    const int nb = (1 << bits) - 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float v[1024], recon[1024];
+        uint32_t idx[1024];
+        for (int d = 0; d < D; ++d) v[d] = ld(x, dtype, r * D + d);
+        const float norm = sqrtf(sum_squares_tree(v, D));
+        const float inv_norm = norm > 1e-8f ? 1.0f / norm : 0.0f;
+        for (int d = 0; d < D; ++d) v[d] = v[d] * inv_norm;
+        for (int d = 0; d < D; ++d) {
+            const float *rot = rotation + (size_t)d * D;
+            float acc = 0.f;
+            for (int j = 0; j < D; ++j) acc = acc + rot[j] * v[j];
+            if (scale) acc = acc / scale[d];
+            uint32_t k = 0;
+            for (int b = 0; b < nb; ++b) k += acc > boundaries[b] ? 1u : 0u;
+            idx[d] = k;
+            recon[d] = scale ? centroids[k] * scale[d] : centroids[k];
+        }
+        orc_pack(idx, 1, D, bits, packed + r * pw);
+        const float recon_norm = sqrtf(sum_squares_tree(recon, D));
+        norms[r] = recon_norm > 1e-8f ? norm / recon_norm : norm;
+    }
+}
+
+/* The calibration statistic on the dense path (same fixed-point sums as orc_turbo_calib_sums). */
+void orc_turbo_calib_sums_dense(const void *x, int dtype, int64_t rows, int D, const float *rotation, int64_t *sums) {
+    memset(sums, 0, sizeof(int64_t) * 2 * (size_t)D);
+#pragma omp parallel
+    {
+        int64_t *local = (int64_t *)calloc(2 * (size_t)D, sizeof(int64_t));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            float v[1024];
+            for (int d = 0; d < D; ++d) v[d] = ld(x, dtype, r * D + d);
+            const float norm = sqrtf(sum_squares_tree(v, D));
+            const float inv_norm = norm > 1e-8f ? 1.0f / norm : 0.0f;
+            for (int d = 0; d < D; ++d) v[d] = v[d] * inv_norm;
+            for (int d = 0; d < D; ++d) {
+                const float *rot = rotation + (size_t)d * D;
+                float acc = 0.f;
+                for (int j = 0; j < D; ++j) acc = acc + rot[j] * v[j];
+                const float sq = acc * acc;
+                local[d] += (int64_t)llrintf(acc * 1073741824.0f);
+                local[D + d] += (int64_t)llrintf(sq * 68719476736.0f);
+            }
+        }
+#pragma omp critical
+        for (int d = 0; d < 2 * D; ++d) sums[d] += local[d];
+        free(local);
+    }
+}
+
 /* First and second moments of the rotated unit rows per dimension, as
  * fixed-point integers (value * 2^30 and square * 2^36, each rounded to
  * nearest): the statistic under computeKeyCalibrationScale
@@ -402,6 +464,8 @@ typedef struct orc_attn {
     const float *q_calib;
     const float *o_signs;
     int32_t precise; /* 1: double accumulation (checker); 0: float (timed baseline) */
+    const float *q_rot; /* dense key rotation Pi [D, D]: q' = Pi q (instead of q_signs) */
+    const float *o_rot; /* dense value rotation: out = o' Pi (instead of o_signs) */
 } orc_attn;
 
 static inline float src_elem(const orc_source *s, int b, int h, int64_t t, int d) {
@@ -447,6 +511,27 @@ static void load_row(const orc_source *s, int b, int h, int64_t t, int D, float 
  * (batch, KV head) that decodes every cached K and V row once and serves all the query rows of the
  * head group from it, the way the reference's kernels share a KV head between its query heads
  * (TurboQuantKernels.swift:424-542) instead of decoding the row again for every query head. */
+/* q' = Pi q (dense forward rotation), in place with a scratch row */
+static void rotate_dense(const float *rot, float *x, int D, float *tmp) {
+    for (int d = 0; d < D; ++d) {
+        const float *r = rot + (size_t)d * D;
+        double acc = 0.0;
+        for (int j = 0; j < D; ++j) acc += (double)r[j] * (double)x[j];
+        tmp[d] = (float)acc;
+    }
+    memcpy(x, tmp, sizeof(float) * (size_t)D);
+}
+
+/* out = o' Pi (dense inverse rotation) */
+static void unrotate_dense(const float *rot, float *x, int D, float *tmp) {
+    for (int j = 0; j < D; ++j) {
+        double acc = 0.0;
+        for (int d = 0; d < D; ++d) acc += (double)x[d] * (double)rot[(size_t)d * D + j];
+        tmp[j] = (float)acc;
+    }
+    memcpy(x, tmp, sizeof(float) * (size_t)D);
+}
+
 static void attention_grouped(const orc_attn *a) {
     const int D = a->D, L = a->L;
     const int rep = a->Hq / a->Hkv;
@@ -475,6 +560,12 @@ static void attention_grouped(const orc_attn *a) {
                     const float f = 1.0f / sqrtf((float)D);
                     for (int d = 0; d < D; ++d) {
                         q[d] = q[d] * f * a->scale;
+                        if (a->q_calib) q[d] *= a->q_calib[d];
+                    }
+                } else if (a->q_rot) {
+                    rotate_dense(a->q_rot, q, D, kv);
+                    for (int d = 0; d < D; ++d) {
+                        q[d] = q[d] * a->scale;
                         if (a->q_calib) q[d] *= a->q_calib[d];
                     }
                 } else {
@@ -519,6 +610,8 @@ static void attention_grouped(const orc_attn *a) {
                     fwht_row(o, D);
                     const float f = 1.0f / sqrtf((float)D);
                     for (int d = 0; d < D; ++d) o[d] = o[d] * f * a->o_signs[d];
+                } else if (a->o_rot) {
+                    unrotate_dense(a->o_rot, o, D, kv);
                 }
                 for (int d = 0; d < D; ++d) st(a->out, a->q_dtype, qbase + d, o[d]);
             }
@@ -557,6 +650,12 @@ void orc_attention(const orc_attn *a) {
                 const float f = 1.0f / sqrtf((float)D);
                 for (int d = 0; d < D; ++d) {
                     qv[d] = qv[d] * f * a->scale;
+                    if (a->q_calib) qv[d] *= a->q_calib[d];
+                }
+            } else if (a->q_rot) {
+                rotate_dense(a->q_rot, qv, D, kv);
+                for (int d = 0; d < D; ++d) {
+                    qv[d] = qv[d] * a->scale;
                     if (a->q_calib) qv[d] *= a->q_calib[d];
                 }
             } else {
@@ -608,6 +707,8 @@ void orc_attention(const orc_attn *a) {
                 fwht_row(qv, D);
                 const float f = 1.0f / sqrtf((float)D);
                 for (int d = 0; d < D; ++d) qv[d] = qv[d] * f * a->o_signs[d];
+            } else if (a->o_rot) {
+                unrotate_dense(a->o_rot, qv, D, kv);
             }
             for (int d = 0; d < D; ++d) st(a->out, a->q_dtype, qbase + d, qv[d]);
         }

@@ -249,7 +249,53 @@ def turbo_encode_scaled(x: np.ndarray, signs: np.ndarray, boundaries: np.ndarray
     return packed, norms
 
 
-def key_calibration_scale(all_keys: np.ndarray, signs: np.ndarray) -> Optional[np.ndarray]:
+def rotation_matrix(dim: int, seed: int) -> np.ndarray:
+    """Seeded dense rotation for head dims that are not powers of two (TurboQuantRotation.rotationMatrix,
+    TurboQuantKVCache.swift:246-259: QR of a Gaussian matrix, columns flipped by the signs of R's diagonal).
+    The reference's draw comes from MLXRandom and MLX's QR (not reproducible here: parity unpinned); this
+    project's own recipe is Box-Muller normals from the splitmix64 stream, row-major, and a double-precision QR."""
+    mask = (1 << 64) - 1
+    x = seed & mask
+    n = dim * dim
+    vals = np.zeros(n + 1, dtype=np.float64)
+
+    def nxt():
+        nonlocal x
+        x = (x + 0x9E3779B97F4A7C15) & mask
+        z = x
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        z = z ^ (z >> 31)
+        return ((z >> 11) + 0.5) / 9007199254740992.0
+
+    for i in range(0, n, 2):
+        u1, u2 = nxt(), nxt()
+        r, t = np.sqrt(-2.0 * np.log(u1)), 6.283185307179586476925286766559 * u2
+        vals[i], vals[i + 1] = r * np.cos(t), r * np.sin(t)
+    a = vals[:n].reshape(dim, dim)
+    qm, rm = np.linalg.qr(a)
+    return (qm * np.sign(np.diag(rm))[None, :]).astype(np.float32)
+
+
+def turbo_encode_dense(x: np.ndarray, rotation: np.ndarray, boundaries: np.ndarray, centroids: np.ndarray, bits: int,
+                       scale: Optional[np.ndarray] = None):
+    """Dense-rotation encode (fusedEncodeSource, TurboQuantKernels.swift:103-204): norm-corrected norms."""
+    x = np.ascontiguousarray(x)
+    D = x.shape[-1]
+    rows = int(np.prod(x.shape[:-1], dtype=np.int64))
+    packed = np.zeros(x.shape[:-1] + (packed_width(D, bits),), dtype=np.uint32)
+    norms = np.zeros(x.shape[:-1], dtype=np.float32)
+    rotation = np.ascontiguousarray(rotation, dtype=np.float32)
+    boundaries = np.ascontiguousarray(boundaries, dtype=np.float32)
+    centroids = np.ascontiguousarray(centroids, dtype=np.float32)
+    sc = None if scale is None else np.ascontiguousarray(scale, dtype=np.float32)
+    if rows:
+        lib().orc_turbo_encode_dense(_p(x), dtype_code(x), ctypes.c_int64(rows), D, _p(rotation), _p(boundaries),
+                                     _p(centroids), _p(sc), bits, _p(packed), _p(norms))
+    return packed, norms
+
+
+def key_calibration_scale(all_keys: np.ndarray, signs: Optional[np.ndarray], rotation: Optional[np.ndarray] = None) -> Optional[np.ndarray]:
     """computeKeyCalibrationScale (TurboQuantKVCache.swift:867-886): per-dimension standard deviation of the
     rotated unit keys pooled over (batch, head, token), divided by its mean over the dimensions, clamped to
     [0.25, 4]; None with fewer than 32 rows or when every dimension is within 10 % of 1.
@@ -263,8 +309,12 @@ def key_calibration_scale(all_keys: np.ndarray, signs: np.ndarray) -> Optional[n
     if rows < 32:
         return None
     sums = np.zeros(2 * D, dtype=np.int64)
-    lib().orc_turbo_calib_sums(_p(x), dtype_code(x), ctypes.c_int64(rows), D,
-                               _p(np.ascontiguousarray(signs, dtype=np.float32)), _p(sums))
+    if rotation is not None:
+        lib().orc_turbo_calib_sums_dense(_p(x), dtype_code(x), ctypes.c_int64(rows), D,
+                                         _p(np.ascontiguousarray(rotation, dtype=np.float32)), _p(sums))
+    else:
+        lib().orc_turbo_calib_sums(_p(x), dtype_code(x), ctypes.c_int64(rows), D,
+                                   _p(np.ascontiguousarray(signs, dtype=np.float32)), _p(sums))
     mean = sums[:D].astype(np.float64) / 1073741824.0 / float(rows)
     ex2 = sums[D:].astype(np.float64) / 68719476736.0 / float(rows)
     sd = np.sqrt(np.maximum(ex2 - mean * mean, 0.0)).astype(np.float32)
@@ -291,7 +341,8 @@ class _Attn(ctypes.Structure):
                 ("mask_mode", ctypes.c_int32), ("mask_dtype", ctypes.c_int32), ("mask", ctypes.c_void_p),
                 ("msb", ctypes.c_int64), ("msh", ctypes.c_int64), ("msl", ctypes.c_int64), ("mst", ctypes.c_int64),
                 ("causal_offset", ctypes.c_int64), ("q_signs", ctypes.c_void_p), ("q_calib", ctypes.c_void_p),
-                ("o_signs", ctypes.c_void_p), ("precise", ctypes.c_int32)]
+                ("o_signs", ctypes.c_void_p), ("precise", ctypes.c_int32),
+                ("q_rot", ctypes.c_void_p), ("o_rot", ctypes.c_void_p)]
 
 
 def _estrides(a: np.ndarray):
@@ -349,7 +400,7 @@ def _fill_source(dst: _Source, src, keep: list):
 
 
 def attention(q: np.ndarray, k_src, v_src, scale: float, mask="none", *, q_signs=None, q_calib=None,
-              o_signs=None, precise: bool = True) -> np.ndarray:
+              o_signs=None, q_rot=None, o_rot=None, precise: bool = True) -> np.ndarray:
     """softmax(scale * q k^T + mask) v over any cache representation.
 
     q [B, Hq, L, D] in storage dtype; returns the same shape and dtype.
@@ -385,7 +436,7 @@ def attention(q: np.ndarray, k_src, v_src, scale: float, mask="none", *, q_signs
         keep.append(m)
         a.mask_mode, a.mask = 2, m.ctypes.data
         a.msb, a.msh, a.msl, a.mst = _estrides(m)
-    for name, arr in (("q_signs", q_signs), ("q_calib", q_calib), ("o_signs", o_signs)):
+    for name, arr in (("q_signs", q_signs), ("q_calib", q_calib), ("o_signs", o_signs), ("q_rot", q_rot), ("o_rot", o_rot)):
         if arr is not None:
             arr = np.ascontiguousarray(arr, dtype=np.float32)
             keep.append(arr)
@@ -946,28 +997,44 @@ class MSECodec:
     seed: int = 42
     codebook: np.ndarray = field(default=None)  # type: ignore[assignment]
     signs: np.ndarray = field(default=None)     # type: ignore[assignment]
+    rotation: np.ndarray = field(default=None)  # type: ignore[assignment]  dense Pi [D, D], non-power-of-two dims
 
     def __post_init__(self):
         if self.codebook is None:
             self.codebook = codebook(self.dim, self.bits)
-        if self.signs is None:
-            self.signs = wht_signs(self.dim, self.seed)
+        # MSECodec.init (:459-486): Walsh-Hadamard for power-of-two dims up to 1024, dense otherwise
+        self.use_wht = self.dim > 0 and (self.dim & (self.dim - 1)) == 0 and self.dim <= 1024
+        if self.use_wht:
+            if self.signs is None:
+                self.signs = wht_signs(self.dim, self.seed)
+            self.rotation = None
+        else:
+            if self.rotation is None:
+                self.rotation = rotation_matrix(self.dim, self.seed)
+            self.signs = None
         self.boundaries = boundaries_of(self.codebook)
 
     def encode(self, x: np.ndarray, scale: Optional[np.ndarray] = None):
+        if not self.use_wht:
+            return turbo_encode_dense(x, self.rotation, self.boundaries, self.codebook, self.bits, scale)
         if scale is not None:
             return turbo_encode_scaled(x, self.signs, self.boundaries, self.codebook, scale, self.bits)
         return turbo_encode(x, self.signs, self.boundaries, self.bits)
 
     def rotate(self, x_f32: np.ndarray) -> np.ndarray:
-        """x . Pi^T = H(signs * x) / sqrt(D)."""
+        """x . Pi^T = H(signs * x) / sqrt(D), or the dense product."""
+        if not self.use_wht:
+            return (x_f32.astype(np.float64) @ self.rotation.astype(np.float64).T).astype(np.float32)
         return fwht(x_f32 * self.signs) * np.float32(1.0 / np.sqrt(np.float32(self.dim)))
 
     def decode(self, packed: np.ndarray, norms: np.ndarray) -> np.ndarray:
         """MSECodec.decode (:573-588): codebook lookup, inverse rotation, norm rescale."""
         idx = unpack_low_bit(packed, self.bits, self.dim)
         approx = self.codebook[idx]
-        un = fwht(approx) * np.float32(1.0 / np.sqrt(np.float32(self.dim))) * self.signs
+        if not self.use_wht:
+            un = (approx.astype(np.float64) @ self.rotation.astype(np.float64)).astype(np.float32)
+        else:
+            un = fwht(approx) * np.float32(1.0 / np.sqrt(np.float32(self.dim))) * self.signs
         return norms[..., None] * un
 
 
@@ -1088,7 +1155,7 @@ class TurboQuantKVCache(BaseKVCache):
         self.raw_keys = None if not self.raw_key_mode else keep_raw
         if not self.raw_key_mode and not self.affine_key_mode:
             # computed once from the whole raw key cache, reused by every later encode (:960-962)
-            self.key_calib_scale = key_calibration_scale(ak, self.key_codec.signs)
+            self.key_calib_scale = key_calibration_scale(ak, self.key_codec.signs, self.key_codec.rotation)
         self._encode_rows(ak, av, 0)
         self.raw_values = None
         self.is_compressed = True
@@ -1120,14 +1187,20 @@ class TurboQuantKVCache(BaseKVCache):
             ks = AffineSource(*(a[:, :, :T] for a in self.aff_key), self.key_group_size, 8)
         else:
             ks = TurboSource(self.key_packed[:, :, :T], self.key_norms[:, :, :T], self.key_codec.codebook, self.key_bits)
-            kw["q_signs"] = self.key_codec.signs
+            if self.key_codec.use_wht:
+                kw["q_signs"] = self.key_codec.signs
+            else:
+                kw["q_rot"] = self.key_codec.rotation
             if self.key_calib_scale is not None:
                 kw["q_calib"] = self.key_calib_scale    # folded into the rotated query (:1348-1352)
         if self.affine_values:
             vs = AffineSource(*(a[:, :, :T] for a in self.aff_val), self.key_group_size, self.value_bits)
         else:
             vs = TurboSource(self.val_packed[:, :, :T], self.val_norms[:, :, :T], self.value_codec.codebook, self.value_bits)
-            kw["o_signs"] = self.value_codec.signs
+            if self.value_codec.use_wht:
+                kw["o_signs"] = self.value_codec.signs
+            else:
+                kw["o_rot"] = self.value_codec.rotation
         return attention(q, ks, vs, scale, mask, precise=precise, **kw)
 
     @property

@@ -250,3 +250,57 @@ def test_outlier_channels_do_not_calibrate(kvc, oracle, cuda):
     for a, b in zip(g.state, o.state):
         assert bits_equal(a, np.ascontiguousarray(b))
     assert max_abs_diff(out, ref) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D,kw", [(80, dict(bits=4)), (96, dict(bits=4, key_bits=3, value_bits=4)), (80, dict(bits=3)),
+                                  (96, dict(bits=4, key_bits=0, value_bits=4))],
+                         ids=["d80-turbo4", "d96-k3v4", "d80-turbo3", "d96-rawk-v4"])
+def test_dense_rotation_codec_for_other_head_dims(kvc, oracle, cuda, tmp_path, dtype, D, kw):
+    """Head dims that are not powers of two (the reference pre-populates 80 and 96 for real models,
+    TurboQuantKVCache.swift:98-110) take the dense random rotation and the norm-corrected encode
+    (fusedEncodeSource, TurboQuantKernels.swift:103-204). Both sides are handed the same rotation matrices
+    (the oracle's QR; the library's own generator is checked against it below): packed indices and
+    corrected norms bit-exact, raw prefill -> compress -> decode -> verify chunk -> array mask in tolerance."""
+    B, Hq, Hkv, P = 2, 8, 2, 150
+    scale = D ** -0.5
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    kr, vr = oracle.rotation_matrix(D, 42), oracle.rotation_matrix(D, 43)
+    g.set_rotation(kr, vr, D)
+    q, k, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype), seeded((B, Hkv, P, D), 3, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    for step in range(6):
+        q, k, v = (seeded((B, Hq, 1, D), 10 + 3 * step, dtype), seeded((B, Hkv, 1, D), 11 + 3 * step, dtype),
+                   seeded((B, Hkv, 1, D), 12 + 3 * step, dtype))
+        out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"decode step {step}"
+    assert g.is_compressed and g.offset == o.offset == P + 6
+    gs, os_ = g.state, o.state
+    assert len(gs) == len(os_)
+    for a, b in zip(gs, os_):
+        assert tuple(a.shape) == tuple(b.shape) and bits_equal(a, np.ascontiguousarray(b))
+    q, k, v = seeded((B, Hq, 6, D), 90, dtype), seeded((B, Hkv, 6, D), 91, dtype), seeded((B, Hkv, 6, D), 92, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+    assert max_abs_diff(out, ref) <= TOL[dtype], "verify chunk"
+    mask = torch.ones((1, 1, 1, g.offset + 1), dtype=torch.bool)
+    mask[..., ::3] = False
+    q, k, v = seeded((B, Hq, 1, D), 95, dtype), seeded((B, Hkv, 1, D), 96, dtype), seeded((B, Hkv, 1, D), 97, dtype)
+    out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, mask.to(cuda))
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, mask.numpy())
+    assert max_abs_diff(out, ref) <= TOL[dtype], "array mask"
+    for a, b in zip(g.state, o.state):
+        assert bits_equal(a, np.ascontiguousarray(b))
+    assert kvc.device_status() == 0
+
+
+def test_library_rotation_generator(kvc, oracle):
+    """The library's own dense rotation (splitmix64 + Box-Muller + Householder QR in double precision) is
+    orthogonal and equals the oracle's restatement of the same recipe up to float32 rounding."""
+    for D, seed in ((80, 42), (96, 43), (24, 7), (160, 9)):
+        r = kvc.turbo_rotation(D, seed)
+        assert np.abs(r.astype(np.float64) @ r.astype(np.float64).T - np.eye(D)).max() < 1e-6
+        assert np.abs(r - oracle.rotation_matrix(D, seed)).max() < 1e-6
