@@ -216,7 +216,8 @@ template <int D, int NWARPS>
 __device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float *red_ml, int red_stride,
                               float *work, int *flag, int b, int hk, int rep, int R, int split, int bh) {
     const int tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L;  // the group's rows are consecutive query rows
+    constexpr int row0 = 0;  // a unit of this epilogue always carries the whole group
+    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L + row0;  // the group's rows are consecutive query rows
     for (int i = tid; i < R * D; i += nthreads) {
         const int r = i / D, d = i % D;
         float m = -INFINITY;
@@ -271,7 +272,7 @@ __device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float 
             float o = 0.f;
             const float *src = u.o_part + ((qrow0 + r) * u.splits) * D + d;
             for (int s = 0; s < u.splits; ++s) o = fmaf(__ldcg(src + (int64_t)s * D), work[r * u.splits + s], o);
-            const int hq = hk * rep + r / u.L, lq = r % u.L;
+            const int hq = hk * rep + (row0 + r) / u.L, lq = (row0 + r) % u.L;
             store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, o);
         }
         return;
@@ -299,7 +300,7 @@ __device__ void unit_epilogue(const UnitOut &u, const float *red_o, const float 
     const float f = rsqrtf((float)D);
     for (int i = tid; i < R * D; i += nthreads) {
         const int r = i / D, d = i % D;
-        const int hq = hk * rep + r / u.L, lq = r % u.L;
+        const int hq = hk * rep + (row0 + r) / u.L, lq = (row0 + r) % u.L;
         store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, rows[i] * f * u.o_signs[d]);
     }
 }
@@ -342,7 +343,9 @@ __device__ __forceinline__ void consumer_bar() {
 template <int D, int NW, int NBUF = NW>
 __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const float *red_o, const float *red_ml,
                                  int red_stride, float *work, int *flag, int unit, int b, int hk, int rep, int R,
-                                 int64_t x_unit = -1, int unit_tiles = 0) {
+                                 int64_t x_unit = -1, int unit_tiles = 0, int row0 = 0) {
+    // row0: the unit covers the query rows row0 .. row0 + R - 1 of its (batch, kv head) group (a group
+    // of more rows than one unit carries is cut into several units)
     const int tid = threadIdx.x;
     constexpr int NT = NW * 32;
     consumer_bar<NW>();
@@ -354,7 +357,7 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
     const int first_cta = flat_cta_of(f, x_unit);
     const int expected = flat_cta_of(f, x_unit + unit_tiles - 1) - first_cta + 1;
     const int slot = (int)blockIdx.x - first_cta;
-    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L;
+    const int64_t qrow0 = ((int64_t)b * u.Hq + hk * rep) * u.L + row0;
     for (int i = tid; i < R * D; i += NT) {
         const int r = i / D, d = i % D;
         float m = -INFINITY;
@@ -417,7 +420,7 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
             }
             o = lsum > 0.f ? o / lsum : 0.f;
             if (!u.o_signs) {
-                const int hq = hk * rep + r / u.L, lq = r % u.L;
+                const int hq = hk * rep + (row0 + r) / u.L, lq = (row0 + r) % u.L;
                 store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, o);
             } else {
                 rows[i] = o;
@@ -439,7 +442,7 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
             const float fs = rsqrtf((float)D);
             for (int i = tid; i < R * D; i += NT) {
                 const int r = i / D, d = i % D;
-                const int hq = hk * rep + r / u.L, lq = r % u.L;
+                const int hq = hk * rep + (row0 + r) / u.L, lq = (row0 + r) % u.L;
                 store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, rows[i] * fs * u.o_signs[d]);
             }
         }

@@ -503,17 +503,18 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     if (a.k.kind != SRC_TURBO || a.v.kind != SRC_TURBO) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv) return 0;
     const int rep = a.Hq / a.Hkv;
-    if (rep * a.L > 8 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    if (a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     if (!turbo_source_fits(a.k, a.D, a.T) || !turbo_source_fits(a.v, a.D, a.T)) return 0;
     if (((uintptr_t)a.q & 1)) return 0;
     const int kb = a.k.bits, vb = a.v.bits;
-    const bool known = (kb == 4 && vb == 4) || (kb == 4 && vb == 2) || (kb == 3 && vb == 3) || (kb == 2 && vb == 2) ||
-                       (kb == 3 && vb == 4);
-    if (!known) return 0;
-    if (vb == 4) {
+    if (vb == 4) {   // key bits 2..4; also takes short chunks (up to 64 query rows per kv head), eight rows at a time
         const int n = launch_attention_turbo_v4(a, stream);
         if (n > 0) return n;
     }
+    const bool known = (kb == 4 && vb == 4) || (kb == 4 && vb == 2) || (kb == 3 && vb == 3) || (kb == 2 && vb == 2) ||
+                       (kb == 3 && vb == 4);
+    if (!known) return 0;
+    if (rep * a.L > 8) return 0;
     const int64_t bh = (int64_t)a.B * a.Hkv;
     if (bh * (int64_t)sizeof(int) > TQ_COUNTER_BYTES) return 0;
     int *status = device_status_word(a.device);

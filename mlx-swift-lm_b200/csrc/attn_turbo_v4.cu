@@ -10,9 +10,12 @@
 // laid over the SM, because the step is bound by the shared-memory pipe and by instruction
 // issue, not by HBM:
 //
-//  * ONE CTA per SM with 16 consumer warps (four groups of four; group i takes every fourth
-//    64-token stage of the ring) and one producer lane, so that the lookup tables exist once
-//    per SM and 16 warps hide each other's table-lookup latency.
+//  * ONE CTA per SM with 16 consumer warps sharing 256-token stages and four producer warps
+//    (one per array of a stage: a thread's bulk copies issue one after the other, and small
+//    copies are bound by issue, not by bytes), so that the lookup tables exist once per SM and
+//    16 warps hide each other's table-lookup latency. A group of more than eight query rows
+//    (a verify chunk) is cut into units of eight rows that stream the same tiles one after
+//    the other (all but the first out of L2).
 //  * Value operands without a transpose. The P V product runs as O^T = V^T P^T (head dims on
 //    the 16-row side), whose A operand pairs TWO TOKENS of one head dim in a register. A lane
 //    loads the same 16 dims (two words) of its four tokens, interleaves the nibbles of a token
@@ -30,6 +33,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 
 namespace kvc {
@@ -44,7 +48,8 @@ using namespace dev;
 constexpr int V4_WARPS = 16;                       // consumer warps
 constexpr int V4_GW = KVC_V4_GROUP_WARPS;          // warps that share a ring stage (16 tokens each)
 constexpr int V4_GROUPS = V4_WARPS / V4_GW;        // warp groups; group i takes every V4_GROUPS-th stage
-constexpr int V4_THREADS = (V4_WARPS + 1) * 32;    // + the producer warp
+constexpr int V4_PRODUCERS = 4;                    // producer warps: one per array of a stage (a thread's bulk copies issue one after the other)
+constexpr int V4_THREADS = (V4_WARPS + V4_PRODUCERS) * 32;
 constexpr int V4_TILE = 16 * V4_GW;                // tokens per ring stage
 constexpr int V4_D = 128;
 constexpr int V4_VW = 16;                         // value words per row (4 bits)
@@ -52,6 +57,7 @@ constexpr int V4_MAX_STAGES = 12;                 // of 64 tokens; fewer when a 
 constexpr int V4_TABLE_BYTES = 256 * 256;
 constexpr int V4_SLOT_FLOATS = 36 * 32;           // one warp's accumulators: 32 outputs + 2 maxima + 2 sums per lane
 constexpr int V4_COUNTER_BYTES = 64 * 1024;
+constexpr int V4_MAX_CHUNKS = 8;                  // up to 64 query rows per (batch, kv head)
 constexpr int V4_RED_STRIDE = V4_D + 8;
 
 struct TurboV4Params {
@@ -70,6 +76,7 @@ struct TurboV4Params {
     int *counters;
     int *status;
     int32_t B, Hq, Hkv, L;
+    int32_t chunks;      // units per (batch, kv head): ceil(query rows of the group / 8)
     int64_t T;
     int32_t causal;
     int32_t out_dtype;
@@ -141,7 +148,7 @@ __device__ __forceinline__ uint32_t key_entry(const uint32_t (&w)[NW], int j, ui
     return (x & MASK) | lane_const;
 }
 
-template <typename T, int KB>
+template <typename T, int KB, bool CHUNKED>
 __global__ void __launch_bounds__(V4_THREADS, 1)
 attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
     constexpr int D = V4_D;
@@ -195,15 +202,15 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
     int *is_last = (int *)(qempty + 2);
 
     const int rep = p.Hq / p.Hkv;
-    const int R = rep * p.L;  // <= 8
+    const int R_all = rep * p.L;   // query rows of a (batch, kv head) group, cut into p.chunks units of eight
     const int tiles = fp.tiles;
     const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
-    const uint32_t q_bytes = (uint32_t)R * D * 2;
+    const uint32_t q_bytes = (uint32_t)R_all * D * 2;   // bulk staging only runs with one chunk
 
     if (tid == 0) {
         for (int s = 0; s < nstage; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], V4_GW);      // the warps of the stage's group
+            mbar_init(&full[s], V4_PRODUCERS);
+            mbar_init(&empty[s], V4_GW);            // the warps of the stage's group
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&qfull[s], 1);
@@ -228,50 +235,47 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
 
     bool ok = true;
 
-    if (warp == V4_WARPS) {
-        // ---------------- producer: one stream of tiles across the segments ----------------
-        // Lanes 0..3 each issue one of a stage's four copies (packed keys, packed values, key norms,
-        // value norms) in the same instruction; lane 0 alone talks to the barriers.
-        if (lane < 4 && !(KVC_SKIP_BITS(p) & 2)) {   // measurement bit 2: no loads at all (consumers compute on stale stages)
+    if (warp >= V4_WARPS) {
+        // ---------------- producers: one stream of tiles across the segments ----------------
+        // Four warps, one lane each: warp i issues copy i of every stage (packed keys, packed values,
+        // key norms, value norms) and announces its bytes on the stage's barrier (four arrivals fill
+        // it); the copies of one thread issue one after the other, those of different warps overlap.
+        // The first producer also stages the query rows of each segment.
+        const int pw = warp - V4_WARPS;
+        if (lane == 0 && !(KVC_SKIP_BITS(p) & 2)) {   // measurement bit 2: no loads at all (consumers compute on stale stages)
             int it = 0, sg = 0;
             for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 const int unit = (int)(x / tiles), tb = (int)(x % tiles);
                 const int n = (int)min((int64_t)(tiles - tb), x_hi - x);
-                const int hk = unit % p.Hkv, b = unit / p.Hkv;
-                if (p.q_bulk) {
+                const int bh = CHUNKED ? unit / p.chunks : unit;
+                const int hk = bh % p.Hkv, b = bh / p.Hkv;
+                if (p.q_bulk && pw == 0) {
                     const int qb = sg & 1;
-                    if (lane == 0) {
-                        if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
-                        if (ok) {
-                            mbar_expect_tx(&qfull[qb], q_bytes);
-                            bulk_load(qbuf + (size_t)qb * (8 * D * 2), (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh,
-                                      q_bytes, &qfull[qb]);
-                        }
-                    }
-                    ok = __shfl_sync(0xFu, ok ? 1 : 0, 0) != 0;
+                    if (sg >= 2) ok = mbar_wait(&qempty[qb], ((sg >> 1) - 1) & 1);
                     if (!ok) break;
+                    mbar_expect_tx(&qfull[qb], q_bytes);
+                    bulk_load(qbuf + (size_t)qb * (8 * D * 2), (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh,
+                              q_bytes, &qfull[qb]);
                 }
-                // this lane's array: source of token 0 of the unit, bytes per token, offset inside a stage
+                // this warp's array: source of token 0 of the unit, bytes per token, offset inside a stage
                 const unsigned char *src;
                 uint32_t per_token, dst_off;
-                if (lane == 0) { src = (const unsigned char *)(p.kp + b * p.kp_sb + hk * p.kp_sh); per_token = KW * 4; dst_off = 0; }
-                else if (lane == 1) { src = (const unsigned char *)(p.vp + b * p.vp_sb + hk * p.vp_sh); per_token = V4_VW * 4; dst_off = K_TILE; }
-                else if (lane == 2) { src = (const unsigned char *)(p.kn + b * p.kn_sb + hk * p.kn_sh); per_token = 4; dst_off = K_TILE + V_TILE; }
+                if (pw == 0) { src = (const unsigned char *)(p.kp + b * p.kp_sb + hk * p.kp_sh); per_token = KW * 4; dst_off = 0; }
+                else if (pw == 1) { src = (const unsigned char *)(p.vp + b * p.vp_sb + hk * p.vp_sh); per_token = V4_VW * 4; dst_off = K_TILE; }
+                else if (pw == 2) { src = (const unsigned char *)(p.kn + b * p.kn_sb + hk * p.kn_sh); per_token = 4; dst_off = K_TILE + V_TILE; }
                 else { src = (const unsigned char *)(p.vn + b * p.vn_sb + hk * p.vn_sh); per_token = 4; dst_off = K_TILE + V_TILE + N_TILE; }
+                const uint32_t bytes = per_token * V4_TILE;
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % nstage;
-                    if (lane == 0) {
-                        if (it >= nstage) ok = mbar_wait(&empty[s], ((it / nstage) - 1) & 1);
-                        if (ok) mbar_expect_tx(&full[s], STAGE_BYTES);
-                    }
-                    ok = __shfl_sync(0xFu, ok ? 1 : 0, 0) != 0;   // also orders the copies after the expect_tx
+                    if (it >= nstage) ok = mbar_wait(&empty[s], ((it / nstage) - 1) & 1);
                     if (!ok) break;
+                    mbar_expect_tx(&full[s], bytes);
                     const int64_t t0 = (int64_t)(tb + j) * V4_TILE;
-                    bulk_load(stages + (size_t)s * STAGE_BYTES + dst_off, src + t0 * per_token, per_token * V4_TILE, &full[s]);
+                    bulk_load(stages + (size_t)s * STAGE_BYTES + dst_off, src + t0 * per_token, bytes, &full[s]);
                 }
                 x += n;
             }
-            if (!ok && lane == 0) atomicExch(p.status, 32);
+            if (!ok) atomicExch(p.status, 32);
         }
         return;
     }
@@ -294,7 +298,9 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
     for (int64_t x = x_lo; x < x_hi; ++sg) {
         const int unit = (int)(x / tiles), tile_begin = (int)(x % tiles);
         const int ntiles = (int)min((int64_t)(tiles - tile_begin), x_hi - x);
-        const int hk = unit % p.Hkv, b = unit / p.Hkv;
+        const int bh = CHUNKED ? unit / p.chunks : unit, row0 = CHUNKED ? (unit % p.chunks) * 8 : 0;
+        const int hk = bh % p.Hkv, b = bh / p.Hkv;
+        const int R = CHUNKED ? min(8, R_all - row0) : R_all;
         // ---- rotated queries of this unit: q' = H(signs * q) / sqrt(D) * scale * log2(e), rows past R zero ----
         const T *q_stage = nullptr;
         if (p.q_bulk) {
@@ -308,7 +314,7 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
             const int r = i / D, d = i % D;
             float xq = 0.f;
             if (r < R && ok) {
-                const int hq = hk * rep + r / p.L, l = r % p.L;
+                const int hq = hk * rep + (row0 + r) / p.L, l = (row0 + r) % p.L;
                 const T qv = q_stage ? q_stage[r * D + d] : ((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d];
                 xq = to_f32<T>(qv) * p.q_signs[d];
             }
@@ -353,7 +359,7 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int r = 2 * c + k;
-            const int l = (r < R) ? r % p.L : 0;
+            const int l = (r < R) ? (row0 + r) % p.L : 0;
             row_limit[k] = p.causal ? (int)min((int64_t)t_last, p.causal_offset + l) : t_last;
         }
         const int min_limit = p.causal ? (int)min((int64_t)t_last, p.causal_offset) : t_last;
@@ -577,12 +583,12 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
         u.o_sb = p.o_sb; u.o_sh = p.o_sh; u.o_sl = p.o_sl;
         u.o_signs = p.o_signs;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
-        segment_epilogue<D, V4_WARPS, 4>(u, fp, red_o, red_ml, V4_RED_STRIDE, work, is_last, unit, b, hk, rep, R);
+        segment_epilogue<D, V4_WARPS, 4>(u, fp, red_o, red_ml, V4_RED_STRIDE, work, is_last, unit, b, hk, rep, R, -1, 0, row0);
         x += ntiles;
     }
 }
 
-template <typename T, int KB>
+template <typename T, int KB, bool CHUNKED>
 bool launch_v4_typed(const TurboV4Params &p, int ctas, size_t smem, cudaStream_t stream) {
     // 0 = not yet, 1 = ready, -1 = the device refused the shared memory
     static std::atomic<int> configured[64];
@@ -590,16 +596,16 @@ bool launch_v4_typed(const TurboV4Params &p, int ctas, size_t smem, cudaStream_t
     if (dev < 0 || dev >= 64) return false;
     int state = configured[dev].load(std::memory_order_acquire);
     if (state == 0) {
-        cudaError_t e = cudaFuncSetAttribute(attn_turbo_v4_kernel<T, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_turbo_v4_kernel<T, KB, CHUNKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_turbo_v4_kernel<T, KB>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+            e = cudaFuncSetAttribute(attn_turbo_v4_kernel<T, KB, CHUNKED>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) (void)cudaGetLastError();
         state = e == cudaSuccess ? 1 : -1;
         configured[dev].store(state, std::memory_order_release);
     }
     if (state < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_turbo_v4_kernel<T, KB>, dim3(ctas), dim3(V4_THREADS), smem, stream, p));
+    KVC_CUDA(launch_pdl(attn_turbo_v4_kernel<T, KB, CHUNKED>, dim3(ctas), dim3(V4_THREADS), smem, stream, p));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
     ++g_launch_count;
@@ -620,7 +626,12 @@ int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream) {
     const int kb = a.k.bits, vb = a.v.bits;
     if (vb != 4 || kb < 2 || kb > 4) return 0;
     const int rep = a.Hq / a.Hkv;
-    const int64_t bh = (int64_t)a.B * a.Hkv;
+    // a group of more than eight query rows (a verify chunk) is cut into units of eight rows; the
+    // units of one (batch, kv head) are neighbours in the flat order, so they stream the same tiles
+    // at about the same time and all but the first find them in L2
+    const int chunks = (rep * a.L + 7) / 8;
+    if (chunks > V4_MAX_CHUNKS) return 0;
+    const int64_t bh = (int64_t)a.B * a.Hkv * chunks;
     if (bh * (int64_t)sizeof(int) > V4_COUNTER_BYTES) return 0;
     {
         // a full last stage must stay inside the (batch, head) slab
@@ -634,7 +645,7 @@ int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream) {
     const int64_t tiles = (a.T + V4_TILE - 1) / V4_TILE;
     FlatPlan plan;
     plan.tiles = (int)tiles;
-    plan.red_rows = rep * a.L;
+    plan.red_rows = std::min(8, rep * a.L);
     const int64_t work_tiles = bh * tiles;
     const int64_t ctas = std::min<int64_t>((int64_t)sm_count(a.device), work_tiles);
     plan.per = (int)(work_tiles / ctas);
@@ -662,12 +673,12 @@ int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream) {
     p.o_part = (float *)scratch;
     p.ml_part = (float2 *)(scratch + ((o_bytes + 255) / 256) * 256);
     p.counters = counters; p.status = status;
-    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.T = a.T; p.chunks = chunks;
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.flat = plan;
-    p.q_bulk = (a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
+    p.q_bulk = (chunks == 1 && a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
     // everything an SM offers a CTA: 227 KB opt-in maximum
     const size_t smem = (size_t)227 * 1024;
     p.smem_bytes = (uint32_t)smem;
@@ -675,13 +686,15 @@ int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream) {
 
     bool taken = false;
 #define KVC_V4(TT, KK) \
-    if (kb == KK) taken = launch_v4_typed<TT, KK>(p, (int)ctas, smem, stream);
+    if (kb == KK) taken = chunks > 1 ? launch_v4_typed<TT, KK, true>(p, (int)ctas, smem, stream) \
+                                     : launch_v4_typed<TT, KK, false>(p, (int)ctas, smem, stream);
     if (a.q_dtype == KVC_BF16) {
         KVC_V4(__nv_bfloat16, 2) KVC_V4(__nv_bfloat16, 3) KVC_V4(__nv_bfloat16, 4)
     } else {
         KVC_V4(__half, 2) KVC_V4(__half, 3) KVC_V4(__half, 4)
     }
 #undef KVC_V4
+    if (taken && chunks > 1 && trace_dispatch()) fprintf(stderr, "[kvc] turbo_v4: %d units of eight query rows per kv head\n", chunks);
     return taken ? 1 : 0;
 }
 

@@ -114,6 +114,36 @@ def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
     assert g.trim(10_000) == o.trim(10_000) and g.offset == 0 and not g.is_compressed and g.state == []
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Hq,Hkv,L,P,kw", [
+    (16, 2, 6, 1000, dict(bits=4, key_bits=3, value_bits=4)),   # 48 rows per kv head: six units of eight
+    (8, 2, 5, 517, dict(bits=4)),                               # 20 rows: the last unit carries four
+    (32, 2, 1, 300, dict(bits=4, key_bits=2, value_bits=4)),    # 16 heads per kv head, one position, no mask
+    (8, 1, 8, 2049, dict(bits=4, key_bits=3, value_bits=4)),    # 64 rows, the most the kernel takes; ragged last stage
+])
+def test_short_chunks_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle, cuda, capfd, monkeypatch, dtype, Hq, Hkv, L, P, kw):
+    """A verify chunk over a compressed cache (4-bit values) is cut into units of eight query rows,
+    each streamed through the decode kernel with its own causal limits."""
+    B, D = 2, 128
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    mask = "causal" if L > 1 else "none"
+    for rnd in range(2):
+        q = seeded((B, Hq, L, D), 3 + rnd, dtype)
+        k1, v1 = seeded((B, Hkv, L, D), 5 + rnd, dtype), seeded((B, Hkv, L, D), 7 + rnd, dtype)
+        capfd.readouterr()
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+        torch.cuda.synchronize()
+        assert "turbo_v4" in capfd.readouterr().err
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
+        assert g.trim(L - 1) == o.trim(L - 1)
+    assert kvc.lib().kvc_device_status() == 0
+
+
 def test_turbo_starts_compressed_when_first_call_is_decode(kvc, oracle, cuda):
     B, Hq, Hkv, D = 1, 4, 1, 64
     g = kvc.TurboQuantKVCache(bits=4)
