@@ -428,22 +428,42 @@ __device__ void segment_epilogue(const UnitOut &u, const FlatPlan &f, const floa
         }
         if (u.o_signs) {
             // TurboQuant values: the merged rows are in the rotated basis; out = signs * H(o) / sqrt(D).
-            for (int half = 1; half < D; half <<= 1) {
-                consumer_bar<NW>();
-                for (int pidx = tid; pidx < R * (D / 2); pidx += NT) {
-                    const int r = pidx / (D / 2), j = pidx % (D / 2);
-                    const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
-                    const float x = rows[r * D + i0], y = rows[r * D + i1];
-                    rows[r * D + i0] = x + y;
-                    rows[r * D + i1] = x - y;
-                }
-            }
+            // A warp takes a row: lane l holds dims E*l .. E*l + E - 1, the stages that pair dims less
+            // than E apart stay inside the lane, the other five are lane exchanges. Pairs and operations
+            // ((a, b) -> (a + b, a - b), lower dim first) are those of the stage-by-stage butterfly.
+            static_assert(D % 32 == 0 && D / 32 >= 1 && D / 32 <= 16, "one warp spans a row");
+            constexpr int E = D / 32;
+            const int warp = tid >> 5, lane = tid & 31;
             consumer_bar<NW>();
             const float fs = rsqrtf((float)D);
-            for (int i = tid; i < R * D; i += NT) {
-                const int r = i / D, d = i % D;
+            for (int r = warp; r < R; r += NW) {
+                float x[E];
+#pragma unroll
+                for (int j = 0; j < E; ++j) x[j] = rows[r * D + E * lane + j];
+#pragma unroll
+                for (int h = 1; h < E; h <<= 1)
+#pragma unroll
+                    for (int i = 0; i < E; ++i)
+                        if ((i & h) == 0) {
+                            const float xa = x[i], ya = x[i + h];
+                            x[i] = xa + ya;
+                            x[i + h] = xa - ya;
+                        }
+#pragma unroll
+                for (int m = 1; m < 32; m <<= 1) {
+                    const bool upper = (lane & m) != 0;
+#pragma unroll
+                    for (int j = 0; j < E; ++j) {
+                        const float y = __shfl_xor_sync(0xffffffffu, x[j], m);
+                        x[j] = upper ? y - x[j] : x[j] + y;
+                    }
+                }
                 const int hq = hk * rep + (row0 + r) / u.L, lq = (row0 + r) % u.L;
-                store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, rows[i] * fs * u.o_signs[d]);
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    const int d = E * lane + j;
+                    store_out(u.out, u.out_dtype, b * u.o_sb + hq * u.o_sh + lq * u.o_sl + d, x[j] * fs * u.o_signs[d]);
+                }
             }
         }
     }

@@ -310,33 +310,41 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
             }
             q_stage = (const T *)(qbuf + (size_t)(sg & 1) * (8 * D * 2));
         }
-        for (int i = tid; i < 8 * D; i += CT) {
-            const int r = i / D, d = i % D;
-            float xq = 0.f;
+        // Warp r rotates row r in registers: lane l holds dims 4l .. 4l+3, the stages of the butterfly that
+        // pair dims 1 and 2 apart stay inside the lane, the other five are lane exchanges. The pairs and
+        // the operations ((a, b) -> (a + b, a - b), lower dim first) are those of the shared-memory
+        // butterfly of the other kernels, so the rotated query is the same bit for bit.
+        if (warp < 8) {
+            const int r = warp;
+            float x[4] = {0.f, 0.f, 0.f, 0.f};
             if (r < R && ok) {
                 const int hq = hk * rep + (row0 + r) / p.L, l = (row0 + r) % p.L;
-                const T qv = q_stage ? q_stage[r * D + d] : ((const T *)p.q)[b * p.q_sb + hq * p.q_sh + l * p.q_sl + d];
-                xq = to_f32<T>(qv) * p.q_signs[d];
+                const T *src = q_stage ? q_stage + r * D : (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = to_f32<T>(src[4 * lane + j]) * p.q_signs[4 * lane + j];
             }
-            qrot[i] = xq;
+            {
+                const float a0 = x[0] + x[1], a1 = x[0] - x[1], a2 = x[2] + x[3], a3 = x[2] - x[3];
+                x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+            }
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const bool upper = (lane & m) != 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float y = __shfl_xor_sync(0xffffffffu, x[j], m);
+                    x[j] = upper ? y - x[j] : x[j] + y;
+                }
+            }
+            if (p.q_calib) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] *= p.q_calib[4 * lane + j];
+            }
+            *(float4 *)(qrot + r * D + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
         }
         if (p.q_bulk) {
             __syncwarp();
             if (ok && lane == 0 && !(KVC_SKIP_BITS(p) & 2)) mbar_arrive(&qempty[sg & 1]);
-        }
-        for (int half = 1; half < D; half <<= 1) {
-            consumer_bar<V4_WARPS>();
-            for (int pi = tid; pi < 8 * (D / 2); pi += CT) {
-                const int r = pi / (D / 2), j = pi % (D / 2);
-                const int i0 = ((j / half) * 2 * half) + (j % half), i1 = i0 + half;
-                const float xa = qrot[r * D + i0], ya = qrot[r * D + i1];
-                qrot[r * D + i0] = xa + ya;
-                qrot[r * D + i1] = xa - ya;
-            }
-        }
-        if (p.q_calib) {
-            consumer_bar<V4_WARPS>();
-            for (int i = tid; i < 8 * D; i += CT) qrot[i] *= p.q_calib[i % D];
         }
         consumer_bar<V4_WARPS>();
         float m_run[2], l_run[2] = {0.f, 0.f};

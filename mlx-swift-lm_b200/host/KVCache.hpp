@@ -125,6 +125,10 @@ class KVCache {
         return wrap(out);
     }
 
+    // prepare(lengths:rightPadding:) / finalize(): no-ops for the caches of this path, as in the reference
+    void prepare(const std::vector<int32_t> &lengths) { check(kvc_prepare(h_, lengths.data(), (int32_t)lengths.size())); }
+    void finalize() { check(kvc_finalize(h_)); }
+
     int32_t kind() const { return kvc_kind_of(h_); }
     int64_t memoryBytes() const { return kvc_memory_bytes(h_); }
     // capacity hint (no reference counterpart): room for `tokens` rows without regrowth
@@ -258,6 +262,74 @@ class TurboQuantKVCache : public KVCache {
     }
 };
 
+// ChunkedKVCache(chunkSize:): a KVCacheSimple whose front can be dropped chunk by chunk.
+class ChunkedKVCache : public KVCache {
+  public:
+    explicit ChunkedKVCache(std::optional<int64_t> chunkSize = std::nullopt) : KVCache(config(chunkSize)) {}
+    explicit ChunkedKVCache(kvc_cache *adopted) : KVCache(adopted) {}
+    void maybeTrimFront() { check(kvc_maybe_trim_front(h_, stream)); }
+    int64_t startPosition() const { return kvc_start_position(h_); }
+
+  private:
+    static kvc_config config(std::optional<int64_t> chunkSize) {
+        kvc_config c = defaults(KVC_KIND_CHUNKED);
+        c.max_size = chunkSize ? (int32_t)*chunkSize : -1;   // the chunk size travels in max_size; -1 = nil
+        return c;
+    }
+};
+
+// CacheList(caches...): a composite whose state / metaState / trim span its children in order. The
+// children are handed over to the list; subscript(index:) gives a borrowed view of one of them.
+class CacheList : public KVCache {
+  public:
+    explicit CacheList(std::vector<std::unique_ptr<KVCache>> children) : KVCache(make(children)) {}
+    explicit CacheList(kvc_cache *adopted) : KVCache(adopted) {}
+    int count() const { return kvc_list_count(h_); }
+    kvc_cache *operator[](int index) const { return kvc_list_child(h_, index); }
+
+  private:
+    static kvc_cache *make(std::vector<std::unique_ptr<KVCache>> &children) {
+        std::vector<kvc_cache *> h;
+        for (auto &c : children) h.push_back(c->handle());
+        kvc_cache *out = nullptr;
+        check(kvc_list_create(h.data(), (int32_t)h.size(), &out));
+        for (auto &c : children) c->release();   // the list owns them now
+        return out;
+    }
+};
+
+// createCausalMask(n:offset:windowSize:lengths:): `maskOut` is device memory, one byte per element,
+// [n, offset + n] without lengths and [batch, 1, n, offset + n] with them (device int32 [batch]).
+inline void createCausalMask(int n, int64_t offset, std::optional<int64_t> windowSize, const int32_t *lengthsDev,
+                             int batch, void *maskOut, void *stream = nullptr) {
+    check(kvc_create_causal_mask(n, offset, windowSize ? *windowSize : -1, lengthsDev, batch, maskOut, stream));
+}
+
+// RoPE(dimensions:traditional:base:scale:) as the attention blocks apply it.
+struct RoPE {
+    int dimensions;
+    bool traditional = false;
+    float base = 10000.f;
+    float scale = 1.f;
+    kvc_rope_config config() const { return kvc_rope_config{dimensions, traditional ? 1 : 0, base, scale}; }
+    // applyRotaryPosition(rope, to: x, offset:)
+    void operator()(const kvc_tensor &x, int64_t offset, const kvc_tensor &out, void *stream = nullptr) const {
+        const kvc_rope_config c = config();
+        check(kvc_rope(&x, offset, &c, &out, stream));
+    }
+};
+
+// The cache step of an attention block: rotary positions at the cache offset, then update + attention.
+inline void attentionWithRope(const kvc_tensor &queries, const kvc_tensor &keys, const kvc_tensor &values,
+                              KVCache *cache, const RoPE &rope, float scale, const Mask &mask, const kvc_tensor &out,
+                              void *stream = nullptr) {
+    const kvc_rope_config c = rope.config();
+    const int32_t mode = mask.kind == MaskKind::none ? KVC_MASK_NONE
+                         : mask.kind == MaskKind::causal ? KVC_MASK_CAUSAL : KVC_MASK_ARRAY;
+    check(kvc_attention_rope(cache ? cache->handle() : nullptr, &queries, &keys, &values, &c, scale, mode,
+                             mask.kind == MaskKind::array ? &mask.array : nullptr, &out, cache ? cache->stream : stream));
+}
+
 inline void attentionWithCacheUpdate(const kvc_tensor &queries, const kvc_tensor &keys, const kvc_tensor &values,
                                      KVCache *cache, float scale, const Mask &mask, const kvc_tensor &out,
                                      void *stream = nullptr) {
@@ -277,6 +349,8 @@ inline std::unique_ptr<KVCache> KVCache::wrap(kvc_cache *adopted) {
         case KVC_KIND_ROTATING: return std::make_unique<RotatingKVCache>(adopted);
         case KVC_KIND_QUANTIZED: return std::make_unique<QuantizedKVCache>(adopted);
         case KVC_KIND_TURBO: return std::make_unique<TurboQuantKVCache>(adopted);
+        case KVC_KIND_CHUNKED: return std::make_unique<ChunkedKVCache>(adopted);
+        case KVC_KIND_LIST: return std::make_unique<CacheList>(adopted);
         default: kvc_free(adopted); throw Error(KVC_ERR_INTERNAL, "unknown cache kind");
     }
 }
@@ -291,17 +365,18 @@ inline void quantizedScaledDotProductAttention(const kvc_tensor &queries, const 
                              groupSize, bits, &out, stream));
 }
 
-using CacheList = std::vector<std::unique_ptr<KVCache>>;
+// [KVCache]: the per-layer cache array the iterators carry
+using CacheArray = std::vector<std::unique_ptr<KVCache>>;
 
 namespace detail {
-inline std::vector<kvc_cache *> handles(const CacheList &caches) {
+inline std::vector<kvc_cache *> handles(const CacheArray &caches) {
     std::vector<kvc_cache *> h;
     for (const auto &c : caches) h.push_back(c->handle());
     return h;
 }
 // Re-adopt the handles a list-level conversion left in `h` (converted slots hold new handles, the old
 // ones were freed by the library).
-inline void readopt(CacheList &caches, const std::vector<kvc_cache *> &h) {
+inline void readopt(CacheArray &caches, const std::vector<kvc_cache *> &h) {
     for (size_t i = 0; i < caches.size(); ++i)
         if (caches[i]->handle() != h[i]) {
             void *stream = caches[i]->stream;
@@ -313,11 +388,11 @@ inline void readopt(CacheList &caches, const std::vector<kvc_cache *> &h) {
 }  // namespace detail
 
 // canTrimPromptCache / trimPromptCache
-inline bool canTrimPromptCache(const CacheList &caches) {
+inline bool canTrimPromptCache(const CacheArray &caches) {
     const auto h = detail::handles(caches);
     return kvc_can_trim_prompt_cache(h.data(), (int32_t)h.size()) != 0;
 }
-inline int64_t trimPromptCache(const CacheList &caches, int64_t numTokens) {
+inline int64_t trimPromptCache(const CacheArray &caches, int64_t numTokens) {
     const auto h = detail::handles(caches);
     int64_t t = 0;
     check(kvc_trim_prompt_cache(h.data(), (int32_t)h.size(), numTokens, &t));
@@ -338,7 +413,7 @@ inline std::optional<std::pair<int, int>> resolveAffineScheme(const std::string 
 
 // maybeAffineQuantizeKVCache / maybeTurboQuantizeKVCache over a flat layer list; returns whether every
 // eligible layer has been converted.
-inline bool maybeAffineQuantizeKVCache(CacheList &caches, int bits, int groupSize, int64_t compressionStart,
+inline bool maybeAffineQuantizeKVCache(CacheArray &caches, int bits, int groupSize, int64_t compressionStart,
                                        void *stream = nullptr) {
     auto h = detail::handles(caches);
     int32_t complete = 0;
@@ -346,7 +421,7 @@ inline bool maybeAffineQuantizeKVCache(CacheList &caches, int bits, int groupSiz
     detail::readopt(caches, h);
     return complete != 0;
 }
-inline bool maybeTurboQuantizeKVCache(CacheList &caches, int keyBits, int valueBits, int64_t quantizedKVStart,
+inline bool maybeTurboQuantizeKVCache(CacheArray &caches, int keyBits, int valueBits, int64_t quantizedKVStart,
                                       void *stream = nullptr) {
     auto h = detail::handles(caches);
     int32_t complete = 0;
@@ -356,7 +431,7 @@ inline bool maybeTurboQuantizeKVCache(CacheList &caches, int keyBits, int valueB
 }
 
 // savePromptCache(url:cache:metadata:) / loadPromptCache(url:)
-inline void savePromptCache(const std::string &path, const CacheList &caches,
+inline void savePromptCache(const std::string &path, const CacheArray &caches,
                             const std::map<std::string, std::string> &metadata = {}, void *stream = nullptr) {
     const auto h = detail::handles(caches);
     std::vector<const char *> keys, values;
@@ -367,7 +442,7 @@ inline void savePromptCache(const std::string &path, const CacheList &caches,
     check(kvc_save_prompt_cache(path.c_str(), h.data(), (int32_t)h.size(), keys.data(), values.data(),
                                 (int32_t)keys.size(), stream));
 }
-inline std::pair<CacheList, std::map<std::string, std::string>> loadPromptCache(const std::string &path, int device = -1,
+inline std::pair<CacheArray, std::map<std::string, std::string>> loadPromptCache(const std::string &path, int device = -1,
                                                                                  void *stream = nullptr) {
     int32_t count = 0;
     size_t need = 0;
@@ -375,7 +450,7 @@ inline std::pair<CacheList, std::map<std::string, std::string>> loadPromptCache(
     std::vector<kvc_cache *> h((size_t)count);
     std::string buf(need ? need : 1, '\0');
     check(kvc_load_prompt_cache(path.c_str(), device, h.data(), count, &count, buf.data(), buf.size(), &need, stream));
-    CacheList caches;
+    CacheArray caches;
     for (int32_t i = 0; i < count; ++i) caches.push_back(KVCache::wrap(h[(size_t)i]));
     std::map<std::string, std::string> meta;
     for (size_t p = 0; p < buf.size() && buf[p] != '\0';) {   // key NUL value NUL ... closed by an empty key
@@ -419,6 +494,46 @@ class StagedRound {
   private:
     kvc_round *r_ = nullptr;
 };
+
+// KVCacheStorage.beginRound / commit over the whole layer array: one staged round per cache, all or
+// nothing (throws Error with KVC_ERR_NOT_TRIMMABLE when some cache cannot stage the round).
+class StorageRound {
+  public:
+    StorageRound(const CacheArray &caches, int maxPositions) : rounds_(caches.size(), nullptr) {
+        const auto h = detail::handles(caches);
+        check(kvc_storage_begin_round(h.data(), (int32_t)h.size(), maxPositions, rounds_.data()));
+    }
+    ~StorageRound() {
+        for (kvc_round *r : rounds_)
+            if (r) kvc_round_free(r);
+    }
+    StorageRound(const StorageRound &) = delete;
+    StorageRound &operator=(const StorageRound &) = delete;
+    // the verify pass of every layer: queries[i], keys[i], values[i], outs[i] belong to layer i
+    void attention(const std::vector<kvc_tensor> &queries, const std::vector<kvc_tensor> &keys,
+                   const std::vector<kvc_tensor> &values, float scale, const Mask &mask,
+                   const std::vector<kvc_tensor> &outs, void *stream = nullptr) {
+        const int32_t mode = mask.kind == MaskKind::none ? KVC_MASK_NONE : KVC_MASK_CAUSAL;
+        check(kvc_storage_round_attention(rounds_.data(), (int32_t)rounds_.size(), queries.data(), keys.data(),
+                                          values.data(), scale, mode, outs.data(), stream));
+    }
+    // commit(retaining:): keeps the first `retaining` positions of the round in every cache (0 = rollback)
+    void commit(int retaining, void *stream = nullptr) {
+        check(kvc_storage_commit(rounds_.data(), (int32_t)rounds_.size(), retaining, stream));
+    }
+
+  private:
+    std::vector<kvc_round *> rounds_;
+};
+
+// The rewind at the end of a speculative round without staged rounds: the main model's caches give back
+// numDraft - accepted positions, the draft model's max(numDraft - accepted - 1, 0).
+inline int64_t speculateRewind(const CacheArray &caches, int numDraft, int accepted, bool isDraft) {
+    const auto h = detail::handles(caches);
+    int64_t t = 0;
+    check(kvc_speculate_rewind(h.data(), (int32_t)h.size(), numDraft, accepted, isDraft ? 1 : 0, &t));
+    return t;
+}
 
 // rewindLastRound(count) -> positions taken back
 inline int64_t rewindLastRound(KVCache &cache, int64_t count) {

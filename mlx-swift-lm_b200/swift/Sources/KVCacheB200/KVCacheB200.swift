@@ -79,6 +79,8 @@ open class B200KVCache<A: DeviceArray> {
         case KVC_KIND_ROTATING: return RotatingKVCacheB200<A>(adopting: h)
         case KVC_KIND_QUANTIZED: return QuantizedKVCacheB200<A>(adopting: h)
         case KVC_KIND_TURBO: return TurboQuantKVCacheB200<A>(adopting: h)
+        case KVC_KIND_CHUNKED: return ChunkedKVCacheB200<A>(adopting: h)
+        case KVC_KIND_LIST: return CacheListB200<A>(adopting: h)
         default: return KVCacheSimpleB200<A>(adopting: h)
         }
     }
@@ -153,6 +155,29 @@ open class B200KVCache<A: DeviceArray> {
         return B200KVCache<A>(adopting: h!)
     }
 
+    /// prepare(lengths:rightPadding:) / finalize() (KVCache.swift:86-104): no-ops for the caches of this path.
+    public func prepare(lengths: [Int32]) {
+        var l = lengths
+        must(kvc_prepare(handle, &l, Int32(l.count)))
+    }
+    public func finalize() { must(kvc_finalize(handle)) }
+
+    /// The cache step of an attention block (Llama.swift:58-100): rotary positions at this cache's offset
+    /// for queries and keys, then attentionWithCacheUpdate.
+    public func attention(queries: A, keys: A, values: A, rope: RoPEB200, scale: Float, mask: MaskMode<A> = .none) -> A {
+        let out = A.empty(shape: queries.shape, kvcDType: queries.kvcDType)
+        var q = describe(queries), k = describe(keys), v = describe(values), o = describe(out)
+        var cfg = rope.config
+        switch mask {
+        case .none: must(kvc_attention_rope(handle, &q, &k, &v, &cfg, scale, Int32(KVC_MASK_NONE.rawValue), nil, &o, stream))
+        case .causal: must(kvc_attention_rope(handle, &q, &k, &v, &cfg, scale, Int32(KVC_MASK_CAUSAL.rawValue), nil, &o, stream))
+        case .array(let m):
+            var mt = describe(m)
+            must(kvc_attention_rope(handle, &q, &k, &v, &cfg, scale, Int32(KVC_MASK_ARRAY.rawValue), &mt, &o, stream))
+        }
+        return out
+    }
+
     /// attentionWithCacheUpdate for this cache (AttentionUtils.swift:37-95).
     public func attention(queries: A, keys: A, values: A, scale: Float, mask: MaskMode<A> = .none) -> A {
         let out = A.empty(shape: queries.shape, kvcDType: queries.kvcDType)
@@ -172,6 +197,63 @@ func defaults(_ kind: kvc_kind) -> kvc_config {
     var cfg = kvc_config()
     kvc_config_default(&cfg, Int32(kind.rawValue))
     return cfg
+}
+
+/// RoPE(dimensions:traditional:base:scale:) as the attention blocks hold it.
+public struct RoPEB200 {
+    public var dimensions: Int
+    public var traditional = false
+    public var base: Float = 10000
+    public var scale: Float = 1
+    public init(dimensions: Int, traditional: Bool = false, base: Float = 10000, scale: Float = 1) {
+        self.dimensions = dimensions; self.traditional = traditional; self.base = base; self.scale = scale
+    }
+    var config: kvc_rope_config {
+        kvc_rope_config(dims: Int32(dimensions), traditional: traditional ? 1 : 0, base: base, scale: scale)
+    }
+    /// applyRotaryPosition(rope, to: x, offset:) (RoPEApplication.swift:58-69)
+    public func callAsFunction<A: DeviceArray>(_ x: A, offset: Int, stream: UnsafeMutableRawPointer? = nil) -> A {
+        let out = A.empty(shape: x.shape, kvcDType: x.kvcDType)
+        var xi = describe(x), o = describe(out), cfg = config
+        must(kvc_rope(&xi, Int64(offset), &cfg, &o, stream))
+        return out
+    }
+}
+
+/// ChunkedKVCache (KVCache.swift:1213-1312).
+public final class ChunkedKVCacheB200<A: DeviceArray>: B200KVCache<A> {
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
+    public init(chunkSize: Int? = nil, step: Int = 256) {
+        var cfg = defaults(KVC_KIND_CHUNKED)
+        cfg.max_size = Int32(chunkSize ?? -1)     // the chunk size travels in max_size; -1 = nil
+        cfg.step = Int32(step)
+        super.init(config: cfg)
+    }
+
+    public func maybeTrimFront() { must(kvc_maybe_trim_front(handle, stream)) }
+    public var startPosition: Int { Int(kvc_start_position(handle)) }
+}
+
+/// CacheList (KVCache.swift:1645-1790): a composite entry of the layer array. The children are handed
+/// over to the list; `subscript` gives a borrowed wrapper of one of them.
+public final class CacheListB200<A: DeviceArray>: B200KVCache<A> {
+    override init(adopting h: OpaquePointer) { super.init(adopting: h) }
+
+    public init(_ caches: B200KVCache<A>...) {
+        var handles: [OpaquePointer?] = caches.map { $0.handle }
+        var h: OpaquePointer? = nil
+        must(kvc_list_create(&handles, Int32(handles.count), &h))
+        for c in caches { c.forgetHandle() }      // the list owns them now
+        super.init(adopting: h!)
+    }
+
+    public var count: Int { Int(kvc_list_count(handle)) }
+    public subscript(index: Int) -> B200KVCache<A> {
+        let w = B200KVCache<A>.wrap(adopting: kvc_list_child(handle, Int32(index))!)
+        w.forgetHandle()                          // borrowed: the list frees it
+        return w
+    }
 }
 
 public final class KVCacheSimpleB200<A: DeviceArray>: B200KVCache<A> {
@@ -287,6 +369,53 @@ public func maybeTurboQuantizeKVCacheB200<A: DeviceArray>(
         cache[i] = B200KVCache<A>.wrap(adopting: handles[i]!)
     }
     return complete != 0
+}
+
+/// createCausalMask(n:offset:windowSize:lengths:) (KVCache.swift:253-275); `lengths` is a device int32 array.
+public func createCausalMaskB200<A: DeviceArray>(
+    n: Int, offset: Int, windowSize: Int? = nil, lengths: A? = nil, stream: UnsafeMutableRawPointer? = nil
+) -> A {
+    let batch = lengths?.shape[0] ?? 0
+    let shape = lengths == nil ? [n, offset + n] : [batch, 1, n, offset + n]
+    let out = A.empty(shape: shape, kvcDType: Int32(KVC_BOOL.rawValue))
+    must(kvc_create_causal_mask(Int32(n), Int64(offset), Int64(windowSize ?? -1),
+                                lengths?.devicePointer?.assumingMemoryBound(to: Int32.self), Int32(batch),
+                                out.devicePointer, stream))
+    return out
+}
+
+/// KVCacheStorage.beginRound / commit over the layer array (KVCachePlan.swift:219-347): one staged round
+/// per cache, all or nothing; throws when some cache cannot stage the round (the caller decodes unstaged).
+public final class StorageRoundB200<A: DeviceArray> {
+    private var rounds: [OpaquePointer?]
+    public init(caches: [B200KVCache<A>], maxPositions: Int) throws {
+        var handles: [OpaquePointer?] = caches.map { $0.handle }
+        rounds = [OpaquePointer?](repeating: nil, count: handles.count)
+        try check(kvc_storage_begin_round(&handles, Int32(handles.count), Int32(maxPositions), &rounds))
+    }
+    deinit { for r in rounds where r != nil { kvc_round_free(r) } }
+
+    /// The verify pass of every layer.
+    public func attention(queries: [A], keys: [A], values: [A], scale: Float, causal: Bool, outs: [A],
+                          stream: UnsafeMutableRawPointer? = nil) {
+        var q = queries.map(describe), k = keys.map(describe), v = values.map(describe), o = outs.map(describe)
+        let mode = Int32((causal ? KVC_MASK_CAUSAL : KVC_MASK_NONE).rawValue)
+        must(kvc_storage_round_attention(&rounds, Int32(rounds.count), &q, &k, &v, scale, mode, &o, stream))
+    }
+
+    /// commit(retaining:): keeps the first `retaining` positions of the round in every cache (0 = rollback).
+    public func commit(retaining: Int, stream: UnsafeMutableRawPointer? = nil) {
+        must(kvc_storage_commit(&rounds, Int32(rounds.count), Int32(retaining), stream))
+    }
+}
+
+/// The rewind at the end of speculateRound without staged rounds (Evaluate.swift:1262-1264).
+@discardableResult
+public func speculateRewindB200<A: DeviceArray>(caches: [B200KVCache<A>], numDraft: Int, accepted: Int, isDraft: Bool) -> Int {
+    var handles: [OpaquePointer?] = caches.map { $0.handle }
+    var trimmed: Int64 = 0
+    must(kvc_speculate_rewind(&handles, Int32(handles.count), Int32(numDraft), Int32(accepted), isDraft ? 1 : 0, &trimmed))
+    return Int(trimmed)
 }
 
 /// One decode step of a ragged batch held as one cache per sequence (kvc_attention_varlen): the

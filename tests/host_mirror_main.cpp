@@ -17,7 +17,7 @@ using namespace kvc::host;
 
 int main(int argc, char **argv) {
     const std::string path = argc > 1 ? argv[1] : "/tmp/host_mirror.safetensors";
-    CacheList caches;
+    CacheArray caches;
     caches.push_back(std::make_unique<KVCacheSimple>());
     caches.push_back(std::make_unique<RotatingKVCache>(32, 4));
     caches.push_back(std::make_unique<QuantizedKVCache>(32, 4));
@@ -53,6 +53,35 @@ int main(int argc, char **argv) {
     EXPECT(dynamic_cast<QuantizedKVCache *>(loaded[2].get()) && dynamic_cast<TurboQuantKVCache *>(loaded[3].get()));
     EXPECT(loaded[1]->metaState() == caches[1]->metaState());
     EXPECT(loaded[3]->metaState() == caches[3]->metaState());
+
+    // the other classes of the protocol: ChunkedKVCache, CacheList (a composite entry of the layer array)
+    {
+        ChunkedKVCache chunked(128);
+        EXPECT(chunked.startPosition() == 0 && chunked.offset() == 0 && chunked.isTrimmable());
+        chunked.prepare({3, 5});
+        chunked.finalize();
+        const auto cm = chunked.metaState();
+        EXPECT(cm.size() == 2 && cm[0] == "128" && cm[1] == "0");
+        std::vector<std::unique_ptr<KVCache>> kids;
+        kids.push_back(std::make_unique<KVCacheSimple>());
+        kids.push_back(std::make_unique<RotatingKVCache>(16, 0));
+        CacheArray nested;
+        nested.push_back(std::make_unique<CacheList>(std::move(kids)));
+        nested.push_back(std::make_unique<ChunkedKVCache>());
+        auto *list = dynamic_cast<CacheList *>(nested[0].get());
+        EXPECT(list && list->count() == 2 && kvc_kind_of((*list)[1]) == KVC_KIND_ROTATING);
+        EXPECT(nested[0]->isTrimmable() && nested[0]->offset() == 0);
+        savePromptCache(path, nested, {});
+        auto [again, m2] = loadPromptCache(path);
+        EXPECT(again.size() == 2 && m2.empty());
+        auto *l2 = dynamic_cast<CacheList *>(again[0].get());
+        EXPECT(l2 && l2->count() == 2 && kvc_kind_of((*l2)[0]) == KVC_KIND_SIMPLE);
+        EXPECT(dynamic_cast<ChunkedKVCache *>(again[1].get()) != nullptr);
+        EXPECT(again[0]->metaState() == nested[0]->metaState());
+        EXPECT(speculateRewind(again, 5, 2, false) == 0);   // nothing stored: nothing to give back
+        const RoPE rope{64, false, 10000.f, 1.f};
+        EXPECT(rope.config().dims == 64 && rope.config().traditional == 0);
+    }
 
     bool threw = false;
     try {

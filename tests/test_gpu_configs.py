@@ -74,6 +74,44 @@ def test_config1_quantized_8bit_llama32_1b_whole(kvc, oracle, cuda):
     assert kvc.device_status() == 0
 
 
+def test_config2_simple_bf16_llama3_8b_chunked_prefill_then_decode(kvc, oracle, cuda):
+    """Configuration 2 as worded: KVCacheSimple (step 256), 32 query heads, 8 KV heads, head dim 128,
+    bfloat16; prefill 8192 tokens in 512-token chunks with causal SDPA, then decode steps. Reduced so
+    that the oracle finishes in seconds: 2 layers of 32, batch 2 of 8, 64 decode steps of 512, and
+    the oracle computes the chunk attention for the first, one middle and the last prefill chunk only
+    (the other chunks are appended with `update` on the oracle side; the library runs attention on
+    every chunk). Cache rows bit-exact after every chunk and at the end, outputs within 2e-2."""
+    layers, B, Hq, Hkv, D, P, C, steps = 2, 2, 32, 8, 128, 8192, 512, 64
+    scale = D ** -0.5
+    dtype = torch.bfloat16
+    pairs = [(kvc.KVCacheSimple(), oracle.KVCacheSimple()) for _ in range(layers)]
+    checked = {0, 7, P // C - 1}
+    for i, (g, o) in enumerate(pairs):
+        for c in range(P // C):
+            q = seeded((B, Hq, C, D), 10_000 * i + 3 * c, dtype)
+            k, v = seeded((B, Hkv, C, D), 10_000 * i + 3 * c + 1, dtype), seeded((B, Hkv, C, D), 10_000 * i + 3 * c + 2, dtype)
+            out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale, "causal")
+            if c in checked:
+                ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale, "causal")
+                assert max_abs_diff(out, ref) <= TOL[dtype], f"layer {i}, chunk {c}"
+            else:
+                o.update(to_oracle(k), to_oracle(v))
+            assert g.offset == o.offset == (c + 1) * C
+            _new_rows_equal(g, o, C, f"layer {i}, chunk {c}")
+        _same_state(g, o, f"after prefill, layer {i}")
+    for s in range(steps):
+        for i, (g, o) in enumerate(pairs):
+            q = seeded((B, Hq, 1, D), 500_000 + 10 * s + i, dtype)
+            k, v = seeded((B, Hkv, 1, D), 600_000 + 10 * s + i, dtype), seeded((B, Hkv, 1, D), 700_000 + 10 * s + i, dtype)
+            out = g.attention(q.to(cuda), k.to(cuda), v.to(cuda), scale)
+            ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, scale)
+            assert max_abs_diff(out, ref) <= TOL[dtype], f"step {s}, layer {i}"
+    for i, (g, o) in enumerate(pairs):
+        assert g.offset == o.offset == P + steps
+        _same_state(g, o, f"end, layer {i}")
+    assert kvc.device_status() == 0
+
+
 def test_config3_rotating_gemma3_schedule(kvc, oracle, cuda):
     """Configuration 3 as worded, on one sliding-window layer and one global layer of its 26 (the other
     local / global layers repeat these two): 4 query heads, 1 KV head, head dim 256, batch 4, bfloat16;
