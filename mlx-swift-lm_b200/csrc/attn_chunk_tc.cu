@@ -61,6 +61,11 @@ struct ChunkTcParams {
     int64_t causal_offset;
     float scale_log2;
     int *status;
+    // SCALED kernels only: one factor per key for the scores (k_scale) and for the probabilities that
+    // enter the output product (v_scale), [B, Hkv, keys] with these strides; TurboQuant rows are stored
+    // as unit centroids and their norms come in here, in fp32
+    const float *k_scale, *v_scale;
+    int64_t ks_sb, ks_sh, vs_sb, vs_sh;
 };
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -141,7 +146,7 @@ enum : int {
     BAR_COUNT = BAR_L_FULL + 1
 };
 
-template <typename T, int D>
+template <typename T, int D, bool SCALED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                      const __grid_constant__ CUtensorMap vmap, const ChunkTcParams p) {
@@ -326,6 +331,18 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             tc_fence_before();
             mbar_arrive(&bars[BAR_S_EMPTY + (j & 1)]);
             const int64_t key0 = (int64_t)j * TC_KEYS;
+            if (SCALED) {
+                // every thread reads the same 128 factors (one broadcast request per vector)
+                const float4 *kn = (const float4 *)(p.k_scale + b * p.ks_sb + hk * p.ks_sh + key0);
+#pragma unroll
+                for (int i4 = 0; i4 < TC_KEYS / 4; ++i4) {
+                    const float4 n = __ldg(kn + i4);
+                    raw[4 * i4 + 0] = __float_as_uint(__uint_as_float(raw[4 * i4 + 0]) * n.x);
+                    raw[4 * i4 + 1] = __float_as_uint(__uint_as_float(raw[4 * i4 + 1]) * n.y);
+                    raw[4 * i4 + 2] = __float_as_uint(__uint_as_float(raw[4 * i4 + 2]) * n.z);
+                    raw[4 * i4 + 3] = __float_as_uint(__uint_as_float(raw[4 * i4 + 3]) * n.w);
+                }
+            }
             if (key0 + TC_KEYS - 1 > block_min_limit) {   // some row of the block loses keys in this tile
 #pragma unroll
                 for (int i = 0; i < TC_KEYS; ++i)
@@ -355,6 +372,13 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 for (int i = 0; i < 8; ++i) {
                     e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));   // exp2(-inf) = 0
                     sum4[i & 3] += e[i];
+                }
+                if (SCALED) {   // the row sum stays that of the probabilities; the product takes p * factor
+                    const float4 *vn = (const float4 *)(p.v_scale + b * p.vs_sb + hk * p.vs_sh + key0 + kc * 8);
+                    const float4 n0 = __ldg(vn), n1 = __ldg(vn + 1);
+                    const float f[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) e[i] = e[i] > 0.f ? e[i] * f[i] : 0.f;   // masked keys past the stored rows carry no factor
                 }
                 uint4 w;
                 w.x = pack_pair<T>(e[0], e[1]);
@@ -475,7 +499,7 @@ bool strides_fit(const void *data, int D, int64_t s_row, int64_t s_h, int64_t s_
 
 // Returns false when the device does not grant the kernel its shared memory (the caller falls back to
 // the mma.sync chunk kernel).
-template <typename T, int D>
+template <typename T, int D, bool SCALED>
 bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + 2 * (size_t)TC_TILE + BAR_COUNT * sizeof(uint64_t) + 64 +
@@ -487,14 +511,14 @@ bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
     int state = configured[dev].load(std::memory_order_acquire);
     if (state == 0) {
         // setting the attribute twice from two racing threads is harmless; the result is the same
-        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D, SCALED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
         state = e == cudaSuccess ? 1 : -1;
         configured[dev].store(state, std::memory_order_release);
     }
     if (state < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
+    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D, SCALED>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
     ++g_launch_count;
     return true;
@@ -504,26 +528,33 @@ bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
 
 // Returns 1 when the call was taken (head dim 64 or 128, f16 / bf16 raw K and V, no array mask, enough
 // 128-row blocks to fill the part), 0 otherwise. KVC_CHUNK_TC=0 turns the path off.
-int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
+bool attention_chunk_tc_accepts(const AttnArgs &a) {
     static const bool off = [] {
         const char *e = std::getenv("KVC_CHUNK_TC");
         return e && e[0] == '0';
     }();
-    if (off) return 0;
-    if ((a.D != 128 && a.D != 64) || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
-    if (a.k.kind != SRC_RAW || a.v.kind != SRC_RAW || a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
-    if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib || a.new_k) return 0;
-    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30 || a.L < 64) return 0;
-    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
+    if (off) return false;
+    if ((a.D != 128 && a.D != 64) || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return false;
+    if (a.k.kind != SRC_RAW || a.v.kind != SRC_RAW || a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return false;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib || a.new_k || a.q_rot || a.o_rot) return false;
+    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30 || a.L < 64) return false;
+    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return false;
     const int64_t row_blocks = ((int64_t)a.L + TC_ROWS - 1) / TC_ROWS;
     const int64_t ctas = (int64_t)a.B * a.Hq * row_blocks;
     // a CTA owns an SM (its TMEM and 193 KB of shared memory): fewer blocks than half the part run
     // better on the split-K kernel
-    if (ctas < sm_count(a.device) / 2 || ctas > (int64_t)1 << 30) return 0;
-    if (!strides_fit(a.q, a.D, a.q_sl, a.q_sh, a.q_sb, a.Hq, a.B)) return 0;
+    if (ctas < sm_count(a.device) / 2 || ctas > (int64_t)1 << 30) return false;
+    if (!strides_fit(a.q, a.D, a.q_sl, a.q_sh, a.q_sb, a.Hq, a.B)) return false;
     if (!strides_fit(a.k.data, a.D, a.k.st, a.k.sh, a.k.sb, a.Hkv, a.B) || !strides_fit(a.v.data, a.D, a.v.st, a.v.sh, a.v.sb, a.Hkv, a.B))
-        return 0;
-    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
+        return false;
+    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return false;
+    return true;
+}
+
+int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
+    if (!attention_chunk_tc_accepts(a)) return 0;
+    const int64_t row_blocks = ((int64_t)a.L + TC_ROWS - 1) / TC_ROWS;
+    const int64_t ctas = (int64_t)a.B * a.Hq * row_blocks;
     int *status = device_status_word(a.device);
     if (!status) return 0;
     CUtensorMap qmap, kmap, vmap;
@@ -539,13 +570,21 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = status;
+    // raw sources that carry norms: rows of unit scale with one factor per key (the TurboQuant path)
+    const bool scaled = a.k.norms != nullptr && a.v.norms != nullptr;
+    if (scaled) {
+        if (((uintptr_t)a.k.norms & 15) || ((uintptr_t)a.v.norms & 15) || (a.k.gsb % 4) || (a.k.gsh % 4) || (a.v.gsb % 4) ||
+            (a.v.gsh % 4))
+            return 0;
+        p.k_scale = a.k.norms; p.v_scale = a.v.norms;
+        p.ks_sb = a.k.gsb; p.ks_sh = a.k.gsh; p.vs_sb = a.v.gsb; p.vs_sh = a.v.gsh;
+    }
     bool taken;
-    if (a.D == 128)
-        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 128>(qmap, kmap, vmap, p, (int)ctas, stream)
-                                      : launch_tc_typed<__half, 128>(qmap, kmap, vmap, p, (int)ctas, stream);
-    else
-        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 64>(qmap, kmap, vmap, p, (int)ctas, stream)
-                                      : launch_tc_typed<__half, 64>(qmap, kmap, vmap, p, (int)ctas, stream);
+#define KVC_TC(TT, DD) (scaled ? launch_tc_typed<TT, DD, true>(qmap, kmap, vmap, p, (int)ctas, stream) \
+                               : launch_tc_typed<TT, DD, false>(qmap, kmap, vmap, p, (int)ctas, stream))
+    if (a.D == 128) taken = a.q_dtype == KVC_BF16 ? KVC_TC(__nv_bfloat16, 128) : KVC_TC(__half, 128);
+    else taken = a.q_dtype == KVC_BF16 ? KVC_TC(__nv_bfloat16, 64) : KVC_TC(__half, 64);
+#undef KVC_TC
     if (taken && trace_dispatch()) fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
     return taken ? 1 : 0;
 }

@@ -12,6 +12,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_chunk_materialized(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (read once per process; used by
@@ -34,6 +35,8 @@ int launch_attention(const AttnArgs &a, cudaStream_t stream) {
         n = launch_attention_affine(a, stream);
         if (n > 0) return n;
         n = launch_attention_turbo(a, stream);
+        if (n > 0) return n;
+        n = launch_attention_chunk_materialized(a, stream);   // long chunks over packed caches: rows written out, then tcgen05
         if (n > 0) return n;
         n = launch_attention_chunk_packed(a, stream);
         if (n > 0) return n;

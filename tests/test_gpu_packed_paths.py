@@ -207,3 +207,91 @@ def test_varlen_decode_over_independent_caches(kvc, oracle, cuda, bits):
         assert a.offset == b.offset == o.offset
         for x, y in zip(a.state, b.state):
             assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,D,bits,group,P,L,mask", [
+    (2, 8, 2, 128, 4, 64, 260, 640, "causal"),     # 80 blocks of 128 rows on a quantised prefix
+    (1, 16, 4, 128, 8, 32, 0, 600, "causal"),      # chunk into an empty cache, last block partial
+    (5, 16, 2, 128, 2, 128, 1000, 128, "none"),    # 2-bit codes, no mask, ragged last key tile
+    (2, 32, 8, 64, 4, 64, 777, 300, "causal"),     # head dim 64
+])
+def test_affine_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, D, bits,
+                                                        group, P, L, mask):
+    """Long chunks over the affine cache: the rows are written out once as f16 / bf16 and the
+    contraction runs on the tcgen05 kernel."""
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
+    if P:
+        k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+        g.update_quantized(k.to(cuda), v.to(cuda))
+        o.update_quantized(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, dtype)
+    k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
+    capfd.readouterr()
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+    torch.cuda.synchronize()
+    err = capfd.readouterr().err
+    assert "chunk_mat" in err and "chunk_tc" in err
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,D,kb,vb,P,L,mask", [
+    (2, 8, 2, 128, 3, 4, 260, 640, "causal"),
+    (1, 16, 4, 128, 4, 4, 1, 600, "causal"),
+    (5, 16, 2, 128, 2, 2, 1000, 128, "none"),
+    (3, 8, 8, 128, 4, 2, 500, 512, "causal"),
+    (2, 32, 8, 64, 3, 3, 777, 300, "causal"),      # head dim 64
+])
+def test_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, D, kb, vb,
+                                                       P, L, mask):
+    """Long chunks over the compressed TurboQuant cache: rows written out in the rotated basis,
+    queries rotated in, outputs rotated back, contraction on the tcgen05 kernel."""
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    kw = dict(bits=max(kb, vb), key_bits=kb, value_bits=vb)
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    q = seeded((B, Hq, L, D), 3, dtype)
+    k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
+    capfd.readouterr()
+    out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+    torch.cuda.synchronize()
+    err = capfd.readouterr().err
+    assert "chunk_mat" in err and "chunk_tc" in err
+    ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
+    assert max_abs_diff(out, ref) <= TOL[dtype]
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_calibrated_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, cuda, capfd, monkeypatch):
+    """Correlated keys: the cache calibrates at compression, and the chunk's rotated queries carry the
+    calibration scale."""
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    B, Hq, Hkv, D, P, L = 2, 8, 2, 128, 600, 640
+    dtype = torch.bfloat16
+    kw = dict(bits=4, key_bits=3, value_bits=4)
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    q = seeded((B, Hq, P, D), 1, dtype)
+    from test_gpu_turbo import _correlated_keys
+    k, v = _correlated_keys((B, Hkv, P, D), 2, dtype), seeded((B, Hkv, P, D), 3, dtype)
+    g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, "causal")          # raw prefill
+    oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5, "causal")
+    q1, k1, v1 = seeded((B, Hq, 1, D), 4, dtype), _correlated_keys((B, Hkv, 1, D), 5, dtype), seeded((B, Hkv, 1, D), 6, dtype)
+    g.attention(q1.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)                  # compresses and calibrates
+    oracle.attention_with_cache_update(to_oracle(q1), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
+    assert g.is_compressed and len(g.state) == 5 and len(o.state) == 5
+    q2 = seeded((B, Hq, L, D), 7, dtype)
+    k2, v2 = _correlated_keys((B, Hkv, L, D), 8, dtype), seeded((B, Hkv, L, D), 9, dtype)
+    capfd.readouterr()
+    out = g.attention(q2.to(cuda), k2.to(cuda), v2.to(cuda), D ** -0.5, "causal")
+    torch.cuda.synchronize()
+    assert "chunk_mat" in capfd.readouterr().err
+    ref = oracle.attention_with_cache_update(to_oracle(q2), to_oracle(k2), to_oracle(v2), o, D ** -0.5, "causal")
+    from helpers import worst_excess
+    assert worst_excess(out, ref, dtype) <= 0
+    assert kvc.lib().kvc_device_status() == 0
