@@ -7,9 +7,10 @@
 //
 //   1. writes the visible rows of K and V once as 16-bit tiles into scratch memory, one 16-byte store
 //      per eight elements: affine rows as scale * code + bias in the cache's dtype (what MLX's
-//      dequantized() hands the matmul); TurboQuant rows as centroid[index] in f16, i.e. the unit rows in
-//      the rotated basis - their fp32 norms are applied inside the contraction kernel, per key, to the
-//      scores and to the probabilities, as the decode kernels do,
+//      dequantized() hands the matmul); TurboQuant rows as norm * centroid[index] in f16 whatever the
+//      caller's dtype, i.e. the rows in the rotated basis at eleven significant bits (the product is
+//      formed in fp32 and saturates at the f16 range: a row norm beyond 1e5 clips instead of
+//      overflowing),
 //   2. for TurboQuant rotates the chunk's queries into the key basis (sign flip, Walsh-Hadamard
 //      butterfly in registers, 1/sqrt(D), optional calibration scale), f16,
 //   3. runs attn_chunk_tc_kernel (tcgen05.mma, accumulators in TMEM) on those arrays,
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(256) materialize_kernel(const __grid_constant_
         }
     } else {
         // indices are a low-bit-first stream of `bits` per dim; eight of them start at bit d0 * bits
+        const float nrm = s.norms[b * s.gsb + h * s.gsh + t * s.gst];
         const int bit0 = d0 * s.bits, w0 = bit0 >> 5, sh = bit0 & 31;
         const int words = (p.D * s.bits + 31) / 32;
         uint64_t win = row[w0];
@@ -107,7 +109,7 @@ __global__ void __launch_bounds__(256) materialize_kernel(const __grid_constant_
         win >>= sh;
         const uint32_t m = (1u << s.bits) - 1u;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = s.codebook[(uint32_t)(win >> (j * s.bits)) & m];
+        for (int j = 0; j < 8; ++j) x[j] = fminf(fmaxf(nrm * s.codebook[(uint32_t)(win >> (j * s.bits)) & m], -65504.f), 65504.f);
     }
     uint4 o;
     o.x = pack2<TO>(x[0], x[1]); o.y = pack2<TO>(x[2], x[3]); o.z = pack2<TO>(x[4], x[5]); o.w = pack2<TO>(x[6], x[7]);
@@ -171,7 +173,7 @@ __global__ void __launch_bounds__(256) rotate_rows_kernel(const __grid_constant_
 
 bool source_ok(const KVSource &s, int D, bool turbo) {
     if (((uintptr_t)s.data & 3) != 0) return false;
-    if (turbo) return s.kind == SRC_TURBO && s.bits >= 2 && s.bits <= 4 && s.norms != nullptr && s.gst == 1;
+    if (turbo) return s.kind == SRC_TURBO && s.bits >= 2 && s.bits <= 4 && s.norms != nullptr;
     if (s.kind != SRC_AFFINE || !s.scales || !s.biases) return false;
     if (s.bits != 2 && s.bits != 4 && s.bits != 8) return false;
     return s.group >= 8 && D % s.group == 0 && s.group % 8 == 0;
@@ -226,7 +228,7 @@ int launch_attention_chunk_materialized(const AttnArgs &a, cudaStream_t stream) 
     r.k = KVSource();
     r.v = KVSource();
     r.k.kind = r.v.kind = SRC_RAW;
-    // TurboQuant runs in f16 whatever the caller's dtype (unit centroids, fp32 norms inside the kernel)
+    // TurboQuant runs in f16 whatever the caller's dtype
     const int32_t work_dtype = turbo ? KVC_F16 : a.q_dtype;
     r.q_dtype = work_dtype;
     r.k.dtype = r.v.dtype = work_dtype;
@@ -282,10 +284,6 @@ int launch_attention_chunk_materialized(const AttnArgs &a, cudaStream_t stream) 
         call.k.data = k_out;
         call.v.data = v_out;
         if (turbo) {
-            call.k.norms = a.k.norms + (int64_t)b0 * a.k.gsb;
-            call.v.norms = a.v.norms + (int64_t)b0 * a.v.gsb;
-            call.k.gsb = a.k.gsb; call.k.gsh = a.k.gsh; call.k.gst = 1;
-            call.v.gsb = a.v.gsb; call.v.gsh = a.v.gsh; call.v.gst = 1;
             RotParams rp = {};
             rp.in = call.q; rp.out = q_out;
             rp.i_sb = a.q_sb; rp.i_sh = a.q_sh; rp.i_sl = a.q_sl;

@@ -61,11 +61,6 @@ struct ChunkTcParams {
     int64_t causal_offset;
     float scale_log2;
     int *status;
-    // SCALED kernels only: one factor per key for the scores (k_scale) and for the probabilities that
-    // enter the output product (v_scale), [B, Hkv, keys] with these strides; TurboQuant rows are stored
-    // as unit centroids and their norms come in here, in fp32
-    const float *k_scale, *v_scale;
-    int64_t ks_sb, ks_sh, vs_sb, vs_sh;
 };
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -146,7 +141,7 @@ enum : int {
     BAR_COUNT = BAR_L_FULL + 1
 };
 
-template <typename T, int D, bool SCALED>
+template <typename T, int D>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                      const __grid_constant__ CUtensorMap vmap, const ChunkTcParams p) {
@@ -331,18 +326,6 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             tc_fence_before();
             mbar_arrive(&bars[BAR_S_EMPTY + (j & 1)]);
             const int64_t key0 = (int64_t)j * TC_KEYS;
-            if (SCALED) {
-                // every thread reads the same 128 factors (one broadcast request per vector)
-                const float4 *kn = (const float4 *)(p.k_scale + b * p.ks_sb + hk * p.ks_sh + key0);
-#pragma unroll
-                for (int i4 = 0; i4 < TC_KEYS / 4; ++i4) {
-                    const float4 n = __ldg(kn + i4);
-                    raw[4 * i4 + 0] = __float_as_uint(__uint_as_float(raw[4 * i4 + 0]) * n.x);
-                    raw[4 * i4 + 1] = __float_as_uint(__uint_as_float(raw[4 * i4 + 1]) * n.y);
-                    raw[4 * i4 + 2] = __float_as_uint(__uint_as_float(raw[4 * i4 + 2]) * n.z);
-                    raw[4 * i4 + 3] = __float_as_uint(__uint_as_float(raw[4 * i4 + 3]) * n.w);
-                }
-            }
             if (key0 + TC_KEYS - 1 > block_min_limit) {   // some row of the block loses keys in this tile
 #pragma unroll
                 for (int i = 0; i < TC_KEYS; ++i)
@@ -372,13 +355,6 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 for (int i = 0; i < 8; ++i) {
                     e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));   // exp2(-inf) = 0
                     sum4[i & 3] += e[i];
-                }
-                if (SCALED) {   // the row sum stays that of the probabilities; the product takes p * factor
-                    const float4 *vn = (const float4 *)(p.v_scale + b * p.vs_sb + hk * p.vs_sh + key0 + kc * 8);
-                    const float4 n0 = __ldg(vn), n1 = __ldg(vn + 1);
-                    const float f[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = e[i] > 0.f ? e[i] * f[i] : 0.f;   // masked keys past the stored rows carry no factor
                 }
                 uint4 w;
                 w.x = pack_pair<T>(e[0], e[1]);
@@ -499,7 +475,7 @@ bool strides_fit(const void *data, int D, int64_t s_row, int64_t s_h, int64_t s_
 
 // Returns false when the device does not grant the kernel its shared memory (the caller falls back to
 // the mma.sync chunk kernel).
-template <typename T, int D, bool SCALED>
+template <typename T, int D>
 bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + 2 * (size_t)TC_TILE + BAR_COUNT * sizeof(uint64_t) + 64 +
@@ -511,14 +487,14 @@ bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUt
     int state = configured[dev].load(std::memory_order_acquire);
     if (state == 0) {
         // setting the attribute twice from two racing threads is harmless; the result is the same
-        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D, SCALED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
         state = e == cudaSuccess ? 1 : -1;
         configured[dev].store(state, std::memory_order_release);
     }
     if (state < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D, SCALED>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
+    KVC_CUDA(launch_pdl(attn_chunk_tc_kernel<T, D>, dim3(ctas), dim3(TC_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
     ++g_launch_count;
     return true;
@@ -570,21 +546,13 @@ int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream) {
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = status;
-    // raw sources that carry norms: rows of unit scale with one factor per key (the TurboQuant path)
-    const bool scaled = a.k.norms != nullptr && a.v.norms != nullptr;
-    if (scaled) {
-        if (((uintptr_t)a.k.norms & 15) || ((uintptr_t)a.v.norms & 15) || (a.k.gsb % 4) || (a.k.gsh % 4) || (a.v.gsb % 4) ||
-            (a.v.gsh % 4))
-            return 0;
-        p.k_scale = a.k.norms; p.v_scale = a.v.norms;
-        p.ks_sb = a.k.gsb; p.ks_sh = a.k.gsh; p.vs_sb = a.v.gsb; p.vs_sh = a.v.gsh;
-    }
     bool taken;
-#define KVC_TC(TT, DD) (scaled ? launch_tc_typed<TT, DD, true>(qmap, kmap, vmap, p, (int)ctas, stream) \
-                               : launch_tc_typed<TT, DD, false>(qmap, kmap, vmap, p, (int)ctas, stream))
-    if (a.D == 128) taken = a.q_dtype == KVC_BF16 ? KVC_TC(__nv_bfloat16, 128) : KVC_TC(__half, 128);
-    else taken = a.q_dtype == KVC_BF16 ? KVC_TC(__nv_bfloat16, 64) : KVC_TC(__half, 64);
-#undef KVC_TC
+    if (a.D == 128)
+        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 128>(qmap, kmap, vmap, p, (int)ctas, stream)
+                                      : launch_tc_typed<__half, 128>(qmap, kmap, vmap, p, (int)ctas, stream);
+    else
+        taken = a.q_dtype == KVC_BF16 ? launch_tc_typed<__nv_bfloat16, 64>(qmap, kmap, vmap, p, (int)ctas, stream)
+                                      : launch_tc_typed<__half, 64>(qmap, kmap, vmap, p, (int)ctas, stream);
     if (taken && trace_dispatch()) fprintf(stderr, "[kvc] chunk_tc: %lld CTAs of 128 rows\n", (long long)ctas);
     return taken ? 1 : 0;
 }
