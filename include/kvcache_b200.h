@@ -149,6 +149,10 @@ typedef struct kvc_config {
 
 void       kvc_config_default(kvc_config *cfg, int32_t kind);
 kvc_status kvc_create(const kvc_config *cfg, kvc_cache **out);
+/* Buffers the handle still holds are released in the order of the stream its last
+ * update / attention / state call ran on (kernels queued there may still read them), on
+ * the handle's own device. A handle driven from several streams must be quiescent on the
+ * others. */
 void       kvc_free(kvc_cache *cache);
 
 /* CacheList(caches...)  KVCache.swift:1556-1568. The list takes ownership of the

@@ -285,7 +285,10 @@ void turbo_rotation(int dim, uint64_t seed, std::vector<float> &rotation) {
 }  // namespace kvc
 
 kvc_cache::~kvc_cache() {
-    cudaStream_t s = nullptr;
+    // free in the order of the stream that last used the arrays, on the handle's device
+    cudaStream_t s = last_stream;
+    int prev = -1;
+    const bool switched = device >= 0 && cudaGetDevice(&prev) == cudaSuccess && prev != device && cudaSetDevice(device) == cudaSuccess;
     kvc::Array4 *arrays[] = {&k, &v, &k_alt, &v_alt, &k_view, &v_view, &kq, &ks, &kb, &vq, &vs, &vb,
                              &kp, &kn, &vp, &vn, &restore.k, &restore.v, &restore.rk, &restore.rv};
     for (auto *a : arrays) a->release(s);
@@ -297,6 +300,7 @@ kvc_cache::~kvc_cache() {
     if (kcodec.rotation_dev) kvc::dev_free(kcodec.rotation_dev, s);
     if (vcodec.rotation_dev) kvc::dev_free(vcodec.rotation_dev, s);
     for (kvc_cache *child : children) delete child;
+    if (switched) (void)cudaSetDevice(prev);
 }
 
 namespace kvc {
@@ -459,6 +463,7 @@ static void chunked_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &
 
 // ChunkedKVCache.maybeTrimFront (KVCache.swift:1222-1232).
 void cache_maybe_trim_front(kvc_cache *c, cudaStream_t s) {
+    c->last_stream = s;
     KVC_REQUIRE(c->cfg.kind == KVC_KIND_CHUNKED, "maybeTrimFront needs a ChunkedKVCache");
     const int64_t chunk = c->cfg.max_size;
     if (!c->k.allocated() || chunk <= 0 || c->len < chunk) return;
@@ -479,6 +484,7 @@ void cache_maybe_trim_front(kvc_cache *c, cudaStream_t s) {
 
 void cache_update(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
                   kvc_tensor *out_k, kvc_tensor *out_v) {
+    c->last_stream = s;
     require4(k, "keys");
     require4(v, "values");
     KVC_REQUIRE(is_float_dtype(k.dtype) && k.dtype == v.dtype, "update: keys/values must share a floating dtype");
@@ -547,6 +553,7 @@ static void quant_triple_alloc(Array4 &q, Array4 &sc, Array4 &bi, int64_t B, int
 
 void cache_update_quantized(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s,
                             kvc_tensor out_k[3], kvc_tensor out_v[3], bool defer_quantize) {
+    c->last_stream = s;
     KVC_REQUIRE(c->cfg.kind == KVC_KIND_QUANTIZED, "updateQuantized needs a QuantizedKVCache");
     require4(k, "keys");
     require4(v, "values");
@@ -877,6 +884,7 @@ static void turbo_compress_raw(kvc_cache *c, cudaStream_t s) {
 // encode the new rows and append them in the compressed domain
 // (TurboQuantKVCache.swift:1176-1200 -> compressRawCache :895, encodeNewToken :1010-1147).
 void cache_turbo_encode_new_token(kvc_cache *c, const kvc_tensor &k, const kvc_tensor &v, cudaStream_t s) {
+    c->last_stream = s;
     KVC_REQUIRE(c->cfg.kind == KVC_KIND_TURBO, "encode_new_token: not a TurboQuant cache");
     if (c->open_round) fail(KVC_ERR_INVALID_STATE, "encode_new_token: a staged round is open on this cache");
     require4(k, "keys");
@@ -934,6 +942,7 @@ static void turbo_compressed_attention(kvc_cache *c, const kvc_tensor &q, const 
 void cache_attention(kvc_cache *c, const kvc_tensor &q, const kvc_tensor &k, const kvc_tensor &v,
                      float scale, int32_t mask_mode, const kvc_tensor *mask, const kvc_tensor &out,
                      cudaStream_t s) {
+    c->last_stream = s;
     require4(q, "queries");
     require4(k, "keys");
     require4(v, "values");
@@ -1136,7 +1145,7 @@ int64_t cache_trim(kvc_cache *c, int64_t n) {
             const int64_t t = std::min(n, c->offset);
             c->offset -= t;
             if (c->offset == 0) {
-                cudaStream_t s = nullptr;
+                cudaStream_t s = c->last_stream;   // trim carries no stream: free behind the last work on the arrays
                 for (Array4 *a : {&c->k, &c->v, &c->kp, &c->kn, &c->vp, &c->vn, &c->kq, &c->ks, &c->kb,
                                   &c->vq, &c->vs, &c->vb})
                     a->release(s);
@@ -1284,6 +1293,7 @@ static void adopt(Array4 &dst, const kvc_tensor &t, cudaStream_t s, int64_t step
 }
 
 void cache_state_set(kvc_cache *c, const kvc_tensor *arrays, int count, cudaStream_t s) {
+    c->last_stream = s;
     if (c->open_round) fail(KVC_ERR_INVALID_STATE, "state: a staged round is open on this cache");
     c->restore.valid = false;
     switch (c->cfg.kind) {
@@ -1596,6 +1606,7 @@ kvc_cache *cache_to_turbo(const kvc_cache *c, int kb, int vb, int kg, cudaStream
 // logical view / masks
 // ---------------------------------------------------------------------
 void cache_logical_view(kvc_cache *c, int64_t tail, cudaStream_t s, kvc_tensor *ok, kvc_tensor *ov) {
+    c->last_stream = s;
     // RotatingKVCache.logicalView(tail:) (KVCache.swift:631-658)
     KVC_REQUIRE(c->cfg.kind == KVC_KIND_ROTATING, "logicalView needs a RotatingKVCache");
     if (!c->k.allocated()) fail(KVC_ERR_INVALID_STATE, "logicalView: nothing has been written yet");

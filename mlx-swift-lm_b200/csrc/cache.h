@@ -64,6 +64,10 @@ struct kvc_cache {
     kvc_config cfg{};
     int device = 0;
     int64_t offset = 0;
+    // The stream of the last call that enqueued work on this handle's arrays: buffers the handle gives
+    // up without being handed a stream (the destructor, trim to empty) are freed in that stream's order,
+    // so the pool cannot hand them out again under kernels still queued there.
+    cudaStream_t last_stream = nullptr;
 
     // simple / rotating / turbo raw phase
     kvc::Array4 k, v;

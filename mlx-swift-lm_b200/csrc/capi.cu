@@ -191,7 +191,7 @@ void kvc_free(kvc_cache *cache) {
     if (!cache) return;
     try {
         if (cache->open_round) cache->open_round->cache = nullptr;
-        delete cache;
+        delete cache;   // frees in the order of the handle's last stream, on the handle's device
     } catch (...) {
     }
 }
@@ -994,7 +994,7 @@ void kvc_round_free(kvc_round *r) {
     if (!r) return;
     try {
         if (r->cache && r->cache->open_round == r) r->cache->open_round = nullptr;
-        cudaStream_t s = nullptr;
+        cudaStream_t s = r->cache ? r->cache->last_stream : nullptr;
         r->sk.release(s); r->sv.release(s); r->pk.release(s); r->pv.release(s);
         delete r;
     } catch (...) {
