@@ -36,6 +36,13 @@ using namespace dev;
 constexpr int PK_WARPS = 4;
 constexpr int PK_THREADS = (PK_WARPS + 1) * 32;
 constexpr int PK_TILE = 64;
+// The 8-row decode kernel takes its consumer-warp count as a template parameter (16 tokens per warp and
+// stage): 4 warps x 3 CTAs per SM, or 15 warps x 1 CTA (16 warps with the producer: 128 registers each).
+// Uniform batches of 4-bit codes at head dim 128 take the 15-warp form (77.8 against 85.4 us per launch on
+// the Qwen2-7B shape); ragged lists of caches keep 64-token tiles (their units end at any length and the
+// 240-token tiles measured 4 % slower there).
+constexpr int affine8_warps(int D, int bits, bool varlen) { return (D == 128 && bits == 4 && !varlen) ? 15 : 4; }
+constexpr int affine8_ctas(int D, int bits, bool varlen) { return affine8_warps(D, bits, varlen) == 15 ? 1 : 3; }
 constexpr int PK_COUNTER_BYTES = 64 * 1024;
 
 struct AffineParams {
@@ -600,7 +607,7 @@ __device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&dst)[
 
 // Flat tile x -> the unit (batch or sequence `b`, KV head `hk`) it belongs to, the tile index inside
 // the unit and the unit's tile count.
-template <bool VARLEN>
+template <bool VARLEN, int TILE>
 __device__ __forceinline__ void resolve_unit(const AffineParams &p, const VarlenAttnTable &vt, int64_t x, int tiles,
                                              int &unit, int &tile, int &utiles, int &hk, int &b) {
     if (!VARLEN) {
@@ -615,16 +622,17 @@ __device__ __forceinline__ void resolve_unit(const AffineParams &p, const Varlen
     for (int step = 16; step >= 1; step >>= 1)   // largest i with Hkv * tile_prefix[i] <= x
         if (i + step < vt.n && (int64_t)p.Hkv * vt.seq[i + step].tile_prefix <= x) i += step;
     const int64_t base = (int64_t)p.Hkv * vt.seq[i].tile_prefix;
-    utiles = (vt.seq[i].T + PK_TILE - 1) / PK_TILE;
+    utiles = (vt.seq[i].T + TILE - 1) / TILE;
     hk = (int)((x - base) / utiles);
     tile = (int)((x - base) % utiles);
     b = i;
     unit = i * p.Hkv + hk;
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN>
-__global__ void __launch_bounds__(PK_THREADS, MINB)
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, MINB)
 attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenAttnTable vt) {
+    constexpr int P8_WARPS = NW, P8_TILE = NW * 16;
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
     constexpr int WPR = RB / 4;
@@ -633,8 +641,8 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     constexpr int MPW = (BITS == 4) ? 2 : 1;
     constexpr int MPG = WPL * MPW;
     constexpr int SB = G * 2;
-    constexpr int CODE_TILE = PK_TILE * RB;
-    constexpr int SC_TILE = PK_TILE * SB;
+    constexpr int CODE_TILE = P8_TILE * RB;
+    constexpr int SC_TILE = P8_TILE * SB;
     constexpr int STAGE_BYTES = 2 * CODE_TILE + 4 * SC_TILE;
     constexpr int EPU = 16 / BITS;
     constexpr int CH = RB / 16;
@@ -654,8 +662,9 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     int *is_last = (int *)(empty + NSTAGE);
     // cross-warp buffers beside the ring (the ring stays live across segments)
     float *red_o = (float *)(is_last + 4);                               // [4][red_rows][RED_STRIDE]
-    float *red_ml = red_o + PK_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
-    float *work = red_ml + PK_WARPS * fp.red_rows * 2;                   // [red_rows][nslots]
+    float *red_ml = red_o + P8_WARPS * fp.red_rows * RED_STRIDE;         // [4][red_rows][2]
+    // the buffers behind keep 16-byte alignment (the staged query rows are a bulk-copy destination)
+    float *work = red_ml + ((P8_WARPS * fp.red_rows * 2 + 3) & ~3);      // [red_rows][nslots]
     // query rows of a segment's unit, brought in by the producer with one bulk copy (two buffers)
     uint64_t *qfull = (uint64_t *)(work + ((fp.red_rows * fp.nslots + 3) & ~3));
     uint64_t *qempty = qfull + 2;
@@ -671,13 +680,19 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], PK_WARPS);
+            mbar_init(&empty[s], P8_WARPS);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&qfull[s], 1);
-            mbar_init(&qempty[s], PK_WARPS);
+            mbar_init(&qempty[s], P8_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (256 % P8_TILE != 0) {
+        // a cut-short last tile leaves the end of its stage as it was: start from zeros, so that what the
+        // masked tokens multiply is always finite
+        for (int i = tid; i < RING / 16; i += (NW + 1) * 32) ((uint4 *)stages)[i] = make_uint4(0u, 0u, 0u, 0u);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
@@ -686,13 +701,13 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     bool ok = true;
     const int g = lane >> 2, c = lane & 3;
 
-    if (warp == PK_WARPS) {
+    if (warp == P8_WARPS) {
         // ---------------- producer: one stream of tiles across the segments ----------------
         if (lane == 0) {
             int it = 0, sg = 0;
             for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 int unit, tb, utiles, hk, b;
-                resolve_unit<VARLEN>(p, vt, x, tiles, unit, tb, utiles, hk, b);
+                resolve_unit<VARLEN, P8_TILE>(p, vt, x, tiles, unit, tb, utiles, hk, b);
                 const int n = (int)min((int64_t)(utiles - tb), x_hi - x);
                 if (p.q_bulk) {
                     const int qb = sg & 1;
@@ -718,19 +733,23 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
                     vs = (const T *)p.vs + b * p.vg_sb + hk * p.vg_sh;
                     vb = (const T *)p.vb + b * p.vg_sb + hk * p.vg_sh;
                 }
+                // tokens of this unit that copies may touch: the stored rows rounded up to 256 (inside the
+                // slab by the launch checks); a tile of 240 tokens may end past them and is then cut short
+                const int64_t t_pad = ((VARLEN ? (int64_t)vt.seq[b].T : p.T) + 255) / 256 * 256;
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % NSTAGE;
                     if (it >= NSTAGE) ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
                     if (!ok) break;
                     unsigned char *st = stages + (size_t)s * STAGE_BYTES;
-                    const int64_t t0 = (int64_t)(tb + j) * PK_TILE;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    bulk_load(st, kc + t0 * WPR, CODE_TILE, &full[s]);
-                    bulk_load(st + CODE_TILE, vc + t0 * WPR, CODE_TILE, &full[s]);
-                    bulk_load(st + 2 * CODE_TILE, ks + t0 * G, SC_TILE, &full[s]);
-                    bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, SC_TILE, &full[s]);
-                    bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, SC_TILE, &full[s]);
-                    bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, SC_TILE, &full[s]);
+                    const int64_t t0 = (int64_t)(tb + j) * P8_TILE;
+                    const uint32_t rows = (uint32_t)min((int64_t)P8_TILE, t_pad - t0);
+                    mbar_expect_tx(&full[s], rows * (2 * RB + 4 * SB));
+                    bulk_load(st, kc + t0 * WPR, rows * RB, &full[s]);
+                    bulk_load(st + CODE_TILE, vc + t0 * WPR, rows * RB, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE, ks + t0 * G, rows * SB, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + SC_TILE, kb + t0 * G, rows * SB, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + 2 * SC_TILE, vs + t0 * G, rows * SB, &full[s]);
+                    bulk_load(st + 2 * CODE_TILE + 3 * SC_TILE, vb + t0 * G, rows * SB, &full[s]);
                 }
                 x += n;
             }
@@ -745,7 +764,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
     int sg = 0;
     for (int64_t x = x_lo; x < x_hi; ++sg) {
         int unit, tile_begin, utiles, hk, b;
-        resolve_unit<VARLEN>(p, vt, x, tiles, unit, tile_begin, utiles, hk, b);
+        resolve_unit<VARLEN, P8_TILE>(p, vt, x, tiles, unit, tile_begin, utiles, hk, b);
         const int ntiles = (int)min((int64_t)(utiles - tile_begin), x_hi - x);
         const int64_t T_seq = VARLEN ? (int64_t)vt.seq[b].T : p.T;   // tokens of this unit's sequence
         // per-lane state for query rows 2c and 2c+1
@@ -857,7 +876,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
             const T *kbt = (const T *)(st + 2 * CODE_TILE + SC_TILE);
             const T *vst = (const T *)(st + 2 * CODE_TILE + 2 * SC_TILE);
             const T *vbt = (const T *)(st + 2 * CODE_TILE + 3 * SC_TILE);
-            const int t_blk = (tile_begin + jt) * PK_TILE + blk * 16;
+            const int t_blk = (tile_begin + jt) * P8_TILE + blk * 16;
             if (KVC_SKIP_BITS(p) & 6) {
                 // measurement aid (results are meaningless): 2 = only the K half, 4 = only the V half
                 if (KVC_SKIP_BITS(p) & 2) {
@@ -1067,7 +1086,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
         u.o_sh = p.o_sh; u.o_sl = p.o_sl;
         u.o_signs = nullptr;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
-        segment_epilogue<D, PK_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R,
+        segment_epilogue<D, P8_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R,
                                       x - tile_begin, utiles);
         x += ntiles;
     }
@@ -1097,26 +1116,27 @@ void launch_affine_typed(const AffineParams &p, int units, cudaStream_t stream) 
     ++g_launch_count;
 }
 
-template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN>
+template <typename T, int D, int BITS, int GROUP, int NSTAGE, int MINB, bool VARLEN, int NW>
 void launch_affine8_typed(const AffineParams &p, const VarlenAttnTable &vt, int ctas, cudaStream_t stream) {
+    constexpr int P8_WARPS = NW, P8_TILE = NW * 16, P8_THREADS = (NW + 1) * 32;
     constexpr int G = D / GROUP;
     constexpr int RB = D * BITS / 8;
-    constexpr int STAGE_BYTES = 2 * PK_TILE * RB + 4 * PK_TILE * G * 2;
-    const size_t red = (size_t)PK_WARPS * p.flat.red_rows * (D + 8) * 4 + (size_t)PK_WARPS * p.flat.red_rows * 8 +
+    constexpr int STAGE_BYTES = 2 * P8_TILE * RB + 4 * P8_TILE * G * 2;
+    const size_t red = (size_t)P8_WARPS * p.flat.red_rows * (D + 8) * 4 + (size_t)P8_WARPS * p.flat.red_rows * 8 + 32 +
                        (size_t)p.flat.red_rows * p.flat.nslots * 4 + 16 + 4 * sizeof(uint64_t) +
                        (size_t)2 * p.flat.red_rows * D * 2;
     const size_t smem = (size_t)NSTAGE * STAGE_BYTES + 16 + 2 * NSTAGE * sizeof(uint64_t) + 64 + red + 128;
     static size_t configured[64] = {0};
     const int dev = current_device();
     if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN, NW>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>,
+        KVC_CUDA(cudaFuncSetAttribute(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN, NW>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, 100));
         configured[dev] = smem;
     }
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN>, dim3(ctas), dim3(PK_THREADS),
+    KVC_CUDA(launch_pdl(attn_affine_decode8_kernel<T, D, BITS, GROUP, NSTAGE, MINB, VARLEN, NW>, dim3(ctas), dim3(P8_THREADS),
                         smem, stream, p, vt));
     timer.stop();
     KVC_CUDA(cudaGetLastError());
@@ -1130,7 +1150,7 @@ bool affine_source_fits(const KVSource &s, int D, int64_t T) {
     if (D % s.group) return false;
     const int wpr = D * s.bits / 32, G = D / s.group;
     if (s.st != wpr || s.gst != G) return false;  // rows must be contiguous
-    const int64_t padded = (T + PK_TILE - 1) / PK_TILE * PK_TILE;
+    const int64_t padded = (T + 255) / 256 * 256;   // the largest stage any of these kernels streams
     // a full last tile must stay inside the (batch, head) slab, and slabs must keep 16-byte alignment
     if (s.sh < padded * wpr || s.gsh < padded * G) return false;
     if ((s.sh * 4) % 16 || (s.sb * 4) % 16 || (s.gsh * 2) % 16 || (s.gsb * 2) % 16) return false;
@@ -1143,14 +1163,19 @@ bool affine_source_fits(const KVSource &s, int D, int64_t T) {
 namespace {
 const VarlenAttnTable kNoVarlen = {};
 
-int affine_resident_ctas(int D, int bits, int group, int rows) {
+constexpr int affine8_stages(int D, int bits, bool varlen) {
+    if (affine8_warps(D, bits, varlen) == 15) return 4;
+    return bits == 4 ? (D == 128 ? 5 : 8) : (D == 128 ? 4 : 6);
+}
+
+int affine_resident_ctas(int D, int bits, int group, int rows, bool varlen) {
     // CTAs that fit an SM by shared memory: ring + cross-warp buffers (+1 KB the driver reserves)
-    const int ns = bits == 4 ? (D == 128 ? 5 : 8) : (D == 128 ? 4 : 6);
-    const size_t stage = (size_t)2 * PK_TILE * (D * bits / 8) + (size_t)4 * PK_TILE * (D / group) * 2;
-    const size_t red = (size_t)PK_WARPS * rows * (D + 8) * 4 + (size_t)PK_WARPS * rows * 8 + (size_t)rows * 64 * 4 +
+    const int ns = affine8_stages(D, bits, varlen), nw = affine8_warps(D, bits, varlen), tile = nw * 16;
+    const size_t stage = (size_t)2 * tile * (D * bits / 8) + (size_t)4 * tile * (D / group) * 2;
+    const size_t red = (size_t)nw * rows * (D + 8) * 4 + (size_t)nw * rows * 8 + 32 + (size_t)rows * 64 * 4 +
                        64 + (size_t)2 * rows * D * 2;
     const size_t per_cta = ns * stage + red + 512 + 1024;
-    return (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / per_cta));
+    return (int)std::max<size_t>(1, std::min<size_t>(affine8_ctas(D, bits, varlen), (size_t)227 * 1024 / per_cta));
 }
 }  // namespace
 
@@ -1187,7 +1212,8 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
         sq.c_sh = a.k.sh; sq.g_sh = a.k.gsh;
         sq.T = (int32_t)a.T;
         sq.tile_prefix = (int32_t)prefix;
-        const int64_t tl = (a.T + PK_TILE - 1) / PK_TILE;
+        const int64_t tile8 = affine8_warps(a0.D, a0.k.bits, true) * 16;
+        const int64_t tl = (a.T + tile8 - 1) / tile8;
         prefix += tl;
         max_tiles = std::max(max_tiles, tl);
     }
@@ -1199,7 +1225,7 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
     int *counters = counters_get(a0.device, stream, PK_COUNTER_BYTES);
 
     const int64_t work_tiles = prefix * a0.Hkv;
-    const int resident = affine_resident_ctas(a0.D, a0.k.bits, a0.k.group, rep);
+    const int resident = affine_resident_ctas(a0.D, a0.k.bits, a0.k.group, rep, true);
     const int64_t ctas = std::min<int64_t>((int64_t)sm_count(a0.device) * resident, work_tiles);
     AffineParams p = {};
     p.flat.tiles = (int)max_tiles;
@@ -1228,7 +1254,7 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
     const int bits = a0.k.bits, group = a0.k.group;
 #define KVC_AFFV(TT, DD, BB, GG, NS)                                                        \
     if (a0.D == DD && bits == BB && group == GG) {                                           \
-        launch_affine8_typed<TT, DD, BB, GG, NS, 3, true>(p, vt, (int)ctas, stream);         \
+        launch_affine8_typed<TT, DD, BB, GG, affine8_stages(DD, BB, true), affine8_ctas(DD, BB, true), true, affine8_warps(DD, BB, true)>(p, vt, (int)ctas, stream);         \
         return 1;                                                                            \
     }
     if (a0.q_dtype == KVC_BF16) {
@@ -1261,9 +1287,10 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (!status) return 0;
     int *counters = counters_get(a.device, stream, PK_COUNTER_BYTES);
 
-    const int64_t tiles = (a.T + PK_TILE - 1) / PK_TILE;
-    // at most 8 query rows and chunk pairs inside one group: transposed decode kernel, 3 or 4 CTAs per SM
+    // at most 8 query rows and chunk pairs inside one group: transposed decode kernel (its own tile size)
     const bool decode8 = rep * a.L <= 8 && (2 * 8 * (16 / a.k.bits)) <= a.k.group;
+    const int64_t tile8 = affine8_warps(a.D, a.k.bits, false) * 16;
+    const int64_t tiles = decode8 ? (a.T + tile8 - 1) / tile8 : (a.T + PK_TILE - 1) / PK_TILE;
     // resident CTAs per SM (a fourth CTA fits the 4-bit kernels at 94 registers but measured slower)
     const int slots = sm_count(a.device) * (decode8 ? 3 : 2);
     int64_t best_s = 1;
@@ -1285,7 +1312,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     // decode8: flat decomposition over one wave of resident CTAs (every CTA streams the same number
     // of tiles); the partial slots per unit take the place of the splits
     const int64_t work_tiles = bh * tiles;
-    const int flat_resident = affine_resident_ctas(a.D, a.k.bits, a.k.group, rep * a.L);
+    const int flat_resident = affine_resident_ctas(a.D, a.k.bits, a.k.group, rep * a.L, false);
     const int64_t flat_ctas = std::min<int64_t>((int64_t)sm_count(a.device) * flat_resident, work_tiles);
     const int64_t flat_per = work_tiles / flat_ctas, flat_rem = work_tiles % flat_ctas;
     const int64_t flat_slots = (tiles + flat_per - 1) / flat_per + 1;
@@ -1324,7 +1351,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     const int bits = a.k.bits, group = a.k.group;
 #define KVC_AFF8(TT, DD, BB, GG, NS)                                         \
     if (a.D == DD && bits == BB && group == GG) {                            \
-        launch_affine8_typed<TT, DD, BB, GG, NS, 3, false>(p, kNoVarlen, units, stream); \
+        launch_affine8_typed<TT, DD, BB, GG, affine8_stages(DD, BB, false), affine8_ctas(DD, BB, false), false, affine8_warps(DD, BB, false)>(p, kNoVarlen, units, stream); \
         return 1;                                                            \
     }
     if (decode8) {
