@@ -42,13 +42,18 @@ namespace {
 
 using namespace dev;
 
-#ifndef KVC_V4_GROUP_WARPS
-#define KVC_V4_GROUP_WARPS 16
+// 15 consumer warps and one producer warp: 16 warps, so that a thread may hold 128 registers (a
+// seventeenth warp would round the CTA up to 20 in the register file's allocation and cap it at 96).
+#ifndef KVC_V4_WARPS
+#define KVC_V4_WARPS 15
 #endif
-constexpr int V4_WARPS = 16;                       // consumer warps
-constexpr int V4_GW = KVC_V4_GROUP_WARPS;          // warps that share a ring stage (16 tokens each)
-constexpr int V4_GROUPS = V4_WARPS / V4_GW;        // warp groups; group i takes every V4_GROUPS-th stage
-constexpr int V4_PRODUCERS = 4;                    // producer warps: one per array of a stage (a thread's bulk copies issue one after the other)
+#ifndef KVC_V4_PRODUCERS
+#define KVC_V4_PRODUCERS 1
+#endif
+constexpr int V4_WARPS = KVC_V4_WARPS;             // consumer warps
+constexpr int V4_GW = V4_WARPS;                    // warps that share a ring stage (16 tokens each)
+constexpr int V4_GROUPS = 1;                       // warp groups; group i takes every V4_GROUPS-th stage
+constexpr int V4_PRODUCERS = KVC_V4_PRODUCERS;     // producer warps: 4 = one per array of a stage, 1 = lanes 0..3 issue them
 constexpr int V4_THREADS = (V4_WARPS + V4_PRODUCERS) * 32;
 constexpr int V4_TILE = 16 * V4_GW;                // tokens per ring stage
 constexpr int V4_D = 128;
@@ -209,7 +214,7 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
 
     if (tid == 0) {
         for (int s = 0; s < nstage; ++s) {
-            mbar_init(&full[s], V4_PRODUCERS);
+            mbar_init(&full[s], 4);             // the four copies of a stage, each announced by its issuer
             mbar_init(&empty[s], V4_GW);            // the warps of the stage's group
         }
         for (int s = 0; s < 2; ++s) {
@@ -230,6 +235,12 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
         const int e = w >> 5;
         ((uint32_t *)tab)[e * 64 + 32 + (w & 31)] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
     }
+    if (256 % V4_TILE != 0) {
+        // a cut-short last stage leaves its end as it was: start from zeros, so that what the masked
+        // tokens multiply is always finite
+        for (int i = tid; i < nstage * (STAGE_BYTES / 16); i += V4_THREADS) ((uint4 *)stages)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
     pdl_wait();  // the tables came from kernel parameters; everything below reads global memory
 
@@ -241,8 +252,11 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
         // key norms, value norms) and announces its bytes on the stage's barrier (four arrivals fill
         // it); the copies of one thread issue one after the other, those of different warps overlap.
         // The first producer also stages the query rows of each segment.
-        const int pw = warp - V4_WARPS;
-        if (lane == 0 && !(KVC_SKIP_BITS(p) & 2)) {   // measurement bit 2: no loads at all (consumers compute on stale stages)
+        // which of the stage's four copies this thread issues: with four producer warps lane 0 of warp i,
+        // with one producer warp its lanes 0..3 (each announces its own bytes: four arrivals fill a stage)
+        const int pw = V4_PRODUCERS == 4 ? warp - V4_WARPS : lane;
+        const bool issuer = V4_PRODUCERS == 4 ? lane == 0 : lane < 4;
+        if (issuer && !(KVC_SKIP_BITS(p) & 2)) {   // measurement bit 2: no loads at all (consumers compute on stale stages)
             int it = 0, sg = 0;
             for (int64_t x = x_lo; x < x_hi && ok; ++sg) {
                 const int unit = (int)(x / tiles), tb = (int)(x % tiles);
@@ -257,20 +271,23 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
                     bulk_load(qbuf + (size_t)qb * (8 * D * 2), (const T *)p.q + b * p.q_sb + (int64_t)hk * rep * p.q_sh,
                               q_bytes, &qfull[qb]);
                 }
-                // this warp's array: source of token 0 of the unit, bytes per token, offset inside a stage
+                // this thread's array: source of token 0 of the unit, bytes per token, offset inside a stage
                 const unsigned char *src;
                 uint32_t per_token, dst_off;
                 if (pw == 0) { src = (const unsigned char *)(p.kp + b * p.kp_sb + hk * p.kp_sh); per_token = KW * 4; dst_off = 0; }
                 else if (pw == 1) { src = (const unsigned char *)(p.vp + b * p.vp_sb + hk * p.vp_sh); per_token = V4_VW * 4; dst_off = K_TILE; }
                 else if (pw == 2) { src = (const unsigned char *)(p.kn + b * p.kn_sb + hk * p.kn_sh); per_token = 4; dst_off = K_TILE + V_TILE; }
                 else { src = (const unsigned char *)(p.vn + b * p.vn_sb + hk * p.vn_sh); per_token = 4; dst_off = K_TILE + V_TILE + N_TILE; }
-                const uint32_t bytes = per_token * V4_TILE;
+                // tokens the copies may touch: the stored rows rounded up to 256 (inside the slab by the
+                // launch checks); a stage that would end past them is cut short
+                const int64_t t_pad = (p.T + 255) / 256 * 256;
                 for (int j = 0; j < n && ok; ++j, ++it) {
                     const int s = it % nstage;
                     if (it >= nstage) ok = mbar_wait(&empty[s], ((it / nstage) - 1) & 1);
                     if (!ok) break;
-                    mbar_expect_tx(&full[s], bytes);
                     const int64_t t0 = (int64_t)(tb + j) * V4_TILE;
+                    const uint32_t bytes = per_token * (uint32_t)min((int64_t)V4_TILE, t_pad - t0);
+                    mbar_expect_tx(&full[s], bytes);
                     bulk_load(stages + (size_t)s * STAGE_BYTES + dst_off, src + t0 * per_token, bytes, &full[s]);
                 }
                 x += n;
@@ -522,7 +539,7 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
 
         // ---- fold the 16 warps down to 4, lane to lane ----
 #pragma unroll 1
-        for (int half = V4_WARPS / 2; half >= 4; half >>= 1) {
+        for (int half = 8; half >= 4; half >>= 1) {   // warp w + half folds into warp w (a missing sixteenth warp folds nothing)
             consumer_bar<V4_WARPS>();   // the slots are free (first pass: the query fragments are in registers)
             if (warp >= half && warp < 2 * half) {
                 float *sl = slots + (warp - half) * V4_SLOT_FLOATS + lane;
@@ -534,7 +551,7 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
                 sl[34 * 32] = l_run[0]; sl[35 * 32] = l_run[1];
             }
             consumer_bar<V4_WARPS>();
-            if (warp < half) {
+            if (warp < half && warp + half < V4_WARPS) {
                 const float *sl = slots + warp * V4_SLOT_FLOATS + lane;
                 float fa[2], fb[2];
 #pragma unroll
@@ -643,7 +660,7 @@ int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream) {
     if (bh * (int64_t)sizeof(int) > V4_COUNTER_BYTES) return 0;
     {
         // a full last stage must stay inside the (batch, head) slab
-        const int64_t padded = (a.T + V4_TILE - 1) / V4_TILE * V4_TILE;
+        const int64_t padded = (a.T + 255) / 256 * 256;
         if (a.k.sh < padded * a.k.words || a.v.sh < padded * a.v.words || a.k.gsh < padded || a.v.gsh < padded) return 0;
     }
     int *status = device_status_word(a.device);
