@@ -79,7 +79,7 @@ MIN_TIMED_S = 0.5  # the timed region is repeated (whole passes of K steps) unti
 # captures summarised under profiles/ (taken on the 2-layer variants: a launch is the same size)
 NCU_TRAFFIC_BYTES = {
     "cfg2_simple_bf16_llama3_8b": (268.8e6 + 5.0e6, "profiles/attn_decode_flat_bf16_cfg2_llama3_8b.md"),
-    "cfg4_quant4_bf16_qwen2_7b": (322.8e6 + 4.4e6, "profiles/attn_affine_decode8_cfg4_qwen2_7b.md"),
+    "cfg4_quant4_bf16_qwen2_7b": (323.8e6 + 4.4e6, "profiles/attn_affine_decode8_cfg4_qwen2_7b.md"),
     "cfg5_turbo_k3v4_llama3_70b": (506.2e6 + 4.1e6, "profiles/attn_turbo_v4_cfg5_llama3_70b.md"),
 }
 for _k in ("cfg2", "cfg4", "cfg5"):
