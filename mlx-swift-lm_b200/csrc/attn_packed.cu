@@ -67,6 +67,7 @@ struct AffineParams {
     float scale_log2;
     FlatPlan flat;  // decode8 kernel: flat tile decomposition
     int32_t q_bulk; // decode8 kernel: a unit's query rows are one contiguous 16-byte aligned block
+    int32_t chunks; // decode8 kernel: units per (batch, kv head) = ceil(query rows of the group / 8); 1 for decode
 };
 
 // One decode step for a list of independent caches (one sequence each, its own length) in one
@@ -614,8 +615,9 @@ __device__ __forceinline__ void resolve_unit(const AffineParams &p, const Varlen
         unit = (int)(x / tiles);
         tile = (int)(x % tiles);
         utiles = tiles;
-        hk = unit % p.Hkv;
-        b = unit / p.Hkv;
+        const int bh = unit / p.chunks;   // a group of more than eight query rows is cut into units of eight
+        hk = bh % p.Hkv;
+        b = bh / p.Hkv;
         return;
     }
     int i = 0;
@@ -672,10 +674,10 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rep = p.Hq / p.Hkv;
-    const int R = rep * p.L;  // <= 8
+    const int R_all = rep * p.L;   // query rows of a (batch, kv head) group; a unit carries up to eight of them
     const int tiles = fp.tiles;
     const int64_t x_lo = flat_lo(fp, blockIdx.x), x_hi = flat_lo(fp, blockIdx.x + 1);
-    const uint32_t q_bytes = (uint32_t)R * D * 2;
+    const uint32_t q_bytes = (uint32_t)R_all * D * 2;   // bulk staging only runs with one unit per group
 
     if (tid == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -767,6 +769,8 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
         resolve_unit<VARLEN, P8_TILE>(p, vt, x, tiles, unit, tile_begin, utiles, hk, b);
         const int ntiles = (int)min((int64_t)(utiles - tile_begin), x_hi - x);
         const int64_t T_seq = VARLEN ? (int64_t)vt.seq[b].T : p.T;   // tokens of this unit's sequence
+        const int row0 = VARLEN ? 0 : (unit % p.chunks) * 8;         // first query row of the group this unit carries
+        const int R = min(8, R_all - row0);
         // per-lane state for query rows 2c and 2c+1
         float m_run[2], l_run[2] = {0.f, 0.f};
         float bsum[2][G];
@@ -804,7 +808,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
                 kslot_dims<BITS>(gr * WPG + c * WPL + m / MPW, m % MPW, dd);
                 float x[4] = {0.f, 0.f, 0.f, 0.f};
                 if (g < R && ok) {
-                    const int hq = hk * rep + g / p.L, l = g % p.L;
+                    const int hq = hk * rep + (row0 + g) / p.L, l = (row0 + g) % p.L;
                     const T *qp = q_stage ? q_stage + g * D
                                   : VARLEN ? (const T *)vt.seq[b].q + hq * p.q_sh + l * p.q_sl
                                            : (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl;
@@ -840,7 +844,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int r = 2 * c + k;
-            const int l = (r < R) ? r % p.L : 0;
+            const int l = (r < R) ? (row0 + r) % p.L : 0;
             row_limit[k] = p.causal ? (int)min((int64_t)t_last, p.causal_offset + l) : t_last;
         }
         const int min_limit = p.causal ? (int)min((int64_t)t_last, p.causal_offset) : t_last;
@@ -1087,7 +1091,7 @@ attn_affine_decode8_kernel(const AffineParams p, const __grid_constant__ VarlenA
         u.o_signs = nullptr;
         u.splits = 0; u.Hq = p.Hq; u.L = p.L;
         segment_epilogue<D, P8_WARPS>(u, fp, red_o, red_ml, RED_STRIDE, work, is_last, unit, b, hk, rep, R,
-                                      x - tile_begin, utiles);
+                                      x - tile_begin, utiles, row0);
         x += ntiles;
     }
 }
@@ -1248,6 +1252,7 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
     p.counters = counters; p.status = status;
     p.B = n; p.Hq = a0.Hq; p.Hkv = a0.Hkv; p.L = 1; p.T = 0;
     p.splits = p.flat.nslots;
+    p.chunks = 1;
     p.causal = 0;
     p.causal_offset = 0;
     p.scale_log2 = a0.scale * 1.4426950408889634f;
@@ -1277,18 +1282,24 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (a.k.bits != a.v.bits || a.k.group != a.v.group) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv) return 0;
     const int rep = a.Hq / a.Hkv;
-    if (rep * a.L > 16 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    if (rep * a.L > 64 || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     if (!affine_source_fits(a.k, a.D, a.T) || !affine_source_fits(a.v, a.D, a.T)) return 0;
     if (a.D / a.k.group > 4 || (a.k.group * a.k.bits) / 32 < 4) return 0;
     if (((uintptr_t)a.q & 1)) return 0;
-    const int64_t bh = (int64_t)a.B * a.Hkv;
+    // Up to 8 query rows per kv head: the transposed decode kernel. 9..16 rows: the 16-row kernel.
+    // 17..64 rows (a verify round of a wide head group): the decode kernel again, the group cut into
+    // units of eight rows that stream the same tiles one after the other (all but the first out of L2).
+    const bool pairs_fit = (2 * 8 * (16 / a.k.bits)) <= a.k.group;
+    const int chunks = rep * a.L > 16 ? (rep * a.L + 7) / 8 : 1;
+    if (chunks > 1 && !pairs_fit) return 0;
+    const int64_t bh = (int64_t)a.B * a.Hkv * chunks;
     if (bh * (int64_t)sizeof(int) > PK_COUNTER_BYTES) return 0;
     int *status = device_status_word(a.device);
     if (!status) return 0;
     int *counters = counters_get(a.device, stream, PK_COUNTER_BYTES);
 
     // at most 8 query rows and chunk pairs inside one group: transposed decode kernel (its own tile size)
-    const bool decode8 = rep * a.L <= 8 && (2 * 8 * (16 / a.k.bits)) <= a.k.group;
+    const bool decode8 = (rep * a.L <= 8 || chunks > 1) && pairs_fit;
     const int64_t tile8 = affine8_warps(a.D, a.k.bits, false) * 16;
     const int64_t tiles = decode8 ? (a.T + tile8 - 1) / tile8 : (a.T + PK_TILE - 1) / PK_TILE;
     // resident CTAs per SM (a fourth CTA fits the 4-bit kernels at 94 registers but measured slower)
@@ -1312,7 +1323,7 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     // decode8: flat decomposition over one wave of resident CTAs (every CTA streams the same number
     // of tiles); the partial slots per unit take the place of the splits
     const int64_t work_tiles = bh * tiles;
-    const int flat_resident = affine_resident_ctas(a.D, a.k.bits, a.k.group, rep * a.L, false);
+    const int flat_resident = affine_resident_ctas(a.D, a.k.bits, a.k.group, std::min(8, rep * a.L), false);
     const int64_t flat_ctas = std::min<int64_t>((int64_t)sm_count(a.device) * flat_resident, work_tiles);
     const int64_t flat_per = work_tiles / flat_ctas, flat_rem = work_tiles % flat_ctas;
     const int64_t flat_slots = (tiles + flat_per - 1) / flat_per + 1;
@@ -1344,8 +1355,9 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     p.scale_log2 = a.scale * 1.4426950408889634f;
     p.flat.tiles = (int)tiles;
     p.flat.per = (int)flat_per; p.flat.rem = (int)flat_rem;
-    p.flat.nslots = (int)flat_slots; p.flat.red_rows = rep * a.L;
-    p.q_bulk = (a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
+    p.flat.nslots = (int)flat_slots; p.flat.red_rows = decode8 ? std::min(8, rep * a.L) : rep * a.L;
+    p.chunks = chunks;
+    p.q_bulk = (chunks == 1 && a.L == 1 && a.q_sh == a.D && ((uintptr_t)a.q & 15) == 0 && (a.q_sb * 2) % 16 == 0) ? 1 : 0;
     const int units = decode8 ? (int)flat_ctas : (int)(bh * splits);
 
     const int bits = a.k.bits, group = a.k.group;

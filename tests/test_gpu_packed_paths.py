@@ -295,3 +295,30 @@ def test_calibrated_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, c
     from helpers import worst_excess
     assert worst_excess(out, ref, dtype) <= 0
     assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,bits,group,P,L", [
+    (2, 28, 4, 4, 64, 1000, 6),      # Qwen2-7B layout, verify round: 42 rows per kv head = six units (the last carries two)
+    (1, 32, 4, 8, 64, 517, 5),       # 8-bit codes, 40 rows
+    (2, 8, 1, 4, 128, 2049, 8),      # 64 rows, the most the decode kernel takes; group 128
+    (1, 17, 1, 4, 64, 300, 1),       # 17 heads on one kv head, one position, no causal limit to speak of
+])
+def test_affine_verify_rounds_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle, cuda, dtype, B, Hq, Hkv, bits, group, P, L):
+    """17 to 64 query rows per kv head over the affine cache: the group is cut into units of eight rows,
+    each streamed through the 8-row decode kernel with its own causal limits (one attention launch)."""
+    D = 128
+    g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.update_quantized(k.to(cuda), v.to(cuda))
+    o.update_quantized(to_oracle(k), to_oracle(v))
+    for rnd in range(2):
+        q = seeded((B, Hq, L, D), 3 + rnd, dtype)
+        k1, v1 = seeded((B, Hkv, L, D), 5 + rnd, dtype), seeded((B, Hkv, L, D), 7 + rnd, dtype)
+        kvc.launch_count(reset=True)
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
+        assert kvc.launch_count(reset=True) == 2            # quantise-append + one attention launch
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
+        assert g.trim(L - 1) == o.trim(L - 1)
+    assert kvc.lib().kvc_device_status() == 0
