@@ -27,7 +27,7 @@ SOURCES = [
     "attn_decode.cu",
     "attn_packed.cu",
     "attn_turbo.cu", "attn_turbo_v4.cu",
-    "attn_chunk_packed.cu", "attn_chunk_tc.cu", "attn_chunk_mat.cu",
+    "attn_chunk_packed.cu", "attn_chunk_tc.cu", "attn_chunk_mat.cu", "attn_verify_tc.cu",
     "attn_dispatch.cu",
     "cache.cu",
     "round.cu",

@@ -205,6 +205,21 @@ void rotate_rows(const RotParams &p, int D, cudaStream_t stream) {
 
 }  // namespace
 
+// out[row] = post * H(pre * in[row]) / sqrt(D) over [B, H, L, D] rows (D 64 or 128); f16 / bf16 in and out.
+void launch_rotate_rows_f16(const void *in, void *out, int32_t in_dtype, int32_t out_dtype, int64_t i_sb, int64_t i_sh, int64_t i_sl,
+                            int64_t o_sb, int64_t o_sh, int64_t o_sl, int B, int H, int L, int D, const float *pre,
+                            const float *post, cudaStream_t stream) {
+    RotParams rp = {};
+    rp.in = in; rp.out = out;
+    rp.i_sb = i_sb; rp.i_sh = i_sh; rp.i_sl = i_sl; rp.o_sb = o_sb; rp.o_sh = o_sh; rp.o_sl = o_sl;
+    rp.B = B; rp.H = H; rp.L = L;
+    rp.pre = pre; rp.post = post; rp.post2 = nullptr;
+    if (in_dtype == KVC_F16 && out_dtype == KVC_BF16) rotate_rows<__half, __nv_bfloat16>(rp, D, stream);
+    else if (in_dtype == KVC_F16) rotate_rows<__half, __half>(rp, D, stream);
+    else if (out_dtype == KVC_F16) rotate_rows<__nv_bfloat16, __half>(rp, D, stream);
+    else rotate_rows<__nv_bfloat16, __nv_bfloat16>(rp, D, stream);
+}
+
 // Returns the number of kernels launched, 0 when the call is left to the other chunk kernels.
 // KVC_CHUNK_MAT=0 turns the path off.
 int launch_attention_chunk_materialized(const AttnArgs &a, cudaStream_t stream) {

@@ -493,7 +493,8 @@ bool turbo_source_fits(const KVSource &s, int D, int64_t T) {
 
 }  // namespace
 
-int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream);   // attn_turbo_v4.cu: 4-bit values
+int launch_attention_turbo_v4(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream);   // attn_turbo_v4.cu: 4-bit values
 
 // Returns the number of kernels launched, or 0 when the call does not fit this path.
 int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
@@ -507,6 +508,10 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream) {
     if (!turbo_source_fits(a.k, a.D, a.T) || !turbo_source_fits(a.v, a.D, a.T)) return 0;
     if (((uintptr_t)a.q & 1)) return 0;
     const int kb = a.k.bits, vb = a.v.bits;
+    if (vb == 4 && rep * a.L > 8) {   // a verify round: the group's rows on the tensor-core kernel, keys and values decoded once
+        const int n = launch_attention_verify_tc(a, stream);
+        if (n > 0) return n;
+    }
     if (vb == 4) {   // key bits 2..4; also takes short chunks (up to 64 query rows per kv head), eight rows at a time
         const int n = launch_attention_turbo_v4(a, stream);
         if (n > 0) return n;

@@ -1,0 +1,709 @@
+// Speculative verify rounds over the TurboQuant cache on the 5th-generation tensor cores.
+//
+// TurboQuantKVCache.compressedAttention for a handful of query positions per head
+// (TurboQuantKVCache.swift:1164-1446; the reference's kernel for this step is the causal flash pass at
+// TurboQuantKernels.swift:879-1026): the rows of a KV head's group (rep heads x L positions, 9 ... 128
+// of them) all read the same keys and values, so the packed rows should be decoded ONCE for the
+// group. The decode kernel cannot do that (its accumulators for more than eight rows do not fit the
+// register file); here the group's rows are the 128-row M side of tcgen05.mma and the accumulators
+// live in TMEM.
+//
+// One CTA per (batch, KV head, split of the keys):
+//   warp 0      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
+//   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
+//   warps 4, 5  softmax: thread = query row = TMEM lane 0..63 (a group has at most 64 rows here, and a warp
+//               reaches the TMEM lanes 32 * (warp % 4) ...)
+//   warps 8, 9  correction: thread = query row, folds O_j into the row's register accumulator (as the
+//               correction warps of attn_chunk_tc.cu)
+//   warps 2, 3, 6, 7  row writers: thread = key row of the tile; the row's packed indices and norm are
+//               copied one tile ahead into shared memory (cp.async by the thread itself), then looked
+//               up, multiplied by the norm and written as the f16 row of the swizzled K / V tile the
+//               tensor cores read (K_{j+1} and V_j per step)
+// Key centroids come from a lane-replicated table of index PAIRS (conflict-free whatever the
+// indices), value centroids from a table of index pairs kept in eight copies (lane l reads copy l % 8).
+// Keys past T are written as zero rows, so masked probabilities never meet a non-finite value.
+//
+// splits > 1 (few units): every CTA writes its rows un-normalised with (max, sum); a merge kernel
+// combines them. The outputs are rows in the rotated basis (f16); the caller rotates them back.
+// Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
+// its TMEM.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <type_traits>
+
+#include "attn_common.cuh"
+#include "common.h"
+#include "tc_common.cuh"
+
+namespace kvc {
+
+void launch_rotate_rows_f16(const void *in, void *out, int32_t in_dtype, int32_t out_dtype, int64_t i_sb, int64_t i_sh, int64_t i_sl,
+                            int64_t o_sb, int64_t o_sh, int64_t o_sl, int B, int H, int L, int D, const float *pre,
+                            const float *post, cudaStream_t stream);
+
+namespace {
+
+using namespace dev;
+using namespace tc;
+
+constexpr int VT_D = 128;
+constexpr int VT_THREADS = 320;
+constexpr int VT_TILE = TC_TILE;             // 32 KB: 128 rows x 128 f16
+
+struct VerifyParams {
+    const uint32_t *kp, *vp;               // packed indices [B, H, cap, words]
+    const float *kn, *vn;                  // norms [B, H, cap]
+    int64_t kp_sb, kp_sh, vp_sb, vp_sh, kn_sb, kn_sh, vn_sb, vn_sh;
+    float kcb[16], vcb[16];
+    void *out;                             // f16 rows, rotated basis, [B, Hq, L, D] with these strides
+    int64_t o_sb, o_sh, o_sl;
+    int32_t B, Hq, Hkv, L, R;              // R = (Hq / Hkv) * L rows per unit
+    int64_t T;
+    int32_t causal;
+    int64_t causal_offset;
+    float scale_log2;
+    int32_t splits, tiles_per_split;
+    float *o_part;                         // [unit][split][R][D]
+    float2 *ml_part;                       // [unit][split][R] (log2-domain max, sum)
+    int *status;
+    int32_t debug_skip;                    // measurement builds only (KVC_SKIP_BITS)
+};
+
+enum : int {
+    VB_Q = 0,
+    VB_K_FULL = 1,                     // [2] 128 arrivals: the key rows of a tile are written
+    VB_K_EMPTY = VB_K_FULL + 2,        // [2] the S product has read the tile
+    VB_V_FULL = VB_K_EMPTY + 2,        // [2]
+    VB_V_EMPTY = VB_V_FULL + 2,        // [2]
+    VB_S_FULL = VB_V_EMPTY + 2,        // [2]
+    VB_S_EMPTY = VB_S_FULL + 2,        // [2]
+    VB_P_FULL = VB_S_EMPTY + 2,        // [1]
+    VB_P_EMPTY = VB_P_FULL + 1,        // [1]
+    VB_O_FULL = VB_P_EMPTY + 1,        // [2]
+    VB_O_EMPTY = VB_O_FULL + 2,        // [2]
+    VB_A_FULL = VB_O_EMPTY + 2,        // [2]
+    VB_A_EMPTY = VB_A_FULL + 2,        // [2]
+    VB_L_FULL = VB_A_EMPTY + 2,
+    VB_COUNT = VB_L_FULL + 1
+};
+
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// Index pair p (bits [2*KB*p, 2*KB*(p+1)) of the row's word stream); p is a compile-time constant
+// after unrolling, so the shifts are immediates.
+template <int KB, int NW>
+__device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int p) {
+    constexpr int B2 = 2 * KB;
+    const int bit = B2 * p, k = bit >> 5, s = bit & 31;
+    uint32_t x = w[k] >> s;
+    if (s + B2 > 32) x |= w[k + 1] << (32 - s);
+    return x & ((1u << B2) - 1u);
+}
+
+template <typename TQ, int KB>
+__global__ void __launch_bounds__(VT_THREADS, 1)
+attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ VerifyParams p) {
+    constexpr int D = VT_D;
+    constexpr int KW = D * KB / 32;          // key words per row
+    constexpr int VW = D * 4 / 32;           // value words per row (4-bit)
+    constexpr int KTAB_ENTRIES = 1 << (2 * KB);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char *sq = base;                                  // Q' block
+    unsigned char *skv = sq + VT_TILE;                         // stage s: K tile | V tile
+    unsigned char *sp = skv + 2 * 2 * VT_TILE;                 // one P tile
+    uint32_t *ktab = (uint32_t *)(sp + VT_TILE);               // [entries][32 lanes] f16x2
+    uint32_t *vtab = ktab + KTAB_ENTRIES * 32;                 // [256 byte values][8 copies] f16x2(c[b & 15], c[b >> 4])
+    // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
+    // held them across the correction step pushed the row accumulator into local memory)
+    uint32_t *kstage = vtab + 256 * 8;                         // [128][KW]
+    uint32_t *vstage = kstage + TC_KEYS * KW;                  // [128][VW]
+    float *nstage = (float *)(vstage + TC_KEYS * VW);          // [2][128] key norms | value norms
+    uint64_t *bars = (uint64_t *)(nstage + 2 * TC_KEYS);
+    uint32_t *tmem_slot = (uint32_t *)(bars + VB_COUNT);
+    float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128]
+    float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128]
+    float *s_mfin = s_lsum + TC_ROWS;                          // [128]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int unit = blockIdx.x / p.splits, split = blockIdx.x % p.splits;
+    const int hk = unit % p.Hkv, b = unit / p.Hkv;
+    const int rep = p.Hq / p.Hkv;
+    const int n_all = (int)((p.T + TC_KEYS - 1) / TC_KEYS);
+    const int j_lo = split * p.tiles_per_split, j_hi = min(n_all, j_lo + p.tiles_per_split);
+    const int n_tiles = max(0, j_hi - j_lo);
+
+    if (tid == 0) {
+        mbar_init(&bars[VB_Q], 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars[VB_K_FULL + s], 128);
+            mbar_init(&bars[VB_K_EMPTY + s], 1);
+            mbar_init(&bars[VB_V_FULL + s], 128);
+            mbar_init(&bars[VB_V_EMPTY + s], 1);
+            mbar_init(&bars[VB_S_FULL + s], 1);
+            mbar_init(&bars[VB_S_EMPTY + s], 64);      // the two softmax warps
+            mbar_init(&bars[VB_O_FULL + s], 1);
+            mbar_init(&bars[VB_O_EMPTY + s], 64);      // the two correction warps
+            mbar_init(&bars[VB_A_FULL + s], 64);
+            mbar_init(&bars[VB_A_EMPTY + s], 64);
+        }
+        mbar_init(&bars[VB_P_FULL], 64);
+        mbar_init(&bars[VB_P_EMPTY], 1);
+        mbar_init(&bars[VB_L_FULL], 64);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // tables: key entry e of lane l = f16x2(centroid[e & m], centroid[e >> KB]); value entry i = (c, c)
+    for (int w = tid; w < KTAB_ENTRIES * 32; w += VT_THREADS) {
+        const int e = w >> 5;
+        ktab[w] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
+    }
+    for (int w = tid; w < 256 * 8; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 3) & 15], p.vcb[w >> 7]);
+    // the P tile's rows 64 .. 127 are never written (no query row lives there): zeros, so that the
+    // products of those rows stay finite
+    for (int i = tid; i < VT_TILE / 16; i += VT_THREADS) ((uint4 *)sp)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars[VB_Q], VT_TILE);
+            tma_load_4d(sq, &qmap, &bars[VB_Q], 0, 0, unit, 0);
+            tma_load_4d(sq + TC_BOX, &qmap, &bars[VB_Q], 64, 0, unit, 0);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);                 // f16 x f16 -> f32
+            constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+            const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
+            const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
+            const uint64_t v_desc = umma_desc(smem_u32(skv) + VT_TILE, 16384, 1024);
+            const uint64_t p_desc = umma_desc(smem_u32(sp), 16, 1024);
+            bool ok = mbar_wait(&bars[VB_Q], 0);
+            auto issue_s = [&](int j) {
+                const int s = j & 1;
+                if (!mbar_wait(&bars[VB_K_FULL + s], (j >> 1) & 1)) return false;
+                if (j >= 2 && !mbar_wait(&bars[VB_S_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+                tc_fence_after();
+                const uint64_t kd = k_desc + (uint64_t)(s * (2 * VT_TILE / 16));
+                const uint32_t d_addr = tmem + (uint32_t)s * 128u;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
+                    umma_f16(d_addr, q_desc + off, kd + off, IDESC, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars[VB_S_FULL + s]);
+                umma_commit(&bars[VB_K_EMPTY + s]);
+                return true;
+            };
+            if (ok && n_tiles > 0) ok = issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = issue_s(j + 1);
+                if (!ok) break;
+                const int s = j & 1;
+                ok = mbar_wait(&bars[VB_V_FULL + s], (j >> 1) & 1);
+                if (ok) ok = mbar_wait(&bars[VB_P_FULL], j & 1);
+                if (ok && j >= 2) ok = mbar_wait(&bars[VB_O_EMPTY + s], ((j >> 1) - 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t vd = v_desc + (uint64_t)(s * (2 * VT_TILE / 16));
+                const uint32_t o_addr = tmem + 256u + (uint32_t)s * 128u;
+#pragma unroll
+                for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
+                    const uint64_t a_off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
+                    umma_f16(o_addr, p_desc + a_off, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars[VB_O_FULL + s]);
+                umma_commit(&bars[VB_P_EMPTY]);
+                umma_commit(&bars[VB_V_EMPTY + s]);
+            }
+            if (!ok) atomicExch(p.status, 26);
+        }
+    } else if (warp == 4 || warp == 5) {
+        // ---------------- softmax: thread = row (TMEM lanes 0..63) ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        // warp-uniform: the TMEM loads below are warp-wide. A warp with any row of the group works on all
+        // its 32 rows (the rows past the group have zero queries: finite scores, results never stored).
+        constexpr bool live = true;   // both warps run all their rows: rows past the group have zero queries
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const int l_pos = row % p.L;
+        const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l_pos) : p.T - 1;
+        const int64_t min_limit = p.causal ? min(p.T - 1, p.causal_offset) : p.T - 1;   // the smallest limit of a live row
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        unsigned char *p_row = sp + row * 128;
+        const int sw = row & 7;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t raw[TC_KEYS];
+            if (live) {
+                const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb) tmem_ld32_issue(s_addr + cb * 32, raw + cb * 32);
+                tmem_ld_wait();
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);
+            float alpha = 0.f, neg_m = 0.f, m_new = -INFINITY;
+            if (live) {
+                const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
+                if (key0 + TC_KEYS - 1 > min_limit) {
+#pragma unroll
+                    for (int i = 0; i < TC_KEYS; ++i)
+                        if (key0 + i > limit) raw[i] = 0xff800000u;   // -inf
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < TC_KEYS; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                m_new = fmaxf(m_run, mx * p.scale_log2);
+                alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+                neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+            }
+            if (j >= 2) ok = mbar_wait(&bars[VB_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
+            if (!ok) break;
+            s_alpha[(j & 1) * TC_ROWS + row] = alpha;
+            mbar_arrive(&bars[VB_A_FULL + (j & 1)]);
+            // the single P tile is free once the O product of the tile before has read it
+            if (j >= 1) ok = mbar_wait(&bars[VB_P_EMPTY], (j - 1) & 1);
+            if (!ok) break;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int kc = 0; kc < TC_KEYS / 8; ++kc) {
+                uint4 w = make_uint4(0u, 0u, 0u, 0u);
+                if (live && !(KVC_SKIP_BITS(p) & 16)) {
+                    float e[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));
+                        sum4[i & 3] += e[i];
+                    }
+                    w.x = pack_h2(e[0], e[1]);
+                    w.y = pack_h2(e[2], e[3]);
+                    w.z = pack_h2(e[4], e[5]);
+                    w.w = pack_h2(e[6], e[7]);
+                }
+                *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bars[VB_P_FULL]);
+            if (live) {
+                l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                m_run = m_new;
+            }
+        }
+        if (ok) {
+            s_lsum[row] = l_run;
+            s_mfin[row] = m_run;
+            mbar_arrive(&bars[VB_L_FULL]);
+        } else {
+            atomicExch(p.status, 27);
+        }
+    } else if (warp == 8 || warp == 9) {
+        // ---------------- correction: thread = query row (TMEM lanes 0..63) ----------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + 256u;
+        constexpr bool live = true;
+        float o_acc[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+        bool ok = true;
+        auto correct = [&](int j) {      // fold O_j into the row's accumulator
+            if (!mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
+            mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
+            if (!mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            tc_fence_after();
+            if (live && !(KVC_SKIP_BITS(p) & 4)) {
+#pragma unroll
+                for (int half = 0; half < D / 64; ++half) {
+                    uint32_t raw[64];
+                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64, raw);
+                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64 + 32, raw + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) o_acc[half * 64 + i] = fmaf(o_acc[half * 64 + i], alpha, __uint_as_float(raw[i]));
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars[VB_O_EMPTY + (j & 1)]);
+            return true;
+        };
+
+        for (int j = 0; j < n_tiles && ok; ++j) ok = correct(j);
+        if (ok) ok = mbar_wait(&bars[VB_L_FULL], 0);
+        if (!ok) {
+            atomicExch(p.status, 28);
+        } else if (row < p.R) {
+            const float l_sum = s_lsum[row];
+            const int hq = hk * rep + row / p.L, lq = row % p.L;
+            if (p.splits == 1) {
+                const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+                __half *dst = (__half *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl;
+#pragma unroll
+                for (int c8 = 0; c8 < D / 8; ++c8) {
+                    uint4 w;
+                    w.x = pack_h2(o_acc[c8 * 8 + 0] * inv, o_acc[c8 * 8 + 1] * inv);
+                    w.y = pack_h2(o_acc[c8 * 8 + 2] * inv, o_acc[c8 * 8 + 3] * inv);
+                    w.z = pack_h2(o_acc[c8 * 8 + 4] * inv, o_acc[c8 * 8 + 5] * inv);
+                    w.w = pack_h2(o_acc[c8 * 8 + 6] * inv, o_acc[c8 * 8 + 7] * inv);
+                    *(uint4 *)(dst + c8 * 8) = w;
+                }
+            } else {
+                const int64_t slot = ((int64_t)unit * p.splits + split) * p.R + row;
+                float4 *dst = (float4 *)(p.o_part + slot * D);
+#pragma unroll
+                for (int c4 = 0; c4 < D / 4; ++c4) dst[c4] = make_float4(o_acc[c4 * 4], o_acc[c4 * 4 + 1], o_acc[c4 * 4 + 2], o_acc[c4 * 4 + 3]);
+                p.ml_part[slot] = make_float2(s_mfin[row], l_sum);
+            }
+        }
+    } else if (warp >= 2) {
+        // ---------------- row writers: thread = key row of the tile ----------------
+        const int row = ((warp & 1) + (warp >= 6 ? 2 : 0)) * 32 + lane;      // warps 2, 3, 6, 7 -> rows 0..127
+        const uint32_t *kbase = p.kp + b * p.kp_sb + hk * p.kp_sh;
+        const uint32_t *vbase = p.vp + b * p.vp_sb + hk * p.vp_sh;
+        const float *knb = p.kn + b * p.kn_sb + hk * p.kn_sh;
+        const float *vnb = p.vn + b * p.vn_sb + hk * p.vn_sh;
+        const uint32_t ktab_a = smem_u32(ktab) + (uint32_t)lane * 4u;
+        const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)(lane & 7) * 4u;   // this lane's copy of the value pair table
+        const int sw = row & 7;
+        bool ok = true;
+        const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
+        const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
+        // every fetch is one cp.async group of this thread (an empty one past the last tile), so that the
+        // waits below can count groups
+        auto fetch_k = [&](int j) {      // tile j of this CTA's range
+            if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
+                const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
+                const uint32_t *src = kbase + t * KW;
+#pragma unroll
+                for (int i = 0; i < KW / 4; ++i)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kst_a + 16u * i), "l"(src + 4 * i) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(knst_a), "l"(knb + t) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto fetch_v = [&](int j) {
+            if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
+                const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
+                const uint32_t *src = vbase + t * VW;
+#pragma unroll
+                for (int i = 0; i < VW / 4; ++i)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vst_a + 16u * i), "l"(src + 4 * i) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(vnst_a), "l"(vnb + t) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
+            const int s = j & 1;
+            if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+            uint32_t kw[KW];
+#pragma unroll
+            for (int i = 0; i < KW / 4; ++i)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(kw[4 * i]), "=r"(kw[4 * i + 1]), "=r"(kw[4 * i + 2]), "=r"(kw[4 * i + 3]) : "r"(kst_a + 16u * i));
+            float knorm;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
+            fetch_k(j + 1);   // the row is in registers: its place takes the next tile's copy while this one is decoded
+            unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
+            const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
+            const float nf = fminf(knorm, 65504.f);
+            const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+#pragma unroll
+            for (int c8 = 0; c8 < D / 8; ++c8) {
+                uint32_t v4[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint32_t e = pair_index<KB, KW>(kw, c8 * 4 + q4);
+                    uint32_t t2;
+                    if (KVC_SKIP_BITS(p) & 2) t2 = e;
+                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2) : "r"(ktab_a + (e << 7)));
+                    v4[q4] = hmul2(t2, n2);
+                }
+                *(uint4 *)(dst + (c8 >> 3) * TC_BOX + (((c8 & 7) ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
+            }
+            if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bars[VB_K_FULL + s]);
+            return true;
+        };
+        auto write_v = [&](int j) {
+            const int s = j & 1;
+            if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+            uint32_t vw[VW];
+#pragma unroll
+            for (int i = 0; i < VW / 4; ++i)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(vw[4 * i]), "=r"(vw[4 * i + 1]), "=r"(vw[4 * i + 2]), "=r"(vw[4 * i + 3]) : "r"(vst_a + 16u * i));
+            float vnorm;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
+            fetch_v(j + 1);
+            unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
+            const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
+            const float nf = fminf(vnorm, 65504.f);
+            const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+#pragma unroll
+            for (int c8 = 0; c8 < D / 8; ++c8) {
+                const uint32_t w = vw[c8];            // eight 4-bit indices = dims 8*c8 .. 8*c8+7
+                uint32_t v4[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    // byte q4 of the word = the indices of dims 2 q4 and 2 q4 + 1: one lookup for the pair
+                    uint32_t t2;
+                    if (KVC_SKIP_BITS(p) & 2) t2 = w >> (8 * q4);
+                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2) : "r"(vtab_a + (((w >> (8 * q4)) & 255u) << 5)));
+                    v4[q4] = hmul2(t2, n2);
+                }
+                *(uint4 *)(dst + (c8 >> 3) * TC_BOX + (((c8 & 7) ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
+            }
+            if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&bars[VB_V_FULL + s]);
+            return true;
+        };
+        // cp.async groups of this thread, oldest first, at the top of step j: keys of tile j + 1, values of
+        // tile j. A row writer takes its row into registers and at once refills the place with the next
+        // tile's row, so that a copy has a whole step to land.
+        if (n_tiles > 0) {
+            fetch_k(0);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            ok = write_k(0);          // commits the copy of the keys of tile 1
+            fetch_v(0);
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            asm volatile("cp.async.wait_group 1;" ::: "memory");     // keys of tile j + 1
+            if (j + 1 < n_tiles) ok = write_k(j + 1);                // commits keys of tile j + 2
+            else fetch_k(n_tiles);                                   // an empty group keeps the count
+            asm volatile("cp.async.wait_group 1;" ::: "memory");     // values of tile j
+            if (ok) ok = write_v(j);                                 // commits values of tile j + 1
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) atomicExch(p.status, 29);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// splits > 1: out[row] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), written as f16 (rotated basis).
+__global__ void __launch_bounds__(128) verify_merge_kernel(const __grid_constant__ VerifyParams p) {
+    const int unit = blockIdx.x / p.R, row = blockIdx.x % p.R, d = threadIdx.x;
+    const int hk = unit % p.Hkv, b = unit / p.Hkv, rep = p.Hq / p.Hkv;
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) {
+        const float2 ml = p.ml_part[((int64_t)unit * p.splits + s) * p.R + row];
+        if (ml.y > 0.f) m = fmaxf(m, ml.x);
+    }
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+        const int64_t slot = ((int64_t)unit * p.splits + s) * p.R + row;
+        const float2 ml = p.ml_part[slot];
+        if (!(ml.y > 0.f)) continue;
+        const float w = fast_exp2(ml.x - m);
+        o = fmaf(p.o_part[slot * VT_D + d], w, o);
+        l = fmaf(ml.y, w, l);
+    }
+    const int hq = hk * rep + row / p.L, lq = row % p.L;
+    ((__half *)p.out)[b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d] = __float2half_rn(l > 0.f ? o / l : 0.f);
+}
+
+struct QPadParams {
+    const void *q;
+    __half *out;                 // [units][128][D]
+    int64_t q_sb, q_sh, q_sl;
+    int32_t B, Hq, Hkv, L, R;
+    const float *signs, *calib;
+};
+
+// Rotated queries of every unit, padded to 128 rows: row r of unit (b, hk) is head hk*rep + r / L at
+// position r % L; out = calib * H(signs * q) / sqrt(D) in f16, rows past R zero. One warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256) verify_q_kernel(const __grid_constant__ QPadParams p) {
+    constexpr int D = VT_D, E = D / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t gr = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t units = (int64_t)p.B * p.Hkv;
+    if (gr >= units * TC_ROWS) return;
+    const int unit = (int)(gr / TC_ROWS), r = (int)(gr % TC_ROWS);
+    __half *dst = p.out + gr * D + E * lane;
+    float x[E] = {0.f, 0.f, 0.f, 0.f};
+    if (r < p.R) {
+        const int hk = unit % p.Hkv, b = unit / p.Hkv, rep = p.Hq / p.Hkv;
+        const int hq = hk * rep + r / p.L, l = r % p.L;
+        const T *src = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + E * lane;
+#pragma unroll
+        for (int j = 0; j < E; ++j) x[j] = to_f32<T>(src[j]) * p.signs[E * lane + j];
+    }
+    {
+        const float a0 = x[0] + x[1], a1 = x[0] - x[1], a2 = x[2] + x[3], a3 = x[2] - x[3];
+        x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+            const float y = __shfl_xor_sync(0xffffffffu, x[j], m);
+            x[j] = upper ? y - x[j] : x[j] + y;
+        }
+    }
+    const float fs = rsqrtf((float)D);
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        float v = x[j] * fs;
+        if (p.calib) v *= p.calib[E * lane + j];
+        dst[j] = __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
+    }
+}
+
+template <typename TQ, int KB>
+bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
+    const size_t smem = (size_t)6 * VT_TILE + ((size_t)1 << (2 * KB)) * 128 + 256 * 8 * 4 +
+                        (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 2) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
+                        4 * TC_ROWS * sizeof(float) + 1024;
+    static std::atomic<int> configured[64];
+    const int dev = current_device();
+    if (dev < 0 || dev >= 64) return false;
+    int state = configured[dev].load(std::memory_order_acquire);
+    if (state == 0) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_verify_tc_kernel<TQ, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        state = e == cudaSuccess ? 1 : -1;
+        configured[dev].store(state, std::memory_order_release);
+    }
+    if (state < 0) return false;
+    KernelTimer timer(stream);
+    KVC_CUDA(launch_pdl(attn_verify_tc_kernel<TQ, KB>, dim3(ctas), dim3(VT_THREADS), smem, stream, qmap, p));
+    timer.stop();
+    ++g_launch_count;
+    return true;
+}
+
+}  // namespace
+
+// Returns the number of kernels launched, 0 when the call is left to the other kernels.
+// KVC_VERIFY_TC=0 turns the path off.
+int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
+    static const bool off = [] {
+        const char *e = std::getenv("KVC_VERIFY_TC");
+        return e && e[0] == '0';
+    }();
+    if (off) return 0;
+    if (a.D != VT_D || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
+    if (a.k.kind != SRC_TURBO || a.v.kind != SRC_TURBO || !a.q_signs || !a.o_signs || a.q_rot || a.o_rot) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.new_k) return 0;
+    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
+    const int kb = a.k.bits, vb = a.v.bits;
+    if (vb != 4 || kb < 2 || kb > 3) return 0;   // 4-bit keys: the lane-replicated pair table (32 KB) does not fit beside the tiles
+    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    const int rep = a.Hq / a.Hkv, R = rep * a.L;
+    if (R <= 8 || R > 64) return 0;           // eight rows and fewer: the decode kernel; the row side uses TMEM lanes 0..63
+    {
+        // rows are read 16 bytes at a time up to the stored rows rounded to a tile of 128 keys
+        const int64_t padded = (a.T + TC_KEYS - 1) / TC_KEYS * TC_KEYS;
+        const int kw = a.D * kb / 32, vw = a.D * vb / 32;
+        if (a.k.st != kw || a.v.st != vw || a.k.gst != 1 || a.v.gst != 1) return 0;
+        if (a.k.sh < padded * kw || a.v.sh < padded * vw || a.k.gsh < padded || a.v.gsh < padded) return 0;
+        if (((uintptr_t)a.k.data & 15) || ((uintptr_t)a.v.data & 15) || (a.k.sh % 4) || (a.k.sb % 4) || (a.v.sh % 4) || (a.v.sb % 4))
+            return 0;
+    }
+    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
+    int *status = device_status_word(a.device);
+    if (!status) return 0;
+
+    const int64_t units = (int64_t)a.B * a.Hkv;
+    const int n_tiles = (int)((a.T + TC_KEYS - 1) / TC_KEYS);
+    const int sms = sm_count(a.device);
+    int splits = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, sms / std::max<int64_t>(units, 1)));
+    if (units > sms) splits = 1;
+    const int tiles_per_split = (n_tiles + splits - 1) / splits;
+    splits = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    const int64_t ctas = units * splits;
+    if (ctas > (int64_t)1 << 30) return 0;
+
+    const size_t q_bytes = (size_t)units * TC_ROWS * VT_D * sizeof(__half);
+    const size_t o_bytes = splits > 1 ? (size_t)ctas * R * VT_D * sizeof(float) : 0;
+    const size_t ml_bytes = splits > 1 ? (size_t)ctas * R * sizeof(float2) : 0;
+    char *scratch = (char *)scratch_get(a.device, q_bytes + o_bytes + ml_bytes + 1024, stream);
+    __half *qpad = (__half *)scratch;
+
+    QPadParams qp = {};
+    qp.q = a.q; qp.out = qpad;
+    qp.q_sb = a.q_sb; qp.q_sh = a.q_sh; qp.q_sl = a.q_sl;
+    qp.B = a.B; qp.Hq = a.Hq; qp.Hkv = a.Hkv; qp.L = a.L; qp.R = R;
+    qp.signs = a.q_signs; qp.calib = a.q_calib;
+    const unsigned qblocks = (unsigned)((units * TC_ROWS + 7) / 8);
+    if (a.q_dtype == KVC_BF16) verify_q_kernel<__nv_bfloat16><<<qblocks, 256, 0, stream>>>(qp);
+    else verify_q_kernel<__half><<<qblocks, 256, 0, stream>>>(qp);
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+    int launches = 1;
+
+    CUtensorMap qmap;
+    if (!make_map_tc(&qmap, qpad, KVC_F16, VT_D, TC_ROWS, (int)units, 1, VT_D, (int64_t)TC_ROWS * VT_D, units * TC_ROWS * VT_D))
+        fail(KVC_ERR_INTERNAL, "verify kernel: the query tensor map could not be encoded");
+
+    VerifyParams p = {};
+    p.kp = (const uint32_t *)a.k.data; p.vp = (const uint32_t *)a.v.data;
+    p.kn = a.k.norms; p.vn = a.v.norms;
+    p.kp_sb = a.k.sb; p.kp_sh = a.k.sh; p.vp_sb = a.v.sb; p.vp_sh = a.v.sh;
+    p.kn_sb = a.k.gsb; p.kn_sh = a.k.gsh; p.vn_sb = a.v.gsb; p.vn_sh = a.v.gsh;
+    for (int i = 0; i < 16; ++i) {
+        p.kcb[i] = a.k.codebook[i];
+        p.vcb[i] = a.v.codebook[i];
+    }
+    p.out = a.out;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.R = R;
+    p.T = a.T;
+    p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    p.causal_offset = a.mask.causal_offset;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.splits = splits; p.tiles_per_split = tiles_per_split;
+    p.o_part = (float *)(scratch + ((q_bytes + 255) / 256) * 256);
+    p.ml_part = (float2 *)((char *)p.o_part + ((o_bytes + 255) / 256) * 256);
+    p.status = status;
+    p.debug_skip = measure_skip_bits();
+
+    bool taken = false;
+    if (kb == 2) taken = launch_verify_typed<__half, 2>(qmap, p, (int)ctas, stream);
+    else taken = launch_verify_typed<__half, 3>(qmap, p, (int)ctas, stream);
+    if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
+    ++launches;
+    if (splits > 1) {
+        verify_merge_kernel<<<(unsigned)(units * R), VT_D, 0, stream>>>(p);
+        KVC_CUDA(cudaGetLastError());
+        ++g_launch_count;
+        ++launches;
+    }
+    // rows back from the rotated basis, in place: f16 in, the caller's dtype out
+    launch_rotate_rows_f16(a.out, a.out, KVC_F16, a.q_dtype, a.o_sb, a.o_sh, a.o_sl, a.o_sb, a.o_sh, a.o_sl, a.B, a.Hq, a.L, a.D,
+                           nullptr, a.o_signs, stream);
+    ++launches;
+    if (trace_dispatch())
+        fprintf(stderr, "[kvc] verify_tc: %lld units of %d rows, %d splits of %d tiles\n", (long long)units, R, splits, tiles_per_split);
+    return launches;
+}
+
+}  // namespace kvc

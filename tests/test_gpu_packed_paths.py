@@ -165,7 +165,9 @@ def test_turbo_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv,
     k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
     kvc.launch_count(reset=True)
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
-    assert kvc.launch_count(reset=True) == 2            # encode-append + one attention launch
+    # encode-append + one attention launch; the tensor-core verify kernel (2- / 3-bit keys, 4-bit values, 9..128
+    # rows per kv head) adds the query rotation in front, the output rotation behind and a merge when it splits
+    assert kvc.launch_count(reset=True) <= 5
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
     assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
@@ -321,4 +323,40 @@ def test_affine_verify_rounds_run_on_the_decode_kernel_eight_rows_at_a_time(kvc,
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
         assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
         assert g.trim(L - 1) == o.trim(L - 1)
+    assert kvc.lib().kvc_device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["turbo_k3v4", "turbo_k4v4", "affine4"])
+def test_decode_at_every_context_length_around_the_stage_boundaries(kvc, oracle, cuda, kind):
+    """The 15-warp decode kernels stream 240-token stages and cut the last one short at the stored rows
+    rounded up to 256: every context length around multiples of 240 and of 256 (and the first tokens of
+    an empty cache) against the oracle, in one growing cache."""
+    B, Hq, Hkv, D = 1, 8, 1, 128
+    dtype = torch.bfloat16
+    if kind == "affine4":
+        g, o = kvc.QuantizedKVCache(64, 4), oracle.QuantizedKVCache(64, 4)
+    else:
+        kw = dict(bits=4, key_bits=3 if kind == "turbo_k3v4" else 4, value_bits=4)
+        g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    scale = D ** -0.5
+    check_at = set(range(1, 6)) | {t + d for t in (240, 256, 480, 512, 720, 768, 960, 1024) for d in (-2, -1, 0, 1, 2)}
+    T = 0
+    for target in sorted(check_at):
+        fill = target - 1 - T               # rows to add before the decode step that makes the context `target`
+        if fill > 0:
+            k, v = seeded((B, Hkv, fill, D), 1000 + target, dtype), seeded((B, Hkv, fill, D), 2000 + target, dtype)
+            if kind == "affine4":
+                g.update_quantized(k.to(cuda), v.to(cuda))
+                o.update_quantized(to_oracle(k), to_oracle(v))
+            else:
+                g.encode_new_token(k.to(cuda), v.to(cuda))
+                o.encode_new_token(to_oracle(k), to_oracle(v))
+            T += fill
+        q = seeded((B, Hq, 1, D), 3000 + target, dtype)
+        k1, v1 = seeded((B, Hkv, 1, D), 4000 + target, dtype), seeded((B, Hkv, 1, D), 5000 + target, dtype)
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), scale)
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, scale)
+        T += 1
+        assert g.offset == o.offset == T == target
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"context {target}"
     assert kvc.lib().kvc_device_status() == 0

@@ -122,8 +122,9 @@ def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
     (8, 1, 8, 2049, dict(bits=4, key_bits=3, value_bits=4)),    # 64 rows, the most the kernel takes; ragged last stage
 ])
 def test_short_chunks_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle, cuda, capfd, monkeypatch, dtype, Hq, Hkv, L, P, kw):
-    """A verify chunk over a compressed cache (4-bit values) is cut into units of eight query rows,
-    each streamed through the decode kernel with its own causal limits."""
+    """A verify chunk over a compressed cache (4-bit values): with 2- or 3-bit keys the group's rows go through
+    the tcgen05 verify kernel, with 4-bit keys they are cut into units of eight query rows, each streamed
+    through the decode kernel with its own causal limits."""
     B, D = 2, 128
     monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
     g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
@@ -137,7 +138,10 @@ def test_short_chunks_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle,
         capfd.readouterr()
         out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
         torch.cuda.synchronize()
-        assert "turbo_v4" in capfd.readouterr().err
+        err = capfd.readouterr().err
+        # 2- and 3-bit keys: the tensor-core verify kernel (rows decoded once per group); 4-bit keys: units of
+        # eight rows on the decode kernel
+        assert ("verify_tc" in err) if kw.get("key_bits", 4) < 4 else ("turbo_v4" in err)
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
         assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
         assert g.trim(L - 1) == o.trim(L - 1)
