@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle
+from helpers import TOL, bits_equal, max_abs_diff, seeded, to_oracle, worst_excess
 
 pytestmark = pytest.mark.gpu
 
@@ -338,3 +338,60 @@ def test_library_rotation_generator(kvc, oracle):
         r = kvc.turbo_rotation(D, seed)
         assert np.abs(r.astype(np.float64) @ r.astype(np.float64).T - np.eye(D)).max() < 1e-6
         assert np.abs(r - oracle.rotation_matrix(D, seed)).max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,L,P,kb,mask", [
+    (1, 9, 1, 1, 50, 3, "none"),        # nine rows, one key tile, one CTA
+    (1, 8, 1, 8, 120, 3, "causal"),     # 64 rows; the chunk itself crosses the first tile boundary
+    (3, 6, 2, 3, 128 * 5, 2, "causal"), # 2-bit keys; stored rows a multiple of the tile; several splits per unit
+    (2, 16, 2, 7, 1531, 3, "causal"),   # 56 rows, ragged last tile, splits with a shorter last one
+    (16, 64, 8, 6, 700, 3, "causal"),   # the 70B layout: 128 units, one CTA each, no split
+])
+def test_tensor_core_verify_kernel_shapes(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, P, kb, mask):
+    """Edge shapes of the tcgen05 verify kernel (9 .. 64 rows per kv head, 2- / 3-bit keys, 4-bit values): row
+    counts, tile boundaries, split counts; two rounds in a row with a rejection in between."""
+    D = 128
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    kw = dict(bits=4, key_bits=kb, value_bits=4)
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.encode_new_token(k.to(cuda), v.to(cuda))
+    o.encode_new_token(to_oracle(k), to_oracle(v))
+    for rnd in range(2):
+        q = seeded((B, Hq, L, D), 3 + rnd, dtype)
+        k1, v1 = seeded((B, Hkv, L, D), 5 + rnd, dtype), seeded((B, Hkv, L, D), 7 + rnd, dtype)
+        capfd.readouterr()
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+        torch.cuda.synchronize()
+        assert "verify_tc" in capfd.readouterr().err
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
+        assert g.trim(max(L - 1, 0)) == o.trim(max(L - 1, 0))
+    assert kvc.lib().kvc_device_status() == 0
+
+
+def test_tensor_core_verify_kernel_with_calibrated_keys(kvc, oracle, cuda, capfd, monkeypatch):
+    """Correlated keys: the cache calibrates at compression; the verify kernel's rotated queries carry the scale."""
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    B, Hq, Hkv, D, P, L = 2, 8, 2, 128, 600, 6
+    dtype = torch.bfloat16
+    kw = dict(bits=4, key_bits=3, value_bits=4)
+    g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
+    q, v = seeded((B, Hq, P, D), 1, dtype), seeded((B, Hkv, P, D), 3, dtype)
+    k = _correlated_keys((B, Hkv, P, D), 2, dtype)
+    g.attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, "causal")
+    oracle.attention_with_cache_update(to_oracle(q), to_oracle(k), to_oracle(v), o, D ** -0.5, "causal")
+    q1, k1, v1 = seeded((B, Hq, 1, D), 4, dtype), _correlated_keys((B, Hkv, 1, D), 5, dtype), seeded((B, Hkv, 1, D), 6, dtype)
+    g.attention(q1.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5)
+    oracle.attention_with_cache_update(to_oracle(q1), to_oracle(k1), to_oracle(v1), o, D ** -0.5)
+    assert g.is_compressed and len(g.state) == 5
+    q2 = seeded((B, Hq, L, D), 7, dtype)
+    k2, v2 = _correlated_keys((B, Hkv, L, D), 8, dtype), seeded((B, Hkv, L, D), 9, dtype)
+    capfd.readouterr()
+    out = g.attention(q2.to(cuda), k2.to(cuda), v2.to(cuda), D ** -0.5, "causal")
+    torch.cuda.synchronize()
+    assert "verify_tc" in capfd.readouterr().err
+    ref = oracle.attention_with_cache_update(to_oracle(q2), to_oracle(k2), to_oracle(v2), o, D ** -0.5, "causal")
+    assert worst_excess(out, ref, dtype) <= 0
+    assert kvc.lib().kvc_device_status() == 0
