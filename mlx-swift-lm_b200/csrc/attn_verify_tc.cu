@@ -19,8 +19,9 @@
 //               copied one tile ahead into shared memory (cp.async by the thread itself), then looked
 //               up, multiplied by the norm and written as the f16 row of the swizzled K / V tile the
 //               tensor cores read (K_{j+1} and V_j per step)
-// Key centroids come from a lane-replicated table of index PAIRS (conflict-free whatever the
-// indices), value centroids from a table of index pairs kept in eight copies (lane l reads copy l % 8).
+// Key and value centroids come from lane-replicated tables of index PAIRS (conflict-free whatever the
+// indices). The probabilities never visit shared memory: the softmax warps store P_j into TMEM over the
+// scores they came from, and the O product reads it there as its A operand.
 // Keys past T are written as zero rows, so masked probabilities never meet a non-finite value.
 //
 // splits > 1 (few units): every CTA writes its rows un-normalised with (max, sum); a merge kernel
@@ -78,9 +79,8 @@ enum : int {
     VB_V_EMPTY = VB_V_FULL + 2,        // [2]
     VB_S_FULL = VB_V_EMPTY + 2,        // [2]
     VB_S_EMPTY = VB_S_FULL + 2,        // [2]
-    VB_P_FULL = VB_S_EMPTY + 2,        // [1]
-    VB_P_EMPTY = VB_P_FULL + 1,        // [1]
-    VB_O_FULL = VB_P_EMPTY + 1,        // [2]
+    VB_P_FULL = VB_S_EMPTY + 2,        // [2] one per S buffer: the softmax warps may finish tile j + 1 before the MMA thread looks at tile j
+    VB_O_FULL = VB_P_FULL + 2,         // [2]
     VB_O_EMPTY = VB_O_FULL + 2,        // [2]
     VB_A_FULL = VB_O_EMPTY + 2,        // [2]
     VB_A_EMPTY = VB_A_FULL + 2,        // [2]
@@ -116,12 +116,11 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q' block
     unsigned char *skv = sq + VT_TILE;                         // stage s: K tile | V tile
-    unsigned char *sp = skv + 2 * 2 * VT_TILE;                 // one P tile
-    uint32_t *ktab = (uint32_t *)(sp + VT_TILE);               // [entries][32 lanes] f16x2
-    uint32_t *vtab = ktab + KTAB_ENTRIES * 32;                 // [256 byte values][8 copies] f16x2(c[b & 15], c[b >> 4])
+    uint32_t *vtab = (uint32_t *)(skv + 2 * 2 * VT_TILE);      // [256 byte values][32 lanes] f16x2(c[b & 15], c[b >> 4])
+    uint32_t *ktab = vtab + 256 * 32;                          // [entries][32 lanes] f16x2
     // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
     // held them across the correction step pushed the row accumulator into local memory)
-    uint32_t *kstage = vtab + 256 * 8;                         // [128][KW]
+    uint32_t *kstage = ktab + KTAB_ENTRIES * 32;               // [128][KW]
     uint32_t *vstage = kstage + TC_KEYS * KW;                  // [128][VW]
     float *nstage = (float *)(vstage + TC_KEYS * VW);          // [2][128] key norms | value norms
     uint64_t *bars = (uint64_t *)(nstage + 2 * TC_KEYS);
@@ -151,9 +150,8 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_init(&bars[VB_O_EMPTY + s], 64);      // the two correction warps
             mbar_init(&bars[VB_A_FULL + s], 64);
             mbar_init(&bars[VB_A_EMPTY + s], 64);
+            mbar_init(&bars[VB_P_FULL + s], 64);
         }
-        mbar_init(&bars[VB_P_FULL], 64);
-        mbar_init(&bars[VB_P_EMPTY], 1);
         mbar_init(&bars[VB_L_FULL], 64);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -163,10 +161,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         const int e = w >> 5;
         ktab[w] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
     }
-    for (int w = tid; w < 256 * 8; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 3) & 15], p.vcb[w >> 7]);
-    // the P tile's rows 64 .. 127 are never written (no query row lives there): zeros, so that the
-    // products of those rows stay finite
-    for (int i = tid; i < VT_TILE / 16; i += VT_THREADS) ((uint4 *)sp)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int w = tid; w < 256 * 32; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 5) & 15], p.vcb[w >> 9]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -194,7 +189,6 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
             const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
             const uint64_t v_desc = umma_desc(smem_u32(skv) + VT_TILE, 16384, 1024);
-            const uint64_t p_desc = umma_desc(smem_u32(sp), 16, 1024);
             bool ok = mbar_wait(&bars[VB_Q], 0);
             auto issue_s = [&](int j) {
                 const int s = j & 1;
@@ -218,19 +212,19 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 if (!ok) break;
                 const int s = j & 1;
                 ok = mbar_wait(&bars[VB_V_FULL + s], (j >> 1) & 1);
-                if (ok) ok = mbar_wait(&bars[VB_P_FULL], j & 1);
+                if (ok) ok = mbar_wait(&bars[VB_P_FULL + s], (j >> 1) & 1);
                 if (ok && j >= 2) ok = mbar_wait(&bars[VB_O_EMPTY + s], ((j >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = v_desc + (uint64_t)(s * (2 * VT_TILE / 16));
                 const uint32_t o_addr = tmem + 256u + (uint32_t)s * 128u;
+                // P_j is read from TMEM, where the softmax warps wrote it over S_j's first 64 columns (16 keys =
+                // 8 columns per product). S_{j+2} is issued after this product and overwrites it in issue order.
+                const uint32_t p_addr = tmem + (uint32_t)s * 128u;
 #pragma unroll
-                for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
-                    const uint64_t a_off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
-                    umma_f16(o_addr, p_desc + a_off, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < TC_KEYS / 16; ++ks)
+                    umma_f16_ts(o_addr, p_addr + (uint32_t)ks * 8u, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
                 umma_commit(&bars[VB_O_FULL + s]);
-                umma_commit(&bars[VB_P_EMPTY]);
                 umma_commit(&bars[VB_V_EMPTY + s]);
             }
             if (!ok) atomicExch(p.status, 26);
@@ -239,77 +233,78 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         // ---------------- softmax: thread = row (TMEM lanes 0..63) ----------------
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        // warp-uniform: the TMEM loads below are warp-wide. A warp with any row of the group works on all
-        // its 32 rows (the rows past the group have zero queries: finite scores, results never stored).
-        constexpr bool live = true;   // both warps run all their rows: rows past the group have zero queries
+        // the TMEM loads and stores below are warp-wide: a warp works on all its 32 rows (the rows past the
+        // group have zero queries: finite scores, results never stored)
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const int l_pos = row % p.L;
         const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l_pos) : p.T - 1;
         const int64_t min_limit = p.causal ? min(p.T - 1, p.causal_offset) : p.T - 1;   // the smallest limit of a live row
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        unsigned char *p_row = sp + row * 128;
-        const int sw = row & 7;
+        // The loops over the four 32-column blocks of a tile stay rolled (and the scores are read from TMEM
+        // twice, once for the row maximum and once for the probabilities): unrolled over 128 columns the
+        // roles of this kernel together outgrow the instruction cache, and every warp waits on fetches.
         for (int j = 0; j < n_tiles; ++j) {
             ok = mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            uint32_t raw[TC_KEYS];
-            if (live) {
-                const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
-#pragma unroll
-                for (int cb = 0; cb < 4; ++cb) tmem_ld32_issue(s_addr + cb * 32, raw + cb * 32);
+            const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
+            const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
+            const bool edge = key0 + TC_KEYS - 1 > min_limit;        // the same for every thread
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int cb = 0; cb < 4; ++cb) {
+                uint32_t raw[32];
+                tmem_ld32_issue(s_addr + cb * 32, raw);
                 tmem_ld_wait();
-            }
-            tc_fence_before();
-            mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);
-            float alpha = 0.f, neg_m = 0.f, m_new = -INFINITY;
-            if (live) {
-                const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
-                if (key0 + TC_KEYS - 1 > min_limit) {
+                if (edge) {
 #pragma unroll
-                    for (int i = 0; i < TC_KEYS; ++i)
-                        if (key0 + i > limit) raw[i] = 0xff800000u;   // -inf
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + cb * 32 + i > limit) raw[i] = 0xff800000u;   // -inf
                 }
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int i = 0; i < TC_KEYS; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                m_new = fmaxf(m_run, mx * p.scale_log2);
-                alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
-                neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
+                mx = fmaxf(mx, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
             }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+            const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
             if (j >= 2) ok = mbar_wait(&bars[VB_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
             if (!ok) break;
             s_alpha[(j & 1) * TC_ROWS + row] = alpha;
             mbar_arrive(&bars[VB_A_FULL + (j & 1)]);
-            // the single P tile is free once the O product of the tile before has read it
-            if (j >= 1) ok = mbar_wait(&bars[VB_P_EMPTY], (j - 1) & 1);
-            if (!ok) break;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int cb = 0; cb < 4; ++cb) {
+                uint32_t raw[32];
+                tmem_ld32_issue(s_addr + cb * 32, raw);
+                tmem_ld_wait();
+                if (edge) {
 #pragma unroll
-            for (int kc = 0; kc < TC_KEYS / 8; ++kc) {
-                uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                if (live && !(KVC_SKIP_BITS(p) & 16)) {
-                    float e[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));
-                        sum4[i & 3] += e[i];
-                    }
-                    w.x = pack_h2(e[0], e[1]);
-                    w.y = pack_h2(e[2], e[3]);
-                    w.z = pack_h2(e[4], e[5]);
-                    w.w = pack_h2(e[6], e[7]);
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + cb * 32 + i > limit) raw[i] = 0xff800000u;
                 }
-                *(uint4 *)(p_row + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = (KVC_SKIP_BITS(p) & 16) ? 0.f : fast_exp2(fmaf(__uint_as_float(raw[2 * i]), p.scale_log2, neg_m));
+                    const float e1 = (KVC_SKIP_BITS(p) & 16) ? 0.f : fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), p.scale_log2, neg_m));
+                    sum4[(2 * i) & 3] += e0;
+                    sum4[(2 * i + 1) & 3] += e1;
+                    pk[i] = pack_h2(e0, e1);
+                }
+                // P_j goes into TMEM over the first 64 columns of S_j (this thread's lane), where the O product
+                // reads it as its A operand: the 32 scores of block cb become columns 16 cb ..., all of them
+                // already read
+                tmem_st16_issue(s_addr + cb * 16, pk);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bars[VB_P_FULL]);
-            if (live) {
-                l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-                m_run = m_new;
-            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);
+            mbar_arrive(&bars[VB_P_FULL + (j & 1)]);
+            l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            m_run = m_new;
         }
         if (ok) {
             s_lsum[row] = l_run;
@@ -385,7 +380,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         const float *knb = p.kn + b * p.kn_sb + hk * p.kn_sh;
         const float *vnb = p.vn + b * p.vn_sb + hk * p.vn_sh;
         const uint32_t ktab_a = smem_u32(ktab) + (uint32_t)lane * 4u;
-        const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)(lane & 7) * 4u;   // this lane's copy of the value pair table
+        const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)lane * 4u;
         const int sw = row & 7;
         bool ok = true;
         const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
@@ -414,34 +409,38 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
+        // The two halves of a row are a rolled loop and each writer has one call site: unrolled, the roles of
+        // this kernel together outgrow the instruction cache. Within a half the 32 lookups are issued back to
+        // back, then multiplied and stored (a lookup directly before its store leaves one load in flight per
+        // thread and the warp waits out every latency).
         auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
             const int s = j & 1;
             if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
-            uint32_t kw[KW];
-#pragma unroll
-            for (int i = 0; i < KW / 4; ++i)
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(kw[4 * i]), "=r"(kw[4 * i + 1]), "=r"(kw[4 * i + 2]), "=r"(kw[4 * i + 3]) : "r"(kst_a + 16u * i));
             float knorm;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
-            fetch_k(j + 1);   // the row is in registers: its place takes the next tile's copy while this one is decoded
             unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
             const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
             const float nf = fminf(knorm, 65504.f);
             const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+#pragma unroll 1
+            for (int h = 0; h < D / 64; ++h) {
+                uint32_t kw[KW / 2];         // 32 index pairs = dims 64 h ... 64 h + 63
 #pragma unroll
-            for (int c8 = 0; c8 < D / 8; ++c8) {
-                uint32_t v4[4];
+                for (int i = 0; i < KW / 4; ++i)
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(kw[2 * i]), "=r"(kw[2 * i + 1]) : "r"(kst_a + (uint32_t)h * (KW * 2u) + 8u * i));
+                uint32_t t2[32];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t e = pair_index<KB, KW>(kw, c8 * 4 + q4);
-                    uint32_t t2;
-                    if (KVC_SKIP_BITS(p) & 2) t2 = e;
-                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2) : "r"(ktab_a + (e << 7)));
-                    v4[q4] = hmul2(t2, n2);
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t e = pair_index<KB, KW / 2>(kw, i);
+                    if (KVC_SKIP_BITS(p) & 2) t2[i] = e;
+                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(ktab_a + (e << 7)));
                 }
-                *(uint4 *)(dst + (c8 >> 3) * TC_BOX + (((c8 & 7) ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
+                        make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
             }
+            fetch_k(j + 1);   // the row has been read: its place takes the next tile's copy
             if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&bars[VB_K_FULL + s]);
             return true;
@@ -449,49 +448,53 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         auto write_v = [&](int j) {
             const int s = j & 1;
             if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
-            uint32_t vw[VW];
-#pragma unroll
-            for (int i = 0; i < VW / 4; ++i)
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(vw[4 * i]), "=r"(vw[4 * i + 1]), "=r"(vw[4 * i + 2]), "=r"(vw[4 * i + 3]) : "r"(vst_a + 16u * i));
             float vnorm;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
-            fetch_v(j + 1);
             unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
             const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
             const float nf = fminf(vnorm, 65504.f);
             const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+#pragma unroll 1
+            for (int h = 0; h < D / 64; ++h) {
+                uint32_t vw[VW / 2];         // word i = the eight 4-bit indices of dims 64 h + 8 i ...
 #pragma unroll
-            for (int c8 = 0; c8 < D / 8; ++c8) {
-                const uint32_t w = vw[c8];            // eight 4-bit indices = dims 8*c8 .. 8*c8+7
-                uint32_t v4[4];
+                for (int i = 0; i < VW / 8; ++i)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(vw[4 * i]), "=r"(vw[4 * i + 1]), "=r"(vw[4 * i + 2]), "=r"(vw[4 * i + 3])
+                                 : "r"(vst_a + (uint32_t)h * (VW * 2u) + 16u * i));
+                uint32_t t2[32];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    // byte q4 of the word = the indices of dims 2 q4 and 2 q4 + 1: one lookup for the pair
-                    uint32_t t2;
-                    if (KVC_SKIP_BITS(p) & 2) t2 = w >> (8 * q4);
-                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2) : "r"(vtab_a + (((w >> (8 * q4)) & 255u) << 5)));
-                    v4[q4] = hmul2(t2, n2);
+                for (int i = 0; i < 32; ++i) {
+                    // byte i % 4 of word i / 4 = the indices of two neighbouring dims: one lookup for the pair
+                    const uint32_t byte = (vw[i >> 2] >> (8 * (i & 3))) & 255u;
+                    if (KVC_SKIP_BITS(p) & 2) t2[i] = byte;
+                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(vtab_a + (byte << 7)));
                 }
-                *(uint4 *)(dst + (c8 >> 3) * TC_BOX + (((c8 & 7) ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
+                        make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
             }
+            fetch_v(j + 1);
             if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&bars[VB_V_FULL + s]);
             return true;
         };
-        // cp.async groups of this thread, oldest first, at the top of step j: keys of tile j + 1, values of
-        // tile j. A row writer takes its row into registers and at once refills the place with the next
-        // tile's row, so that a copy has a whole step to land.
-        if (n_tiles > 0) {
-            fetch_k(0);
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            ok = write_k(0);          // commits the copy of the keys of tile 1
-            fetch_v(0);
-        }
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        // cp.async groups of this thread, oldest first, at the top of step j >= 0: keys of tile j + 1, values
+        // of tile j. A row writer reads its row and at once refills the place with the next tile's row, so
+        // that a copy has a whole step to land. Step -1 writes the keys of tile 0 and fetches the values of
+        // tile 0 (the empty group makes its wait the same as every other step's).
+        fetch_k(0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll 1
+        for (int j = -1; j < n_tiles && ok; ++j) {
             asm volatile("cp.async.wait_group 1;" ::: "memory");     // keys of tile j + 1
             if (j + 1 < n_tiles) ok = write_k(j + 1);                // commits keys of tile j + 2
             else fetch_k(n_tiles);                                   // an empty group keeps the count
+            if (j < 0) {
+                fetch_v(0);
+                continue;
+            }
             asm volatile("cp.async.wait_group 1;" ::: "memory");     // values of tile j
             if (ok) ok = write_v(j);                                 // commits values of tile j + 1
         }
@@ -579,7 +582,7 @@ __global__ void __launch_bounds__(256) verify_q_kernel(const __grid_constant__ Q
 
 template <typename TQ, int KB>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
-    const size_t smem = (size_t)6 * VT_TILE + ((size_t)1 << (2 * KB)) * 128 + 256 * 8 * 4 +
+    const size_t smem = (size_t)6 * VT_TILE + ((size_t)1 << (2 * KB)) * 128 +
                         (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 2) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
                         4 * TC_ROWS * sizeof(float) + 1024;
     static std::atomic<int> configured[64];
