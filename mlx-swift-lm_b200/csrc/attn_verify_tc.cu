@@ -9,16 +9,17 @@
 // live in TMEM.
 //
 // One CTA per (batch, KV head, split of the keys):
-//   warp 0      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
-//   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
+//   warp 2      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
+//   warp 3      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
 //   warps 4, 5  softmax: thread = query row = TMEM lane 0..63 (a group has at most 64 rows here, and a warp
 //               reaches the TMEM lanes 32 * (warp % 4) ...)
-//   warps 8, 9  correction: thread = query row, folds O_j into the row's register accumulator (as the
-//               correction warps of attn_chunk_tc.cu)
-//   warps 2, 3, 6, 7  row writers: thread = key row of the tile; the row's packed indices and norm are
-//               copied one tile ahead into shared memory (cp.async by the thread itself), then looked
-//               up, multiplied by the norm and written as the f16 row of the swizzled K / V tile the
-//               tensor cores read (K_{j+1} and V_j per step)
+//   warps 8, 9, 12, 13  correction: thread = (query row, half of the dims), folds O_j into the row's
+//               register accumulator (as the correction warps of attn_chunk_tc.cu)
+//   warps 0, 6, 10, 14 (keys) and 1, 7, 11, 15 (values)  row writers: thread = key row of the tile; the
+//               row's packed indices and norm are copied one tile ahead into shared memory (cp.async by
+//               the thread itself), then looked up, multiplied by the norm and written as the f16 row of
+//               the swizzled K / V tile the tensor cores read
+// 16 warps leave a thread 128 registers, which is why a correction thread holds half a row.
 // Key and value centroids come from lane-replicated tables of index PAIRS (conflict-free whatever the
 // indices). The probabilities never visit shared memory: the softmax warps store P_j into TMEM over the
 // scores they came from, and the O product reads it there as its A operand.
@@ -49,7 +50,7 @@ using namespace dev;
 using namespace tc;
 
 constexpr int VT_D = 128;
-constexpr int VT_THREADS = 320;
+constexpr int VT_THREADS = 512;            // 16 warps: at most 128 registers each
 constexpr int VT_TILE = TC_TILE;             // 32 KB: 128 rows x 128 f16
 
 struct VerifyParams {
@@ -147,9 +148,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_init(&bars[VB_S_FULL + s], 1);
             mbar_init(&bars[VB_S_EMPTY + s], 64);      // the two softmax warps
             mbar_init(&bars[VB_O_FULL + s], 1);
-            mbar_init(&bars[VB_O_EMPTY + s], 64);      // the two correction warps
+            mbar_init(&bars[VB_O_EMPTY + s], 128);     // the four correction warps
             mbar_init(&bars[VB_A_FULL + s], 64);
-            mbar_init(&bars[VB_A_EMPTY + s], 64);
+            mbar_init(&bars[VB_A_EMPTY + s], 128);
             mbar_init(&bars[VB_P_FULL + s], 64);
         }
         mbar_init(&bars[VB_L_FULL], 64);
@@ -164,7 +165,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     for (int w = tid; w < 256 * 32; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 5) & 15], p.vcb[w >> 9]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 3) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -175,13 +176,13 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     const uint32_t tmem = *tmem_slot;
     pdl_wait();
 
-    if (warp == 0) {
+    if (warp == 2) {
         if (lane == 0) {
             mbar_expect_tx(&bars[VB_Q], VT_TILE);
             tma_load_4d(sq, &qmap, &bars[VB_Q], 0, 0, unit, 0);
             tma_load_4d(sq + TC_BOX, &qmap, &bars[VB_Q], 64, 0, unit, 0);
         }
-    } else if (warp == 1) {
+    } else if (warp == 3) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);                 // f16 x f16 -> f32
@@ -313,39 +314,39 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         } else {
             atomicExch(p.status, 27);
         }
-    } else if (warp == 8 || warp == 9) {
-        // ---------------- correction: thread = query row (TMEM lanes 0..63) ----------------
-        const int quarter = warp & 3;
+    } else if ((warp & 2) == 0 && warp >= 8) {
+        // ---------------- correction: thread = (query row, half of the dims); TMEM lanes 0..63 ----------------
+        // warps 8, 9 hold dims 0..63 of rows 0..31 / 32..63, warps 12, 13 dims 64..127
+        const int quarter = warp & 3, dh = (warp >> 2) & 1;
         const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + 256u;
-        constexpr bool live = true;
-        float o_acc[D];
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)dh * 64u;
+        constexpr int DH = D / 2;
+        float o_acc[DH];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+        for (int i = 0; i < DH; ++i) o_acc[i] = 0.f;
         bool ok = true;
-        auto correct = [&](int j) {      // fold O_j into the row's accumulator
-            if (!mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1)) return false;
+#pragma unroll 1
+        for (int j = 0; j < n_tiles && ok; ++j) {      // fold O_j into the row's accumulator
+            ok = mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
             const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
             mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
-            if (!mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            ok = mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1);
+            if (!ok) break;
             tc_fence_after();
-            if (live && !(KVC_SKIP_BITS(p) & 4)) {
+            if (!(KVC_SKIP_BITS(p) & 4)) {
 #pragma unroll
-                for (int half = 0; half < D / 64; ++half) {
-                    uint32_t raw[64];
-                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64, raw);
-                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64 + 32, raw + 32);
+                for (int part = 0; part < DH / 32; ++part) {
+                    uint32_t raw[32];
+                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + part * 32, raw);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) o_acc[half * 64 + i] = fmaf(o_acc[half * 64 + i], alpha, __uint_as_float(raw[i]));
+                    for (int i = 0; i < 32; ++i) o_acc[part * 32 + i] = fmaf(o_acc[part * 32 + i], alpha, __uint_as_float(raw[i]));
                 }
             }
             tc_fence_before();
             mbar_arrive(&bars[VB_O_EMPTY + (j & 1)]);
-            return true;
-        };
-
-        for (int j = 0; j < n_tiles && ok; ++j) ok = correct(j);
+        }
         if (ok) ok = mbar_wait(&bars[VB_L_FULL], 0);
         if (!ok) {
             atomicExch(p.status, 28);
@@ -354,9 +355,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const int hq = hk * rep + row / p.L, lq = row % p.L;
             if (p.splits == 1) {
                 const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-                __half *dst = (__half *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl;
+                __half *dst = (__half *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl + dh * DH;
 #pragma unroll
-                for (int c8 = 0; c8 < D / 8; ++c8) {
+                for (int c8 = 0; c8 < DH / 8; ++c8) {
                     uint4 w;
                     w.x = pack_h2(o_acc[c8 * 8 + 0] * inv, o_acc[c8 * 8 + 1] * inv);
                     w.y = pack_h2(o_acc[c8 * 8 + 2] * inv, o_acc[c8 * 8 + 3] * inv);
@@ -366,15 +367,17 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 }
             } else {
                 const int64_t slot = ((int64_t)unit * p.splits + split) * p.R + row;
-                float4 *dst = (float4 *)(p.o_part + slot * D);
+                float4 *dst = (float4 *)(p.o_part + slot * D + dh * DH);
 #pragma unroll
-                for (int c4 = 0; c4 < D / 4; ++c4) dst[c4] = make_float4(o_acc[c4 * 4], o_acc[c4 * 4 + 1], o_acc[c4 * 4 + 2], o_acc[c4 * 4 + 3]);
-                p.ml_part[slot] = make_float2(s_mfin[row], l_sum);
+                for (int c4 = 0; c4 < DH / 4; ++c4) dst[c4] = make_float4(o_acc[c4 * 4], o_acc[c4 * 4 + 1], o_acc[c4 * 4 + 2], o_acc[c4 * 4 + 3]);
+                if (dh == 0) p.ml_part[slot] = make_float2(s_mfin[row], l_sum);
             }
         }
-    } else if (warp >= 2) {
+    } else {
         // ---------------- row writers: thread = key row of the tile ----------------
-        const int row = ((warp & 1) + (warp >= 6 ? 2 : 0)) * 32 + lane;      // warps 2, 3, 6, 7 -> rows 0..127
+        // warps 0, 6, 10, 14 write the key rows, warps 1, 7, 11, 15 the value rows (32 rows each), at the same time
+        const bool is_v = (warp & 1) != 0;
+        const int row = (warp >> 2) * 32 + lane;
         const uint32_t *kbase = p.kp + b * p.kp_sb + hk * p.kp_sh;
         const uint32_t *vbase = p.vp + b * p.vp_sb + hk * p.vp_sh;
         const float *knb = p.kn + b * p.kn_sb + hk * p.kn_sh;
@@ -385,8 +388,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         bool ok = true;
         const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
         const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
-        // every fetch is one cp.async group of this thread (an empty one past the last tile), so that the
-        // waits below can count groups
+        // every fetch is one cp.async group of this thread (an empty one past the last tile)
         auto fetch_k = [&](int j) {      // tile j of this CTA's range
             if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
                 const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
@@ -480,30 +482,29 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_arrive(&bars[VB_V_FULL + s]);
             return true;
         };
-        // cp.async groups of this thread, oldest first, at the top of step j >= 0: keys of tile j + 1, values
-        // of tile j. A row writer reads its row and at once refills the place with the next tile's row, so
-        // that a copy has a whole step to land. Step -1 writes the keys of tile 0 and fetches the values of
-        // tile 0 (the empty group makes its wait the same as every other step's).
-        fetch_k(0);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        // A row writer reads its row and at once refills the place with the next tile's row (one cp.async
+        // group), so that a copy has a whole step to land.
+        if (is_v) {
+            fetch_v(0);
 #pragma unroll 1
-        for (int j = -1; j < n_tiles && ok; ++j) {
-            asm volatile("cp.async.wait_group 1;" ::: "memory");     // keys of tile j + 1
-            if (j + 1 < n_tiles) ok = write_k(j + 1);                // commits keys of tile j + 2
-            else fetch_k(n_tiles);                                   // an empty group keeps the count
-            if (j < 0) {
-                fetch_v(0);
-                continue;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                ok = write_v(j);
             }
-            asm volatile("cp.async.wait_group 1;" ::: "memory");     // values of tile j
-            if (ok) ok = write_v(j);                                 // commits values of tile j + 1
+        } else {
+            fetch_k(0);
+#pragma unroll 1
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                ok = write_k(j);
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!ok) atomicExch(p.status, 29);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 3) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
