@@ -9,13 +9,14 @@
 // live in TMEM.
 //
 // One CTA per (batch, KV head, split of the keys):
-//   warp 2      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
-//   warp 3      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
+//   warp 0      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
+//   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
 //   warps 4, 5  softmax: thread = query row = TMEM lane 0..63 (a group has at most 64 rows here, and a warp
-//               reaches the TMEM lanes 32 * (warp % 4) ...)
+//               reaches the TMEM lanes 32 * (warp % 4) ...): scores to probabilities, row sums
 //   warps 8, 9, 12, 13  correction: thread = (query row, half of the dims), folds O_j into the row's
-//               register accumulator (as the correction warps of attn_chunk_tc.cu)
-//   warps 0, 6, 10, 14 (keys) and 1, 7, 11, 15 (values)  row writers: thread = key row of the tile; the
+//               register accumulator (as the correction warps of attn_chunk_tc.cu); warps 12, 13 also
+//               keep the running row maxima (they wait most of a step for the O product anyway)
+//   warps 2, 6, 10, 14 (keys) and 3, 7, 11, 15 (values)  row writers: thread = key row of the tile; the
 //               row's packed indices and norm are copied one tile ahead into shared memory (cp.async by
 //               the thread itself), then looked up, multiplied by the norm and written as the f16 row of
 //               the swizzled K / V tile the tensor cores read
@@ -150,10 +151,10 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_init(&bars[VB_O_FULL + s], 1);
             mbar_init(&bars[VB_O_EMPTY + s], 128);     // the four correction warps
             mbar_init(&bars[VB_A_FULL + s], 64);
-            mbar_init(&bars[VB_A_EMPTY + s], 128);
+            mbar_init(&bars[VB_A_EMPTY + s], 192);     // the softmax and the correction threads read a tile's row statistics
             mbar_init(&bars[VB_P_FULL + s], 64);
         }
-        mbar_init(&bars[VB_L_FULL], 64);
+        mbar_init(&bars[VB_L_FULL], 128);              // row sums (softmax warps) and row maxima (warps 12, 13)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -165,7 +166,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     for (int w = tid; w < 256 * 32; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 5) & 15], p.vcb[w >> 9]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    if (warp == 3) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -176,13 +177,13 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     const uint32_t tmem = *tmem_slot;
     pdl_wait();
 
-    if (warp == 2) {
+    if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(&bars[VB_Q], VT_TILE);
             tma_load_4d(sq, &qmap, &bars[VB_Q], 0, 0, unit, 0);
             tma_load_4d(sq + TC_BOX, &qmap, &bars[VB_Q], 64, 0, unit, 0);
         }
-    } else if (warp == 3) {
+    } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
             constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);                 // f16 x f16 -> f32
@@ -240,41 +241,22 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         const int l_pos = row % p.L;
         const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l_pos) : p.T - 1;
         const int64_t min_limit = p.causal ? min(p.T - 1, p.causal_offset) : p.T - 1;   // the smallest limit of a live row
-        float m_run = -INFINITY, l_run = 0.f;
+        float l_run = 0.f;
         bool ok = true;
-        // The loops over the four 32-column blocks of a tile stay rolled (and the scores are read from TMEM
-        // twice, once for the row maximum and once for the probabilities): unrolled over 128 columns the
-        // roles of this kernel together outgrow the instruction cache, and every warp waits on fetches.
+        // The row maximum of a tile comes from warps 12, 13 (which read the scores first); here the scores are
+        // read once more and turned into probabilities. The loop over the four 32-column blocks of a tile
+        // stays rolled: unrolled over 128 columns the roles of this kernel together outgrow the instruction
+        // cache, and every warp waits on fetches.
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1);
+            ok = mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1);
+            if (ok) ok = mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1);    // complete since the statistics were taken
             if (!ok) break;
+            const float alpha = s_alpha[(j & 1) * TC_ROWS + row], neg_m = s_alpha[(j & 1) * TC_ROWS + 64 + row];
+            mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
             tc_fence_after();
             const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
             const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
             const bool edge = key0 + TC_KEYS - 1 > min_limit;        // the same for every thread
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t raw[32];
-                tmem_ld32_issue(s_addr + cb * 32, raw);
-                tmem_ld_wait();
-                if (edge) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + cb * 32 + i > limit) raw[i] = 0xff800000u;   // -inf
-                }
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
-                mx = fmaxf(mx, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
-            }
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);
-            const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
-            const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
-            if (j >= 2) ok = mbar_wait(&bars[VB_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
-            if (!ok) break;
-            s_alpha[(j & 1) * TC_ROWS + row] = alpha;
-            mbar_arrive(&bars[VB_A_FULL + (j & 1)]);
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {
@@ -305,11 +287,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);
             mbar_arrive(&bars[VB_P_FULL + (j & 1)]);
             l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            m_run = m_new;
         }
         if (ok) {
             s_lsum[row] = l_run;
-            s_mfin[row] = m_run;
             mbar_arrive(&bars[VB_L_FULL]);
         } else {
             atomicExch(p.status, 27);
@@ -325,14 +305,52 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 #pragma unroll
         for (int i = 0; i < DH; ++i) o_acc[i] = 0.f;
         bool ok = true;
+        // warps 12, 13 also keep the running row maximum: they read S_j as soon as it is complete (the S product
+        // of tile j + 1 is issued before the O product of tile j, so this runs ahead of the fold below) and
+        // publish (alpha, -max) of the tile for the softmax and the correction threads
+        const int l_pos = row % p.L;
+        const int64_t limit = p.causal ? min(p.T - 1, p.causal_offset + l_pos) : p.T - 1;
+        const int64_t min_limit = p.causal ? min(p.T - 1, p.causal_offset) : p.T - 1;   // the smallest limit of a live row
+        const uint32_t s_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        float m_run = -INFINITY;
+        auto stats = [&](int j) {
+            if (!mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            tc_fence_after();
+            const uint32_t s_addr = s_lane + (uint32_t)(j & 1) * 128u;
+            const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
+            const bool edge = key0 + TC_KEYS - 1 > min_limit;        // the same for every thread
+            float mx = -INFINITY;
 #pragma unroll 1
-        for (int j = 0; j < n_tiles && ok; ++j) {      // fold O_j into the row's accumulator
-            ok = mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1);
-            if (!ok) break;
+            for (int cb = 0; cb < 4; ++cb) {
+                uint32_t raw[32];
+                tmem_ld32_issue(s_addr + cb * 32, raw);
+                tmem_ld_wait();
+                if (edge) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + cb * 32 + i > limit) raw[i] = 0xff800000u;   // -inf
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
+                mx = fmaxf(mx, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+            const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+            if (j >= 2 && !mbar_wait(&bars[VB_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
+            s_alpha[(j & 1) * TC_ROWS + row] = alpha;
+            s_alpha[(j & 1) * TC_ROWS + 64 + row] = neg_m;
+            tc_fence_before();
+            mbar_arrive(&bars[VB_A_FULL + (j & 1)]);
+            m_run = m_new;
+            return true;
+        };
+        auto fold = [&](int j) {      // fold O_j into the row's accumulator
+            if (!mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1)) return false;
             const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
             mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
-            ok = mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1);
-            if (!ok) break;
+            if (!mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
             tc_fence_after();
             if (!(KVC_SKIP_BITS(p) & 4)) {
 #pragma unroll
@@ -346,6 +364,16 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             }
             tc_fence_before();
             mbar_arrive(&bars[VB_O_EMPTY + (j & 1)]);
+            return true;
+        };
+#pragma unroll 1
+        for (int j = 0; j <= n_tiles && ok; ++j) {
+            if (dh == 1 && j < n_tiles) ok = stats(j);
+            if (ok && j >= 1) ok = fold(j - 1);
+        }
+        if (ok && dh == 1) {
+            s_mfin[row] = m_run;
+            mbar_arrive(&bars[VB_L_FULL]);
         }
         if (ok) ok = mbar_wait(&bars[VB_L_FULL], 0);
         if (!ok) {
@@ -375,7 +403,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         }
     } else {
         // ---------------- row writers: thread = key row of the tile ----------------
-        // warps 0, 6, 10, 14 write the key rows, warps 1, 7, 11, 15 the value rows (32 rows each), at the same time
+        // warps 2, 6, 10, 14 write the key rows, warps 3, 7, 11, 15 the value rows (32 rows each), at the same time
         const bool is_v = (warp & 1) != 0;
         const int row = (warp >> 2) * 32 + lane;
         const uint32_t *kbase = p.kp + b * p.kp_sb + hk * p.kp_sh;
@@ -417,9 +445,16 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         // thread and the warp waits out every latency).
         auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
             const int s = j & 1;
-            if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+            // the staged row goes to registers and its place takes the next tile's copy at once
+            uint32_t all[KW];
+#pragma unroll
+            for (int i = 0; i < KW / 4; ++i)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(kst_a + 16u * i));
             float knorm;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
+            fetch_k(j + 1);
+            if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
             unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
             const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
             const float nf = fminf(knorm, 65504.f);
@@ -428,8 +463,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             for (int h = 0; h < D / 64; ++h) {
                 uint32_t kw[KW / 2];         // 32 index pairs = dims 64 h ... 64 h + 63
 #pragma unroll
-                for (int i = 0; i < KW / 4; ++i)
-                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(kw[2 * i]), "=r"(kw[2 * i + 1]) : "r"(kst_a + (uint32_t)h * (KW * 2u) + 8u * i));
+                for (int i = 0; i < KW / 2; ++i) kw[i] = h ? all[KW / 2 + i] : all[i];
                 uint32_t t2[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -442,16 +476,21 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
                         make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
             }
-            fetch_k(j + 1);   // the row has been read: its place takes the next tile's copy
             if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&bars[VB_K_FULL + s]);
             return true;
         };
         auto write_v = [&](int j) {
             const int s = j & 1;
-            if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+            uint32_t all[VW];
+#pragma unroll
+            for (int i = 0; i < VW / 4; ++i)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(vst_a + 16u * i));
             float vnorm;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
+            fetch_v(j + 1);
+            if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
             unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
             const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
             const float nf = fminf(vnorm, 65504.f);
@@ -460,10 +499,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             for (int h = 0; h < D / 64; ++h) {
                 uint32_t vw[VW / 2];         // word i = the eight 4-bit indices of dims 64 h + 8 i ...
 #pragma unroll
-                for (int i = 0; i < VW / 8; ++i)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(vw[4 * i]), "=r"(vw[4 * i + 1]), "=r"(vw[4 * i + 2]), "=r"(vw[4 * i + 3])
-                                 : "r"(vst_a + (uint32_t)h * (VW * 2u) + 16u * i));
+                for (int i = 0; i < VW / 2; ++i) vw[i] = h ? all[VW / 2 + i] : all[i];
                 uint32_t t2[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -477,7 +513,6 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
                         make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
             }
-            fetch_v(j + 1);
             if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&bars[VB_V_FULL + s]);
             return true;
@@ -504,7 +539,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 3) {
+    if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
