@@ -1273,6 +1273,8 @@ int launch_attention_affine_varlen(const AttnArgs *args, int n, cudaStream_t str
     return 0;
 }
 
+int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream);   // attn_verify_tc.cu
+
 int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16) return 0;
     if (a.D != 64 && a.D != 128) return 0;
@@ -1286,8 +1288,12 @@ int launch_attention_affine(const AttnArgs &a, cudaStream_t stream) {
     if (!affine_source_fits(a.k, a.D, a.T) || !affine_source_fits(a.v, a.D, a.T)) return 0;
     if (a.D / a.k.group > 4 || (a.k.group * a.k.bits) / 32 < 4) return 0;
     if (((uintptr_t)a.q & 1)) return 0;
+    if (rep * a.L > 16) {      // a verify round of a wide head group: the rows decoded once, on the tensor cores
+        const int n = launch_attention_verify_tc_affine(a, stream);
+        if (n) return n;
+    }
     // Up to 8 query rows per kv head: the transposed decode kernel. 9..16 rows: the 16-row kernel.
-    // 17..64 rows (a verify round of a wide head group): the decode kernel again, the group cut into
+    // 17..64 rows where the tensor-core verify kernel does not apply: the decode kernel again, the group cut into
     // units of eight rows that stream the same tiles one after the other (all but the first out of L2).
     const bool pairs_fit = (2 * 8 * (16 / a.k.bits)) <= a.k.group;
     const int chunks = rep * a.L > 16 ? (rep * a.L + 7) / 8 : 1;

@@ -56,8 +56,12 @@ constexpr int VT_TILE = TC_TILE;             // 32 KB: 128 rows x 128 f16
 
 struct VerifyParams {
     const uint32_t *kp, *vp;               // packed indices [B, H, cap, words]
-    const float *kn, *vn;                  // norms [B, H, cap]
+    const float *kn, *vn;                  // TurboQuant: norms [B, H, cap]
     int64_t kp_sb, kp_sh, vp_sb, vp_sh, kn_sb, kn_sh, vn_sb, vn_sh;
+    const uint16_t *ks, *kz, *vs, *vz;     // affine: scales and biases [B, H, cap, D / 64] (strides kn_* / vn_*, in elements)
+    int32_t sz_bf16;                       // affine: scales and biases are bf16 (else f16)
+    int32_t out_bf16;                      // affine: the output rows are bf16 (else f16); TurboQuant rows are f16
+    int32_t permuted;                      // affine: column c of a row is dim affine_dim_of(c)
     float kcb[16], vcb[16];
     void *out;                             // f16 rows, rotated basis, [B, Hq, L, D] with these strides
     int64_t o_sb, o_sh, o_sl;
@@ -90,6 +94,27 @@ enum : int {
     VB_COUNT = VB_L_FULL + 1
 };
 
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+// One 16-bit scale or bias (bf16 or f16 bits) as an f16 pair (x, x), kept inside the f16 range.
+__device__ __forceinline__ uint32_t splat_f16(uint32_t bits16, bool is_bf16) {
+    float x = is_bf16 ? __uint_as_float(bits16 << 16) : __half2float(__ushort_as_half((unsigned short)bits16));
+    x = fminf(fmaxf(x, -65504.f), 65504.f);
+    return pack_h2(x, x);
+}
+// The affine codec writes the dims of every group of eight in the order 0 4 1 5 2 6 3 7 (the nibbles i and
+// i + 4 of a word come out of one mask as an f16 pair): the queries are laid out the same way, so the
+// scores do not change, and the output rows are put back in order when they are stored.
+__host__ __device__ constexpr int affine_dim_of(int pos) { return (pos & ~7) | (((pos & 7) >> 1) + 4 * (pos & 1)); }
+
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -107,25 +132,28 @@ __device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int p) {
     return x & ((1u << B2) - 1u);
 }
 
-template <typename TQ, int KB>
+// AFFINE: the cache is the group-wise affine one (4-bit codes, groups of 64, QuantizedKVCache); the rows are
+// code * scale + bias instead of norm * centroid, there are no tables, the output rows are TO.
+template <typename TO, int KB, bool AFFINE>
 __global__ void __launch_bounds__(VT_THREADS, 1)
 attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ VerifyParams p) {
     constexpr int D = VT_D;
     constexpr int KW = D * KB / 32;          // key words per row
     constexpr int VW = D * 4 / 32;           // value words per row (4-bit)
-    constexpr int KTAB_ENTRIES = 1 << (2 * KB);
+    constexpr int KTAB_ENTRIES = AFFINE ? 0 : 1 << (2 * KB);
+    constexpr int VTAB_WORDS = AFFINE ? 0 : 256 * 32;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q' block
     unsigned char *skv = sq + VT_TILE;                         // stage s: K tile | V tile
     uint32_t *vtab = (uint32_t *)(skv + 2 * 2 * VT_TILE);      // [256 byte values][32 lanes] f16x2(c[b & 15], c[b >> 4])
-    uint32_t *ktab = vtab + 256 * 32;                          // [entries][32 lanes] f16x2
+    uint32_t *ktab = vtab + VTAB_WORDS;                        // [entries][32 lanes] f16x2
     // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
     // held them across the correction step pushed the row accumulator into local memory)
     uint32_t *kstage = ktab + KTAB_ENTRIES * 32;               // [128][KW]
     uint32_t *vstage = kstage + TC_KEYS * KW;                  // [128][VW]
-    float *nstage = (float *)(vstage + TC_KEYS * VW);          // [2][128] key norms | value norms
-    uint64_t *bars = (uint64_t *)(nstage + 2 * TC_KEYS);
+    float *nstage = (float *)(vstage + TC_KEYS * VW);          // [4][128] key norms | value norms (affine: scales, biases of K, of V)
+    uint64_t *bars = (uint64_t *)(nstage + 4 * TC_KEYS);
     uint32_t *tmem_slot = (uint32_t *)(bars + VB_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128]
     float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128]
@@ -159,11 +187,13 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     // tables: key entry e of lane l = f16x2(centroid[e & m], centroid[e >> KB]); value entry i = (c, c)
-    for (int w = tid; w < KTAB_ENTRIES * 32; w += VT_THREADS) {
-        const int e = w >> 5;
-        ktab[w] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
+    if constexpr (!AFFINE) {
+        for (int w = tid; w < KTAB_ENTRIES * 32; w += VT_THREADS) {
+            const int e = w >> 5;
+            ktab[w] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
+        }
+        for (int w = tid; w < VTAB_WORDS; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 5) & 15], p.vcb[w >> 9]);
     }
-    for (int w = tid; w < 256 * 32; w += VT_THREADS) vtab[w] = pack_h2(p.vcb[(w >> 5) & 15], p.vcb[w >> 9]);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -383,14 +413,17 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const int hq = hk * rep + row / p.L, lq = row % p.L;
             if (p.splits == 1) {
                 const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-                __half *dst = (__half *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl + dh * DH;
+                TO *dst = (TO *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl + dh * DH;
 #pragma unroll
                 for (int c8 = 0; c8 < DH / 8; ++c8) {
+                    // affine rows: column 8 c + pos holds dim 8 c + affine_dim_of(pos)
+                    constexpr int P0 = AFFINE ? 0 : 0, P1 = AFFINE ? 2 : 1, P2 = AFFINE ? 4 : 2, P3 = AFFINE ? 6 : 3;
+                    constexpr int P4 = AFFINE ? 1 : 4, P5 = AFFINE ? 3 : 5, P6 = AFFINE ? 5 : 6, P7 = AFFINE ? 7 : 7;
                     uint4 w;
-                    w.x = pack_h2(o_acc[c8 * 8 + 0] * inv, o_acc[c8 * 8 + 1] * inv);
-                    w.y = pack_h2(o_acc[c8 * 8 + 2] * inv, o_acc[c8 * 8 + 3] * inv);
-                    w.z = pack_h2(o_acc[c8 * 8 + 4] * inv, o_acc[c8 * 8 + 5] * inv);
-                    w.w = pack_h2(o_acc[c8 * 8 + 6] * inv, o_acc[c8 * 8 + 7] * inv);
+                    w.x = pack_pair<TO>(o_acc[c8 * 8 + P0] * inv, o_acc[c8 * 8 + P1] * inv);
+                    w.y = pack_pair<TO>(o_acc[c8 * 8 + P2] * inv, o_acc[c8 * 8 + P3] * inv);
+                    w.z = pack_pair<TO>(o_acc[c8 * 8 + P4] * inv, o_acc[c8 * 8 + P5] * inv);
+                    w.w = pack_pair<TO>(o_acc[c8 * 8 + P6] * inv, o_acc[c8 * 8 + P7] * inv);
                     *(uint4 *)(dst + c8 * 8) = w;
                 }
             } else {
@@ -406,136 +439,201 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         // warps 2, 6, 10, 14 write the key rows, warps 3, 7, 11, 15 the value rows (32 rows each), at the same time
         const bool is_v = (warp & 1) != 0;
         const int row = (warp >> 2) * 32 + lane;
-        const uint32_t *kbase = p.kp + b * p.kp_sb + hk * p.kp_sh;
-        const uint32_t *vbase = p.vp + b * p.vp_sb + hk * p.vp_sh;
-        const float *knb = p.kn + b * p.kn_sb + hk * p.kn_sh;
-        const float *vnb = p.vn + b * p.vn_sb + hk * p.vn_sh;
-        const uint32_t ktab_a = smem_u32(ktab) + (uint32_t)lane * 4u;
-        const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)lane * 4u;
-        const int sw = row & 7;
-        bool ok = true;
-        const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
-        const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
-        // every fetch is one cp.async group of this thread (an empty one past the last tile)
-        auto fetch_k = [&](int j) {      // tile j of this CTA's range
-            if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
-                const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
-                const uint32_t *src = kbase + t * KW;
+        if constexpr (AFFINE) {
+            const int sw = row & 7;
+            bool ok = true;
+            // one code path for key and value rows (the warp's kind picks the arrays, the staging places, the tile
+            // and the barriers)
+            const uint32_t *cbase = is_v ? p.vp + b * p.vp_sb + hk * p.vp_sh : p.kp + b * p.kp_sb + hk * p.kp_sh;
+            const uint16_t *sbase = is_v ? p.vs + b * p.vn_sb + hk * p.vn_sh : p.ks + b * p.kn_sb + hk * p.kn_sh;
+            const uint16_t *zbase = is_v ? p.vz + b * p.vn_sb + hk * p.vn_sh : p.kz + b * p.kn_sb + hk * p.kn_sh;
+            const uint32_t st_a = smem_u32((is_v ? vstage : kstage) + row * KW);
+            const uint32_t sst_a = smem_u32(nstage + (is_v ? 2 : 0) * TC_KEYS + row), zst_a = sst_a + TC_KEYS * 4u;
+            const int full_bar = is_v ? VB_V_FULL : VB_K_FULL, empty_bar = is_v ? VB_V_EMPTY : VB_K_EMPTY;
+            const bool sz_bf16 = p.sz_bf16 != 0;
+            auto fetch = [&](int j) {      // tile j of this CTA's range: one cp.async group of this thread
+                if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
+                    const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
+                    const uint32_t *src = cbase + t * KW;
+#pragma unroll
+                    for (int i = 0; i < KW / 4; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st_a + 16u * i), "l"(src + 4 * i) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sst_a), "l"(sbase + t * 2) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(zst_a), "l"(zbase + t * 2) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            fetch(0);
+#pragma unroll 1
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                const int s = j & 1;
+                // the staged row goes to registers and its place takes the next tile's copy at once
+                uint32_t all[KW], sc, zp;
 #pragma unroll
                 for (int i = 0; i < KW / 4; ++i)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kst_a + 16u * i), "l"(src + 4 * i) : "memory");
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(knst_a), "l"(knb + t) : "memory");
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(st_a + 16u * i));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc) : "r"(sst_a));
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zp) : "r"(zst_a));
+                fetch(j + 1);
+                if (j >= 2) ok = mbar_wait(&bars[empty_bar + s], ((j >> 1) - 1) & 1);
+                if (!ok) break;
+                unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + (is_v ? VT_TILE : 0) + row * 128;
+                const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
+#pragma unroll 1
+                for (int h = 0; h < D / 64; ++h) {      // half a row = one group of 64
+                    const uint32_t s2 = valid ? splat_f16(h ? sc >> 16 : sc & 0xffffu, sz_bf16) : 0u;
+                    const uint32_t z2 = valid ? splat_f16(h ? zp >> 16 : zp & 0xffffu, sz_bf16) : 0u;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint32_t w = h ? all[KW / 2 + c] : all[c];      // eight 4-bit codes = dims 64 h + 8 c ...
+                        uint32_t v4[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            // codes q and q + 4 as the f16 pair (1024 + code): minus 1024 is exact, then one fma
+                            const uint32_t m = ((w >> (4 * q)) & 0x000F000Fu) | 0x64006400u;
+                            v4[q] = hfma2(hsub2(m, 0x64006400u), s2, z2);
+                        }
+                        *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
+                    }
+                }
+                if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&bars[full_bar + s]);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        auto fetch_v = [&](int j) {
-            if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
-                const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
-                const uint32_t *src = vbase + t * VW;
+            if (!ok) atomicExch(p.status, 29);
+        } else {
+            const uint32_t *kbase = p.kp + b * p.kp_sb + hk * p.kp_sh;
+            const uint32_t *vbase = p.vp + b * p.vp_sb + hk * p.vp_sh;
+            const float *knb = p.kn + b * p.kn_sb + hk * p.kn_sh;
+            const float *vnb = p.vn + b * p.vn_sb + hk * p.vn_sh;
+            const uint32_t ktab_a = smem_u32(ktab) + (uint32_t)lane * 4u;
+            const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)lane * 4u;
+            const int sw = row & 7;
+            bool ok = true;
+            const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
+            const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
+            // every fetch is one cp.async group of this thread (an empty one past the last tile)
+            auto fetch_k = [&](int j) {      // tile j of this CTA's range
+                if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
+                    const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
+                    const uint32_t *src = kbase + t * KW;
+#pragma unroll
+                    for (int i = 0; i < KW / 4; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kst_a + 16u * i), "l"(src + 4 * i) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(knst_a), "l"(knb + t) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            auto fetch_v = [&](int j) {
+                if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
+                    const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
+                    const uint32_t *src = vbase + t * VW;
+#pragma unroll
+                    for (int i = 0; i < VW / 4; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vst_a + 16u * i), "l"(src + 4 * i) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(vnst_a), "l"(vnb + t) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            // The two halves of a row are a rolled loop and each writer has one call site: unrolled, the roles of
+            // this kernel together outgrow the instruction cache. Within a half the 32 lookups are issued back to
+            // back, then multiplied and stored (a lookup directly before its store leaves one load in flight per
+            // thread and the warp waits out every latency).
+            auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
+                const int s = j & 1;
+                // the staged row goes to registers and its place takes the next tile's copy at once
+                uint32_t all[KW];
+#pragma unroll
+                for (int i = 0; i < KW / 4; ++i)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(kst_a + 16u * i));
+                float knorm;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
+                fetch_k(j + 1);
+                if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+                unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
+                const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
+                const float nf = fminf(knorm, 65504.f);
+                const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+#pragma unroll 1
+                for (int h = 0; h < D / 64; ++h) {
+                    uint32_t kw[KW / 2];         // 32 index pairs = dims 64 h ... 64 h + 63
+#pragma unroll
+                    for (int i = 0; i < KW / 2; ++i) kw[i] = h ? all[KW / 2 + i] : all[i];
+                    uint32_t t2[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t e = pair_index<KB, KW / 2>(kw, i);
+                        if (KVC_SKIP_BITS(p) & 2) t2[i] = e;
+                        else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(ktab_a + (e << 7)));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
+                            make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
+                }
+                if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&bars[VB_K_FULL + s]);
+                return true;
+            };
+            auto write_v = [&](int j) {
+                const int s = j & 1;
+                uint32_t all[VW];
 #pragma unroll
                 for (int i = 0; i < VW / 4; ++i)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vst_a + 16u * i), "l"(src + 4 * i) : "memory");
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(vnst_a), "l"(vnb + t) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        // The two halves of a row are a rolled loop and each writer has one call site: unrolled, the roles of
-        // this kernel together outgrow the instruction cache. Within a half the 32 lookups are issued back to
-        // back, then multiplied and stored (a lookup directly before its store leaves one load in flight per
-        // thread and the warp waits out every latency).
-        auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
-            const int s = j & 1;
-            // the staged row goes to registers and its place takes the next tile's copy at once
-            uint32_t all[KW];
-#pragma unroll
-            for (int i = 0; i < KW / 4; ++i)
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(kst_a + 16u * i));
-            float knorm;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
-            fetch_k(j + 1);
-            if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
-            unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
-            const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
-            const float nf = fminf(knorm, 65504.f);
-            const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(vst_a + 16u * i));
+                float vnorm;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
+                fetch_v(j + 1);
+                if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
+                unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
+                const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
+                const float nf = fminf(vnorm, 65504.f);
+                const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
 #pragma unroll 1
-            for (int h = 0; h < D / 64; ++h) {
-                uint32_t kw[KW / 2];         // 32 index pairs = dims 64 h ... 64 h + 63
+                for (int h = 0; h < D / 64; ++h) {
+                    uint32_t vw[VW / 2];         // word i = the eight 4-bit indices of dims 64 h + 8 i ...
 #pragma unroll
-                for (int i = 0; i < KW / 2; ++i) kw[i] = h ? all[KW / 2 + i] : all[i];
-                uint32_t t2[32];
+                    for (int i = 0; i < VW / 2; ++i) vw[i] = h ? all[VW / 2 + i] : all[i];
+                    uint32_t t2[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const uint32_t e = pair_index<KB, KW / 2>(kw, i);
-                    if (KVC_SKIP_BITS(p) & 2) t2[i] = e;
-                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(ktab_a + (e << 7)));
+                    for (int i = 0; i < 32; ++i) {
+                        // byte i % 4 of word i / 4 = the indices of two neighbouring dims: one lookup for the pair
+                        const uint32_t byte = (vw[i >> 2] >> (8 * (i & 3))) & 255u;
+                        if (KVC_SKIP_BITS(p) & 2) t2[i] = byte;
+                        else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(vtab_a + (byte << 7)));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
+                            make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
                 }
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
-                        make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
-            }
-            if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bars[VB_K_FULL + s]);
-            return true;
-        };
-        auto write_v = [&](int j) {
-            const int s = j & 1;
-            uint32_t all[VW];
-#pragma unroll
-            for (int i = 0; i < VW / 4; ++i)
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(vst_a + 16u * i));
-            float vnorm;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
-            fetch_v(j + 1);
-            if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
-            unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
-            const bool valid = (int64_t)(j_lo + j) * TC_KEYS + row < p.T;
-            const float nf = fminf(vnorm, 65504.f);
-            const uint32_t n2 = valid ? pack_h2(nf, nf) : 0u;
+                if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&bars[VB_V_FULL + s]);
+                return true;
+            };
+            // A row writer reads its row and at once refills the place with the next tile's row (one cp.async
+            // group), so that a copy has a whole step to land.
+            if (is_v) {
+                fetch_v(0);
 #pragma unroll 1
-            for (int h = 0; h < D / 64; ++h) {
-                uint32_t vw[VW / 2];         // word i = the eight 4-bit indices of dims 64 h + 8 i ...
-#pragma unroll
-                for (int i = 0; i < VW / 2; ++i) vw[i] = h ? all[VW / 2 + i] : all[i];
-                uint32_t t2[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    // byte i % 4 of word i / 4 = the indices of two neighbouring dims: one lookup for the pair
-                    const uint32_t byte = (vw[i >> 2] >> (8 * (i & 3))) & 255u;
-                    if (KVC_SKIP_BITS(p) & 2) t2[i] = byte;
-                    else asm("ld.shared.u32 %0, [%1];" : "=r"(t2[i]) : "r"(vtab_a + (byte << 7)));
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    ok = write_v(j);
                 }
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) =
-                        make_uint4(hmul2(t2[4 * c], n2), hmul2(t2[4 * c + 1], n2), hmul2(t2[4 * c + 2], n2), hmul2(t2[4 * c + 3], n2));
-            }
-            if (!(KVC_SKIP_BITS(p) & 8)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&bars[VB_V_FULL + s]);
-            return true;
-        };
-        // A row writer reads its row and at once refills the place with the next tile's row (one cp.async
-        // group), so that a copy has a whole step to land.
-        if (is_v) {
-            fetch_v(0);
+            } else {
+                fetch_k(0);
 #pragma unroll 1
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                ok = write_v(j);
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    ok = write_k(j);
+                }
             }
-        } else {
-            fetch_k(0);
-#pragma unroll 1
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                ok = write_k(j);
-            }
+            if (!ok) atomicExch(p.status, 29);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (!ok) atomicExch(p.status, 29);
     }
     tc_fence_before();
     __syncthreads();
@@ -564,7 +662,10 @@ __global__ void __launch_bounds__(128) verify_merge_kernel(const __grid_constant
         l = fmaf(ml.y, w, l);
     }
     const int hq = hk * rep + row / p.L, lq = row % p.L;
-    ((__half *)p.out)[b * p.o_sb + hq * p.o_sh + lq * p.o_sl + d] = __float2half_rn(l > 0.f ? o / l : 0.f);
+    const int64_t at = b * p.o_sb + hq * p.o_sh + lq * p.o_sl + (p.permuted ? affine_dim_of(d) : d);
+    const float val = l > 0.f ? o / l : 0.f;
+    if (p.out_bf16) ((__nv_bfloat16 *)p.out)[at] = __float2bfloat16_rn(val);
+    else ((__half *)p.out)[at] = __float2half_rn(val);
 }
 
 struct QPadParams {
@@ -616,24 +717,52 @@ __global__ void __launch_bounds__(256) verify_q_kernel(const __grid_constant__ Q
     }
 }
 
-template <typename TQ, int KB>
+// Queries of every unit for the affine cache, padded to 128 rows, as f16 in the column order of the key
+// tiles (affine_dim_of). One thread per eight dims.
+template <typename T>
+__global__ void __launch_bounds__(256) verify_q_plain_kernel(const __grid_constant__ QPadParams p) {
+    constexpr int D = VT_D;
+    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t units = (int64_t)p.B * p.Hkv;
+    if (g >= units * TC_ROWS * (D / 8)) return;
+    const int c8 = (int)(g % (D / 8));
+    const int64_t gr = g / (D / 8);
+    const int unit = (int)(gr / TC_ROWS), r = (int)(gr % TC_ROWS);
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (r < p.R) {
+        const int hk = unit % p.Hkv, b = unit / p.Hkv, rep = p.Hq / p.Hkv;
+        const int hq = hk * rep + r / p.L, l = r % p.L;
+        const T *src = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + c8 * 8;
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = fminf(fmaxf(to_f32<T>(src[i]), -65504.f), 65504.f);
+        w.x = pack_h2(x[affine_dim_of(0)], x[affine_dim_of(1)]);
+        w.y = pack_h2(x[affine_dim_of(2)], x[affine_dim_of(3)]);
+        w.z = pack_h2(x[affine_dim_of(4)], x[affine_dim_of(5)]);
+        w.w = pack_h2(x[affine_dim_of(6)], x[affine_dim_of(7)]);
+    }
+    *(uint4 *)(p.out + gr * D + c8 * 8) = w;
+}
+
+template <typename TO, int KB, bool AFFINE>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
-    const size_t smem = (size_t)6 * VT_TILE + ((size_t)1 << (2 * KB)) * 128 +
-                        (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 2) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
+    // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
+    const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + ((size_t)1 << (2 * KB)) * 128) +
+                        (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
                         4 * TC_ROWS * sizeof(float) + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
     if (dev < 0 || dev >= 64) return false;
     int state = configured[dev].load(std::memory_order_acquire);
     if (state == 0) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_verify_tc_kernel<TQ, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_verify_tc_kernel<TO, KB, AFFINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
         state = e == cudaSuccess ? 1 : -1;
         configured[dev].store(state, std::memory_order_release);
     }
     if (state < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_verify_tc_kernel<TQ, KB>, dim3(ctas), dim3(VT_THREADS), smem, stream, qmap, p));
+    KVC_CUDA(launch_pdl(attn_verify_tc_kernel<TO, KB, AFFINE>, dim3(ctas), dim3(VT_THREADS), smem, stream, qmap, p));
     timer.stop();
     ++g_launch_count;
     return true;
@@ -726,8 +855,8 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     p.debug_skip = measure_skip_bits();
 
     bool taken = false;
-    if (kb == 2) taken = launch_verify_typed<__half, 2>(qmap, p, (int)ctas, stream);
-    else taken = launch_verify_typed<__half, 3>(qmap, p, (int)ctas, stream);
+    if (kb == 2) taken = launch_verify_typed<__half, 2, false>(qmap, p, (int)ctas, stream);
+    else taken = launch_verify_typed<__half, 3, false>(qmap, p, (int)ctas, stream);
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
     if (splits > 1) {
@@ -742,6 +871,109 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     ++launches;
     if (trace_dispatch())
         fprintf(stderr, "[kvc] verify_tc: %lld units of %d rows, %d splits of %d tiles\n", (long long)units, R, splits, tiles_per_split);
+    return launches;
+}
+
+
+// QuantizedKVCache verify rounds (quantizedScaledDotProductAttention over a handful of positions per head,
+// KVCache.swift:1045-1110 via AttentionUtils.swift:53-71): 4-bit codes in groups of 64, head dim 128,
+// 9 ... 64 rows per KV head. Returns the number of kernels launched, 0 when the call is left to the other
+// kernels. KVC_VERIFY_TC=0 turns the path off.
+int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
+    static const bool off = [] {
+        const char *e = std::getenv("KVC_VERIFY_TC");
+        return e && e[0] == '0';
+    }();
+    if (off) return 0;
+    if (a.D != VT_D || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
+    if (a.k.kind != SRC_AFFINE || a.v.kind != SRC_AFFINE || a.q_signs || a.o_signs || a.q_rot || a.o_rot || a.q_calib) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.new_k) return 0;
+    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
+    if (a.k.bits != 4 || a.v.bits != 4 || a.k.group != 64 || a.v.group != 64) return 0;
+    if (a.k.dtype != a.v.dtype || (a.k.dtype != KVC_BF16 && a.k.dtype != KVC_F16)) return 0;
+    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    const int rep = a.Hq / a.Hkv, R = rep * a.L;
+    if (R <= 16 || R > 64) return 0;          // up to 16 rows: the decode kernel streams the cache once or twice
+    constexpr int W = VT_D * 4 / 32, G = VT_D / 64;
+    {
+        // rows are read 16 bytes at a time up to the stored rows rounded to a tile of 128 keys
+        const int64_t padded = (a.T + TC_KEYS - 1) / TC_KEYS * TC_KEYS;
+        for (const KVSource *s : {&a.k, &a.v}) {
+            if (s->st != W || s->gst != G || s->sh < padded * W || s->gsh < padded * G) return 0;
+            if (((uintptr_t)s->data & 15) || (s->sh % 4) || (s->sb % 4)) return 0;
+            if (((uintptr_t)s->scales & 3) || ((uintptr_t)s->biases & 3) || (s->gsh % 2) || (s->gsb % 2)) return 0;
+        }
+    }
+    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
+    int *status = device_status_word(a.device);
+    if (!status) return 0;
+
+    const int64_t units = (int64_t)a.B * a.Hkv;
+    const int n_tiles = (int)((a.T + TC_KEYS - 1) / TC_KEYS);
+    const int sms = sm_count(a.device);
+    int splits = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, sms / std::max<int64_t>(units, 1)));
+    if (units > sms) splits = 1;
+    const int tiles_per_split = (n_tiles + splits - 1) / splits;
+    splits = (n_tiles + tiles_per_split - 1) / tiles_per_split;
+    const int64_t ctas = units * splits;
+    if (ctas > (int64_t)1 << 30) return 0;
+
+    const size_t q_bytes = (size_t)units * TC_ROWS * VT_D * sizeof(__half);
+    const size_t o_bytes = splits > 1 ? (size_t)ctas * R * VT_D * sizeof(float) : 0;
+    const size_t ml_bytes = splits > 1 ? (size_t)ctas * R * sizeof(float2) : 0;
+    char *scratch = (char *)scratch_get(a.device, q_bytes + o_bytes + ml_bytes + 1024, stream);
+    __half *qpad = (__half *)scratch;
+
+    QPadParams qp = {};
+    qp.q = a.q; qp.out = qpad;
+    qp.q_sb = a.q_sb; qp.q_sh = a.q_sh; qp.q_sl = a.q_sl;
+    qp.B = a.B; qp.Hq = a.Hq; qp.Hkv = a.Hkv; qp.L = a.L; qp.R = R;
+    const unsigned qblocks = (unsigned)((units * TC_ROWS * (VT_D / 8) + 255) / 256);
+    if (a.q_dtype == KVC_BF16) verify_q_plain_kernel<__nv_bfloat16><<<qblocks, 256, 0, stream>>>(qp);
+    else verify_q_plain_kernel<__half><<<qblocks, 256, 0, stream>>>(qp);
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+    int launches = 1;
+
+    CUtensorMap qmap;
+    if (!make_map_tc(&qmap, qpad, KVC_F16, VT_D, TC_ROWS, (int)units, 1, VT_D, (int64_t)TC_ROWS * VT_D, units * TC_ROWS * VT_D))
+        fail(KVC_ERR_INTERNAL, "verify kernel: the query tensor map could not be encoded");
+
+    VerifyParams p = {};
+    p.kp = (const uint32_t *)a.k.data; p.vp = (const uint32_t *)a.v.data;
+    p.ks = (const uint16_t *)a.k.scales; p.kz = (const uint16_t *)a.k.biases;
+    p.vs = (const uint16_t *)a.v.scales; p.vz = (const uint16_t *)a.v.biases;
+    p.kp_sb = a.k.sb; p.kp_sh = a.k.sh; p.vp_sb = a.v.sb; p.vp_sh = a.v.sh;
+    p.kn_sb = a.k.gsb; p.kn_sh = a.k.gsh; p.vn_sb = a.v.gsb; p.vn_sh = a.v.gsh;
+    p.sz_bf16 = a.k.dtype == KVC_BF16 ? 1 : 0;
+    p.out_bf16 = a.q_dtype == KVC_BF16 ? 1 : 0;
+    p.permuted = 1;
+    p.out = a.out;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.R = R;
+    p.T = a.T;
+    p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    p.causal_offset = a.mask.causal_offset;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.splits = splits; p.tiles_per_split = tiles_per_split;
+    p.o_part = (float *)(scratch + ((q_bytes + 255) / 256) * 256);
+    p.ml_part = (float2 *)((char *)p.o_part + ((o_bytes + 255) / 256) * 256);
+    p.status = status;
+    p.debug_skip = measure_skip_bits();
+
+    bool taken = false;
+    if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, true>(qmap, p, (int)ctas, stream);
+    else taken = launch_verify_typed<__half, 4, true>(qmap, p, (int)ctas, stream);
+    if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
+    ++launches;
+    if (splits > 1) {
+        verify_merge_kernel<<<(unsigned)(units * R), VT_D, 0, stream>>>(p);
+        KVC_CUDA(cudaGetLastError());
+        ++g_launch_count;
+        ++launches;
+    }
+    if (trace_dispatch())
+        fprintf(stderr, "[kvc] verify_tc affine: %lld units of %d rows, %d splits of %d tiles\n", (long long)units, R, splits, tiles_per_split);
     return launches;
 }
 

@@ -301,28 +301,39 @@ def test_calibrated_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, c
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,Hq,Hkv,bits,group,P,L", [
-    (2, 28, 4, 4, 64, 1000, 6),      # Qwen2-7B layout, verify round: 42 rows per kv head = six units (the last carries two)
-    (1, 32, 4, 8, 64, 517, 5),       # 8-bit codes, 40 rows
-    (2, 8, 1, 4, 128, 2049, 8),      # 64 rows, the most the decode kernel takes; group 128
+    (2, 28, 4, 4, 64, 1000, 6),      # Qwen2-7B layout, verify round: 42 rows per kv head; tensor-core kernel, split keys
+    (1, 32, 4, 8, 64, 517, 5),       # 8-bit codes, 40 rows: units of eight rows on the decode kernel
+    (2, 8, 1, 4, 128, 2049, 8),      # 64 rows; group 128: units of eight rows on the decode kernel
     (1, 17, 1, 4, 64, 300, 1),       # 17 heads on one kv head, one position, no causal limit to speak of
+    (16, 56, 8, 4, 64, 700, 6),      # 128 units: one CTA each, six tiles in a row, no split
+    (1, 8, 1, 4, 64, 120, 8),        # 64 rows; the chunk itself crosses the first tile boundary
 ])
-def test_affine_verify_rounds_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle, cuda, dtype, B, Hq, Hkv, bits, group, P, L):
-    """17 to 64 query rows per kv head over the affine cache: the group is cut into units of eight rows,
-    each streamed through the 8-row decode kernel with its own causal limits (one attention launch)."""
+def test_affine_verify_rounds(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, bits, group, P, L):
+    """17 to 64 query rows per kv head over the affine cache. 4-bit codes in groups of 64: the tcgen05 verify
+    kernel (rows decoded once per kv head). Otherwise the group is cut into units of eight rows, each streamed
+    through the 8-row decode kernel with its own causal limits (one attention launch)."""
     D = 128
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
     g, o = kvc.QuantizedKVCache(group, bits), oracle.QuantizedKVCache(group, bits)
     k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
     g.update_quantized(k.to(cuda), v.to(cuda))
     o.update_quantized(to_oracle(k), to_oracle(v))
+    mask = "causal" if L > 1 else "none"
     for rnd in range(2):
         q = seeded((B, Hq, L, D), 3 + rnd, dtype)
         k1, v1 = seeded((B, Hkv, L, D), 5 + rnd, dtype), seeded((B, Hkv, L, D), 7 + rnd, dtype)
         kvc.launch_count(reset=True)
-        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
-        assert kvc.launch_count(reset=True) == 2            # quantise-append + one attention launch
-        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
+        capfd.readouterr()
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+        torch.cuda.synchronize()
+        launches, err = kvc.launch_count(reset=True), capfd.readouterr().err
+        if bits == 4 and group == 64:
+            assert "verify_tc affine" in err
+        else:
+            assert launches == 2            # quantise-append + one attention launch
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
         assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
-        assert g.trim(L - 1) == o.trim(L - 1)
+        assert g.trim(max(L - 1, 0)) == o.trim(max(L - 1, 0))
     assert kvc.lib().kvc_device_status() == 0
 
 
