@@ -85,12 +85,13 @@ enum : int {
     VB_V_EMPTY = VB_V_FULL + 2,        // [2]
     VB_S_FULL = VB_V_EMPTY + 2,        // [2]
     VB_S_EMPTY = VB_S_FULL + 2,        // [2]
-    VB_P_FULL = VB_S_EMPTY + 2,        // [2] one per S buffer: the softmax warps may finish tile j + 1 before the MMA thread looks at tile j
-    VB_O_FULL = VB_P_FULL + 2,         // [2]
-    VB_O_EMPTY = VB_O_FULL + 2,        // [2]
-    VB_A_FULL = VB_O_EMPTY + 2,        // [2]
-    VB_A_EMPTY = VB_A_FULL + 2,        // [2]
-    VB_L_FULL = VB_A_EMPTY + 2,
+    VB_P_FULL = VB_S_EMPTY + 2,        // [2] P_j is in TMEM
+    VB_P_EMPTY = VB_P_FULL + 2,        // [2] the O product has read P_j
+    VB_O_FULL = VB_P_EMPTY + 2,        // [1] the O accumulator of one tile (single: it is folded away long before the next)
+    VB_O_EMPTY = VB_O_FULL + 1,        // [1]
+    VB_A_FULL = VB_O_EMPTY + 1,        // [4] row statistics of a tile (taken two tiles ahead of the fold)
+    VB_A_EMPTY = VB_A_FULL + 4,        // [4]
+    VB_L_FULL = VB_A_EMPTY + 4,
     VB_COUNT = VB_L_FULL + 1
 };
 
@@ -155,8 +156,8 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     float *nstage = (float *)(vstage + TC_KEYS * VW);          // [4][128] key norms | value norms (affine: scales, biases of K, of V)
     uint64_t *bars = (uint64_t *)(nstage + 4 * TC_KEYS);
     uint32_t *tmem_slot = (uint32_t *)(bars + VB_COUNT);
-    float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128]
-    float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128]
+    float *s_alpha = (float *)(tmem_slot + 4);                 // [4][128]: rows 0..63 alpha, rows 64..127 -max
+    float *s_lsum = s_alpha + 4 * TC_ROWS;                     // [128]
     float *s_mfin = s_lsum + TC_ROWS;                          // [128]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -176,12 +177,15 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             mbar_init(&bars[VB_V_EMPTY + s], 1);
             mbar_init(&bars[VB_S_FULL + s], 1);
             mbar_init(&bars[VB_S_EMPTY + s], 64);      // the two softmax warps
-            mbar_init(&bars[VB_O_FULL + s], 1);
-            mbar_init(&bars[VB_O_EMPTY + s], 128);     // the four correction warps
-            mbar_init(&bars[VB_A_FULL + s], 64);
-            mbar_init(&bars[VB_A_EMPTY + s], 192);     // the softmax and the correction threads read a tile's row statistics
             mbar_init(&bars[VB_P_FULL + s], 64);
+            mbar_init(&bars[VB_P_EMPTY + s], 1);
         }
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(&bars[VB_A_FULL + s], 64);       // warps 12, 13
+            mbar_init(&bars[VB_A_EMPTY + s], 192);     // the softmax and the correction threads read a tile's row statistics
+        }
+        mbar_init(&bars[VB_O_FULL], 1);
+        mbar_init(&bars[VB_O_EMPTY], 128);             // the four correction warps
         mbar_init(&bars[VB_L_FULL], 128);              // row sums (softmax warps) and row maxima (warps 12, 13)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -238,25 +242,29 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 umma_commit(&bars[VB_K_EMPTY + s]);
                 return true;
             };
+            // TMEM columns: S_0, S_1 at 0, 128; O at 256; P_0, P_1 at 384, 448. The S product runs two tiles ahead
+            // of the O product: S_{j+2} (which the row statistics and then the softmax of tile j + 2 wait for) is
+            // issued the moment the softmax warps have read S_j, in front of O_j.
             if (ok && n_tiles > 0) ok = issue_s(0);
+            if (ok && n_tiles > 1) ok = issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) ok = issue_s(j + 1);
+                if (j + 2 < n_tiles) ok = issue_s(j + 2);
                 if (!ok) break;
                 const int s = j & 1;
                 ok = mbar_wait(&bars[VB_V_FULL + s], (j >> 1) & 1);
                 if (ok) ok = mbar_wait(&bars[VB_P_FULL + s], (j >> 1) & 1);
-                if (ok && j >= 2) ok = mbar_wait(&bars[VB_O_EMPTY + s], ((j >> 1) - 1) & 1);
+                if (ok && j >= 1) ok = mbar_wait(&bars[VB_O_EMPTY], (j - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = v_desc + (uint64_t)(s * (2 * VT_TILE / 16));
-                const uint32_t o_addr = tmem + 256u + (uint32_t)s * 128u;
-                // P_j is read from TMEM, where the softmax warps wrote it over S_j's first 64 columns (16 keys =
-                // 8 columns per product). S_{j+2} is issued after this product and overwrites it in issue order.
-                const uint32_t p_addr = tmem + (uint32_t)s * 128u;
+                const uint32_t o_addr = tmem + 256u;
+                // P_j is read from TMEM, where the softmax warps wrote it (16 keys = 8 columns per product)
+                const uint32_t p_addr = tmem + 384u + (uint32_t)s * 64u;
 #pragma unroll
                 for (int ks = 0; ks < TC_KEYS / 16; ++ks)
                     umma_f16_ts(o_addr, p_addr + (uint32_t)ks * 8u, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
-                umma_commit(&bars[VB_O_FULL + s]);
+                umma_commit(&bars[VB_O_FULL]);
+                umma_commit(&bars[VB_P_EMPTY + s]);
                 umma_commit(&bars[VB_V_EMPTY + s]);
             }
             if (!ok) atomicExch(p.status, 26);
@@ -278,11 +286,12 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         // stays rolled: unrolled over 128 columns the roles of this kernel together outgrow the instruction
         // cache, and every warp waits on fetches.
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1);
+            ok = mbar_wait(&bars[VB_A_FULL + (j & 3)], (j >> 2) & 1);
             if (ok) ok = mbar_wait(&bars[VB_S_FULL + (j & 1)], (j >> 1) & 1);    // complete since the statistics were taken
+            if (ok && j >= 2) ok = mbar_wait(&bars[VB_P_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);   // the O product of tile j - 2 has read its P
             if (!ok) break;
-            const float alpha = s_alpha[(j & 1) * TC_ROWS + row], neg_m = s_alpha[(j & 1) * TC_ROWS + 64 + row];
-            mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
+            const float alpha = s_alpha[(j & 3) * TC_ROWS + row], neg_m = s_alpha[(j & 3) * TC_ROWS + 64 + row];
+            mbar_arrive(&bars[VB_A_EMPTY + (j & 3)]);
             tc_fence_after();
             const uint32_t s_addr = lane_addr + (uint32_t)(j & 1) * 128u;
             const int64_t key0 = (int64_t)(j_lo + j) * TC_KEYS;
@@ -307,14 +316,14 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     sum4[(2 * i + 1) & 3] += e1;
                     pk[i] = pack_h2(e0, e1);
                 }
-                // P_j goes into TMEM over the first 64 columns of S_j (this thread's lane), where the O product
-                // reads it as its A operand: the 32 scores of block cb become columns 16 cb ..., all of them
-                // already read
-                tmem_st16_issue(s_addr + cb * 16, pk);
+                // P_j goes into TMEM (this thread's lane, columns of its own), where the O product reads it as its
+                // A operand: the 32 scores of block cb become 16 columns
+                tmem_st16_issue(lane_addr + 384u + (uint32_t)(j & 1) * 64u + cb * 16, pk);
             }
+            tc_fence_before();
+            mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);     // S_j has been read: the S product of tile j + 2 may overwrite it
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&bars[VB_S_EMPTY + (j & 1)]);
             mbar_arrive(&bars[VB_P_FULL + (j & 1)]);
             l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         }
@@ -368,38 +377,38 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
             const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
-            if (j >= 2 && !mbar_wait(&bars[VB_A_EMPTY + (j & 1)], ((j >> 1) - 1) & 1)) return false;
-            s_alpha[(j & 1) * TC_ROWS + row] = alpha;
-            s_alpha[(j & 1) * TC_ROWS + 64 + row] = neg_m;
+            if (j >= 4 && !mbar_wait(&bars[VB_A_EMPTY + (j & 3)], ((j >> 2) - 1) & 1)) return false;
+            s_alpha[(j & 3) * TC_ROWS + row] = alpha;
+            s_alpha[(j & 3) * TC_ROWS + 64 + row] = neg_m;
             tc_fence_before();
-            mbar_arrive(&bars[VB_A_FULL + (j & 1)]);
+            mbar_arrive(&bars[VB_A_FULL + (j & 3)]);
             m_run = m_new;
             return true;
         };
         auto fold = [&](int j) {      // fold O_j into the row's accumulator
-            if (!mbar_wait(&bars[VB_A_FULL + (j & 1)], (j >> 1) & 1)) return false;
-            const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
-            mbar_arrive(&bars[VB_A_EMPTY + (j & 1)]);
-            if (!mbar_wait(&bars[VB_O_FULL + (j & 1)], (j >> 1) & 1)) return false;
+            if (!mbar_wait(&bars[VB_A_FULL + (j & 3)], (j >> 2) & 1)) return false;
+            const float alpha = s_alpha[(j & 3) * TC_ROWS + row];
+            mbar_arrive(&bars[VB_A_EMPTY + (j & 3)]);
+            if (!mbar_wait(&bars[VB_O_FULL], j & 1)) return false;
             tc_fence_after();
             if (!(KVC_SKIP_BITS(p) & 4)) {
 #pragma unroll
                 for (int part = 0; part < DH / 32; ++part) {
                     uint32_t raw[32];
-                    tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + part * 32, raw);
+                    tmem_ld32_issue(lane_addr + part * 32, raw);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o_acc[part * 32 + i] = fmaf(o_acc[part * 32 + i], alpha, __uint_as_float(raw[i]));
                 }
             }
             tc_fence_before();
-            mbar_arrive(&bars[VB_O_EMPTY + (j & 1)]);
+            mbar_arrive(&bars[VB_O_EMPTY]);
             return true;
         };
 #pragma unroll 1
-        for (int j = 0; j <= n_tiles && ok; ++j) {
+        for (int j = 0; j < n_tiles + 2 && ok; ++j) {      // the statistics run two tiles ahead of the fold
             if (dh == 1 && j < n_tiles) ok = stats(j);
-            if (ok && j >= 1) ok = fold(j - 1);
+            if (ok && j >= 2) ok = fold(j - 2);
         }
         if (ok && dh == 1) {
             s_mfin[row] = m_run;
@@ -749,7 +758,7 @@ bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int cta
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
     const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + ((size_t)1 << (2 * KB)) * 128) +
                         (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
-                        4 * TC_ROWS * sizeof(float) + 1024;
+                        6 * TC_ROWS * sizeof(float) + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
     if (dev < 0 || dev >= 64) return false;
