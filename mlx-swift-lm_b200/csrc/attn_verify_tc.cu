@@ -116,6 +116,8 @@ __device__ __forceinline__ uint32_t splat_f16(uint32_t bits16, bool is_bf16) {
 // scores do not change, and the output rows are put back in order when they are stored.
 __host__ __device__ constexpr int affine_dim_of(int pos) { return (pos & ~7) | (((pos & 7) >> 1) + 4 * (pos & 1)); }
 
+__host__ __device__ constexpr int stage_stride(int words) { return (words / 4) % 2 ? words : words + 4; }
+
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -143,6 +145,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     constexpr int VW = D * 4 / 32;           // value words per row (4-bit)
     constexpr int KTAB_ENTRIES = AFFINE ? 0 : 1 << (2 * KB);
     constexpr int VTAB_WORDS = AFFINE ? 0 : 256 * 32;
+    // a staged row starts an odd multiple of 16 bytes after the one before: the eight threads of a quarter
+    // warp then read (and cp.async writes) their 16-byte pieces from eight different bank groups
+    constexpr int KWS = stage_stride(KW), VWS = stage_stride(VW);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q' block
@@ -151,9 +156,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     uint32_t *ktab = vtab + VTAB_WORDS;                        // [entries][32 lanes] f16x2
     // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
     // held them across the correction step pushed the row accumulator into local memory)
-    uint32_t *kstage = ktab + KTAB_ENTRIES * 32;               // [128][KW]
-    uint32_t *vstage = kstage + TC_KEYS * KW;                  // [128][VW]
-    float *nstage = (float *)(vstage + TC_KEYS * VW);          // [4][128] key norms | value norms (affine: scales, biases of K, of V)
+    uint32_t *kstage = ktab + KTAB_ENTRIES * 32;               // [128][KWS]
+    uint32_t *vstage = kstage + TC_KEYS * KWS;                 // [128][VWS]
+    float *nstage = (float *)(vstage + TC_KEYS * VWS);         // [4][128] key norms | value norms (affine: scales, biases of K, of V)
     uint64_t *bars = (uint64_t *)(nstage + 4 * TC_KEYS);
     uint32_t *tmem_slot = (uint32_t *)(bars + VB_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [4][128]: rows 0..63 alpha, rows 64..127 -max
@@ -456,7 +461,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint32_t *cbase = is_v ? p.vp + b * p.vp_sb + hk * p.vp_sh : p.kp + b * p.kp_sb + hk * p.kp_sh;
             const uint16_t *sbase = is_v ? p.vs + b * p.vn_sb + hk * p.vn_sh : p.ks + b * p.kn_sb + hk * p.kn_sh;
             const uint16_t *zbase = is_v ? p.vz + b * p.vn_sb + hk * p.vn_sh : p.kz + b * p.kn_sb + hk * p.kn_sh;
-            const uint32_t st_a = smem_u32((is_v ? vstage : kstage) + row * KW);
+            const uint32_t st_a = smem_u32((is_v ? vstage : kstage) + row * KWS);
             const uint32_t sst_a = smem_u32(nstage + (is_v ? 2 : 0) * TC_KEYS + row), zst_a = sst_a + TC_KEYS * 4u;
             const int full_bar = is_v ? VB_V_FULL : VB_K_FULL, empty_bar = is_v ? VB_V_EMPTY : VB_K_EMPTY;
             const bool sz_bf16 = p.sz_bf16 != 0;
@@ -520,7 +525,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)lane * 4u;
             const int sw = row & 7;
             bool ok = true;
-            const uint32_t kst_a = smem_u32(kstage + row * KW), vst_a = smem_u32(vstage + row * VW);
+            const uint32_t kst_a = smem_u32(kstage + row * KWS), vst_a = smem_u32(vstage + row * VWS);
             const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
             // every fetch is one cp.async group of this thread (an empty one past the last tile)
             auto fetch_k = [&](int j) {      // tile j of this CTA's range
@@ -757,7 +762,7 @@ template <typename TO, int KB, bool AFFINE>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
     const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + ((size_t)1 << (2 * KB)) * 128) +
-                        (size_t)TC_KEYS * ((VT_D * KB / 32) + (VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
+                        (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
                         6 * TC_ROWS * sizeof(float) + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
