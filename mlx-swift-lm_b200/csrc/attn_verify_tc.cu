@@ -31,6 +31,7 @@
 // Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
 // its TMEM.
 #include <atomic>
+#include <cstring>
 #include <cstdio>
 #include <cstdlib>
 #include <type_traits>
@@ -143,7 +144,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     constexpr int D = VT_D;
     constexpr int KW = D * KB / 32;          // key words per row
     constexpr int VW = D * 4 / 32;           // value words per row (4-bit)
-    constexpr int KTAB_ENTRIES = AFFINE ? 0 : 1 << (2 * KB);
+    // 4-bit keys share the value pair table (the launcher checks that the two codebooks are the same): a second
+    // 32 KB table does not fit beside the tiles
+    constexpr int KTAB_ENTRIES = (AFFINE || KB == 4) ? 0 : 1 << (2 * KB);
     constexpr int VTAB_WORDS = AFFINE ? 0 : 256 * 32;
     // a staged row starts an odd multiple of 16 bytes after the one before: the eight threads of a quarter
     // warp then read (and cp.async writes) their 16-byte pieces from eight different bank groups
@@ -153,10 +156,11 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     unsigned char *sq = base;                                  // Q' block
     unsigned char *skv = sq + VT_TILE;                         // stage s: K tile | V tile
     uint32_t *vtab = (uint32_t *)(skv + 2 * 2 * VT_TILE);      // [256 byte values][32 lanes] f16x2(c[b & 15], c[b >> 4])
-    uint32_t *ktab = vtab + VTAB_WORDS;                        // [entries][32 lanes] f16x2
+    uint32_t *ktab_own = vtab + VTAB_WORDS;                    // [entries][32 lanes] f16x2
+    uint32_t *ktab = KB == 4 ? vtab : ktab_own;
     // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
     // held them across the correction step pushed the row accumulator into local memory)
-    uint32_t *kstage = ktab + KTAB_ENTRIES * 32;               // [128][KWS]
+    uint32_t *kstage = ktab_own + KTAB_ENTRIES * 32;           // [128][KWS]
     uint32_t *vstage = kstage + TC_KEYS * KWS;                 // [128][VWS]
     float *nstage = (float *)(vstage + TC_KEYS * VWS);         // [4][128] key norms | value norms (affine: scales, biases of K, of V)
     uint64_t *bars = (uint64_t *)(nstage + 4 * TC_KEYS);
@@ -761,7 +765,7 @@ __global__ void __launch_bounds__(256) verify_q_plain_kernel(const __grid_consta
 template <typename TO, int KB, bool AFFINE>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
-    const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + ((size_t)1 << (2 * KB)) * 128) +
+    const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
                         (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
                         6 * TC_ROWS * sizeof(float) + 1024;
     static std::atomic<int> configured[64];
@@ -797,7 +801,8 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     if (a.mask.mode == KVC_MASK_ARRAY || a.new_k) return 0;
     if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
     const int kb = a.k.bits, vb = a.v.bits;
-    if (vb != 4 || kb < 2 || kb > 3) return 0;   // 4-bit keys: the lane-replicated pair table (32 KB) does not fit beside the tiles
+    if (vb != 4 || kb < 2 || kb > 4) return 0;
+    if (kb == 4 && std::memcmp(a.k.codebook, a.v.codebook, sizeof(a.k.codebook)) != 0) return 0;   // 4-bit keys read the value pair table
     if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     const int rep = a.Hq / a.Hkv, R = rep * a.L;
     if (R <= 8 || R > 64) return 0;           // eight rows and fewer: the decode kernel; the row side uses TMEM lanes 0..63
@@ -870,6 +875,7 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
 
     bool taken = false;
     if (kb == 2) taken = launch_verify_typed<__half, 2, false>(qmap, p, (int)ctas, stream);
+    else if (kb == 4) taken = launch_verify_typed<__half, 4, false>(qmap, p, (int)ctas, stream);
     else taken = launch_verify_typed<__half, 3, false>(qmap, p, (int)ctas, stream);
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;

@@ -116,15 +116,14 @@ def test_turbo_cache_decode_and_verify(kvc, oracle, cuda, dtype, kw):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("Hq,Hkv,L,P,kw", [
-    (16, 2, 6, 1000, dict(bits=4, key_bits=3, value_bits=4)),   # 48 rows per kv head: six units of eight
-    (8, 2, 5, 517, dict(bits=4)),                               # 20 rows: the last unit carries four
+    (16, 2, 6, 1000, dict(bits=4, key_bits=3, value_bits=4)),   # 48 rows per kv head
+    (8, 2, 5, 517, dict(bits=4)),                               # 20 rows, 4-bit keys
     (32, 2, 1, 300, dict(bits=4, key_bits=2, value_bits=4)),    # 16 heads per kv head, one position, no mask
     (8, 1, 8, 2049, dict(bits=4, key_bits=3, value_bits=4)),    # 64 rows, the most the kernel takes; ragged last stage
 ])
-def test_short_chunks_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle, cuda, capfd, monkeypatch, dtype, Hq, Hkv, L, P, kw):
-    """A verify chunk over a compressed cache (4-bit values): with 2- or 3-bit keys the group's rows go through
-    the tcgen05 verify kernel, with 4-bit keys they are cut into units of eight query rows, each streamed
-    through the decode kernel with its own causal limits."""
+def test_short_chunks_run_on_the_tensor_core_verify_kernel(kvc, oracle, cuda, capfd, monkeypatch, dtype, Hq, Hkv, L, P, kw):
+    """A verify chunk over a compressed cache (4-bit values, 9 to 64 rows per kv head): the group's rows go
+    through the tcgen05 verify kernel."""
     B, D = 2, 128
     monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
     g, o = kvc.TurboQuantKVCache(**kw), oracle.TurboQuantKVCache(**kw)
@@ -139,9 +138,8 @@ def test_short_chunks_run_on_the_decode_kernel_eight_rows_at_a_time(kvc, oracle,
         out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
         torch.cuda.synchronize()
         err = capfd.readouterr().err
-        # 2- and 3-bit keys: the tensor-core verify kernel (rows decoded once per group); 4-bit keys: units of
-        # eight rows on the decode kernel
-        assert ("verify_tc" in err) if kw.get("key_bits", 4) < 4 else ("turbo_v4" in err)
+        # the tensor-core verify kernel (rows decoded once per group)
+        assert "verify_tc" in err
         ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
         assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
         assert g.trim(L - 1) == o.trim(L - 1)
@@ -347,6 +345,7 @@ def test_library_rotation_generator(kvc, oracle):
     (3, 6, 2, 3, 128 * 5, 2, "causal"), # 2-bit keys; stored rows a multiple of the tile; several splits per unit
     (2, 16, 2, 7, 1531, 3, "causal"),   # 56 rows, ragged last tile, splits with a shorter last one
     (16, 64, 8, 6, 700, 3, "causal"),   # the 70B layout: 128 units, one CTA each, no split
+    (2, 16, 2, 5, 900, 4, "causal"),    # 4-bit keys (turbo4): the keys read the value pair table
 ])
 def test_tensor_core_verify_kernel_shapes(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, P, kb, mask):
     """Edge shapes of the tcgen05 verify kernel (9 .. 64 rows per kv head, 2- / 3-bit keys, 4-bit values): row
