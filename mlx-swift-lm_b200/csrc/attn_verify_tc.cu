@@ -8,7 +8,8 @@
 // register file); here the group's rows are the 128-row M side of tcgen05.mma and the accumulators
 // live in TMEM.
 //
-// One CTA per (batch, KV head, split of the keys):
+// The key tiles of all (batch, KV head) units, laid end to end, are cut into one equal range per SM; a CTA
+// works through its range unit by unit. In a CTA:
 //   warp 0      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
 //   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
 //   warps 4, 5  softmax: thread = query row = TMEM lane 0..63 (a group has at most 64 rows here, and a warp
@@ -26,7 +27,7 @@
 // scores they came from, and the O product reads it there as its A operand.
 // Keys past T are written as zero rows, so masked probabilities never meet a non-finite value.
 //
-// splits > 1 (few units): every CTA writes its rows un-normalised with (max, sum); a merge kernel
+// A unit cut by a CTA boundary: every piece writes its rows un-normalised with (max, sum); a merge kernel
 // combines them. The outputs are rows in the rotated basis (f16); the caller rotates them back.
 // Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
 // its TMEM.
@@ -71,9 +72,9 @@ struct VerifyParams {
     int32_t causal;
     int64_t causal_offset;
     float scale_log2;
-    int32_t splits, tiles_per_split;
-    float *o_part;                         // [unit][split][R][D]
-    float2 *ml_part;                       // [unit][split][R] (log2-domain max, sum)
+    int32_t tiles_per_cta, max_pieces;     // flat decomposition: CTA c owns the tiles [c, c + 1) * tiles_per_cta of all units laid end to end
+    float *o_part;                         // [unit][piece][R][D]: a unit cut by a CTA boundary is merged from its pieces
+    float2 *ml_part;                       // [unit][piece][R] (log2-domain max, sum)
     int *status;
     int32_t debug_skip;                    // measurement builds only (KVC_SKIP_BITS)
 };
@@ -170,14 +171,16 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     float *s_mfin = s_lsum + TC_ROWS;                          // [128]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int unit = blockIdx.x / p.splits, split = blockIdx.x % p.splits;
-    const int hk = unit % p.Hkv, b = unit / p.Hkv;
     const int rep = p.Hq / p.Hkv;
     const int n_all = (int)((p.T + TC_KEYS - 1) / TC_KEYS);
-    const int j_lo = split * p.tiles_per_split, j_hi = min(n_all, j_lo + p.tiles_per_split);
-    const int n_tiles = max(0, j_hi - j_lo);
+    // The key tiles of all units laid end to end are cut into equal ranges, one per CTA (so that every SM has
+    // the same work whatever the number of units): a CTA walks its range one segment (= its part of one unit)
+    // after the other, the pipeline drained and the barriers set up again in between.
+    const int64_t flat_end = (int64_t)p.B * p.Hkv * n_all;
+    const int64_t flat_lo = (int64_t)blockIdx.x * p.tiles_per_cta, flat_hi = min(flat_end, flat_lo + (int64_t)p.tiles_per_cta);
+    int *seg_stop = (int *)(s_mfin + TC_ROWS);
 
-    if (tid == 0) {
+    auto init_barriers = [&]() {
         mbar_init(&bars[VB_Q], 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars[VB_K_FULL + s], 128);
@@ -198,7 +201,8 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         mbar_init(&bars[VB_L_FULL], 128);              // row sums (softmax warps) and row maxima (warps 12, 13)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
+    };
+    if (tid == 0) init_barriers();
     // tables: key entry e of lane l = f16x2(centroid[e & m], centroid[e >> KB]); value entry i = (c, c)
     if constexpr (!AFFINE) {
         for (int w = tid; w < KTAB_ENTRIES * 32; w += VT_THREADS) {
@@ -219,6 +223,23 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     pdl_wait();
+
+    int seg = 0;
+    for (int64_t pos = flat_lo; pos < flat_hi; ++seg) {
+    const int unit = (int)(pos / n_all), j_lo = (int)(pos % n_all);
+    const int n_tiles = (int)min((int64_t)(n_all - j_lo), flat_hi - pos);
+    const int hk = unit % p.Hkv, b = unit / p.Hkv;
+    const bool whole = j_lo == 0 && n_tiles == n_all;                                   // this CTA has the unit to itself
+    const int piece = (int)blockIdx.x - (int)(((int64_t)unit * n_all) / p.tiles_per_cta);
+    if (seg > 0) {
+        // everything of the segment before has completed (the MMA thread waited for its last commits): fresh
+        // barriers, all phases at zero
+        if (tid == 0) {
+            for (int i = 0; i < VB_COUNT; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars[i])) : "memory");
+            init_barriers();
+        }
+        __syncthreads();
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -275,6 +296,14 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 umma_commit(&bars[VB_O_FULL]);
                 umma_commit(&bars[VB_P_EMPTY + s]);
                 umma_commit(&bars[VB_V_EMPTY + s]);
+            }
+            // the commits of the last two tiles nobody else waits for: they must have arrived before the barriers
+            // are set up again for the next segment
+            for (int back = 1; back <= 2 && ok; ++back) {
+                const int jl = n_tiles - back;
+                if (jl < 0) break;
+                const int s = jl & 1, par = (jl >> 1) & 1;
+                ok = mbar_wait(&bars[VB_K_EMPTY + s], par) && mbar_wait(&bars[VB_V_EMPTY + s], par) && mbar_wait(&bars[VB_P_EMPTY + s], par);
             }
             if (!ok) atomicExch(p.status, 26);
         }
@@ -429,7 +458,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         } else if (row < p.R) {
             const float l_sum = s_lsum[row];
             const int hq = hk * rep + row / p.L, lq = row % p.L;
-            if (p.splits == 1) {
+            if (whole) {
                 const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
                 TO *dst = (TO *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl + dh * DH;
 #pragma unroll
@@ -445,7 +474,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     *(uint4 *)(dst + c8 * 8) = w;
                 }
             } else {
-                const int64_t slot = ((int64_t)unit * p.splits + split) * p.R + row;
+                const int64_t slot = ((int64_t)unit * p.max_pieces + piece) * p.R + row;
                 float4 *dst = (float4 *)(p.o_part + slot * D + dh * DH);
 #pragma unroll
                 for (int c4 = 0; c4 < DH / 4; ++c4) dst[c4] = make_float4(o_acc[c4 * 4], o_acc[c4 * 4 + 1], o_acc[c4 * 4 + 2], o_acc[c4 * 4 + 3]);
@@ -655,24 +684,35 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+    pos += n_tiles;
+    if (pos < flat_hi) {      // a wait that ran out anywhere: stop here (the status word tells the host)
+        if (tid == 0) *seg_stop = *(volatile int *)p.status;
+        __syncthreads();
+        if (*seg_stop != 0) break;
+    }
+    }
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
 }
 
-// splits > 1: out[row] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), written as f16 (rotated basis).
+// Units cut by a CTA boundary: out[row] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) over the unit's pieces.
 __global__ void __launch_bounds__(128) verify_merge_kernel(const __grid_constant__ VerifyParams p) {
     const int unit = blockIdx.x / p.R, row = blockIdx.x % p.R, d = threadIdx.x;
     const int hk = unit % p.Hkv, b = unit / p.Hkv, rep = p.Hq / p.Hkv;
+    const int n_all = (int)((p.T + TC_KEYS - 1) / TC_KEYS);
+    const int first = (int)(((int64_t)unit * n_all) / p.tiles_per_cta), last = (int)((((int64_t)unit + 1) * n_all - 1) / p.tiles_per_cta);
+    const int pieces = last - first + 1;
+    if (pieces == 1) return;      // written by its CTA
     float m = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) {
-        const float2 ml = p.ml_part[((int64_t)unit * p.splits + s) * p.R + row];
+    for (int s = 0; s < pieces; ++s) {
+        const float2 ml = p.ml_part[((int64_t)unit * p.max_pieces + s) * p.R + row];
         if (ml.y > 0.f) m = fmaxf(m, ml.x);
     }
     float o = 0.f, l = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-        const int64_t slot = ((int64_t)unit * p.splits + s) * p.R + row;
+    for (int s = 0; s < pieces; ++s) {
+        const int64_t slot = ((int64_t)unit * p.max_pieces + s) * p.R + row;
         const float2 ml = p.ml_part[slot];
         if (!(ml.y > 0.f)) continue;
         const float w = fast_exp2(ml.x - m);
@@ -767,7 +807,7 @@ bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int cta
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
     const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
                         (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
-                        6 * TC_ROWS * sizeof(float) + 1024;
+                        6 * TC_ROWS * sizeof(float) + 16 + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
     if (dev < 0 || dev >= 64) return false;
@@ -822,16 +862,19 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     const int64_t units = (int64_t)a.B * a.Hkv;
     const int n_tiles = (int)((a.T + TC_KEYS - 1) / TC_KEYS);
     const int sms = sm_count(a.device);
-    int splits = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, sms / std::max<int64_t>(units, 1)));
-    if (units > sms) splits = 1;
-    const int tiles_per_split = (n_tiles + splits - 1) / splits;
-    splits = (n_tiles + tiles_per_split - 1) / tiles_per_split;
-    const int64_t ctas = units * splits;
-    if (ctas > (int64_t)1 << 30) return 0;
+    // the tiles of all units end to end, cut into one equal range per SM
+    const int64_t flat = units * n_tiles;
+    if (flat > (int64_t)1 << 40) return 0;
+    const int64_t tpc64 = (flat + std::min<int64_t>(sms, flat) - 1) / std::min<int64_t>(sms, flat);
+    if (tpc64 > (int64_t)1 << 30) return 0;
+    const int tiles_per_cta = (int)tpc64;
+    const int64_t ctas = (flat + tiles_per_cta - 1) / tiles_per_cta;
+    const bool merge = tiles_per_cta % n_tiles != 0;            // some unit is cut by a CTA boundary
+    const int max_pieces = (n_tiles + tiles_per_cta - 1) / tiles_per_cta + 1;
 
     const size_t q_bytes = (size_t)units * TC_ROWS * VT_D * sizeof(__half);
-    const size_t o_bytes = splits > 1 ? (size_t)ctas * R * VT_D * sizeof(float) : 0;
-    const size_t ml_bytes = splits > 1 ? (size_t)ctas * R * sizeof(float2) : 0;
+    const size_t o_bytes = merge ? (size_t)units * max_pieces * R * VT_D * sizeof(float) : 0;
+    const size_t ml_bytes = merge ? (size_t)units * max_pieces * R * sizeof(float2) : 0;
     char *scratch = (char *)scratch_get(a.device, q_bytes + o_bytes + ml_bytes + 1024, stream);
     __half *qpad = (__half *)scratch;
 
@@ -867,7 +910,7 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.splits = splits; p.tiles_per_split = tiles_per_split;
+    p.tiles_per_cta = tiles_per_cta; p.max_pieces = max_pieces;
     p.o_part = (float *)(scratch + ((q_bytes + 255) / 256) * 256);
     p.ml_part = (float2 *)((char *)p.o_part + ((o_bytes + 255) / 256) * 256);
     p.status = status;
@@ -879,7 +922,7 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     else taken = launch_verify_typed<__half, 3, false>(qmap, p, (int)ctas, stream);
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
-    if (splits > 1) {
+    if (merge) {
         verify_merge_kernel<<<(unsigned)(units * R), VT_D, 0, stream>>>(p);
         KVC_CUDA(cudaGetLastError());
         ++g_launch_count;
@@ -890,7 +933,7 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
                            nullptr, a.o_signs, stream);
     ++launches;
     if (trace_dispatch())
-        fprintf(stderr, "[kvc] verify_tc: %lld units of %d rows, %d splits of %d tiles\n", (long long)units, R, splits, tiles_per_split);
+        fprintf(stderr, "[kvc] verify_tc: %lld units of %d rows and %d tiles, %lld CTAs of %d tiles\n", (long long)units, R, n_tiles, (long long)ctas, tiles_per_cta);
     return launches;
 }
 
@@ -931,16 +974,19 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     const int64_t units = (int64_t)a.B * a.Hkv;
     const int n_tiles = (int)((a.T + TC_KEYS - 1) / TC_KEYS);
     const int sms = sm_count(a.device);
-    int splits = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, sms / std::max<int64_t>(units, 1)));
-    if (units > sms) splits = 1;
-    const int tiles_per_split = (n_tiles + splits - 1) / splits;
-    splits = (n_tiles + tiles_per_split - 1) / tiles_per_split;
-    const int64_t ctas = units * splits;
-    if (ctas > (int64_t)1 << 30) return 0;
+    // the tiles of all units end to end, cut into one equal range per SM
+    const int64_t flat = units * n_tiles;
+    if (flat > (int64_t)1 << 40) return 0;
+    const int64_t tpc64 = (flat + std::min<int64_t>(sms, flat) - 1) / std::min<int64_t>(sms, flat);
+    if (tpc64 > (int64_t)1 << 30) return 0;
+    const int tiles_per_cta = (int)tpc64;
+    const int64_t ctas = (flat + tiles_per_cta - 1) / tiles_per_cta;
+    const bool merge = tiles_per_cta % n_tiles != 0;            // some unit is cut by a CTA boundary
+    const int max_pieces = (n_tiles + tiles_per_cta - 1) / tiles_per_cta + 1;
 
     const size_t q_bytes = (size_t)units * TC_ROWS * VT_D * sizeof(__half);
-    const size_t o_bytes = splits > 1 ? (size_t)ctas * R * VT_D * sizeof(float) : 0;
-    const size_t ml_bytes = splits > 1 ? (size_t)ctas * R * sizeof(float2) : 0;
+    const size_t o_bytes = merge ? (size_t)units * max_pieces * R * VT_D * sizeof(float) : 0;
+    const size_t ml_bytes = merge ? (size_t)units * max_pieces * R * sizeof(float2) : 0;
     char *scratch = (char *)scratch_get(a.device, q_bytes + o_bytes + ml_bytes + 1024, stream);
     __half *qpad = (__half *)scratch;
 
@@ -975,7 +1021,7 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
     p.causal_offset = a.mask.causal_offset;
     p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.splits = splits; p.tiles_per_split = tiles_per_split;
+    p.tiles_per_cta = tiles_per_cta; p.max_pieces = max_pieces;
     p.o_part = (float *)(scratch + ((q_bytes + 255) / 256) * 256);
     p.ml_part = (float2 *)((char *)p.o_part + ((o_bytes + 255) / 256) * 256);
     p.status = status;
@@ -986,14 +1032,14 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     else taken = launch_verify_typed<__half, 4, true>(qmap, p, (int)ctas, stream);
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
-    if (splits > 1) {
+    if (merge) {
         verify_merge_kernel<<<(unsigned)(units * R), VT_D, 0, stream>>>(p);
         KVC_CUDA(cudaGetLastError());
         ++g_launch_count;
         ++launches;
     }
     if (trace_dispatch())
-        fprintf(stderr, "[kvc] verify_tc affine: %lld units of %d rows, %d splits of %d tiles\n", (long long)units, R, splits, tiles_per_split);
+        fprintf(stderr, "[kvc] verify_tc affine: %lld units of %d rows and %d tiles, %lld CTAs of %d tiles\n", (long long)units, R, n_tiles, (long long)ctas, tiles_per_cta);
     return launches;
 }
 
