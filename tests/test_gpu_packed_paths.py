@@ -127,7 +127,8 @@ def test_turbo_kernel_small_causal_chunk(kvc, oracle, cuda):
     (1, 2, 1, 4, 128, 0, 130),       # chunk into an empty cache
 ])
 def test_affine_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, bits, group, P, L):
-    """Multi-token chunks over the affine cache: dequantise-to-shared-memory tensor-core kernel."""
+    """Multi-token chunks over the affine cache: dequantise-to-shared-memory tensor-core kernel; the verify round
+    of the Qwen2-7B layout (4-bit, groups of 64, 42 rows per kv head) goes to the tcgen05 verify kernel."""
     D = 128
     g, o = kvc.QuantizedKVCache(group, bits, reserve_tokens=P + L), oracle.QuantizedKVCache(group, bits)
     if P:
@@ -138,7 +139,11 @@ def test_affine_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv
     k1, v1 = seeded((B, Hkv, L, D), 4, dtype), seeded((B, Hkv, L, D), 5, dtype)
     kvc.launch_count(reset=True)
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
-    assert kvc.launch_count(reset=True) == 2            # quantise-append + one attention launch
+    launches = kvc.launch_count(reset=True)
+    if bits == 4 and group == 64 and 16 < (Hq // Hkv) * L <= 64:
+        assert 3 <= launches <= 4       # quantise-append + the tcgen05 verify kernel behind its query kernel (+ merge)
+    else:
+        assert launches == 2            # quantise-append + one attention launch
     ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, "causal")
     assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
