@@ -63,7 +63,7 @@ struct VerifyParams {
     const uint16_t *ks, *kz, *vs, *vz;     // affine: scales and biases [B, H, cap, D / 64] (strides kn_* / vn_*, in elements)
     int32_t sz_bf16;                       // affine: scales and biases are bf16 (else f16)
     int32_t out_bf16;                      // affine: the output rows are bf16 (else f16); TurboQuant rows are f16
-    int32_t permuted;                      // affine: column c of a row is dim affine_dim_of(c)
+    int32_t permuted;                      // affine: the code bits (4 or 8); column c of a row is dim affine_dim_of(c, bits). 0: columns are dims
     float kcb[16], vcb[16];
     void *out;                             // f16 rows, rotated basis, [B, Hq, L, D] with these strides
     int64_t o_sb, o_sh, o_sl;
@@ -113,10 +113,17 @@ __device__ __forceinline__ uint32_t splat_f16(uint32_t bits16, bool is_bf16) {
     x = fminf(fmaxf(x, -65504.f), 65504.f);
     return pack_h2(x, x);
 }
-// The affine codec writes the dims of every group of eight in the order 0 4 1 5 2 6 3 7 (the nibbles i and
-// i + 4 of a word come out of one mask as an f16 pair): the queries are laid out the same way, so the
+// The affine codec writes the dims of every group of eight in the order 0 4 1 5 2 6 3 7 (4-bit codes: the
+// nibbles i and i + 4 of a word come out of one mask as an f16 pair) or 0 2 1 3 4 6 5 7 (8-bit codes: the
+// bytes i and i + 2 of a word come out of one byte permute): the queries are laid out the same way, so the
 // scores do not change, and the output rows are put back in order when they are stored.
-__host__ __device__ constexpr int affine_dim_of(int pos) { return (pos & ~7) | (((pos & 7) >> 1) + 4 * (pos & 1)); }
+__host__ __device__ constexpr int affine_dim_of(int pos, int bits) {
+    return bits == 4 ? (pos & ~7) | (((pos & 7) >> 1) + 4 * (pos & 1)) : (pos & ~3) | ((pos & 1) << 1) | ((pos >> 1) & 1);
+}
+// the column that holds dim `dim`
+__host__ __device__ constexpr int affine_pos_of(int dim, int bits) {
+    return bits == 4 ? (dim & ~7) | (2 * (dim & 3) + ((dim >> 2) & 1)) : (dim & ~3) | ((dim & 1) << 1) | ((dim >> 1) & 1);
+}
 
 __host__ __device__ constexpr int stage_stride(int words) { return (words / 4) % 2 ? words : words + 4; }
 
@@ -137,14 +144,14 @@ __device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int p) {
     return x & ((1u << B2) - 1u);
 }
 
-// AFFINE: the cache is the group-wise affine one (4-bit codes, groups of 64, QuantizedKVCache); the rows are
+// AFFINE: the cache is the group-wise affine one (KB = 4- or 8-bit codes, groups of 64, QuantizedKVCache); the rows are
 // code * scale + bias instead of norm * centroid, there are no tables, the output rows are TO.
 template <typename TO, int KB, bool AFFINE>
 __global__ void __launch_bounds__(VT_THREADS, 1)
 attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ VerifyParams p) {
     constexpr int D = VT_D;
     constexpr int KW = D * KB / 32;          // key words per row
-    constexpr int VW = D * 4 / 32;           // value words per row (4-bit)
+    constexpr int VW = AFFINE ? KW : D * 4 / 32;   // value words per row (TurboQuant: 4-bit; affine: as the keys)
     // 4-bit keys share the value pair table (the launcher checks that the two codebooks are the same): a second
     // 32 KB table does not fit beside the tiles
     constexpr int KTAB_ENTRIES = (AFFINE || KB == 4) ? 0 : 1 << (2 * KB);
@@ -463,9 +470,11 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 TO *dst = (TO *)p.out + b * p.o_sb + hq * p.o_sh + lq * p.o_sl + dh * DH;
 #pragma unroll
                 for (int c8 = 0; c8 < DH / 8; ++c8) {
-                    // affine rows: column 8 c + pos holds dim 8 c + affine_dim_of(pos)
-                    constexpr int P0 = AFFINE ? 0 : 0, P1 = AFFINE ? 2 : 1, P2 = AFFINE ? 4 : 2, P3 = AFFINE ? 6 : 3;
-                    constexpr int P4 = AFFINE ? 1 : 4, P5 = AFFINE ? 3 : 5, P6 = AFFINE ? 5 : 6, P7 = AFFINE ? 7 : 7;
+                    // affine rows: dim 8 c + i sits in column 8 c + affine_pos_of(i)
+                    constexpr int P0 = AFFINE ? affine_pos_of(0, KB) : 0, P1 = AFFINE ? affine_pos_of(1, KB) : 1;
+                    constexpr int P2 = AFFINE ? affine_pos_of(2, KB) : 2, P3 = AFFINE ? affine_pos_of(3, KB) : 3;
+                    constexpr int P4 = AFFINE ? affine_pos_of(4, KB) : 4, P5 = AFFINE ? affine_pos_of(5, KB) : 5;
+                    constexpr int P6 = AFFINE ? affine_pos_of(6, KB) : 6, P7 = AFFINE ? affine_pos_of(7, KB) : 7;
                     uint4 w;
                     w.x = pack_pair<TO>(o_acc[c8 * 8 + P0] * inv, o_acc[c8 * 8 + P1] * inv);
                     w.y = pack_pair<TO>(o_acc[c8 * 8 + P2] * inv, o_acc[c8 * 8 + P3] * inv);
@@ -534,13 +543,23 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     const uint32_t z2 = valid ? splat_f16(h ? zp >> 16 : zp & 0xffffu, sz_bf16) : 0u;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
-                        const uint32_t w = h ? all[KW / 2 + c] : all[c];      // eight 4-bit codes = dims 64 h + 8 c ...
                         uint32_t v4[4];
+                        if constexpr (KB == 4) {
+                            const uint32_t w = h ? all[KW / 2 + c] : all[c];      // eight 4-bit codes = dims 64 h + 8 c ...
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            // codes q and q + 4 as the f16 pair (1024 + code): minus 1024 is exact, then one fma
-                            const uint32_t m = ((w >> (4 * q)) & 0x000F000Fu) | 0x64006400u;
-                            v4[q] = hfma2(hsub2(m, 0x64006400u), s2, z2);
+                            for (int q = 0; q < 4; ++q) {
+                                // codes q and q + 4 as the f16 pair (1024 + code): minus 1024 is exact, then one fma
+                                const uint32_t m = ((w >> (4 * q)) & 0x000F000Fu) | 0x64006400u;
+                                v4[q] = hfma2(hsub2(m, 0x64006400u), s2, z2);
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                const uint32_t w = h ? all[KW / 2 + 2 * c + q] : all[2 * c + q];   // four 8-bit codes = dims 64 h + 8 c + 4 q ...
+                                // bytes 0 and 2, then 1 and 3, each under the high byte of 1024
+                                v4[2 * q] = hfma2(hsub2(__byte_perm(w, 0x64646464u, 0x4240), 0x64006400u), s2, z2);
+                                v4[2 * q + 1] = hfma2(hsub2(__byte_perm(w, 0x64646464u, 0x4341), 0x64006400u), s2, z2);
+                            }
                         }
                         *(uint4 *)(dst + h * TC_BOX + ((c ^ sw) << 4)) = make_uint4(v4[0], v4[1], v4[2], v4[3]);
                     }
@@ -720,7 +739,7 @@ __global__ void __launch_bounds__(128) verify_merge_kernel(const __grid_constant
         l = fmaf(ml.y, w, l);
     }
     const int hq = hk * rep + row / p.L, lq = row % p.L;
-    const int64_t at = b * p.o_sb + hq * p.o_sh + lq * p.o_sl + (p.permuted ? affine_dim_of(d) : d);
+    const int64_t at = b * p.o_sb + hq * p.o_sh + lq * p.o_sl + (p.permuted ? affine_dim_of(d, p.permuted) : d);
     const float val = l > 0.f ? o / l : 0.f;
     if (p.out_bf16) ((__nv_bfloat16 *)p.out)[at] = __float2bfloat16_rn(val);
     else ((__half *)p.out)[at] = __float2half_rn(val);
@@ -732,6 +751,7 @@ struct QPadParams {
     int64_t q_sb, q_sh, q_sl;
     int32_t B, Hq, Hkv, L, R;
     const float *signs, *calib;
+    int32_t perm_bits;           // verify_q_plain_kernel: the code bits of the affine cache
 };
 
 // Rotated queries of every unit, padded to 128 rows: row r of unit (b, hk) is head hk*rep + r / L at
@@ -776,7 +796,7 @@ __global__ void __launch_bounds__(256) verify_q_kernel(const __grid_constant__ Q
 }
 
 // Queries of every unit for the affine cache, padded to 128 rows, as f16 in the column order of the key
-// tiles (affine_dim_of). One thread per eight dims.
+// tiles (affine_dim_of; p.perm_bits = the code bits). One thread per eight dims.
 template <typename T>
 __global__ void __launch_bounds__(256) verify_q_plain_kernel(const __grid_constant__ QPadParams p) {
     constexpr int D = VT_D;
@@ -794,10 +814,11 @@ __global__ void __launch_bounds__(256) verify_q_plain_kernel(const __grid_consta
         float x[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = fminf(fmaxf(to_f32<T>(src[i]), -65504.f), 65504.f);
-        w.x = pack_h2(x[affine_dim_of(0)], x[affine_dim_of(1)]);
-        w.y = pack_h2(x[affine_dim_of(2)], x[affine_dim_of(3)]);
-        w.z = pack_h2(x[affine_dim_of(4)], x[affine_dim_of(5)]);
-        w.w = pack_h2(x[affine_dim_of(6)], x[affine_dim_of(7)]);
+        const int bits = p.perm_bits;
+        w.x = pack_h2(x[affine_dim_of(0, bits)], x[affine_dim_of(1, bits)]);
+        w.y = pack_h2(x[affine_dim_of(2, bits)], x[affine_dim_of(3, bits)]);
+        w.z = pack_h2(x[affine_dim_of(4, bits)], x[affine_dim_of(5, bits)]);
+        w.w = pack_h2(x[affine_dim_of(6, bits)], x[affine_dim_of(7, bits)]);
     }
     *(uint4 *)(p.out + gr * D + c8 * 8) = w;
 }
@@ -806,7 +827,7 @@ template <typename TO, int KB, bool AFFINE>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
     const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
-                        (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
+                        (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(AFFINE ? VT_D * KB / 32 : VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
                         6 * TC_ROWS * sizeof(float) + 16 + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
@@ -939,7 +960,7 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
 
 
 // QuantizedKVCache verify rounds (quantizedScaledDotProductAttention over a handful of positions per head,
-// KVCache.swift:1045-1110 via AttentionUtils.swift:53-71): 4-bit codes in groups of 64, head dim 128,
+// KVCache.swift:1045-1110 via AttentionUtils.swift:53-71): 4- or 8-bit codes in groups of 64, head dim 128,
 // 9 ... 64 rows per KV head. Returns the number of kernels launched, 0 when the call is left to the other
 // kernels. KVC_VERIFY_TC=0 turns the path off.
 int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
@@ -952,12 +973,13 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     if (a.k.kind != SRC_AFFINE || a.v.kind != SRC_AFFINE || a.q_signs || a.o_signs || a.q_rot || a.o_rot || a.q_calib) return 0;
     if (a.mask.mode == KVC_MASK_ARRAY || a.new_k) return 0;
     if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
-    if (a.k.bits != 4 || a.v.bits != 4 || a.k.group != 64 || a.v.group != 64) return 0;
+    if ((a.k.bits != 4 && a.k.bits != 8) || a.v.bits != a.k.bits || a.k.group != 64 || a.v.group != 64) return 0;
     if (a.k.dtype != a.v.dtype || (a.k.dtype != KVC_BF16 && a.k.dtype != KVC_F16)) return 0;
     if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
     const int rep = a.Hq / a.Hkv, R = rep * a.L;
     if (R <= 16 || R > 64) return 0;          // up to 16 rows: the decode kernel streams the cache once or twice
-    constexpr int W = VT_D * 4 / 32, G = VT_D / 64;
+    const int W = VT_D * a.k.bits / 32;
+    constexpr int G = VT_D / 64;
     {
         // rows are read 16 bytes at a time up to the stored rows rounded to a tile of 128 keys
         const int64_t padded = (a.T + TC_KEYS - 1) / TC_KEYS * TC_KEYS;
@@ -994,6 +1016,7 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     qp.q = a.q; qp.out = qpad;
     qp.q_sb = a.q_sb; qp.q_sh = a.q_sh; qp.q_sl = a.q_sl;
     qp.B = a.B; qp.Hq = a.Hq; qp.Hkv = a.Hkv; qp.L = a.L; qp.R = R;
+    qp.perm_bits = a.k.bits;
     const unsigned qblocks = (unsigned)((units * TC_ROWS * (VT_D / 8) + 255) / 256);
     if (a.q_dtype == KVC_BF16) verify_q_plain_kernel<__nv_bfloat16><<<qblocks, 256, 0, stream>>>(qp);
     else verify_q_plain_kernel<__half><<<qblocks, 256, 0, stream>>>(qp);
@@ -1013,7 +1036,7 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     p.kn_sb = a.k.gsb; p.kn_sh = a.k.gsh; p.vn_sb = a.v.gsb; p.vn_sh = a.v.gsh;
     p.sz_bf16 = a.k.dtype == KVC_BF16 ? 1 : 0;
     p.out_bf16 = a.q_dtype == KVC_BF16 ? 1 : 0;
-    p.permuted = 1;
+    p.permuted = a.k.bits;
     p.out = a.out;
     p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.R = R;
@@ -1028,8 +1051,13 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     p.debug_skip = measure_skip_bits();
 
     bool taken = false;
-    if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, true>(qmap, p, (int)ctas, stream);
-    else taken = launch_verify_typed<__half, 4, true>(qmap, p, (int)ctas, stream);
+    if (a.k.bits == 4) {
+        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, true>(qmap, p, (int)ctas, stream);
+        else taken = launch_verify_typed<__half, 4, true>(qmap, p, (int)ctas, stream);
+    } else {
+        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 8, true>(qmap, p, (int)ctas, stream);
+        else taken = launch_verify_typed<__half, 8, true>(qmap, p, (int)ctas, stream);
+    }
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
     if (merge) {

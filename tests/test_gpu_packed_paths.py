@@ -128,7 +128,7 @@ def test_turbo_kernel_small_causal_chunk(kvc, oracle, cuda):
 ])
 def test_affine_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, bits, group, P, L):
     """Multi-token chunks over the affine cache: dequantise-to-shared-memory tensor-core kernel; the verify round
-    of the Qwen2-7B layout (4-bit, groups of 64, 42 rows per kv head) goes to the tcgen05 verify kernel."""
+    of the Qwen2-7B layout (groups of 64, 42 rows per kv head) goes to the tcgen05 verify kernel."""
     D = 128
     g, o = kvc.QuantizedKVCache(group, bits, reserve_tokens=P + L), oracle.QuantizedKVCache(group, bits)
     if P:
@@ -140,7 +140,7 @@ def test_affine_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv
     kvc.launch_count(reset=True)
     out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, "causal")
     launches = kvc.launch_count(reset=True)
-    if bits == 4 and group == 64 and 16 < (Hq // Hkv) * L <= 64:
+    if group == 64 and 16 < (Hq // Hkv) * L <= 64:
         assert 3 <= launches <= 4       # quantise-append + the tcgen05 verify kernel behind its query kernel (+ merge)
     else:
         assert launches == 2            # quantise-append + one attention launch
@@ -307,14 +307,15 @@ def test_calibrated_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, c
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,Hq,Hkv,bits,group,P,L", [
     (2, 28, 4, 4, 64, 1000, 6),      # Qwen2-7B layout, verify round: 42 rows per kv head; tensor-core kernel, split keys
-    (1, 32, 4, 8, 64, 517, 5),       # 8-bit codes, 40 rows: units of eight rows on the decode kernel
+    (1, 32, 4, 8, 64, 517, 5),       # 8-bit codes, 40 rows: tensor-core kernel
+    (2, 16, 2, 8, 64, 1300, 6),      # 8-bit codes, 48 rows, bigger
     (2, 8, 1, 4, 128, 2049, 8),      # 64 rows; group 128: units of eight rows on the decode kernel
     (1, 17, 1, 4, 64, 300, 1),       # 17 heads on one kv head, one position, no causal limit to speak of
     (16, 56, 8, 4, 64, 700, 6),      # 128 units: one CTA each, six tiles in a row, no split
     (1, 8, 1, 4, 64, 120, 8),        # 64 rows; the chunk itself crosses the first tile boundary
 ])
 def test_affine_verify_rounds(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, bits, group, P, L):
-    """17 to 64 query rows per kv head over the affine cache. 4-bit codes in groups of 64: the tcgen05 verify
+    """17 to 64 query rows per kv head over the affine cache. 4- or 8-bit codes in groups of 64: the tcgen05 verify
     kernel (rows decoded once per kv head). Otherwise the group is cut into units of eight rows, each streamed
     through the 8-row decode kernel with its own causal limits (one attention launch)."""
     D = 128
@@ -332,7 +333,7 @@ def test_affine_verify_rounds(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, H
         out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
         torch.cuda.synchronize()
         launches, err = kvc.launch_count(reset=True), capfd.readouterr().err
-        if bits == 4 and group == 64:
+        if group == 64:
             assert "verify_tc affine" in err
         else:
             assert launches == 2            # quantise-append + one attention launch
