@@ -87,8 +87,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
     constexpr int QKV_TILE = NBOX * TC_BOX;                    // bytes of a 128-row tile of D head dims
     unsigned char *sq = base;                                  // Q block
     unsigned char *skv = sq + QKV_TILE;                        // ring: stage s = K tile | V tile
-    unsigned char *sp = skv + TC_STAGES * 2 * QKV_TILE;        // two P tiles
-    uint64_t *bars = (uint64_t *)(sp + 2 * TC_TILE);
+    uint64_t *bars = (uint64_t *)(skv + TC_STAGES * 2 * QKV_TILE);
     uint32_t *tmem_slot = (uint32_t *)(bars + BAR_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [2][128] rescale factor of tile j for each row
     float *s_lsum = s_alpha + 2 * TC_ROWS;                     // [128] final row sums
@@ -195,7 +194,6 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
             const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
             const uint64_t v_desc = umma_desc(smem_u32(skv) + QKV_TILE, 16384, 1024);
-            const uint64_t p_desc = umma_desc(smem_u32(sp), 16, 1024);
             bool ok = mbar_wait(&bars[BAR_Q], 0);
             auto issue_s = [&](int j) {
                 const int s = j % TC_STAGES;
@@ -220,18 +218,19 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                 const int s = j % TC_STAGES;
                 ok = mbar_wait(&bars[BAR_V_FULL + s], (j / TC_STAGES) & 1);
                 if (ok) ok = mbar_wait(&bars[BAR_P_FULL + (j & 1)], (j >> 1) & 1);
-                if (ok && j >= 2) ok = mbar_wait(&bars[BAR_O_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
+                if (ok && j >= 1) ok = mbar_wait(&bars[BAR_O_EMPTY], (j - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = v_desc + (uint64_t)(s * (2 * QKV_TILE / 16));
-                const uint64_t pd = p_desc + (uint64_t)((j & 1) * (TC_TILE / 16));
-                const uint32_t o_addr = tmem + 256u + (uint32_t)(j & 1) * 128u;
+                // TMEM columns: S_0, S_1 at 0, 128; O at 256 (one accumulator: it is folded away long before the
+                // next O product is due); P_0, P_1 at 384, 448, written there by the softmax warps and read as
+                // the A operand (16 keys = 8 columns per product)
+                const uint32_t o_addr = tmem + 256u;
+                const uint32_t p_addr = tmem + 384u + (uint32_t)(j & 1) * 64u;
 #pragma unroll
-                for (int ks = 0; ks < TC_KEYS / 16; ++ks) {
-                    const uint64_t a_off = (uint64_t)((ks >> 2) * (TC_BOX / 16) + (ks & 3) * 2);
-                    umma_f16(o_addr, pd + a_off, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
-                }
-                umma_commit(&bars[BAR_O_FULL + (j & 1)]);
+                for (int ks = 0; ks < TC_KEYS / 16; ++ks)
+                    umma_f16_ts(o_addr, p_addr + (uint32_t)ks * 8u, vd + (uint64_t)(ks * 128), IDESC_PV, ks > 0 ? 1u : 0u);
+                umma_commit(&bars[BAR_O_FULL]);
                 umma_commit(&bars[BAR_P_EMPTY + (j & 1)]);
                 umma_commit(&bars[BAR_V_EMPTY + s]);
             }
@@ -247,8 +246,6 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
         const int64_t block_min_limit = p.causal ? min(p.T - 1, p.causal_offset + l0) : p.T - 1;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        unsigned char *p_row = sp + row * 128;
-        const int sw = row & 7;
         for (int j = 0; j < n_tiles; ++j) {
             ok = mbar_wait(&bars[BAR_S_FULL + (j & 1)], (j >> 1) & 1);
             if (!ok) break;
@@ -282,7 +279,6 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             // this P tile is free once the O product of two tiles ago has read it
             if (j >= 2) ok = mbar_wait(&bars[BAR_P_EMPTY + (j & 1)], ((j >> 1) - 1) & 1);
             if (!ok) break;
-            unsigned char *p_dst = p_row + (j & 1) * TC_TILE;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int kc = 0; kc < TC_KEYS / 8; ++kc) {   // 16-byte chunk (8 keys) of the row
@@ -292,15 +288,16 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
                     e[i] = fast_exp2(fmaf(__uint_as_float(raw[kc * 8 + i]), p.scale_log2, neg_m));   // exp2(-inf) = 0
                     sum4[i & 3] += e[i];
                 }
-                uint4 w;
-                w.x = pack_pair<T>(e[0], e[1]);
-                w.y = pack_pair<T>(e[2], e[3]);
-                w.z = pack_pair<T>(e[4], e[5]);
-                w.w = pack_pair<T>(e[6], e[7]);
-                *(uint4 *)(p_dst + (kc >> 3) * TC_BOX + (((kc & 7) ^ sw) << 4)) = w;
+                // the probabilities as pairs, kept in the registers the scores came in (entry 4 kc + q of the
+                // packed row: always behind the scores still to be read)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) raw[kc * 4 + q] = pack_pair<T>(e[2 * q], e[2 * q + 1]);
+                // P_j goes into TMEM (this thread's lane), where the O product reads it as its A operand
+                if (kc == 7) tmem_st32_issue(lane_addr + 384u + (uint32_t)(j & 1) * 64u, raw);
             }
-            // P is visible to the tensor cores (async proxy) before the MMA warp hears about it
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_st32_issue(lane_addr + 384u + (uint32_t)(j & 1) * 64u + 32u, raw + 32);
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(&bars[BAR_P_FULL + (j & 1)]);
             l_run = l_run * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_run = m_new;
@@ -326,20 +323,20 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
             if (!ok) break;
             const float alpha = s_alpha[(j & 1) * TC_ROWS + row];
             mbar_arrive(&bars[BAR_A_EMPTY + (j & 1)]);
-            ok = mbar_wait(&bars[BAR_O_FULL + (j & 1)], (j >> 1) & 1);
+            ok = mbar_wait(&bars[BAR_O_FULL], j & 1);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int half = 0; half < D / 64; ++half) {
                 uint32_t raw[64];
-                tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64, raw);
-                tmem_ld32_issue(lane_addr + (uint32_t)(j & 1) * 128u + half * 64 + 32, raw + 32);
+                tmem_ld32_issue(lane_addr + half * 64, raw);
+                tmem_ld32_issue(lane_addr + half * 64 + 32, raw + 32);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 64; ++i) o_acc[half * 64 + i] = fmaf(o_acc[half * 64 + i], alpha, __uint_as_float(raw[i]));
             }
             tc_fence_before();
-            mbar_arrive(&bars[BAR_O_EMPTY + (j & 1)]);
+            mbar_arrive(&bars[BAR_O_EMPTY]);
         }
         if (ok) ok = mbar_wait(&bars[BAR_L_FULL], 0);
         if (!ok) {
@@ -371,7 +368,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 template <typename T, int D>
 bool launch_tc_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const ChunkTcParams &p, int ctas,
                      cudaStream_t stream) {
-    const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + 2 * (size_t)TC_TILE + BAR_COUNT * sizeof(uint64_t) + 64 +
+    const size_t smem = (size_t)(D / 64) * TC_BOX * (1 + 2 * TC_STAGES) + BAR_COUNT * sizeof(uint64_t) + 64 +
                         3 * TC_ROWS * sizeof(float) + 1024;
     // 0 = not yet, 1 = ready, -1 = refused; distinct handles may call from distinct host threads
     static std::atomic<int> configured[64];

@@ -17,7 +17,7 @@ constexpr int TC_ROWS = 128;                 // query rows per CTA = TMEM lanes
 constexpr int TC_KEYS = 128;                 // keys per tile
 constexpr int TC_BOX = 128 * 128;            // bytes of one 64-element-wide box of 128 rows
 constexpr int TC_TILE = 2 * TC_BOX;          // 32 KB: a 128 x 128 16-bit tile (P; Q, K and V at head dim 128)
-constexpr int TC_STAGES = 2;
+constexpr int TC_STAGES = 3;             // K / V ring of the prefill kernel (its P tile lives in TMEM)
 constexpr int TC_THREADS = 320;
 constexpr uint32_t TC_TMEM_COLS = 512;       // S0 | S1 | O0 | O1, 128 fp32 columns each
 
