@@ -313,6 +313,7 @@ def test_calibrated_turbo_prefill_chunk_on_the_tensor_core_kernel(kvc, oracle, c
     (1, 17, 1, 4, 64, 300, 1),       # 17 heads on one kv head, one position, no causal limit to speak of
     (16, 56, 8, 4, 64, 700, 6),      # 128 units: one CTA each, six tiles in a row, no split
     (1, 8, 1, 4, 64, 120, 8),        # 64 rows; the chunk itself crosses the first tile boundary
+    (40, 20, 4, 4, 64, 300, 4),      # 160 units of three tiles on fewer SMs: CTAs that walk two or three units
 ])
 def test_affine_verify_rounds(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, bits, group, P, L):
     """17 to 64 query rows per kv head over the affine cache. 4- or 8-bit codes in groups of 64: the tcgen05 verify

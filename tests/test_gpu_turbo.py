@@ -346,6 +346,8 @@ def test_library_rotation_generator(kvc, oracle):
     (2, 16, 2, 7, 1531, 3, "causal"),   # 56 rows, ragged last tile, splits with a shorter last one
     (16, 64, 8, 6, 700, 3, "causal"),   # the 70B layout: 128 units, one CTA each, no split
     (2, 16, 2, 5, 900, 4, "causal"),    # 4-bit keys (turbo4): the keys read the value pair table
+    (40, 12, 4, 3, 300, 3, "causal"),   # 160 units of three tiles on fewer SMs: CTAs that walk two or three units, whole and cut
+    (37, 25, 5, 2, 530, 2, "causal"),   # 185 units of five tiles: ranges of seven tiles, every unit cut somewhere else
 ])
 def test_tensor_core_verify_kernel_shapes(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, P, kb, mask):
     """Edge shapes of the tcgen05 verify kernel (9 .. 64 rows per kv head, 2- / 3-bit keys, 4-bit values): row
