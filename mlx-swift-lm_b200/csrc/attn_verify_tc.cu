@@ -125,8 +125,6 @@ __host__ __device__ constexpr int affine_pos_of(int dim, int bits) {
     return bits == 4 ? (dim & ~7) | (2 * (dim & 3) + ((dim >> 2) & 1)) : (dim & ~3) | ((dim & 1) << 1) | ((dim >> 1) & 1);
 }
 
-__host__ __device__ constexpr int stage_stride(int words) { return (words / 4) % 2 ? words : words + 4; }
-
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -156,9 +154,6 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     // 32 KB table does not fit beside the tiles
     constexpr int KTAB_ENTRIES = (AFFINE || KB == 4) ? 0 : 1 << (2 * KB);
     constexpr int VTAB_WORDS = AFFINE ? 0 : 256 * 32;
-    // a staged row starts an odd multiple of 16 bytes after the one before: the eight threads of a quarter
-    // warp then read (and cp.async writes) their 16-byte pieces from eight different bank groups
-    constexpr int KWS = stage_stride(KW), VWS = stage_stride(VW);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q' block
@@ -166,12 +161,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     uint32_t *vtab = (uint32_t *)(skv + 2 * 2 * VT_TILE);      // [256 byte values][32 lanes] f16x2(c[b & 15], c[b >> 4])
     uint32_t *ktab_own = vtab + VTAB_WORDS;                    // [entries][32 lanes] f16x2
     uint32_t *ktab = KB == 4 ? vtab : ktab_own;
-    // packed rows of the next key / value tile, copied in by their own thread with cp.async (registers that
-    // held them across the correction step pushed the row accumulator into local memory)
-    uint32_t *kstage = ktab_own + KTAB_ENTRIES * 32;           // [128][KWS]
-    uint32_t *vstage = kstage + TC_KEYS * KWS;                 // [128][VWS]
-    float *nstage = (float *)(vstage + TC_KEYS * VWS);         // [4][128] key norms | value norms (affine: scales, biases of K, of V)
-    uint64_t *bars = (uint64_t *)(nstage + 4 * TC_KEYS);
+    uint64_t *bars = (uint64_t *)(ktab_own + KTAB_ENTRIES * 32);
     uint32_t *tmem_slot = (uint32_t *)(bars + VB_COUNT);
     float *s_alpha = (float *)(tmem_slot + 4);                 // [4][128]: rows 0..63 alpha, rows 64..127 -max
     float *s_lsum = s_alpha + 4 * TC_ROWS;                     // [128]
@@ -503,35 +493,35 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint32_t *cbase = is_v ? p.vp + b * p.vp_sb + hk * p.vp_sh : p.kp + b * p.kp_sb + hk * p.kp_sh;
             const uint16_t *sbase = is_v ? p.vs + b * p.vn_sb + hk * p.vn_sh : p.ks + b * p.kn_sb + hk * p.kn_sh;
             const uint16_t *zbase = is_v ? p.vz + b * p.vn_sb + hk * p.vn_sh : p.kz + b * p.kn_sb + hk * p.kn_sh;
-            const uint32_t st_a = smem_u32((is_v ? vstage : kstage) + row * KWS);
-            const uint32_t sst_a = smem_u32(nstage + (is_v ? 2 : 0) * TC_KEYS + row), zst_a = sst_a + TC_KEYS * 4u;
             const int full_bar = is_v ? VB_V_FULL : VB_K_FULL, empty_bar = is_v ? VB_V_EMPTY : VB_K_EMPTY;
             const bool sz_bf16 = p.sz_bf16 != 0;
-            auto fetch = [&](int j) {      // tile j of this CTA's range: one cp.async group of this thread
+            // The packed row of the NEXT tile is loaded straight into registers while this one is decoded (a
+            // thread's row is 64 or 128 contiguous bytes; a warp reads 32 rows in a row): no staging in shared
+            // memory, whose data pipe is what bounds this kernel.
+            uint4 nxt[KW / 4];
+            uint32_t nsc = 0u, nzp = 0u;
+            auto fetch = [&](int j) {      // tile j of this CTA's range
                 if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
                     const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
-                    const uint32_t *src = cbase + t * KW;
+                    const uint4 *src = (const uint4 *)(cbase + t * KW);
 #pragma unroll
-                    for (int i = 0; i < KW / 4; ++i)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st_a + 16u * i), "l"(src + 4 * i) : "memory");
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sst_a), "l"(sbase + t * 2) : "memory");
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(zst_a), "l"(zbase + t * 2) : "memory");
+                    for (int i = 0; i < KW / 4; ++i) nxt[i] = __ldg(src + i);
+                    nsc = __ldg((const uint32_t *)(sbase + t * 2));
+                    nzp = __ldg((const uint32_t *)(zbase + t * 2));
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
             };
+#pragma unroll
+            for (int i = 0; i < KW / 4; ++i) nxt[i] = make_uint4(0u, 0u, 0u, 0u);
             fetch(0);
 #pragma unroll 1
             for (int j = 0; j < n_tiles && ok; ++j) {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
                 const int s = j & 1;
-                // the staged row goes to registers and its place takes the next tile's copy at once
-                uint32_t all[KW], sc, zp;
+                uint32_t all[KW];
 #pragma unroll
-                for (int i = 0; i < KW / 4; ++i)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(st_a + 16u * i));
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc) : "r"(sst_a));
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zp) : "r"(zst_a));
+                for (int i = 0; i < KW / 4; ++i) {
+                    all[4 * i] = nxt[i].x; all[4 * i + 1] = nxt[i].y; all[4 * i + 2] = nxt[i].z; all[4 * i + 3] = nxt[i].w;
+                }
+                const uint32_t sc = nsc, zp = nzp;
                 fetch(j + 1);
                 if (j >= 2) ok = mbar_wait(&bars[empty_bar + s], ((j >> 1) - 1) & 1);
                 if (!ok) break;
@@ -577,30 +567,32 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint32_t vtab_a = smem_u32(vtab) + (uint32_t)lane * 4u;
             const int sw = row & 7;
             bool ok = true;
-            const uint32_t kst_a = smem_u32(kstage + row * KWS), vst_a = smem_u32(vstage + row * VWS);
-            const uint32_t knst_a = smem_u32(nstage + row), vnst_a = smem_u32(nstage + TC_KEYS + row);
-            // every fetch is one cp.async group of this thread (an empty one past the last tile)
+            // The packed row of the NEXT tile is loaded straight into registers while this one is decoded (a
+            // thread's row is 32 to 64 contiguous bytes; a warp reads 32 rows in a row): no staging in shared
+            // memory, whose data pipe is what bounds this kernel.
+            uint4 nk[KW / 4], nv[VW / 4];
+            float nkn = 0.f, nvn = 0.f;
+#pragma unroll
+            for (int i = 0; i < KW / 4; ++i) nk[i] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int i = 0; i < VW / 4; ++i) nv[i] = make_uint4(0u, 0u, 0u, 0u);
             auto fetch_k = [&](int j) {      // tile j of this CTA's range
                 if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
                     const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
-                    const uint32_t *src = kbase + t * KW;
+                    const uint4 *src = (const uint4 *)(kbase + t * KW);
 #pragma unroll
-                    for (int i = 0; i < KW / 4; ++i)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kst_a + 16u * i), "l"(src + 4 * i) : "memory");
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(knst_a), "l"(knb + t) : "memory");
+                    for (int i = 0; i < KW / 4; ++i) nk[i] = __ldg(src + i);
+                    nkn = __ldg(knb + t);
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
             };
             auto fetch_v = [&](int j) {
                 if (j < n_tiles && !(KVC_SKIP_BITS(p) & 1)) {
                     const int64_t t = (int64_t)(j_lo + j) * TC_KEYS + row;
-                    const uint32_t *src = vbase + t * VW;
+                    const uint4 *src = (const uint4 *)(vbase + t * VW);
 #pragma unroll
-                    for (int i = 0; i < VW / 4; ++i)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vst_a + 16u * i), "l"(src + 4 * i) : "memory");
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(vnst_a), "l"(vnb + t) : "memory");
+                    for (int i = 0; i < VW / 4; ++i) nv[i] = __ldg(src + i);
+                    nvn = __ldg(vnb + t);
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
             };
             // The two halves of a row are a rolled loop and each writer has one call site: unrolled, the roles of
             // this kernel together outgrow the instruction cache. Within a half the 32 lookups are issued back to
@@ -608,14 +600,12 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             // thread and the warp waits out every latency).
             auto write_k = [&](int j) {      // the row's copy (the group before the newest) has landed
                 const int s = j & 1;
-                // the staged row goes to registers and its place takes the next tile's copy at once
                 uint32_t all[KW];
 #pragma unroll
-                for (int i = 0; i < KW / 4; ++i)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(kst_a + 16u * i));
-                float knorm;
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(knorm) : "r"(knst_a));
+                for (int i = 0; i < KW / 4; ++i) {
+                    all[4 * i] = nk[i].x; all[4 * i + 1] = nk[i].y; all[4 * i + 2] = nk[i].z; all[4 * i + 3] = nk[i].w;
+                }
+                const float knorm = nkn;
                 fetch_k(j + 1);
                 if (j >= 2 && !mbar_wait(&bars[VB_K_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
                 unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + row * 128;
@@ -647,11 +637,10 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 const int s = j & 1;
                 uint32_t all[VW];
 #pragma unroll
-                for (int i = 0; i < VW / 4; ++i)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(all[4 * i]), "=r"(all[4 * i + 1]), "=r"(all[4 * i + 2]), "=r"(all[4 * i + 3]) : "r"(vst_a + 16u * i));
-                float vnorm;
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vnorm) : "r"(vnst_a));
+                for (int i = 0; i < VW / 4; ++i) {
+                    all[4 * i] = nv[i].x; all[4 * i + 1] = nv[i].y; all[4 * i + 2] = nv[i].z; all[4 * i + 3] = nv[i].w;
+                }
+                const float vnorm = nvn;
                 fetch_v(j + 1);
                 if (j >= 2 && !mbar_wait(&bars[VB_V_EMPTY + s], ((j >> 1) - 1) & 1)) return false;
                 unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + VT_TILE + row * 128;
@@ -680,26 +669,17 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                 mbar_arrive(&bars[VB_V_FULL + s]);
                 return true;
             };
-            // A row writer reads its row and at once refills the place with the next tile's row (one cp.async
-            // group), so that a copy has a whole step to land.
             if (is_v) {
                 fetch_v(0);
 #pragma unroll 1
-                for (int j = 0; j < n_tiles && ok; ++j) {
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-                    ok = write_v(j);
-                }
+                for (int j = 0; j < n_tiles && ok; ++j) ok = write_v(j);
             } else {
                 fetch_k(0);
 #pragma unroll 1
-                for (int j = 0; j < n_tiles && ok; ++j) {
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-                    ok = write_k(j);
-                }
+                for (int j = 0; j < n_tiles && ok; ++j) ok = write_k(j);
             }
             if (!ok) atomicExch(p.status, 29);
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -827,7 +807,7 @@ template <typename TO, int KB, bool AFFINE>
 bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
     const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
-                        (size_t)TC_KEYS * (stage_stride(VT_D * KB / 32) + stage_stride(AFFINE ? VT_D * KB / 32 : VT_D * 4 / 32) + 4) * 4 + VB_COUNT * sizeof(uint64_t) + 64 +
+                        VB_COUNT * sizeof(uint64_t) + 64 +
                         6 * TC_ROWS * sizeof(float) + 16 + 1024;
     static std::atomic<int> configured[64];
     const int dev = current_device();
