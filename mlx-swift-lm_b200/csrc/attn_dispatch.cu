@@ -13,6 +13,7 @@ int launch_attention_turbo(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_packed(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_tc(const AttnArgs &a, cudaStream_t stream);
 int launch_attention_chunk_materialized(const AttnArgs &a, cudaStream_t stream);
+int launch_attention_verify_tc_raw(const AttnArgs &a, cudaStream_t stream);
 
 namespace {
 // KVC_ATTENTION_PATH=general forces the general kernel (read once per process; used by
@@ -29,6 +30,8 @@ bool force_general() {
 int launch_attention(const AttnArgs &a, cudaStream_t stream) {
     if (!force_general()) {
         int n = launch_attention_chunk_tc(a, stream);   // long chunks over raw caches: tcgen05 kernel
+        if (n > 0) return n;
+        n = launch_attention_verify_tc_raw(a, stream);   // verify rounds of 17 ... 64 rows per KV head over raw caches
         if (n > 0) return n;
         n = launch_attention_decode(a, stream);
         if (n > 0) return n;

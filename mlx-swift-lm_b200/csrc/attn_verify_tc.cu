@@ -144,16 +144,20 @@ __device__ __forceinline__ uint32_t pair_index(const uint32_t (&w)[NW], int p) {
 
 // AFFINE: the cache is the group-wise affine one (KB = 4- or 8-bit codes, groups of 64, QuantizedKVCache); the rows are
 // code * scale + bias instead of norm * centroid, there are no tables, the output rows are TO.
-template <typename TO, int KB, bool AFFINE>
+// RAW: the cache holds plain f16 / bf16 rows (KVCacheSimple): the K / V tiles come in by tiled TMA loads (two lanes
+// are the producers, the other writer warps idle), queries, tiles and probabilities are TO.
+template <typename TO, int KB, bool AFFINE, bool RAW = false>
 __global__ void __launch_bounds__(VT_THREADS, 1)
-attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ VerifyParams p) {
+attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                      const __grid_constant__ CUtensorMap vmap, const __grid_constant__ VerifyParams p) {
+    using TP = typename std::conditional<RAW, TO, __half>::type;      // operand type of Q', K, V and P
     constexpr int D = VT_D;
     constexpr int KW = D * KB / 32;          // key words per row
     constexpr int VW = AFFINE ? KW : D * 4 / 32;   // value words per row (TurboQuant: 4-bit; affine: as the keys)
     // 4-bit keys share the value pair table (the launcher checks that the two codebooks are the same): a second
     // 32 KB table does not fit beside the tiles
-    constexpr int KTAB_ENTRIES = (AFFINE || KB == 4) ? 0 : 1 << (2 * KB);
-    constexpr int VTAB_WORDS = AFFINE ? 0 : 256 * 32;
+    constexpr int KTAB_ENTRIES = (AFFINE || RAW || KB == 4) ? 0 : 1 << (2 * KB);
+    constexpr int VTAB_WORDS = (AFFINE || RAW) ? 0 : 256 * 32;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *sq = base;                                  // Q' block
@@ -180,9 +184,9 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     auto init_barriers = [&]() {
         mbar_init(&bars[VB_Q], 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars[VB_K_FULL + s], 128);
+            mbar_init(&bars[VB_K_FULL + s], RAW ? 1 : 128);
             mbar_init(&bars[VB_K_EMPTY + s], 1);
-            mbar_init(&bars[VB_V_FULL + s], 128);
+            mbar_init(&bars[VB_V_FULL + s], RAW ? 1 : 128);
             mbar_init(&bars[VB_V_EMPTY + s], 1);
             mbar_init(&bars[VB_S_FULL + s], 1);
             mbar_init(&bars[VB_S_EMPTY + s], 64);      // the two softmax warps
@@ -201,7 +205,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     };
     if (tid == 0) init_barriers();
     // tables: key entry e of lane l = f16x2(centroid[e & m], centroid[e >> KB]); value entry i = (c, c)
-    if constexpr (!AFFINE) {
+    if constexpr (!AFFINE && !RAW) {
         for (int w = tid; w < KTAB_ENTRIES * 32; w += VT_THREADS) {
             const int e = w >> 5;
             ktab[w] = pack_h2(p.kcb[e & ((1 << KB) - 1)], p.kcb[e >> KB]);
@@ -247,8 +251,10 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
-            constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);                 // f16 x f16 -> f32
-            constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
+            // operand formats at bits 7-9 (A) and 10-12 (B): 0 = f16, 1 = bf16
+            constexpr uint32_t FMT = std::is_same<TP, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t IDESC_PV = (1u << 4) | (FMT << 7) | (FMT << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t q_desc = umma_desc(smem_u32(sq), 16, 1024);
             const uint64_t k_desc = umma_desc(smem_u32(skv), 16, 1024);
             const uint64_t v_desc = umma_desc(smem_u32(skv) + VT_TILE, 16384, 1024);
@@ -349,7 +355,7 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
                     const float e1 = (KVC_SKIP_BITS(p) & 16) ? 0.f : fast_exp2(fmaf(__uint_as_float(raw[2 * i + 1]), p.scale_log2, neg_m));
                     sum4[(2 * i) & 3] += e0;
                     sum4[(2 * i + 1) & 3] += e1;
-                    pk[i] = pack_h2(e0, e1);
+                    pk[i] = pack_pair<TP>(e0, e1);
                 }
                 // P_j goes into TMEM (this thread's lane, columns of its own), where the O product reads it as its
                 // A operand: the 32 scores of block cb become 16 columns
@@ -485,7 +491,26 @@ attn_verify_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         // warps 2, 6, 10, 14 write the key rows, warps 3, 7, 11, 15 the value rows (32 rows each), at the same time
         const bool is_v = (warp & 1) != 0;
         const int row = (warp >> 2) * 32 + lane;
-        if constexpr (AFFINE) {
+        if constexpr (RAW) {
+            // lane 0 of warp 2 loads the key tiles, lane 0 of warp 3 the value tiles (two boxes of 64 dims each,
+            // 128-byte swizzle; rows past T come in as zeros)
+            if (warp < 4 && lane == 0) {
+                bool ok = true;
+                const CUtensorMap *map = is_v ? &vmap : &kmap;
+                const int full_bar = is_v ? VB_V_FULL : VB_K_FULL, empty_bar = is_v ? VB_V_EMPTY : VB_K_EMPTY;
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    const int s = j & 1;
+                    if (j >= 2) ok = mbar_wait(&bars[empty_bar + s], ((j >> 1) - 1) & 1);
+                    if (!ok) break;
+                    unsigned char *dst = skv + (size_t)s * 2 * VT_TILE + (is_v ? VT_TILE : 0);
+                    mbar_expect_tx(&bars[full_bar + s], VT_TILE);
+#pragma unroll
+                    for (int bx = 0; bx < D / 64; ++bx)
+                        tma_load_4d(dst + bx * TC_BOX, map, &bars[full_bar + s], bx * 64, (j_lo + j) * TC_KEYS, hk, b);
+                }
+                if (!ok) atomicExch(p.status, 29);
+            }
+        } else if constexpr (AFFINE) {
             const int sw = row & 7;
             bool ok = true;
             // one code path for key and value rows (the warp's kind picks the arrays, the staging places, the tile
@@ -803,10 +828,11 @@ __global__ void __launch_bounds__(256) verify_q_plain_kernel(const __grid_consta
     *(uint4 *)(p.out + gr * D + c8 * 8) = w;
 }
 
-template <typename TO, int KB, bool AFFINE>
-bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int ctas, cudaStream_t stream) {
+template <typename TO, int KB, bool AFFINE, bool RAW = false>
+bool launch_verify_typed(const CUtensorMap &qmap, const CUtensorMap &kmap, const CUtensorMap &vmap, const VerifyParams &p, int ctas,
+                         cudaStream_t stream) {
     // Q' and two stages of (K tile, V tile); the two lookup tables (TurboQuant); the staged rows
-    const size_t smem = (size_t)5 * VT_TILE + (AFFINE ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
+    const size_t smem = (size_t)5 * VT_TILE + ((AFFINE || RAW) ? 0 : (size_t)VT_TILE + (KB == 4 ? 0 : ((size_t)1 << (2 * KB)) * 128)) +
                         VB_COUNT * sizeof(uint64_t) + 64 +
                         6 * TC_ROWS * sizeof(float) + 16 + 1024;
     static std::atomic<int> configured[64];
@@ -814,14 +840,14 @@ bool launch_verify_typed(const CUtensorMap &qmap, const VerifyParams &p, int cta
     if (dev < 0 || dev >= 64) return false;
     int state = configured[dev].load(std::memory_order_acquire);
     if (state == 0) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_verify_tc_kernel<TO, KB, AFFINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_verify_tc_kernel<TO, KB, AFFINE, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) (void)cudaGetLastError();
         state = e == cudaSuccess ? 1 : -1;
         configured[dev].store(state, std::memory_order_release);
     }
     if (state < 0) return false;
     KernelTimer timer(stream);
-    KVC_CUDA(launch_pdl(attn_verify_tc_kernel<TO, KB, AFFINE>, dim3(ctas), dim3(VT_THREADS), smem, stream, qmap, p));
+    KVC_CUDA(launch_pdl(attn_verify_tc_kernel<TO, KB, AFFINE, RAW>, dim3(ctas), dim3(VT_THREADS), smem, stream, qmap, kmap, vmap, p));
     timer.stop();
     ++g_launch_count;
     return true;
@@ -918,9 +944,9 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     p.debug_skip = measure_skip_bits();
 
     bool taken = false;
-    if (kb == 2) taken = launch_verify_typed<__half, 2, false>(qmap, p, (int)ctas, stream);
-    else if (kb == 4) taken = launch_verify_typed<__half, 4, false>(qmap, p, (int)ctas, stream);
-    else taken = launch_verify_typed<__half, 3, false>(qmap, p, (int)ctas, stream);
+    if (kb == 2) taken = launch_verify_typed<__half, 2, false>(qmap, qmap, qmap, p, (int)ctas, stream);
+    else if (kb == 4) taken = launch_verify_typed<__half, 4, false>(qmap, qmap, qmap, p, (int)ctas, stream);
+    else taken = launch_verify_typed<__half, 3, false>(qmap, qmap, qmap, p, (int)ctas, stream);
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
     if (merge) {
@@ -938,6 +964,34 @@ int launch_attention_verify_tc(const AttnArgs &a, cudaStream_t stream) {
     return launches;
 }
 
+
+// Queries of every unit for the raw cache, padded to 128 rows (zero rows past R), element type unchanged.
+// One thread per eight dims.
+template <typename T>
+__global__ void __launch_bounds__(256) verify_q_raw_kernel(const QPadParams p) {
+    constexpr int D = VT_D;
+    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t units = (int64_t)p.B * p.Hkv;
+    if (g >= units * TC_ROWS * (D / 8)) return;
+    const int c8 = (int)(g % (D / 8));
+    const int64_t gr = g / (D / 8);
+    const int unit = (int)(gr / TC_ROWS), r = (int)(gr % TC_ROWS);
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (r < p.R) {
+        const int hk = unit % p.Hkv, b = unit / p.Hkv, rep = p.Hq / p.Hkv;
+        const int hq = hk * rep + r / p.L, l = r % p.L;
+        const T *src = (const T *)p.q + b * p.q_sb + hq * p.q_sh + l * p.q_sl + c8 * 8;
+        if (((uintptr_t)src & 15) == 0) {
+            w = *(const uint4 *)src;
+        } else {
+            T tmp[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tmp[i] = src[i];
+            w = *(const uint4 *)tmp;
+        }
+    }
+    *(uint4 *)((T *)p.out + gr * D + c8 * 8) = w;
+}
 
 // QuantizedKVCache verify rounds (quantizedScaledDotProductAttention over a handful of positions per head,
 // KVCache.swift:1045-1110 via AttentionUtils.swift:53-71): 4- or 8-bit codes in groups of 64, head dim 128,
@@ -1032,11 +1086,11 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
 
     bool taken = false;
     if (a.k.bits == 4) {
-        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, true>(qmap, p, (int)ctas, stream);
-        else taken = launch_verify_typed<__half, 4, true>(qmap, p, (int)ctas, stream);
+        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, true>(qmap, qmap, qmap, p, (int)ctas, stream);
+        else taken = launch_verify_typed<__half, 4, true>(qmap, qmap, qmap, p, (int)ctas, stream);
     } else {
-        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 8, true>(qmap, p, (int)ctas, stream);
-        else taken = launch_verify_typed<__half, 8, true>(qmap, p, (int)ctas, stream);
+        if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 8, true>(qmap, qmap, qmap, p, (int)ctas, stream);
+        else taken = launch_verify_typed<__half, 8, true>(qmap, qmap, qmap, p, (int)ctas, stream);
     }
     if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
     ++launches;
@@ -1048,6 +1102,93 @@ int launch_attention_verify_tc_affine(const AttnArgs &a, cudaStream_t stream) {
     }
     if (trace_dispatch())
         fprintf(stderr, "[kvc] verify_tc affine: %lld units of %d rows and %d tiles, %lld CTAs of %d tiles\n", (long long)units, R, n_tiles, (long long)ctas, tiles_per_cta);
+    return launches;
+}
+
+
+// KVCacheSimple verify rounds (17 ... 64 rows per KV head over plain f16 / bf16 rows, head dim 128): the same
+// kernel with TMA-loaded K / V tiles. Returns the number of kernels launched, 0 when the call is left to the
+// other kernels. KVC_VERIFY_TC=0 turns the path off.
+int launch_attention_verify_tc_raw(const AttnArgs &a, cudaStream_t stream) {
+    static const bool off = [] {
+        const char *e = std::getenv("KVC_VERIFY_TC");
+        return e && e[0] == '0';
+    }();
+    if (off) return 0;
+    if (a.D != VT_D || (a.q_dtype != KVC_BF16 && a.q_dtype != KVC_F16)) return 0;
+    if (a.k.kind != SRC_RAW || a.v.kind != SRC_RAW || a.k.dtype != a.q_dtype || a.v.dtype != a.q_dtype) return 0;
+    if (a.mask.mode == KVC_MASK_ARRAY || a.q_signs || a.o_signs || a.q_calib || a.new_k || a.q_rot || a.o_rot) return 0;
+    if (a.mask.mode == KVC_MASK_CAUSAL && a.mask.causal_offset < 0) return 0;
+    if (a.Hkv <= 0 || a.Hq % a.Hkv || a.T < 1 || a.T > (int64_t)1 << 30) return 0;
+    const int rep = a.Hq / a.Hkv, R = rep * a.L;
+    if (R <= 16 || R > 64) return 0;          // up to 16 rows: the decode kernels
+    if (!strides_fit(a.k.data, a.D, a.k.st, a.k.sh, a.k.sb, a.Hkv, a.B) || !strides_fit(a.v.data, a.D, a.v.st, a.v.sh, a.v.sb, a.Hkv, a.B))
+        return 0;
+    if (((uintptr_t)a.out & 15) != 0 || (a.o_sl * 2) % 16 || (a.o_sh * 2) % 16 || (a.o_sb * 2) % 16) return 0;
+    int *status = device_status_word(a.device);
+    if (!status) return 0;
+
+    const int64_t units = (int64_t)a.B * a.Hkv;
+    const int n_tiles = (int)((a.T + TC_KEYS - 1) / TC_KEYS);
+    const int sms = sm_count(a.device);
+    const int64_t flat = units * n_tiles;
+    if (flat > (int64_t)1 << 40) return 0;
+    const int64_t tpc64 = (flat + std::min<int64_t>(sms, flat) - 1) / std::min<int64_t>(sms, flat);
+    if (tpc64 > (int64_t)1 << 30) return 0;
+    const int tiles_per_cta = (int)tpc64;
+    const int64_t ctas = (flat + tiles_per_cta - 1) / tiles_per_cta;
+    const bool merge = tiles_per_cta % n_tiles != 0;
+    const int max_pieces = (n_tiles + tiles_per_cta - 1) / tiles_per_cta + 1;
+
+    const size_t q_bytes = (size_t)units * TC_ROWS * VT_D * 2;
+    const size_t o_bytes = merge ? (size_t)units * max_pieces * R * VT_D * sizeof(float) : 0;
+    const size_t ml_bytes = merge ? (size_t)units * max_pieces * R * sizeof(float2) : 0;
+    char *scratch = (char *)scratch_get(a.device, q_bytes + o_bytes + ml_bytes + 1024, stream);
+
+    CUtensorMap qmap, kmap, vmap;
+    if (!make_map_tc(&qmap, scratch, a.q_dtype, VT_D, TC_ROWS, (int)units, 1, VT_D, (int64_t)TC_ROWS * VT_D, units * TC_ROWS * VT_D)) return 0;
+    if (!make_map_tc(&kmap, a.k.data, a.k.dtype, a.D, a.T, a.Hkv, a.B, a.k.st, a.k.sh, a.k.sb)) return 0;
+    if (!make_map_tc(&vmap, a.v.data, a.v.dtype, a.D, a.T, a.Hkv, a.B, a.v.st, a.v.sh, a.v.sb)) return 0;
+
+    QPadParams qp = {};
+    qp.q = a.q; qp.out = (__half *)scratch;
+    qp.q_sb = a.q_sb; qp.q_sh = a.q_sh; qp.q_sl = a.q_sl;
+    qp.B = a.B; qp.Hq = a.Hq; qp.Hkv = a.Hkv; qp.L = a.L; qp.R = R;
+    const unsigned qblocks = (unsigned)((units * TC_ROWS * (VT_D / 8) + 255) / 256);
+    if (a.q_dtype == KVC_BF16) verify_q_raw_kernel<__nv_bfloat16><<<qblocks, 256, 0, stream>>>(qp);
+    else verify_q_raw_kernel<__half><<<qblocks, 256, 0, stream>>>(qp);
+    KVC_CUDA(cudaGetLastError());
+    ++g_launch_count;
+    int launches = 1;
+
+    VerifyParams p = {};
+    p.out_bf16 = a.q_dtype == KVC_BF16 ? 1 : 0;
+    p.out = a.out;
+    p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_sl = a.o_sl;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.L = a.L; p.R = R;
+    p.T = a.T;
+    p.causal = a.mask.mode == KVC_MASK_CAUSAL ? 1 : 0;
+    p.causal_offset = a.mask.causal_offset;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.tiles_per_cta = tiles_per_cta; p.max_pieces = max_pieces;
+    p.o_part = (float *)(scratch + ((q_bytes + 255) / 256) * 256);
+    p.ml_part = (float2 *)((char *)p.o_part + ((o_bytes + 255) / 256) * 256);
+    p.status = status;
+    p.debug_skip = measure_skip_bits();
+
+    bool taken = false;
+    if (a.q_dtype == KVC_BF16) taken = launch_verify_typed<__nv_bfloat16, 4, false, true>(qmap, kmap, vmap, p, (int)ctas, stream);
+    else taken = launch_verify_typed<__half, 4, false, true>(qmap, kmap, vmap, p, (int)ctas, stream);
+    if (!taken) fail(KVC_ERR_INTERNAL, "verify kernel: the device refused its shared memory");
+    ++launches;
+    if (merge) {
+        verify_merge_kernel<<<(unsigned)(units * R), VT_D, 0, stream>>>(p);
+        KVC_CUDA(cudaGetLastError());
+        ++g_launch_count;
+        ++launches;
+    }
+    if (trace_dispatch())
+        fprintf(stderr, "[kvc] verify_tc raw: %lld units of %d rows and %d tiles, %lld CTAs of %d tiles\n", (long long)units, R, n_tiles, (long long)ctas, tiles_per_cta);
     return launches;
 }
 

@@ -302,3 +302,33 @@ def test_bounded_wait_reports_through_the_status_word(kvc, cuda):
     k = seeded((1, 2, 300, 128), 2, torch.bfloat16).to(cuda)
     out = kvc.scaled_dot_product_attention(q, k, k, 0.09)       # the device still answers
     assert torch.isfinite(out.float()).all() and kvc.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,Hq,Hkv,L,P,mask", [
+    (2, 32, 8, 6, 1000, "causal"),     # Llama-3-8B layout, verify round: 24 rows per kv head; split keys
+    (8, 32, 8, 6, 2100, "causal"),     # 64 units of 17 tiles on 148 SMs: CTAs that walk a cut unit and a whole one
+    (1, 17, 1, 1, 300, "none"),        # 17 heads on one kv head, one position
+    (1, 8, 1, 8, 120, "causal"),       # 64 rows; the chunk itself crosses the first tile boundary
+    (40, 12, 4, 6, 300, "causal"),     # 160 units of three tiles: more units than SMs
+])
+def test_raw_cache_verify_rounds_run_on_the_tensor_core_verify_kernel(kvc, oracle, cuda, capfd, monkeypatch, dtype, B, Hq, Hkv, L, P, mask):
+    """17 to 64 query rows per kv head over a KVCacheSimple at head dim 128: the tcgen05 verify kernel with
+    TMA-loaded K / V tiles; two rounds in a row with a rejection in between."""
+    D = 128
+    monkeypatch.setenv("KVC_TRACE_DISPATCH", "1")
+    g, o = kvc.KVCacheSimple(), oracle.KVCacheSimple()
+    k, v = seeded((B, Hkv, P, D), 1, dtype), seeded((B, Hkv, P, D), 2, dtype)
+    g.update(k.to(cuda), v.to(cuda))
+    o.update(to_oracle(k), to_oracle(v))
+    for rnd in range(2):
+        q = seeded((B, Hq, L, D), 3 + rnd, dtype)
+        k1, v1 = seeded((B, Hkv, L, D), 5 + rnd, dtype), seeded((B, Hkv, L, D), 7 + rnd, dtype)
+        capfd.readouterr()
+        out = g.attention(q.to(cuda), k1.to(cuda), v1.to(cuda), D ** -0.5, mask)
+        torch.cuda.synchronize()
+        assert "verify_tc raw" in capfd.readouterr().err
+        ref = oracle.attention_with_cache_update(to_oracle(q), to_oracle(k1), to_oracle(v1), o, D ** -0.5, mask)
+        assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
+        assert g.trim(max(L - 1, 0)) == o.trim(max(L - 1, 0))
+    assert kvc.lib().kvc_device_status() == 0
