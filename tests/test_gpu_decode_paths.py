@@ -102,12 +102,17 @@ print(kvc.launch_count())
     (1, 2, 1, 128, 512, 512, "causal"),     # one 512-token chunk from an empty cache
 ])
 def test_chunk_kernel_matches_oracle(kvc, oracle, cuda, dtype, B, Hq, Hkv, D, L, T, mask):
-    """Multi-token chunks (more than 16 rows per KV head): rows split across the warps."""
+    """Multi-token chunks (more than 16 rows per KV head): rows split across the warps of the mma.sync chunk
+    kernel; 17 to 64 rows per KV head at head dim 128 go to the tcgen05 verify kernel."""
     q = seeded((B, Hq, L, D), 1, dtype)
     k, v = seeded((B, Hkv, T, D), 2, dtype), seeded((B, Hkv, T, D), 3, dtype)
     n0 = kvc.launch_count(reset=True)
     out = kvc.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), D ** -0.5, mask)
-    assert kvc.launch_count(reset=True) == 1            # one kernel: partial + merge in one launch
+    launches = kvc.launch_count(reset=True)
+    if D == 128 and 16 < (Hq // Hkv) * L <= 64:
+        assert 2 <= launches <= 3       # the tcgen05 verify kernel behind its query kernel (+ merge)
+    else:
+        assert launches == 1            # one kernel: partial + merge in one launch
     ref = oracle.sdpa(to_oracle(q), to_oracle(k), to_oracle(v), D ** -0.5, mask)
     assert max_abs_diff(out, ref) <= TOL[dtype]
     assert kvc.lib().kvc_device_status() == 0
