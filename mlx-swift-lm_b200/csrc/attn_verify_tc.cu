@@ -1,34 +1,36 @@
-// Speculative verify rounds over the TurboQuant cache on the 5th-generation tensor cores.
+// Speculative verify rounds on the 5th-generation tensor cores: TurboQuant, affine and raw caches.
 //
 // TurboQuantKVCache.compressedAttention for a handful of query positions per head
 // (TurboQuantKVCache.swift:1164-1446; the reference's kernel for this step is the causal flash pass at
-// TurboQuantKernels.swift:879-1026): the rows of a KV head's group (rep heads x L positions, 9 ... 128
-// of them) all read the same keys and values, so the packed rows should be decoded ONCE for the
-// group. The decode kernel cannot do that (its accumulators for more than eight rows do not fit the
-// register file); here the group's rows are the 128-row M side of tcgen05.mma and the accumulators
-// live in TMEM.
+// TurboQuantKernels.swift:879-1026), quantizedScaledDotProductAttention over the QuantizedKVCache
+// (KVCache.swift:1045-1110) and plain scaled-dot-product attention over a KVCacheSimple for the same call
+// shape: the rows of a KV head's group (rep heads x L positions, 9 ... 64 of them) all read the same keys
+// and values, so the packed rows should be decoded ONCE for the group. The decode kernels cannot do that
+// (their accumulators for more than eight rows do not fit the register file); here the group's rows are the
+// 128-row M side of tcgen05.mma and the accumulators live in TMEM.
 //
 // The key tiles of all (batch, KV head) units, laid end to end, are cut into one equal range per SM; a CTA
 // works through its range unit by unit. In a CTA:
-//   warp 0      loads the group's rotated queries once (TMA, 128 rows x D, rows past the group zero)
-//   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T and O_j = P_j V_j (as attn_chunk_tc.cu)
+//   warp 0      loads the group's queries once (TMA, 128 rows x D, rows past the group zero; rotated for
+//               TurboQuant, column-permuted for the affine codec, as they are for raw caches)
+//   warp 1      owns TMEM; lane 0 issues S_j = Q' K_j^T (two tiles ahead) and O_j = P_j V_j
 //   warps 4, 5  softmax: thread = query row = TMEM lane 0..63 (a group has at most 64 rows here, and a warp
 //               reaches the TMEM lanes 32 * (warp % 4) ...): scores to probabilities, row sums
 //   warps 8, 9, 12, 13  correction: thread = (query row, half of the dims), folds O_j into the row's
-//               register accumulator (as the correction warps of attn_chunk_tc.cu); warps 12, 13 also
-//               keep the running row maxima (they wait most of a step for the O product anyway)
+//               register accumulator; warps 12, 13 also keep the running row maxima (they wait most of a
+//               step for the O product anyway)
 //   warps 2, 6, 10, 14 (keys) and 3, 7, 11, 15 (values)  row writers: thread = key row of the tile; the
-//               row's packed indices and norm are copied one tile ahead into shared memory (cp.async by
-//               the thread itself), then looked up, multiplied by the norm and written as the f16 row of
-//               the swizzled K / V tile the tensor cores read
+//               row's packed codes and norm (affine: scales and biases) of the NEXT tile are prefetched
+//               into registers while this one is decoded and written as the f16 row of the swizzled K / V
+//               tile the tensor cores read. Raw caches: lane 0 of warps 2 and 3 issue tiled TMA loads instead.
 // 16 warps leave a thread 128 registers, which is why a correction thread holds half a row.
-// Key and value centroids come from lane-replicated tables of index PAIRS (conflict-free whatever the
-// indices). The probabilities never visit shared memory: the softmax warps store P_j into TMEM over the
-// scores they came from, and the O product reads it there as its A operand.
+// TurboQuant centroids come from lane-replicated tables of index PAIRS (conflict-free whatever the
+// indices); affine codes become f16 by a mask and one fma. The probabilities never visit shared memory:
+// the softmax warps store P_j into TMEM columns of its own, and the O product reads it there as its A operand.
 // Keys past T are written as zero rows, so masked probabilities never meet a non-finite value.
 //
 // A unit cut by a CTA boundary: every piece writes its rows un-normalised with (max, sum); a merge kernel
-// combines them. The outputs are rows in the rotated basis (f16); the caller rotates them back.
+// combines them. TurboQuant outputs are rows in the rotated basis (f16); the caller rotates them back.
 // Every wait is bounded; a wait that runs out sets the device status word, the CTA drains and frees
 // its TMEM.
 #include <atomic>
