@@ -161,7 +161,6 @@ attn_turbo_v4_kernel(const __grid_constant__ TurboV4Params p) {
     constexpr int K_TILE = V4_TILE * KW * 4, V_TILE = V4_TILE * V4_VW * 4, N_TILE = V4_TILE * 4;
     constexpr int STAGE_BYTES = K_TILE + V_TILE + 2 * N_TILE;
     static_assert(K_TILE % 16 == 0 && STAGE_BYTES % 128 == 0, "bulk copies need 16-byte multiples");
-    constexpr int CT = V4_WARPS * 32;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const FlatPlan &fp = p.flat;
