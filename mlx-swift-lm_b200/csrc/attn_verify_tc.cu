@@ -126,6 +126,14 @@ __host__ __device__ constexpr int affine_dim_of(int pos, int bits) {
 __host__ __device__ constexpr int affine_pos_of(int dim, int bits) {
     return bits == 4 ? (dim & ~7) | (2 * (dim & 3) + ((dim >> 2) & 1)) : (dim & ~3) | ((dim & 1) << 1) | ((dim >> 1) & 1);
 }
+constexpr bool affine_orders_invert(int bits) {
+    for (int i = 0; i < 16; ++i)
+        if (affine_pos_of(affine_dim_of(i, bits), bits) != i || affine_dim_of(affine_pos_of(i, bits), bits) != i) return false;
+    return true;
+}
+static_assert(affine_orders_invert(4) && affine_orders_invert(8), "affine_pos_of must undo affine_dim_of");
+static_assert(affine_dim_of(1, 4) == 4 && affine_dim_of(2, 4) == 1 && affine_dim_of(1, 8) == 2 && affine_dim_of(2, 8) == 1,
+              "column order of the affine codec: nibbles (i, i + 4) and bytes (i, i + 2) come out as pairs");
 
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     uint32_t r;
