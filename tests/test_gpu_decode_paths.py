@@ -337,3 +337,47 @@ def test_raw_cache_verify_rounds_run_on_the_tensor_core_verify_kernel(kvc, oracl
         assert max_abs_diff(out, ref) <= TOL[dtype], f"round {rnd}"
         assert g.trim(max(L - 1, 0)) == o.trim(max(L - 1, 0))
     assert kvc.lib().kvc_device_status() == 0
+
+
+def test_verify_rounds_agree_with_the_tensor_core_verify_kernel_switched_off(tmp_path):
+    """The same verify rounds (TurboQuant K4/V4 and K3/V4, affine 4-bit, raw bf16) with the tcgen05 verify
+    kernel and, in a child process with KVC_VERIFY_TC=0, on the kernels behind it (eight-row units on the
+    decode kernels, the mma.sync chunk kernel): outputs agree within the attention tolerance and the
+    trace names the path that ran."""
+    code = r"""
+import os, sys, torch
+sys.path.insert(0, os.path.join(%r, "mlx-swift-lm_b200", "python"))
+sys.path.insert(0, os.path.join(%r, "tests"))
+import kvcache_b200 as kvc
+from helpers import seeded
+dev = torch.device("cuda:0")
+B, Hq, Hkv, D, P, L = 2, 16, 2, 128, 700, 6
+dt = torch.bfloat16
+outs = []
+for kind in ("k4v4", "k3v4", "affine4", "raw"):
+    if kind == "affine4": c = kvc.QuantizedKVCache(64, 4)
+    elif kind == "raw": c = kvc.KVCacheSimple()
+    else: c = kvc.TurboQuantKVCache(bits=4, key_bits=4 if kind == "k4v4" else 3, value_bits=4)
+    k, v = seeded((B, Hkv, P, D), 1, dt).to(dev), seeded((B, Hkv, P, D), 2, dt).to(dev)
+    if kind == "affine4": c.update_quantized(k, v)
+    elif kind == "raw": c.update(k, v)
+    else: c.encode_new_token(k, v)
+    q = seeded((B, Hq, L, D), 3, dt).to(dev)
+    k1, v1 = seeded((B, Hkv, L, D), 4, dt).to(dev), seeded((B, Hkv, L, D), 5, dt).to(dev)
+    outs.append(c.attention(q, k1, v1, D ** -0.5, "causal").float().cpu())
+torch.cuda.synchronize()
+assert kvc.lib().kvc_device_status() == 0
+torch.save(outs, sys.argv[1])
+""" % (ROOT, ROOT)
+    results, traces = [], []
+    for switch in ("1", "0"):
+        env = dict(os.environ)
+        env["KVC_VERIFY_TC"] = switch
+        env["KVC_TRACE_DISPATCH"] = "1"
+        f = str(tmp_path / f"verify_{switch}.pt")
+        r = subprocess.run([sys.executable, "-c", code, f], check=True, env=env, timeout=300, capture_output=True, text=True)
+        results.append(torch.load(f))
+        traces.append(r.stderr)
+    assert traces[0].count("verify_tc") >= 4 and "verify_tc" not in traces[1]
+    for a, b in zip(*results):
+        assert float((a - b).abs().max()) <= 2e-2
